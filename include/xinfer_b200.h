@@ -1,0 +1,197 @@
+/* C-ABI of libxinfer_b200.so: the speculative-decode hot path of xInfer on NVIDIA B200 (sm_100a).
+ *
+ * Plain pointers and sizes only.  Every compute entry point takes a CUDA stream where the reference
+ * takes `sycl::queue&`, raw DEVICE pointers owned by the caller (row-major, no strides) exactly as the
+ * reference's ops do, and returns an int status instead of throwing (0 = ok).  Entry points are
+ * asynchronous on the stream unless stated otherwise.  One stream per device at a time: the library
+ * keeps per-device scratch that concurrent launches on different streams would share, which mirrors
+ * the reference's single in-order queue (src/core/device.cpp:54-58).
+ *
+ * Each declaration names the reference interface it replaces (path within the reference project).
+ */
+#ifndef XINFER_B200_H_
+#define XINFER_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define XINFER_EXPORT __attribute__((visibility("default")))
+
+typedef void* xinfer_stream_t; /* a cudaStream_t; NULL is the default stream */
+
+/* ---- status codes ------------------------------------------------------------------------------ */
+enum {
+    XINFER_OK = 0,
+    XINFER_NOOP_INVALID_SHAPE = 1,   /* the reference returns silently (src/ops/linear.cpp:176,359); so do
+                                        we, but the caller is told */
+    XINFER_ERR_CUDA = -1,            /* a CUDA runtime call failed; see xinfer_last_cuda_error() */
+    XINFER_ERR_INVALID_ARGUMENT = -2,/* std::invalid_argument in the reference */
+    XINFER_ERR_OUT_OF_MEMORY = -3,   /* std::bad_alloc in the reference */
+    XINFER_ERR_CONTRACT = -4,        /* std::logic_error in the reference (fail-loud accounting) */
+    XINFER_ERR_DEVICE_TIMEOUT = -5,  /* a bounded device-side wait gave up (see xinfer_device_status) */
+    XINFER_ERR_NO_DEVICE = -6        /* no CUDA device / sm_100a code cannot run here */
+};
+
+/* ---- library / device set-up ------------------------------------------------------------------- */
+/* Allocates this device's scratch (split-K partials, tile counters, sampling partials, status word).
+ * Called implicitly by the first compute call on a device; call it explicitly before any stream
+ * capture, because it allocates.  No counterpart in the reference (SYCL USM is allocated per call there). */
+XINFER_EXPORT int xinfer_b200_init(int device);
+/* 0 when no bounded device-side wait has given up on `device` since the last call, else the code. */
+XINFER_EXPORT int xinfer_device_status(int device);
+XINFER_EXPORT const char* xinfer_last_cuda_error(void);
+XINFER_EXPORT const char* xinfer_b200_version(void);
+/* Which kernel family the last linear call on this thread used: 0 none, 1 tcgen05, 2 CUDA cores. */
+XINFER_EXPORT int xinfer_last_linear_path(void);
+/* Force a kernel family for the linear entry points: 0 = automatic, 1 = tcgen05 when eligible
+ * (default for fp16 activations), 2 = CUDA cores only.  For measurements and tests. */
+XINFER_EXPORT void xinfer_set_linear_path(int path);
+
+/* ---- INT4-G128-SYM W4A16 linear:  Y[M,N] = X[M,K] * W^T + bias ---------------------------------
+ * W_int4  [N][K/2] bytes, low nibble = even k, two's-complement int4
+ * scales  [N][K/group_size] fp16
+ * bias    [N] fp32 or NULL
+ * Replaces xinfer::ops::linear_int4, src/ops/linear.h:30-63 (impl src/ops/linear.cpp:165-348,
+ * split-K variant :33-163). */
+XINFER_EXPORT int xinfer_linear_int4_f16f16(xinfer_stream_t s, void* Y_f16, const void* X_f16, const uint8_t* W_int4,
+                                            const void* scales_f16, const float* bias, int64_t M, int64_t N,
+                                            int64_t K, int group_size);
+XINFER_EXPORT int xinfer_linear_int4_f16f32(xinfer_stream_t s, float* Y, const void* X_f16, const uint8_t* W_int4,
+                                            const void* scales_f16, const float* bias, int64_t M, int64_t N,
+                                            int64_t K, int group_size);
+XINFER_EXPORT int xinfer_linear_int4_f32f32(xinfer_stream_t s, float* Y, const float* X, const uint8_t* W_int4,
+                                            const void* scales_f16, const float* bias, int64_t M, int64_t N,
+                                            int64_t K, int group_size);
+
+/* Up to 4 projections sharing X and K.  Replaces xinfer::ops::linear_int4_fused and
+ * FusedProjectionDesc / FusedProjectionDescFP32, src/ops/linear.h:66-111 (impl src/ops/linear.cpp:351-498).
+ * num_descs outside [1,4] is a no-op as in the reference (src/ops/linear.cpp:359). */
+typedef struct xinfer_fused_desc {
+    void* Y;                /* [M][N] fp16 (or fp32 for the _f32 entry point) */
+    const uint8_t* W_int4;  /* [N][K/2] */
+    const void* scales;     /* [N][K/group_size] fp16 */
+    const float* bias;      /* [N] or NULL */
+    int64_t N;
+} xinfer_fused_desc;
+XINFER_EXPORT int xinfer_linear_int4_fused_f16(xinfer_stream_t s, const void* X_f16, const xinfer_fused_desc* descs,
+                                               int num_descs, int64_t M, int64_t K, int group_size);
+XINFER_EXPORT int xinfer_linear_int4_fused_f32(xinfer_stream_t s, const float* X, const xinfer_fused_desc* descs,
+                                               int num_descs, int64_t M, int64_t K, int group_size);
+
+/* Y[m,n] = silu(gate . x) * (up . x); gate and up never reach memory.  Replaces
+ * xinfer::ops::mlp_gate_up_swiglu_int4, src/ops/linear.h:117-139 (impl src/ops/linear.cpp:501-632). */
+XINFER_EXPORT int xinfer_mlp_gate_up_swiglu_int4_f16(xinfer_stream_t s, void* Y_f16, const void* X_f16,
+                                                     const uint8_t* W_gate, const void* scales_gate,
+                                                     const uint8_t* W_up, const void* scales_up, int64_t M,
+                                                     int64_t N, int64_t K, int group_size);
+XINFER_EXPORT int xinfer_mlp_gate_up_swiglu_int4_f32(xinfer_stream_t s, float* Y, const float* X,
+                                                     const uint8_t* W_gate, const void* scales_gate,
+                                                     const uint8_t* W_up, const void* scales_up, int64_t M,
+                                                     int64_t N, int64_t K, int group_size);
+
+/* Column-sliced variant for N-split tensor parallelism: the output row stride `ldy` (elements) may
+ * exceed N so that a rank writes its slice of a wider activation.  No counterpart in the reference
+ * (it has no multi-GPU code). */
+XINFER_EXPORT int xinfer_linear_int4_f16f16_ld(xinfer_stream_t s, void* Y_f16, int64_t ldy, const void* X_f16,
+                                               const uint8_t* W_int4, const void* scales_f16, const float* bias,
+                                               int64_t M, int64_t N, int64_t K, int group_size);
+
+/* ---- sampling ---------------------------------------------------------------------------------- */
+/* Replaces xinfer::ops::argmax_scratch_size, src/ops/sampling.h:11-15. */
+XINFER_EXPORT size_t xinfer_argmax_scratch_size(int64_t vocab_size);
+/* Synchronous greedy argmax of one fp32 logit row on the device; ties -> lowest index; vocab <= 0 or
+ * NULL -> 0.  partial_max / partial_idx are optional caller scratch (device or managed memory, at
+ * least xinfer_argmax_scratch_size entries).  Replaces xinfer::ops::argmax, src/ops/sampling.h:17-25. */
+XINFER_EXPORT int64_t xinfer_argmax(xinfer_stream_t s, const float* logits, int64_t vocab_size, float* partial_max,
+                                    int64_t* partial_idx);
+/* Asynchronous, batched, result stays on the device: out_dev[r] = argmax(logits[r*row_stride ..]).
+ * The graph-capturable form of the same op (the reference's argmax blocks the host,
+ * src/ops/sampling.cpp:73). */
+XINFER_EXPORT int xinfer_argmax_rows(xinfer_stream_t s, const float* logits, int64_t row_stride, int64_t rows,
+                                     int64_t vocab_size, int64_t* out_dev);
+
+/* POD form of xinfer::ops::SpeculativeAcceptanceResult, src/ops/sampling.h:27-36. */
+#define XINFER_MAX_DRAFT_TOKENS 64
+typedef struct xinfer_accept_result {
+    int64_t accepted_tokens[XINFER_MAX_DRAFT_TOKENS];
+    int64_t bonus_or_resampled_token; /* -1 for empty / invalid input */
+    int64_t rejected_token;           /* -1 when none */
+    int64_t num_accepted;
+    int64_t num_rejected;
+    int64_t num_resampled;
+    int64_t num_remaining;
+    int32_t has_rejected_token;
+    int32_t reserved;
+} xinfer_accept_result;
+
+/* Synchronous.  draft_tokens / draft_probs / rand_uniform are HOST pointers, target_logits is a DEVICE
+ * pointer [num_draft_tokens][vocab_size] fp32, as in the reference.  draft_probs == NULL selects the
+ * greedy rule.  Returns XINFER_ERR_CONTRACT where the reference throws std::logic_error.
+ * Replaces xinfer::ops::speculative_accept_reject, src/ops/sampling.h:42-49 (impl sampling.cpp:94-199). */
+XINFER_EXPORT int xinfer_speculative_accept_reject(xinfer_stream_t s, const int64_t* draft_tokens,
+                                                   size_t num_draft_tokens, const float* target_logits,
+                                                   int64_t vocab_size, const float* draft_probs,
+                                                   const float* rand_uniform, xinfer_accept_result* out);
+
+/* Device-side, batched, asynchronous form for `batch` independent sequences: all pointers are DEVICE
+ * pointers.  Sequence b owns logit rows b*rows_per_seq + i (row stride `row_stride` floats), verifies
+ * draft token i against row i for i < num_draft, and on full acceptance takes its bonus token from row
+ * `bonus_row` (num_draft-1 reproduces the reference; num_draft is the (k+1)-row convention).
+ * Logits are multiplied by inv_temperature before the stochastic rule (1.0 reproduces the reference;
+ * the reference has no temperature, src/runtime/engine.cpp:279-303).  out_dev: one record per sequence. */
+typedef struct xinfer_accept_record {
+    int64_t bonus_or_resampled_token;
+    int64_t rejected_token;
+    int32_t num_accepted;
+    int32_t num_rejected;
+    int32_t num_resampled;
+    int32_t num_remaining;
+    int32_t has_rejected_token;
+    int32_t reserved;
+} xinfer_accept_record;
+XINFER_EXPORT int xinfer_speculative_accept_reject_batched(xinfer_stream_t s, const int64_t* draft_tokens_dev,
+                                                           const float* target_logits_dev, int64_t row_stride,
+                                                           int64_t vocab_size, const float* draft_probs_dev,
+                                                           const float* rand_uniform_dev, float inv_temperature,
+                                                           int batch, int num_draft, int rows_per_seq, int bonus_row,
+                                                           xinfer_accept_record* out_dev);
+
+/* Philox4x32-10 uniforms in [0,1): out[i] = (word(i&3) of block(i>>2) >> 8) * 2^-24 with counter
+ * {lo(i>>2), hi(i>>2), lo(subsequence), hi(subsequence)} and key {lo(seed), hi(seed)}.  No counterpart
+ * in the reference (its acceptance op takes caller-supplied uniforms). */
+XINFER_EXPORT int xinfer_philox_uniform(xinfer_stream_t s, float* out_dev, int64_t n, uint64_t seed,
+                                        uint64_t subsequence);
+
+/* ---- device arena ------------------------------------------------------------------------------
+ * cudaMalloc-backed bump allocator.  Replaces xinfer::core::DeviceArena, src/core/arena.h:14-66
+ * (impl src/core/arena.cpp:84-139): 64-byte default alignment, allocate(0) -> NULL, overflow ->
+ * XINFER_ERR_OUT_OF_MEMORY (std::bad_alloc there), persistent allocations survive reset(), one
+ * persistent buffer that refuses to grow (XINFER_ERR_INVALID_ARGUMENT). */
+typedef struct xinfer_arena xinfer_arena;
+XINFER_EXPORT int xinfer_arena_create(size_t capacity_bytes, size_t default_alignment, xinfer_arena** out);
+XINFER_EXPORT void xinfer_arena_destroy(xinfer_arena* a);
+XINFER_EXPORT int xinfer_arena_allocate(xinfer_arena* a, size_t bytes, size_t alignment, void** out);
+XINFER_EXPORT int xinfer_arena_allocate_persistent(xinfer_arena* a, size_t bytes, size_t alignment, void** out);
+XINFER_EXPORT int xinfer_arena_persistent_buffer(xinfer_arena* a, size_t bytes, size_t alignment, void** out);
+XINFER_EXPORT void xinfer_arena_reset(xinfer_arena* a);
+XINFER_EXPORT size_t xinfer_arena_capacity(const xinfer_arena* a);
+XINFER_EXPORT size_t xinfer_arena_allocated_bytes(const xinfer_arena* a);
+XINFER_EXPORT size_t xinfer_arena_remaining_bytes(const xinfer_arena* a);
+XINFER_EXPORT size_t xinfer_arena_peak_allocated_bytes(const xinfer_arena* a);
+XINFER_EXPORT void* xinfer_arena_base_ptr(xinfer_arena* a);
+
+/* ---- artifact checksum (kept unchanged) -------------------------------------------------------
+ * The two exports of the reference's xinfer_artifact_c library, src/artifact/c_api.h:12-20:
+ * CRC-64 with reflected polynomial 0xC96C5795D7870F42, init and xor-out all ones; NULL or empty -> 0;
+ * file variant reads at most max_bytes (0 = whole file), unreadable file -> 0. */
+XINFER_EXPORT uint64_t xinfer_crc64(const void* data, size_t length);
+XINFER_EXPORT uint64_t xinfer_crc64_file(const char* filepath, uint64_t max_bytes);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* XINFER_B200_H_ */

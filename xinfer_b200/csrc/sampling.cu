@@ -1,0 +1,315 @@
+// Greedy argmax and speculative acceptance on the device.
+//
+// Contracts follow the reference:
+//   argmax                      src/ops/sampling.cpp:12-92   strict '>' everywhere, so the lowest index
+//                               of a tie wins; vocab <= 0 or null -> 0; vocab == 1 -> 0
+//   speculative_accept_reject   src/ops/sampling.cpp:94-199  greedy rule, stochastic rule
+//                               r < p_target / p_draft with p_target the softmax probability of the
+//                               draft token, first rejection stops the scan and the replacement is the
+//                               target's argmax at that row; all accepted -> bonus = argmax of a bonus row
+// The reference walks the rows on the host with one argmax launch, one synchronisation and (in the
+// stochastic branch) one device-to-host copy of the whole logit row per draft token.  Here one pass
+// over the logits produces, per (row, chunk), the maximum, its lowest index, and the chunk's
+// sum of exp(l * inv_temperature - chunk_max); a second tiny kernel merges the chunks per row
+// (online-softmax merge), evaluates p_target and runs the accept scan for every sequence of the batch.
+// Nothing returns to the host until the caller asks for the result.
+#include <cuda_runtime.h>
+#include <math.h>
+#include <stdint.h>
+
+#include "sampling.h"
+
+namespace xb {
+
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kChunk = 4096;  // logits per block: 256 threads x 4 float4
+
+struct Partial {
+    float max_raw;   // maximum raw logit of the chunk
+    int idx;         // its lowest index (global)
+    float max_scaled;
+    float sum_exp;   // sum over the chunk of exp(l * inv_t - max_scaled)
+};
+
+__device__ __forceinline__ void better(float& v, int& i, float ov, int oi) {
+    // strict '>' on the value; on equal values the lower index wins; an empty candidate never wins
+    if (oi < 0) return;
+    if (i < 0 || ov > v || (ov == v && oi < i)) {
+        v = ov;
+        i = oi;
+    }
+}
+
+// grid = (chunks, rows).  `row_stride` is the distance between logit rows in floats.
+__global__ void __launch_bounds__(kThreads) logits_partials_kernel(const float* __restrict__ logits, long long row_stride,
+                                                                   int vocab, float inv_t, int want_sum,
+                                                                   Partial* __restrict__ out, int chunks) {
+    const int row = blockIdx.y;
+    const int chunk = blockIdx.x;
+    const float* l = logits + static_cast<long long>(row) * row_stride;
+    const int base = chunk * kChunk;
+    const int end = min(vocab, base + kChunk);
+
+    float vals[16];
+    float best = -INFINITY;
+    int best_i = -1;
+    const bool vec_ok = ((reinterpret_cast<uintptr_t>(l) & 15) == 0);
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+        const int i0 = base + (r * kThreads + threadIdx.x) * 4;
+        if (vec_ok && i0 + 3 < end) {
+            const float4 v = __ldg(reinterpret_cast<const float4*>(l + i0));
+            vals[r * 4 + 0] = v.x; vals[r * 4 + 1] = v.y; vals[r * 4 + 2] = v.z; vals[r * 4 + 3] = v.w;
+        } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) vals[r * 4 + j] = (i0 + j < end) ? __ldg(l + i0 + j) : -INFINITY;
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int idx = i0 + j;
+            if (idx < end) {
+                if (best_i < 0 || vals[r * 4 + j] > best) { best = vals[r * 4 + j]; best_i = idx; }
+            }
+        }
+    }
+    // block argmax (value, lowest index)
+    __shared__ float s_v[kThreads / 32];
+    __shared__ int s_i[kThreads / 32];
+    __shared__ float s_f[kThreads / 32];
+    __shared__ float s_bcast;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, off);
+        const int oi = __shfl_xor_sync(0xffffffffu, best_i, off);
+        better(best, best_i, ov, oi);
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) { s_v[warp] = best; s_i[warp] = best_i; }
+    __syncthreads();
+    if (warp == 0) {
+        float v = (lane < kThreads / 32) ? s_v[lane] : -INFINITY;
+        int i = (lane < kThreads / 32) ? s_i[lane] : -1;
+#pragma unroll
+        for (int off = 4; off > 0; off >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, v, off);
+            const int oi = __shfl_xor_sync(0xffffffffu, i, off);
+            better(v, i, ov, oi);
+        }
+        if (lane == 0) { s_v[0] = v; s_i[0] = i; s_bcast = v * inv_t; }
+    }
+    __syncthreads();
+    Partial res;
+    res.max_raw = s_v[0];
+    res.idx = s_i[0];
+    res.max_scaled = 0.f;
+    res.sum_exp = 0.f;
+    if (want_sum) {
+        // maximum of the scaled logits: scaling by a positive factor is monotone but may round two
+        // values together, so take the maximum of the scaled values themselves
+        float ms = -INFINITY;
+#pragma unroll
+        for (int r = 0; r < 16; ++r) {
+            const int idx = base + ((r >> 2) * kThreads + threadIdx.x) * 4 + (r & 3);
+            if (idx < end) ms = fmaxf(ms, vals[r] * inv_t);
+        }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) ms = fmaxf(ms, __shfl_xor_sync(0xffffffffu, ms, off));
+        __syncthreads();
+        if (lane == 0) s_f[warp] = ms;
+        __syncthreads();
+        ms = s_f[0];
+#pragma unroll
+        for (int w = 1; w < kThreads / 32; ++w) ms = fmaxf(ms, s_f[w]);
+        float se = 0.f;
+#pragma unroll
+        for (int r = 0; r < 16; ++r) {
+            const int idx = base + ((r >> 2) * kThreads + threadIdx.x) * 4 + (r & 3);
+            if (idx < end) se += expf(vals[r] * inv_t - ms);
+        }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) se += __shfl_xor_sync(0xffffffffu, se, off);
+        __syncthreads();
+        if (lane == 0) s_f[warp] = se;
+        __syncthreads();
+        se = 0.f;
+#pragma unroll
+        for (int w = 0; w < kThreads / 32; ++w) se += s_f[w];
+        res.max_scaled = ms;
+        res.sum_exp = se;
+    }
+    if (threadIdx.x == 0) out[static_cast<long long>(row) * chunks + chunk] = res;
+}
+
+// Optional mirror of the reference's per-256 partial arrays (src/ops/sampling.cpp:35-73): when the
+// caller passes scratch, stage 1 results are also published there, one entry per chunk.
+__global__ void publish_partials_kernel(const Partial* in, int chunks, float* partial_max, long long* partial_idx) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < chunks) {
+        partial_max[i] = in[i].max_raw;
+        partial_idx[i] = in[i].idx;
+    }
+}
+
+__device__ __forceinline__ void merge_row(const Partial* p, int chunks, int lane, float& mx, int& idx, float& ms,
+                                          float& se) {
+    // one warp merges the chunk partials of one row
+    mx = -INFINITY; idx = -1; ms = -INFINITY; se = 0.f;
+    for (int c = lane; c < chunks; c += 32) {
+        const Partial q = p[c];
+        better(mx, idx, q.max_raw, q.idx);
+        if (q.max_scaled > ms) { se = se * expf(ms - q.max_scaled) + q.sum_exp; ms = q.max_scaled; }
+        else if (q.sum_exp > 0.f) se += q.sum_exp * expf(q.max_scaled - ms);
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, mx, off);
+        const int oi = __shfl_xor_sync(0xffffffffu, idx, off);
+        better(mx, idx, ov, oi);
+        const float oms = __shfl_xor_sync(0xffffffffu, ms, off);
+        const float ose = __shfl_xor_sync(0xffffffffu, se, off);
+        const float nm = fmaxf(ms, oms);
+        float a = (ms == -INFINITY) ? 0.f : se * expf(ms - nm);
+        float b = (oms == -INFINITY) ? 0.f : ose * expf(oms - nm);
+        se = a + b;
+        ms = nm;
+    }
+}
+
+__global__ void argmax_finish_kernel(const Partial* partials, int chunks, long long* out) {
+    const int row = blockIdx.x;
+    float mx, ms, se;
+    int idx;
+    merge_row(partials + static_cast<long long>(row) * chunks, chunks, threadIdx.x, mx, idx, ms, se);
+    if (threadIdx.x == 0) out[row] = idx < 0 ? 0 : idx;
+}
+
+// One warp per sequence.  Rows of sequence b are b * rows_per_seq + i.
+__global__ void accept_finish_kernel(const Partial* partials, int chunks, const float* logits, long long row_stride,
+                                     int vocab, float inv_t, const long long* draft_tokens, const float* draft_probs,
+                                     const float* uniforms, int num_draft, int rows_per_seq, int bonus_row,
+                                     AcceptOut* out) {
+    const int b = blockIdx.x;
+    const int lane = threadIdx.x;
+    AcceptOut r;
+    r.num_accepted = 0;
+    r.bonus_or_resampled_token = -1;
+    r.rejected_token = -1;
+    r.has_rejected_token = 0;
+    r.num_rejected = 0;
+    r.num_resampled = 0;
+    r.num_remaining = 0;
+    bool rejected = false;
+    for (int i = 0; i < num_draft && !rejected; ++i) {
+        const long long row = static_cast<long long>(b) * rows_per_seq + i;
+        float mx, ms, se;
+        int t;
+        merge_row(partials + row * chunks, chunks, lane, mx, t, ms, se);
+        const long long d = draft_tokens[static_cast<long long>(b) * num_draft + i];
+        bool accepted;
+        if (!draft_probs) {
+            accepted = (d == t);
+        } else {
+            const float p_draft = draft_probs[static_cast<long long>(b) * num_draft + i];
+            const float rr = uniforms ? uniforms[static_cast<long long>(b) * num_draft + i] : 0.f;
+            if (p_draft <= 0.f) {
+                accepted = (d == t);
+            } else if (d == t && rr <= 0.f) {
+                accepted = true;
+            } else {
+                float p_target = 0.f;
+                if (d >= 0 && d < vocab && se > 0.f) p_target = expf(logits[row * row_stride + d] * inv_t - ms) / se;
+                accepted = rr < (p_target / p_draft);
+            }
+        }
+        if (accepted) {
+            r.num_accepted++;
+        } else {
+            rejected = true;
+            r.has_rejected_token = 1;
+            r.rejected_token = d;
+            r.num_rejected = 1;
+            r.bonus_or_resampled_token = t;
+            r.num_resampled = 1;
+            r.num_remaining = num_draft - (r.num_accepted + 1);
+        }
+    }
+    if (!rejected) {
+        const long long row = static_cast<long long>(b) * rows_per_seq + bonus_row;
+        float mx, ms, se;
+        int t;
+        merge_row(partials + row * chunks, chunks, lane, mx, t, ms, se);
+        r.bonus_or_resampled_token = t;
+    }
+    if (lane == 0) out[b] = r;
+}
+
+// Philox4x32-10, Salmon et al. SC'11.  Uniform i of (seed, subsequence) is word (i & 3) of the block
+// with counter {lo(i>>2), hi(i>>2), lo(subsequence), hi(subsequence)} and key {lo(seed), hi(seed)},
+// mapped to [0, 1) as (word >> 8) * 2^-24.
+__device__ __forceinline__ void philox4x32_10(uint32_t c[4], uint32_t k0, uint32_t k1) {
+#pragma unroll
+    for (int r = 0; r < 10; ++r) {
+        const uint32_t hi0 = __umulhi(0xD2511F53u, c[0]), lo0 = 0xD2511F53u * c[0];
+        const uint32_t hi1 = __umulhi(0xCD9E8D57u, c[2]), lo1 = 0xCD9E8D57u * c[2];
+        const uint32_t n0 = hi1 ^ c[1] ^ k0, n2 = hi0 ^ c[3] ^ k1;
+        c[0] = n0; c[1] = lo1; c[2] = n2; c[3] = lo0;
+        k0 += 0x9E3779B9u;
+        k1 += 0xBB67AE85u;
+    }
+}
+
+__global__ void philox_uniform_kernel(float* out, long long n, unsigned long long seed, unsigned long long subseq) {
+    const long long blk = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (blk * 4 >= n) return;
+    uint32_t c[4] = {static_cast<uint32_t>(blk), static_cast<uint32_t>(static_cast<unsigned long long>(blk) >> 32),
+                     static_cast<uint32_t>(subseq), static_cast<uint32_t>(subseq >> 32)};
+    philox4x32_10(c, static_cast<uint32_t>(seed), static_cast<uint32_t>(seed >> 32));
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+        if (blk * 4 + j < n) out[blk * 4 + j] = static_cast<float>(c[j] >> 8) * (1.0f / 16777216.0f);
+}
+
+}  // namespace
+
+int sampling_chunks(long long vocab) { return static_cast<int>((vocab + kChunk - 1) / kChunk); }
+size_t sampling_scratch_bytes(long long rows, long long vocab) {
+    return static_cast<size_t>(rows) * sampling_chunks(vocab) * sizeof(Partial);
+}
+
+int argmax_rows(cudaStream_t stream, const float* logits, long long row_stride, int rows, long long vocab,
+                void* scratch, long long* out_dev, float* partial_max, long long* partial_idx) {
+    const int chunks = sampling_chunks(vocab);
+    Partial* part = static_cast<Partial*>(scratch);
+    logits_partials_kernel<<<dim3(chunks, rows), kThreads, 0, stream>>>(logits, row_stride, static_cast<int>(vocab),
+                                                                        1.0f, 0, part, chunks);
+    if (partial_max && partial_idx && rows == 1)
+        publish_partials_kernel<<<(chunks + 127) / 128, 128, 0, stream>>>(part, chunks, partial_max, partial_idx);
+    argmax_finish_kernel<<<rows, 32, 0, stream>>>(part, chunks, out_dev);
+    return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+int accept_reject_batched(cudaStream_t stream, const float* logits, long long row_stride, long long vocab,
+                          float inv_temperature, const long long* draft_tokens, const float* draft_probs,
+                          const float* uniforms, int batch, int num_draft, int rows_per_seq, int bonus_row,
+                          void* scratch, AcceptOut* out_dev) {
+    const int chunks = sampling_chunks(vocab);
+    Partial* part = static_cast<Partial*>(scratch);
+    const int rows = batch * rows_per_seq;
+    logits_partials_kernel<<<dim3(chunks, rows), kThreads, 0, stream>>>(
+        logits, row_stride, static_cast<int>(vocab), inv_temperature, draft_probs ? 1 : 0, part, chunks);
+    accept_finish_kernel<<<batch, 32, 0, stream>>>(part, chunks, logits, row_stride, static_cast<int>(vocab),
+                                                   inv_temperature, draft_tokens, draft_probs, uniforms, num_draft,
+                                                   rows_per_seq, bonus_row, out_dev);
+    return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+int philox_uniform(cudaStream_t stream, float* out, long long n, unsigned long long seed, unsigned long long subseq) {
+    if (n <= 0) return 0;
+    const long long blocks4 = (n + 3) / 4;
+    philox_uniform_kernel<<<static_cast<unsigned>((blocks4 + 127) / 128), 128, 0, stream>>>(out, n, seed, subseq);
+    return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+}  // namespace xb

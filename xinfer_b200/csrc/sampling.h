@@ -1,0 +1,36 @@
+// Internal interface of the sampling / acceptance kernels (sampling.cu).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+namespace xb {
+
+// Device-side form of SpeculativeAcceptanceResult (src/ops/sampling.h:27-36 of the reference); the
+// accepted tokens are the first num_accepted draft tokens and are not repeated here.
+struct AcceptOut {
+    long long bonus_or_resampled_token;
+    long long rejected_token;
+    int num_accepted;
+    int num_rejected;
+    int num_resampled;
+    int num_remaining;
+    int has_rejected_token;
+    int pad;
+};
+
+int sampling_chunks(long long vocab);
+size_t sampling_scratch_bytes(long long rows, long long vocab);
+
+int argmax_rows(cudaStream_t stream, const float* logits, long long row_stride, int rows, long long vocab,
+                void* scratch, long long* out_dev, float* partial_max, long long* partial_idx);
+
+int accept_reject_batched(cudaStream_t stream, const float* logits, long long row_stride, long long vocab,
+                          float inv_temperature, const long long* draft_tokens, const float* draft_probs,
+                          const float* uniforms, int batch, int num_draft, int rows_per_seq, int bonus_row,
+                          void* scratch, AcceptOut* out_dev);
+
+int philox_uniform(cudaStream_t stream, float* out, long long n, unsigned long long seed, unsigned long long subseq);
+
+}  // namespace xb

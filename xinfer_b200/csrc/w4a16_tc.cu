@@ -1,0 +1,562 @@
+// W4A16 skinny GEMM on tcgen05 tensor cores for 1 <= M <= 32 activation rows.
+//
+//   Y[m, n] = sum_g scale[n, g] * ( sum_{k in group g} X[m, k] * q[n, k] )  (+ bias[n])
+//
+// Replaces the Xe2 sub-group kernels of the reference for fp16 activations:
+//   linear_int4                 src/ops/linear.cpp:165-305   (one projection)
+//   splitk_int4_impl            src/ops/linear.cpp:33-163    (small N: K is split across CTAs here)
+//   linear_int4_fused           src/ops/linear.cpp:351-478   (<= 4 projections sharing X)
+//   mlp_gate_up_swiglu_int4     src/ops/linear.cpp:501-602   (gate and up rows paired in one CTA)
+// The weight layout is the reference's own ([N][K/2] bytes, low nibble = even k; [N][K/128] fp16
+// scales), read in place, and the association is the reference's: an fp32 dot of exact integers per
+// 128-k group, then one multiply by the group's scale.
+//
+// Mapping to the hardware.  The weights sit on the MMA's M side: a CTA owns 256 output rows as two
+// 128-row halves, one per consumer warpgroup, and thread t of a warpgroup owns row t of its half.
+// That thread reads its row's packed bytes from the TMA-staged tile (128B-swizzled, conflict free),
+// unpacks them to exact fp16 integers in registers, and writes them with tcgen05.st into TMEM lane
+// t, where they are the A operand (128 x 16 per MMA).  The <= 32 activation rows are the MMA's N
+// side: their K slice arrives by a 3-D TMA load directly in the canonical K-major core-matrix
+// layout and is the B operand from shared memory.  Each 128-k group accumulates into a fresh TMEM
+// tile D[128 x NMMA]; its owner thread reads lane t back (tcgen05.ld) and folds it into fp32
+// register accumulators with its own row's scale.  Nothing about a row ever leaves its thread.
+//
+// The unpack yields k in the order (0,4,1,5,2,6,3,7) inside each 8-k block; the consumer threads
+// permute the staged activations in place to the same order before the MMA reads them.
+//
+// Work is cut stream-K style: the (tile, 256-k stage) units are split evenly over one CTA per SM;
+// a tile finished by several CTAs is summed by the last one to arrive, in CTA order, from fp32
+// partials in a scratch buffer (deterministic, no float atomics).
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <string.h>
+
+#include "ptx_sm100.cuh"
+#include "w4a16.h"
+
+namespace xb {
+
+namespace {
+
+constexpr int kTileRows = 256;
+constexpr int kHalfRows = 128;
+constexpr int kStageK = 256;                                 // weights per row per stage = 2 groups
+constexpr int kStageRowBytes = kStageK / 2;                  // 128 B of packed int4 per row
+constexpr int kWHalfBytes = kHalfRows * kStageRowBytes;      // 16 KiB
+constexpr int kWStageBytes = 2 * kWHalfBytes;                // 32 KiB
+constexpr int kKCoresPerStage = kStageK / 8;                 // 32 sixteen-byte K cores
+constexpr int kConsumerThreads = 256;
+constexpr int kProducerWarp = 8;
+constexpr int kMmaWarp = 9;
+constexpr int kThreads = 320;
+constexpr uint32_t kTmemCols = 512;
+constexpr int kMaxSegs = 4;
+
+template <int NMMA>
+struct Cfg {
+    static constexpr int kXStageBytes = NMMA * kStageK * 2;
+    static constexpr int kStageBytes = kWStageBytes + kXStageBytes;
+    static constexpr int kStages = (NMMA == 32) ? 4 : 5;
+    static constexpr int kXchgBytes = kHalfRows * NMMA * 4;
+    static constexpr int kCtrlBytes = 512;
+    static constexpr int kSmemBytes = kStages * kStageBytes + kXchgBytes + kCtrlBytes + 1024;  // + align slack
+};
+
+struct Seg {
+    const __half* scales;
+    const float* bias;
+    void* y;
+    long long ldy;  // row stride of y in elements
+    int n;          // output features of this projection
+    int tile_begin; // first tile index of this projection
+};
+
+struct Params {
+    CUtensorMap w_map[kMaxSegs];
+    CUtensorMap x_map;
+    Seg seg[kMaxSegs];
+    int num_segs;
+    int swiglu;       // 1: seg[0] = gate, seg[1] = up, one tile = 128 gate rows + the same 128 up rows
+    int m;            // activation rows (<= NMMA)
+    int groups;       // K / 128
+    int stages;       // ceil(groups / 2), stage units per tile
+    int total_tiles;
+    long long total_units;
+    float* workspace; // [ctas][2][NMMA][256] fp32 partials
+    int* counters;    // [total_tiles], zero between launches
+    int* status;      // device status word
+};
+
+struct Ctrl {
+    uint64_t full[8];
+    uint64_t empty[8];
+    uint64_t x_ready[8];
+    uint64_t a_full[2][2];
+    uint64_t d_full[2][2];
+    uint32_t tmem_base;
+    int abort_flag;
+    int is_last;
+};
+static_assert(sizeof(Ctrl) <= 512, "control block");
+
+__device__ __forceinline__ long long unit_begin(long long cta, long long total, long long ctas) {
+    return cta * total / ctas;
+}
+__device__ __forceinline__ int unit_owner(long long unit, long long total, long long ctas) {
+    // the CTA c with unit_begin(c) <= unit < unit_begin(c + 1)
+    return static_cast<int>(((unit + 1) * ctas + total - 1) / total - 1);
+}
+
+template <typename OutT>
+__device__ __forceinline__ void store_out(OutT* p, float v);
+template <>
+__device__ __forceinline__ void store_out<float>(float* p, float v) { *p = v; }
+template <>
+__device__ __forceinline__ void store_out<__half>(__half* p, float v) { *p = __float2half_rn(v); }
+
+struct TileInfo {
+    int seg;
+    int row0;  // first output row of the tile within its projection
+};
+
+__device__ __forceinline__ TileInfo locate_tile(const Params& p, int tile) {
+    TileInfo ti;
+    ti.seg = 0;
+    if (!p.swiglu) {
+#pragma unroll
+        for (int i = 1; i < kMaxSegs; ++i)
+            if (i < p.num_segs && tile >= p.seg[i].tile_begin) ti.seg = i;
+    }
+    ti.row0 = (tile - p.seg[ti.seg].tile_begin) * (p.swiglu ? kHalfRows : kTileRows);
+    return ti;
+}
+
+template <int NMMA, typename OutT>
+__global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_constant__ Params p) {
+    using C = Cfg<NMMA>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* xchg_raw = smem + C::kStages * C::kStageBytes;
+    Ctrl* ctrl = reinterpret_cast<Ctrl*>(xchg_raw + C::kXchgBytes);
+    float* xchg = reinterpret_cast<float*>(xchg_raw);
+
+    const int tid = threadIdx.x;
+    const int warp = tid >> 5;
+    const int lane = tid & 31;
+    volatile int* abort_flag = &ctrl->abort_flag;
+
+    if (tid == 0) {
+        for (int i = 0; i < C::kStages; ++i) {
+            mbar_init(smem_u32(&ctrl->full[i]), 1);
+            mbar_init(smem_u32(&ctrl->empty[i]), kConsumerThreads);
+            mbar_init(smem_u32(&ctrl->x_ready[i]), kConsumerThreads);
+        }
+        for (int w = 0; w < 2; ++w)
+            for (int b = 0; b < 2; ++b) {
+                mbar_init(smem_u32(&ctrl->a_full[w][b]), kHalfRows);
+                mbar_init(smem_u32(&ctrl->d_full[w][b]), 1);
+            }
+        ctrl->abort_flag = 0;
+        ctrl->is_last = 0;
+        mbar_fence_init();
+    }
+    if (warp == kMmaWarp) {
+        tmem_alloc(smem_u32(&ctrl->tmem_base), kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = ctrl->tmem_base;
+
+    const long long ctas = gridDim.x;
+    const long long u_begin = unit_begin(blockIdx.x, p.total_units, ctas);
+    const long long u_end = unit_begin(blockIdx.x + 1, p.total_units, ctas);
+    const int S = p.stages;
+
+    if (warp == kProducerWarp) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            for (int i = 0; i < kMaxSegs; ++i)
+                if (i < (p.swiglu ? 2 : p.num_segs)) tma_prefetch_desc(&p.w_map[i]);
+            tma_prefetch_desc(&p.x_map);
+            const uint64_t pol_w = l2_policy_evict_first();
+            const uint64_t pol_x = l2_policy_evict_last();
+            uint32_t n = 0;
+            for (long long u = u_begin; u < u_end; ++u, ++n) {
+                const int slot = n % C::kStages;
+                const uint32_t ph = (n / C::kStages) & 1u;
+                if (!mbar_wait(smem_u32(&ctrl->empty[slot]), ph ^ 1u, abort_flag)) break;
+                const int tile = static_cast<int>(u / S);
+                const int s = static_cast<int>(u - static_cast<long long>(tile) * S);
+                const TileInfo ti = locate_tile(p, tile);
+                const uint32_t full = smem_u32(&ctrl->full[slot]);
+                const uint32_t dst = smem_u32(smem + slot * C::kStageBytes);
+                mbar_arrive_expect_tx(full, C::kStageBytes);
+                const int map_b = p.swiglu ? 1 : ti.seg;
+                const int row_b = p.swiglu ? ti.row0 : ti.row0 + kHalfRows;
+                tma_load_2d(dst, &p.w_map[ti.seg], full, s * kStageRowBytes, ti.row0, pol_w);
+                tma_load_2d(dst + kWHalfBytes, &p.w_map[map_b], full, s * kStageRowBytes, row_b, pol_w);
+                tma_load_3d(dst + kWStageBytes, &p.x_map, full, 0, 0, s * kKCoresPerStage, pol_x);
+            }
+            if (*abort_flag) {
+                // give the copies still in flight a bounded chance to land before the CTA exits
+                for (int i = 0; i < C::kStages && i < static_cast<int>(n); ++i) {
+                    const uint32_t k = n - 1 - i;
+                    const long long t0 = clock64();
+                    while (!mbar_try_wait(smem_u32(&ctrl->full[k % C::kStages]), (k / C::kStages) & 1u) &&
+                           clock64() - t0 < kWaitLimitClocks / 8) {
+                    }
+                }
+            }
+        }
+    } else if (warp == kMmaWarp) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_idesc_f16_f32(128, NMMA);
+            constexpr uint32_t lbo = NMMA * 16;  // between the two K cores of one step
+            constexpr uint32_t sbo = 128;        // between 8-row groups
+            uint32_t n = 0, gc = 0;
+            bool ok = true;
+            for (long long u = u_begin; u < u_end && ok; ++u, ++n) {
+                const int slot = n % C::kStages;
+                const uint32_t ph = (n / C::kStages) & 1u;
+                const int s = static_cast<int>(u % S);
+                const int groups = min(2, p.groups - 2 * s);
+                if (!mbar_wait(smem_u32(&ctrl->x_ready[slot]), ph, abort_flag)) break;
+                const uint32_t xbase = smem_u32(smem + slot * C::kStageBytes + kWStageBytes);
+                for (int gi = 0; gi < groups && ok; ++gi, ++gc) {
+                    const uint32_t buf = gc & 1u;
+                    const uint32_t aph = (gc >> 1) & 1u;
+#pragma unroll
+                    for (int w = 0; w < 2; ++w) {
+                        if (!mbar_wait(smem_u32(&ctrl->a_full[w][buf]), aph, abort_flag)) { ok = false; break; }
+                        tc_fence_after_sync();
+                        const uint32_t a_t = tmem_base + w * 128 + buf * 64;
+                        const uint32_t d_t = tmem_base + 256 + w * 64 + buf * 32;
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            const uint64_t bdesc =
+                                umma_smem_desc_kmajor_noswizzle(xbase + (gi * 16 + i * 2) * lbo, lbo, sbo);
+                            umma_ts_f16(d_t, a_t + i * 8, bdesc, idesc, i > 0 ? 1u : 0u);
+                        }
+                        umma_commit(smem_u32(&ctrl->d_full[w][buf]));
+                    }
+                }
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ consumers: unpack, read out, epilogue
+        const int wg = tid >> 7;
+        const int t = tid & 127;
+        const uint32_t lane_sel = static_cast<uint32_t>(((tid >> 5) & 3) * 32) << 16;
+        const uint32_t a_t0 = tmem_base + lane_sel + wg * 128;
+        const uint32_t d_t0 = tmem_base + lane_sel + 256 + wg * 64;
+        const int swz = t & 7;
+
+        float acc[NMMA];
+        uint32_t n = 0, gc = 0;
+        bool ok = true;
+
+        // pending read-out of the previous group
+        bool pend = false;
+        uint32_t pend_buf = 0, pend_ph = 0;
+        int pend_release = -1;
+        float pend_scale = 0.f;
+
+        auto readout = [&]() {
+            if (!mbar_wait(smem_u32(&ctrl->d_full[wg][pend_buf]), pend_ph, abort_flag)) { ok = false; return; }
+            tc_fence_after_sync();
+            uint32_t d[NMMA];
+#pragma unroll
+            for (int c = 0; c < NMMA / 16; ++c) tmem_ld16(d_t0 + pend_buf * 32 + c * 16, d + c * 16);
+            tmem_wait_ld();
+#pragma unroll
+            for (int j = 0; j < NMMA; ++j) acc[j] = fmaf(__uint_as_float(d[j]), pend_scale, acc[j]);
+            if (pend_release >= 0) mbar_arrive(smem_u32(&ctrl->empty[pend_release]));
+            pend = false;
+        };
+
+        long long u = u_begin;
+        while (u < u_end && ok) {
+            const int tile = static_cast<int>(u / S);
+            const int s0 = static_cast<int>(u - static_cast<long long>(tile) * S);
+            const int s1 = static_cast<int>(min(static_cast<long long>(S), s0 + (u_end - u)));
+            const TileInfo ti = locate_tile(p, tile);
+            const Seg& sg = p.seg[p.swiglu ? wg : ti.seg];
+            const int my_row = p.swiglu ? ti.row0 + t : ti.row0 + wg * kHalfRows + t;
+            const bool valid = my_row < sg.n;
+            const __half* my_scales = sg.scales + static_cast<long long>(valid ? my_row : 0) * p.groups;
+
+#pragma unroll
+            for (int j = 0; j < NMMA; ++j) acc[j] = 0.f;
+
+            float sc_cur[2], sc_next[2];
+            sc_next[0] = __half2float(my_scales[2 * s0]);
+            sc_next[1] = (2 * s0 + 1 < p.groups) ? __half2float(my_scales[2 * s0 + 1]) : 0.f;
+
+            for (int s = s0; s < s1 && ok; ++s, ++n) {
+                const int slot = n % C::kStages;
+                const uint32_t ph = (n / C::kStages) & 1u;
+                sc_cur[0] = sc_next[0];
+                sc_cur[1] = sc_next[1];
+                if (s + 1 < s1) {  // scales of the next stage, consumed about one stage later
+                    sc_next[0] = __half2float(my_scales[2 * s + 2]);
+                    sc_next[1] = (2 * s + 3 < p.groups) ? __half2float(my_scales[2 * s + 3]) : 0.f;
+                }
+                if (!mbar_wait(smem_u32(&ctrl->full[slot]), ph, abort_flag)) { ok = false; break; }
+                uint8_t* stage = smem + slot * C::kStageBytes;
+
+                // activations: reorder each 8-k block to (0,4,1,5,2,6,3,7), in place
+                {
+                    uint4* xs = reinterpret_cast<uint4*>(stage + kWStageBytes);
+#pragma unroll
+                    for (int i = 0; i < C::kXStageBytes / 16 / kConsumerThreads; ++i) {
+                        uint4 v = xs[tid + i * kConsumerThreads];
+                        uint4 o;
+                        o.x = prmt(v.x, v.z, 0x5410u);
+                        o.y = prmt(v.x, v.z, 0x7632u);
+                        o.z = prmt(v.y, v.w, 0x5410u);
+                        o.w = prmt(v.y, v.w, 0x7632u);
+                        xs[tid + i * kConsumerThreads] = o;
+                    }
+                    fence_proxy_async_smem();
+                    mbar_arrive(smem_u32(&ctrl->x_ready[slot]));
+                }
+
+                const int groups = min(2, p.groups - 2 * s);
+                const uint8_t* my_w = stage + wg * kWHalfBytes + t * kStageRowBytes;
+                for (int gi = 0; gi < groups && ok; ++gi, ++gc) {
+                    const uint32_t buf = gc & 1u;
+                    uint32_t a[64];
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        const uint4 v = *reinterpret_cast<const uint4*>(my_w + (((gi * 4 + c) ^ swz) << 4));
+                        dequant_word(v.x, a + c * 16 + 0);
+                        dequant_word(v.y, a + c * 16 + 4);
+                        dequant_word(v.z, a + c * 16 + 8);
+                        dequant_word(v.w, a + c * 16 + 12);
+                    }
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) tmem_st16(a_t0 + buf * 64 + c * 16, a + c * 16);
+                    tmem_wait_st();
+                    tc_fence_before_sync();
+                    mbar_arrive(smem_u32(&ctrl->a_full[wg][buf]));
+
+                    if (pend) readout();
+                    pend = true;
+                    pend_buf = buf;
+                    pend_ph = (gc >> 1) & 1u;
+                    pend_scale = valid ? sc_cur[gi] : 0.f;
+                    pend_release = (gi == groups - 1) ? slot : -1;
+                }
+            }
+            if (pend && ok) readout();
+            if (!ok) break;
+
+            // ---------------------------------------------------------------- tile epilogue
+            const bool whole = (s0 == 0 && s1 == S);
+            bool finish = whole;
+            if (!whole) {
+                const int first_tile = static_cast<int>(u_begin / S);
+                const int wslot = blockIdx.x * 2 + (tile == first_tile ? 0 : 1);
+                float* ws = p.workspace + static_cast<long long>(wslot) * (NMMA * kTileRows);
+#pragma unroll
+                for (int j = 0; j < NMMA; ++j) ws[j * kTileRows + tid] = acc[j];
+                __threadfence();
+                named_barrier_sync(1, kConsumerThreads);
+                if (tid == 0) {
+                    const long long t_lo = static_cast<long long>(tile) * S;
+                    const int c_lo = unit_owner(t_lo, p.total_units, ctas);
+                    const int c_hi = unit_owner(t_lo + S - 1, p.total_units, ctas);
+                    const int old = atomicAdd(&p.counters[tile], 1);
+                    ctrl->is_last = (old == c_hi - c_lo) ? 1 : 0;
+                }
+                named_barrier_sync(1, kConsumerThreads);
+                finish = ctrl->is_last != 0;
+                if (finish) {
+                    __threadfence();
+                    const long long t_lo = static_cast<long long>(tile) * S;
+                    const int c_lo = unit_owner(t_lo, p.total_units, ctas);
+                    const int c_hi = unit_owner(t_lo + S - 1, p.total_units, ctas);
+#pragma unroll
+                    for (int j = 0; j < NMMA; ++j) acc[j] = 0.f;
+                    for (int c = c_lo; c <= c_hi; ++c) {  // fixed CTA order: deterministic sum
+                        const int c_first_tile = static_cast<int>(unit_begin(c, p.total_units, ctas) / S);
+                        const float* src = p.workspace +
+                                           static_cast<long long>(c * 2 + (tile == c_first_tile ? 0 : 1)) * (NMMA * kTileRows);
+#pragma unroll
+                        for (int j = 0; j < NMMA; ++j) acc[j] += __ldcg(src + j * kTileRows + tid);
+                    }
+                    if (tid == 0) p.counters[tile] = 0;
+                }
+                named_barrier_sync(1, kConsumerThreads);  // is_last may be rewritten by the next tile
+            }
+            if (finish) {
+                if (p.swiglu) {
+                    if (wg == 1) {
+#pragma unroll
+                        for (int j = 0; j < NMMA; ++j) xchg[j * kHalfRows + t] = acc[j];
+                    }
+                    named_barrier_sync(1, kConsumerThreads);
+                    if (wg == 0 && valid) {
+                        OutT* y = static_cast<OutT*>(p.seg[0].y);
+#pragma unroll
+                        for (int j = 0; j < NMMA; ++j) {
+                            if (j < p.m) {
+                                const float g = acc[j];
+                                const float up = xchg[j * kHalfRows + t];
+                                const float silu = g / (1.0f + expf(-g));
+                                store_out<OutT>(y + static_cast<long long>(j) * p.seg[0].ldy + my_row, silu * up);
+                            }
+                        }
+                    }
+                    named_barrier_sync(1, kConsumerThreads);
+                } else if (valid) {
+                    OutT* y = static_cast<OutT*>(sg.y);
+                    const float b = sg.bias ? sg.bias[my_row] : 0.f;
+#pragma unroll
+                    for (int j = 0; j < NMMA; ++j) {
+                        if (j < p.m) {
+                            const float v = sg.bias ? acc[j] + b : acc[j];
+                            store_out<OutT>(y + static_cast<long long>(j) * sg.ldy + my_row, v);
+                        }
+                    }
+                }
+            }
+            u += (s1 - s0);
+        }
+    }
+
+    // ---------------------------------------------------------------------- teardown
+    tc_fence_before_sync();
+    __syncthreads();
+    if (tid == 0 && ctrl->abort_flag) atomicExch(p.status, kStatusWaitTimeout);
+    if (warp == kMmaWarp) {
+        __syncwarp();
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+// ------------------------------------------------------------------------------------ host side
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = []() -> EncodeTiledFn {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            return nullptr;
+        return reinterpret_cast<EncodeTiledFn>(sym);
+    }();
+    return fn;
+}
+
+bool encode_w_map(CUtensorMap* map, const uint8_t* w, long long n, long long k) {
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(k / 2), static_cast<cuuint64_t>(n)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(k / 2)};
+    const cuuint32_t box[2] = {kStageRowBytes, kHalfRows};
+    const cuuint32_t estr[2] = {1, 1};
+    return encode_fn()(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(w), dims, strides, box, estr,
+                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+bool encode_x_map(CUtensorMap* map, const __half* x, long long m, long long k, int nmma) {
+    // view X[m][k] as (8 elements, m rows, k/8 cores): a box lands as [core][row][16 B], the canonical
+    // K-major core-matrix layout of the MMA's shared-memory operand
+    const cuuint64_t dims[3] = {8, static_cast<cuuint64_t>(m), static_cast<cuuint64_t>(k / 8)};
+    const cuuint64_t strides[2] = {static_cast<cuuint64_t>(k) * 2, 16};
+    const cuuint32_t box[3] = {8, static_cast<cuuint32_t>(nmma), kKCoresPerStage};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    return encode_fn()(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<__half*>(x), dims, strides, box, estr,
+                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int NMMA, typename OutT>
+cudaError_t launch(const Params& p, int ctas, cudaStream_t stream) {
+    auto kern = w4a16_tc_kernel<NMMA, OutT>;
+    static bool configured = false;  // per instantiation; the attribute is per device-function
+    static int configured_dev = -1;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (!configured || configured_dev != dev) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<NMMA>::kSmemBytes);
+        if (e != cudaSuccess) return e;
+        configured = true;
+        configured_dev = dev;
+    }
+    kern<<<ctas, kThreads, Cfg<NMMA>::kSmemBytes, stream>>>(p);
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+size_t tc_workspace_bytes(int ctas) { return static_cast<size_t>(ctas) * 2 * 32 * kTileRows * sizeof(float); }
+
+bool tc_eligible(const void* x, const TcProj* proj, int num, bool swiglu, long long m, long long k, int group_size) {
+    if (group_size != 128 || m < 1 || m > 32 || k < 128 || (k % 128) != 0) return false;
+    if (k / 8 > (1ll << 31) || (reinterpret_cast<uintptr_t>(x) & 15)) return false;
+    if (encode_fn() == nullptr) return false;
+    const int cnt = swiglu ? 2 : num;
+    for (int i = 0; i < cnt; ++i) {
+        if (proj[i].n < 1 || proj[i].n > (1ll << 30)) return false;
+        if (reinterpret_cast<uintptr_t>(proj[i].w) & 15) return false;
+    }
+    return true;
+}
+
+// Launches the tensor-core kernel.  `scratch` holds tc_workspace_bytes(ctas) bytes of partials followed by
+// `counter_capacity` zeroed ints; both are owned by the caller.  Returns 0, or a negative code when the
+// problem cannot be described to the kernel (the caller then uses the CUDA-core path).
+int tc_launch(cudaStream_t stream, const void* x, const TcProj* proj, int num, bool swiglu, bool out_f32,
+              long long m, long long k, int num_sms, float* workspace, int* counters, int counter_capacity,
+              int* status) {
+    Params p;
+    memset(&p, 0, sizeof(p));
+    const int nmma = (m <= 16) ? 16 : 32;
+    p.num_segs = swiglu ? 1 : num;
+    p.swiglu = swiglu ? 1 : 0;
+    p.m = static_cast<int>(m);
+    p.groups = static_cast<int>(k / 128);
+    p.stages = (p.groups + 1) / 2;
+    int tiles = 0;
+    const int cnt = swiglu ? 2 : num;
+    for (int i = 0; i < cnt; ++i) {
+        if (!encode_w_map(&p.w_map[i], proj[i].w, proj[i].n, k)) return -2;
+        p.seg[i].scales = static_cast<const __half*>(proj[i].scales);
+        p.seg[i].bias = proj[i].bias;
+        p.seg[i].y = proj[i].y;
+        p.seg[i].ldy = proj[i].ldy > 0 ? proj[i].ldy : proj[i].n;
+        p.seg[i].n = static_cast<int>(proj[i].n);
+        p.seg[i].tile_begin = tiles;
+        if (swiglu) {
+            if (i == 0) tiles += static_cast<int>((proj[0].n + kHalfRows - 1) / kHalfRows);
+            else p.seg[i].tile_begin = 0;
+        } else {
+            tiles += static_cast<int>((proj[i].n + kTileRows - 1) / kTileRows);
+        }
+    }
+    if (!encode_x_map(&p.x_map, static_cast<const __half*>(x), m, k, nmma)) return -2;
+    if (tiles > counter_capacity) return -3;
+    p.total_tiles = tiles;
+    p.total_units = static_cast<long long>(tiles) * p.stages;
+    p.workspace = workspace;
+    p.counters = counters;
+    p.status = status;
+    const int ctas = static_cast<int>(p.total_units < num_sms ? p.total_units : num_sms);
+    cudaError_t e;
+    if (nmma == 16) e = out_f32 ? launch<16, float>(p, ctas, stream) : launch<16, __half>(p, ctas, stream);
+    else e = out_f32 ? launch<32, float>(p, ctas, stream) : launch<32, __half>(p, ctas, stream);
+    return e == cudaSuccess ? 0 : -1;
+}
+
+}  // namespace xb
