@@ -1,0 +1,310 @@
+"""GPU parity: the W4A16 linear family through the C-ABI against the CPU oracle.
+
+Tolerances.  On the reference tests' own cases the reference's own max-abs bounds apply
+(tests/test_ops_oracle.cpp:368, :459, :774, :782: 1e-4 fp32 out, 1e-3 split-K shape, 5e-3 fp16 out).
+On the benchmark distributions the bound is 1e-3 relative at fp32 accumulation, taken per element
+against max(|ref|, rms(ref)); fp16 outputs are additionally allowed one fp16 rounding (2^-10 relative).
+Int4 unpacking is checked bit-exactly through one-hot activations.
+"""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from conftest import fill_scales, fill_weights, synth_linear
+
+pytestmark = pytest.mark.gpu
+
+TC, SIMT = 1, 2
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def rel_err(got, ref):
+    ref = np.asarray(ref, np.float64)
+    got = np.asarray(got, np.float64)
+    denom = np.maximum(np.abs(ref), np.sqrt(np.mean(ref ** 2)) + 1e-30)
+    return float(np.max(np.abs(got - ref) / denom))
+
+
+def run_linear(ops, X, W, S, bias=None, out_dtype=torch.float32, path=0):
+    M, K = X.shape
+    N = W.shape[0]
+    Y = torch.full((M, N), float("nan"), dtype=out_dtype, device="cuda")
+    ops.set_linear_path(path)
+    try:
+        rc = ops.linear_int4(Y, dev(X), dev(W), dev(S), None if bias is None else dev(bias), M, N, K)
+    finally:
+        ops.set_linear_path(0)
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert ops.device_status(0) == 0
+    return Y.float().cpu().numpy(), ops.last_linear_path()
+
+
+# ------------------------------------------------------------------ the reference's own test cases
+def test_reference_case_fp32_m2_k5120_n2048(cuda, golden):
+    arrays, meta = golden
+    m = meta["lin"]
+    W = fill_weights(m["N"] * m["K"] // 2, *m["w_fill"]).reshape(m["N"], m["K"] // 2)
+    S = fill_scales(m["N"] * (m["K"] // 128)).reshape(m["N"], m["K"] // 128)
+    got, path = run_linear(cuda, arrays["lin_X"], W, S)
+    assert path == SIMT  # fp32 activations stay on CUDA cores
+    assert np.max(np.abs(got - arrays["lin_Y"])) <= m["tol_abs"]
+
+
+def test_reference_case_splitk_n48(cuda, golden):
+    arrays, meta = golden
+    m = meta["splitk"]
+    W = fill_weights(m["N"] * m["K"] // 2, *m["w_fill"]).reshape(m["N"], m["K"] // 2)
+    S = fill_scales(m["N"] * (m["K"] // 128)).reshape(m["N"], m["K"] // 128)
+    got, _ = run_linear(cuda, arrays["splitk_X"], W, S)
+    assert np.max(np.abs(got - arrays["splitk_Y"])) <= 1e-4  # tighter than the reference's 1e-3
+    # same shape with fp16 activations exercises the tensor-core kernel's K split
+    Xh = arrays["splitk_X"].astype(np.float16)
+    ref = oracle.linear_int4_f64(Xh.astype(np.float32), W, S)
+    got, path = run_linear(cuda, Xh, W, S)
+    assert path == TC
+    assert np.max(np.abs(got - ref)) <= 1e-4
+
+
+@pytest.mark.parametrize("act", ["f32", "f16"])
+def test_reference_case_fused_four_projections(cuda, golden, act):
+    arrays, meta = golden
+    K = meta["fused"]["K"]
+    X = arrays["fused_X"] if act == "f32" else arrays["fused_X"].astype(np.float16)
+    Xd = dev(X)
+    descs, keep, refs = [], [], []
+    for p, n in enumerate(meta["fused"]["N"]):
+        W = fill_weights(n * K // 2, p + 3, p + 7).reshape(n, K // 2)
+        S = fill_scales(n * (K // 128), shift=p).reshape(n, K // 128)
+        Y = torch.full((1, n), float("nan"), dtype=torch.float32 if act == "f32" else torch.float16, device="cuda")
+        Wd, Sd = dev(W), dev(S)
+        keep += [Wd, Sd, Y]
+        descs.append({"Y": Y, "W_int4": Wd, "scales": Sd, "bias": None, "N": n})
+        refs.append(arrays[f"fused_Y{p}"] if act == "f32" else oracle.linear_int4_f64(X.astype(np.float32), W, S))
+    assert cuda.linear_int4_fused(Xd, descs, 1, K) == 0
+    torch.cuda.synchronize()
+    assert cuda.device_status(0) == 0
+    for d, ref in zip(descs, refs):
+        got = d["Y"].float().cpu().numpy()
+        assert np.max(np.abs(got - ref)) <= (1e-4 if act == "f32" else 5e-3)
+    # num_descs outside [1, 4] is a silent no-op (src/ops/linear.cpp:359)
+    assert cuda.linear_int4_fused(Xd, descs + descs[:1], 1, K) == 1
+    assert cuda.linear_int4_fused(Xd, [], 1, K) == 1
+
+
+@pytest.mark.parametrize("act", ["f32", "f16"])
+def test_reference_case_swiglu(cuda, golden, act):
+    arrays, meta = golden
+    K, N = meta["swiglu"]["K"], meta["swiglu"]["N"]
+    Wg = fill_weights(N * K // 2, 2, 5).reshape(N, K // 2)
+    Wu = fill_weights(N * K // 2, 4, 9).reshape(N, K // 2)
+    Sg = fill_scales(N * (K // 128)).reshape(N, K // 128)
+    Su = fill_scales(N * (K // 128), base=0.020, shift=3).reshape(N, K // 128)
+    X = arrays["swiglu_X"] if act == "f32" else arrays["swiglu_X"].astype(np.float16)
+    ref = arrays["swiglu_Y"] if act == "f32" else oracle.mlp_gate_up_swiglu_f64(X.astype(np.float32), Wg, Sg, Wu, Su)
+    Y = torch.full((1, N), float("nan"), dtype=torch.float32 if act == "f32" else torch.float16, device="cuda")
+    assert cuda.mlp_gate_up_swiglu_int4(Y, dev(X), dev(Wg), dev(Sg), dev(Wu), dev(Su), 1, N, K) == 0
+    torch.cuda.synchronize()
+    assert cuda.device_status(0) == 0
+    assert np.max(np.abs(Y.float().cpu().numpy() - ref)) <= (1e-4 if act == "f32" else 5e-3)
+
+
+def test_reference_case_half_activations(cuda, golden):
+    arrays, meta = golden
+    m = meta["half"]
+    W = fill_weights(m["N"] * m["K"] // 2, *m["w_fill"]).reshape(m["N"], m["K"] // 2)
+    S = fill_scales(m["N"] * (m["K"] // 128)).reshape(m["N"], m["K"] // 128)
+    for path in (TC, SIMT):
+        got16, used = run_linear(cuda, arrays["half_X"], W, S, out_dtype=torch.float16, path=path)
+        assert used == path
+        assert np.max(np.abs(got16 - arrays["half_Y"])) <= m["tol_abs_f16"]
+        got32, _ = run_linear(cuda, arrays["half_X"], W, S, out_dtype=torch.float32, path=path)
+        assert np.max(np.abs(got32 - arrays["half_Y"])) <= m["tol_abs_f32"]
+
+
+# ------------------------------------------------------------------ int4 unpacking, bit exact
+@pytest.mark.parametrize("path", [TC, SIMT])
+def test_int4_unpack_bit_exact_via_one_hot(cuda, path):
+    """X rows are one-hot in k, so Y[m, n] = q[n, k_m] * scale[n, g] exactly: any unpack or K-order
+    error shows as a wrong integer."""
+    K, N = 512, 300
+    rng = np.random.default_rng(1)
+    q = rng.integers(-8, 8, size=(N, K), dtype=np.int8)
+    W = ((q[:, 0::2] & 0xF) | ((q[:, 1::2] & 0xF) << 4)).astype(np.uint8)
+    S = np.ones((N, K // 128), np.float16)
+    assert np.array_equal(oracle.unpack_int4(W), q)
+    for k0 in range(0, K, 32):
+        X = np.zeros((32, K), np.float16)
+        X[np.arange(32), k0 + np.arange(32)] = 1.0
+        got, used = run_linear(cuda, X, W, S, path=path)
+        assert used == path
+        assert np.array_equal(got, q[:, k0:k0 + 32].T.astype(np.float32)), k0
+
+
+# ------------------------------------------------------------------ benchmark configuration sweep
+LAYER_SHAPES = [(5120, 6144), (5120, 1024), (6144, 5120), (5120, 17408), (17408, 5120)]
+
+
+@pytest.mark.parametrize("K,N", LAYER_SHAPES)
+@pytest.mark.parametrize("M", [1, 4, 8, 16, 32])
+def test_sweep_against_oracle(cuda, M, K, N):
+    """The MTP-verify sweep, checked on a row subset (the oracle on the full N would take minutes);
+    every output column is produced by the full-size launch."""
+    X, W, S, _ = synth_linear(M, K, N, seed=0)
+    got16, used = run_linear(cuda, X, W, S, out_dtype=torch.float16)
+    assert used == TC
+    got32, _ = run_linear(cuda, X, W, S, out_dtype=torch.float32)
+    rows = np.unique(np.concatenate([np.arange(0, 300), np.arange(N - 300, N),
+                                     np.random.default_rng(1).integers(0, N, 400)]))
+    ref = oracle.linear_int4_f64(X.astype(np.float32), W[rows], S[rows])
+    assert rel_err(got32[:, rows], ref) <= 1e-3
+    assert rel_err(got16[:, rows], ref) <= 1e-3 + 2.0 ** -10
+    # much tighter in practice: exact integer products, fp32 accumulation
+    assert rel_err(got32[:, rows], ref) <= 2e-5
+    # every column was written
+    assert not np.isnan(got32).any() and not np.isnan(got16).any()
+
+
+def test_config0_gemv_both_paths_and_reference_true_shapes(cuda):
+    X, W, S, _ = synth_linear(1, 5120, 17408, seed=0)
+    ref = oracle.linear_int4_f64(X.astype(np.float32), W, S)
+    for path in (TC, SIMT):
+        got, used = run_linear(cuda, X, W, S, path=path)
+        assert used == path
+        assert rel_err(got, ref) <= 2e-5
+    for (K, N) in [(5120, 12288), (5120, 10240), (5120, 48)]:
+        X, W, S, _ = synth_linear(3, K, N, seed=2)
+        rows = np.arange(0, N, max(1, N // 500))
+        ref = oracle.linear_int4_f64(X.astype(np.float32), W[rows], S[rows])
+        got, _ = run_linear(cuda, X, W, S)
+        assert rel_err(got[:, rows], ref) <= 2e-5
+
+
+def test_lm_head_fp32_logits_rows_sampled(cuda):
+    M, K, N = 8, 5120, 151936
+    X, W, S, _ = synth_linear(M, K, N, seed=3)
+    got, used = run_linear(cuda, X, W, S, out_dtype=torch.float32)
+    assert used == TC
+    rows = np.unique(np.random.default_rng(0).integers(0, N, 600))
+    rows = np.concatenate([rows, np.arange(N - 64, N)])
+    ref = oracle.linear_int4_f64(X.astype(np.float32), W[rows], S[rows])
+    assert rel_err(got[:, rows], ref) <= 2e-5
+    assert not np.isnan(got).any()
+
+
+# ------------------------------------------------------------------ edge cases
+@pytest.mark.parametrize("M,K,N", [(1, 128, 1), (2, 128, 3), (5, 256, 47), (32, 384, 129), (17, 640, 257),
+                                   (31, 1152, 513), (1, 5120, 48), (9, 128, 1000)])
+@pytest.mark.parametrize("path", [TC, SIMT])
+def test_ragged_shapes_with_bias(cuda, M, K, N, path):
+    X, W, S, _ = synth_linear(M, K, N, seed=M + N)
+    bias = np.random.default_rng(N).normal(0, 1, N).astype(np.float32)
+    ref = oracle.linear_int4_f64(X.astype(np.float32), W, S, bias)
+    got, used = run_linear(cuda, X, W, S, bias=bias, path=path)
+    assert used == path
+    assert rel_err(got, ref) <= 2e-5
+    got16, _ = run_linear(cuda, X, W, S, bias=bias, out_dtype=torch.float16, path=path)
+    assert rel_err(got16, ref) <= 1e-3 + 2.0 ** -10
+
+
+def test_invalid_shapes_are_noops(cuda):
+    X, W, S, _ = synth_linear(1, 128, 4, seed=0)
+    Y = torch.full((1, 4), 7.0, device="cuda")
+    Xd, Wd, Sd = dev(X), dev(W), dev(S)
+    for (M, N, K) in [(0, 4, 128), (1, 0, 128), (1, 4, 0), (-1, 4, 128)]:
+        assert cuda.linear_int4(Y, Xd, Wd, Sd, None, M, N, K) == 1
+    torch.cuda.synchronize()
+    assert torch.all(Y == 7.0)
+
+
+def test_large_m_and_other_group_size_use_cuda_cores(cuda):
+    X, W, S, _ = synth_linear(40, 512, 96, seed=4)
+    ref = oracle.linear_int4_f64(X.astype(np.float32), W, S)
+    got, used = run_linear(cuda, X, W, S)
+    assert used == SIMT and rel_err(got, ref) <= 2e-5
+    # group size 64: only the naive path of the reference honours it (src/ops/linear.cpp:703-722)
+    rng = np.random.default_rng(6)
+    S64 = (np.abs(rng.normal(0, 0.02, size=(96, 8))) / 7).astype(np.float16)
+    ref64 = oracle.linear_int4_f64(X.astype(np.float32), W, S64, group_size=64)
+    Y = torch.empty((40, 96), dtype=torch.float32, device="cuda")
+    assert cuda.linear_int4(Y, dev(X), dev(W), dev(S64), None, 40, 96, 512, 64) == 0
+    torch.cuda.synchronize()
+    assert rel_err(Y.cpu().numpy(), ref64) <= 2e-5
+
+
+# ------------------------------------------------------------------ fused launches at layer shapes
+def test_fused_layer_shapes(cuda):
+    K, M = 5120, 32
+    X = np.random.default_rng(0).normal(0, 1, size=(M, K)).astype(np.float16)
+    Xd = dev(X)
+    for Ns in ([12288, 1024, 1024], [10240, 6144, 48, 48]):
+        descs, keep, hosts = [], [], []
+        for i, n in enumerate(Ns):
+            _, W, S, _ = synth_linear(1, K, n, seed=10 + i)
+            Y = torch.full((M, n), float("nan"), dtype=torch.float16, device="cuda")
+            Wd, Sd = dev(W), dev(S)
+            keep += [Wd, Sd]
+            hosts.append((W, S))
+            descs.append({"Y": Y, "W_int4": Wd, "scales": Sd, "bias": None, "N": n})
+        assert cuda.linear_int4_fused(Xd, descs, M, K) == 0
+        torch.cuda.synchronize()
+        assert cuda.device_status(0) == 0 and cuda.last_linear_path() == TC
+        for d, (W, S) in zip(descs, hosts):
+            n = d["N"]
+            rows = np.unique(np.concatenate([np.arange(min(n, 40)), np.arange(max(0, n - 40), n)]))
+            ref = oracle.linear_int4_f64(X.astype(np.float32), W[rows], S[rows])
+            got = d["Y"].float().cpu().numpy()
+            assert not np.isnan(got).any()
+            assert rel_err(got[:, rows], ref) <= 1e-3 + 2.0 ** -10
+
+
+@pytest.mark.parametrize("M", [1, 8, 32])
+def test_swiglu_layer_shape(cuda, M):
+    K, N = 5120, 17408
+    X, Wg, Sg, _ = synth_linear(M, K, N, seed=20)
+    _, Wu, Su, _ = synth_linear(1, K, N, seed=21)
+    # scales large enough that silu is exercised away from zero
+    Sg = (Sg.astype(np.float32) * 8).astype(np.float16)
+    Y = torch.full((M, N), float("nan"), dtype=torch.float16, device="cuda")
+    assert cuda.mlp_gate_up_swiglu_int4(Y, dev(X), dev(Wg), dev(Sg), dev(Wu), dev(Su), M, N, K) == 0
+    torch.cuda.synchronize()
+    assert cuda.device_status(0) == 0 and cuda.last_linear_path() == TC
+    rows = np.unique(np.concatenate([np.arange(200), np.arange(N - 200, N)]))
+    ref = oracle.mlp_gate_up_swiglu_f64(X.astype(np.float32), Wg[rows], Sg[rows], Wu[rows], Su[rows])
+    got = Y.float().cpu().numpy()
+    assert not np.isnan(got).any()
+    assert rel_err(got[:, rows], ref) <= 1e-3 + 2.0 ** -10
+
+
+# ------------------------------------------------------------------ size-independent properties
+def test_linearity_and_determinism_full_size(cuda):
+    M, K, N = 32, 17408, 5120
+    X, W, S, _ = synth_linear(M, K, N, seed=5)
+    a, _ = run_linear(cuda, X, W, S)
+    b, _ = run_linear(cuda, X, W, S)
+    assert np.array_equal(a, b)  # fixed summation order across K splits
+    # doubling the activations doubles the output exactly (power-of-two scaling is exact in fp16/fp32)
+    c, _ = run_linear(cuda, (X.astype(np.float32) * 2).astype(np.float16), W, S)
+    assert np.array_equal(c, 2 * a)
+    # rows are independent: a launch on the first 7 rows equals the first 7 rows of the 32-row launch
+    d, _ = run_linear(cuda, X[:7], W, S)
+    assert rel_err(d, a[:7]) <= 1e-6
+
+
+def test_column_slice_output_for_tensor_parallel(cuda):
+    M, K, N = 8, 1024, 512
+    X, W, S, _ = synth_linear(M, K, N, seed=8)
+    full, _ = run_linear(cuda, X, W, S, out_dtype=torch.float16)
+    Y = torch.zeros((M, N), dtype=torch.float16, device="cuda")
+    Xd, Wd, Sd = dev(X), dev(W), dev(S)
+    half = N // 2
+    for r in range(2):
+        ysl = Y[:, r * half:]
+        assert cuda.linear_int4_ld(ysl, N, Xd, Wd[r * half:(r + 1) * half], Sd[r * half:(r + 1) * half], None,
+                                   M, half, K) == 0
+    torch.cuda.synchronize()
+    assert np.array_equal(Y.float().cpu().numpy(), full)

@@ -1,0 +1,193 @@
+"""GPU parity: argmax, speculative acceptance and the Philox uniform source against the CPU oracle.
+Token ids and accept counts are integers: the bar is exact equality."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+
+pytestmark = pytest.mark.gpu
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def mt_logits(seed, n, lo, hi):
+    raw = np.random.RandomState(seed).randint(0, 2**32, size=n, dtype=np.uint64).astype(np.uint32)
+    u = raw.astype(np.float32) * np.float32(2.0 ** -32)
+    u = np.where(u >= 1.0, np.nextafter(np.float32(1.0), np.float32(0.0)), u).astype(np.float32)
+    return (u * np.float32(hi - lo) + np.float32(lo)).astype(np.float32)
+
+
+def test_argmax_reference_case(cuda, golden):
+    _, meta = golden
+    a = meta["argmax"]
+    logits = mt_logits(a["seed"], a["vocab"], -100.0, 100.0)
+    logits[a["planted"]] = 999.0
+    assert f"{oracle.crc64(logits.tobytes()):016x}" == a["logits_crc64"]
+    d = dev(logits)
+    assert cuda.argmax(d, a["vocab"]) == a["expected"]
+    # with caller scratch, as the reference allows (src/ops/sampling.h:17-25)
+    n = cuda.argmax_scratch_size(a["vocab"])
+    assert n == (a["vocab"] + 255) // 256
+    pm = torch.empty(n, dtype=torch.float32, device="cuda")
+    pi = torch.empty(n, dtype=torch.int64, device="cuda")
+    assert cuda.argmax(d, a["vocab"], pm, pi) == a["expected"]
+
+
+def test_argmax_edges_and_ties(cuda):
+    assert cuda.argmax(None, 100) == 0
+    z = dev(np.zeros(5, np.float32))
+    assert cuda.argmax(z, 0) == 0 and cuda.argmax(z, -3) == 0 and cuda.argmax(z, 1) == 0
+    rng = np.random.default_rng(0)
+    for V in (2, 255, 256, 257, 4095, 4096, 4097, 151936):
+        x = rng.normal(0, 3, V).astype(np.float32)
+        assert cuda.argmax(dev(x), V) == oracle.argmax(x)
+        # ties: lowest index wins, also across block boundaries
+        t = np.zeros(V, np.float32)
+        idx = np.unique(rng.integers(0, V, 5))
+        t[idx] = 9.0
+        assert cuda.argmax(dev(t), V) == int(idx.min()) == oracle.argmax(t)
+    allneg = np.full(5000, -np.inf, np.float32)
+    assert cuda.argmax(dev(allneg), 5000) == oracle.argmax(allneg) == 0
+
+
+def test_argmax_rows_batched(cuda):
+    rng = np.random.default_rng(1)
+    x = rng.normal(0, 3, size=(32, 151936)).astype(np.float32)
+    out = torch.empty(32, dtype=torch.int64, device="cuda")
+    assert cuda.argmax_rows(dev(x), out) == 0
+    torch.cuda.synchronize()
+    assert out.cpu().tolist() == [oracle.argmax(r) for r in x]
+
+
+def test_accept_reject_reference_scenarios(cuda, golden):
+    _, meta = golden
+    acc = meta["accept"]
+    V = acc["vocab"]
+    tl = np.full((4, V), -10.0, np.float32)
+    for i, t in enumerate(acc["argmax_tokens"]):
+        tl[i, t] = 10.0
+    d = dev(tl)
+    for name, s in acc["scenarios"].items():
+        got = cuda.speculative_accept_reject(s["draft"], 4, d, V, s.get("draft_probs"), s.get("rand_uniform"))
+        want = {k: v for k, v in s["expected"].items() if k != "contract_violated"}
+        assert got == want, name
+    empty = cuda.speculative_accept_reject([], 0, d, V)
+    assert empty["bonus_or_resampled_token"] == -1 and empty["num_accepted"] == 0
+    assert cuda.speculative_accept_reject([1], 1, None, V)["bonus_or_resampled_token"] == -1
+
+
+def make_config2(seed, B=8, k=3, V=151936, temperature=0.7):
+    """Benchmark acceptance configuration: draft logits N(0, 3), target = draft + N(0, 1)."""
+    rng = np.random.default_rng(seed)
+    draft = rng.normal(0, 3, size=(B, k, V)).astype(np.float32)
+    target = (draft + rng.normal(0, 1, size=(B, k, V)).astype(np.float32)).astype(np.float32)
+    return draft, target
+
+
+def test_config2_greedy_exact(cuda):
+    B, k, V = 8, 3, 151936
+    draft, target = make_config2(0)
+    toks = np.array([[oracle.argmax(draft[b, i]) for i in range(k)] for b in range(B)], np.int64)
+    # make the outcome varied: force some draft tokens to the target's argmax
+    for b in range(0, B, 2):
+        toks[b, 0] = oracle.argmax(target[b, 0])
+    toks[0, 1] = oracle.argmax(target[0, 1])
+    toks[0, 2] = oracle.argmax(target[0, 2])
+    out = torch.zeros(B * cuda.ACCEPT_RECORD_BYTES, dtype=torch.uint8, device="cuda")
+    assert cuda.speculative_accept_reject_batched(dev(toks), dev(target), None, None, out) == 0
+    recs = cuda.decode_accept_records(out)
+    n_acc = []
+    for b in range(B):
+        want = oracle.speculative_accept_reject(toks[b], target[b])
+        for f in ("bonus_or_resampled_token", "rejected_token", "num_accepted", "num_rejected", "num_resampled",
+                  "num_remaining"):
+            assert recs[b][f] == want[f], (b, f)
+        assert bool(recs[b]["has_rejected_token"]) == want["has_rejected_token"]
+        n_acc.append(want["num_accepted"])
+        # the host-facing synchronous form agrees too
+        single = cuda.speculative_accept_reject(toks[b].tolist(), k, dev(target[b]), V)
+        assert single == {kk: v for kk, v in want.items() if kk != "contract_violated"}
+    assert n_acc[0] == 3 and 0 in n_acc  # both outcomes are present
+
+
+@pytest.mark.parametrize("seed", [0, 1])
+def test_config2_stochastic_exact_with_philox_uniforms(cuda, seed):
+    """Temperature 0.7, draft tokens sampled from softmax(draft / T) on the host, acceptance uniforms
+    from Philox generated ON THE DEVICE and checked bit-exactly against the oracle's generator; both
+    sides then see identical uniforms and must take identical decisions."""
+    B, k, V, T = 8, 3, 151936, 0.7
+    inv_t = np.float32(1.0 / T)
+    draft, target = make_config2(seed)
+    u_dev = torch.empty(B * k, dtype=torch.float32, device="cuda")
+    assert cuda.philox_uniform(u_dev, seed=1000 + seed, subsequence=1) == 0
+    uni = oracle.philox_uniform(B * k, seed=1000 + seed, subsequence=1)
+    assert np.array_equal(u_dev.cpu().numpy(), uni)
+    pick = oracle.philox_uniform(B * k, seed=1000 + seed, subsequence=0).reshape(B, k)
+    toks = np.zeros((B, k), np.int64)
+    probs = np.zeros((B, k), np.float32)
+    for b in range(B):
+        for i in range(k):
+            p = oracle.softmax((draft[b, i] * inv_t)[None])[0].astype(np.float64)
+            c = np.cumsum(p)
+            t = int(min(np.searchsorted(c, pick[b, i] * c[-1], side="right"), V - 1))
+            toks[b, i] = t
+            probs[b, i] = np.float32(p[t])
+    uni = uni.reshape(B, k)
+    out = torch.zeros(B * cuda.ACCEPT_RECORD_BYTES, dtype=torch.uint8, device="cuda")
+    assert cuda.speculative_accept_reject_batched(dev(toks), dev(target), dev(probs), dev(uni), out,
+                                                  inv_temperature=float(inv_t)) == 0
+    recs = cuda.decode_accept_records(out)
+    accepted_total = 0
+    for b in range(B):
+        want = oracle.speculative_accept_reject(toks[b], target[b], probs[b], uni[b], inv_temperature=float(inv_t))
+        assert not want["contract_violated"]
+        for f in ("bonus_or_resampled_token", "rejected_token", "num_accepted", "num_rejected", "num_resampled",
+                  "num_remaining"):
+            assert recs[b][f] == want[f], (b, f)
+        accepted_total += want["num_accepted"]
+    assert 0 < accepted_total < B * k  # the rule is exercised in both directions
+
+
+def test_stochastic_margins_and_fallback_rules(cuda):
+    """p_draft <= 0 -> greedy rule; missing uniforms -> r = 0; out-of-range token -> p_target = 0."""
+    V = 5000
+    rng = np.random.default_rng(3)
+    tl = rng.normal(0, 2, size=(3, V)).astype(np.float32)
+    am = [oracle.argmax(tl[i]) for i in range(3)]
+    d = dev(tl)
+    cases = [
+        (am, [0.0, -1.0, 0.5], None),
+        ([am[0], V + 9, am[2]], [0.5, 0.5, 0.5], [0.0, 0.0, 0.0]),
+        (am, [1.0, 1.0, 1.0], [0.9999, 0.0, 0.5]),
+        ([7, 8, 9], [1e-6, 1e-6, 1e-6], [0.5, 0.5, 0.5]),
+    ]
+    for toks, probs, unif in cases:
+        got = cuda.speculative_accept_reject(toks, 3, d, V, probs, unif)
+        want = oracle.speculative_accept_reject(np.array(toks, np.int64), tl, np.array(probs, np.float32),
+                                                None if unif is None else np.array(unif, np.float32))
+        assert got == {k: v for k, v in want.items() if k != "contract_violated"}
+
+
+def test_bonus_row_convention_k_plus_one(cuda):
+    """With k+1 target rows per sequence the bonus token comes from row k on full acceptance."""
+    B, k, V = 2, 3, 2048
+    rng = np.random.default_rng(9)
+    tl = rng.normal(0, 1, size=(B, k + 1, V)).astype(np.float32)
+    toks = np.array([[oracle.argmax(tl[b, i]) for i in range(k)] for b in range(B)], np.int64)
+    toks[1, 1] = (toks[1, 1] + 1) % V
+    out = torch.zeros(B * cuda.ACCEPT_RECORD_BYTES, dtype=torch.uint8, device="cuda")
+    assert cuda.speculative_accept_reject_batched(dev(toks), dev(tl), None, None, out, bonus_row=k) == 0
+    recs = cuda.decode_accept_records(out)
+    assert recs[0]["num_accepted"] == 3 and recs[0]["bonus_or_resampled_token"] == oracle.argmax(tl[0, k])
+    assert recs[1]["num_accepted"] == 1 and recs[1]["bonus_or_resampled_token"] == oracle.argmax(tl[1, 1])
+    assert recs[1]["num_remaining"] == 1
+
+
+def test_philox_uniform_bit_exact(cuda):
+    for n, seed, sub in [(1, 0, 0), (3, 1, 2), (4, 2**40 + 3, 2**33 + 1), (10007, 77, 5)]:
+        out = torch.empty(n, dtype=torch.float32, device="cuda")
+        assert cuda.philox_uniform(out, seed=seed, subsequence=sub) == 0
+        assert np.array_equal(out.cpu().numpy(), oracle.philox_uniform(n, seed, sub))
