@@ -31,6 +31,7 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include "ptx_sm100.cuh"
@@ -49,8 +50,8 @@ constexpr int kWStageBytes = 2 * kWHalfBytes;                // 32 KiB
 constexpr int kKCoresPerStage = kStageK / 8;                 // 32 sixteen-byte K cores
 constexpr int kConsumerThreads = 256;
 constexpr int kProducerWarp = 8;
-constexpr int kMmaWarp = 9;
-constexpr int kThreads = 320;
+constexpr int kMmaWarp = 9;   // issues the MMAs of half 0 and owns the TMEM allocation; warp 10 issues half 1
+constexpr int kThreads = 352;
 constexpr uint32_t kTmemCols = 512;
 constexpr int kMaxSegs = 4;
 
@@ -84,7 +85,7 @@ struct Params {
     int stages;       // ceil(groups / 2), stage units per tile
     int total_tiles;
     long long total_units;
-    float* workspace; // [ctas][2][NMMA][256] fp32 partials
+    float* workspace; // [ctas][2][32][256] fp32 partials
     int* counters;    // [total_tiles], zero between launches
     int* status;      // device status word
 };
@@ -133,7 +134,7 @@ __device__ __forceinline__ TileInfo locate_tile(const Params& p, int tile) {
     return ti;
 }
 
-template <int NMMA, typename OutT>
+template <int NMMA, int NREAD, typename OutT>
 __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_constant__ Params p) {
     using C = Cfg<NMMA>;
     extern __shared__ uint8_t smem_raw[];
@@ -150,12 +151,12 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
     if (tid == 0) {
         for (int i = 0; i < C::kStages; ++i) {
             mbar_init(smem_u32(&ctrl->full[i]), 1);
-            mbar_init(smem_u32(&ctrl->empty[i]), kConsumerThreads);
-            mbar_init(smem_u32(&ctrl->x_ready[i]), kConsumerThreads);
+            mbar_init(smem_u32(&ctrl->empty[i]), kConsumerThreads / 32);
+            mbar_init(smem_u32(&ctrl->x_ready[i]), kConsumerThreads / 32);
         }
         for (int w = 0; w < 2; ++w)
             for (int b = 0; b < 2; ++b) {
-                mbar_init(smem_u32(&ctrl->a_full[w][b]), kHalfRows);
+                mbar_init(smem_u32(&ctrl->a_full[w][b]), kHalfRows / 32);
                 mbar_init(smem_u32(&ctrl->d_full[w][b]), 1);
             }
         ctrl->abort_flag = 0;
@@ -176,6 +177,9 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
     const long long u_end = unit_begin(blockIdx.x + 1, p.total_units, ctas);
     const int S = p.stages;
 
+    // Every stage carries exactly two 128-k groups.  When K/128 is odd the second group of a tile's last
+    // stage lies beyond the tensors' extent: TMA fills it with zeros, its products are zero, and its
+    // scale is taken as zero, so the code below never branches on the group count.
     if (warp == kProducerWarp) {
         // ------------------------------------------------------------------ TMA producer
         if (lane == 0) {
@@ -188,7 +192,7 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
             for (long long u = u_begin; u < u_end; ++u, ++n) {
                 const int slot = n % C::kStages;
                 const uint32_t ph = (n / C::kStages) & 1u;
-                if (!mbar_wait(smem_u32(&ctrl->empty[slot]), ph ^ 1u, abort_flag)) break;
+                if (!mbar_wait_parked(smem_u32(&ctrl->empty[slot]), ph ^ 1u, abort_flag)) break;
                 const int tile = static_cast<int>(u / S);
                 const int s = static_cast<int>(u - static_cast<long long>(tile) * S);
                 const TileInfo ti = locate_tile(p, tile);
@@ -212,38 +216,35 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
                 }
             }
         }
-    } else if (warp == kMmaWarp) {
-        // ------------------------------------------------------------------ MMA issuer
+    } else if (warp == kMmaWarp || warp == kMmaWarp + 1) {
+        // ------------------------------------------------------------------ MMA issuers, one thread per half
         if (lane == 0) {
+            const int w = warp - kMmaWarp;
             constexpr uint32_t idesc = umma_idesc_f16_f32(128, NMMA);
             constexpr uint32_t lbo = NMMA * 16;  // between the two K cores of one step
             constexpr uint32_t sbo = 128;        // between 8-row groups
-            uint32_t n = 0, gc = 0;
+            // shared-memory descriptor: only the 14-bit start address changes between MMAs
+            constexpr uint32_t desc_hi = ((sbo >> 4) & 0x3FFFu) | (1u << 14);
+            constexpr uint32_t desc_lo_const = ((lbo >> 4) & 0x3FFFu) << 16;
+            uint32_t n = 0;
             bool ok = true;
             for (long long u = u_begin; u < u_end && ok; ++u, ++n) {
                 const int slot = n % C::kStages;
-                const uint32_t ph = (n / C::kStages) & 1u;
-                const int s = static_cast<int>(u % S);
-                const int groups = min(2, p.groups - 2 * s);
-                if (!mbar_wait(smem_u32(&ctrl->x_ready[slot]), ph, abort_flag)) break;
-                const uint32_t xbase = smem_u32(smem + slot * C::kStageBytes + kWStageBytes);
-                for (int gi = 0; gi < groups && ok; ++gi, ++gc) {
-                    const uint32_t buf = gc & 1u;
-                    const uint32_t aph = (gc >> 1) & 1u;
+                if (!mbar_wait_parked(smem_u32(&ctrl->x_ready[slot]), (n / C::kStages) & 1u, abort_flag)) break;
+                const uint32_t xlo = desc_lo_const | (smem_u32(smem + slot * C::kStageBytes + kWStageBytes) >> 4);
 #pragma unroll
-                    for (int w = 0; w < 2; ++w) {
-                        if (!mbar_wait(smem_u32(&ctrl->a_full[w][buf]), aph, abort_flag)) { ok = false; break; }
-                        tc_fence_after_sync();
-                        const uint32_t a_t = tmem_base + w * 128 + buf * 64;
-                        const uint32_t d_t = tmem_base + 256 + w * 64 + buf * 32;
+                for (int gi = 0; gi < 2; ++gi) {
+                    if (!mbar_wait_parked(smem_u32(&ctrl->a_full[w][gi]), n & 1u, abort_flag)) { ok = false; break; }
+                    tc_fence_after_sync();
+                    const uint32_t a_t = tmem_base + w * 128 + gi * 64;
+                    const uint32_t d_t = tmem_base + 256 + w * 64 + gi * 32;
 #pragma unroll
-                        for (int i = 0; i < 8; ++i) {
-                            const uint64_t bdesc =
-                                umma_smem_desc_kmajor_noswizzle(xbase + (gi * 16 + i * 2) * lbo, lbo, sbo);
-                            umma_ts_f16(d_t, a_t + i * 8, bdesc, idesc, i > 0 ? 1u : 0u);
-                        }
-                        umma_commit(smem_u32(&ctrl->d_full[w][buf]));
+                    for (int i = 0; i < 8; ++i) {
+                        const uint32_t lo = xlo + (((gi * 16 + i * 2) * lbo) >> 4);
+                        const uint64_t bdesc = (static_cast<uint64_t>(desc_hi) << 32) | lo;
+                        umma_ts_f16(d_t, a_t + i * 8, bdesc, idesc, i > 0 ? 1u : 0u);
                     }
+                    umma_commit(smem_u32(&ctrl->d_full[w][gi]));
                 }
             }
         }
@@ -254,29 +255,37 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
         const uint32_t lane_sel = static_cast<uint32_t>(((tid >> 5) & 3) * 32) << 16;
         const uint32_t a_t0 = tmem_base + lane_sel + wg * 128;
         const uint32_t d_t0 = tmem_base + lane_sel + 256 + wg * 64;
-        const int swz = t & 7;
+        // byte offsets of this thread's eight 16-byte chunks inside a stage (128B-swizzled rows)
+        uint32_t w_off[8];
+#pragma unroll
+        for (int c = 0; c < 8; ++c) w_off[c] = wg * kWHalfBytes + t * kStageRowBytes + ((c ^ (t & 7)) << 4);
+        const uint32_t smem_base = smem_u32(smem);
+        const uint32_t full0 = smem_u32(&ctrl->full[0]);
+        const uint32_t empty0 = smem_u32(&ctrl->empty[0]);
+        const uint32_t xready0 = smem_u32(&ctrl->x_ready[0]);
+        const uint32_t afull0 = smem_u32(&ctrl->a_full[wg][0]);
+        const uint32_t dfull0 = smem_u32(&ctrl->d_full[wg][0]);
 
-        float acc[NMMA];
-        uint32_t n = 0, gc = 0;
+        float acc[NREAD];
+        uint32_t n = 0;  // stages processed by this CTA so far
         bool ok = true;
 
-        // pending read-out of the previous group
-        bool pend = false;
-        uint32_t pend_buf = 0, pend_ph = 0;
-        int pend_release = -1;
-        float pend_scale = 0.f;
-
-        auto readout = [&]() {
-            if (!mbar_wait(smem_u32(&ctrl->d_full[wg][pend_buf]), pend_ph, abort_flag)) { ok = false; return; }
+        // Read-out of stage n-1 is interleaved into stage n: group gi's accumulator is fetched right before
+        // group gi of the next stage reuses its TMEM buffers, one full group of unpacking after its MMAs
+        // were handed off, which hides the hand-off latency.
+        auto readout = [&](const int gi, const uint32_t phase, const float scale) {
+            if (!mbar_wait(dfull0 + gi * 8, phase, abort_flag)) { ok = false; return; }
             tc_fence_after_sync();
-            uint32_t d[NMMA];
+            uint32_t d[NREAD];
+            if constexpr (NREAD == 8) {
+                tmem_ld8(d_t0 + gi * 32, d);
+            } else {
 #pragma unroll
-            for (int c = 0; c < NMMA / 16; ++c) tmem_ld16(d_t0 + pend_buf * 32 + c * 16, d + c * 16);
+                for (int c = 0; c < NREAD / 16; ++c) tmem_ld16(d_t0 + gi * 32 + c * 16, d + c * 16);
+            }
             tmem_wait_ld();
 #pragma unroll
-            for (int j = 0; j < NMMA; ++j) acc[j] = fmaf(__uint_as_float(d[j]), pend_scale, acc[j]);
-            if (pend_release >= 0) mbar_arrive(smem_u32(&ctrl->empty[pend_release]));
-            pend = false;
+            for (int j = 0; j < NREAD; ++j) acc[j] = fmaf(__uint_as_float(d[j]), scale, acc[j]);
         };
 
         long long u = u_begin;
@@ -289,72 +298,82 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
             const int my_row = p.swiglu ? ti.row0 + t : ti.row0 + wg * kHalfRows + t;
             const bool valid = my_row < sg.n;
             const __half* my_scales = sg.scales + static_cast<long long>(valid ? my_row : 0) * p.groups;
+            const int gmax = valid ? p.groups : 0;  // scale index limit; rows beyond N use scale 0
 
 #pragma unroll
-            for (int j = 0; j < NMMA; ++j) acc[j] = 0.f;
+            for (int j = 0; j < NREAD; ++j) acc[j] = 0.f;
 
-            float sc_cur[2], sc_next[2];
-            sc_next[0] = __half2float(my_scales[2 * s0]);
-            sc_next[1] = (2 * s0 + 1 < p.groups) ? __half2float(my_scales[2 * s0 + 1]) : 0.f;
+            float sc_pend0 = 0.f, sc_pend1 = 0.f, sc_cur0, sc_cur1, sc_next0, sc_next1;
+            sc_next0 = (2 * s0 < gmax) ? __half2float(my_scales[2 * s0]) : 0.f;
+            sc_next1 = (2 * s0 + 1 < gmax) ? __half2float(my_scales[2 * s0 + 1]) : 0.f;
+            bool have_prev = false;
 
             for (int s = s0; s < s1 && ok; ++s, ++n) {
-                const int slot = n % C::kStages;
-                const uint32_t ph = (n / C::kStages) & 1u;
-                sc_cur[0] = sc_next[0];
-                sc_cur[1] = sc_next[1];
-                if (s + 1 < s1) {  // scales of the next stage, consumed about one stage later
-                    sc_next[0] = __half2float(my_scales[2 * s + 2]);
-                    sc_next[1] = (2 * s + 3 < p.groups) ? __half2float(my_scales[2 * s + 3]) : 0.f;
+                const uint32_t slot = n % C::kStages;
+                sc_cur0 = sc_next0;
+                sc_cur1 = sc_next1;
+                if (s + 1 < s1) {  // scales of the next stage, consumed one stage later
+                    sc_next0 = (2 * s + 2 < gmax) ? __half2float(my_scales[2 * s + 2]) : 0.f;
+                    sc_next1 = (2 * s + 3 < gmax) ? __half2float(my_scales[2 * s + 3]) : 0.f;
                 }
-                if (!mbar_wait(smem_u32(&ctrl->full[slot]), ph, abort_flag)) { ok = false; break; }
-                uint8_t* stage = smem + slot * C::kStageBytes;
+                if (!mbar_wait(full0 + slot * 8, (n / C::kStages) & 1u, abort_flag)) { ok = false; break; }
+                const uint32_t stage = smem_base + slot * C::kStageBytes;
 
                 // activations: reorder each 8-k block to (0,4,1,5,2,6,3,7), in place
                 {
-                    uint4* xs = reinterpret_cast<uint4*>(stage + kWStageBytes);
 #pragma unroll
                     for (int i = 0; i < C::kXStageBytes / 16 / kConsumerThreads; ++i) {
-                        uint4 v = xs[tid + i * kConsumerThreads];
+                        const uint32_t addr = stage + kWStageBytes + (tid + i * kConsumerThreads) * 16;
+                        const uint4 v = lds128(addr);
                         uint4 o;
                         o.x = prmt(v.x, v.z, 0x5410u);
                         o.y = prmt(v.x, v.z, 0x7632u);
                         o.z = prmt(v.y, v.w, 0x5410u);
                         o.w = prmt(v.y, v.w, 0x7632u);
-                        xs[tid + i * kConsumerThreads] = o;
+                        sts128(addr, o);
                     }
                     fence_proxy_async_smem();
-                    mbar_arrive(smem_u32(&ctrl->x_ready[slot]));
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(xready0 + slot * 8);
                 }
 
-                const int groups = min(2, p.groups - 2 * s);
-                const uint8_t* my_w = stage + wg * kWHalfBytes + t * kStageRowBytes;
-                for (int gi = 0; gi < groups && ok; ++gi, ++gc) {
-                    const uint32_t buf = gc & 1u;
+#pragma unroll
+                for (int gi = 0; gi < 2; ++gi) {
                     uint32_t a[64];
 #pragma unroll
                     for (int c = 0; c < 4; ++c) {
-                        const uint4 v = *reinterpret_cast<const uint4*>(my_w + (((gi * 4 + c) ^ swz) << 4));
+                        const uint4 v = lds128(stage + w_off[gi * 4 + c]);
                         dequant_word(v.x, a + c * 16 + 0);
                         dequant_word(v.y, a + c * 16 + 4);
                         dequant_word(v.z, a + c * 16 + 8);
                         dequant_word(v.w, a + c * 16 + 12);
                     }
+                    if (have_prev) {  // previous stage's group gi: frees A[gi] and D[gi]
+                        readout(gi, (n - 1) & 1u, gi ? sc_pend1 : sc_pend0);
+                        if (!ok) break;
+                        if (gi == 1) {  // both groups of the previous stage are done with its smem slot
+                            __syncwarp();
+                            if (lane == 0) mbar_arrive(empty0 + ((n - 1) % C::kStages) * 8);
+                        }
+                    }
 #pragma unroll
-                    for (int c = 0; c < 4; ++c) tmem_st16(a_t0 + buf * 64 + c * 16, a + c * 16);
+                    for (int c = 0; c < 4; ++c) tmem_st16(a_t0 + gi * 64 + c * 16, a + c * 16);
                     tmem_wait_st();
                     tc_fence_before_sync();
-                    mbar_arrive(smem_u32(&ctrl->a_full[wg][buf]));
-
-                    if (pend) readout();
-                    pend = true;
-                    pend_buf = buf;
-                    pend_ph = (gc >> 1) & 1u;
-                    pend_scale = valid ? sc_cur[gi] : 0.f;
-                    pend_release = (gi == groups - 1) ? slot : -1;
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(afull0 + gi * 8);
                 }
+                sc_pend0 = sc_cur0;
+                sc_pend1 = sc_cur1;
+                have_prev = true;
             }
-            if (pend && ok) readout();
             if (!ok) break;
+            // drain the tile's last stage (n already counts it)
+            readout(0, (n - 1) & 1u, sc_pend0);
+            if (ok) readout(1, (n - 1) & 1u, sc_pend1);
+            if (!ok) break;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(empty0 + ((n - 1) % C::kStages) * 8);
 
             // ---------------------------------------------------------------- tile epilogue
             const bool whole = (s0 == 0 && s1 == S);
@@ -362,9 +381,10 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
             if (!whole) {
                 const int first_tile = static_cast<int>(u_begin / S);
                 const int wslot = blockIdx.x * 2 + (tile == first_tile ? 0 : 1);
-                float* ws = p.workspace + static_cast<long long>(wslot) * (NMMA * kTileRows);
+                float* ws = p.workspace + static_cast<long long>(wslot) * (32 * kTileRows);
 #pragma unroll
-                for (int j = 0; j < NMMA; ++j) ws[j * kTileRows + tid] = acc[j];
+                for (int j = 0; j < NREAD; ++j)
+                    if (j < p.m) ws[j * kTileRows + tid] = acc[j];
                 __threadfence();
                 named_barrier_sync(1, kConsumerThreads);
                 if (tid == 0) {
@@ -382,13 +402,14 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
                     const int c_lo = unit_owner(t_lo, p.total_units, ctas);
                     const int c_hi = unit_owner(t_lo + S - 1, p.total_units, ctas);
 #pragma unroll
-                    for (int j = 0; j < NMMA; ++j) acc[j] = 0.f;
+                    for (int j = 0; j < NREAD; ++j) acc[j] = 0.f;
                     for (int c = c_lo; c <= c_hi; ++c) {  // fixed CTA order: deterministic sum
                         const int c_first_tile = static_cast<int>(unit_begin(c, p.total_units, ctas) / S);
                         const float* src = p.workspace +
-                                           static_cast<long long>(c * 2 + (tile == c_first_tile ? 0 : 1)) * (NMMA * kTileRows);
+                                           static_cast<long long>(c * 2 + (tile == c_first_tile ? 0 : 1)) * (32 * kTileRows);
 #pragma unroll
-                        for (int j = 0; j < NMMA; ++j) acc[j] += __ldcg(src + j * kTileRows + tid);
+                        for (int j = 0; j < NREAD; ++j)
+                            if (j < p.m) acc[j] += __ldcg(src + j * kTileRows + tid);
                     }
                     if (tid == 0) p.counters[tile] = 0;
                 }
@@ -398,13 +419,13 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
                 if (p.swiglu) {
                     if (wg == 1) {
 #pragma unroll
-                        for (int j = 0; j < NMMA; ++j) xchg[j * kHalfRows + t] = acc[j];
+                        for (int j = 0; j < NREAD; ++j) xchg[j * kHalfRows + t] = acc[j];
                     }
                     named_barrier_sync(1, kConsumerThreads);
                     if (wg == 0 && valid) {
                         OutT* y = static_cast<OutT*>(p.seg[0].y);
 #pragma unroll
-                        for (int j = 0; j < NMMA; ++j) {
+                        for (int j = 0; j < NREAD; ++j) {
                             if (j < p.m) {
                                 const float g = acc[j];
                                 const float up = xchg[j * kHalfRows + t];
@@ -418,7 +439,7 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
                     OutT* y = static_cast<OutT*>(sg.y);
                     const float b = sg.bias ? sg.bias[my_row] : 0.f;
 #pragma unroll
-                    for (int j = 0; j < NMMA; ++j) {
+                    for (int j = 0; j < NREAD; ++j) {
                         if (j < p.m) {
                             const float v = sg.bias ? acc[j] + b : acc[j];
                             store_out<OutT>(y + static_cast<long long>(j) * sg.ldy + my_row, v);
@@ -481,9 +502,9 @@ bool encode_x_map(CUtensorMap* map, const __half* x, long long m, long long k, i
                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int NMMA, typename OutT>
+template <int NMMA, int NREAD, typename OutT>
 cudaError_t launch(const Params& p, int ctas, cudaStream_t stream) {
-    auto kern = w4a16_tc_kernel<NMMA, OutT>;
+    auto kern = w4a16_tc_kernel<NMMA, NREAD, OutT>;
     static bool configured = false;  // per instantiation; the attribute is per device-function
     static int configured_dev = -1;
     int dev = 0;
@@ -552,10 +573,23 @@ int tc_launch(cudaStream_t stream, const void* x, const TcProj* proj, int num, b
     p.workspace = workspace;
     p.counters = counters;
     p.status = status;
-    const int ctas = static_cast<int>(p.total_units < num_sms ? p.total_units : num_sms);
+    // CTA count.  With at least one tile per SM the units are cut evenly over one CTA per SM (tiles that
+    // straddle two CTAs are summed by the later one).  With fewer tiles every tile is split into the same
+    // whole number of K ranges, so unit ranges stay tile-aligned and a tile covered by one CTA needs no
+    // second pass at all.
+    int ctas;
+    if (tiles >= num_sms) {
+        ctas = num_sms;
+    } else {
+        int splits = num_sms / tiles;
+        if (splits > p.stages) splits = p.stages;
+        if (splits < 1) splits = 1;
+        ctas = tiles * splits;
+    }
     cudaError_t e;
-    if (nmma == 16) e = out_f32 ? launch<16, float>(p, ctas, stream) : launch<16, __half>(p, ctas, stream);
-    else e = out_f32 ? launch<32, float>(p, ctas, stream) : launch<32, __half>(p, ctas, stream);
+    if (m <= 8) e = out_f32 ? launch<16, 8, float>(p, ctas, stream) : launch<16, 8, __half>(p, ctas, stream);
+    else if (m <= 16) e = out_f32 ? launch<16, 16, float>(p, ctas, stream) : launch<16, 16, __half>(p, ctas, stream);
+    else e = out_f32 ? launch<32, 32, float>(p, ctas, stream) : launch<32, 32, __half>(p, ctas, stream);
     return e == cudaSuccess ? 0 : -1;
 }
 
