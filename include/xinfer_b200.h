@@ -166,6 +166,49 @@ XINFER_EXPORT int xinfer_speculative_accept_reject_batched(xinfer_stream_t s, co
 XINFER_EXPORT int xinfer_philox_uniform(xinfer_stream_t s, float* out_dev, int64_t n, uint64_t seed,
                                         uint64_t subsequence);
 
+/* ---- speculative decode runtime -------------------------------------------------------------------
+ * A random-init Qwen-hybrid target (Gated-DeltaNet + full-attention layers, INT4-G128 weights), one MTP
+ * draft head, and the step   k draft passes -> batched verify (k+1 rows per sequence) -> acceptance ->
+ * commit   for `batch` independent sequences.  Stands in for the speculative loop of Engine::generate
+ * (src/runtime/engine.cpp:400-525), draft_decode_loop / forward_verify
+ * (src/targets/qwen3_8/forward.cpp:600-734) and DecodeGraph (src/targets/qwen3_8/decode_graph.h:18-60;
+ * xinfer_spec_decoder_capture records the whole step into one CUDA graph, token ids and positions
+ * living in device memory as in the reference).  The MTP head has no counterpart in the reference. */
+typedef struct xinfer_model_config {   /* the shape fields of ModelConfig, src/targets/qwen3_8_27b/weights.h:58-107 */
+    int64_t hidden_size;
+    int64_t intermediate_size;
+    int64_t num_hidden_layers;
+    int64_t num_attention_heads;       /* head_dim is 256 */
+    int64_t num_key_value_heads;
+    int64_t vocab_size;
+    int64_t linear_num_v_heads;        /* Gated-DeltaNet head dims are 128 */
+    int64_t linear_num_k_heads;
+    int32_t full_attention_interval;   /* layer l is full attention iff l % interval == interval - 1 */
+    int32_t rope_dim;
+    float rms_norm_eps;
+    float rope_theta;
+} xinfer_model_config;
+typedef struct xinfer_spec_decoder xinfer_spec_decoder;
+XINFER_EXPORT int xinfer_spec_decoder_create(const xinfer_model_config* cfg, int batch, int k, int64_t max_seq,
+                                             uint64_t seed, xinfer_spec_decoder** out);
+XINFER_EXPORT void xinfer_spec_decoder_destroy(xinfer_spec_decoder* d);
+/* Synthetic context of `context_len` positions per sequence: random KV cache and recurrent state. */
+XINFER_EXPORT int xinfer_spec_decoder_reset(xinfer_spec_decoder* d, int64_t context_len, uint64_t seed);
+XINFER_EXPORT int xinfer_spec_decoder_set_tokens(xinfer_spec_decoder* d, const int64_t* cur_tokens_host);
+/* Enqueues one speculative step (replays the captured graph when there is one). */
+XINFER_EXPORT int xinfer_spec_decoder_step(xinfer_spec_decoder* d, xinfer_stream_t stream);
+XINFER_EXPORT int xinfer_spec_decoder_capture(xinfer_spec_decoder* d, xinfer_stream_t stream);
+/* Synchronous: emitted_host [batch][k+1] (accepted drafts, then the bonus token, then -1), counts_host [batch]. */
+XINFER_EXPORT int xinfer_spec_decoder_results(xinfer_spec_decoder* d, xinfer_stream_t stream, int64_t* emitted_host,
+                                              int* counts_host);
+/* Test hook (eager steps only): the next steps verify `drafts_host` [batch][k] instead of the MTP head's
+ * tokens; the draft passes still run.  NULL disarms it. */
+XINFER_EXPORT int xinfer_spec_decoder_override_drafts(xinfer_spec_decoder* d, const int64_t* drafts_host);
+/* what: 0 weight bytes, 1 state bytes, 2 kernel launches per step, 3 graph captured */
+XINFER_EXPORT int64_t xinfer_spec_decoder_info(const xinfer_spec_decoder* d, int what);
+XINFER_EXPORT void* xinfer_spec_decoder_tensor(xinfer_spec_decoder* d, int layer, const char* name, int64_t* bytes);
+XINFER_EXPORT const char* xinfer_spec_decoder_error(const xinfer_spec_decoder* d);
+
 /* ---- device arena ------------------------------------------------------------------------------
  * cudaMalloc-backed bump allocator.  Replaces xinfer::core::DeviceArena, src/core/arena.h:14-66
  * (impl src/core/arena.cpp:84-139): 64-byte default alignment, allocate(0) -> NULL, overflow ->
@@ -183,6 +226,12 @@ XINFER_EXPORT size_t xinfer_arena_allocated_bytes(const xinfer_arena* a);
 XINFER_EXPORT size_t xinfer_arena_remaining_bytes(const xinfer_arena* a);
 XINFER_EXPORT size_t xinfer_arena_peak_allocated_bytes(const xinfer_arena* a);
 XINFER_EXPORT void* xinfer_arena_base_ptr(xinfer_arena* a);
+
+/* Synchronous copies between host memory and raw device pointers handed out by this library (arena blocks,
+ * decoder tensors).  The reference's counterpart is DeviceContext::copy_host_to_device /
+ * copy_device_to_host, src/core/device.h:26-72. */
+XINFER_EXPORT int xinfer_copy_device_to_host(void* dst_host, const void* src_dev, size_t bytes);
+XINFER_EXPORT int xinfer_copy_host_to_device(void* dst_dev, const void* src_host, size_t bytes);
 
 /* ---- artifact checksum (kept unchanged) -------------------------------------------------------
  * The two exports of the reference's xinfer_artifact_c library, src/artifact/c_api.h:12-20:

@@ -193,3 +193,104 @@ def reference_crc_lib():
     ref.xinfer_crc64_file.restype = C.c_uint64
     ref.xinfer_crc64_file.argtypes = [C.c_char_p, C.c_uint64]
     return ref
+
+
+# ------------------------------------------------------------------------------------------------
+# Per-layer glue (mixers_oracle.cpp).  fp16 arrays are numpy float16; states are float32, updated in place.
+# ------------------------------------------------------------------------------------------------
+def _h(a):
+    return np.ascontiguousarray(a, dtype=np.float16)
+
+
+def embed(table_bf16_bits: np.ndarray, tokens, vocab: int) -> np.ndarray:
+    """embed_tokens_lookup (src/targets/qwen3_8/forward.cpp:17-64); table given as uint16 bf16 bits."""
+    table = _c(table_bf16_bits, np.uint16)
+    toks = _c(tokens, np.int64)
+    hidden = table.shape[1]
+    out = np.empty((toks.size, hidden), np.float16)
+    lib().oracle_embed(_p(out), _p(table), _p(toks), C.c_int64(toks.size), C.c_int64(hidden), C.c_int64(vocab))
+    return out
+
+
+def rmsnorm_f16(x, w, eps: float = 1e-6) -> np.ndarray:
+    x = _h(x)
+    w = _c(w, np.float32)
+    hidden = x.shape[-1]
+    out = np.empty_like(x)
+    lib().oracle_rmsnorm_f16(_p(out), _p(x), _p(w), C.c_int64(x.size // hidden), C.c_int64(hidden), C.c_float(eps))
+    return out
+
+
+def add_inplace_f16(a, b) -> np.ndarray:
+    a = _h(a).copy()
+    b = _h(b)
+    lib().oracle_add_inplace_f16(_p(a), _p(b), C.c_int64(a.size))
+    return a
+
+
+def rope_f16(q, k, positions, theta: float, rotary_dim: int):
+    """In place on copies; q [T, hq, hd], k [T, hkv, hd]."""
+    q = _h(q).copy()
+    k = _h(k).copy()
+    pos = _c(positions, np.int64)
+    T, hq, hd = q.shape
+    lib().oracle_rope_f16(_p(q), _p(k), C.c_int64(T), C.c_int64(hq), C.c_int64(k.shape[1]), C.c_int64(hd), _p(pos),
+                          C.c_float(theta), C.c_int64(rotary_dim))
+    return q, k
+
+
+def kv_write(k_cache, v_cache, k_in, v_in, start_pos: int):
+    """Caches [max_seq, hkv, hd] float16, modified in place."""
+    assert k_cache.dtype == np.float16 and k_cache.flags.c_contiguous
+    k_in, v_in = _h(k_in), _h(v_in)
+    T, hkv, hd = k_in.shape
+    lib().oracle_kv_write(_p(k_cache), _p(v_cache), _p(k_in), _p(v_in), C.c_int64(start_pos), C.c_int64(T),
+                          C.c_int64(hkv), C.c_int64(hd), C.c_int64(k_cache.shape[0]))
+
+
+def sdpa_cached(q, k_cache, v_cache, start_pos: int) -> np.ndarray:
+    q = _h(q)
+    T, hq, hd = q.shape
+    out = np.zeros_like(q)
+    lib().oracle_sdpa_cached(_p(out), _p(q), _p(k_cache), _p(v_cache), C.c_int64(start_pos), C.c_int64(T),
+                             C.c_int64(hq), C.c_int64(k_cache.shape[1]), C.c_int64(hd), C.c_float(0.0),
+                             C.c_int64(k_cache.shape[0]))
+    return out
+
+
+def conv1d_silu(x, conv_w, conv_state) -> np.ndarray:
+    """x [T, C] fp16; conv_state [3, C] float32 updated in place (or None)."""
+    x = _h(x)
+    w = _c(conv_w, np.float32)
+    out = np.empty_like(x)
+    if conv_state is not None:
+        assert conv_state.dtype == np.float32 and conv_state.flags.c_contiguous
+    lib().oracle_conv1d_silu(_p(out), _p(x), _p(w), C.c_int64(x.shape[0]), _p(conv_state), C.c_int64(x.shape[1]))
+    return out
+
+
+def gdn(qkv, z, b, a, A_log, dt_bias, norm_w, state, hv: int, hk: int, zero_state: bool = False) -> np.ndarray:
+    """state [hv, 128, 128] float32 updated in place."""
+    qkv, z, b, a = _h(qkv), _h(z), _h(b), _h(a)
+    assert state.dtype == np.float32 and state.flags.c_contiguous
+    T = qkv.shape[0]
+    out = np.empty((T, hv * 128), np.float16)
+    lib().oracle_gdn(_p(out), _p(qkv), _p(z), _p(b), _p(a), _p(_c(A_log, np.float32)), _p(_c(dt_bias, np.float32)),
+                     _p(_c(norm_w, np.float32)), _p(state), C.c_int64(T), C.c_int(1 if zero_state else 0),
+                     C.c_int64(hv), C.c_int64(hk))
+    return out
+
+
+def split_q(q_gate, hq: int, hd: int) -> np.ndarray:
+    q_gate = _h(q_gate)
+    T = q_gate.shape[0]
+    out = np.empty((T, hq, hd), np.float16)
+    lib().oracle_split_q(_p(out), _p(q_gate), C.c_int64(T), C.c_int64(hq), C.c_int64(hd))
+    return out
+
+
+def gate_output(attn, q_gate, hq: int, hd: int) -> np.ndarray:
+    attn = _h(attn).copy()
+    q_gate = _h(q_gate)
+    lib().oracle_gate_output(_p(attn), _p(q_gate), C.c_int64(attn.shape[0]), C.c_int64(hq), C.c_int64(hd))
+    return attn

@@ -1,0 +1,128 @@
+"""CPU oracle of the speculative step, sequence by sequence, token by token (test infrastructure).
+
+A literal composition of the reference's per-layer forward (src/targets/qwen3_8/forward.cpp:96-308)
+from the oracle's restatements of its kernels, plus the pieces the reference does not have and this
+repository defines: the MTP draft head and the (k+1)-row verify / accept / commit step.  Rejected
+tokens are handled the slow, obviously-correct way: recurrent state is restored from a copy taken before
+the verify pass and the accepted tokens are run again.
+"""
+from __future__ import annotations
+
+import numpy as np
+
+import oracle
+
+
+class OracleLayer:
+    def __init__(self, full, w):
+        self.full = full
+        self.w = w  # dict name -> numpy array
+
+
+def linear16(x16, W, S):
+    """fp16 activations -> fp16 output through the fp64-accumulate linear oracle."""
+    return oracle.linear_int4_f64(np.asarray(x16, np.float16).astype(np.float32), W, S).astype(np.float16)
+
+
+class OracleModel:
+    def __init__(self, shape, layers, mtp_layer, top, k):
+        self.s, self.layers, self.mtp_layer, self.top, self.k = shape, layers, mtp_layer, top, k
+
+    # one sequence: x [T, H] fp16, positions start_pos .. start_pos + T - 1
+    def forward_layer(self, L, x, start_pos, st):
+        s = self.s
+        w = L.w
+        T = x.shape[0]
+        normed = oracle.rmsnorm_f16(x, w["input_norm"], s.rms_norm_eps)
+        if L.full:
+            hq, hkv = s.num_attention_heads, s.num_key_value_heads
+            q_gate = linear16(normed, w["q_proj.w"], w["q_proj.s"])
+            kk = linear16(normed, w["k_proj.w"], w["k_proj.s"])
+            vv = linear16(normed, w["v_proj.w"], w["v_proj.s"])
+            q = oracle.split_q(q_gate, hq, 256)
+            q = oracle.rmsnorm_f16(q.reshape(T * hq, 256), w["q_norm"], s.rms_norm_eps).reshape(T, hq, 256)
+            kk = oracle.rmsnorm_f16(kk.reshape(T * hkv, 256), w["k_norm"], s.rms_norm_eps).reshape(T, hkv, 256)
+            pos = np.arange(start_pos, start_pos + T, dtype=np.int64)
+            q, kk = oracle.rope_f16(q, kk, pos, s.rope_theta, s.rope_dim)
+            oracle.kv_write(st["k_cache"], st["v_cache"], kk, vv.reshape(T, hkv, 256), start_pos)
+            attn = oracle.sdpa_cached(q, st["k_cache"], st["v_cache"], start_pos)
+            attn = oracle.gate_output(attn.reshape(T, hq, 256), q_gate, hq, 256).reshape(T, hq * 256)
+            proj = linear16(attn, w["o_proj.w"], w["o_proj.s"])
+        else:
+            hv, hk = s.linear_num_v_heads, s.linear_num_k_heads
+            qkv = linear16(normed, w["in_qkv.w"], w["in_qkv.s"])
+            z = linear16(normed, w["in_z.w"], w["in_z.s"])
+            b = linear16(normed, w["in_b.w"], w["in_b.s"])
+            a = linear16(normed, w["in_a.w"], w["in_a.s"])
+            conv = oracle.conv1d_silu(qkv, w["conv_w"], st["conv_state"])
+            delta = oracle.gdn(conv, z, b, a, w["A_log"], w["dt_bias"], w["gdn_norm"], st["S"], hv, hk)
+            proj = linear16(delta, w["out_proj.w"], w["out_proj.s"])
+        x = oracle.add_inplace_f16(x, proj)
+        normed = oracle.rmsnorm_f16(x, w["post_norm"], s.rms_norm_eps)
+        act = oracle.mlp_gate_up_swiglu_f64(normed.astype(np.float32), w["gate.w"], w["gate.s"], w["up.w"],
+                                            w["up.s"]).astype(np.float16)
+        proj = linear16(act, w["down.w"], w["down.s"])
+        return oracle.add_inplace_f16(x, proj)
+
+    def target(self, tokens, start_pos, seq_state):
+        x = oracle.embed(self.top["embed"], tokens, self.s.vocab_size)
+        for L, st in zip(self.layers, seq_state["layers"]):
+            x = self.forward_layer(L, x, start_pos, st)
+        normed = oracle.rmsnorm_f16(x, self.top["final_norm"], self.s.rms_norm_eps)
+        logits = oracle.linear_int4_f64(normed.astype(np.float32), self.top["lm_head.w"], self.top["lm_head.s"])
+        return x, logits
+
+    def draft(self, tok, h_prev, pos, seq_state):
+        e = oracle.embed(self.top["embed"], [tok], self.s.vocab_size)
+        cat = np.concatenate([oracle.rmsnorm_f16(e, self.top["mtp_enorm"], self.s.rms_norm_eps),
+                              oracle.rmsnorm_f16(h_prev[None], self.top["mtp_hnorm"], self.s.rms_norm_eps)], axis=1)
+        x = linear16(cat, self.top["mtp_fc.w"], self.top["mtp_fc.s"])
+        x = self.forward_layer(self.mtp_layer, x, pos, seq_state["mtp"])
+        normed = oracle.rmsnorm_f16(x, self.top["final_norm"], self.s.rms_norm_eps)
+        logits = oracle.linear_int4_f64(normed.astype(np.float32), self.top["lm_head.w"], self.top["lm_head.s"])
+        return x[0], logits[0]
+
+    def greedy_continuation(self, seq_state, n):
+        """The n tokens the target itself would emit after cur_tok (state is left untouched)."""
+        import copy
+        st = copy.deepcopy(seq_state)
+        toks, tok = [], st["cur_tok"]
+        for i in range(n):
+            _, lg = self.target([tok], st["ctx"] + i, st)
+            tok = oracle.argmax(lg[0])
+            toks.append(tok)
+        return toks
+
+    def step(self, seq_state, draft_override=None):
+        """One speculative step of one sequence.  Returns (emitted tokens, debug dict)."""
+        k = self.k
+        ctx = seq_state["ctx"]
+        tok, h = seq_state["cur_tok"], seq_state["h_last"]
+        drafts = []
+        draft_logits = []
+        for i in range(k):
+            h, lg = self.draft(tok, h, ctx + i, seq_state)
+            tok = oracle.argmax(lg)
+            drafts.append(tok)
+            draft_logits.append(lg)
+        mtp_drafts = list(drafts)
+        if draft_override is not None:
+            drafts = [int(t) for t in draft_override]
+        # verify: save recurrent state, run k+1 rows
+        saved = [{n: (v.copy() if n in ("S", "conv_state") else v) for n, v in st.items()} for st in seq_state["layers"]]
+        tokens = [seq_state["cur_tok"]] + drafts
+        x, logits = self.target(tokens, ctx, seq_state)
+        res = oracle.speculative_accept_reject(np.array(drafts, np.int64), logits[:k])
+        na = res["num_accepted"]
+        bonus = res["bonus_or_resampled_token"] if res["has_rejected_token"] else oracle.argmax(logits[k])
+        if na < k:  # roll the recurrent state back and run the accepted prefix again
+            for st, sv in zip(seq_state["layers"], saved):
+                for n in ("S", "conv_state"):
+                    if n in st:
+                        st[n][...] = sv[n]
+            self.target(tokens[:na + 1], ctx, seq_state)
+        seq_state["ctx"] = ctx + na + 1
+        seq_state["cur_tok"] = bonus
+        seq_state["h_last"] = x[na]
+        return drafts[:na] + [bonus], {"drafts": drafts, "logits": logits, "hidden": x, "num_accepted": na,
+                                       "draft_logits": draft_logits, "mtp_drafts": mtp_drafts}

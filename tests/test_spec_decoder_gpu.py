@@ -1,0 +1,218 @@
+"""GPU parity of the per-layer mixers and of the whole speculative step against the CPU oracle.
+
+The decoder is created with a reduced shape (the kernels are the production ones; only extents shrink),
+its random weights and synthetic context are copied to the host, and the oracle replays the same step
+sequence by sequence.  Integer results (draft tokens, accepted counts, emitted tokens, context lengths)
+must match exactly; fp16 hidden states within a few fp16 roundings of the oracle (the two sides round
+identical fp32 values at every fp16 boundary except where their fp32 sums differ in the last bits)."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from oracle.model import OracleLayer, OracleModel
+
+pytestmark = pytest.mark.gpu
+
+FULL_NAMES = {"q_proj.w": np.uint8, "q_proj.s": np.float16, "k_proj.w": np.uint8, "k_proj.s": np.float16,
+              "v_proj.w": np.uint8, "v_proj.s": np.float16, "o_proj.w": np.uint8, "o_proj.s": np.float16,
+              "q_norm": np.float32, "k_norm": np.float32}
+GDN_NAMES = {"in_qkv.w": np.uint8, "in_qkv.s": np.float16, "in_z.w": np.uint8, "in_z.s": np.float16,
+             "in_b.w": np.uint8, "in_b.s": np.float16, "in_a.w": np.uint8, "in_a.s": np.float16,
+             "out_proj.w": np.uint8, "out_proj.s": np.float16, "conv_w": np.float32, "A_log": np.float32,
+             "dt_bias": np.float32, "gdn_norm": np.float32}
+COMMON = {"input_norm": np.float32, "post_norm": np.float32, "gate.w": np.uint8, "gate.s": np.float16,
+          "up.w": np.uint8, "up.s": np.float16, "down.w": np.uint8, "down.s": np.float16}
+
+
+def lin_shape(name, shape_cfg, full):
+    s = shape_cfg
+    H, F = s.hidden_size, s.intermediate_size
+    dims = {"gate": (F, H), "up": (F, H), "down": (H, F), "q_proj": (s.num_attention_heads * 512, H),
+            "k_proj": (s.num_key_value_heads * 256, H), "v_proj": (s.num_key_value_heads * 256, H),
+            "o_proj": (H, s.num_attention_heads * 256), "in_qkv": (s.conv_channels, H),
+            "in_z": (s.linear_num_v_heads * 128, H), "in_b": (s.linear_num_v_heads, H),
+            "in_a": (s.linear_num_v_heads, H), "out_proj": (H, s.linear_num_v_heads * 128),
+            "lm_head": (s.vocab_size, H), "mtp_fc": (H, 2 * H)}
+    base, kind = name.rsplit(".", 1)
+    n, k = dims[base]
+    return (n, k // 2) if kind == "w" else (n, k // 128)
+
+
+def pull_layer(dec, idx, shape_cfg):
+    full = dec.is_full(idx)
+    names = dict(COMMON)
+    names.update(FULL_NAMES if full else GDN_NAMES)
+    w = {}
+    for n, dt in names.items():
+        arr = dec.tensor(idx, n, dt)
+        if n.endswith(".w") or n.endswith(".s"):
+            arr = arr.reshape(lin_shape(n, shape_cfg, full))
+        if n == "conv_w":
+            arr = arr.reshape(shape_cfg.conv_channels, 4)
+        w[n] = arr
+    return OracleLayer(full, w)
+
+
+def pull_model(dec, shape_cfg, k):
+    L = shape_cfg.num_hidden_layers
+    layers = [pull_layer(dec, i, shape_cfg) for i in range(L)]
+    mtp = pull_layer(dec, L, shape_cfg)
+    top = {"embed": dec.tensor(-1, "embed", np.uint16).reshape(shape_cfg.vocab_size, shape_cfg.hidden_size)}
+    for n in ("final_norm", "mtp_enorm", "mtp_hnorm"):
+        top[n] = dec.tensor(-1, n, np.float32)
+    for n in ("lm_head", "mtp_fc"):
+        top[n + ".w"] = dec.tensor(-1, n + ".w", np.uint8).reshape(lin_shape(n + ".w", shape_cfg, True))
+        top[n + ".s"] = dec.tensor(-1, n + ".s", np.float16).reshape(lin_shape(n + ".s", shape_cfg, True))
+    return OracleModel(shape_cfg, layers, mtp, top, k)
+
+
+def pull_state(dec, model, shape_cfg, batch, max_seq):
+    s = shape_cfg
+    ctx = dec.tensor(-1, "ctx", np.int32)
+    cur = dec.tensor(-1, "cur_tok", np.int64)
+    h_last = dec.tensor(-1, "h_last", np.float16).reshape(batch, s.hidden_size)
+    seqs = []
+    per_layer = []
+    for i in range(s.num_hidden_layers + 1):
+        if dec.is_full(i):
+            kc = dec.tensor(i, "k_cache", np.float16).reshape(batch, max_seq, s.num_key_value_heads, 256)
+            vc = dec.tensor(i, "v_cache", np.float16).reshape(batch, max_seq, s.num_key_value_heads, 256)
+            per_layer.append(("full", kc, vc))
+        else:
+            S = dec.tensor(i, "S", np.float32).reshape(batch, s.linear_num_v_heads, 128, 128)
+            cs = dec.tensor(i, "conv_state", np.float32).reshape(batch, 3, s.conv_channels)
+            per_layer.append(("gdn", S, cs))
+    for b in range(batch):
+        layers = []
+        for kind, a0, a1 in per_layer[:-1]:
+            if kind == "full":
+                layers.append({"k_cache": np.ascontiguousarray(a0[b]), "v_cache": np.ascontiguousarray(a1[b])})
+            else:
+                layers.append({"S": np.ascontiguousarray(a0[b]), "conv_state": np.ascontiguousarray(a1[b])})
+        _, kc, vc = per_layer[-1]
+        seqs.append({"ctx": int(ctx[b]), "cur_tok": int(cur[b]), "h_last": h_last[b].copy(), "layers": layers,
+                     "mtp": {"k_cache": np.ascontiguousarray(kc[b]), "v_cache": np.ascontiguousarray(vc[b])}})
+    return seqs
+
+
+def rel_rms(got, ref):
+    got = np.asarray(got, np.float64)
+    ref = np.asarray(ref, np.float64)
+    return float(np.sqrt(np.mean((got - ref) ** 2)) / (np.sqrt(np.mean(ref ** 2)) + 1e-30))
+
+
+@pytest.fixture(scope="module")
+def small():
+    from xinfer_b200.spec import Shape, SpecDecoder
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    shape_cfg = Shape(hidden_size=1024, intermediate_size=2048, num_hidden_layers=4, num_attention_heads=4,
+                      num_key_value_heads=2, vocab_size=4096, linear_num_v_heads=6, linear_num_k_heads=2)
+    dec = SpecDecoder(shape_cfg, batch=2, k=3, max_seq=96, seed=5)
+    yield dec, shape_cfg
+    dec.close()
+
+
+def compare_step(dec, model, seqs, shape_cfg, overrides=None, tag=""):
+    B, k = dec.batch, dec.k
+    dec.override_drafts(None if overrides is None else np.array(overrides, np.int64))
+    dec.step()
+    emitted, counts = dec.results()
+    x_gpu = dec.tensor(-1, "x", np.float16).reshape(B, k + 1, shape_cfg.hidden_size)
+    logits_gpu = dec.tensor(-1, "logits", np.float32).reshape(B, k + 1, shape_cfg.vocab_size)
+    ctx_gpu = dec.tensor(-1, "ctx", np.int32)
+    accepted = []
+    for b in range(B):
+        want, dbg = model.step(seqs[b], None if overrides is None else overrides[b])
+        assert rel_rms(x_gpu[b], dbg["hidden"]) < 2e-2, (tag, b)
+        assert rel_rms(logits_gpu[b], dbg["logits"]) < 2e-2, (tag, b)
+        assert counts[b] == len(want) and emitted[b, :counts[b]].tolist() == want, (tag, b, emitted[b], want)
+        assert (emitted[b, counts[b]:] == -1).all()
+        assert ctx_gpu[b] == seqs[b]["ctx"], (tag, b)
+        accepted.append(dbg["num_accepted"])
+    dec.override_drafts(None)
+    return accepted
+
+
+@pytest.mark.parametrize("ctx0", [0, 37])
+def test_speculative_steps_match_oracle(small, ctx0):
+    """Plain steps: the MTP head drafts, the target verifies; every integer result equals the oracle's."""
+    dec, shape_cfg = small
+    dec.reset(ctx0, seed=ctx0 + 1)
+    model = pull_model(dec, shape_cfg, dec.k)
+    seqs = pull_state(dec, model, shape_cfg, dec.batch, dec.max_seq)
+    for step in range(3):
+        drafts_gpu_before = None
+        compare_step(dec, model, seqs, shape_cfg, tag=f"plain{step}")
+    assert dec.info(2) > 0
+
+
+def test_acceptance_paths_and_lazy_state_commit(small):
+    """Random weights almost never accept, so the drafts are overridden with the target's own greedy
+    continuation (all accepted), then with a corrupted copy (partial acceptance).  Each following step
+    replays the accepted recurrent updates of the one before; the tokens can only keep matching the
+    oracle (which restores and recomputes its state) if that lazy commit is exact."""
+    dec, shape_cfg = small
+    B, k = dec.batch, dec.k
+    dec.reset(25, seed=4)
+    model = pull_model(dec, shape_cfg, k)
+    seqs = pull_state(dec, model, shape_cfg, B, dec.max_seq)
+    plans = [(k, k), (1, 2), (0, k), (2, 0), (k, 1)]  # accepted drafts wanted per sequence, per step
+    for step, plan in enumerate(plans):
+        overrides = []
+        for b in range(B):
+            cont = model.greedy_continuation(seqs[b], k)
+            keep = plan[b]
+            if keep < k:
+                cont[keep] = (cont[keep] + 1 + b) % shape_cfg.vocab_size  # first wrong draft at index `keep`
+            overrides.append(cont)
+        accepted = compare_step(dec, model, seqs, shape_cfg, overrides, tag=f"forced{step}")
+        assert accepted == list(plan), (step, accepted, plan)
+    # two plain steps afterwards still agree
+    for step in range(2):
+        compare_step(dec, model, seqs, shape_cfg, tag=f"after{step}")
+
+
+def test_long_context_attention_splits():
+    """Context 2048 (the reduced-stack configuration's length): 65 key chunks over 8 splits."""
+    from xinfer_b200.spec import Shape, SpecDecoder
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    shape_cfg = Shape(hidden_size=512, intermediate_size=1024, num_hidden_layers=4, num_attention_heads=12,
+                      num_key_value_heads=2, vocab_size=2048, linear_num_v_heads=3, linear_num_k_heads=1)
+    dec = SpecDecoder(shape_cfg, batch=1, k=3, max_seq=2100, seed=11)
+    dec.reset(2048, seed=2)
+    model = pull_model(dec, shape_cfg, dec.k)
+    seqs = pull_state(dec, model, shape_cfg, dec.batch, dec.max_seq)
+    compare_step(dec, model, seqs, shape_cfg, tag="long0")
+    cont = model.greedy_continuation(seqs[0], 3)
+    compare_step(dec, model, seqs, shape_cfg, [cont], tag="long1")
+    dec.close()
+
+
+def test_graph_replay_equals_eager(small):
+    dec, shape_cfg = small
+    B, k = dec.batch, dec.k
+    from xinfer_b200.spec import SpecDecoder
+    eager = SpecDecoder(shape_cfg, batch=B, k=k, max_seq=dec.max_seq, seed=5)
+    graph = SpecDecoder(shape_cfg, batch=B, k=k, max_seq=dec.max_seq, seed=5)
+    eager.reset(30, seed=3)
+    graph.reset(30, seed=3)
+    stream = torch.cuda.Stream()
+    outs_e, outs_g = [], []
+    with torch.cuda.stream(stream):
+        eager.step()  # the capture runs one eager step first; mirror it
+        outs_e.append(eager.results())
+        graph.capture(stream)
+        outs_g.append(graph.results())
+        assert graph.info(3) == 1
+        for _ in range(3):
+            eager.step()
+            outs_e.append(eager.results())
+            graph.step()
+            outs_g.append(graph.results())
+    for (ee, ce), (eg, cg) in zip(outs_e, outs_g):
+        assert np.array_equal(ee, eg) and np.array_equal(ce, cg)
+    eager.close()
+    graph.close()

@@ -38,6 +38,15 @@ class AcceptResult(C.Structure):
                 ("reserved", C.c_int32)]
 
 
+class ModelConfig(C.Structure):
+    """xinfer_model_config: the shape fields of the reference's ModelConfig (src/targets/qwen3_8_27b/weights.h:58-107)."""
+    _fields_ = [("hidden_size", C.c_int64), ("intermediate_size", C.c_int64), ("num_hidden_layers", C.c_int64),
+                ("num_attention_heads", C.c_int64), ("num_key_value_heads", C.c_int64), ("vocab_size", C.c_int64),
+                ("linear_num_v_heads", C.c_int64), ("linear_num_k_heads", C.c_int64),
+                ("full_attention_interval", C.c_int32), ("rope_dim", C.c_int32), ("rms_norm_eps", C.c_float),
+                ("rope_theta", C.c_float)]
+
+
 class AcceptRecord(C.Structure):
     _fields_ = [("bonus_or_resampled_token", C.c_int64), ("rejected_token", C.c_int64), ("num_accepted", C.c_int32),
                 ("num_rejected", C.c_int32), ("num_resampled", C.c_int32), ("num_remaining", C.c_int32),
@@ -69,6 +78,17 @@ SIGNATURES = {
     "xinfer_speculative_accept_reject_batched": (_i32, [_vp, _vp, _vp, _i64, _i64, _vp, _vp, _f32, _i32, _i32, _i32,
                                                         _i32, _vp]),
     "xinfer_philox_uniform": (_i32, [_vp, _vp, _i64, _u64, _u64]),
+    "xinfer_spec_decoder_create": (_i32, [_vp, _i32, _i32, _i64, _u64, C.POINTER(_vp)]),
+    "xinfer_spec_decoder_destroy": (None, [_vp]),
+    "xinfer_spec_decoder_reset": (_i32, [_vp, _i64, _u64]),
+    "xinfer_spec_decoder_set_tokens": (_i32, [_vp, _vp]),
+    "xinfer_spec_decoder_step": (_i32, [_vp, _vp]),
+    "xinfer_spec_decoder_capture": (_i32, [_vp, _vp]),
+    "xinfer_spec_decoder_results": (_i32, [_vp, _vp, _vp, _vp]),
+    "xinfer_spec_decoder_override_drafts": (_i32, [_vp, _vp]),
+    "xinfer_spec_decoder_info": (_i64, [_vp, _i32]),
+    "xinfer_spec_decoder_tensor": (_vp, [_vp, _i32, C.c_char_p, C.POINTER(_i64)]),
+    "xinfer_spec_decoder_error": (C.c_char_p, [_vp]),
     "xinfer_arena_create": (_i32, [_sz, _sz, C.POINTER(_vp)]),
     "xinfer_arena_destroy": (None, [_vp]),
     "xinfer_arena_allocate": (_i32, [_vp, _sz, _sz, C.POINTER(_vp)]),
@@ -80,6 +100,8 @@ SIGNATURES = {
     "xinfer_arena_remaining_bytes": (_sz, [_vp]),
     "xinfer_arena_peak_allocated_bytes": (_sz, [_vp]),
     "xinfer_arena_base_ptr": (_vp, [_vp]),
+    "xinfer_copy_device_to_host": (_i32, [_vp, _vp, _sz]),
+    "xinfer_copy_host_to_device": (_i32, [_vp, _vp, _sz]),
     "xinfer_crc64": (_u64, [_vp, _sz]),
     "xinfer_crc64_file": (_u64, [C.c_char_p, _u64]),
 }

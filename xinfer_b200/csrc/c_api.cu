@@ -338,6 +338,19 @@ int xinfer_philox_uniform(xinfer_stream_t s, float* out_dev, int64_t n, uint64_t
     return XINFER_OK;
 }
 
+int xinfer_copy_device_to_host(void* dst_host, const void* src_dev, size_t bytes) {
+    if (bytes == 0) return XINFER_OK;
+    if (!dst_host || !src_dev) return XINFER_ERR_INVALID_ARGUMENT;
+    cudaError_t e = cudaMemcpy(dst_host, src_dev, bytes, cudaMemcpyDeviceToHost);
+    return e == cudaSuccess ? XINFER_OK : fail_cuda(e);
+}
+int xinfer_copy_host_to_device(void* dst_dev, const void* src_host, size_t bytes) {
+    if (bytes == 0) return XINFER_OK;
+    if (!dst_dev || !src_host) return XINFER_ERR_INVALID_ARGUMENT;
+    cudaError_t e = cudaMemcpy(dst_dev, src_host, bytes, cudaMemcpyHostToDevice);
+    return e == cudaSuccess ? XINFER_OK : fail_cuda(e);
+}
+
 // ------------------------------------------------------------------------------------ checksum
 uint64_t xinfer_crc64(const void* data, size_t length) {
     if (!data || length == 0) return 0ull;

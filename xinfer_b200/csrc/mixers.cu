@@ -1,0 +1,661 @@
+// Per-layer glue of the speculative decode / verify step: embedding lookup, RMSNorm (+ residual add),
+// the full-attention mixer (q/k head norm, partial RoPE, KV-cache write, split-KV GQA attention over an
+// fp16 cache, sigmoid output gate) and the Gated-DeltaNet mixer (causal conv1d + SiLU, gated delta-rule
+// recurrence with fused gated RMSNorm).
+//
+// Semantics follow the reference's kernels; every fp16 rounding point of the reference is kept so
+// that a CPU restatement of the reference agrees to the last fp16 bit in most elements:
+//   embed_tokens_lookup            src/targets/qwen3_8/forward.cpp:17-64
+//   rmsnorm                        src/ops/rmsnorm.cpp:15-82
+//   add_inplace (fp16)             src/ops/elementwise.cpp:213-236
+//   q/gate split, sigmoid gating   src/targets/qwen3_8/forward.cpp:145-151, 217-226
+//   rope                           src/ops/rope.cpp:12-62
+//   attention_write_kv_cache       src/ops/attention.cpp:84-116
+//   sdpa_causal_cached             src/ops/attention.cpp:151-243
+//   causal_conv1d_silu             src/targets/qwen3_8/linear_attn.cpp:37-122
+//   recurrent_gated_delta_net      src/targets/qwen3_8/linear_attn.cpp:144-343
+//
+// What is different is the batching and the speculative state handling, which the reference does not
+// have: rows are (sequence b, position i) with i < R, R = 1 while drafting and k+1 while verifying;
+// sequence b sees keys below ctx[b] + i + 1; and the recurrent states (DeltaNet S, conv window) are
+// committed lazily: a step stores its per-token updates, and the NEXT step first replays the
+// n_commit[b] accepted ones onto the stored state, bit-identically, before it processes new tokens.
+// Nothing is copied or restored when draft tokens are rejected.
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <math.h>
+#include <stdint.h>
+
+#include "mixers.h"
+
+namespace xb {
+
+namespace {
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+    return v;
+}
+
+// block-wide sum for up to 1024 threads; every thread gets the result
+__device__ __forceinline__ float block_sum(float v, float* smem) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) smem[warp] = v;
+    __syncthreads();
+    float t = (lane < nw) ? smem[lane] : 0.f;
+    t = warp_sum(t);
+    return t;
+}
+
+// ------------------------------------------------------------------------------- embedding
+__global__ void embed_kernel(__half* out, const uint16_t* table_bf16, const long long* tokens, int hidden, long long vocab) {
+    const int row = blockIdx.x;
+    const long long tok = tokens[row];
+    const bool ok = tok >= 0 && (vocab <= 0 || tok < vocab);
+    for (int d = threadIdx.x; d < hidden; d += blockDim.x) {
+        float v = 0.f;
+        if (ok) v = __uint_as_float(static_cast<uint32_t>(table_bf16[tok * hidden + d]) << 16);
+        out[static_cast<long long>(row) * hidden + d] = __float2half_rn(v);
+    }
+}
+
+// ------------------------------------------------------------------------------- RMSNorm family
+// mode 0: out = rmsnorm(in) * w
+// mode 1: x = half(float(x) + float(delta)); out = rmsnorm(x) * w   (residual add, then norm)
+// `out` may have a wider row (ld_out) and a column offset so that two norms can fill one concatenated row.
+__global__ void __launch_bounds__(256) rmsnorm_kernel(__half* out, long long ld_out, __half* x, const __half* delta,
+                                                      const float* w, int hidden, float eps) {
+    __shared__ float red[32];
+    const long long row = blockIdx.x;
+    __half* xr = x + row * hidden;
+    const __half* dr = delta ? delta + row * hidden : nullptr;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        float v = __half2float(xr[i]);
+        if (dr) {
+            const __half s = __float2half_rn(v + __half2float(dr[i]));
+            xr[i] = s;
+            v = __half2float(s);
+        }
+        ss += v * v;
+    }
+    const float total = block_sum(ss, red);
+    const float r = 1.0f / sqrtf(total / static_cast<float>(hidden) + eps);
+    __half* orow = out + row * ld_out;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x)
+        orow[i] = __float2half_rn(__half2float(xr[i]) * r * w[i]);
+}
+
+// ------------------------------------------------------------------------------- attention prologue
+// One block per (row, head slot); head slots 0..Hq-1 are query heads, Hq..Hq+Hkv-1 key heads,
+// Hq+Hkv..Hq+2Hkv-1 value heads.  256 threads = head_dim.
+__global__ void __launch_bounds__(256) attn_prep_kernel(__half* q_out, __half* k_cache, __half* v_cache,
+                                                        const __half* q_gate, const __half* k_in, const __half* v_in,
+                                                        const float* q_norm_w, const float* k_norm_w, const int* ctx,
+                                                        int rows_per_seq, int hq, int hkv, long long max_seq,
+                                                        float eps, float log_theta, int rope_dim) {
+    __shared__ float red[32];
+    __shared__ float vals[256];
+    const int row = blockIdx.x;
+    const int slot = blockIdx.y;
+    const int d = threadIdx.x;
+    const int b = row / rows_per_seq, i = row % rows_per_seq;
+    const long long pos = static_cast<long long>(ctx[b]) + i;
+    const bool in_cache = pos >= 0 && pos < max_seq;
+    if (slot >= hq + hkv) {  // value head: plain copy into the cache
+        const int h = slot - hq - hkv;
+        if (in_cache)
+            v_cache[((static_cast<long long>(b) * max_seq + pos) * hkv + h) * 256 + d] =
+                v_in[(static_cast<long long>(row) * hkv + h) * 256 + d];
+        return;
+    }
+    const bool is_q = slot < hq;
+    const int h = is_q ? slot : slot - hq;
+    // the reference first copies q out of the interleaved [q | gate] head block (fp16, exact)
+    const float x = is_q ? __half2float(q_gate[(static_cast<long long>(row) * hq + h) * 512 + d])
+                         : __half2float(k_in[(static_cast<long long>(row) * hkv + h) * 256 + d]);
+    const float total = block_sum(x * x, red);
+    const float r = 1.0f / sqrtf(total / 256.0f + eps);
+    const float* w = is_q ? q_norm_w : k_norm_w;
+    // rounding point: the head RMSNorm writes fp16
+    const float normed = __half2float(__float2half_rn(x * r * w[d]));
+    vals[d] = normed;
+    __syncthreads();
+    float outv = normed;
+    const int half_rot = rope_dim / 2;
+    if (d < rope_dim) {
+        const int pair = d < half_rot ? d : d - half_rot;
+        const float freq = expf(-static_cast<float>(2 * pair) * (1.0f / static_cast<float>(rope_dim)) * log_theta);
+        const float angle = static_cast<float>(pos) * freq;
+        const float c = cosf(angle), s = sinf(angle);
+        const float v0 = vals[pair], v1 = vals[pair + half_rot];
+        outv = d < half_rot ? v0 * c - v1 * s : v1 * c + v0 * s;
+    }
+    const __half o = __float2half_rn(outv);
+    if (is_q) {
+        q_out[(static_cast<long long>(row) * hq + h) * 256 + d] = o;
+    } else if (in_cache) {
+        k_cache[((static_cast<long long>(b) * max_seq + pos) * hkv + h) * 256 + d] = o;
+    }
+}
+
+// ------------------------------------------------------------------------------- split-KV GQA attention
+// Grid (splits, Hkv, B), 128 threads.  The G * R query rows that share one KV head (G = Hq / Hkv, at most
+// 32 rows) form the M side of mma.sync m16n8k16 tiles; keys stream through shared memory in chunks of
+// 32 via cp.async, double buffered.  Each CTA writes an unnormalised partial (max, sum, O) per row.
+constexpr int kAttnChunk = 32;
+constexpr int kAttnLd = 264;  // padded row of 256 halves (528 B): conflict-free ldmatrix
+constexpr int kAttnRows = 32;
+
+struct AttnSmem {
+    __half q[kAttnRows][kAttnLd];
+    __half k[2][kAttnChunk][kAttnLd];
+    __half v[2][kAttnChunk][kAttnLd];
+    float s[kAttnRows][kAttnChunk + 1];
+    __half p[kAttnRows][kAttnChunk + 8];
+    float row_max[kAttnRows];
+    float row_sum[kAttnRows];
+    float row_alpha[kAttnRows];
+};
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+    const uint32_t s = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t* r, const void* p) {
+    const uint32_t a = static_cast<uint32_t>(__cvta_generic_to_shared(p));
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void ldmatrix_x2(uint32_t* r, const void* p) {
+    const uint32_t a = static_cast<uint32_t>(__cvta_generic_to_shared(p));
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0, %1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(a));
+}
+__device__ __forceinline__ void ldmatrix_x2_trans(uint32_t* r, const void* p) {
+    const uint32_t a = static_cast<uint32_t>(__cvta_generic_to_shared(p));
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0, %1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(a));
+}
+__device__ __forceinline__ void mma16816(float* c, const uint32_t* a, const uint32_t* b) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+        "{%0, %1, %2, %3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+
+__global__ void __launch_bounds__(128) attn_split_kernel(float* part_o, float* part_ml, const __half* q,
+                                                         const __half* k_cache, const __half* v_cache, const int* ctx,
+                                                         int rows_per_seq, int hq, int hkv, long long max_seq,
+                                                         float scale) {
+    extern __shared__ __align__(16) uint8_t attn_smem_raw[];
+    AttnSmem& sm = *reinterpret_cast<AttnSmem*>(attn_smem_raw);
+    const int split = blockIdx.x, nsplit = gridDim.x, kvh = blockIdx.y, b = blockIdx.z;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int G = hq / hkv;
+    const int nrows = G * rows_per_seq;  // valid query rows, row = g * R + i
+    const int ctx_b = ctx[b];
+    long long total_keys = static_cast<long long>(ctx_b) + rows_per_seq;
+    if (total_keys > max_seq) total_keys = max_seq;
+    const int nchunks = static_cast<int>((total_keys + kAttnChunk - 1) / kAttnChunk);
+    const int c_begin = static_cast<int>(static_cast<long long>(split) * nchunks / nsplit);
+    const int c_end = static_cast<int>(static_cast<long long>(split + 1) * nchunks / nsplit);
+
+    // stage the query rows (zero padded to 32)
+    for (int idx = tid; idx < kAttnRows * 32; idx += 128) {
+        const int r = idx >> 5, seg = idx & 31;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (r < nrows) {
+            const int g = r / rows_per_seq, i = r % rows_per_seq;
+            const long long row = static_cast<long long>(b) * rows_per_seq + i;
+            v = *reinterpret_cast<const uint4*>(q + (row * hq + kvh * G + g) * 256 + seg * 8);
+        }
+        *reinterpret_cast<uint4*>(&sm.q[r][seg * 8]) = v;
+    }
+    if (tid < kAttnRows) {
+        sm.row_max[tid] = -INFINITY;
+        sm.row_sum[tid] = 0.f;
+    }
+
+    auto load_chunk = [&](int c, int buf) {
+        const long long key0 = static_cast<long long>(c) * kAttnChunk;
+        for (int idx = tid; idx < kAttnChunk * 32; idx += 128) {
+            const int r = idx >> 5, seg = idx & 31;
+            long long key = key0 + r;
+            if (key >= total_keys) key = total_keys - 1;  // clamped rows are masked out below
+            const long long off = ((static_cast<long long>(b) * max_seq + key) * hkv + kvh) * 256 + seg * 8;
+            cp_async16(&sm.k[buf][r][seg * 8], k_cache + off);
+            cp_async16(&sm.v[buf][r][seg * 8], v_cache + off);
+        }
+        cp_async_commit();
+    };
+
+    float o_acc[2][8][4];
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) o_acc[mt][nt][e] = 0.f;
+
+    if (c_begin < c_end) load_chunk(c_begin, 0);
+    for (int c = c_begin; c < c_end; ++c) {
+        const int buf = (c - c_begin) & 1;
+        if (c + 1 < c_end) {
+            load_chunk(c + 1, buf ^ 1);
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+
+        // S = Q K^T: warp w owns keys [8w, 8w+8) of the chunk, both 16-row tiles
+        {
+            float s_acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+            for (int ks = 0; ks < 16; ++ks) {
+                uint32_t bfr[2];
+                ldmatrix_x2(bfr, &sm.k[buf][warp * 8 + (lane & 7)][ks * 16 + ((lane >> 3) & 1) * 8]);
+#pragma unroll
+                for (int mt = 0; mt < 2; ++mt) {
+                    uint32_t afr[4];
+                    ldmatrix_x4(afr, &sm.q[mt * 16 + (lane & 15)][ks * 16 + (lane >> 4) * 8]);
+                    mma16816(s_acc[mt], afr, bfr);
+                }
+            }
+            const int g4 = lane >> 2, t4 = lane & 3;
+#pragma unroll
+            for (int mt = 0; mt < 2; ++mt) {
+                sm.s[mt * 16 + g4][warp * 8 + t4 * 2] = s_acc[mt][0];
+                sm.s[mt * 16 + g4][warp * 8 + t4 * 2 + 1] = s_acc[mt][1];
+                sm.s[mt * 16 + g4 + 8][warp * 8 + t4 * 2] = s_acc[mt][2];
+                sm.s[mt * 16 + g4 + 8][warp * 8 + t4 * 2 + 1] = s_acc[mt][3];
+            }
+        }
+        __syncthreads();
+
+        // online softmax: 4 threads per row, 8 keys each
+        {
+            const int r = tid >> 2, part = tid & 3;
+            const int i = r % rows_per_seq;
+            const long long limit = static_cast<long long>(ctx_b) + i + 1;  // keys visible to this row
+            const long long key0 = static_cast<long long>(c) * kAttnChunk + part * 8;
+            float sc[8];
+            float mx = -INFINITY;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const bool vis = (r < nrows) && (key0 + j < limit) && (key0 + j < total_keys);
+                sc[j] = vis ? sm.s[r][part * 8 + j] * scale : -INFINITY;
+                mx = fmaxf(mx, sc[j]);
+            }
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+            const float old_max = sm.row_max[r];
+            const float new_max = fmaxf(old_max, mx);
+            float sum = 0.f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const float pv = (sc[j] == -INFINITY) ? 0.f : expf(sc[j] - new_max);
+                sum += pv;
+                sm.p[r][part * 8 + j] = __float2half_rn(pv);
+            }
+            sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+            sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+            __syncwarp();
+            if (part == 0) {
+                const float alpha = (old_max == -INFINITY) ? 0.f : expf(old_max - new_max);
+                sm.row_alpha[r] = alpha;
+                sm.row_sum[r] = sm.row_sum[r] * alpha + sum;
+                sm.row_max[r] = new_max;
+            }
+        }
+        __syncthreads();
+
+        // O = alpha * O + P V: warp w owns output dims [64w, 64w+64)
+        {
+            const int g4 = lane >> 2;
+#pragma unroll
+            for (int mt = 0; mt < 2; ++mt) {
+                const float a0 = sm.row_alpha[mt * 16 + g4], a1 = sm.row_alpha[mt * 16 + g4 + 8];
+#pragma unroll
+                for (int nt = 0; nt < 8; ++nt) {
+                    o_acc[mt][nt][0] *= a0;
+                    o_acc[mt][nt][1] *= a0;
+                    o_acc[mt][nt][2] *= a1;
+                    o_acc[mt][nt][3] *= a1;
+                }
+            }
+#pragma unroll
+            for (int ks = 0; ks < kAttnChunk / 16; ++ks) {
+                uint32_t afr[2][4];
+#pragma unroll
+                for (int mt = 0; mt < 2; ++mt)
+                    ldmatrix_x4(afr[mt], &sm.p[mt * 16 + (lane & 15)][ks * 16 + (lane >> 4) * 8]);
+#pragma unroll
+                for (int nt = 0; nt < 8; ++nt) {
+                    uint32_t bfr[2];
+                    ldmatrix_x2_trans(bfr, &sm.v[buf][ks * 16 + (lane & 15)][warp * 64 + nt * 8]);
+#pragma unroll
+                    for (int mt = 0; mt < 2; ++mt) mma16816(o_acc[mt][nt], afr[mt], bfr);
+                }
+            }
+        }
+        __syncthreads();
+    }
+
+    // write the partial: O [rows][256] fp32, (max, sum) per row
+    const long long pbase = (static_cast<long long>(b) * hkv + kvh) * nsplit + split;
+    float* po = part_o + pbase * (kAttnRows * 256);
+    const int g4 = lane >> 2, t4 = lane & 3;
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt) {
+            const int col = warp * 64 + nt * 8 + t4 * 2;
+            const int r0 = mt * 16 + g4;
+            if (r0 < nrows) *reinterpret_cast<float2*>(po + r0 * 256 + col) = make_float2(o_acc[mt][nt][0], o_acc[mt][nt][1]);
+            if (r0 + 8 < nrows)
+                *reinterpret_cast<float2*>(po + (r0 + 8) * 256 + col) = make_float2(o_acc[mt][nt][2], o_acc[mt][nt][3]);
+        }
+    if (tid < nrows) {
+        part_ml[pbase * (kAttnRows * 2) + tid * 2] = sm.row_max[tid];
+        part_ml[pbase * (kAttnRows * 2) + tid * 2 + 1] = sm.row_sum[tid];
+    }
+}
+
+// Merge the splits, normalise, apply the sigmoid output gate, write fp16 [rows][Hq * 256].
+// Grid (G * R, Hkv, B), 256 threads = head_dim.
+__global__ void __launch_bounds__(256) attn_combine_kernel(__half* out, const float* part_o, const float* part_ml,
+                                                           const __half* q_gate, int nsplit, int rows_per_seq, int hq,
+                                                           int hkv) {
+    const int r = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z, d = threadIdx.x;
+    const int G = hq / hkv;
+    const int g = r / rows_per_seq, i = r % rows_per_seq;
+    const long long pbase = (static_cast<long long>(b) * hkv + kvh) * nsplit;
+    float m = -INFINITY;
+    for (int s = 0; s < nsplit; ++s) m = fmaxf(m, part_ml[(pbase + s) * (kAttnRows * 2) + r * 2]);
+    float acc = 0.f, l = 0.f;
+    for (int s = 0; s < nsplit; ++s) {
+        const float ms = part_ml[(pbase + s) * (kAttnRows * 2) + r * 2];
+        if (ms == -INFINITY) continue;
+        const float w = expf(ms - m);
+        l += part_ml[(pbase + s) * (kAttnRows * 2) + r * 2 + 1] * w;
+        acc += part_o[(pbase + s) * (kAttnRows * 256) + r * 256 + d] * w;
+    }
+    const float inv = 1.0f / (l > 0.f ? l : 1.0f);
+    const long long row = static_cast<long long>(b) * rows_per_seq + i;
+    const int h = kvh * G + g;
+    // rounding point: the reference's SDPA writes fp16, the gate then multiplies in fp32
+    const float attn = __half2float(__float2half_rn(acc * inv));
+    const float gate = __half2float(q_gate[(row * hq + h) * 512 + 256 + d]);
+    const float sig = 1.0f / (1.0f + expf(-gate));
+    out[(row * hq + h) * 256 + d] = __float2half_rn(attn * sig);
+}
+
+// ------------------------------------------------------------------------------- causal conv1d + SiLU
+// One thread per (sequence, channel).  state [B][3][C] holds the last three committed inputs; pending
+// [B][Rmax][C] the raw inputs of the previous step, of which the first n_commit[b] were accepted.
+__global__ void conv1d_spec_kernel(__half* out, const __half* in, const float* conv_w, float* state, float* pending,
+                                   const int* n_commit, int rows_per_seq, int prev_rows, int channels) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    const int b = blockIdx.y;
+    if (c >= channels) return;
+    float* st = state + static_cast<long long>(b) * 3 * channels;
+    float* pd = pending + static_cast<long long>(b) * 8 * channels;
+    float s0 = st[c], s1 = st[channels + c], s2 = st[2 * channels + c];
+    int nc = n_commit ? n_commit[b] : 0;
+    if (nc > prev_rows) nc = prev_rows;
+    for (int i = 0; i < nc; ++i) {  // replay the accepted inputs of the previous step
+        s0 = s1;
+        s1 = s2;
+        s2 = pd[i * channels + c];
+    }
+    st[c] = s0;
+    st[channels + c] = s1;
+    st[2 * channels + c] = s2;
+    const float w0 = conv_w[c * 4], w1 = conv_w[c * 4 + 1], w2 = conv_w[c * 4 + 2], w3 = conv_w[c * 4 + 3];
+    for (int i = 0; i < rows_per_seq; ++i) {
+        const long long row = static_cast<long long>(b) * rows_per_seq + i;
+        const float x = __half2float(in[row * channels + c]);
+        const float sum = w0 * s0 + w1 * s1 + w2 * s2 + w3 * x;
+        out[row * channels + c] = __float2half_rn(sum / (1.0f + expf(-sum)));
+        pd[i * channels + c] = x;
+        s0 = s1;
+        s1 = s2;
+        s2 = x;
+    }
+}
+
+// ------------------------------------------------------------------------------- Gated DeltaNet recurrence
+// Grid (v heads, B), 128 threads; thread j owns column j of the 128 x 128 fp32 state, in registers.
+// pend_k [B][Hv][8][128] normalised keys, pend_d [B][Hv][8][128] deltas, pend_g [B][Hv][8] decay factors of
+// the previous step.
+__global__ void __launch_bounds__(128) gdn_spec_kernel(__half* out, const __half* qkv, const __half* z,
+                                                       const __half* bb, const __half* aa, const float* A_log,
+                                                       const float* dt_bias, const float* norm_w, float* state,
+                                                       float* pend_k, float* pend_d, float* pend_g,
+                                                       const int* n_commit, int rows_per_seq, int prev_rows, int hv,
+                                                       int hk) {
+    __shared__ float sh_q[128], sh_k[128], red[32];
+    const int h = blockIdx.x, b = blockIdx.y, j = threadIdx.x;
+    const int h_k = h / (hv / hk);
+    const int channels = 2 * hk * 128 + hv * 128;
+    const int value_dim = hv * 128;
+    float* S = state + (static_cast<long long>(b) * hv + h) * (128 * 128);
+    const long long pbase = (static_cast<long long>(b) * hv + h) * 8;
+    float col[128];
+#pragma unroll
+    for (int i = 0; i < 128; ++i) col[i] = S[i * 128 + j];
+
+    int nc = n_commit ? n_commit[b] : 0;
+    if (nc > prev_rows) nc = prev_rows;
+    if (nc > 0) {
+        for (int t = 0; t < nc; ++t) {  // replay accepted updates: same operations, same order
+            __syncthreads();
+            sh_k[j] = pend_k[(pbase + t) * 128 + j];
+            __syncthreads();
+            const float eg = pend_g[pbase + t];
+            const float dj = pend_d[(pbase + t) * 128 + j];
+#pragma unroll
+            for (int i = 0; i < 128; ++i) {
+                const float sv = col[i] * eg;
+                col[i] = sv + sh_k[i] * dj;
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < 128; ++i) S[i * 128 + j] = col[i];
+    }
+
+    const float exp_a_log = expf(A_log[h]);
+    const float dtb = dt_bias[h];
+    for (int t = 0; t < rows_per_seq; ++t) {
+        const long long row = static_cast<long long>(b) * rows_per_seq + t;
+        const __half* cur = qkv + row * channels;
+        const float raw_q = __half2float(cur[h_k * 128 + j]);
+        const float raw_k = __half2float(cur[hk * 128 + h_k * 128 + j]);
+        const float v = __half2float(cur[2 * hk * 128 + h * 128 + j]);
+        const float inv_q = 1.0f / sqrtf(block_sum(raw_q * raw_q, red) + 1e-6f);
+        const float inv_k = 1.0f / sqrtf(block_sum(raw_k * raw_k, red) + 1e-6f);
+        __syncthreads();
+        sh_q[j] = (raw_q * inv_q) * 0.08838834764f;
+        sh_k[j] = raw_k * inv_k;
+        __syncthreads();
+        const float b_val = __half2float(bb[row * hv + h]);
+        const float beta = 1.0f / (1.0f + expf(-b_val));
+        const float a_val = __half2float(aa[row * hv + h]) + dtb;
+        const float softplus = (a_val > 20.0f) ? a_val : logf(1.0f + expf(a_val));
+        const float eg = expf(-exp_a_log * softplus);
+        float kv_mem = 0.f;
+#pragma unroll
+        for (int i = 0; i < 128; ++i) {
+            const float sv = col[i] * eg;
+            col[i] = sv;
+            kv_mem += sv * sh_k[i];
+        }
+        const float delta = (v - kv_mem) * beta;
+        float attn = 0.f;
+#pragma unroll
+        for (int i = 0; i < 128; ++i) {
+            const float ns = col[i] + sh_k[i] * delta;
+            col[i] = ns;
+            attn += ns * sh_q[i];
+        }
+        pend_k[(pbase + t) * 128 + j] = sh_k[j];
+        pend_d[(pbase + t) * 128 + j] = delta;
+        if (j == 0) pend_g[pbase + t] = eg;
+        const float var = block_sum(attn * attn, red) / 128.0f;
+        const float inv_std = 1.0f / sqrtf(var + 1e-6f);
+        const float zv = __half2float(z[row * value_dim + h * 128 + j]);
+        const float silu_z = zv / (1.0f + expf(-zv));
+        out[row * value_dim + h * 128 + j] = __float2half_rn(attn * inv_std * norm_w[j] * silu_z);
+    }
+}
+
+// ------------------------------------------------------------------------------- speculative bookkeeping
+struct AcceptRec {
+    long long bonus;
+    long long rejected;
+    int num_accepted, num_rejected, num_resampled, num_remaining, has_rejected, pad;
+};
+
+// After acceptance: per sequence, publish the emitted tokens (accepted drafts then the bonus token),
+// advance the context, remember how many recurrent updates to replay, pick the hidden row that feeds
+// the next draft, and set the next step's first token.
+__global__ void spec_commit_kernel(const AcceptRec* rec, const long long* draft_tokens, int k, int rows_per_seq,
+                                   int* ctx, int* n_commit, long long* cur_tok, long long* emitted, int* emitted_n,
+                                   __half* h_last, const __half* hidden_rows, int hidden) {
+    const int b = blockIdx.x;
+    const int na = rec[b].num_accepted;
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < na; ++i) emitted[b * (k + 1) + i] = draft_tokens[b * k + i];
+        emitted[b * (k + 1) + na] = rec[b].bonus;
+        for (int i = na + 1; i < k + 1; ++i) emitted[b * (k + 1) + i] = -1;
+        emitted_n[b] = na + 1;
+        ctx[b] += na + 1;
+        n_commit[b] = na + 1;
+        cur_tok[b] = rec[b].bonus;
+    }
+    const __half* src = hidden_rows + (static_cast<long long>(b) * rows_per_seq + na) * hidden;
+    for (int d = threadIdx.x; d < hidden; d += blockDim.x) h_last[static_cast<long long>(b) * hidden + d] = src[d];
+}
+
+// rows of the verify pass: row (b, 0) = current token, rows (b, 1..k) = draft tokens
+__global__ void build_verify_tokens_kernel(long long* out, const long long* cur_tok, const long long* draft, int k) {
+    const int b = blockIdx.x, i = threadIdx.x;
+    if (i == 0) out[b * (k + 1)] = cur_tok[b];
+    else if (i <= k) out[b * (k + 1) + i] = draft[b * k + i - 1];
+}
+
+__global__ void fill_int_kernel(int* p, int n, int v) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) p[i] = v;
+}
+
+__global__ void copy_token_column_kernel(long long* draft, const long long* argmax_out, int k, int col) {
+    const int b = threadIdx.x + blockIdx.x * blockDim.x;
+    draft[b * k + col] = argmax_out[b];
+}
+
+}  // namespace
+
+#define XB_LAUNCH_OK() (cudaGetLastError() == cudaSuccess ? 0 : -1)
+
+int embed_rows(cudaStream_t s, __half* out, const void* table_bf16, const long long* tokens, int rows, int hidden,
+               long long vocab) {
+    embed_kernel<<<rows, 256, 0, s>>>(out, static_cast<const uint16_t*>(table_bf16), tokens, hidden, vocab);
+    return XB_LAUNCH_OK();
+}
+
+int rmsnorm_rows(cudaStream_t s, __half* out, long long ld_out, const __half* in, const float* w, int rows, int hidden,
+                 float eps) {
+    rmsnorm_kernel<<<rows, 256, 0, s>>>(out, ld_out, const_cast<__half*>(in), nullptr, w, hidden, eps);
+    return XB_LAUNCH_OK();
+}
+
+int add_rmsnorm_rows(cudaStream_t s, __half* out, __half* x, const __half* delta, const float* w, int rows, int hidden,
+                     float eps) {
+    rmsnorm_kernel<<<rows, 256, 0, s>>>(out, hidden, x, delta, w, hidden, eps);
+    return XB_LAUNCH_OK();
+}
+
+int attn_prep(cudaStream_t s, __half* q_out, __half* k_cache, __half* v_cache, const __half* q_gate, const __half* k_in,
+              const __half* v_in, const float* q_norm_w, const float* k_norm_w, const int* ctx, int batch,
+              int rows_per_seq, int hq, int hkv, long long max_seq, float eps, float rope_theta, int rope_dim) {
+    dim3 grid(batch * rows_per_seq, hq + 2 * hkv);
+    attn_prep_kernel<<<grid, 256, 0, s>>>(q_out, k_cache, v_cache, q_gate, k_in, v_in, q_norm_w, k_norm_w, ctx,
+                                          rows_per_seq, hq, hkv, max_seq, eps, logf(rope_theta), rope_dim);
+    return XB_LAUNCH_OK();
+}
+
+size_t attn_scratch_bytes(int batch, int hkv, int nsplit) {
+    return static_cast<size_t>(batch) * hkv * nsplit * (kAttnRows * 256 + kAttnRows * 2) * sizeof(float);
+}
+
+int attn_decode(cudaStream_t s, __half* out, const __half* q, const __half* q_gate, const __half* k_cache,
+                const __half* v_cache, const int* ctx, int batch, int rows_per_seq, int hq, int hkv, long long max_seq,
+                int nsplit, float* scratch) {
+    if (hq % hkv != 0 || (hq / hkv) * rows_per_seq > kAttnRows) return -2;
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(attn_split_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 static_cast<int>(sizeof(AttnSmem))) != cudaSuccess)
+            return -1;
+        configured = true;
+    }
+    float* part_o = scratch;
+    float* part_ml = scratch + static_cast<size_t>(batch) * hkv * nsplit * (kAttnRows * 256);
+    dim3 grid(nsplit, hkv, batch);
+    attn_split_kernel<<<grid, 128, sizeof(AttnSmem), s>>>(part_o, part_ml, q, k_cache, v_cache, ctx, rows_per_seq, hq,
+                                                          hkv, max_seq, 1.0f / sqrtf(256.0f));
+    dim3 grid2((hq / hkv) * rows_per_seq, hkv, batch);
+    attn_combine_kernel<<<grid2, 256, 0, s>>>(out, part_o, part_ml, q_gate, nsplit, rows_per_seq, hq, hkv);
+    return XB_LAUNCH_OK();
+}
+
+int conv1d_spec(cudaStream_t s, __half* out, const __half* in, const float* conv_w, float* state, float* pending,
+                const int* n_commit, int batch, int rows_per_seq, int prev_rows, int channels) {
+    dim3 grid((channels + 255) / 256, batch);
+    conv1d_spec_kernel<<<grid, 256, 0, s>>>(out, in, conv_w, state, pending, n_commit, rows_per_seq, prev_rows, channels);
+    return XB_LAUNCH_OK();
+}
+
+int gdn_spec(cudaStream_t s, __half* out, const __half* qkv, const __half* z, const __half* b, const __half* a,
+             const float* A_log, const float* dt_bias, const float* norm_w, float* state, float* pend_k, float* pend_d,
+             float* pend_g, const int* n_commit, int batch, int rows_per_seq, int prev_rows, int hv, int hk) {
+    dim3 grid(hv, batch);
+    gdn_spec_kernel<<<grid, 128, 0, s>>>(out, qkv, z, b, a, A_log, dt_bias, norm_w, state, pend_k, pend_d, pend_g,
+                                         n_commit, rows_per_seq, prev_rows, hv, hk);
+    return XB_LAUNCH_OK();
+}
+
+int spec_commit(cudaStream_t s, const void* accept_records, const long long* draft_tokens, int batch, int k,
+                int rows_per_seq, int* ctx, int* n_commit, long long* cur_tok, long long* emitted, int* emitted_n,
+                __half* h_last, const __half* hidden_rows, int hidden) {
+    spec_commit_kernel<<<batch, 256, 0, s>>>(static_cast<const AcceptRec*>(accept_records), draft_tokens, k, rows_per_seq,
+                                             ctx, n_commit, cur_tok, emitted, emitted_n, h_last, hidden_rows, hidden);
+    return XB_LAUNCH_OK();
+}
+
+int build_verify_tokens(cudaStream_t s, long long* out, const long long* cur_tok, const long long* draft, int batch,
+                        int k) {
+    build_verify_tokens_kernel<<<batch, 32, 0, s>>>(out, cur_tok, draft, k);
+    return XB_LAUNCH_OK();
+}
+
+int fill_int(cudaStream_t s, int* p, int n, int v) {
+    fill_int_kernel<<<(n + 127) / 128, 128, 0, s>>>(p, n, v);
+    return XB_LAUNCH_OK();
+}
+
+int copy_token_column(cudaStream_t s, long long* draft, const long long* argmax_out, int batch, int k, int col) {
+    copy_token_column_kernel<<<1, batch, 0, s>>>(draft, argmax_out, k, col);
+    return XB_LAUNCH_OK();
+}
+
+}  // namespace xb

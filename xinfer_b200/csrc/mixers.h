@@ -1,0 +1,45 @@
+// Internal interface of the per-layer glue kernels (mixers.cu).  Rows are (sequence b, position i),
+// i < rows_per_seq; every function is asynchronous on the stream and returns 0 or a negative code.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stddef.h>
+
+namespace xb {
+
+int embed_rows(cudaStream_t s, __half* out, const void* table_bf16, const long long* tokens, int rows, int hidden,
+               long long vocab);
+int rmsnorm_rows(cudaStream_t s, __half* out, long long ld_out, const __half* in, const float* w, int rows, int hidden,
+                 float eps);
+// x = half(x + delta) in place, out = rmsnorm(x) * w
+int add_rmsnorm_rows(cudaStream_t s, __half* out, __half* x, const __half* delta, const float* w, int rows, int hidden,
+                     float eps);
+
+// q/k head RMSNorm + partial RoPE + KV-cache write.  Caches are [batch][max_seq][hkv][256] fp16.
+int attn_prep(cudaStream_t s, __half* q_out, __half* k_cache, __half* v_cache, const __half* q_gate, const __half* k_in,
+              const __half* v_in, const float* q_norm_w, const float* k_norm_w, const int* ctx, int batch,
+              int rows_per_seq, int hq, int hkv, long long max_seq, float eps, float rope_theta, int rope_dim);
+size_t attn_scratch_bytes(int batch, int hkv, int nsplit);
+// causal GQA attention over the cache (row i of sequence b sees keys below ctx[b] + i + 1), then * sigmoid(gate)
+int attn_decode(cudaStream_t s, __half* out, const __half* q, const __half* q_gate, const __half* k_cache,
+                const __half* v_cache, const int* ctx, int batch, int rows_per_seq, int hq, int hkv, long long max_seq,
+                int nsplit, float* scratch);
+
+// state [batch][3][channels], pending [batch][8][channels] fp32
+int conv1d_spec(cudaStream_t s, __half* out, const __half* in, const float* conv_w, float* state, float* pending,
+                const int* n_commit, int batch, int rows_per_seq, int prev_rows, int channels);
+// state [batch][hv][128][128], pend_k / pend_d [batch][hv][8][128], pend_g [batch][hv][8] fp32
+int gdn_spec(cudaStream_t s, __half* out, const __half* qkv, const __half* z, const __half* b, const __half* a,
+             const float* A_log, const float* dt_bias, const float* norm_w, float* state, float* pend_k, float* pend_d,
+             float* pend_g, const int* n_commit, int batch, int rows_per_seq, int prev_rows, int hv, int hk);
+
+int spec_commit(cudaStream_t s, const void* accept_records, const long long* draft_tokens, int batch, int k,
+                int rows_per_seq, int* ctx, int* n_commit, long long* cur_tok, long long* emitted, int* emitted_n,
+                __half* h_last, const __half* hidden_rows, int hidden);
+int build_verify_tokens(cudaStream_t s, long long* out, const long long* cur_tok, const long long* draft, int batch,
+                        int k);
+int fill_int(cudaStream_t s, int* p, int n, int v);
+int copy_token_column(cudaStream_t s, long long* draft, const long long* argmax_out, int batch, int k, int col);
+
+}  // namespace xb

@@ -1,0 +1,124 @@
+"""Host-side handle of the speculative decode runtime (xinfer_spec_decoder_* in the C-ABI)."""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+
+import numpy as np
+import torch
+
+from . import _lib
+from ._lib import ModelConfig, check, lib
+
+
+@dataclass
+class Shape:
+    """Shape fields of the reference's ModelConfig (src/targets/qwen3_8_27b/weights.h:58-107)."""
+    hidden_size: int = 5120
+    intermediate_size: int = 17408
+    num_hidden_layers: int = 64
+    num_attention_heads: int = 24
+    num_key_value_heads: int = 4
+    vocab_size: int = 151936
+    linear_num_v_heads: int = 48
+    linear_num_k_heads: int = 16
+    full_attention_interval: int = 4
+    rope_dim: int = 64
+    rms_norm_eps: float = 1e-6
+    rope_theta: float = 1.0e7
+
+    def to_c(self) -> ModelConfig:
+        return ModelConfig(self.hidden_size, self.intermediate_size, self.num_hidden_layers, self.num_attention_heads,
+                           self.num_key_value_heads, self.vocab_size, self.linear_num_v_heads, self.linear_num_k_heads,
+                           self.full_attention_interval, self.rope_dim, self.rms_norm_eps, self.rope_theta)
+
+    @property
+    def conv_channels(self) -> int:
+        return 2 * self.linear_num_k_heads * 128 + self.linear_num_v_heads * 128
+
+
+_DTYPES = {"w": np.uint8, "s": np.float16}
+
+
+class SpecDecoder:
+    def __init__(self, shape: Shape, batch: int = 8, k: int = 3, max_seq: int = 8448, seed: int = 0):
+        self.shape, self.batch, self.k, self.max_seq = shape, batch, k, max_seq
+        h = C.c_void_p()
+        cfg = shape.to_c()
+        code = lib().xinfer_spec_decoder_create(C.byref(cfg), batch, k, max_seq, seed, C.byref(h))
+        if code == _lib.ERR_OUT_OF_MEMORY:
+            raise MemoryError("SpecDecoder: device allocation failed")
+        check(code, "spec_decoder_create")
+        self._h = h
+        self._emitted = np.zeros((batch, k + 1), np.int64)
+        self._counts = np.zeros(batch, np.int32)
+
+    def close(self):
+        if getattr(self, "_h", None):
+            lib().xinfer_spec_decoder_destroy(self._h)
+            self._h = None
+
+    __del__ = close
+
+    def _err(self):
+        return lib().xinfer_spec_decoder_error(self._h).decode()
+
+    def reset(self, context_len: int, seed: int = 0):
+        check(lib().xinfer_spec_decoder_reset(self._h, context_len, seed), "spec_decoder_reset")
+
+    def set_tokens(self, toks):
+        t = np.ascontiguousarray(toks, np.int64)
+        check(lib().xinfer_spec_decoder_set_tokens(self._h, t.ctypes.data_as(C.c_void_p)), "set_tokens")
+
+    def override_drafts(self, drafts):
+        """Test hook: verify these [batch, k] tokens instead of the MTP head's (None disarms)."""
+        if drafts is None:
+            check(lib().xinfer_spec_decoder_override_drafts(self._h, None), "override_drafts")
+            return
+        t = np.ascontiguousarray(drafts, np.int64)
+        check(lib().xinfer_spec_decoder_override_drafts(self._h, t.ctypes.data_as(C.c_void_p)), "override_drafts")
+
+    def step(self):
+        code = lib().xinfer_spec_decoder_step(self._h, torch.cuda.current_stream().cuda_stream)
+        if code < 0:
+            raise _lib.XInferError(code, "spec_decoder_step: " + self._err())
+
+    def capture(self, stream: torch.cuda.Stream):
+        code = lib().xinfer_spec_decoder_capture(self._h, stream.cuda_stream)
+        if code < 0:
+            raise _lib.XInferError(code, "spec_decoder_capture: " + self._err())
+
+    def results(self):
+        """(emitted [batch, k+1] int64 with -1 padding, counts [batch]); synchronises the stream."""
+        check(lib().xinfer_spec_decoder_results(self._h, torch.cuda.current_stream().cuda_stream,
+                                                self._emitted.ctypes.data_as(C.c_void_p),
+                                                self._counts.ctypes.data_as(C.c_void_p)), "spec_decoder_results")
+        return self._emitted.copy(), self._counts.copy()
+
+    def info(self, what: int) -> int:
+        return int(lib().xinfer_spec_decoder_info(self._h, what))
+
+    def tensor(self, layer: int, name: str, dtype, shape=None) -> np.ndarray:
+        """Host copy of a named device tensor (weights or state)."""
+        nbytes = C.c_int64()
+        ptr = lib().xinfer_spec_decoder_tensor(self._h, layer, name.encode(), C.byref(nbytes))
+        if not ptr:
+            raise KeyError(f"{layer}:{name}")
+        torch.cuda.synchronize()
+        raw = np.empty(nbytes.value, np.uint8)
+        check(lib().xinfer_copy_device_to_host(raw.ctypes.data_as(C.c_void_p), ptr, nbytes.value), "copy_device_to_host")
+        arr = raw.view(dtype)
+        return arr.reshape(shape) if shape is not None else arr
+
+    def write_tensor(self, layer: int, name: str, array: np.ndarray):
+        nbytes = C.c_int64()
+        ptr = lib().xinfer_spec_decoder_tensor(self._h, layer, name.encode(), C.byref(nbytes))
+        if not ptr:
+            raise KeyError(f"{layer}:{name}")
+        a = np.ascontiguousarray(array)
+        assert a.nbytes == nbytes.value, (a.nbytes, nbytes.value)
+        torch.cuda.synchronize()
+        check(lib().xinfer_copy_host_to_device(ptr, a.ctypes.data_as(C.c_void_p), a.nbytes), "copy_host_to_device")
+
+    def is_full(self, layer: int) -> bool:
+        return bool(lib().xinfer_spec_decoder_tensor(self._h, layer, b"is_full", None))
