@@ -1,9 +1,13 @@
 #!/usr/bin/env python
 """Benchmark of the speculative-decode hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload gemv|sweep] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload step|gemv|sweep] [--impl reference]
 
 Prints ONE JSON line on rank 0.  Workloads:
+  step   (default) accepted tokens/s of the 27B-shape speculative decode step: 64-layer random-init
+         hybrid, MTP k=3, batch 8, context 8192; a step is k draft passes + one 32-row verify pass +
+         acceptance + commit, replayed as one CUDA graph.  The roofline object is for the dominant
+         kernel (the tcgen05 W4A16 linear): the step's linear launches replayed alone and event-timed.
   gemv   the INT4-G128 W4A16 GEMV/skinny-GEMM at the 27B layer shapes (default: M=1, 5120->17408,
          the shape the reference quotes its GEMV bandwidth on); a step is `--launches` back-to-back
          launches rotating over distinct weight buffers whose total exceeds twice the L2, so every
@@ -311,13 +315,192 @@ def sweep(args):
     return rows
 
 
+STEP_SHAPES_M32 = [  # (K, N, count per step) of the 27B-shape verify pass, for the CPU sample
+    (5120, 12288 + 1024 + 1024, 16), (6144, 5120, 16 + 48), (5120, 10240 + 6144 + 48 + 48, 48),
+    (5120, 17408 * 2, 64), (17408, 5120, 64), (5120, 151936, 1)]
+
+
+def cpu_step_sample(batch, k, budget_s=15.0):
+    """CPU arm of the speculative step: the oracle's port of linear_int4_naive (fp32, OpenMP over N) at
+    M = batch*(k+1) on a row sample of each distinct projection shape of the 27B stack; the step time is
+    the sample time scaled by weight bytes (the path is weight-streaming bound on the CPU as well).
+    Tokens per step are taken as `batch` (one bonus token per sequence, what random weights give)."""
+    import oracle
+    M = batch * (k + 1)
+    total_w = sum(K * N // 2 * cnt for K, N, cnt in STEP_SHAPES_M32) * 1.0
+    # MTP head: k passes of fc + one full layer + LM head, M = batch rows (counted by bytes only)
+    total_w += k * (10240 * 5120 // 2 + 5120 * 14336 // 2 + 6144 * 5120 // 2 + 5120 * 17408 + 17408 * 5120 // 2 +
+                    5120 * 151936 // 2)
+    rows = 1024
+    t_sample, w_sample = 0.0, 0.0
+    t_end = time.perf_counter() + budget_s
+    reps = 0
+    while reps < 1 or time.perf_counter() < t_end:
+        for K, N, _ in STEP_SHAPES_M32:
+            X, W, S = synth(M, K, min(rows, N), reps)
+            Xf = X.astype(np.float32)
+            t0 = time.perf_counter()
+            oracle.linear_int4_naive_f32(Xf, W, S)
+            t_sample += time.perf_counter() - t0
+            w_sample += W.size
+        reps += 1
+    step_s = t_sample * (total_w / w_sample)
+    return {"value": batch / step_s, "unit": "tok/s", "cores": oracle.num_threads(), "kind": "port",
+            "sample": f"{reps} passes over a {rows}-row sample of each projection shape at M={M} with the oracle's "
+                      f"linear_int4_naive port; step time extrapolated by weight bytes "
+                      f"({w_sample / reps / 1e6:.0f} MB sampled of {total_w / 1e9:.2f} GB); {batch} tokens per step",
+            "extrapolated_step_s": step_s}
+
+
+def step_bench(args):
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    import xinfer_b200.ops as ops
+    from xinfer_b200 import lib
+    from xinfer_b200.spec import Shape, SpecDecoder
+    assert lib().xinfer_b200_init(local_rank) == 0, lib().xinfer_last_cuda_error()
+
+    shape = Shape(num_hidden_layers=args.layers)
+    B, k, ctx0 = args.batch, args.k, args.context
+    dec = SpecDecoder(shape, batch=B, k=k, max_seq=ctx0 + 1024, seed=rank)
+    dec.reset(ctx0, seed=rank)
+    stream = torch.cuda.Stream()
+    steps, warm = args.steps, max(3, args.warmup)
+    with torch.cuda.stream(stream):
+        dec.capture(stream)          # runs one eager step, then records the step as a CUDA graph
+        for _ in range(warm):
+            dec.step()
+        stream.synchronize()
+        ctx_before = dec.tensor(-1, "ctx", np.int32).astype(np.int64).sum()
+        if world > 1:
+            dist.barrier()
+        sampler = ClockSampler(local_rank)
+        sampler.start()
+        torch.cuda.synchronize()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record(stream)
+        for _ in range(steps):
+            dec.step()
+        ev1.record(stream)
+        torch.cuda.synchronize()
+        clocks = sampler.stop()
+        ms = ev0.elapsed_time(ev1)
+        tokens = int(dec.tensor(-1, "ctx", np.int32).astype(np.int64).sum() - ctx_before)
+        launches = dec.info(2)
+
+        # the dominant kernel alone: the step's W4A16 launches, same order and weights, event-timed
+        dec.enqueue_linears()
+        stream.synchronize()
+        lin_bytes, lin_launches = dec.info(4), dec.info(5)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream):
+            dec.enqueue_linears()
+        g.replay()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        lin_reps = 5
+        for _ in range(lin_reps):
+            g.replay()
+        e1.record(stream)
+        torch.cuda.synchronize()
+        lin_ms = e0.elapsed_time(e1) / lin_reps
+
+        # end to end through the decoder's public calls: host token ids in, host emitted tokens out
+        toks = np.zeros(B, np.int64)
+        e2e_steps = max(5, steps)
+        ctx_a = dec.tensor(-1, "ctx", np.int32).astype(np.int64).sum()
+        if world > 1:
+            dist.barrier()
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            dec.set_tokens(toks)                      # H2D: the tokens the server decided to continue from
+            dec.step()
+            emitted, counts = dec.results()           # D2H + sync: what the server streams to its clients
+            toks = emitted[np.arange(B), counts - 1]
+        e2e_s = time.perf_counter() - t0
+        e2e_tokens = int(dec.tensor(-1, "ctx", np.int32).astype(np.int64).sum() - ctx_a)
+    assert ops.device_status(local_rank) == 0
+    if world > 1:
+        t = torch.tensor([ms, e2e_s, float(tokens), float(e2e_tokens)], device="cuda", dtype=torch.float64)
+        tmax = t.clone()
+        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        ms, e2e_s = float(tmax[0]), float(tmax[1])
+        tokens, e2e_tokens = int(t[2]), int(t[3])
+    value = tokens / (ms * 1e-3)
+    peak, peak_kind = measured_peak()
+    lin_gbs = lin_bytes / (lin_ms * 1e-3) / 1e9
+    line = {
+        "metric": "accepted_tok_per_s", "value": value, "unit": "tok/s", "n_gpus": world, "steps": steps, "warmup": warm,
+        "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "int4 weights x fp16 activations, fp32 accumulate", "data": "synthetic",
+        "config": {"workload": f"27B-shape hybrid ({args.layers} layers: Gated-DeltaNet + full attention, hidden 5120, "
+                               f"FFN 17408, vocab 151936, INT4-G128), MTP k={k}, batch {B}, context {ctx0}, greedy; "
+                               f"one step = {k} MTP draft passes + one {B * (k + 1)}-row verify pass + acceptance + "
+                               f"commit, replayed as one CUDA graph",
+                   "layers": args.layers, "batch": B, "k": k, "context": ctx0,
+                   "parallelism": f"{world} independent replica(s), one per GPU",
+                   "l2": "inputs larger than L2: every step streams %.1f GB of weights" % (dec.info(0) / 1e9),
+                   "accepted_per_step_per_seq": tokens / max(1, steps * B * world),
+                   "note": "random-init weights: the draft head and the target agree only by chance, so almost "
+                           "every step emits the bonus token alone"},
+        "roofline": {"bound": "hbm", "achieved": lin_gbs, "peak": peak, "unit": "GB/s", "frac": lin_gbs / peak,
+                     "peak_kind": f"of {peak_kind}", "frac_of_nominal_8000": lin_gbs / 8000.0, "traffic": None,
+                     "kernel": "w4a16_tc_kernel", "launches_per_step": lin_launches,
+                     "bytes_per_launch": lin_bytes / max(1, lin_launches),
+                     "us_per_launch": lin_ms * 1e3 / max(1, lin_launches), "linears_ms_per_step": lin_ms,
+                     "linears_share_of_step": lin_ms / (ms / steps)},
+        "e2e": {"value": e2e_tokens / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": B * 8,
+                "d2h_bytes_per_step": B * (k + 1) * 8 + B * 4, "ms_per_step": e2e_s / e2e_steps * 1e3},
+        "gpu_launches": launches * steps, "clocks": clocks,
+    }
+    if rank == 0:
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_step_sample(B, k)
+        print(json.dumps(line), flush=True)
+    dec.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def step_reference_arm(args):
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    B, k = args.batch, args.k
+    per = max(2.0, min(20.0, 90.0 / max(1, args.steps + args.warmup)))
+    for _ in range(min(1, args.warmup)):
+        cpu_step_sample(B, k, budget_s=1.0)
+    res = [cpu_step_sample(B, k, budget_s=per) for _ in range(min(args.steps, 5))]
+    step_s = statistics.median(r["extrapolated_step_s"] for r in res)
+    val = B / step_s
+    line = {"impl": "reference", "metric": "accepted_tok_per_s", "value": val, "unit": "tok/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_s * 1e3, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "int4 weights, fp32 accumulate", "data": "synthetic",
+            "config": {"workload": f"27B-shape hybrid, MTP k={k}, batch {B}: CPU oracle port, sampled and extrapolated",
+                       "batch": B, "k": k, "context": args.context},
+            "cpu_baseline": dict(res[0], value=val),
+            "e2e": {"value": val, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="gemv", choices=["gemv", "sweep"])
+    ap.add_argument("--workload", default="step", choices=["step", "gemv", "sweep"])
+    ap.add_argument("--layers", type=int, default=64)
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--k", type=int, default=3)
+    ap.add_argument("--context", type=int, default=8192)
     ap.add_argument("--shape", default="gate_up", choices=sorted(LAYER_SHAPES))
     ap.add_argument("--m", type=int, default=1)
     ap.add_argument("--launches", type=int, default=64)
@@ -325,6 +508,12 @@ def main():
     args = ap.parse_args()
     K, N = LAYER_SHAPES[args.shape]
     cfg = {"workload": f"INT4-G128 W4A16 linear M={args.m} K={K} N={N} ({args.shape})", "M": args.m, "K": K, "N": N}
+    if args.workload == "step":
+        if args.impl == "reference":
+            step_reference_arm(args)
+        else:
+            step_bench(args)
+        return
     if args.impl == "reference":
         run_reference_arm(args, cfg)
         return

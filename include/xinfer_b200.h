@@ -204,7 +204,10 @@ XINFER_EXPORT int xinfer_spec_decoder_results(xinfer_spec_decoder* d, xinfer_str
 /* Test hook (eager steps only): the next steps verify `drafts_host` [batch][k] instead of the MTP head's
  * tokens; the draft passes still run.  NULL disarms it. */
 XINFER_EXPORT int xinfer_spec_decoder_override_drafts(xinfer_spec_decoder* d, const int64_t* drafts_host);
-/* what: 0 weight bytes, 1 state bytes, 2 kernel launches per step, 3 graph captured */
+/* Measurement entry: enqueues only the W4A16 linear launches of one step (same order, same weights). */
+XINFER_EXPORT int xinfer_spec_decoder_enqueue_linears(xinfer_spec_decoder* d, xinfer_stream_t stream);
+/* what: 0 weight bytes, 1 state bytes, 2 kernel launches per step, 3 graph captured,
+ * 4 algorithmic bytes of the step's linear launches, 5 number of linear launches per step */
 XINFER_EXPORT int64_t xinfer_spec_decoder_info(const xinfer_spec_decoder* d, int what);
 XINFER_EXPORT void* xinfer_spec_decoder_tensor(xinfer_spec_decoder* d, int layer, const char* name, int64_t* bytes);
 XINFER_EXPORT const char* xinfer_spec_decoder_error(const xinfer_spec_decoder* d);

@@ -86,6 +86,7 @@ SIGNATURES = {
     "xinfer_spec_decoder_capture": (_i32, [_vp, _vp]),
     "xinfer_spec_decoder_results": (_i32, [_vp, _vp, _vp, _vp]),
     "xinfer_spec_decoder_override_drafts": (_i32, [_vp, _vp]),
+    "xinfer_spec_decoder_enqueue_linears": (_i32, [_vp, _vp]),
     "xinfer_spec_decoder_info": (_i64, [_vp, _i32]),
     "xinfer_spec_decoder_tensor": (_vp, [_vp, _i32, C.c_char_p, C.POINTER(_i64)]),
     "xinfer_spec_decoder_error": (C.c_char_p, [_vp]),

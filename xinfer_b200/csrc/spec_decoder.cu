@@ -129,6 +129,9 @@ struct xinfer_spec_decoder {
     std::string error;
     size_t weight_bytes = 0, state_bytes = 0;
     long long launches_per_step = 0;
+    bool linears_only = false;   // measurement mode: enqueue only the W4A16 launches of a step
+    long long linear_launches = 0;
+    double linear_bytes = 0;     // algorithmic bytes of those launches
 };
 
 namespace {
@@ -206,6 +209,11 @@ void make_layer(Dec* d, Layer& L, bool full) {
     }
 }
 
+#define NL(expr)                                                        \
+    do {                                                                \
+        if (!d->linears_only) CK(expr);                                 \
+    } while (0)
+
 #define CK(expr)                                                        \
     do {                                                                \
         int _rc = (expr);                                               \
@@ -215,8 +223,15 @@ void make_layer(Dec* d, Layer& L, bool full) {
         }                                                               \
     } while (0)
 
+void account(Dec* d, const Linear& l, int M, int out_bytes, bool count_x) {
+    d->linear_bytes += static_cast<double>(l.n) * (l.k / 2) + static_cast<double>(l.n) * (l.k / 128) * 2 +
+                       (count_x ? static_cast<double>(M) * l.k * 2 : 0.0) + static_cast<double>(M) * l.n * out_bytes;
+}
+
 int lin(Dec* d, cudaStream_t s, __half* y, const __half* x, const Linear& l, int M) {
     ++d->launches_per_step;
+    ++d->linear_launches;
+    account(d, l, M, 2, true);
     return xinfer_linear_int4_f16f16(s, y, x, l.w, l.s, nullptr, M, l.n, l.k, 128);
 }
 
@@ -229,18 +244,22 @@ int layer_forward(Dec* d, cudaStream_t s, Layer& L, int R, const int* ctx, const
     const int B = d->batch, M = B * R;
     const int H = static_cast<int>(c.hidden_size);
     // x += previous layer's MLP output (none for the first layer), then input RMSNorm
-    if (first) CK(xb::rmsnorm_rows(s, d->normed, H, d->x, L.input_norm, M, H, c.rms_norm_eps));
-    else CK(xb::add_rmsnorm_rows(s, d->normed, d->x, d->proj_out, L.input_norm, M, H, c.rms_norm_eps));
+    if (first) NL(xb::rmsnorm_rows(s, d->normed, H, d->x, L.input_norm, M, H, c.rms_norm_eps));
+    else NL(xb::add_rmsnorm_rows(s, d->normed, d->x, d->proj_out, L.input_norm, M, H, c.rms_norm_eps));
     ++d->launches_per_step;
     if (L.full) {
         xinfer_fused_desc fd[3] = {{d->q_gate, L.q_proj.w, L.q_proj.s, nullptr, L.q_proj.n},
                                    {d->kbuf, L.k_proj.w, L.k_proj.s, nullptr, L.k_proj.n},
                                    {d->vbuf, L.v_proj.w, L.v_proj.s, nullptr, L.v_proj.n}};
         CK(xinfer_linear_int4_fused_f16(s, d->normed, fd, 3, M, H, 128));
-        CK(xb::attn_prep(s, d->qbuf, L.k_cache, L.v_cache, d->q_gate, d->kbuf, d->vbuf, L.q_norm, L.k_norm, ctx, B, R,
+        ++d->linear_launches;
+        account(d, L.q_proj, M, 2, true);
+        account(d, L.k_proj, M, 2, false);
+        account(d, L.v_proj, M, 2, false);
+        NL(xb::attn_prep(s, d->qbuf, L.k_cache, L.v_cache, d->q_gate, d->kbuf, d->vbuf, L.q_norm, L.k_norm, ctx, B, R,
                          static_cast<int>(c.num_attention_heads), static_cast<int>(c.num_key_value_heads), d->max_seq,
                          c.rms_norm_eps, c.rope_theta, c.rope_dim));
-        CK(xb::attn_decode(s, d->attn_out, d->qbuf, d->q_gate, L.k_cache, L.v_cache, ctx, B, R,
+        NL(xb::attn_decode(s, d->attn_out, d->qbuf, d->q_gate, L.k_cache, L.v_cache, ctx, B, R,
                            static_cast<int>(c.num_attention_heads), static_cast<int>(c.num_key_value_heads), d->max_seq,
                            d->attn_splits, d->attn_scratch));
         d->launches_per_step += 4;
@@ -253,15 +272,23 @@ int layer_forward(Dec* d, cudaStream_t s, Layer& L, int R, const int* ctx, const
                                    {d->bbuf, L.in_b.w, L.in_b.s, nullptr, L.in_b.n},
                                    {d->abuf, L.in_a.w, L.in_a.s, nullptr, L.in_a.n}};
         CK(xinfer_linear_int4_fused_f16(s, d->normed, fd, 4, M, H, 128));
-        CK(xb::conv1d_spec(s, d->qkv_conv, d->qkv_raw, L.conv_w, L.conv_state, L.conv_pend, n_commit, B, R, prev_rows, ch));
-        CK(xb::gdn_spec(s, d->delta_out, d->qkv_conv, d->zbuf, d->bbuf, d->abuf, L.A_log, L.dt_bias, L.gdn_norm, L.S,
+        ++d->linear_launches;
+        account(d, L.in_qkv, M, 2, true);
+        account(d, L.in_z, M, 2, false);
+        account(d, L.in_b, M, 2, false);
+        account(d, L.in_a, M, 2, false);
+        NL(xb::conv1d_spec(s, d->qkv_conv, d->qkv_raw, L.conv_w, L.conv_state, L.conv_pend, n_commit, B, R, prev_rows, ch));
+        NL(xb::gdn_spec(s, d->delta_out, d->qkv_conv, d->zbuf, d->bbuf, d->abuf, L.A_log, L.dt_bias, L.gdn_norm, L.S,
                         L.pend_k, L.pend_d, L.pend_g, n_commit, B, R, prev_rows, hv, hk));
         d->launches_per_step += 3;
         CK(lin(d, s, d->proj_out, d->delta_out, L.out_proj, M));
     }
     // x += mixer output, post-attention RMSNorm
-    CK(xb::add_rmsnorm_rows(s, d->normed, d->x, d->proj_out, L.post_norm, M, H, c.rms_norm_eps));
+    NL(xb::add_rmsnorm_rows(s, d->normed, d->x, d->proj_out, L.post_norm, M, H, c.rms_norm_eps));
     CK(xinfer_mlp_gate_up_swiglu_int4_f16(s, d->mlp, d->normed, L.gate.w, L.gate.s, L.up.w, L.up.s, M, L.gate.n, H, 128));
+    ++d->linear_launches;
+    account(d, L.gate, M, 2, true);
+    d->linear_bytes += static_cast<double>(L.up.n) * (L.up.k / 2) + static_cast<double>(L.up.n) * (L.up.k / 128) * 2;
     d->launches_per_step += 2;
     CK(lin(d, s, d->proj_out, d->mlp, L.down, M));  // the caller adds proj_out into x
     return 0;
@@ -271,9 +298,11 @@ int layer_forward(Dec* d, cudaStream_t s, Layer& L, int R, const int* ctx, const
 int head_forward(Dec* d, cudaStream_t s, int M) {
     const auto& c = d->cfg;
     const int H = static_cast<int>(c.hidden_size);
-    CK(xb::add_rmsnorm_rows(s, d->normed, d->x, d->proj_out, d->final_norm, M, H, c.rms_norm_eps));
+    NL(xb::add_rmsnorm_rows(s, d->normed, d->x, d->proj_out, d->final_norm, M, H, c.rms_norm_eps));
     CK(xinfer_linear_int4_f16f32(s, d->logits, d->normed, d->lm_head.w, d->lm_head.s, nullptr, M, d->lm_head.n,
                                  d->lm_head.k, 128));
+    ++d->linear_launches;
+    account(d, d->lm_head, M, 4, true);
     d->launches_per_step += 2;
     return 0;
 }
@@ -284,20 +313,23 @@ int draft_pass(Dec* d, cudaStream_t s, int i) {
     const long long* tok = (i == 0) ? d->cur_tok : d->argmax_out;
     const __half* hprev = (i == 0) ? d->h_last : d->mtp_hidden;
     // cat = [rmsnorm(embed(tok)) ; rmsnorm(h_prev)]  ->  fc  ->  x
-    CK(xb::embed_rows(s, d->x, d->embed, tok, B, H, c.vocab_size));
-    CK(xb::rmsnorm_rows(s, d->cat, 2 * H, d->x, d->mtp_enorm, B, H, c.rms_norm_eps));
-    CK(xb::rmsnorm_rows(s, d->cat + H, 2 * H, hprev, d->mtp_hnorm, B, H, c.rms_norm_eps));
+    NL(xb::embed_rows(s, d->x, d->embed, tok, B, H, c.vocab_size));
+    NL(xb::rmsnorm_rows(s, d->cat, 2 * H, d->x, d->mtp_enorm, B, H, c.rms_norm_eps));
+    NL(xb::rmsnorm_rows(s, d->cat + H, 2 * H, hprev, d->mtp_hnorm, B, H, c.rms_norm_eps));
     CK(lin(d, s, d->x, d->cat, d->mtp_fc, B));
-    add_int_kernel<<<1, 64, 0, s>>>(d->ctx_draft, d->ctx, B, i);
+    if (!d->linears_only) add_int_kernel<<<1, 64, 0, s>>>(d->ctx_draft, d->ctx, B, i);
     d->launches_per_step += 4;
     CK(layer_forward(d, s, d->mtp_layer, 1, d->ctx_draft, d->n_commit_zero, 0, true, nullptr));
     // keep the head's output hidden for the next draft pass: x + proj_out (pre final norm)
-    CK(xb::add_rmsnorm_rows(s, d->normed, d->x, d->proj_out, d->final_norm, B, H, c.rms_norm_eps));
-    cudaMemcpyAsync(d->mtp_hidden, d->x, static_cast<size_t>(B) * H * sizeof(__half), cudaMemcpyDeviceToDevice, s);
+    NL(xb::add_rmsnorm_rows(s, d->normed, d->x, d->proj_out, d->final_norm, B, H, c.rms_norm_eps));
+    if (!d->linears_only)
+        cudaMemcpyAsync(d->mtp_hidden, d->x, static_cast<size_t>(B) * H * sizeof(__half), cudaMemcpyDeviceToDevice, s);
     CK(xinfer_linear_int4_f16f32(s, d->logits, d->normed, d->lm_head.w, d->lm_head.s, nullptr, B, d->lm_head.n,
                                  d->lm_head.k, 128));
-    CK(xinfer_argmax_rows(s, d->logits, c.vocab_size, B, c.vocab_size, reinterpret_cast<int64_t*>(d->argmax_out)));
-    CK(xb::copy_token_column(s, d->draft, d->argmax_out, B, d->k, i));
+    ++d->linear_launches;
+    account(d, d->lm_head, B, 4, true);
+    NL(xinfer_argmax_rows(s, d->logits, c.vocab_size, B, c.vocab_size, reinterpret_cast<int64_t*>(d->argmax_out)));
+    NL(xb::copy_token_column(s, d->draft, d->argmax_out, B, d->k, i));
     d->launches_per_step += 6;
     return 0;
 }
@@ -305,12 +337,12 @@ int draft_pass(Dec* d, cudaStream_t s, int i) {
 int target_pass(Dec* d, cudaStream_t s, int R, const long long* tokens) {
     const auto& c = d->cfg;
     const int M = d->batch * R, H = static_cast<int>(c.hidden_size);
-    CK(xb::embed_rows(s, d->x, d->embed, tokens, M, H, c.vocab_size));
+    NL(xb::embed_rows(s, d->x, d->embed, tokens, M, H, c.vocab_size));
     ++d->launches_per_step;
     for (size_t l = 0; l < d->layers.size(); ++l)
         CK(layer_forward(d, s, d->layers[l], R, d->ctx, d->n_commit, d->prev_rows, l == 0, nullptr));
     CK(head_forward(d, s, M));
-    d->prev_rows = R;
+    if (!d->linears_only) d->prev_rows = R;
     return 0;
 }
 
@@ -318,15 +350,17 @@ int enqueue_step(Dec* d, cudaStream_t s) {
     const auto& c = d->cfg;
     const int B = d->batch, k = d->k, R = k + 1;
     d->launches_per_step = 0;
+    d->linear_launches = 0;
+    d->linear_bytes = 0;
     for (int i = 0; i < k; ++i) CK(draft_pass(d, s, i));
-    if (d->override_armed)
+    if (d->override_armed && !d->linears_only)
         cudaMemcpyAsync(d->draft, d->draft_override, static_cast<size_t>(B) * k * sizeof(long long), cudaMemcpyDeviceToDevice, s);
-    CK(xb::build_verify_tokens(s, d->verify_tokens, d->cur_tok, d->draft, B, k));
+    NL(xb::build_verify_tokens(s, d->verify_tokens, d->cur_tok, d->draft, B, k));
     CK(target_pass(d, s, R, d->verify_tokens));
-    CK(xinfer_speculative_accept_reject_batched(s, reinterpret_cast<const int64_t*>(d->draft), d->logits, c.vocab_size,
+    NL(xinfer_speculative_accept_reject_batched(s, reinterpret_cast<const int64_t*>(d->draft), d->logits, c.vocab_size,
                                                 c.vocab_size, nullptr, nullptr, 1.0f, B, k, R, k, d->records));
     // x still holds the pre-norm hidden rows of the verify pass (head_forward added the last MLP output)
-    CK(xb::spec_commit(s, d->records, d->draft, B, k, R, d->ctx, d->n_commit, d->cur_tok, d->emitted, d->emitted_n,
+    NL(xb::spec_commit(s, d->records, d->draft, B, k, R, d->ctx, d->n_commit, d->cur_tok, d->emitted, d->emitted_n,
                        d->h_last, d->x, static_cast<int>(c.hidden_size)));
     d->launches_per_step += 5;
     return 0;
@@ -524,8 +558,19 @@ int xinfer_spec_decoder_results(xinfer_spec_decoder* d, xinfer_stream_t stream, 
 
 int xinfer_spec_decoder_set_tokens(xinfer_spec_decoder* d, const int64_t* cur_tokens_host) {
     if (!d || !cur_tokens_host) return XINFER_ERR_INVALID_ARGUMENT;
-    return cudaMemcpy(d->cur_tok, cur_tokens_host, static_cast<size_t>(d->batch) * sizeof(long long),
+    memcpy(d->h_emitted, cur_tokens_host, static_cast<size_t>(d->batch) * sizeof(long long));  // pinned staging
+    return cudaMemcpy(d->cur_tok, d->h_emitted, static_cast<size_t>(d->batch) * sizeof(long long),
                       cudaMemcpyHostToDevice) == cudaSuccess ? XINFER_OK : XINFER_ERR_CUDA;
+}
+
+// Measurement entry: enqueue only the W4A16 launches of one step, in the step's order and on the step's
+// weights, so that their device time can be taken with events apart from the mixers.
+int xinfer_spec_decoder_enqueue_linears(xinfer_spec_decoder* d, xinfer_stream_t stream) {
+    if (!d) return XINFER_ERR_INVALID_ARGUMENT;
+    d->linears_only = true;
+    int rc = enqueue_step(d, static_cast<cudaStream_t>(stream));
+    d->linears_only = false;
+    return rc;
 }
 
 int xinfer_spec_decoder_override_drafts(xinfer_spec_decoder* d, const int64_t* drafts_host) {
@@ -543,6 +588,8 @@ int64_t xinfer_spec_decoder_info(const xinfer_spec_decoder* d, int what) {
         case 1: return static_cast<int64_t>(d->state_bytes);
         case 2: return d->launches_per_step;
         case 3: return d->graph_exec ? 1 : 0;
+        case 4: return static_cast<int64_t>(d->linear_bytes);
+        case 5: return d->linear_launches;
         default: return -1;
     }
 }

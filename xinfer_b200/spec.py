@@ -83,6 +83,12 @@ class SpecDecoder:
         if code < 0:
             raise _lib.XInferError(code, "spec_decoder_step: " + self._err())
 
+    def enqueue_linears(self):
+        """Measurement: only the W4A16 launches of one step, on the current stream."""
+        code = lib().xinfer_spec_decoder_enqueue_linears(self._h, torch.cuda.current_stream().cuda_stream)
+        if code < 0:
+            raise _lib.XInferError(code, "enqueue_linears: " + self._err())
+
     def capture(self, stream: torch.cuda.Stream):
         code = lib().xinfer_spec_decoder_capture(self._h, stream.cuda_stream)
         if code < 0:
