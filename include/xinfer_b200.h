@@ -47,6 +47,9 @@ XINFER_EXPORT const char* xinfer_last_cuda_error(void);
 XINFER_EXPORT const char* xinfer_b200_version(void);
 /* Which kernel family the last linear call on this thread used: 0 none, 1 tcgen05, 2 CUDA cores. */
 XINFER_EXPORT int xinfer_last_linear_path(void);
+/* Debug aid: when non-NULL, every CTA of the tcgen05 linear kernel writes eight %globaltimer stamps
+ * (start, set-up done, first tile landed, main loop done, epilogue done, teardown) to dev_ptr[cta*8+i]. */
+XINFER_EXPORT void xinfer_debug_set_trace(void* dev_ptr);
 /* Force a kernel family for the linear entry points: 0 = automatic, 1 = tcgen05 when eligible
  * (default for fp16 activations), 2 = CUDA cores only.  For measurements and tests. */
 XINFER_EXPORT void xinfer_set_linear_path(int path);

@@ -63,6 +63,7 @@ SIGNATURES = {
     "xinfer_b200_version": (C.c_char_p, []),
     "xinfer_last_linear_path": (_i32, []),
     "xinfer_set_linear_path": (None, [_i32]),
+    "xinfer_debug_set_trace": (None, [_vp]),
     "xinfer_linear_int4_f16f16": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i32]),
     "xinfer_linear_int4_f16f32": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i32]),
     "xinfer_linear_int4_f32f32": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i32]),

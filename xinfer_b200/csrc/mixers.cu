@@ -26,6 +26,7 @@
 #include <math.h>
 #include <stdint.h>
 
+#include "launch.cuh"
 #include "mixers.h"
 
 namespace xb {
@@ -52,6 +53,7 @@ __device__ __forceinline__ float block_sum(float v, float* smem) {
 
 // ------------------------------------------------------------------------------- embedding
 __global__ void embed_kernel(__half* out, const uint16_t* table_bf16, const long long* tokens, int hidden, long long vocab) {
+    griddep_prologue();
     const int row = blockIdx.x;
     const long long tok = tokens[row];
     const bool ok = tok >= 0 && (vocab <= 0 || tok < vocab);
@@ -68,10 +70,65 @@ __global__ void embed_kernel(__half* out, const uint16_t* table_bf16, const long
 // `out` may have a wider row (ld_out) and a column offset so that two norms can fill one concatenated row.
 __global__ void __launch_bounds__(256) rmsnorm_kernel(__half* out, long long ld_out, __half* x, const __half* delta,
                                                       const float* w, int hidden, float eps) {
+    griddep_prologue();
     __shared__ float red[32];
     const long long row = blockIdx.x;
     __half* xr = x + row * hidden;
     const __half* dr = delta ? delta + row * hidden : nullptr;
+    __half* orow = out + row * ld_out;
+    const int nvec = hidden >> 3;
+    const bool vec_ok = (hidden & 7) == 0 && nvec <= 4 * 256 && ((reinterpret_cast<uintptr_t>(xr) & 15) == 0) &&
+                        ((reinterpret_cast<uintptr_t>(orow) & 15) == 0) &&
+                        (!dr || (reinterpret_cast<uintptr_t>(dr) & 15) == 0);
+    if (vec_ok) {
+        // one pass: each thread keeps its (up to four) 8-element vectors in registers
+        uint4 v[4];
+        float ss = 0.f;
+#pragma unroll
+        for (int it = 0; it < 4; ++it) {
+            const int i = threadIdx.x + it * 256;
+            if (i < nvec) {
+                v[it] = *reinterpret_cast<const uint4*>(xr + i * 8);
+                __half2* h = reinterpret_cast<__half2*>(&v[it]);
+                if (dr) {
+                    const uint4 dv = *reinterpret_cast<const uint4*>(dr + i * 8);
+                    const __half2* dh = reinterpret_cast<const __half2*>(&dv);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const float2 a = __half22float2(h[j]), b = __half22float2(dh[j]);
+                        h[j] = __halves2half2(__float2half_rn(a.x + b.x), __float2half_rn(a.y + b.y));
+                    }
+                    *reinterpret_cast<uint4*>(xr + i * 8) = v[it];
+                }
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float2 a = __half22float2(h[j]);
+                    ss += a.x * a.x + a.y * a.y;
+                }
+            }
+        }
+        const float total = block_sum(ss, red);
+        const float r = 1.0f / sqrtf(total / static_cast<float>(hidden) + eps);
+#pragma unroll
+        for (int it = 0; it < 4; ++it) {
+            const int i = threadIdx.x + it * 256;
+            if (i < nvec) {
+                const __half2* h = reinterpret_cast<const __half2*>(&v[it]);
+                const float4 w0 = *reinterpret_cast<const float4*>(w + i * 8);
+                const float4 w1 = *reinterpret_cast<const float4*>(w + i * 8 + 4);
+                const float ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+                uint4 o;
+                __half2* oh = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float2 a = __half22float2(h[j]);
+                    oh[j] = __halves2half2(__float2half_rn(a.x * r * ww[2 * j]), __float2half_rn(a.y * r * ww[2 * j + 1]));
+                }
+                *reinterpret_cast<uint4*>(orow + i * 8) = o;
+            }
+        }
+        return;
+    }
     float ss = 0.f;
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
         float v = __half2float(xr[i]);
@@ -84,7 +141,6 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(__half* out, long long ld_
     }
     const float total = block_sum(ss, red);
     const float r = 1.0f / sqrtf(total / static_cast<float>(hidden) + eps);
-    __half* orow = out + row * ld_out;
     for (int i = threadIdx.x; i < hidden; i += blockDim.x)
         orow[i] = __float2half_rn(__half2float(xr[i]) * r * w[i]);
 }
@@ -97,6 +153,7 @@ __global__ void __launch_bounds__(256) attn_prep_kernel(__half* q_out, __half* k
                                                         const float* q_norm_w, const float* k_norm_w, const int* ctx,
                                                         int rows_per_seq, int hq, int hkv, long long max_seq,
                                                         float eps, float log_theta, int rope_dim) {
+    griddep_prologue();
     __shared__ float red[32];
     __shared__ float vals[256];
     const int row = blockIdx.x;
@@ -194,6 +251,7 @@ __global__ void __launch_bounds__(128) attn_split_kernel(float* part_o, float* p
                                                          const __half* k_cache, const __half* v_cache, const int* ctx,
                                                          int rows_per_seq, int hq, int hkv, long long max_seq,
                                                          float scale) {
+    griddep_prologue();
     extern __shared__ __align__(16) uint8_t attn_smem_raw[];
     AttnSmem& sm = *reinterpret_cast<AttnSmem*>(attn_smem_raw);
     const int split = blockIdx.x, nsplit = gridDim.x, kvh = blockIdx.y, b = blockIdx.z;
@@ -374,6 +432,7 @@ __global__ void __launch_bounds__(128) attn_split_kernel(float* part_o, float* p
 __global__ void __launch_bounds__(256) attn_combine_kernel(__half* out, const float* part_o, const float* part_ml,
                                                            const __half* q_gate, int nsplit, int rows_per_seq, int hq,
                                                            int hkv) {
+    griddep_prologue();
     const int r = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z, d = threadIdx.x;
     const int G = hq / hkv;
     const int g = r / rows_per_seq, i = r % rows_per_seq;
@@ -403,6 +462,7 @@ __global__ void __launch_bounds__(256) attn_combine_kernel(__half* out, const fl
 // [B][Rmax][C] the raw inputs of the previous step, of which the first n_commit[b] were accepted.
 __global__ void conv1d_spec_kernel(__half* out, const __half* in, const float* conv_w, float* state, float* pending,
                                    const int* n_commit, int rows_per_seq, int prev_rows, int channels) {
+    griddep_prologue();
     const int c = blockIdx.x * blockDim.x + threadIdx.x;
     const int b = blockIdx.y;
     if (c >= channels) return;
@@ -433,43 +493,48 @@ __global__ void conv1d_spec_kernel(__half* out, const __half* in, const float* c
 }
 
 // ------------------------------------------------------------------------------- Gated DeltaNet recurrence
-// Grid (v heads, B), 128 threads; thread j owns column j of the 128 x 128 fp32 state, in registers.
+// Grid (v heads, B), 512 threads: thread (part, j) keeps rows [32 part, 32 part + 32) of column j of the
+// 128 x 128 fp32 state in registers; column sums are finished across the four parts through shared memory.
 // pend_k [B][Hv][8][128] normalised keys, pend_d [B][Hv][8][128] deltas, pend_g [B][Hv][8] decay factors of
-// the previous step.
-__global__ void __launch_bounds__(128) gdn_spec_kernel(__half* out, const __half* qkv, const __half* z,
+// the previous step: replaying them touches each state element with the same two operations, in the same
+// order, as the step that produced them, so the committed state is bit-identical.
+__global__ void __launch_bounds__(512, 2) gdn_spec_kernel(__half* out, const __half* qkv, const __half* z,
                                                        const __half* bb, const __half* aa, const float* A_log,
                                                        const float* dt_bias, const float* norm_w, float* state,
                                                        float* pend_k, float* pend_d, float* pend_g,
                                                        const int* n_commit, int rows_per_seq, int prev_rows, int hv,
                                                        int hk) {
-    __shared__ float sh_q[128], sh_k[128], red[32];
-    const int h = blockIdx.x, b = blockIdx.y, j = threadIdx.x;
+    griddep_prologue();
+    __shared__ float sh_q[128], sh_k[128], red[32], part_sum[4][128], sh_delta[128];
+    const int h = blockIdx.x, b = blockIdx.y;
+    const int j = threadIdx.x & 127, part = threadIdx.x >> 7;
+    const int i0 = part * 32;
     const int h_k = h / (hv / hk);
     const int channels = 2 * hk * 128 + hv * 128;
     const int value_dim = hv * 128;
     float* S = state + (static_cast<long long>(b) * hv + h) * (128 * 128);
     const long long pbase = (static_cast<long long>(b) * hv + h) * 8;
-    float col[128];
+    float col[32];
 #pragma unroll
-    for (int i = 0; i < 128; ++i) col[i] = S[i * 128 + j];
+    for (int i = 0; i < 32; ++i) col[i] = S[(i0 + i) * 128 + j];
 
     int nc = n_commit ? n_commit[b] : 0;
     if (nc > prev_rows) nc = prev_rows;
     if (nc > 0) {
         for (int t = 0; t < nc; ++t) {  // replay accepted updates: same operations, same order
             __syncthreads();
-            sh_k[j] = pend_k[(pbase + t) * 128 + j];
+            if (part == 0) sh_k[j] = pend_k[(pbase + t) * 128 + j];
             __syncthreads();
             const float eg = pend_g[pbase + t];
             const float dj = pend_d[(pbase + t) * 128 + j];
 #pragma unroll
-            for (int i = 0; i < 128; ++i) {
+            for (int i = 0; i < 32; ++i) {
                 const float sv = col[i] * eg;
-                col[i] = sv + sh_k[i] * dj;
+                col[i] = sv + sh_k[i0 + i] * dj;
             }
         }
 #pragma unroll
-        for (int i = 0; i < 128; ++i) S[i * 128 + j] = col[i];
+        for (int i = 0; i < 32; ++i) S[(i0 + i) * 128 + j] = col[i];
     }
 
     const float exp_a_log = expf(A_log[h]);
@@ -480,11 +545,13 @@ __global__ void __launch_bounds__(128) gdn_spec_kernel(__half* out, const __half
         const float raw_q = __half2float(cur[h_k * 128 + j]);
         const float raw_k = __half2float(cur[hk * 128 + h_k * 128 + j]);
         const float v = __half2float(cur[2 * hk * 128 + h * 128 + j]);
-        const float inv_q = 1.0f / sqrtf(block_sum(raw_q * raw_q, red) + 1e-6f);
-        const float inv_k = 1.0f / sqrtf(block_sum(raw_k * raw_k, red) + 1e-6f);
+        const float inv_q = 1.0f / sqrtf(block_sum(part == 0 ? raw_q * raw_q : 0.f, red) + 1e-6f);
+        const float inv_k = 1.0f / sqrtf(block_sum(part == 0 ? raw_k * raw_k : 0.f, red) + 1e-6f);
         __syncthreads();
-        sh_q[j] = (raw_q * inv_q) * 0.08838834764f;
-        sh_k[j] = raw_k * inv_k;
+        if (part == 0) {
+            sh_q[j] = (raw_q * inv_q) * 0.08838834764f;
+            sh_k[j] = raw_k * inv_k;
+        }
         __syncthreads();
         const float b_val = __half2float(bb[row * hv + h]);
         const float beta = 1.0f / (1.0f + expf(-b_val));
@@ -493,28 +560,39 @@ __global__ void __launch_bounds__(128) gdn_spec_kernel(__half* out, const __half
         const float eg = expf(-exp_a_log * softplus);
         float kv_mem = 0.f;
 #pragma unroll
-        for (int i = 0; i < 128; ++i) {
+        for (int i = 0; i < 32; ++i) {
             const float sv = col[i] * eg;
             col[i] = sv;
-            kv_mem += sv * sh_k[i];
+            kv_mem += sv * sh_k[i0 + i];
         }
-        const float delta = (v - kv_mem) * beta;
+        part_sum[part][j] = kv_mem;
+        __syncthreads();
+        const float delta = (v - (((part_sum[0][j] + part_sum[1][j]) + part_sum[2][j]) + part_sum[3][j])) * beta;
+        __syncthreads();
         float attn = 0.f;
 #pragma unroll
-        for (int i = 0; i < 128; ++i) {
-            const float ns = col[i] + sh_k[i] * delta;
+        for (int i = 0; i < 32; ++i) {
+            const float ns = col[i] + sh_k[i0 + i] * delta;
             col[i] = ns;
-            attn += ns * sh_q[i];
+            attn += ns * sh_q[i0 + i];
         }
-        pend_k[(pbase + t) * 128 + j] = sh_k[j];
-        pend_d[(pbase + t) * 128 + j] = delta;
-        if (j == 0) pend_g[pbase + t] = eg;
-        const float var = block_sum(attn * attn, red) / 128.0f;
+        part_sum[part][j] = attn;
+        if (part == 0) {
+            pend_k[(pbase + t) * 128 + j] = sh_k[j];
+            pend_d[(pbase + t) * 128 + j] = delta;
+            if (j == 0) pend_g[pbase + t] = eg;
+        }
+        __syncthreads();
+        attn = ((part_sum[0][j] + part_sum[1][j]) + part_sum[2][j]) + part_sum[3][j];
+        const float var = block_sum(part == 0 ? attn * attn : 0.f, red) / 128.0f;
         const float inv_std = 1.0f / sqrtf(var + 1e-6f);
-        const float zv = __half2float(z[row * value_dim + h * 128 + j]);
-        const float silu_z = zv / (1.0f + expf(-zv));
-        out[row * value_dim + h * 128 + j] = __float2half_rn(attn * inv_std * norm_w[j] * silu_z);
+        if (part == 0) {
+            const float zv = __half2float(z[row * value_dim + h * 128 + j]);
+            const float silu_z = zv / (1.0f + expf(-zv));
+            out[row * value_dim + h * 128 + j] = __float2half_rn(attn * inv_std * norm_w[j] * silu_z);
+        }
     }
+    (void)sh_delta;
 }
 
 // ------------------------------------------------------------------------------- speculative bookkeeping
@@ -530,6 +608,7 @@ struct AcceptRec {
 __global__ void spec_commit_kernel(const AcceptRec* rec, const long long* draft_tokens, int k, int rows_per_seq,
                                    int* ctx, int* n_commit, long long* cur_tok, long long* emitted, int* emitted_n,
                                    __half* h_last, const __half* hidden_rows, int hidden) {
+    griddep_prologue();
     const int b = blockIdx.x;
     const int na = rec[b].num_accepted;
     if (threadIdx.x == 0) {
@@ -547,17 +626,20 @@ __global__ void spec_commit_kernel(const AcceptRec* rec, const long long* draft_
 
 // rows of the verify pass: row (b, 0) = current token, rows (b, 1..k) = draft tokens
 __global__ void build_verify_tokens_kernel(long long* out, const long long* cur_tok, const long long* draft, int k) {
+    griddep_prologue();
     const int b = blockIdx.x, i = threadIdx.x;
     if (i == 0) out[b * (k + 1)] = cur_tok[b];
     else if (i <= k) out[b * (k + 1) + i] = draft[b * k + i - 1];
 }
 
 __global__ void fill_int_kernel(int* p, int n, int v) {
+    griddep_prologue();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) p[i] = v;
 }
 
 __global__ void copy_token_column_kernel(long long* draft, const long long* argmax_out, int k, int col) {
+    griddep_prologue();
     const int b = threadIdx.x + blockIdx.x * blockDim.x;
     draft[b * k + col] = argmax_out[b];
 }
@@ -568,19 +650,19 @@ __global__ void copy_token_column_kernel(long long* draft, const long long* argm
 
 int embed_rows(cudaStream_t s, __half* out, const void* table_bf16, const long long* tokens, int rows, int hidden,
                long long vocab) {
-    embed_kernel<<<rows, 256, 0, s>>>(out, static_cast<const uint16_t*>(table_bf16), tokens, hidden, vocab);
+    launch_pdl(embed_kernel, dim3(rows), dim3(256), 0, s, out, static_cast<const uint16_t*>(table_bf16), tokens, hidden, vocab);
     return XB_LAUNCH_OK();
 }
 
 int rmsnorm_rows(cudaStream_t s, __half* out, long long ld_out, const __half* in, const float* w, int rows, int hidden,
                  float eps) {
-    rmsnorm_kernel<<<rows, 256, 0, s>>>(out, ld_out, const_cast<__half*>(in), nullptr, w, hidden, eps);
+    launch_pdl(rmsnorm_kernel, dim3(rows), dim3(256), 0, s, out, ld_out, const_cast<__half*>(in), nullptr, w, hidden, eps);
     return XB_LAUNCH_OK();
 }
 
 int add_rmsnorm_rows(cudaStream_t s, __half* out, __half* x, const __half* delta, const float* w, int rows, int hidden,
                      float eps) {
-    rmsnorm_kernel<<<rows, 256, 0, s>>>(out, hidden, x, delta, w, hidden, eps);
+    launch_pdl(rmsnorm_kernel, dim3(rows), dim3(256), 0, s, out, hidden, x, delta, w, hidden, eps);
     return XB_LAUNCH_OK();
 }
 
@@ -588,7 +670,7 @@ int attn_prep(cudaStream_t s, __half* q_out, __half* k_cache, __half* v_cache, c
               const __half* v_in, const float* q_norm_w, const float* k_norm_w, const int* ctx, int batch,
               int rows_per_seq, int hq, int hkv, long long max_seq, float eps, float rope_theta, int rope_dim) {
     dim3 grid(batch * rows_per_seq, hq + 2 * hkv);
-    attn_prep_kernel<<<grid, 256, 0, s>>>(q_out, k_cache, v_cache, q_gate, k_in, v_in, q_norm_w, k_norm_w, ctx,
+    launch_pdl(attn_prep_kernel, dim3(grid), dim3(256), 0, s, q_out, k_cache, v_cache, q_gate, k_in, v_in, q_norm_w, k_norm_w, ctx,
                                           rows_per_seq, hq, hkv, max_seq, eps, logf(rope_theta), rope_dim);
     return XB_LAUNCH_OK();
 }
@@ -611,17 +693,17 @@ int attn_decode(cudaStream_t s, __half* out, const __half* q, const __half* q_ga
     float* part_o = scratch;
     float* part_ml = scratch + static_cast<size_t>(batch) * hkv * nsplit * (kAttnRows * 256);
     dim3 grid(nsplit, hkv, batch);
-    attn_split_kernel<<<grid, 128, sizeof(AttnSmem), s>>>(part_o, part_ml, q, k_cache, v_cache, ctx, rows_per_seq, hq,
+    launch_pdl(attn_split_kernel, dim3(grid), dim3(128), sizeof(AttnSmem), s, part_o, part_ml, q, k_cache, v_cache, ctx, rows_per_seq, hq,
                                                           hkv, max_seq, 1.0f / sqrtf(256.0f));
     dim3 grid2((hq / hkv) * rows_per_seq, hkv, batch);
-    attn_combine_kernel<<<grid2, 256, 0, s>>>(out, part_o, part_ml, q_gate, nsplit, rows_per_seq, hq, hkv);
+    launch_pdl(attn_combine_kernel, dim3(grid2), dim3(256), 0, s, out, part_o, part_ml, q_gate, nsplit, rows_per_seq, hq, hkv);
     return XB_LAUNCH_OK();
 }
 
 int conv1d_spec(cudaStream_t s, __half* out, const __half* in, const float* conv_w, float* state, float* pending,
                 const int* n_commit, int batch, int rows_per_seq, int prev_rows, int channels) {
     dim3 grid((channels + 255) / 256, batch);
-    conv1d_spec_kernel<<<grid, 256, 0, s>>>(out, in, conv_w, state, pending, n_commit, rows_per_seq, prev_rows, channels);
+    launch_pdl(conv1d_spec_kernel, dim3(grid), dim3(256), 0, s, out, in, conv_w, state, pending, n_commit, rows_per_seq, prev_rows, channels);
     return XB_LAUNCH_OK();
 }
 
@@ -629,7 +711,7 @@ int gdn_spec(cudaStream_t s, __half* out, const __half* qkv, const __half* z, co
              const float* A_log, const float* dt_bias, const float* norm_w, float* state, float* pend_k, float* pend_d,
              float* pend_g, const int* n_commit, int batch, int rows_per_seq, int prev_rows, int hv, int hk) {
     dim3 grid(hv, batch);
-    gdn_spec_kernel<<<grid, 128, 0, s>>>(out, qkv, z, b, a, A_log, dt_bias, norm_w, state, pend_k, pend_d, pend_g,
+    launch_pdl(gdn_spec_kernel, dim3(grid), dim3(512), 0, s, out, qkv, z, b, a, A_log, dt_bias, norm_w, state, pend_k, pend_d, pend_g,
                                          n_commit, rows_per_seq, prev_rows, hv, hk);
     return XB_LAUNCH_OK();
 }
@@ -637,24 +719,24 @@ int gdn_spec(cudaStream_t s, __half* out, const __half* qkv, const __half* z, co
 int spec_commit(cudaStream_t s, const void* accept_records, const long long* draft_tokens, int batch, int k,
                 int rows_per_seq, int* ctx, int* n_commit, long long* cur_tok, long long* emitted, int* emitted_n,
                 __half* h_last, const __half* hidden_rows, int hidden) {
-    spec_commit_kernel<<<batch, 256, 0, s>>>(static_cast<const AcceptRec*>(accept_records), draft_tokens, k, rows_per_seq,
+    launch_pdl(spec_commit_kernel, dim3(batch), dim3(256), 0, s, static_cast<const AcceptRec*>(accept_records), draft_tokens, k, rows_per_seq,
                                              ctx, n_commit, cur_tok, emitted, emitted_n, h_last, hidden_rows, hidden);
     return XB_LAUNCH_OK();
 }
 
 int build_verify_tokens(cudaStream_t s, long long* out, const long long* cur_tok, const long long* draft, int batch,
                         int k) {
-    build_verify_tokens_kernel<<<batch, 32, 0, s>>>(out, cur_tok, draft, k);
+    launch_pdl(build_verify_tokens_kernel, dim3(batch), dim3(32), 0, s, out, cur_tok, draft, k);
     return XB_LAUNCH_OK();
 }
 
 int fill_int(cudaStream_t s, int* p, int n, int v) {
-    fill_int_kernel<<<(n + 127) / 128, 128, 0, s>>>(p, n, v);
+    launch_pdl(fill_int_kernel, dim3((n + 127) / 128), dim3(128), 0, s, p, n, v);
     return XB_LAUNCH_OK();
 }
 
 int copy_token_column(cudaStream_t s, long long* draft, const long long* argmax_out, int batch, int k, int col) {
-    copy_token_column_kernel<<<1, batch, 0, s>>>(draft, argmax_out, k, col);
+    launch_pdl(copy_token_column_kernel, dim3(1), dim3(batch), 0, s, draft, argmax_out, k, col);
     return XB_LAUNCH_OK();
 }
 

@@ -125,6 +125,43 @@ __device__ __forceinline__ void named_barrier_sync(uint32_t id, uint32_t threads
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
 
+// ----------------------------------------------------------------------------- programmatic dependent launch
+// launch_dependents: the next kernel in the stream may start being scheduled (it will block in its own
+// griddep_wait until this grid has completed and its memory is visible).  wait: block until the previous
+// kernel in the stream has completed.  Both are no-ops for a kernel launched without the attribute.
+__device__ __forceinline__ void griddep_launch_dependents() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+// ----------------------------------------------------------------------------- thread-block clusters
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// Cluster-wide barrier; every thread of every CTA in the cluster must call it the same number of times,
+// each warp with all its lanes converged (.aligned).
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Address of this CTA's shared-memory location `addr` as seen in CTA `rank` of the cluster.
+__device__ __forceinline__ uint32_t mapa_shared_cluster(uint32_t addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void st_shared_cluster_f32(uint32_t addr, float v) {
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+}
+__device__ __forceinline__ float ld_shared_cluster_f32(uint32_t addr) {
+    float v;
+    // volatile keeps it between the cluster barriers; no memory clobber, so a batch can be in flight together
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr));
+    return v;
+}
+
 // ----------------------------------------------------------------------------- TMA (tiled, no multicast)
 __device__ __forceinline__ uint64_t l2_policy_evict_first() {
     uint64_t p;

@@ -20,6 +20,10 @@ struct TcProj {
 
 // ---- tcgen05 path (w4a16_tc.cu): fp16 activations, 1 <= m <= 32, k % 128 == 0
 size_t tc_workspace_bytes(int ctas);
+void tc_set_trace(long long* dev_ptr);
+// Programmatic dependent launch (on unless XINFER_PDL=0): kernels are launched with the stream-serialization
+// attribute and call griddepcontrol.wait before they touch data of the previous kernel.
+bool pdl_enabled();
 bool tc_eligible(const void* x, const TcProj* proj, int num, bool swiglu, long long m, long long k, int group_size);
 int tc_launch(cudaStream_t stream, const void* x, const TcProj* proj, int num, bool swiglu, bool out_f32,
               long long m, long long k, int num_sms, float* workspace, int* counters, int counter_capacity,

@@ -60,7 +60,7 @@ struct Cfg {
     static constexpr int kXStageBytes = NMMA * kStageK * 2;
     static constexpr int kStageBytes = kWStageBytes + kXStageBytes;
     static constexpr int kStages = (NMMA == 32) ? 4 : 5;
-    static constexpr int kXchgBytes = kHalfRows * NMMA * 4;
+    static constexpr int kXchgBytes = kTileRows * NMMA * 4;  // accumulators parked for the epilogue
     static constexpr int kCtrlBytes = 512;
     static constexpr int kSmemBytes = kStages * kStageBytes + kXchgBytes + kCtrlBytes + 1024;  // + align slack
 };
@@ -88,6 +88,8 @@ struct Params {
     float* workspace; // [ctas][2][32][256] fp32 partials
     int* counters;    // [total_tiles], zero between launches
     int* status;      // device status word
+    int cluster;      // CTAs per thread-block cluster = K splits per tile summed through distributed shared memory (1: none)
+    long long* trace; // optional [ctas][8] globaltimer stamps (debug aid, null in production)
 };
 
 struct Ctrl {
@@ -134,6 +136,14 @@ __device__ __forceinline__ TileInfo locate_tile(const Params& p, int tile) {
     return ti;
 }
 
+__device__ __forceinline__ void stamp(const Params& p, int slot) {
+    if (p.trace) {
+        long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        p.trace[blockIdx.x * 8 + slot] = t;
+    }
+}
+
 template <int NMMA, int NREAD, typename OutT>
 __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_constant__ Params p) {
     using C = Cfg<NMMA>;
@@ -147,6 +157,8 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
     const int warp = tid >> 5;
     const int lane = tid & 31;
     volatile int* abort_flag = &ctrl->abort_flag;
+    if (tid == 0) stamp(p, 0);
+    griddep_launch_dependents();
 
     if (tid == 0) {
         for (int i = 0; i < C::kStages; ++i) {
@@ -171,6 +183,7 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = ctrl->tmem_base;
+    if (tid == 0) stamp(p, 1);
 
     const long long ctas = gridDim.x;
     const long long u_begin = unit_begin(blockIdx.x, p.total_units, ctas);
@@ -188,22 +201,36 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
             tma_prefetch_desc(&p.x_map);
             const uint64_t pol_w = l2_policy_evict_first();
             const uint64_t pol_x = l2_policy_evict_last();
-            uint32_t n = 0;
-            for (long long u = u_begin; u < u_end; ++u, ++n) {
+            // The weights do not depend on the previous kernel in the stream, the activations do: the first
+            // ring of weight tiles is requested before waiting for that kernel, so the weight stream is
+            // already in flight while it drains (programmatic dependent launch).
+            auto issue = [&](long long u, uint32_t n, bool weights, bool acts) {
                 const int slot = n % C::kStages;
-                const uint32_t ph = (n / C::kStages) & 1u;
-                if (!mbar_wait_parked(smem_u32(&ctrl->empty[slot]), ph ^ 1u, abort_flag)) break;
                 const int tile = static_cast<int>(u / S);
                 const int s = static_cast<int>(u - static_cast<long long>(tile) * S);
                 const TileInfo ti = locate_tile(p, tile);
                 const uint32_t full = smem_u32(&ctrl->full[slot]);
                 const uint32_t dst = smem_u32(smem + slot * C::kStageBytes);
-                mbar_arrive_expect_tx(full, C::kStageBytes);
-                const int map_b = p.swiglu ? 1 : ti.seg;
-                const int row_b = p.swiglu ? ti.row0 : ti.row0 + kHalfRows;
-                tma_load_2d(dst, &p.w_map[ti.seg], full, s * kStageRowBytes, ti.row0, pol_w);
-                tma_load_2d(dst + kWHalfBytes, &p.w_map[map_b], full, s * kStageRowBytes, row_b, pol_w);
-                tma_load_3d(dst + kWStageBytes, &p.x_map, full, 0, 0, s * kKCoresPerStage, pol_x);
+                if (weights) {
+                    mbar_arrive_expect_tx(full, C::kStageBytes);
+                    const int map_b = p.swiglu ? 1 : ti.seg;
+                    const int row_b = p.swiglu ? ti.row0 : ti.row0 + kHalfRows;
+                    tma_load_2d(dst, &p.w_map[ti.seg], full, s * kStageRowBytes, ti.row0, pol_w);
+                    tma_load_2d(dst + kWHalfBytes, &p.w_map[map_b], full, s * kStageRowBytes, row_b, pol_w);
+                }
+                if (acts) tma_load_3d(dst + kWStageBytes, &p.x_map, full, 0, 0, s * kKCoresPerStage, pol_x);
+            };
+            const long long total_mine = u_end - u_begin;
+            const uint32_t pre = static_cast<uint32_t>(total_mine < C::kStages ? total_mine : C::kStages);
+            for (uint32_t n = 0; n < pre; ++n) issue(u_begin + n, n, true, false);
+            griddep_wait();
+            for (uint32_t n = 0; n < pre; ++n) issue(u_begin + n, n, false, true);
+            uint32_t n = pre;
+            for (long long u = u_begin + pre; u < u_end; ++u, ++n) {
+                const int slot = n % C::kStages;
+                const uint32_t ph = (n / C::kStages) & 1u;
+                if (!mbar_wait_parked(smem_u32(&ctrl->empty[slot]), ph ^ 1u, abort_flag)) break;
+                issue(u, n, true, true);
             }
             if (*abort_flag) {
                 // give the copies still in flight a bounded chance to land before the CTA exits
@@ -216,6 +243,7 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
                 }
             }
         }
+        if (p.cluster > 1) { __syncwarp(); cluster_sync_all(); cluster_sync_all(); }
     } else if (warp == kMmaWarp || warp == kMmaWarp + 1) {
         // ------------------------------------------------------------------ MMA issuers, one thread per half
         if (lane == 0) {
@@ -231,7 +259,8 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
             for (long long u = u_begin; u < u_end && ok; ++u, ++n) {
                 const int slot = n % C::kStages;
                 if (!mbar_wait_parked(smem_u32(&ctrl->x_ready[slot]), (n / C::kStages) & 1u, abort_flag)) break;
-                const uint32_t xlo = desc_lo_const | (smem_u32(smem + slot * C::kStageBytes + kWStageBytes) >> 4);
+                // (in a cluster launch a shared-window address carries the CTA's rank in its upper bits: keep 14 bits)
+                const uint32_t xlo = desc_lo_const | ((smem_u32(smem + slot * C::kStageBytes + kWStageBytes) >> 4) & 0x3FFFu);
 #pragma unroll
                 for (int gi = 0; gi < 2; ++gi) {
                     if (!mbar_wait_parked(smem_u32(&ctrl->a_full[w][gi]), n & 1u, abort_flag)) { ok = false; break; }
@@ -248,6 +277,7 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
                 }
             }
         }
+        if (p.cluster > 1) { __syncwarp(); cluster_sync_all(); cluster_sync_all(); }
     } else {
         // ------------------------------------------------------------------ consumers: unpack, read out, epilogue
         const int wg = tid >> 7;
@@ -269,6 +299,7 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
         float acc[NREAD];
         uint32_t n = 0;  // stages processed by this CTA so far
         bool ok = true;
+        int cluster_syncs = 0;
 
         // Read-out of stage n-1 is interleaved into stage n: group gi's accumulator is fetched right before
         // group gi of the next stage reuses its TMEM buffers, one full group of unpacking after its MMAs
@@ -317,6 +348,7 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
                     sc_next1 = (2 * s + 3 < gmax) ? __half2float(my_scales[2 * s + 3]) : 0.f;
                 }
                 if (!mbar_wait(full0 + slot * 8, (n / C::kStages) & 1u, abort_flag)) { ok = false; break; }
+                if (tid == 0 && n == 0) stamp(p, 2);
                 const uint32_t stage = smem_base + slot * C::kStageBytes;
 
                 // activations: reorder each 8-k block to (0,4,1,5,2,6,3,7), in place
@@ -375,22 +407,69 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
             __syncwarp();
             if (lane == 0) mbar_arrive(empty0 + ((n - 1) % C::kStages) * 8);
 
+            if (tid == 0) stamp(p, 3);
             // ---------------------------------------------------------------- tile epilogue
+            // Runs once per tile, so its instructions are cold in the instruction caches: the accumulators
+            // are parked in shared memory with one unrolled burst of stores and everything after that is
+            // written as rolled loops (a fully unrolled epilogue cost ~10 us in instruction fetches alone).
+            float* stage_acc = xchg;  // [NREAD][256] fp32, this thread's values at [j][tid]
+            named_barrier_sync(1, kConsumerThreads);  // previous tile's readers of stage_acc are done
+#pragma unroll
+            for (int j = 0; j < NREAD; ++j) stage_acc[j * kTileRows + tid] = acc[j];
+            const int m_rows = p.m < NREAD ? p.m : NREAD;
             const bool whole = (s0 == 0 && s1 == S);
             bool finish = whole;
-            if (!whole) {
+            int j0 = 0, jstep = 1;
+            if (!whole && p.cluster > 1) {
+                // K splits of one tile form a thread-block cluster.  Activation row j is finished by CTA
+                // j % cluster: every CTA pushes its fp32 partial of that row into the owner's shared memory
+                // (remote stores do not stall), and after a cluster barrier the owner sums the `cluster`
+                // copies in rank order (deterministic) from its own shared memory.
+                float* part = reinterpret_cast<float*>(smem);  // the stage buffers, free once every CTA is done
+                const uint32_t my_rank = cluster_ctarank();
+                const uint32_t csz = static_cast<uint32_t>(p.cluster);
+                const uint32_t rows_cap = (static_cast<uint32_t>(m_rows) + csz - 1) / csz;
+                cluster_sync_all();  // (1) every CTA of the cluster has finished reading its stage buffers
+                ++cluster_syncs;
+                {
+                    const uint32_t base = smem_u32(part) + ((my_rank * rows_cap) * kTileRows + tid) * 4;
+                    uint32_t owner = 0, jl = 0;
+#pragma unroll 1
+                    for (int j = 0; j < m_rows; ++j) {
+                        st_shared_cluster_f32(mapa_shared_cluster(base, owner) + jl * (kTileRows * 4),
+                                              stage_acc[j * kTileRows + tid]);
+                        if (++owner == csz) { owner = 0; ++jl; }
+                    }
+                }
+                cluster_sync_all();  // (2) all partials have landed
+                ++cluster_syncs;
+                {
+                    uint32_t jl = 0;
+#pragma unroll 1
+                    for (int j = static_cast<int>(my_rank); j < m_rows; j += static_cast<int>(csz), ++jl) {
+                        float sum = 0.f;
+#pragma unroll 1
+                        for (uint32_t r = 0; r < csz; ++r) sum += part[((r * rows_cap + jl) * kTileRows) + tid];
+                        stage_acc[j * kTileRows + tid] = sum;
+                    }
+                }
+                finish = true;
+                j0 = static_cast<int>(my_rank);
+                jstep = static_cast<int>(csz);
+            } else if (!whole) {
+                // tiles that straddle CTAs (one CTA per SM, units cut evenly): partials go through the scratch
+                // buffer and the last CTA to arrive sums them in CTA order
                 const int first_tile = static_cast<int>(u_begin / S);
                 const int wslot = blockIdx.x * 2 + (tile == first_tile ? 0 : 1);
                 float* ws = p.workspace + static_cast<long long>(wslot) * (32 * kTileRows);
-#pragma unroll
-                for (int j = 0; j < NREAD; ++j)
-                    if (j < p.m) ws[j * kTileRows + tid] = acc[j];
+#pragma unroll 1
+                for (int j = 0; j < m_rows; ++j) ws[j * kTileRows + tid] = stage_acc[j * kTileRows + tid];
                 __threadfence();
                 named_barrier_sync(1, kConsumerThreads);
+                const long long t_lo = static_cast<long long>(tile) * S;
+                const int c_lo = unit_owner(t_lo, p.total_units, ctas);
+                const int c_hi = unit_owner(t_lo + S - 1, p.total_units, ctas);
                 if (tid == 0) {
-                    const long long t_lo = static_cast<long long>(tile) * S;
-                    const int c_lo = unit_owner(t_lo, p.total_units, ctas);
-                    const int c_hi = unit_owner(t_lo + S - 1, p.total_units, ctas);
                     const int old = atomicAdd(&p.counters[tile], 1);
                     ctrl->is_last = (old == c_hi - c_lo) ? 1 : 0;
                 }
@@ -398,62 +477,55 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
                 finish = ctrl->is_last != 0;
                 if (finish) {
                     __threadfence();
-                    const long long t_lo = static_cast<long long>(tile) * S;
-                    const int c_lo = unit_owner(t_lo, p.total_units, ctas);
-                    const int c_hi = unit_owner(t_lo + S - 1, p.total_units, ctas);
-#pragma unroll
-                    for (int j = 0; j < NREAD; ++j) acc[j] = 0.f;
-                    for (int c = c_lo; c <= c_hi; ++c) {  // fixed CTA order: deterministic sum
-                        const int c_first_tile = static_cast<int>(unit_begin(c, p.total_units, ctas) / S);
-                        const float* src = p.workspace +
-                                           static_cast<long long>(c * 2 + (tile == c_first_tile ? 0 : 1)) * (32 * kTileRows);
-#pragma unroll
-                        for (int j = 0; j < NREAD; ++j)
-                            if (j < p.m) acc[j] += __ldcg(src + j * kTileRows + tid);
+#pragma unroll 1
+                    for (int j = 0; j < m_rows; ++j) {
+                        float sum = 0.f;
+#pragma unroll 1
+                        for (int c = c_lo; c <= c_hi; ++c) {  // fixed CTA order: deterministic sum
+                            const int c_first_tile = static_cast<int>(unit_begin(c, p.total_units, ctas) / S);
+                            const float* src = p.workspace + static_cast<long long>(c * 2 + (tile == c_first_tile ? 0 : 1)) *
+                                                                 (32 * kTileRows);
+                            sum += __ldcg(src + j * kTileRows + tid);
+                        }
+                        stage_acc[j * kTileRows + tid] = sum;
                     }
                     if (tid == 0) p.counters[tile] = 0;
                 }
-                named_barrier_sync(1, kConsumerThreads);  // is_last may be rewritten by the next tile
             }
             if (finish) {
                 if (p.swiglu) {
-                    if (wg == 1) {
-#pragma unroll
-                        for (int j = 0; j < NREAD; ++j) xchg[j * kHalfRows + t] = acc[j];
-                    }
-                    named_barrier_sync(1, kConsumerThreads);
+                    named_barrier_sync(1, kConsumerThreads);  // the up half's values are visible to the gate half
                     if (wg == 0 && valid) {
-                        OutT* y = static_cast<OutT*>(p.seg[0].y);
-#pragma unroll
-                        for (int j = 0; j < NREAD; ++j) {
-                            if (j < p.m) {
-                                const float g = acc[j];
-                                const float up = xchg[j * kHalfRows + t];
-                                const float silu = g / (1.0f + expf(-g));
-                                store_out<OutT>(y + static_cast<long long>(j) * p.seg[0].ldy + my_row, silu * up);
-                            }
+                        OutT* y = static_cast<OutT*>(p.seg[0].y) + my_row;
+                        const long long ldy = p.seg[0].ldy;
+#pragma unroll 1
+                        for (int j = j0; j < m_rows; j += jstep) {
+                            const float g = stage_acc[j * kTileRows + t];
+                            const float up = stage_acc[j * kTileRows + kHalfRows + t];
+                            store_out<OutT>(y + static_cast<long long>(j) * ldy, (g / (1.0f + expf(-g))) * up);
                         }
                     }
-                    named_barrier_sync(1, kConsumerThreads);
                 } else if (valid) {
-                    OutT* y = static_cast<OutT*>(sg.y);
+                    OutT* y = static_cast<OutT*>(sg.y) + my_row;
+                    const long long ldy = sg.ldy;
                     const float b = sg.bias ? sg.bias[my_row] : 0.f;
-#pragma unroll
-                    for (int j = 0; j < NREAD; ++j) {
-                        if (j < p.m) {
-                            const float v = sg.bias ? acc[j] + b : acc[j];
-                            store_out<OutT>(y + static_cast<long long>(j) * sg.ldy + my_row, v);
-                        }
-                    }
+#pragma unroll 1
+                    for (int j = j0; j < m_rows; j += jstep)
+                        store_out<OutT>(y + static_cast<long long>(j) * ldy, stage_acc[j * kTileRows + tid] + b);
                 }
             }
+            if (tid == 0) stamp(p, 4);
             u += (s1 - s0);
         }
+        // every thread of a cluster passes exactly two cluster barriers, also when a wait gave up
+        if (p.cluster > 1)
+            for (; cluster_syncs < 2; ++cluster_syncs) cluster_sync_all();
     }
 
     // ---------------------------------------------------------------------- teardown
     tc_fence_before_sync();
     __syncthreads();
+    if (tid == 0) stamp(p, 5);
     if (tid == 0 && ctrl->abort_flag) atomicExch(p.status, kStatusWaitTimeout);
     if (warp == kMmaWarp) {
         __syncwarp();
@@ -502,24 +574,78 @@ bool encode_x_map(CUtensorMap* map, const __half* x, long long m, long long k, i
                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// Chooses the decomposition and launches.  With at least one tile per SM the (tile, stage) units are cut
+// evenly over one CTA per SM (tiles that straddle CTAs are summed through the scratch buffer).  With fewer
+// tiles every tile is split into the same whole number of K ranges and those CTAs form a thread-block
+// cluster that sums its partials through distributed shared memory; the split count is the largest one
+// (at most 8, the portable cluster size) whose clusters are all co-resident in one wave.
 template <int NMMA, int NREAD, typename OutT>
-cudaError_t launch(const Params& p, int ctas, cudaStream_t stream) {
+cudaError_t launch(Params& p, int tiles, int num_sms, cudaStream_t stream) {
     auto kern = w4a16_tc_kernel<NMMA, NREAD, OutT>;
-    static bool configured = false;  // per instantiation; the attribute is per device-function
     static int configured_dev = -1;
+    static int max_clusters[9];
     int dev = 0;
     cudaGetDevice(&dev);
-    if (!configured || configured_dev != dev) {
+    if (configured_dev != dev) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<NMMA>::kSmemBytes);
         if (e != cudaSuccess) return e;
-        configured = true;
+        for (int cs = 1; cs <= 8; ++cs) {
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3(cs * 64);
+            cfg.blockDim = dim3(kThreads);
+            cfg.dynamicSmemBytes = Cfg<NMMA>::kSmemBytes;
+            cudaLaunchAttribute at[1];
+            at[0].id = cudaLaunchAttributeClusterDimension;
+            at[0].val.clusterDim.x = cs;
+            at[0].val.clusterDim.y = 1;
+            at[0].val.clusterDim.z = 1;
+            cfg.attrs = at;
+            cfg.numAttrs = 1;
+            int n = 0;
+            if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess) { n = 0; cudaGetLastError(); }
+            max_clusters[cs] = n;
+        }
         configured_dev = dev;
     }
-    kern<<<ctas, kThreads, Cfg<NMMA>::kSmemBytes, stream>>>(p);
-    return cudaGetLastError();
+    int ctas, cluster = 1;
+    if (tiles >= num_sms) {
+        ctas = num_sms;
+    } else {
+        int best = tiles;  // one CTA per tile, no split
+        for (int cs = 2; cs <= 8 && cs <= p.stages; ++cs) {
+            if (max_clusters[cs] < tiles) continue;  // would need a second wave
+            if (tiles * cs > best && tiles * cs <= num_sms) { best = tiles * cs; cluster = cs; }
+        }
+        ctas = tiles * cluster;
+    }
+    p.cluster = cluster;
+    { const char* e = getenv("XINFER_TC_CLUSTER_MODE"); if (e && atoi(e) == 2) p.cluster = 1; if (e && atoi(e) == 0) { p.cluster = 1; cluster = 1; } }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(ctas);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = Cfg<NMMA>::kSmemBytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute at[2];
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = cluster;
+    at[0].val.clusterDim.y = 1;
+    at[0].val.clusterDim.z = 1;
+    at[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = pdl_enabled() ? 2 : 1;
+    return cudaLaunchKernelEx(&cfg, kern, p);
 }
 
 }  // namespace
+
+bool pdl_enabled() {
+    static const bool on = [] { const char* e = getenv("XINFER_PDL"); return !(e && atoi(e) == 0); }();
+    return on;
+}
+
+static long long* g_trace = nullptr;
+void tc_set_trace(long long* dev_ptr) { g_trace = dev_ptr; }
 
 size_t tc_workspace_bytes(int ctas) { return static_cast<size_t>(ctas) * 2 * 32 * kTileRows * sizeof(float); }
 
@@ -573,23 +699,11 @@ int tc_launch(cudaStream_t stream, const void* x, const TcProj* proj, int num, b
     p.workspace = workspace;
     p.counters = counters;
     p.status = status;
-    // CTA count.  With at least one tile per SM the units are cut evenly over one CTA per SM (tiles that
-    // straddle two CTAs are summed by the later one).  With fewer tiles every tile is split into the same
-    // whole number of K ranges, so unit ranges stay tile-aligned and a tile covered by one CTA needs no
-    // second pass at all.
-    int ctas;
-    if (tiles >= num_sms) {
-        ctas = num_sms;
-    } else {
-        int splits = num_sms / tiles;
-        if (splits > p.stages) splits = p.stages;
-        if (splits < 1) splits = 1;
-        ctas = tiles * splits;
-    }
+    p.trace = g_trace;
     cudaError_t e;
-    if (m <= 8) e = out_f32 ? launch<16, 8, float>(p, ctas, stream) : launch<16, 8, __half>(p, ctas, stream);
-    else if (m <= 16) e = out_f32 ? launch<16, 16, float>(p, ctas, stream) : launch<16, 16, __half>(p, ctas, stream);
-    else e = out_f32 ? launch<32, 32, float>(p, ctas, stream) : launch<32, 32, __half>(p, ctas, stream);
+    if (m <= 8) e = out_f32 ? launch<16, 8, float>(p, tiles, num_sms, stream) : launch<16, 8, __half>(p, tiles, num_sms, stream);
+    else if (m <= 16) e = out_f32 ? launch<16, 16, float>(p, tiles, num_sms, stream) : launch<16, 16, __half>(p, tiles, num_sms, stream);
+    else e = out_f32 ? launch<32, 32, float>(p, tiles, num_sms, stream) : launch<32, 32, __half>(p, tiles, num_sms, stream);
     return e == cudaSuccess ? 0 : -1;
 }
 
