@@ -103,6 +103,22 @@ XINFER_EXPORT int xinfer_linear_int4_f16f16_ld(xinfer_stream_t s, void* Y_f16, i
                                                const uint8_t* W_int4, const void* scales_f16, const float* bias,
                                                int64_t M, int64_t N, int64_t K, int group_size);
 
+/* The same fp16 -> fp16 linear for callers that must not allocate device memory: a serving process that has
+ * already given all free HBM to its cache pool, a job under a fixed memory quota, code that runs while a
+ * CUDA graph is being captured.  This entry point calls no cudaMalloc / cudaFree and no allocating library
+ * routine: its scratch (split-K partials, tile counters, status word; 10.5 MB) is a fixed array inside the
+ * library image, held by every GPU that loads the library until the process exits.  It has no counterpart
+ * in the reference.
+ *   - Limits: 1 <= M <= 32, K a multiple of 128, group_size 128, 16-byte aligned X and W, N <= 2,097,152,
+ *     at most 160 SMs.  Anything else returns XINFER_ERR_INVALID_ARGUMENT (there is no fallback path).
+ *   - The first call on a device resolves the array's device address and configures the kernel; make that
+ *     first call before any stream capture.  Later calls only enqueue work on `s`.
+ *   - Every call uses the same array.  Counters are cleared at the start of each call, on `s`; two calls
+ *     that overlap on the GPU (different streams, or graphs replayed concurrently) race on it. */
+XINFER_EXPORT int xinfer_linear_int4_f16f16_noalloc(xinfer_stream_t s, void* Y_f16, const void* X_f16,
+                                                    const uint8_t* W_int4, const void* scales_f16, const float* bias,
+                                                    int64_t M, int64_t N, int64_t K, int group_size);
+
 /* ---- sampling ---------------------------------------------------------------------------------- */
 /* Replaces xinfer::ops::argmax_scratch_size, src/ops/sampling.h:11-15. */
 XINFER_EXPORT size_t xinfer_argmax_scratch_size(int64_t vocab_size);

@@ -68,6 +68,7 @@ SIGNATURES = {
     "xinfer_linear_int4_f16f32": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i32]),
     "xinfer_linear_int4_f32f32": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i32]),
     "xinfer_linear_int4_f16f16_ld": (_i32, [_vp, _vp, _i64, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i32]),
+    "xinfer_linear_int4_f16f16_noalloc": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i32]),
     "xinfer_linear_int4_fused_f16": (_i32, [_vp, _vp, C.POINTER(FusedDesc), _i32, _i64, _i64, _i32]),
     "xinfer_linear_int4_fused_f32": (_i32, [_vp, _vp, C.POINTER(FusedDesc), _i32, _i64, _i64, _i32]),
     "xinfer_mlp_gate_up_swiglu_int4_f16": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i32]),

@@ -707,4 +707,71 @@ int tc_launch(cudaStream_t stream, const void* x, const TcProj* proj, int num, b
     return e == cudaSuccess ? 0 : -1;
 }
 
+// ------------------------------------------------------------------------------------ allocation-free entry point
+//
+// Some hosts of this library may not allocate device memory once they are up and running: an inference
+// server that has handed every free byte of HBM to its KV-cache pool, a process inside a container whose
+// memory quota is already committed, or a caller that is in the middle of a CUDA-graph capture, where
+// cudaMalloc is forbidden.  For them the fp16 -> fp16 linear is offered once more with its scratch (split-K
+// partials, tile counters) living in a fixed array inside the library image instead of in a buffer from
+// cudaMalloc.  The array is sized for up to kNoAllocMaxCtas CTAs and kNoAllocMaxTiles weight tiles; every
+// GPU that loads the library holds these bytes until the process exits.
+namespace {
+
+constexpr int kNoAllocMaxCtas = 160;     // B200 has 148 SMs; one CTA per SM
+constexpr int kNoAllocMaxTiles = 8192;   // 256-row tiles, i.e. N up to 2,097,152 output features
+constexpr size_t kNoAllocPartialFloats = static_cast<size_t>(kNoAllocMaxCtas) * 2 * 32 * kTileRows;
+
+struct NoAllocScratch {
+    float partials[kNoAllocPartialFloats];  // 10,485,760 bytes
+    int counters[kNoAllocMaxTiles];
+    int status;
+};
+// In host code this name is only a handle for cudaGetSymbolAddress; it is not a device address.
+static __device__ __align__(256) NoAllocScratch g_noalloc_scratch;
+
+struct NoAllocDevice {
+    NoAllocScratch* ptr = nullptr;
+    int num_sms = 0;
+};
+NoAllocDevice g_noalloc_dev[64];
+
+}  // namespace
 }  // namespace xb
+
+extern "C" __attribute__((visibility("default"))) int xinfer_linear_int4_f16f16_noalloc(
+    void* stream, void* Y_f16, const void* X_f16, const uint8_t* W_int4, const void* scales_f16, const float* bias,
+    int64_t M, int64_t N, int64_t K, int group_size) {
+    using namespace xb;
+    if (M <= 0 || N <= 0 || K <= 0) return 1;  // XINFER_NOOP_INVALID_SHAPE, as the allocating entry point
+    if (!Y_f16 || !X_f16 || !W_int4 || !scales_f16) return -2;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -6;
+    NoAllocDevice& nd = g_noalloc_dev[dev];
+    if (!nd.ptr) {
+        // once per device, with that device current: resolve the array's device address
+        void* p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_noalloc_scratch) != cudaSuccess || !p) {
+            cudaGetLastError();
+            return -1;
+        }
+        int sms = 0;
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return -1;
+        nd.num_sms = sms;
+        nd.ptr = static_cast<NoAllocScratch*>(p);
+    }
+    TcProj proj{Y_f16, W_int4, scales_f16, bias, N, 0};
+    // sizes beyond the fixed scratch, or shapes the tensor-core kernel does not take, are refused: this entry
+    // point has no second code path to fall back on
+    if (nd.num_sms > kNoAllocMaxCtas) return -2;
+    if (!tc_eligible(X_f16, &proj, 1, false, M, K, group_size)) return -2;  // needs 1 <= M <= 32, K % 128 == 0, group 128
+    const long long tiles = (N + kTileRows - 1) / kTileRows;
+    if (tiles > kNoAllocMaxTiles) return -2;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // the array keeps whatever the last call left: the counters (and the status word) must start at zero
+    if (cudaMemsetAsync(nd.ptr->counters, 0, static_cast<size_t>(tiles) * sizeof(int), s) != cudaSuccess) return -1;
+    if (cudaMemsetAsync(&nd.ptr->status, 0, sizeof(int), s) != cudaSuccess) return -1;
+    const int rc = tc_launch(s, X_f16, &proj, 1, false, false, M, K, nd.num_sms, nd.ptr->partials, nd.ptr->counters,
+                             kNoAllocMaxTiles, &nd.ptr->status);
+    return rc == 0 ? 0 : (rc == -1 ? -1 : -2);
+}

@@ -59,6 +59,13 @@ def linear_int4_ld(Y: torch.Tensor, ldy: int, X, W_int4, scales, bias, M: int, N
                                                     _ptr(bias), M, N, K, group_size), "linear_int4_ld")
 
 
+def linear_int4_noalloc(Y: torch.Tensor, X, W_int4, scales, bias, M: int, N: int, K: int, group_size: int = 128) -> int:
+    """fp16 -> fp16 linear_int4 through the entry point that allocates nothing (fixed in-library scratch); for
+    hosts that cannot call cudaMalloc once running.  Refuses shapes outside its limits with ERR_INVALID_ARGUMENT."""
+    return check(lib().xinfer_linear_int4_f16f16_noalloc(_stream(), _ptr(Y), _ptr(X), _ptr(W_int4), _ptr(scales),
+                                                         _ptr(bias), M, N, K, group_size), "linear_int4_noalloc")
+
+
 def linear_int4_fused(X: torch.Tensor, descs: Sequence[dict], M: int, K: int, group_size: int = 128) -> int:
     """``xinfer::ops::linear_int4_fused`` (src/ops/linear.h:96-111).
 
