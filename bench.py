@@ -60,6 +60,21 @@ def synth(M, K, N, seed):
     return X, W, S
 
 
+def reduce_over_ranks(maxima, sums, device="cpu"):
+    """Whole-job aggregation for N > 1 (one process per GPU): element-wise MAX of `maxima` (timings: the job
+    is as slow as its slowest rank) and SUM of `sums` (units processed) over all ranks.  Works on any
+    torch.distributed backend; returns the inputs unchanged when there is a single process."""
+    import torch
+    import torch.distributed as dist
+    if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size() == 1:
+        return list(maxima), list(sums)
+    tmax = torch.tensor(list(maxima), dtype=torch.float64, device=device)
+    tsum = torch.tensor(list(sums), dtype=torch.float64, device=device)
+    dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+    dist.all_reduce(tsum, op=dist.ReduceOp.SUM)
+    return tmax.tolist(), tsum.tolist()
+
+
 class ClockSampler:
     QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
@@ -427,13 +442,8 @@ def step_bench(args):
         e2e_s = time.perf_counter() - t0
         e2e_tokens = int(dec.tensor(-1, "ctx", np.int32).astype(np.int64).sum() - ctx_a)
     assert ops.device_status(local_rank) == 0
-    if world > 1:
-        t = torch.tensor([ms, e2e_s, float(tokens), float(e2e_tokens)], device="cuda", dtype=torch.float64)
-        tmax = t.clone()
-        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
-        dist.all_reduce(t, op=dist.ReduceOp.SUM)
-        ms, e2e_s = float(tmax[0]), float(tmax[1])
-        tokens, e2e_tokens = int(t[2]), int(t[3])
+    (ms, e2e_s), (tokens, e2e_tokens) = reduce_over_ranks([ms, e2e_s], [tokens, e2e_tokens], device="cuda")
+    tokens, e2e_tokens = int(tokens), int(e2e_tokens)
     value = tokens / (ms * 1e-3)
     peak, peak_kind = measured_peak()
     lin_gbs = lin_bytes / (lin_ms * 1e-3) / 1e9

@@ -494,20 +494,24 @@ __global__ void conv1d_spec_kernel(__half* out, const __half* in, const float* c
 
 // ------------------------------------------------------------------------------- Gated DeltaNet recurrence
 // Grid (v heads, B), 512 threads: thread (part, j) keeps rows [32 part, 32 part + 32) of column j of the
-// 128 x 128 fp32 state in registers; column sums are finished across the four parts through shared memory.
+// 128 x 128 fp32 state in registers.  Everything that does not depend on the state (q/k L2 norms, beta, the
+// decay factor) is computed for all tokens at once before the recurrence, and the gated RMSNorm of the
+// outputs for all tokens after it, so the sequential part is one barrier and 64 FMAs per token.
 // pend_k [B][Hv][8][128] normalised keys, pend_d [B][Hv][8][128] deltas, pend_g [B][Hv][8] decay factors of
 // the previous step: replaying them touches each state element with the same two operations, in the same
 // order, as the step that produced them, so the committed state is bit-identical.
 __global__ void __launch_bounds__(512, 2) gdn_spec_kernel(__half* out, const __half* qkv, const __half* z,
-                                                       const __half* bb, const __half* aa, const float* A_log,
-                                                       const float* dt_bias, const float* norm_w, float* state,
-                                                       float* pend_k, float* pend_d, float* pend_g,
-                                                       const int* n_commit, int rows_per_seq, int prev_rows, int hv,
-                                                       int hk) {
+                                                          const __half* bb, const __half* aa, const float* A_log,
+                                                          const float* dt_bias, const float* norm_w, float* state,
+                                                          float* pend_k, float* pend_d, float* pend_g,
+                                                          const int* n_commit, int rows_per_seq, int prev_rows, int hv,
+                                                          int hk) {
     griddep_prologue();
-    __shared__ float sh_q[128], sh_k[128], red[32], part_sum[4][128], sh_delta[128];
+    __shared__ float sh_q[8][128], sh_k[8][128], sh_beta[8], sh_eg[8], red[2][16];
+    __shared__ float part_sum[2][4][128], attn_all[8][4][128];
     const int h = blockIdx.x, b = blockIdx.y;
-    const int j = threadIdx.x & 127, part = threadIdx.x >> 7;
+    const int j = threadIdx.x & 127, part = threadIdx.x >> 7;  // part doubles as the token group in phases 0 and 2
+    const int lane = threadIdx.x & 31, wig = (threadIdx.x >> 5) & 3;
     const int i0 = part * 32;
     const int h_k = h / (hv / hk);
     const int channels = 2 * hk * 128 + hv * 128;
@@ -518,81 +522,106 @@ __global__ void __launch_bounds__(512, 2) gdn_spec_kernel(__half* out, const __h
 #pragma unroll
     for (int i = 0; i < 32; ++i) col[i] = S[(i0 + i) * 128 + j];
 
+    // ---- phase 0: per-token quantities that do not depend on the state (token tt handled by thread group tt % 4)
+    const float exp_a_log = expf(A_log[h]);
+    const float dtb = dt_bias[h];
+    for (int t0 = 0; t0 < rows_per_seq; t0 += 4) {
+        const int tt = t0 + part;
+        float raw_q = 0.f, raw_k = 0.f;
+        if (tt < rows_per_seq) {
+            const __half* cur = qkv + (static_cast<long long>(b) * rows_per_seq + tt) * channels;
+            raw_q = __half2float(cur[h_k * 128 + j]);
+            raw_k = __half2float(cur[hk * 128 + h_k * 128 + j]);
+        }
+        const float wq = warp_sum(raw_q * raw_q), wk = warp_sum(raw_k * raw_k);
+        __syncthreads();
+        if (lane == 0) { red[0][part * 4 + wig] = wq; red[1][part * 4 + wig] = wk; }
+        __syncthreads();
+        if (tt < rows_per_seq) {
+            const float q_sq = ((red[0][part * 4] + red[0][part * 4 + 1]) + red[0][part * 4 + 2]) + red[0][part * 4 + 3];
+            const float k_sq = ((red[1][part * 4] + red[1][part * 4 + 1]) + red[1][part * 4 + 2]) + red[1][part * 4 + 3];
+            sh_q[tt][j] = (raw_q * (1.0f / sqrtf(q_sq + 1e-6f))) * 0.08838834764f;
+            sh_k[tt][j] = raw_k * (1.0f / sqrtf(k_sq + 1e-6f));
+            if (j == 0) {
+                const long long row = static_cast<long long>(b) * rows_per_seq + tt;
+                const float b_val = __half2float(bb[row * hv + h]);
+                sh_beta[tt] = 1.0f / (1.0f + expf(-b_val));
+                const float a_val = __half2float(aa[row * hv + h]) + dtb;
+                const float softplus = (a_val > 20.0f) ? a_val : logf(1.0f + expf(a_val));
+                sh_eg[tt] = expf(-exp_a_log * softplus);
+            }
+        }
+    }
+
+    // ---- replay of the previous step's accepted updates, then write the committed state
     int nc = n_commit ? n_commit[b] : 0;
     if (nc > prev_rows) nc = prev_rows;
     if (nc > 0) {
-        for (int t = 0; t < nc; ++t) {  // replay accepted updates: same operations, same order
-            __syncthreads();
-            if (part == 0) sh_k[j] = pend_k[(pbase + t) * 128 + j];
-            __syncthreads();
+        for (int t = 0; t < nc; ++t) {
             const float eg = pend_g[pbase + t];
             const float dj = pend_d[(pbase + t) * 128 + j];
+            const float* pk = pend_k + (pbase + t) * 128 + i0;
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
                 const float sv = col[i] * eg;
-                col[i] = sv + sh_k[i0 + i] * dj;
+                col[i] = sv + __ldg(pk + i) * dj;
             }
         }
 #pragma unroll
         for (int i = 0; i < 32; ++i) S[(i0 + i) * 128 + j] = col[i];
     }
+    __syncthreads();  // phase 0 results visible; replay reads of pend_* are done before they are overwritten
 
-    const float exp_a_log = expf(A_log[h]);
-    const float dtb = dt_bias[h];
+    // ---- phase 1: the recurrence
     for (int t = 0; t < rows_per_seq; ++t) {
         const long long row = static_cast<long long>(b) * rows_per_seq + t;
-        const __half* cur = qkv + row * channels;
-        const float raw_q = __half2float(cur[h_k * 128 + j]);
-        const float raw_k = __half2float(cur[hk * 128 + h_k * 128 + j]);
-        const float v = __half2float(cur[2 * hk * 128 + h * 128 + j]);
-        const float inv_q = 1.0f / sqrtf(block_sum(part == 0 ? raw_q * raw_q : 0.f, red) + 1e-6f);
-        const float inv_k = 1.0f / sqrtf(block_sum(part == 0 ? raw_k * raw_k : 0.f, red) + 1e-6f);
-        __syncthreads();
-        if (part == 0) {
-            sh_q[j] = (raw_q * inv_q) * 0.08838834764f;
-            sh_k[j] = raw_k * inv_k;
-        }
-        __syncthreads();
-        const float b_val = __half2float(bb[row * hv + h]);
-        const float beta = 1.0f / (1.0f + expf(-b_val));
-        const float a_val = __half2float(aa[row * hv + h]) + dtb;
-        const float softplus = (a_val > 20.0f) ? a_val : logf(1.0f + expf(a_val));
-        const float eg = expf(-exp_a_log * softplus);
+        const float v = __half2float(qkv[row * channels + 2 * hk * 128 + h * 128 + j]);
+        const float eg = sh_eg[t];
         float kv_mem = 0.f;
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
             const float sv = col[i] * eg;
             col[i] = sv;
-            kv_mem += sv * sh_k[i0 + i];
+            kv_mem += sv * sh_k[t][i0 + i];
         }
-        part_sum[part][j] = kv_mem;
+        part_sum[t & 1][part][j] = kv_mem;
         __syncthreads();
-        const float delta = (v - (((part_sum[0][j] + part_sum[1][j]) + part_sum[2][j]) + part_sum[3][j])) * beta;
-        __syncthreads();
+        const float* ps = &part_sum[t & 1][0][j];
+        const float delta = (v - (((ps[0] + ps[128]) + ps[256]) + ps[384])) * sh_beta[t];
         float attn = 0.f;
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-            const float ns = col[i] + sh_k[i0 + i] * delta;
+            const float ns = col[i] + sh_k[t][i0 + i] * delta;
             col[i] = ns;
-            attn += ns * sh_q[i0 + i];
+            attn += ns * sh_q[t][i0 + i];
         }
-        part_sum[part][j] = attn;
+        attn_all[t][part][j] = attn;
         if (part == 0) {
-            pend_k[(pbase + t) * 128 + j] = sh_k[j];
+            pend_k[(pbase + t) * 128 + j] = sh_k[t][j];
             pend_d[(pbase + t) * 128 + j] = delta;
             if (j == 0) pend_g[pbase + t] = eg;
         }
+    }
+    __syncthreads();
+
+    // ---- phase 2: gated RMSNorm of every token's output (token tt handled by thread group tt % 4)
+    for (int t0 = 0; t0 < rows_per_seq; t0 += 4) {
+        const int tt = t0 + part;
+        float attn = 0.f;
+        if (tt < rows_per_seq) attn = ((attn_all[tt][0][j] + attn_all[tt][1][j]) + attn_all[tt][2][j]) + attn_all[tt][3][j];
+        const float wsq = warp_sum(attn * attn);
         __syncthreads();
-        attn = ((part_sum[0][j] + part_sum[1][j]) + part_sum[2][j]) + part_sum[3][j];
-        const float var = block_sum(part == 0 ? attn * attn : 0.f, red) / 128.0f;
-        const float inv_std = 1.0f / sqrtf(var + 1e-6f);
-        if (part == 0) {
+        if (lane == 0) red[0][part * 4 + wig] = wsq;
+        __syncthreads();
+        if (tt < rows_per_seq) {
+            const float sq = ((red[0][part * 4] + red[0][part * 4 + 1]) + red[0][part * 4 + 2]) + red[0][part * 4 + 3];
+            const float inv_std = 1.0f / sqrtf(sq / 128.0f + 1e-6f);
+            const long long row = static_cast<long long>(b) * rows_per_seq + tt;
             const float zv = __half2float(z[row * value_dim + h * 128 + j]);
             const float silu_z = zv / (1.0f + expf(-zv));
             out[row * value_dim + h * 128 + j] = __float2half_rn(attn * inv_std * norm_w[j] * silu_z);
         }
     }
-    (void)sh_delta;
 }
 
 // ------------------------------------------------------------------------------- speculative bookkeeping
