@@ -300,14 +300,15 @@ __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
 // One little-endian u32 of packed int4 (nibble i <-> k+i, two's complement) -> four half2 registers
 // holding the exact integers as fp16, in the order (k0,k4) (k1,k5) (k2,k6) (k3,k7).
 // Bit-exact with the reference's (word << (28-4i)) >> 28 (src/ops/linear.cpp:100-110): the sign
-// bit of each nibble is flipped inside the lop3 (q+8 in 0..15), the result is or-ed under the fp16
-// exponent of 1024, and the bias 1032 (or 72 after the exact 1/16 scaling) is subtracted.
+// bit of each nibble is flipped inside the lop3 (q+8 in 0..15) and the result is or-ed under an fp16
+// exponent whose ulp equals the nibble's lowest bit: 1024 for bits 0-3 (ulp 1), 64 for bits 4-7
+// (ulp 1/16); subtracting the bias 1032 (or 72) leaves the signed integer exactly.
 __device__ __forceinline__ void dequant_word(uint32_t w, uint32_t* out4) {
     const uint32_t hi = w >> 8;
     out4[0] = hsub2_u32(lop3_6a(w, 0x000F000Fu, 0x64086408u), 0x64086408u);
-    out4[1] = hfma2_u32(lop3_6a(w, 0x00F000F0u, 0x64806480u), 0x2C002C00u, 0xD480D480u);
+    out4[1] = hsub2_u32(lop3_6a(w, 0x00F000F0u, 0x54805480u), 0x54805480u);
     out4[2] = hsub2_u32(lop3_6a(hi, 0x000F000Fu, 0x64086408u), 0x64086408u);
-    out4[3] = hfma2_u32(lop3_6a(hi, 0x00F000F0u, 0x64806480u), 0x2C002C00u, 0xD480D480u);
+    out4[3] = hsub2_u32(lop3_6a(hi, 0x00F000F0u, 0x54805480u), 0x54805480u);
 }
 
 }  // namespace xb

@@ -16,8 +16,8 @@
 // That thread reads its row's packed bytes from the TMA-staged tile (128B-swizzled, conflict free),
 // unpacks them to exact fp16 integers in registers, and writes them with tcgen05.st into TMEM lane
 // t, where they are the A operand (128 x 16 per MMA).  The <= 32 activation rows are the MMA's N
-// side: their K slice arrives by a 3-D TMA load directly in the canonical K-major core-matrix
-// layout and is the B operand from shared memory.  Each 128-k group accumulates into a fresh TMEM
+// side: their K slice arrives as TMA boxes of 64 k per row in the 128-byte-swizzled K-major layout
+// and is the B operand from shared memory.  Each 128-k group accumulates into a fresh TMEM
 // tile D[128 x NMMA]; its owner thread reads lane t back (tcgen05.ld) and folds it into fp32
 // register accumulators with its own row's scale.  Nothing about a row ever leaves its thread.
 //
@@ -47,7 +47,7 @@ constexpr int kStageK = 256;                                 // weights per row 
 constexpr int kStageRowBytes = kStageK / 2;                  // 128 B of packed int4 per row
 constexpr int kWHalfBytes = kHalfRows * kStageRowBytes;      // 16 KiB
 constexpr int kWStageBytes = 2 * kWHalfBytes;                // 32 KiB
-constexpr int kKCoresPerStage = kStageK / 8;                 // 32 sixteen-byte K cores
+constexpr int kXBoxesPerStage = kStageK / 64;                // activation boxes of 64 k (128 bytes) per stage
 constexpr int kConsumerThreads = 256;
 constexpr int kProducerWarp = 8;
 constexpr int kMmaWarp = 9;   // issues the MMAs of half 0 and owns the TMEM allocation; warp 10 issues half 1
@@ -163,7 +163,7 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
     if (tid == 0) {
         for (int i = 0; i < C::kStages; ++i) {
             mbar_init(smem_u32(&ctrl->full[i]), 1);
-            mbar_init(smem_u32(&ctrl->empty[i]), kConsumerThreads / 32);
+            mbar_init(smem_u32(&ctrl->empty[i]), kConsumerThreads / 32 + 2);  // + one MMA commit per half
             mbar_init(smem_u32(&ctrl->x_ready[i]), kConsumerThreads / 32);
         }
         for (int w = 0; w < 2; ++w)
@@ -218,7 +218,12 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
                     tma_load_2d(dst, &p.w_map[ti.seg], full, s * kStageRowBytes, ti.row0, pol_w);
                     tma_load_2d(dst + kWHalfBytes, &p.w_map[map_b], full, s * kStageRowBytes, row_b, pol_w);
                 }
-                if (acts) tma_load_3d(dst + kWStageBytes, &p.x_map, full, 0, 0, s * kKCoresPerStage, pol_x);
+                if (acts) {
+                    // activations: four [NMMA rows][64 k] boxes, each in the 128-byte-swizzled K-major layout
+#pragma unroll
+                    for (int b = 0; b < kXBoxesPerStage; ++b)
+                        tma_load_2d(dst + kWStageBytes + b * (NMMA * 128), &p.x_map, full, s * kStageK + b * 64, 0, pol_x);
+                }
             };
             const long long total_mine = u_end - u_begin;
             const uint32_t pre = static_cast<uint32_t>(total_mine < C::kStages ? total_mine : C::kStages);
@@ -249,11 +254,11 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
         if (lane == 0) {
             const int w = warp - kMmaWarp;
             constexpr uint32_t idesc = umma_idesc_f16_f32(128, NMMA);
-            constexpr uint32_t lbo = NMMA * 16;  // between the two K cores of one step
-            constexpr uint32_t sbo = 128;        // between 8-row groups
-            // shared-memory descriptor: only the 14-bit start address changes between MMAs
-            constexpr uint32_t desc_hi = ((sbo >> 4) & 0x3FFFu) | (1u << 14);
-            constexpr uint32_t desc_lo_const = ((lbo >> 4) & 0x3FFFu) << 16;
+            // Shared-memory descriptor of the activation operand: K-major, 128-byte swizzle (rows of 64 k,
+            // 8-row groups 1024 bytes apart); only the 14-bit start address changes between MMAs.
+            constexpr uint32_t sbo = 1024;
+            constexpr uint32_t desc_hi = ((sbo >> 4) & 0x3FFFu) | (1u << 14) | (2u << 29);  // version 1, SWIZZLE_128B
+            constexpr uint32_t desc_lo_const = 1u << 16;  // leading-dimension offset: unused for swizzled K-major
             uint32_t n = 0;
             bool ok = true;
             for (long long u = u_begin; u < u_end && ok; ++u, ++n) {
@@ -269,12 +274,17 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
                     const uint32_t d_t = tmem_base + 256 + w * 64 + gi * 32;
 #pragma unroll
                     for (int i = 0; i < 8; ++i) {
-                        const uint32_t lo = xlo + (((gi * 16 + i * 2) * lbo) >> 4);
+                        // K step kk = gi * 8 + i of the stage: box kk / 4, then 32 bytes per step inside the box
+                        const uint32_t kk = gi * 8 + i;
+                        const uint32_t lo = xlo + (((kk >> 2) * (NMMA * 128) + (kk & 3) * 32) >> 4);
                         const uint64_t bdesc = (static_cast<uint64_t>(desc_hi) << 32) | lo;
                         umma_ts_f16(d_t, a_t + i * 8, bdesc, idesc, i > 0 ? 1u : 0u);
                     }
                     umma_commit(smem_u32(&ctrl->d_full[w][gi]));
                 }
+                // the stage's activations are no longer read once both groups' MMAs have completed: hand the
+                // slot back from here instead of from the read-out a stage later, so one more load is in flight
+                if (ok) umma_commit(smem_u32(&ctrl->empty[slot]));
             }
         }
         if (p.cluster > 1) { __syncwarp(); cluster_sync_all(); cluster_sync_all(); }
@@ -380,16 +390,31 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
                         dequant_word(v.z, a + c * 16 + 8);
                         dequant_word(v.w, a + c * 16 + 12);
                     }
-                    if (have_prev) {  // previous stage's group gi: frees A[gi] and D[gi]
-                        readout(gi, (n - 1) & 1u, gi ? sc_pend1 : sc_pend0);
-                        if (!ok) break;
-                        if (gi == 1) {  // both groups of the previous stage are done with its smem slot
-                            __syncwarp();
-                            if (lane == 0) mbar_arrive(empty0 + ((n - 1) % C::kStages) * 8);
+                    if (gi == 1) {  // this warp has read all its weights of the stage
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(empty0 + slot * 8);
+                    }
+                    // Previous stage's group gi frees A[gi] and D[gi].  Its accumulator fetch and this group's
+                    // operand stores are issued back to back so that their TMEM latencies overlap.
+                    uint32_t d[NREAD];
+                    if (have_prev) {
+                        if (!mbar_wait(dfull0 + gi * 8, (n - 1) & 1u, abort_flag)) { ok = false; break; }
+                        tc_fence_after_sync();
+                        if constexpr (NREAD == 8) {
+                            tmem_ld8(d_t0 + gi * 32, d);
+                        } else {
+#pragma unroll
+                            for (int c = 0; c < NREAD / 16; ++c) tmem_ld16(d_t0 + gi * 32 + c * 16, d + c * 16);
                         }
                     }
 #pragma unroll
                     for (int c = 0; c < 4; ++c) tmem_st16(a_t0 + gi * 64 + c * 16, a + c * 16);
+                    if (have_prev) {
+                        tmem_wait_ld();
+                        const float scale = gi ? sc_pend1 : sc_pend0;
+#pragma unroll
+                        for (int j = 0; j < NREAD; ++j) acc[j] = fmaf(__uint_as_float(d[j]), scale, acc[j]);
+                    }
                     tmem_wait_st();
                     tc_fence_before_sync();
                     __syncwarp();
@@ -404,8 +429,6 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
             readout(0, (n - 1) & 1u, sc_pend0);
             if (ok) readout(1, (n - 1) & 1u, sc_pend1);
             if (!ok) break;
-            __syncwarp();
-            if (lane == 0) mbar_arrive(empty0 + ((n - 1) % C::kStages) * 8);
 
             if (tid == 0) stamp(p, 3);
             // ---------------------------------------------------------------- tile epilogue
@@ -434,7 +457,7 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
                 {
                     const uint32_t base = smem_u32(part) + ((my_rank * rows_cap) * kTileRows + tid) * 4;
                     uint32_t owner = 0, jl = 0;
-#pragma unroll 1
+#pragma unroll 4
                     for (int j = 0; j < m_rows; ++j) {
                         st_shared_cluster_f32(mapa_shared_cluster(base, owner) + jl * (kTileRows * 4),
                                               stage_acc[j * kTileRows + tid]);
@@ -445,7 +468,7 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
                 ++cluster_syncs;
                 {
                     uint32_t jl = 0;
-#pragma unroll 1
+#pragma unroll 2
                     for (int j = static_cast<int>(my_rank); j < m_rows; j += static_cast<int>(csz), ++jl) {
                         float sum = 0.f;
 #pragma unroll 1
@@ -498,7 +521,7 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
                     if (wg == 0 && valid) {
                         OutT* y = static_cast<OutT*>(p.seg[0].y) + my_row;
                         const long long ldy = p.seg[0].ldy;
-#pragma unroll 1
+#pragma unroll 4
                         for (int j = j0; j < m_rows; j += jstep) {
                             const float g = stage_acc[j * kTileRows + t];
                             const float up = stage_acc[j * kTileRows + kHalfRows + t];
@@ -509,7 +532,7 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
                     OutT* y = static_cast<OutT*>(sg.y) + my_row;
                     const long long ldy = sg.ldy;
                     const float b = sg.bias ? sg.bias[my_row] : 0.f;
-#pragma unroll 1
+#pragma unroll 4
                     for (int j = j0; j < m_rows; j += jstep)
                         store_out<OutT>(y + static_cast<long long>(j) * ldy, stage_acc[j * kTileRows + tid] + b);
                 }
@@ -563,14 +586,15 @@ bool encode_w_map(CUtensorMap* map, const uint8_t* w, long long n, long long k) 
 }
 
 bool encode_x_map(CUtensorMap* map, const __half* x, long long m, long long k, int nmma) {
-    // view X[m][k] as (8 elements, m rows, k/8 cores): a box lands as [core][row][16 B], the canonical
-    // K-major core-matrix layout of the MMA's shared-memory operand
-    const cuuint64_t dims[3] = {8, static_cast<cuuint64_t>(m), static_cast<cuuint64_t>(k / 8)};
-    const cuuint64_t strides[2] = {static_cast<cuuint64_t>(k) * 2, 16};
-    const cuuint32_t box[3] = {8, static_cast<cuuint32_t>(nmma), kKCoresPerStage};
-    const cuuint32_t estr[3] = {1, 1, 1};
-    return encode_fn()(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<__half*>(x), dims, strides, box, estr,
-                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+    // A box of [nmma rows][64 k] lands as 128-byte rows whose 16-byte chunks are XOR-swizzled by the row
+    // index: the canonical 128-byte-swizzled K-major layout of the MMA's shared-memory operand.  One row of
+    // the box is one 128-byte request (a 16-byte-wide box would be one request per 8 elements).
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(k), static_cast<cuuint64_t>(m)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(k) * 2};
+    const cuuint32_t box[2] = {64, static_cast<cuuint32_t>(nmma)};
+    const cuuint32_t estr[2] = {1, 1};
+    return encode_fn()(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<__half*>(x), dims, strides, box, estr,
+                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
