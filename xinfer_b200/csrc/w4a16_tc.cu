@@ -57,12 +57,17 @@ constexpr int kMaxSegs = 4;
 
 template <int NMMA>
 struct Cfg {
+    // Two rings.  A weight slot is free again as soon as the consumers have unpacked it; an activation slot
+    // only when the MMAs that read it have completed, about a stage later.  Keeping them apart lets the
+    // weight stream (the HBM traffic) run as far ahead as its own ring allows.
     static constexpr int kXStageBytes = NMMA * kStageK * 2;
-    static constexpr int kStageBytes = kWStageBytes + kXStageBytes;
-    static constexpr int kStages = (NMMA == 32) ? 4 : 5;
+    static constexpr int kStages = (NMMA == 32) ? 4 : 5;   // weight ring, 32 KiB per slot
+    static constexpr int kXStages = (NMMA == 32) ? 4 : 6;  // activation ring
+    static constexpr int kWRingBytes = kStages * kWStageBytes;
+    static constexpr int kXRingBytes = kXStages * kXStageBytes;
     static constexpr int kXchgBytes = kTileRows * NMMA * 4;  // accumulators parked for the epilogue
     static constexpr int kCtrlBytes = 512;
-    static constexpr int kSmemBytes = kStages * kStageBytes + kXchgBytes + kCtrlBytes + 1024;  // + align slack
+    static constexpr int kSmemBytes = kWRingBytes + kXRingBytes + kXchgBytes + kCtrlBytes + 1024;  // + align slack
 };
 
 struct Seg {
@@ -93,9 +98,11 @@ struct Params {
 };
 
 struct Ctrl {
-    uint64_t full[8];
-    uint64_t empty[8];
-    uint64_t x_ready[8];
+    uint64_t full[8];     // weights of a stage have landed
+    uint64_t empty[8];    // every consumer warp has unpacked them
+    uint64_t x_full[8];   // activations of a stage have landed
+    uint64_t x_ready[8];  // every consumer warp has reordered its share of them
+    uint64_t x_empty[8];  // both halves' MMAs that read them have completed
     uint64_t a_full[2][2];
     uint64_t d_full[2][2];
     uint32_t tmem_base;
@@ -149,7 +156,8 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
     using C = Cfg<NMMA>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint8_t* xchg_raw = smem + C::kStages * C::kStageBytes;
+    uint8_t* xring = smem + C::kWRingBytes;
+    uint8_t* xchg_raw = xring + C::kXRingBytes;
     Ctrl* ctrl = reinterpret_cast<Ctrl*>(xchg_raw + C::kXchgBytes);
     float* xchg = reinterpret_cast<float*>(xchg_raw);
 
@@ -163,8 +171,12 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
     if (tid == 0) {
         for (int i = 0; i < C::kStages; ++i) {
             mbar_init(smem_u32(&ctrl->full[i]), 1);
-            mbar_init(smem_u32(&ctrl->empty[i]), kConsumerThreads / 32 + 2);  // + one MMA commit per half
+            mbar_init(smem_u32(&ctrl->empty[i]), kConsumerThreads / 32);
+        }
+        for (int i = 0; i < C::kXStages; ++i) {
+            mbar_init(smem_u32(&ctrl->x_full[i]), 1);
             mbar_init(smem_u32(&ctrl->x_ready[i]), kConsumerThreads / 32);
+            mbar_init(smem_u32(&ctrl->x_empty[i]), 2);  // one MMA commit per half
         }
         for (int w = 0; w < 2; ++w)
             for (int b = 0; b < 2; ++b) {
@@ -195,63 +207,92 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
     // scale is taken as zero, so the code below never branches on the group count.
     if (warp == kProducerWarp) {
         // ------------------------------------------------------------------ TMA producer
-        if (lane == 0) {
+        // The whole warp runs the (warp-uniform) index arithmetic and the waits; one elected lane issues.
+        const bool leader = elect_one_sync();
+        if (leader) {
             for (int i = 0; i < kMaxSegs; ++i)
                 if (i < (p.swiglu ? 2 : p.num_segs)) tma_prefetch_desc(&p.w_map[i]);
             tma_prefetch_desc(&p.x_map);
-            const uint64_t pol_w = l2_policy_evict_first();
-            const uint64_t pol_x = l2_policy_evict_last();
-            // The weights do not depend on the previous kernel in the stream, the activations do: the first
-            // ring of weight tiles is requested before waiting for that kernel, so the weight stream is
-            // already in flight while it drains (programmatic dependent launch).
-            auto issue = [&](long long u, uint32_t n, bool weights, bool acts) {
-                const int slot = n % C::kStages;
-                const int tile = static_cast<int>(u / S);
-                const int s = static_cast<int>(u - static_cast<long long>(tile) * S);
-                const TileInfo ti = locate_tile(p, tile);
-                const uint32_t full = smem_u32(&ctrl->full[slot]);
-                const uint32_t dst = smem_u32(smem + slot * C::kStageBytes);
-                if (weights) {
-                    mbar_arrive_expect_tx(full, C::kStageBytes);
-                    const int map_b = p.swiglu ? 1 : ti.seg;
-                    const int row_b = p.swiglu ? ti.row0 : ti.row0 + kHalfRows;
-                    tma_load_2d(dst, &p.w_map[ti.seg], full, s * kStageRowBytes, ti.row0, pol_w);
-                    tma_load_2d(dst + kWHalfBytes, &p.w_map[map_b], full, s * kStageRowBytes, row_b, pol_w);
-                }
-                if (acts) {
-                    // activations: four [NMMA rows][64 k] boxes, each in the 128-byte-swizzled K-major layout
-#pragma unroll
-                    for (int b = 0; b < kXBoxesPerStage; ++b)
-                        tma_load_2d(dst + kWStageBytes + b * (NMMA * 128), &p.x_map, full, s * kStageK + b * 64, 0, pol_x);
-                }
-            };
-            const long long total_mine = u_end - u_begin;
-            const uint32_t pre = static_cast<uint32_t>(total_mine < C::kStages ? total_mine : C::kStages);
-            for (uint32_t n = 0; n < pre; ++n) issue(u_begin + n, n, true, false);
-            griddep_wait();
-            for (uint32_t n = 0; n < pre; ++n) issue(u_begin + n, n, false, true);
-            uint32_t n = pre;
-            for (long long u = u_begin + pre; u < u_end; ++u, ++n) {
-                const int slot = n % C::kStages;
-                const uint32_t ph = (n / C::kStages) & 1u;
-                if (!mbar_wait_parked(smem_u32(&ctrl->empty[slot]), ph ^ 1u, abort_flag)) break;
-                issue(u, n, true, true);
+        }
+        const uint64_t pol_w = l2_policy_evict_first();
+        const uint64_t pol_x = l2_policy_evict_last();
+        const uint32_t total_mine = static_cast<uint32_t>(u_end - u_begin);
+        // (tile, stage-in-tile) of the next stage to request, one cursor per ring
+        int w_tile = static_cast<int>(u_begin / S);
+        int w_s = static_cast<int>(u_begin - static_cast<long long>(w_tile) * S);
+        int x_s = w_s;
+        const uint32_t smem_w = smem_u32(smem);
+        const uint32_t smem_x = smem_u32(xring);
+        auto issue_w = [&](uint32_t n) {
+            const uint32_t slot = n % C::kStages;
+            const TileInfo ti = locate_tile(p, w_tile);
+            const uint32_t full = smem_u32(&ctrl->full[slot]);
+            const uint32_t dst = smem_w + slot * kWStageBytes;
+            const int map_b = p.swiglu ? 1 : ti.seg;
+            const int row_b = p.swiglu ? ti.row0 : ti.row0 + kHalfRows;
+            if (leader) {
+                mbar_arrive_expect_tx(full, kWStageBytes);
+                tma_load_2d(dst, &p.w_map[ti.seg], full, w_s * kStageRowBytes, ti.row0, pol_w);
+                tma_load_2d(dst + kWHalfBytes, &p.w_map[map_b], full, w_s * kStageRowBytes, row_b, pol_w);
             }
-            if (*abort_flag) {
-                // give the copies still in flight a bounded chance to land before the CTA exits
-                for (int i = 0; i < C::kStages && i < static_cast<int>(n); ++i) {
-                    const uint32_t k = n - 1 - i;
-                    const long long t0 = clock64();
-                    while (!mbar_try_wait(smem_u32(&ctrl->full[k % C::kStages]), (k / C::kStages) & 1u) &&
-                           clock64() - t0 < kWaitLimitClocks / 8) {
-                    }
+            if (++w_s == S) { w_s = 0; ++w_tile; }
+        };
+        auto issue_x = [&](uint32_t n) {
+            // activations: four [NMMA rows][64 k] boxes, each in the 128-byte-swizzled K-major layout
+            const uint32_t slot = n % C::kXStages;
+            const uint32_t full = smem_u32(&ctrl->x_full[slot]);
+            const uint32_t dst = smem_x + slot * C::kXStageBytes;
+            if (leader) {
+                mbar_arrive_expect_tx(full, C::kXStageBytes);
+#pragma unroll
+                for (int b = 0; b < kXBoxesPerStage; ++b)
+                    tma_load_2d(dst + b * (NMMA * 128), &p.x_map, full, x_s * kStageK + b * 64, 0, pol_x);
+            }
+            if (++x_s == S) x_s = 0;
+        };
+        // The weights do not depend on the previous kernel in the stream, the activations do: the first
+        // ring of weight tiles is requested before waiting for that kernel, so the weight stream is
+        // already in flight while it drains (programmatic dependent launch).
+        const uint32_t pre_w = total_mine < C::kStages ? total_mine : C::kStages;
+        const uint32_t pre_x = total_mine < C::kXStages ? total_mine : C::kXStages;
+        for (uint32_t n = 0; n < pre_w; ++n) issue_w(n);
+        griddep_wait();
+        for (uint32_t n = 0; n < pre_x; ++n) issue_x(n);
+        uint32_t nw = pre_w, nx = pre_x;
+        bool ok = true;
+        while (ok && (nw < total_mine || nx < total_mine)) {
+            if (nw < total_mine) {
+                ok = mbar_wait_parked(smem_u32(&ctrl->empty[nw % C::kStages]), ((nw / C::kStages) & 1u) ^ 1u, abort_flag);
+                if (ok) issue_w(nw++);
+            }
+            if (ok && nx < total_mine) {
+                ok = mbar_wait_parked(smem_u32(&ctrl->x_empty[nx % C::kXStages]), ((nx / C::kXStages) & 1u) ^ 1u, abort_flag);
+                if (ok) issue_x(nx++);
+            }
+        }
+        if (*abort_flag) {
+            // give the copies still in flight a bounded chance to land before the CTA exits
+            const long long t0 = clock64();
+            for (int i = 0; i < C::kStages && i < static_cast<int>(nw); ++i) {
+                const uint32_t k = nw - 1 - i;
+                while (!mbar_try_wait(smem_u32(&ctrl->full[k % C::kStages]), (k / C::kStages) & 1u) &&
+                       clock64() - t0 < kWaitLimitClocks / 8) {
+                }
+            }
+            for (int i = 0; i < C::kXStages && i < static_cast<int>(nx); ++i) {
+                const uint32_t k = nx - 1 - i;
+                while (!mbar_try_wait(smem_u32(&ctrl->x_full[k % C::kXStages]), (k / C::kXStages) & 1u) &&
+                       clock64() - t0 < kWaitLimitClocks / 8) {
                 }
             }
         }
+        __syncwarp();
         if (p.cluster > 1) { __syncwarp(); cluster_sync_all(); cluster_sync_all(); }
     } else if (warp == kMmaWarp || warp == kMmaWarp + 1) {
-        // ------------------------------------------------------------------ MMA issuers, one thread per half
-        if (lane == 0) {
+        // ------------------------------------------------------------------ MMA issuers, one warp per half
+        // The warp waits and computes descriptors as a whole (warp-uniform values); one elected lane issues.
+        {
+            const bool leader = elect_one_sync();
             const int w = warp - kMmaWarp;
             constexpr uint32_t idesc = umma_idesc_f16_f32(128, NMMA);
             // Shared-memory descriptor of the activation operand: K-major, 128-byte swizzle (rows of 64 k,
@@ -259,32 +300,39 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
             constexpr uint32_t sbo = 1024;
             constexpr uint32_t desc_hi = ((sbo >> 4) & 0x3FFFu) | (1u << 14) | (2u << 29);  // version 1, SWIZZLE_128B
             constexpr uint32_t desc_lo_const = 1u << 16;  // leading-dimension offset: unused for swizzled K-major
-            uint32_t n = 0;
+            // (in a cluster launch a shared-window address carries the CTA's rank in its upper bits: keep 14 bits)
+            const uint32_t xring_lo = (smem_u32(xring) >> 4) & 0x3FFFu;
+            const uint32_t xready0 = smem_u32(&ctrl->x_ready[0]);
+            const uint32_t xempty0 = smem_u32(&ctrl->x_empty[0]);
+            const uint32_t afull0 = smem_u32(&ctrl->a_full[w][0]);
+            const uint32_t dfull0 = smem_u32(&ctrl->d_full[w][0]);
+            const uint32_t a_t0 = tmem_base + w * 128;
+            const uint32_t d_t0 = tmem_base + 256 + w * 64;
+            const uint32_t total_mine = static_cast<uint32_t>(u_end - u_begin);
             bool ok = true;
-            for (long long u = u_begin; u < u_end && ok; ++u, ++n) {
-                const int slot = n % C::kStages;
-                if (!mbar_wait_parked(smem_u32(&ctrl->x_ready[slot]), (n / C::kStages) & 1u, abort_flag)) break;
-                // (in a cluster launch a shared-window address carries the CTA's rank in its upper bits: keep 14 bits)
-                const uint32_t xlo = desc_lo_const | ((smem_u32(smem + slot * C::kStageBytes + kWStageBytes) >> 4) & 0x3FFFu);
+            for (uint32_t n = 0; n < total_mine && ok; ++n) {
+                const uint32_t slot = n % C::kXStages;
+                if (!mbar_wait_parked(xready0 + slot * 8, (n / C::kXStages) & 1u, abort_flag)) break;
+                const uint32_t xlo = desc_lo_const | (xring_lo + slot * (C::kXStageBytes >> 4));
 #pragma unroll
                 for (int gi = 0; gi < 2; ++gi) {
-                    if (!mbar_wait_parked(smem_u32(&ctrl->a_full[w][gi]), n & 1u, abort_flag)) { ok = false; break; }
+                    if (!mbar_wait_parked(afull0 + gi * 8, n & 1u, abort_flag)) { ok = false; break; }
                     tc_fence_after_sync();
-                    const uint32_t a_t = tmem_base + w * 128 + gi * 64;
-                    const uint32_t d_t = tmem_base + 256 + w * 64 + gi * 32;
+                    if (leader) {
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        // K step kk = gi * 8 + i of the stage: box kk / 4, then 32 bytes per step inside the box
-                        const uint32_t kk = gi * 8 + i;
-                        const uint32_t lo = xlo + (((kk >> 2) * (NMMA * 128) + (kk & 3) * 32) >> 4);
-                        const uint64_t bdesc = (static_cast<uint64_t>(desc_hi) << 32) | lo;
-                        umma_ts_f16(d_t, a_t + i * 8, bdesc, idesc, i > 0 ? 1u : 0u);
+                        for (int i = 0; i < 8; ++i) {
+                            // K step kk = gi * 8 + i of the stage: box kk / 4, then 32 bytes per step inside the box
+                            const uint32_t kk = gi * 8 + i;
+                            const uint32_t lo = xlo + (((kk >> 2) * (NMMA * 128) + (kk & 3) * 32) >> 4);
+                            const uint64_t bdesc = (static_cast<uint64_t>(desc_hi) << 32) | lo;
+                            umma_ts_f16(d_t0 + gi * 32, a_t0 + gi * 64 + i * 8, bdesc, idesc, i > 0 ? 1u : 0u);
+                        }
+                        umma_commit(dfull0 + gi * 8);
+                        // the stage's activations are no longer read once both groups' MMAs have completed
+                        if (gi == 1) umma_commit(xempty0 + slot * 8);
                     }
-                    umma_commit(smem_u32(&ctrl->d_full[w][gi]));
+                    __syncwarp();
                 }
-                // the stage's activations are no longer read once both groups' MMAs have completed: hand the
-                // slot back from here instead of from the read-out a stage later, so one more load is in flight
-                if (ok) umma_commit(smem_u32(&ctrl->empty[slot]));
             }
         }
         if (p.cluster > 1) { __syncwarp(); cluster_sync_all(); cluster_sync_all(); }
@@ -300,8 +348,10 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
 #pragma unroll
         for (int c = 0; c < 8; ++c) w_off[c] = wg * kWHalfBytes + t * kStageRowBytes + ((c ^ (t & 7)) << 4);
         const uint32_t smem_base = smem_u32(smem);
+        const uint32_t xring_base = smem_u32(xring);
         const uint32_t full0 = smem_u32(&ctrl->full[0]);
         const uint32_t empty0 = smem_u32(&ctrl->empty[0]);
+        const uint32_t xfull0 = smem_u32(&ctrl->x_full[0]);
         const uint32_t xready0 = smem_u32(&ctrl->x_ready[0]);
         const uint32_t afull0 = smem_u32(&ctrl->a_full[wg][0]);
         const uint32_t dfull0 = smem_u32(&ctrl->d_full[wg][0]);
@@ -357,15 +407,15 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
                     sc_next0 = (2 * s + 2 < gmax) ? __half2float(my_scales[2 * s + 2]) : 0.f;
                     sc_next1 = (2 * s + 3 < gmax) ? __half2float(my_scales[2 * s + 3]) : 0.f;
                 }
-                if (!mbar_wait(full0 + slot * 8, (n / C::kStages) & 1u, abort_flag)) { ok = false; break; }
-                if (tid == 0 && n == 0) stamp(p, 2);
-                const uint32_t stage = smem_base + slot * C::kStageBytes;
+                const uint32_t xslot = n % C::kXStages;
+                if (!mbar_wait(xfull0 + xslot * 8, (n / C::kXStages) & 1u, abort_flag)) { ok = false; break; }
+                const uint32_t stage = smem_base + slot * kWStageBytes;
 
                 // activations: reorder each 8-k block to (0,4,1,5,2,6,3,7), in place
                 {
 #pragma unroll
                     for (int i = 0; i < C::kXStageBytes / 16 / kConsumerThreads; ++i) {
-                        const uint32_t addr = stage + kWStageBytes + (tid + i * kConsumerThreads) * 16;
+                        const uint32_t addr = xring_base + xslot * C::kXStageBytes + (tid + i * kConsumerThreads) * 16;
                         const uint4 v = lds128(addr);
                         uint4 o;
                         o.x = prmt(v.x, v.z, 0x5410u);
@@ -376,8 +426,10 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
                     }
                     fence_proxy_async_smem();
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(xready0 + slot * 8);
+                    if (lane == 0) mbar_arrive(xready0 + xslot * 8);
                 }
+                if (!mbar_wait(full0 + slot * 8, (n / C::kStages) & 1u, abort_flag)) { ok = false; break; }
+                if (tid == 0 && n == 0) stamp(p, 2);
 
 #pragma unroll
                 for (int gi = 0; gi < 2; ++gi) {
