@@ -119,6 +119,14 @@ __device__ __forceinline__ int unit_owner(long long unit, long long total, long 
     return static_cast<int>(((unit + 1) * ctas + total - 1) / total - 1);
 }
 
+// Non-blocking L2 prefetch of [ptr, ptr + bytes), one request per 32-byte sector.
+__device__ __forceinline__ void prefetch_l2_range(const void* ptr, int bytes) {
+    const uintptr_t lo = reinterpret_cast<uintptr_t>(ptr) & ~uintptr_t(31);
+    const uintptr_t hi = reinterpret_cast<uintptr_t>(ptr) + static_cast<uintptr_t>(bytes > 0 ? bytes : 0);
+#pragma unroll 1
+    for (uintptr_t a = lo; a < hi; a += 32) asm volatile("prefetch.global.L2 [%0];" ::"l"(a));
+}
+
 template <typename OutT>
 __device__ __forceinline__ void store_out(OutT* p, float v);
 template <>
@@ -390,23 +398,45 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
             const bool valid = my_row < sg.n;
             const __half* my_scales = sg.scales + static_cast<long long>(valid ? my_row : 0) * p.groups;
             const int gmax = valid ? p.groups : 0;  // scale index limit; rows beyond N use scale 0
+            // A row's scales are 2 bytes per 128 k, far apart from its neighbours': behind a saturated weight
+            // stream a miss on them waits microseconds.  Pull this tile's (first tile of the CTA only) and
+            // the next tile's scale bytes into L2 now, so the loads in the loop only ever see L2 latency.
+            {
+                if (u == u_begin && valid) prefetch_l2_range(my_scales + 2 * s0, (min(2 * s1, gmax) - 2 * s0) * 2);
+                const long long u_next = u + (s1 - s0);
+                if (u_next < u_end) {
+                    const int tile_n = tile + 1;
+                    const TileInfo tn = locate_tile(p, tile_n);
+                    const Seg& sn = p.seg[p.swiglu ? wg : tn.seg];
+                    const int row_n = p.swiglu ? tn.row0 + t : tn.row0 + wg * kHalfRows + t;
+                    const int s1n = static_cast<int>(min(static_cast<long long>(S), u_end - u_next));
+                    if (row_n < sn.n)
+                        prefetch_l2_range(sn.scales + static_cast<long long>(row_n) * p.groups, min(2 * s1n, p.groups) * 2);
+                }
+            }
 
 #pragma unroll
             for (int j = 0; j < NREAD; ++j) acc[j] = 0.f;
 
-            float sc_pend0 = 0.f, sc_pend1 = 0.f, sc_cur0, sc_cur1, sc_next0, sc_next1;
-            sc_next0 = (2 * s0 < gmax) ? __half2float(my_scales[2 * s0]) : 0.f;
-            sc_next1 = (2 * s0 + 1 < gmax) ? __half2float(my_scales[2 * s0 + 1]) : 0.f;
+            // The row's two scales of a stage are fetched two stages ahead as raw 16-bit values and only
+            // converted when the stage starts, so the load latency never sits in the loop's critical path.
+            const unsigned short* raw_scales = reinterpret_cast<const unsigned short*>(my_scales);
+            auto load_scales = [&](int g) -> uint32_t {  // groups g and g + 1, packed
+                const uint32_t a = g < gmax ? __ldg(raw_scales + g) : 0u;
+                const uint32_t b = g + 1 < gmax ? __ldg(raw_scales + g + 1) : 0u;
+                return a | (b << 16);
+            };
+            float sc_pend0 = 0.f, sc_pend1 = 0.f, sc_cur0, sc_cur1;
+            uint32_t q0 = load_scales(2 * s0);
+            uint32_t q1 = (s0 + 1 < s1) ? load_scales(2 * s0 + 2) : 0u;
             bool have_prev = false;
 
             for (int s = s0; s < s1 && ok; ++s, ++n) {
                 const uint32_t slot = n % C::kStages;
-                sc_cur0 = sc_next0;
-                sc_cur1 = sc_next1;
-                if (s + 1 < s1) {  // scales of the next stage, consumed one stage later
-                    sc_next0 = (2 * s + 2 < gmax) ? __half2float(my_scales[2 * s + 2]) : 0.f;
-                    sc_next1 = (2 * s + 3 < gmax) ? __half2float(my_scales[2 * s + 3]) : 0.f;
-                }
+                sc_cur0 = __half2float(__ushort_as_half(static_cast<unsigned short>(q0 & 0xFFFFu)));
+                sc_cur1 = __half2float(__ushort_as_half(static_cast<unsigned short>(q0 >> 16)));
+                q0 = q1;
+                if (s + 2 < s1) q1 = load_scales(2 * s + 4);
                 const uint32_t xslot = n % C::kXStages;
                 if (!mbar_wait(xfull0 + xslot * 8, (n / C::kXStages) & 1u, abort_flag)) { ok = false; break; }
                 const uint32_t stage = smem_base + slot * kWStageBytes;
