@@ -48,10 +48,20 @@ constexpr int kStageRowBytes = kStageK / 2;                  // 128 B of packed 
 constexpr int kWHalfBytes = kHalfRows * kStageRowBytes;      // 16 KiB
 constexpr int kWStageBytes = 2 * kWHalfBytes;                // 32 KiB
 constexpr int kXBoxesPerStage = kStageK / 64;                // activation boxes of 64 k (128 bytes) per stage
-constexpr int kConsumerThreads = 256;
-constexpr int kProducerWarp = 8;
-constexpr int kMmaWarp = 9;   // issues the MMAs of half 0 and owns the TMEM allocation; warp 10 issues half 1
-constexpr int kThreads = 352;
+constexpr int kConsumerThreads = 512;  // warps 0..15
+constexpr int kProducerWarp = 16;
+constexpr int kMmaWarp = 17;  // issues the MMAs of half 0 and owns the TMEM allocation; warp 18 issues half 1
+constexpr int kIdleWarp = 19;
+constexpr int kThreads = 640;
+// Register re-split between warpgroups.  The kernel starts with kLaunchRegs per thread (what 640 threads leave
+// of the 64K file); the helper warpgroup releases down to kHelperRegs and the four consumer warpgroups grow
+// to kConsumerRegs.  A consumer's request blocks until the CTA's own released registers cover it, so the
+// released amount must be at least the requested one.
+constexpr int kLaunchRegs = 96;
+constexpr int kConsumerRegs = 112;
+constexpr int kHelperRegs = 32;
+static_assert(kConsumerThreads * (kConsumerRegs - kLaunchRegs) <= (kThreads - kConsumerThreads) * (kLaunchRegs - kHelperRegs),
+              "consumer register request exceeds what the helper warpgroup releases");
 constexpr uint32_t kTmemCols = 512;
 constexpr int kMaxSegs = 4;
 
@@ -105,6 +115,7 @@ struct Ctrl {
     uint64_t x_empty[8];  // both halves' MMAs that read them have completed
     uint64_t a_full[2][2];
     uint64_t d_full[2][2];
+    uint64_t epi;         // epilogue barrier of the consumer warps
     uint32_t tmem_base;
     int abort_flag;
     int is_last;
@@ -191,6 +202,7 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
                 mbar_init(smem_u32(&ctrl->a_full[w][b]), kHalfRows / 32);
                 mbar_init(smem_u32(&ctrl->d_full[w][b]), 1);
             }
+        mbar_init(smem_u32(&ctrl->epi), kConsumerThreads / 32);
         ctrl->abort_flag = 0;
         ctrl->is_last = 0;
         mbar_fence_init();
@@ -213,6 +225,9 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
     // Every stage carries exactly two 128-k groups.  When K/128 is odd the second group of a tile's last
     // stage lies beyond the tensors' extent: TMA fills it with zeros, its products are zero, and its
     // scale is taken as zero, so the code below never branches on the group count.
+    // The helper warpgroup (producer, MMA issuers) hands most of its registers to the four consumer warpgroups.
+    if (warp >= kProducerWarp) {
+    setmaxnreg_dec<kHelperRegs>();
     if (warp == kProducerWarp) {
         // ------------------------------------------------------------------ TMA producer
         // The whole warp runs the (warp-uniform) index arithmetic and the waits; one elected lane issues.
@@ -345,46 +360,74 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
         }
         if (p.cluster > 1) { __syncwarp(); cluster_sync_all(); cluster_sync_all(); }
     } else {
+        // kIdleWarp fills the helper warpgroup (register reallocation works on whole warpgroups)
+        if (p.cluster > 1) { __syncwarp(); cluster_sync_all(); cluster_sync_all(); }
+    }
+    } else {
+        setmaxnreg_inc<kConsumerRegs>();
         // ------------------------------------------------------------------ consumers: unpack, read out, epilogue
-        const int wg = tid >> 7;
-        const int t = tid & 127;
-        const uint32_t lane_sel = static_cast<uint32_t>(((tid >> 5) & 3) * 32) << 16;
-        const uint32_t a_t0 = tmem_base + lane_sel + wg * 128;
-        const uint32_t d_t0 = tmem_base + lane_sel + 256 + wg * 64;
-        // byte offsets of this thread's eight 16-byte chunks inside a stage (128B-swizzled rows)
-        uint32_t w_off[8];
+        // Sixteen warps, four per scheduler.  Warp (half, group, quarter) owns rows quarter*32.. of its
+        // 128-row half (TMEM lanes are only reachable from the warp with the same index mod 4) and, in every
+        // stage, the 128 k of one group: its thread unpacks 64 bytes of its row, hands them to the MMA and
+        // folds the previous stage's accumulator of the same group into its own fp32 registers.  The two
+        // threads that share a row (one per group) add their partial sums in the epilogue.
+        const int quarter = warp & 3;
+        const int gi = (warp >> 2) & 1;
+        const int wg = warp >> 3;
+        const int t = quarter * 32 + lane;      // row within the half = TMEM lane
+        const int rt = wg * kHalfRows + t;      // row within the tile
+        const uint32_t lane_sel = static_cast<uint32_t>(quarter * 32) << 16;
+        const uint32_t a_t = tmem_base + lane_sel + wg * 128 + gi * 64;
+        const uint32_t d_t = tmem_base + lane_sel + 256 + wg * 64 + gi * 32;
+        // byte offsets of this thread's four 16-byte chunks inside a stage (128B-swizzled rows)
+        uint32_t w_off[4];
 #pragma unroll
-        for (int c = 0; c < 8; ++c) w_off[c] = wg * kWHalfBytes + t * kStageRowBytes + ((c ^ (t & 7)) << 4);
+        for (int c = 0; c < 4; ++c) w_off[c] = wg * kWHalfBytes + t * kStageRowBytes + (((gi * 4 + c) ^ (t & 7)) << 4);
         const uint32_t smem_base = smem_u32(smem);
         const uint32_t xring_base = smem_u32(xring);
         const uint32_t full0 = smem_u32(&ctrl->full[0]);
         const uint32_t empty0 = smem_u32(&ctrl->empty[0]);
         const uint32_t xfull0 = smem_u32(&ctrl->x_full[0]);
         const uint32_t xready0 = smem_u32(&ctrl->x_ready[0]);
-        const uint32_t afull0 = smem_u32(&ctrl->a_full[wg][0]);
-        const uint32_t dfull0 = smem_u32(&ctrl->d_full[wg][0]);
+        const uint32_t afull = smem_u32(&ctrl->a_full[wg][gi]);
+        const uint32_t dfull = smem_u32(&ctrl->d_full[wg][gi]);
 
         float acc[NREAD];
         uint32_t n = 0;  // stages processed by this CTA so far
         bool ok = true;
         int cluster_syncs = 0;
 
-        // Read-out of stage n-1 is interleaved into stage n: group gi's accumulator is fetched right before
-        // group gi of the next stage reuses its TMEM buffers, one full group of unpacking after its MMAs
-        // were handed off, which hides the hand-off latency.
-        auto readout = [&](const int gi, const uint32_t phase, const float scale) {
-            if (!mbar_wait(dfull0 + gi * 8, phase, abort_flag)) { ok = false; return; }
-            tc_fence_after_sync();
-            uint32_t d[NREAD];
+        // Barrier among the sixteen consumer warps with a bounded wait (a plain bar.sync would hang the CTA
+        // if one warp had given up on a wait and left): false when the CTA is aborting.
+        const uint32_t epi_bar = smem_u32(&ctrl->epi);
+        uint32_t epi_phase = 0;
+        auto consumer_sync = [&]() -> bool {
+            __syncwarp();
+            if (lane == 0) mbar_arrive(epi_bar);
+            const bool r = mbar_wait(epi_bar, epi_phase, abort_flag);
+            epi_phase ^= 1u;
+            if (!r) ok = false;
+            return r;
+        };
+
+        // acc += scale * D: the accumulator tile of this warp's group, 16 columns at a time
+        auto fold = [&](const float scale) {
             if constexpr (NREAD == 8) {
-                tmem_ld8(d_t0 + gi * 32, d);
+                uint32_t d[8];
+                tmem_ld8(d_t, d);
+                tmem_wait_ld();
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[j] = fmaf(__uint_as_float(d[j]), scale, acc[j]);
             } else {
 #pragma unroll
-                for (int c = 0; c < NREAD / 16; ++c) tmem_ld16(d_t0 + gi * 32 + c * 16, d + c * 16);
-            }
-            tmem_wait_ld();
+                for (int c = 0; c < NREAD / 16; ++c) {
+                    uint32_t d[16];
+                    tmem_ld16(d_t + c * 16, d);
+                    tmem_wait_ld();
 #pragma unroll
-            for (int j = 0; j < NREAD; ++j) acc[j] = fmaf(__uint_as_float(d[j]), scale, acc[j]);
+                    for (int j = 0; j < 16; ++j) acc[c * 16 + j] = fmaf(__uint_as_float(d[j]), scale, acc[c * 16 + j]);
+                }
+            }
         };
 
         long long u = u_begin;
@@ -394,21 +437,20 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
             const int s1 = static_cast<int>(min(static_cast<long long>(S), s0 + (u_end - u)));
             const TileInfo ti = locate_tile(p, tile);
             const Seg& sg = p.seg[p.swiglu ? wg : ti.seg];
-            const int my_row = p.swiglu ? ti.row0 + t : ti.row0 + wg * kHalfRows + t;
+            const int my_row = p.swiglu ? ti.row0 + t : ti.row0 + rt;
             const bool valid = my_row < sg.n;
             const __half* my_scales = sg.scales + static_cast<long long>(valid ? my_row : 0) * p.groups;
             const int gmax = valid ? p.groups : 0;  // scale index limit; rows beyond N use scale 0
             // A row's scales are 2 bytes per 128 k, far apart from its neighbours': behind a saturated weight
             // stream a miss on them waits microseconds.  Pull this tile's (first tile of the CTA only) and
             // the next tile's scale bytes into L2 now, so the loads in the loop only ever see L2 latency.
-            {
+            if (gi == 0) {
                 if (u == u_begin && valid) prefetch_l2_range(my_scales + 2 * s0, (min(2 * s1, gmax) - 2 * s0) * 2);
                 const long long u_next = u + (s1 - s0);
                 if (u_next < u_end) {
-                    const int tile_n = tile + 1;
-                    const TileInfo tn = locate_tile(p, tile_n);
+                    const TileInfo tn = locate_tile(p, tile + 1);
                     const Seg& sn = p.seg[p.swiglu ? wg : tn.seg];
-                    const int row_n = p.swiglu ? tn.row0 + t : tn.row0 + wg * kHalfRows + t;
+                    const int row_n = p.swiglu ? tn.row0 + t : tn.row0 + rt;
                     const int s1n = static_cast<int>(min(static_cast<long long>(S), u_end - u_next));
                     if (row_n < sn.n)
                         prefetch_l2_range(sn.scales + static_cast<long long>(row_n) * p.groups, min(2 * s1n, p.groups) * 2);
@@ -418,30 +460,27 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
 #pragma unroll
             for (int j = 0; j < NREAD; ++j) acc[j] = 0.f;
 
-            // The row's two scales of a stage are fetched two stages ahead as raw 16-bit values and only
-            // converted when the stage starts, so the load latency never sits in the loop's critical path.
+            // The scale of this warp's group is fetched two stages ahead as a raw 16-bit value and only
+            // converted when its stage starts, so the load latency never sits in the loop's critical path.
             const unsigned short* raw_scales = reinterpret_cast<const unsigned short*>(my_scales);
-            auto load_scales = [&](int g) -> uint32_t {  // groups g and g + 1, packed
-                const uint32_t a = g < gmax ? __ldg(raw_scales + g) : 0u;
-                const uint32_t b = g + 1 < gmax ? __ldg(raw_scales + g + 1) : 0u;
-                return a | (b << 16);
+            auto load_scale = [&](int s) -> uint32_t {
+                const int g = 2 * s + gi;
+                return g < gmax ? static_cast<uint32_t>(__ldg(raw_scales + g)) : 0u;
             };
-            float sc_pend0 = 0.f, sc_pend1 = 0.f, sc_cur0, sc_cur1;
-            uint32_t q0 = load_scales(2 * s0);
-            uint32_t q1 = (s0 + 1 < s1) ? load_scales(2 * s0 + 2) : 0u;
+            float sc_pend = 0.f;
+            uint32_t q0 = load_scale(s0);
+            uint32_t q1 = (s0 + 1 < s1) ? load_scale(s0 + 1) : 0u;
             bool have_prev = false;
 
             for (int s = s0; s < s1 && ok; ++s, ++n) {
                 const uint32_t slot = n % C::kStages;
-                sc_cur0 = __half2float(__ushort_as_half(static_cast<unsigned short>(q0 & 0xFFFFu)));
-                sc_cur1 = __half2float(__ushort_as_half(static_cast<unsigned short>(q0 >> 16)));
-                q0 = q1;
-                if (s + 2 < s1) q1 = load_scales(2 * s + 4);
                 const uint32_t xslot = n % C::kXStages;
-                if (!mbar_wait(xfull0 + xslot * 8, (n / C::kXStages) & 1u, abort_flag)) { ok = false; break; }
-                const uint32_t stage = smem_base + slot * kWStageBytes;
+                const float sc_cur = __half2float(__ushort_as_half(static_cast<unsigned short>(q0)));
+                q0 = q1;
+                if (s + 2 < s1) q1 = load_scale(s + 2);
 
                 // activations: reorder each 8-k block to (0,4,1,5,2,6,3,7), in place
+                if (!mbar_wait(xfull0 + xslot * 8, (n / C::kXStages) & 1u, abort_flag)) { ok = false; break; }
                 {
 #pragma unroll
                     for (int i = 0; i < C::kXStageBytes / 16 / kConsumerThreads; ++i) {
@@ -460,107 +499,99 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
                 }
                 if (!mbar_wait(full0 + slot * 8, (n / C::kStages) & 1u, abort_flag)) { ok = false; break; }
                 if (tid == 0 && n == 0) stamp(p, 2);
+                const uint32_t stage = smem_base + slot * kWStageBytes;
+                uint4 v[4];
+#pragma unroll
+                for (int c = 0; c < 4; ++c) v[c] = lds128(stage + w_off[c]);
 
-#pragma unroll
-                for (int gi = 0; gi < 2; ++gi) {
-                    uint32_t a[64];
-#pragma unroll
-                    for (int c = 0; c < 4; ++c) {
-                        const uint4 v = lds128(stage + w_off[gi * 4 + c]);
-                        dequant_word(v.x, a + c * 16 + 0);
-                        dequant_word(v.y, a + c * 16 + 4);
-                        dequant_word(v.z, a + c * 16 + 8);
-                        dequant_word(v.w, a + c * 16 + 12);
-                    }
-                    if (gi == 1) {  // this warp has read all its weights of the stage
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(empty0 + slot * 8);
-                    }
-                    // Previous stage's group gi frees A[gi] and D[gi].  Its accumulator fetch and this group's
-                    // operand stores are issued back to back so that their TMEM latencies overlap.
-                    uint32_t d[NREAD];
-                    if (have_prev) {
-                        if (!mbar_wait(dfull0 + gi * 8, (n - 1) & 1u, abort_flag)) { ok = false; break; }
-                        tc_fence_after_sync();
-                        if constexpr (NREAD == 8) {
-                            tmem_ld8(d_t0 + gi * 32, d);
-                        } else {
-#pragma unroll
-                            for (int c = 0; c < NREAD / 16; ++c) tmem_ld16(d_t0 + gi * 32 + c * 16, d + c * 16);
-                        }
-                    }
-#pragma unroll
-                    for (int c = 0; c < 4; ++c) tmem_st16(a_t0 + gi * 64 + c * 16, a + c * 16);
-                    if (have_prev) {
-                        tmem_wait_ld();
-                        const float scale = gi ? sc_pend1 : sc_pend0;
-#pragma unroll
-                        for (int j = 0; j < NREAD; ++j) acc[j] = fmaf(__uint_as_float(d[j]), scale, acc[j]);
-                    }
-                    tmem_wait_st();
-                    tc_fence_before_sync();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(afull0 + gi * 8);
+                // The previous stage's MMAs of this group must be done before its A buffer is overwritten.
+                if (have_prev) {
+                    if (!mbar_wait(dfull, (n - 1) & 1u, abort_flag)) { ok = false; break; }
+                    tc_fence_after_sync();
                 }
-                sc_pend0 = sc_cur0;
-                sc_pend1 = sc_cur1;
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t a[16];
+                    dequant_word(v[c].x, a + 0);
+                    dequant_word(v[c].y, a + 4);
+                    dequant_word(v[c].z, a + 8);
+                    dequant_word(v[c].w, a + 12);
+                    tmem_st16(a_t + c * 16, a);
+                }
+                // this warp has read its weights of the stage
+                __syncwarp();
+                if (lane == 0) mbar_arrive(empty0 + slot * 8);
+                if (have_prev) fold(sc_pend);  // previous stage's accumulator, before its D buffer is reused
+                tmem_wait_st();
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(afull);
+                sc_pend = sc_cur;
                 have_prev = true;
             }
             if (!ok) break;
             // drain the tile's last stage (n already counts it)
-            readout(0, (n - 1) & 1u, sc_pend0);
-            if (ok) readout(1, (n - 1) & 1u, sc_pend1);
-            if (!ok) break;
+            if (!mbar_wait(dfull, (n - 1) & 1u, abort_flag)) { ok = false; break; }
+            tc_fence_after_sync();
+            fold(sc_pend);
 
             if (tid == 0) stamp(p, 3);
             // ---------------------------------------------------------------- tile epilogue
             // Runs once per tile, so its instructions are cold in the instruction caches: the accumulators
-            // are parked in shared memory with one unrolled burst of stores and everything after that is
-            // written as rolled loops (a fully unrolled epilogue cost ~10 us in instruction fetches alone).
-            float* stage_acc = xchg;  // [NREAD][256] fp32, this thread's values at [j][tid]
-            named_barrier_sync(1, kConsumerThreads);  // previous tile's readers of stage_acc are done
+            // are parked in shared memory and everything after that is written as rolled loops (a fully
+            // unrolled epilogue cost ~10 us in instruction fetches alone).  The two threads of a row first
+            // add their groups' partial sums there; afterwards they split the activation rows by parity.
+            float* stage_acc = xchg;  // [NREAD][256] fp32, row rt's values at [j][rt]
+            if (!consumer_sync()) break;  // previous tile's readers of stage_acc are done
+            if (gi == 0) {
 #pragma unroll
-            for (int j = 0; j < NREAD; ++j) stage_acc[j * kTileRows + tid] = acc[j];
+                for (int j = 0; j < NREAD; ++j) stage_acc[j * kTileRows + rt] = acc[j];
+            }
+            if (!consumer_sync()) break;
+            if (gi == 1) {
+#pragma unroll
+                for (int j = 0; j < NREAD; ++j) stage_acc[j * kTileRows + rt] += acc[j];
+            }
+            if (!consumer_sync()) break;
             const int m_rows = p.m < NREAD ? p.m : NREAD;
             const bool whole = (s0 == 0 && s1 == S);
             bool finish = whole;
-            int j0 = 0, jstep = 1;
+            int j0 = gi, jstep = 2;  // activation rows this thread finishes: j0, j0 + jstep, ...
             if (!whole && p.cluster > 1) {
                 // K splits of one tile form a thread-block cluster.  Activation row j is finished by CTA
                 // j % cluster: every CTA pushes its fp32 partial of that row into the owner's shared memory
                 // (remote stores do not stall), and after a cluster barrier the owner sums the `cluster`
                 // copies in rank order (deterministic) from its own shared memory.
-                float* part = reinterpret_cast<float*>(smem);  // the stage buffers, free once every CTA is done
+                float* part = reinterpret_cast<float*>(smem);  // the weight ring, free once every CTA is done
                 const uint32_t my_rank = cluster_ctarank();
                 const uint32_t csz = static_cast<uint32_t>(p.cluster);
                 const uint32_t rows_cap = (static_cast<uint32_t>(m_rows) + csz - 1) / csz;
                 cluster_sync_all();  // (1) every CTA of the cluster has finished reading its stage buffers
                 ++cluster_syncs;
                 {
-                    const uint32_t base = smem_u32(part) + ((my_rank * rows_cap) * kTileRows + tid) * 4;
-                    uint32_t owner = 0, jl = 0;
+                    const uint32_t base = smem_u32(part) + ((my_rank * rows_cap) * kTileRows + rt) * 4;
 #pragma unroll 4
-                    for (int j = 0; j < m_rows; ++j) {
+                    for (int j = gi; j < m_rows; j += 2) {
+                        const uint32_t owner = static_cast<uint32_t>(j) % csz;
+                        const uint32_t jl = static_cast<uint32_t>(j) / csz;
                         st_shared_cluster_f32(mapa_shared_cluster(base, owner) + jl * (kTileRows * 4),
-                                              stage_acc[j * kTileRows + tid]);
-                        if (++owner == csz) { owner = 0; ++jl; }
+                                              stage_acc[j * kTileRows + rt]);
                     }
                 }
                 cluster_sync_all();  // (2) all partials have landed
                 ++cluster_syncs;
                 {
-                    uint32_t jl = 0;
 #pragma unroll 2
-                    for (int j = static_cast<int>(my_rank); j < m_rows; j += static_cast<int>(csz), ++jl) {
+                    for (uint32_t jl = gi; my_rank + jl * csz < static_cast<uint32_t>(m_rows); jl += 2) {
                         float sum = 0.f;
 #pragma unroll 1
-                        for (uint32_t r = 0; r < csz; ++r) sum += part[((r * rows_cap + jl) * kTileRows) + tid];
-                        stage_acc[j * kTileRows + tid] = sum;
+                        for (uint32_t r = 0; r < csz; ++r) sum += part[((r * rows_cap + jl) * kTileRows) + rt];
+                        stage_acc[(my_rank + jl * csz) * kTileRows + rt] = sum;
                     }
                 }
                 finish = true;
-                j0 = static_cast<int>(my_rank);
-                jstep = static_cast<int>(csz);
+                j0 = static_cast<int>(my_rank + gi * csz);
+                jstep = static_cast<int>(2 * csz);
             } else if (!whole) {
                 // tiles that straddle CTAs (one CTA per SM, units cut evenly): partials go through the scratch
                 // buffer and the last CTA to arrive sums them in CTA order
@@ -568,9 +599,9 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
                 const int wslot = blockIdx.x * 2 + (tile == first_tile ? 0 : 1);
                 float* ws = p.workspace + static_cast<long long>(wslot) * (32 * kTileRows);
 #pragma unroll 1
-                for (int j = 0; j < m_rows; ++j) ws[j * kTileRows + tid] = stage_acc[j * kTileRows + tid];
+                for (int j = gi; j < m_rows; j += 2) ws[j * kTileRows + rt] = stage_acc[j * kTileRows + rt];
                 __threadfence();
-                named_barrier_sync(1, kConsumerThreads);
+                if (!consumer_sync()) break;
                 const long long t_lo = static_cast<long long>(tile) * S;
                 const int c_lo = unit_owner(t_lo, p.total_units, ctas);
                 const int c_hi = unit_owner(t_lo + S - 1, p.total_units, ctas);
@@ -578,28 +609,28 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
                     const int old = atomicAdd(&p.counters[tile], 1);
                     ctrl->is_last = (old == c_hi - c_lo) ? 1 : 0;
                 }
-                named_barrier_sync(1, kConsumerThreads);
+                if (!consumer_sync()) break;
                 finish = ctrl->is_last != 0;
                 if (finish) {
                     __threadfence();
 #pragma unroll 1
-                    for (int j = 0; j < m_rows; ++j) {
+                    for (int j = gi; j < m_rows; j += 2) {
                         float sum = 0.f;
 #pragma unroll 1
                         for (int c = c_lo; c <= c_hi; ++c) {  // fixed CTA order: deterministic sum
                             const int c_first_tile = static_cast<int>(unit_begin(c, p.total_units, ctas) / S);
                             const float* src = p.workspace + static_cast<long long>(c * 2 + (tile == c_first_tile ? 0 : 1)) *
                                                                  (32 * kTileRows);
-                            sum += __ldcg(src + j * kTileRows + tid);
+                            sum += __ldcg(src + j * kTileRows + rt);
                         }
-                        stage_acc[j * kTileRows + tid] = sum;
+                        stage_acc[j * kTileRows + rt] = sum;
                     }
                     if (tid == 0) p.counters[tile] = 0;
                 }
             }
             if (finish) {
                 if (p.swiglu) {
-                    named_barrier_sync(1, kConsumerThreads);  // the up half's values are visible to the gate half
+                    if (!consumer_sync()) break;  // the up half's values are visible to the gate half
                     if (wg == 0 && valid) {
                         OutT* y = static_cast<OutT*>(p.seg[0].y) + my_row;
                         const long long ldy = p.seg[0].ldy;
@@ -616,7 +647,7 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
                     const float b = sg.bias ? sg.bias[my_row] : 0.f;
 #pragma unroll 4
                     for (int j = j0; j < m_rows; j += jstep)
-                        store_out<OutT>(y + static_cast<long long>(j) * ldy, stage_acc[j * kTileRows + tid] + b);
+                        store_out<OutT>(y + static_cast<long long>(j) * ldy, stage_acc[j * kTileRows + rt] + b);
                 }
             }
             if (tid == 0) stamp(p, 4);
@@ -695,6 +726,12 @@ cudaError_t launch(Params& p, int tiles, int num_sms, cudaStream_t stream) {
     if (configured_dev != dev) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<NMMA>::kSmemBytes);
         if (e != cudaSuccess) return e;
+        // The in-kernel register re-split is balanced for exactly kLaunchRegs per thread at launch: with any
+        // other allocation the consumers' request could block forever, so such a build is refused here.
+        cudaFuncAttributes fa;
+        e = cudaFuncGetAttributes(&fa, kern);
+        if (e != cudaSuccess) return e;
+        if (fa.numRegs != kLaunchRegs) return cudaErrorInvalidDeviceFunction;
         for (int cs = 1; cs <= 8; ++cs) {
             cudaLaunchConfig_t cfg = {};
             cfg.gridDim = dim3(cs * 64);
@@ -725,7 +762,6 @@ cudaError_t launch(Params& p, int tiles, int num_sms, cudaStream_t stream) {
         ctas = tiles * cluster;
     }
     p.cluster = cluster;
-    { const char* e = getenv("XINFER_TC_CLUSTER_MODE"); if (e && atoi(e) == 2) p.cluster = 1; if (e && atoi(e) == 0) { p.cluster = 1; cluster = 1; } }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(ctas);
     cfg.blockDim = dim3(kThreads);
