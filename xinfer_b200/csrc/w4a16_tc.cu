@@ -130,6 +130,8 @@ __device__ __forceinline__ int unit_owner(long long unit, long long total, long 
     return static_cast<int>(((unit + 1) * ctas + total - 1) / total - 1);
 }
 
+constexpr int kScalePrefetchStages = 10;
+__device__ __forceinline__ void prefetch_l1(const void* ptr) { asm volatile("prefetch.global.L1 [%0];" ::"l"(ptr)); }
 // Non-blocking L2 prefetch of [ptr, ptr + bytes), one request per 32-byte sector.
 __device__ __forceinline__ void prefetch_l2_range(const void* ptr, int bytes) {
     const uintptr_t lo = reinterpret_cast<uintptr_t>(ptr) & ~uintptr_t(31);
@@ -278,11 +280,19 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
         // already in flight while it drains (programmatic dependent launch).
         const uint32_t pre_w = total_mine < C::kStages ? total_mine : C::kStages;
         const uint32_t pre_x = total_mine < C::kXStages ? total_mine : C::kXStages;
-        for (uint32_t n = 0; n < pre_w; ++n) issue_w(n);
+        // All CTAs start together: were every CTA to request its whole ring at once, the first stages would
+        // come back interleaved with the deeper ones and the consumers would sit idle for the whole burst.
+        // Two stages go out first; the rest of the ring follows once the first stage has landed.
+        const uint32_t pre_a = pre_w < 2u ? pre_w : 2u;
+        for (uint32_t n = 0; n < pre_a; ++n) issue_w(n);
         griddep_wait();
         for (uint32_t n = 0; n < pre_x; ++n) issue_x(n);
-        uint32_t nw = pre_w, nx = pre_x;
         bool ok = true;
+        if (pre_w > pre_a) {
+            ok = mbar_wait_parked(smem_u32(&ctrl->full[0]), 0u, abort_flag);
+            for (uint32_t n = pre_a; ok && n < pre_w; ++n) issue_w(n);
+        }
+        uint32_t nw = pre_w, nx = pre_x;
         while (ok && (nw < total_mine || nx < total_mine)) {
             if (nw < total_mine) {
                 ok = mbar_wait_parked(smem_u32(&ctrl->empty[nw % C::kStages]), ((nw / C::kStages) & 1u) ^ 1u, abort_flag);
@@ -478,6 +488,10 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
                 const float sc_cur = __half2float(__ushort_as_half(static_cast<unsigned short>(q0)));
                 q0 = q1;
                 if (s + 2 < s1) q1 = load_scale(s + 2);
+                // Behind the weight stream's queue of requests a miss of this SM takes several stages to come
+                // back: ask for the scale's sector many stages early, so the load above finds it in L1.
+                if (s + kScalePrefetchStages < s1 && 2 * (s + kScalePrefetchStages) + gi < gmax)
+                    prefetch_l1(raw_scales + 2 * (s + kScalePrefetchStages) + gi);
 
                 // activations: reorder each 8-k block to (0,4,1,5,2,6,3,7), in place
                 if (!mbar_wait(xfull0 + xslot * 8, (n / C::kXStages) & 1u, abort_flag)) { ok = false; break; }
