@@ -79,18 +79,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 // Bounded wait.  Returns false when the CTA is aborting (this wait ran out, or another one did).
+// The poll loop is kept to the try_wait and one counter: every instruction it issues competes with the
+// warps that have work, so the clock and the abort flag are only looked at every 256 polls.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
-    uint32_t spins = 0;
     while (true) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((++spins & 63u) == 0u) {
-            if (*abort_flag) return false;
-            if (clock64() - t0 > kWaitLimitClocks) {
-                *abort_flag = 1;
-                return false;
-            }
+#pragma unroll 1
+        for (int spins = 0; spins < 256; ++spins)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (clock64() - t0 > kWaitLimitClocks) {
+            *abort_flag = 1;
+            return false;
         }
     }
 }

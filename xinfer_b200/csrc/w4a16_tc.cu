@@ -21,8 +21,8 @@
 // tile D[128 x NMMA]; its owner thread reads lane t back (tcgen05.ld) and folds it into fp32
 // register accumulators with its own row's scale.  Nothing about a row ever leaves its thread.
 //
-// The unpack yields k in the order (0,4,1,5,2,6,3,7) inside each 8-k block; the consumer threads
-// permute the staged activations in place to the same order before the MMA reads them.
+// The unpack yields k in the order (0,4,1,5,2,6,3,7) inside each 8-k block; a dedicated warp
+// permutes the staged activations in place to the same order before the MMA reads them.
 //
 // Work is cut stream-K style: the (tile, 256-k stage) units are split evenly over one CTA per SM;
 // a tile finished by several CTAs is summed by the last one to arrive, in CTA order, from fp32
@@ -51,7 +51,7 @@ constexpr int kXBoxesPerStage = kStageK / 64;                // activation boxes
 constexpr int kConsumerThreads = 512;  // warps 0..15
 constexpr int kProducerWarp = 16;
 constexpr int kMmaWarp = 17;  // issues the MMAs of half 0 and owns the TMEM allocation; warp 18 issues half 1
-constexpr int kIdleWarp = 19;
+constexpr int kReorderWarp = 19;  // rewrites the staged activations in the k order of the unpack
 constexpr int kThreads = 640;
 // Register re-split between warpgroups.  The kernel starts with kLaunchRegs per thread (what 640 threads leave
 // of the 64K file); the helper warpgroup releases down to kHelperRegs and the four consumer warpgroups grow
@@ -111,7 +111,7 @@ struct Ctrl {
     uint64_t full[8];     // weights of a stage have landed
     uint64_t empty[8];    // every consumer warp has unpacked them
     uint64_t x_full[8];   // activations of a stage have landed
-    uint64_t x_ready[8];  // every consumer warp has reordered its share of them
+    uint64_t x_ready[8];  // the reorder warp has rewritten them in the unpack's k order
     uint64_t x_empty[8];  // both halves' MMAs that read them have completed
     uint64_t a_full[2][2];
     uint64_t d_full[2][2];
@@ -196,7 +196,7 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
         }
         for (int i = 0; i < C::kXStages; ++i) {
             mbar_init(smem_u32(&ctrl->x_full[i]), 1);
-            mbar_init(smem_u32(&ctrl->x_ready[i]), kConsumerThreads / 32);
+            mbar_init(smem_u32(&ctrl->x_ready[i]), 1);
             mbar_init(smem_u32(&ctrl->x_empty[i]), 2);  // one MMA commit per half
         }
         for (int w = 0; w < 2; ++w)
@@ -370,7 +370,33 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
         }
         if (p.cluster > 1) { __syncwarp(); cluster_sync_all(); cluster_sync_all(); }
     } else {
-        // kIdleWarp fills the helper warpgroup (register reallocation works on whole warpgroups)
+        // ------------------------------------------------------------------ activation reorder warp
+        // The unpack yields k in the order (0,4,1,5,2,6,3,7) inside each 8-k block: this warp rewrites every
+        // staged activation slot to the same order, in place, before the MMAs read it.
+        const uint32_t xring_base = smem_u32(xring);
+        const uint32_t xfull0 = smem_u32(&ctrl->x_full[0]);
+        const uint32_t xready0 = smem_u32(&ctrl->x_ready[0]);
+        const uint32_t total_mine = static_cast<uint32_t>(u_end - u_begin);
+        constexpr int kChunksPerLane = C::kXStageBytes / 16 / 32;
+        for (uint32_t n = 0; n < total_mine; ++n) {
+            const uint32_t xslot = n % C::kXStages;
+            if (!mbar_wait_parked(xfull0 + xslot * 8, (n / C::kXStages) & 1u, abort_flag)) break;
+            const uint32_t base = xring_base + xslot * C::kXStageBytes + lane * 16;
+#pragma unroll 8
+            for (int i = 0; i < kChunksPerLane; ++i) {
+                const uint32_t addr = base + i * 512;
+                const uint4 v = lds128(addr);
+                uint4 o;
+                o.x = prmt(v.x, v.z, 0x5410u);
+                o.y = prmt(v.x, v.z, 0x7632u);
+                o.z = prmt(v.y, v.w, 0x5410u);
+                o.w = prmt(v.y, v.w, 0x7632u);
+                sts128(addr, o);
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(xready0 + xslot * 8);
+        }
         if (p.cluster > 1) { __syncwarp(); cluster_sync_all(); cluster_sync_all(); }
     }
     } else {
@@ -394,11 +420,8 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
 #pragma unroll
         for (int c = 0; c < 4; ++c) w_off[c] = wg * kWHalfBytes + t * kStageRowBytes + (((gi * 4 + c) ^ (t & 7)) << 4);
         const uint32_t smem_base = smem_u32(smem);
-        const uint32_t xring_base = smem_u32(xring);
         const uint32_t full0 = smem_u32(&ctrl->full[0]);
         const uint32_t empty0 = smem_u32(&ctrl->empty[0]);
-        const uint32_t xfull0 = smem_u32(&ctrl->x_full[0]);
-        const uint32_t xready0 = smem_u32(&ctrl->x_ready[0]);
         const uint32_t afull = smem_u32(&ctrl->a_full[wg][gi]);
         const uint32_t dfull = smem_u32(&ctrl->d_full[wg][gi]);
 
@@ -484,7 +507,6 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
 
             for (int s = s0; s < s1 && ok; ++s, ++n) {
                 const uint32_t slot = n % C::kStages;
-                const uint32_t xslot = n % C::kXStages;
                 const float sc_cur = __half2float(__ushort_as_half(static_cast<unsigned short>(q0)));
                 q0 = q1;
                 if (s + 2 < s1) q1 = load_scale(s + 2);
@@ -493,24 +515,6 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
                 if (s + kScalePrefetchStages < s1 && 2 * (s + kScalePrefetchStages) + gi < gmax)
                     prefetch_l1(raw_scales + 2 * (s + kScalePrefetchStages) + gi);
 
-                // activations: reorder each 8-k block to (0,4,1,5,2,6,3,7), in place
-                if (!mbar_wait(xfull0 + xslot * 8, (n / C::kXStages) & 1u, abort_flag)) { ok = false; break; }
-                {
-#pragma unroll
-                    for (int i = 0; i < C::kXStageBytes / 16 / kConsumerThreads; ++i) {
-                        const uint32_t addr = xring_base + xslot * C::kXStageBytes + (tid + i * kConsumerThreads) * 16;
-                        const uint4 v = lds128(addr);
-                        uint4 o;
-                        o.x = prmt(v.x, v.z, 0x5410u);
-                        o.y = prmt(v.x, v.z, 0x7632u);
-                        o.z = prmt(v.y, v.w, 0x5410u);
-                        o.w = prmt(v.y, v.w, 0x7632u);
-                        sts128(addr, o);
-                    }
-                    fence_proxy_async_smem();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(xready0 + xslot * 8);
-                }
                 if (!mbar_wait(full0 + slot * 8, (n / C::kStages) & 1u, abort_flag)) { ok = false; break; }
                 if (tid == 0 && n == 0) stamp(p, 2);
                 const uint32_t stage = smem_base + slot * kWStageBytes;
