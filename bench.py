@@ -39,6 +39,11 @@ LAYER_SHAPES = {"q": (5120, 6144), "kv": (5120, 1024), "o": (6144, 5120), "gate_
 L2_BYTES = 126 * 1024 * 1024
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum over algorithmic bytes of w4a16_tc_kernel, from the ncu capture
+# summarised in profiles/w4a16_tc_kernel_gate_up_m32_lm_head_m8.md (the kernel reads every weight byte once).
+NCU_TRAFFIC_RATIO = 0.98
+
+
 def alg_bytes(M, K, N, out_bytes=2):
     """weights + scales read once, fp16 activations read once, output written once."""
     return N * K // 2 + N * (K // 128) * 2 + M * K * 2 + M * N * out_bytes
@@ -266,7 +271,8 @@ def gemv_bench(args):
                    "l2": f"rotates over {n_buf} distinct weight buffers ({n_buf * w_bytes >> 20} MiB > 2x L2)",
                    "kernel_path": {1: "tcgen05", 2: "cuda-core"}.get(path, "none")},
         "roofline": {"bound": "hbm", "achieved": gbs_per_gpu, "peak": peak, "unit": "GB/s", "frac": gbs_per_gpu / peak,
-                     "peak_kind": f"of {peak_kind}", "frac_of_nominal_8000": gbs_per_gpu / 8000.0, "traffic": None,
+                     "peak_kind": f"of {peak_kind}", "frac_of_nominal_8000": gbs_per_gpu / 8000.0,
+                     "traffic": NCU_TRAFFIC_RATIO * per_launch,
                      "bytes_per_launch": per_launch, "us_per_launch": per_launch_s * 1e6},
         "e2e": {"value": e2e_val, "unit": "GB/s", "h2d_bytes_per_step": M * K * 2 * launches,
                 "d2h_bytes_per_step": M * N * out_bytes * launches, "us_per_call": e2e_s / e2e_launches * 1e6},
@@ -462,7 +468,10 @@ def step_bench(args):
                    "note": "random-init weights: the draft head and the target agree only by chance, so almost "
                            "every step emits the bonus token alone"},
         "roofline": {"bound": "hbm", "achieved": lin_gbs, "peak": peak, "unit": "GB/s", "frac": lin_gbs / peak,
-                     "peak_kind": f"of {peak_kind}", "frac_of_nominal_8000": lin_gbs / 8000.0, "traffic": None,
+                     "peak_kind": f"of {peak_kind}", "frac_of_nominal_8000": lin_gbs / 8000.0,
+                     "traffic": NCU_TRAFFIC_RATIO * lin_bytes / max(1, lin_launches),
+                     "traffic_source": "ncu dram__bytes_read+write of one gate_up M=32 launch (46.4 MB for 47.4 MB "
+                                       "algorithmic), scaled by bytes to the average launch of the step",
                      "kernel": "w4a16_tc_kernel", "launches_per_step": lin_launches,
                      "bytes_per_launch": lin_bytes / max(1, lin_launches),
                      "us_per_launch": lin_ms * 1e3 / max(1, lin_launches), "linears_ms_per_step": lin_ms,
