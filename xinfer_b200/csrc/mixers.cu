@@ -200,17 +200,21 @@ __global__ void __launch_bounds__(256) attn_prep_kernel(__half* q_out, __half* k
 }
 
 // ------------------------------------------------------------------------------- split-KV GQA attention
-// Grid (splits, Hkv, B), 128 threads.  The G * R query rows that share one KV head (G = Hq / Hkv, at most
-// 32 rows) form the M side of mma.sync m16n8k16 tiles; keys stream through shared memory in chunks of
-// 32 via cp.async, double buffered.  Each CTA writes an unnormalised partial (max, sum, O) per row.
+// Grid (splits, Hkv, B), 256 threads, two CTAs per SM.  The G * R query rows that share one KV head
+// (G = Hq / Hkv, at most 32 rows) form the M side of mma.sync m16n8k16 tiles; keys stream through shared
+// memory in chunks of 32 via cp.async, double buffered.  Warp (mt, wq) owns the 16-row tile mt and, per
+// chunk, the keys [8 wq, 8 wq + 8) of S = Q K^T and the output dims [64 wq, 64 wq + 64) of O += P V.
+// Each CTA writes an unnormalised partial (max, sum, O) per row.
 constexpr int kAttnChunk = 32;
+constexpr int kAttnStages = 2;
+constexpr int kAttnThreads = 256;
 constexpr int kAttnLd = 264;  // padded row of 256 halves (528 B): conflict-free ldmatrix
 constexpr int kAttnRows = 32;
 
 struct AttnSmem {
     __half q[kAttnRows][kAttnLd];
-    __half k[2][kAttnChunk][kAttnLd];
-    __half v[2][kAttnChunk][kAttnLd];
+    __half k[kAttnStages][kAttnChunk][kAttnLd];
+    __half v[kAttnStages][kAttnChunk][kAttnLd];
     float s[kAttnRows][kAttnChunk + 1];
     __half p[kAttnRows][kAttnChunk + 8];
     float row_max[kAttnRows];
@@ -247,7 +251,7 @@ __device__ __forceinline__ void mma16816(float* c, const uint32_t* a, const uint
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
 }
 
-__global__ void __launch_bounds__(128) attn_split_kernel(float* part_o, float* part_ml, const __half* q,
+__global__ void __launch_bounds__(kAttnThreads, 2) attn_split_kernel(float* part_o, float* part_ml, const __half* q,
                                                          const __half* k_cache, const __half* v_cache, const int* ctx,
                                                          int rows_per_seq, int hq, int hkv, long long max_seq,
                                                          float scale) {
@@ -256,6 +260,7 @@ __global__ void __launch_bounds__(128) attn_split_kernel(float* part_o, float* p
     AttnSmem& sm = *reinterpret_cast<AttnSmem*>(attn_smem_raw);
     const int split = blockIdx.x, nsplit = gridDim.x, kvh = blockIdx.y, b = blockIdx.z;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int mt = warp >> 2, wq = warp & 3;
     const int G = hq / hkv;
     const int nrows = G * rows_per_seq;  // valid query rows, row = g * R + i
     const int ctx_b = ctx[b];
@@ -266,7 +271,7 @@ __global__ void __launch_bounds__(128) attn_split_kernel(float* part_o, float* p
     const int c_end = static_cast<int>(static_cast<long long>(split + 1) * nchunks / nsplit);
 
     // stage the query rows (zero padded to 32)
-    for (int idx = tid; idx < kAttnRows * 32; idx += 128) {
+    for (int idx = tid; idx < kAttnRows * 32; idx += kAttnThreads) {
         const int r = idx >> 5, seg = idx & 31;
         uint4 v = make_uint4(0, 0, 0, 0);
         if (r < nrows) {
@@ -281,9 +286,12 @@ __global__ void __launch_bounds__(128) attn_split_kernel(float* part_o, float* p
         sm.row_sum[tid] = 0.f;
     }
 
+    // one cp.async group per chunk slot, also when the slot lies past the split's end (an empty group), so that
+    // "all but the newest kAttnStages - 1 groups have landed" always means "chunk c has landed"
     auto load_chunk = [&](int c, int buf) {
         const long long key0 = static_cast<long long>(c) * kAttnChunk;
-        for (int idx = tid; idx < kAttnChunk * 32; idx += 128) {
+        if (c < c_end)
+        for (int idx = tid; idx < kAttnChunk * 32; idx += kAttnThreads) {
             const int r = idx >> 5, seg = idx & 31;
             long long key = key0 + r;
             if (key >= total_keys) key = total_keys - 1;  // clamped rows are masked out below
@@ -294,77 +302,67 @@ __global__ void __launch_bounds__(128) attn_split_kernel(float* part_o, float* p
         cp_async_commit();
     };
 
-    float o_acc[2][8][4];
+    float o_acc[8][4];
 #pragma unroll
-    for (int mt = 0; mt < 2; ++mt)
+    for (int nt = 0; nt < 8; ++nt)
 #pragma unroll
-        for (int nt = 0; nt < 8; ++nt)
-#pragma unroll
-            for (int e = 0; e < 4; ++e) o_acc[mt][nt][e] = 0.f;
+        for (int e = 0; e < 4; ++e) o_acc[nt][e] = 0.f;
 
-    if (c_begin < c_end) load_chunk(c_begin, 0);
+    for (int i = 0; i < kAttnStages - 1; ++i) load_chunk(c_begin + i, i);
     for (int c = c_begin; c < c_end; ++c) {
-        const int buf = (c - c_begin) & 1;
-        if (c + 1 < c_end) {
-            load_chunk(c + 1, buf ^ 1);
-            cp_async_wait<1>();
-        } else {
-            cp_async_wait<0>();
-        }
+        const int buf = (c - c_begin) % kAttnStages;
+        // the slot refilled here was read in the previous iteration, which ended with a barrier
+        load_chunk(c + kAttnStages - 1, (c - c_begin + kAttnStages - 1) % kAttnStages);
+        cp_async_wait<kAttnStages - 1>();
         __syncthreads();
 
-        // S = Q K^T: warp w owns keys [8w, 8w+8) of the chunk, both 16-row tiles
+        // S = Q K^T for this warp's 16 rows and 8 keys
         {
-            float s_acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+            float s_acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int ks = 0; ks < 16; ++ks) {
-                uint32_t bfr[2];
-                ldmatrix_x2(bfr, &sm.k[buf][warp * 8 + (lane & 7)][ks * 16 + ((lane >> 3) & 1) * 8]);
-#pragma unroll
-                for (int mt = 0; mt < 2; ++mt) {
-                    uint32_t afr[4];
-                    ldmatrix_x4(afr, &sm.q[mt * 16 + (lane & 15)][ks * 16 + (lane >> 4) * 8]);
-                    mma16816(s_acc[mt], afr, bfr);
-                }
+                uint32_t bfr[2], afr[4];
+                ldmatrix_x2(bfr, &sm.k[buf][wq * 8 + (lane & 7)][ks * 16 + ((lane >> 3) & 1) * 8]);
+                ldmatrix_x4(afr, &sm.q[mt * 16 + (lane & 15)][ks * 16 + (lane >> 4) * 8]);
+                mma16816(s_acc, afr, bfr);
             }
             const int g4 = lane >> 2, t4 = lane & 3;
-#pragma unroll
-            for (int mt = 0; mt < 2; ++mt) {
-                sm.s[mt * 16 + g4][warp * 8 + t4 * 2] = s_acc[mt][0];
-                sm.s[mt * 16 + g4][warp * 8 + t4 * 2 + 1] = s_acc[mt][1];
-                sm.s[mt * 16 + g4 + 8][warp * 8 + t4 * 2] = s_acc[mt][2];
-                sm.s[mt * 16 + g4 + 8][warp * 8 + t4 * 2 + 1] = s_acc[mt][3];
-            }
+            sm.s[mt * 16 + g4][wq * 8 + t4 * 2] = s_acc[0];
+            sm.s[mt * 16 + g4][wq * 8 + t4 * 2 + 1] = s_acc[1];
+            sm.s[mt * 16 + g4 + 8][wq * 8 + t4 * 2] = s_acc[2];
+            sm.s[mt * 16 + g4 + 8][wq * 8 + t4 * 2 + 1] = s_acc[3];
         }
         __syncthreads();
 
-        // online softmax: 4 threads per row, 8 keys each
+        // online softmax: 8 threads per row, 4 keys each
         {
-            const int r = tid >> 2, part = tid & 3;
+            const int r = tid >> 3, part = tid & 7;
             const int i = r % rows_per_seq;
             const long long limit = static_cast<long long>(ctx_b) + i + 1;  // keys visible to this row
-            const long long key0 = static_cast<long long>(c) * kAttnChunk + part * 8;
-            float sc[8];
+            const long long key0 = static_cast<long long>(c) * kAttnChunk + part * 4;
+            float sc[4];
             float mx = -INFINITY;
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
+            for (int j = 0; j < 4; ++j) {
                 const bool vis = (r < nrows) && (key0 + j < limit) && (key0 + j < total_keys);
-                sc[j] = vis ? sm.s[r][part * 8 + j] * scale : -INFINITY;
+                sc[j] = vis ? sm.s[r][part * 4 + j] * scale : -INFINITY;
                 mx = fmaxf(mx, sc[j]);
             }
             mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
             mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
             const float old_max = sm.row_max[r];
             const float new_max = fmaxf(old_max, mx);
             float sum = 0.f;
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
+            for (int j = 0; j < 4; ++j) {
                 const float pv = (sc[j] == -INFINITY) ? 0.f : expf(sc[j] - new_max);
                 sum += pv;
-                sm.p[r][part * 8 + j] = __float2half_rn(pv);
+                sm.p[r][part * 4 + j] = __float2half_rn(pv);
             }
             sum += __shfl_xor_sync(0xffffffffu, sum, 1);
             sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+            sum += __shfl_xor_sync(0xffffffffu, sum, 4);
             __syncwarp();
             if (part == 0) {
                 const float alpha = (old_max == -INFINITY) ? 0.f : expf(old_max - new_max);
@@ -375,32 +373,26 @@ __global__ void __launch_bounds__(128) attn_split_kernel(float* part_o, float* p
         }
         __syncthreads();
 
-        // O = alpha * O + P V: warp w owns output dims [64w, 64w+64)
+        // O = alpha * O + P V for this warp's 16 rows and 64 output dims
         {
             const int g4 = lane >> 2;
+            const float a0 = sm.row_alpha[mt * 16 + g4], a1 = sm.row_alpha[mt * 16 + g4 + 8];
 #pragma unroll
-            for (int mt = 0; mt < 2; ++mt) {
-                const float a0 = sm.row_alpha[mt * 16 + g4], a1 = sm.row_alpha[mt * 16 + g4 + 8];
-#pragma unroll
-                for (int nt = 0; nt < 8; ++nt) {
-                    o_acc[mt][nt][0] *= a0;
-                    o_acc[mt][nt][1] *= a0;
-                    o_acc[mt][nt][2] *= a1;
-                    o_acc[mt][nt][3] *= a1;
-                }
+            for (int nt = 0; nt < 8; ++nt) {
+                o_acc[nt][0] *= a0;
+                o_acc[nt][1] *= a0;
+                o_acc[nt][2] *= a1;
+                o_acc[nt][3] *= a1;
             }
 #pragma unroll
             for (int ks = 0; ks < kAttnChunk / 16; ++ks) {
-                uint32_t afr[2][4];
-#pragma unroll
-                for (int mt = 0; mt < 2; ++mt)
-                    ldmatrix_x4(afr[mt], &sm.p[mt * 16 + (lane & 15)][ks * 16 + (lane >> 4) * 8]);
+                uint32_t afr[4];
+                ldmatrix_x4(afr, &sm.p[mt * 16 + (lane & 15)][ks * 16 + (lane >> 4) * 8]);
 #pragma unroll
                 for (int nt = 0; nt < 8; ++nt) {
                     uint32_t bfr[2];
-                    ldmatrix_x2_trans(bfr, &sm.v[buf][ks * 16 + (lane & 15)][warp * 64 + nt * 8]);
-#pragma unroll
-                    for (int mt = 0; mt < 2; ++mt) mma16816(o_acc[mt][nt], afr[mt], bfr);
+                    ldmatrix_x2_trans(bfr, &sm.v[buf][ks * 16 + (lane & 15)][wq * 64 + nt * 8]);
+                    mma16816(o_acc[nt], afr, bfr);
                 }
             }
         }
@@ -412,15 +404,12 @@ __global__ void __launch_bounds__(128) attn_split_kernel(float* part_o, float* p
     float* po = part_o + pbase * (kAttnRows * 256);
     const int g4 = lane >> 2, t4 = lane & 3;
 #pragma unroll
-    for (int mt = 0; mt < 2; ++mt)
-#pragma unroll
-        for (int nt = 0; nt < 8; ++nt) {
-            const int col = warp * 64 + nt * 8 + t4 * 2;
-            const int r0 = mt * 16 + g4;
-            if (r0 < nrows) *reinterpret_cast<float2*>(po + r0 * 256 + col) = make_float2(o_acc[mt][nt][0], o_acc[mt][nt][1]);
-            if (r0 + 8 < nrows)
-                *reinterpret_cast<float2*>(po + (r0 + 8) * 256 + col) = make_float2(o_acc[mt][nt][2], o_acc[mt][nt][3]);
-        }
+    for (int nt = 0; nt < 8; ++nt) {
+        const int col = wq * 64 + nt * 8 + t4 * 2;
+        const int r0 = mt * 16 + g4;
+        if (r0 < nrows) *reinterpret_cast<float2*>(po + r0 * 256 + col) = make_float2(o_acc[nt][0], o_acc[nt][1]);
+        if (r0 + 8 < nrows) *reinterpret_cast<float2*>(po + (r0 + 8) * 256 + col) = make_float2(o_acc[nt][2], o_acc[nt][3]);
+    }
     if (tid < nrows) {
         part_ml[pbase * (kAttnRows * 2) + tid * 2] = sm.row_max[tid];
         part_ml[pbase * (kAttnRows * 2) + tid * 2 + 1] = sm.row_sum[tid];
@@ -722,7 +711,7 @@ int attn_decode(cudaStream_t s, __half* out, const __half* q, const __half* q_ga
     float* part_o = scratch;
     float* part_ml = scratch + static_cast<size_t>(batch) * hkv * nsplit * (kAttnRows * 256);
     dim3 grid(nsplit, hkv, batch);
-    launch_pdl(attn_split_kernel, dim3(grid), dim3(128), sizeof(AttnSmem), s, part_o, part_ml, q, k_cache, v_cache, ctx, rows_per_seq, hq,
+    launch_pdl(attn_split_kernel, dim3(grid), dim3(kAttnThreads), sizeof(AttnSmem), s, part_o, part_ml, q, k_cache, v_cache, ctx, rows_per_seq, hq,
                                                           hkv, max_seq, 1.0f / sqrtf(256.0f));
     dim3 grid2((hq / hkv) * rows_per_seq, hkv, batch);
     launch_pdl(attn_combine_kernel, dim3(grid2), dim3(256), 0, s, out, part_o, part_ml, q_gate, nsplit, rows_per_seq, hq, hkv);

@@ -441,6 +441,14 @@ int xinfer_spec_decoder_create(const xinfer_model_config* cfg, int batch, int k,
         d->delta_out = dalloc<__half>(d, static_cast<size_t>(M) * hv * 128, true);
         d->cat = dalloc<__half>(d, static_cast<size_t>(batch) * 2 * H, true);
         d->logits = dalloc<float>(d, static_cast<size_t>(M) * V, true);
+        {
+            // KV splits: with one attention CTA per SM, two waves of CTAs over (split, kv head, sequence)
+            int sms = 148;
+            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, d->device);
+            const int units = batch * static_cast<int>(c.num_key_value_heads);
+            int splits = (2 * sms) / (units > 0 ? units : 1);
+            d->attn_splits = splits < 1 ? 1 : (splits > 16 ? 16 : splits);
+        }
         d->attn_scratch = dalloc<float>(
             d, xb::attn_scratch_bytes(batch, static_cast<int>(c.num_key_value_heads), d->attn_splits) / sizeof(float), true);
         if (cudaMallocHost(&d->h_emitted, static_cast<size_t>(M) * sizeof(long long)) != cudaSuccess ||
