@@ -171,6 +171,16 @@ __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
     asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
+// The two halves of the cluster barrier, for code that has useful work between arriving and waiting.
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+// Asynchronous 4-byte store into another CTA's shared memory that, on landing, counts 4 bytes on an mbarrier
+// of that CTA (both addresses in the shared::cluster window): the receiver waits on its own barrier only.
+__device__ __forceinline__ void st_async_cluster_f32(uint32_t addr, float v, uint32_t remote_bar) {
+    asm volatile("st.async.shared::cluster.mbarrier::complete_tx::bytes.u32 [%0], %1, [%2];" ::"r"(addr),
+                 "r"(__float_as_uint(v)), "r"(remote_bar)
+                 : "memory");
+}
 // Address of this CTA's shared-memory location `addr` as seen in CTA `rank` of the cluster.
 __device__ __forceinline__ uint32_t mapa_shared_cluster(uint32_t addr, uint32_t rank) {
     uint32_t r;

@@ -116,6 +116,7 @@ struct Ctrl {
     uint64_t a_full[2][2];
     uint64_t d_full[2][2];
     uint64_t epi;         // epilogue barrier of the consumer warps
+    uint64_t red;         // counts the bytes of split-K partials that other CTAs of the cluster store here
     uint32_t tmem_base;
     int abort_flag;
     int is_last;
@@ -168,7 +169,7 @@ __device__ __forceinline__ void stamp(const Params& p, int slot) {
     if (p.trace) {
         long long t;
         asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-        p.trace[blockIdx.x * 8 + slot] = t;
+        p.trace[blockIdx.x * 16 + slot] = t;
     }
 }
 
@@ -205,6 +206,15 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
                 mbar_init(smem_u32(&ctrl->d_full[w][b]), 1);
             }
         mbar_init(smem_u32(&ctrl->epi), kConsumerThreads / 32);
+        mbar_init(smem_u32(&ctrl->red), 1);
+        if (p.cluster > 1) {
+            // bytes this CTA will receive: every other CTA of the cluster sends 256 floats for each activation
+            // row this CTA finishes (rows rank, rank + cluster, ...)
+            const int m_rows = p.m < NREAD ? p.m : NREAD;
+            const int rank = static_cast<int>(cluster_ctarank());
+            const int owned = rank < m_rows ? (m_rows - rank + p.cluster - 1) / p.cluster : 0;
+            mbar_arrive_expect_tx(smem_u32(&ctrl->red), static_cast<uint32_t>((p.cluster - 1) * owned * kTileRows * 4));
+        }
         ctrl->abort_flag = 0;
         ctrl->is_last = 0;
         mbar_fence_init();
@@ -320,7 +330,7 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
             }
         }
         __syncwarp();
-        if (p.cluster > 1) { __syncwarp(); cluster_sync_all(); cluster_sync_all(); }
+        if (p.cluster > 1) { __syncwarp(); cluster_arrive(); cluster_wait(); }
     } else if (warp == kMmaWarp || warp == kMmaWarp + 1) {
         // ------------------------------------------------------------------ MMA issuers, one warp per half
         // The warp waits and computes descriptors as a whole (warp-uniform values); one elected lane issues.
@@ -368,7 +378,7 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
                 }
             }
         }
-        if (p.cluster > 1) { __syncwarp(); cluster_sync_all(); cluster_sync_all(); }
+        if (p.cluster > 1) { __syncwarp(); cluster_arrive(); cluster_wait(); }
     } else {
         // ------------------------------------------------------------------ activation reorder warp
         // The unpack yields k in the order (0,4,1,5,2,6,3,7) inside each 8-k block: this warp rewrites every
@@ -397,7 +407,7 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
             __syncwarp();
             if (lane == 0) mbar_arrive(xready0 + xslot * 8);
         }
-        if (p.cluster > 1) { __syncwarp(); cluster_sync_all(); cluster_sync_all(); }
+        if (p.cluster > 1) { __syncwarp(); cluster_arrive(); cluster_wait(); }
     }
     } else {
         setmaxnreg_inc<kConsumerRegs>();
@@ -428,7 +438,7 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
         float acc[NREAD];
         uint32_t n = 0;  // stages processed by this CTA so far
         bool ok = true;
-        int cluster_syncs = 0;
+        bool cl_arrived = false, cl_waited = false;  // this thread's half-steps of the one cluster barrier
 
         // Barrier among the sixteen consumer warps with a bounded wait (a plain bar.sync would hang the CTA
         // if one warp had given up on a wait and left): false when the CTA is aborting.
@@ -539,6 +549,13 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
                 // this warp has read its weights of the stage
                 __syncwarp();
                 if (lane == 0) mbar_arrive(empty0 + slot * 8);
+                if (p.cluster > 1 && s + 1 == s1) {
+                    // Last stage of this CTA's K range: its weight ring may now be overwritten by the other CTAs
+                    // of the cluster.  Arriving here, not at the exchange, lets the read-out below overlap with
+                    // waiting for them.
+                    cluster_arrive();
+                    cl_arrived = true;
+                }
                 if (have_prev) fold(sc_pend);  // previous stage's accumulator, before its D buffer is reused
                 tmem_wait_st();
                 tc_fence_before_sync();
@@ -565,49 +582,71 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
 #pragma unroll
                 for (int j = 0; j < NREAD; ++j) stage_acc[j * kTileRows + rt] = acc[j];
             }
+            if (tid == 0) stamp(p, 8);
             if (!consumer_sync()) break;
+            if (tid == 0) stamp(p, 9);
             if (gi == 1) {
 #pragma unroll
                 for (int j = 0; j < NREAD; ++j) stage_acc[j * kTileRows + rt] += acc[j];
             }
             if (!consumer_sync()) break;
+            if (tid == 0) stamp(p, 6);
             const int m_rows = p.m < NREAD ? p.m : NREAD;
             const bool whole = (s0 == 0 && s1 == S);
             bool finish = whole;
             int j0 = gi, jstep = 2;  // activation rows this thread finishes: j0, j0 + jstep, ...
             if (!whole && p.cluster > 1) {
                 // K splits of one tile form a thread-block cluster.  Activation row j is finished by CTA
-                // j % cluster: every CTA pushes its fp32 partial of that row into the owner's shared memory
-                // (remote stores do not stall), and after a cluster barrier the owner sums the `cluster`
-                // copies in rank order (deterministic) from its own shared memory.
-                float* part = reinterpret_cast<float*>(smem);  // the weight ring, free once every CTA is done
+                // j % cluster: every other CTA stores its fp32 partial of that row into the owner's shared memory
+                // with asynchronous stores that count bytes on the owner's mbarrier, so the owner waits for
+                // exactly its incoming data and nobody waits for a second cluster-wide rendezvous.  The owner
+                // sums the `cluster` copies in rank order (deterministic).
+                float* part = reinterpret_cast<float*>(smem);  // the weight ring, free once every CTA has arrived
                 const uint32_t my_rank = cluster_ctarank();
                 const uint32_t csz = static_cast<uint32_t>(p.cluster);
                 const uint32_t rows_cap = (static_cast<uint32_t>(m_rows) + csz - 1) / csz;
-                cluster_sync_all();  // (1) every CTA of the cluster has finished reading its stage buffers
-                ++cluster_syncs;
+                if (!cl_arrived) { cluster_arrive(); cl_arrived = true; }
+                cluster_wait();  // every CTA of the cluster has finished reading its weight ring
+                cl_waited = true;
+                if (tid == 0) stamp(p, 10);
                 {
-                    const uint32_t base = smem_u32(part) + ((my_rank * rows_cap) * kTileRows + rt) * 4;
-#pragma unroll 4
-                    for (int j = gi; j < m_rows; j += 2) {
-                        const uint32_t owner = static_cast<uint32_t>(j) % csz;
-                        const uint32_t jl = static_cast<uint32_t>(j) / csz;
-                        st_shared_cluster_f32(mapa_shared_cluster(base, owner) + jl * (kTileRows * 4),
-                                              stage_acc[j * kTileRows + rt]);
-                    }
-                }
-                cluster_sync_all();  // (2) all partials have landed
-                ++cluster_syncs;
-                {
+                    // rows gi, gi + 2, ...: owner j % cluster and its local row index j / cluster, stepped without
+                    // divisions (this code runs once per launch: its size, not its arithmetic, is what costs)
+                    uint32_t dst = smem_u32(part) + ((my_rank * rows_cap) * kTileRows + rt) * 4;
+                    const uint32_t red_bar = smem_u32(&ctrl->red);
+                    uint32_t owner = static_cast<uint32_t>(gi);
 #pragma unroll 2
-                    for (uint32_t jl = gi; my_rank + jl * csz < static_cast<uint32_t>(m_rows); jl += 2) {
-                        float sum = 0.f;
-#pragma unroll 1
-                        for (uint32_t r = 0; r < csz; ++r) sum += part[((r * rows_cap + jl) * kTileRows) + rt];
-                        stage_acc[(my_rank + jl * csz) * kTileRows + rt] = sum;
+                    for (int j = gi; j < m_rows; j += 2) {
+                        if (owner != my_rank)
+                            st_async_cluster_f32(mapa_shared_cluster(dst, owner), stage_acc[j * kTileRows + rt],
+                                                 mapa_shared_cluster(red_bar, owner));
+                        owner += 2;
+                        if (owner >= csz) { owner -= csz; dst += kTileRows * 4; }
                     }
                 }
-                finish = true;
+                if (tid == 0) stamp(p, 11);
+                if (!mbar_wait(smem_u32(&ctrl->red), 0u, abort_flag)) { ok = false; break; }
+                if (tid == 0) stamp(p, 7);
+                {
+                    // this CTA's rows rank, rank + cluster, ...; the two threads of a tile row take every other one
+                    const bool direct = !p.swiglu && valid;
+                    OutT* y = static_cast<OutT*>(sg.y) + my_row;
+                    const long long ldy = sg.ldy;
+                    const float bias = (direct && sg.bias) ? sg.bias[my_row] : 0.f;
+                    const float* pp0 = part + gi * kTileRows + rt;
+#pragma unroll 1
+                    for (uint32_t j = my_rank + gi * csz; j < static_cast<uint32_t>(m_rows); j += 2 * csz, pp0 += 2 * kTileRows) {
+                        float sum = 0.f;
+                        const float* pp = pp0;
+#pragma unroll 2
+                        for (uint32_t r = 0; r < csz; ++r, pp += rows_cap * kTileRows)
+                            sum += (r == my_rank) ? stage_acc[j * kTileRows + rt] : *pp;
+                        if (direct) store_out<OutT>(y + static_cast<long long>(j) * ldy, sum + bias);
+                        else stage_acc[j * kTileRows + rt] = sum;
+                    }
+                    finish = p.swiglu != 0;  // plain projections are already written
+                }
+                if (tid == 0) stamp(p, 12);
                 j0 = static_cast<int>(my_rank + gi * csz);
                 jstep = static_cast<int>(2 * csz);
             } else if (!whole) {
@@ -671,9 +710,12 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
             if (tid == 0) stamp(p, 4);
             u += (s1 - s0);
         }
-        // every thread of a cluster passes exactly two cluster barriers, also when a wait gave up
-        if (p.cluster > 1)
-            for (; cluster_syncs < 2; ++cluster_syncs) cluster_sync_all();
+        // every thread of a cluster arrives at and waits for the cluster barrier exactly once, also when a wait gave up
+        if (p.cluster > 1) {
+            __syncwarp();
+            if (!cl_arrived) cluster_arrive();
+            if (!cl_waited) cluster_wait();
+        }
     }
 
     // ---------------------------------------------------------------------- teardown
