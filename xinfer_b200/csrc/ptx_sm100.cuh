@@ -131,6 +131,11 @@ __device__ __forceinline__ uint4 lds128(uint32_t addr) {
     asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
     return v;
 }
+__device__ __forceinline__ float lds_f32(uint32_t addr) {
+    float v;
+    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr));
+    return v;
+}
 __device__ __forceinline__ void sts128(uint32_t addr, const uint4& v) {
     asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
                  : "memory");
@@ -179,6 +184,15 @@ __device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.w
 __device__ __forceinline__ void st_async_cluster_f32(uint32_t addr, float v, uint32_t remote_bar) {
     asm volatile("st.async.shared::cluster.mbarrier::complete_tx::bytes.u32 [%0], %1, [%2];" ::"r"(addr),
                  "r"(__float_as_uint(v)), "r"(remote_bar)
+                 : "memory");
+}
+// Bulk copy of `bytes` (multiple of 16, 16-byte aligned) from this CTA's shared memory into another CTA's, done
+// by the copy engine; on landing it counts the bytes on an mbarrier of the receiving CTA.  `dst` and
+// `remote_bar` are shared::cluster addresses (mapa), `src` a shared::cta address.  The source must stay
+// allocated until the receiver has seen the bytes.
+__device__ __forceinline__ void bulk_copy_to_cluster(uint32_t dst, uint32_t src, uint32_t bytes, uint32_t remote_bar) {
+    asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+                 "r"(src), "r"(bytes), "r"(remote_bar)
                  : "memory");
 }
 // Address of this CTA's shared-memory location `addr` as seen in CTA `rank` of the cluster.

@@ -177,7 +177,9 @@ template <int NMMA, int NREAD, typename OutT>
 __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_constant__ Params p) {
     using C = Cfg<NMMA>;
     extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    // 1 KiB alignment as an offset into the shared array (not a cast through an integer), so that every pointer
+    // derived from it is still known to point to shared memory and compiles to 32-bit shared loads and stores
+    uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     uint8_t* xring = smem + C::kWRingBytes;
     uint8_t* xchg_raw = xring + C::kXRingBytes;
     Ctrl* ctrl = reinterpret_cast<Ctrl*>(xchg_raw + C::kXchgBytes);
@@ -208,12 +210,14 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
         mbar_init(smem_u32(&ctrl->epi), kConsumerThreads / 32);
         mbar_init(smem_u32(&ctrl->red), 1);
         if (p.cluster > 1) {
-            // bytes this CTA will receive: every other CTA of the cluster sends 256 floats for each activation
-            // row this CTA finishes (rows rank, rank + cluster, ...)
+            // bytes this CTA will receive: every CTA of the cluster (itself included) sends 256 floats for each
+            // activation row this CTA finishes (a contiguous block of ceil(m / cluster) rows per rank)
             const int m_rows = p.m < NREAD ? p.m : NREAD;
             const int rank = static_cast<int>(cluster_ctarank());
-            const int owned = rank < m_rows ? (m_rows - rank + p.cluster - 1) / p.cluster : 0;
-            mbar_arrive_expect_tx(smem_u32(&ctrl->red), static_cast<uint32_t>((p.cluster - 1) * owned * kTileRows * 4));
+            const int rows_cap = (m_rows + p.cluster - 1) / p.cluster;
+            int owned = m_rows - rank * rows_cap;
+            owned = owned < 0 ? 0 : (owned > rows_cap ? rows_cap : owned);
+            mbar_arrive_expect_tx(smem_u32(&ctrl->red), static_cast<uint32_t>(p.cluster * owned * kTileRows * 4));
         }
         ctrl->abort_flag = 0;
         ctrl->is_last = 0;
@@ -330,7 +334,7 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
             }
         }
         __syncwarp();
-        if (p.cluster > 1) { __syncwarp(); cluster_arrive(); cluster_wait(); }
+        if (p.cluster > 1) { __syncwarp(); cluster_arrive(); cluster_wait(); cluster_arrive(); cluster_wait(); }
     } else if (warp == kMmaWarp || warp == kMmaWarp + 1) {
         // ------------------------------------------------------------------ MMA issuers, one warp per half
         // The warp waits and computes descriptors as a whole (warp-uniform values); one elected lane issues.
@@ -378,7 +382,7 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
                 }
             }
         }
-        if (p.cluster > 1) { __syncwarp(); cluster_arrive(); cluster_wait(); }
+        if (p.cluster > 1) { __syncwarp(); cluster_arrive(); cluster_wait(); cluster_arrive(); cluster_wait(); }
     } else {
         // ------------------------------------------------------------------ activation reorder warp
         // The unpack yields k in the order (0,4,1,5,2,6,3,7) inside each 8-k block: this warp rewrites every
@@ -407,7 +411,7 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
             __syncwarp();
             if (lane == 0) mbar_arrive(xready0 + xslot * 8);
         }
-        if (p.cluster > 1) { __syncwarp(); cluster_arrive(); cluster_wait(); }
+        if (p.cluster > 1) { __syncwarp(); cluster_arrive(); cluster_wait(); cluster_arrive(); cluster_wait(); }
     }
     } else {
         setmaxnreg_inc<kConsumerRegs>();
@@ -438,8 +442,8 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
         float acc[NREAD];
         uint32_t n = 0;  // stages processed by this CTA so far
         bool ok = true;
-        bool cl_arrived = false, cl_waited = false;  // this thread's half-steps of the one cluster barrier
-
+        // This thread's progress through the two cluster barriers: arrive A, wait A, arrive B, wait B.
+        int cl_steps = 0;
         // Barrier among the sixteen consumer warps with a bounded wait (a plain bar.sync would hang the CTA
         // if one warp had given up on a wait and left): false when the CTA is aborting.
         const uint32_t epi_bar = smem_u32(&ctrl->epi);
@@ -554,7 +558,7 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
                     // of the cluster.  Arriving here, not at the exchange, lets the read-out below overlap with
                     // waiting for them.
                     cluster_arrive();
-                    cl_arrived = true;
+                    cl_steps = 1;
                 }
                 if (have_prev) fold(sc_pend);  // previous stage's accumulator, before its D buffer is reused
                 tmem_wait_st();
@@ -589,66 +593,70 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
 #pragma unroll
                 for (int j = 0; j < NREAD; ++j) stage_acc[j * kTileRows + rt] += acc[j];
             }
+            fence_proxy_async_smem();  // the copy engine may read the parked rows (split-K exchange)
             if (!consumer_sync()) break;
             if (tid == 0) stamp(p, 6);
             const int m_rows = p.m < NREAD ? p.m : NREAD;
             const bool whole = (s0 == 0 && s1 == S);
             bool finish = whole;
-            int j0 = gi, jstep = 2;  // activation rows this thread finishes: j0, j0 + jstep, ...
+            int j0 = gi, jstep = 2, jend = m_rows;  // activation rows this thread finishes: j0, j0 + jstep, ... < jend
             if (!whole && p.cluster > 1) {
-                // K splits of one tile form a thread-block cluster.  Activation row j is finished by CTA
-                // j % cluster: every other CTA stores its fp32 partial of that row into the owner's shared memory
-                // with asynchronous stores that count bytes on the owner's mbarrier, so the owner waits for
-                // exactly its incoming data and nobody waits for a second cluster-wide rendezvous.  The owner
-                // sums the `cluster` copies in rank order (deterministic).
+                // K splits of one tile form a thread-block cluster.  CTA r of the cluster finishes a contiguous
+                // block of activation rows (ceil(m / cluster) of them): every CTA sends its fp32 partials of
+                // that block, contiguous in the parked accumulators, into r's shared memory with ONE bulk copy
+                // that counts its bytes on r's mbarrier, so r waits for exactly its incoming data.  It then sums
+                // the `cluster` copies in rank order (deterministic).
                 float* part = reinterpret_cast<float*>(smem);  // the weight ring, free once every CTA has arrived
                 const uint32_t my_rank = cluster_ctarank();
                 const uint32_t csz = static_cast<uint32_t>(p.cluster);
                 const uint32_t rows_cap = (static_cast<uint32_t>(m_rows) + csz - 1) / csz;
-                if (!cl_arrived) { cluster_arrive(); cl_arrived = true; }
-                cluster_wait();  // every CTA of the cluster has finished reading its weight ring
-                cl_waited = true;
+                if (cl_steps == 0) { cluster_arrive(); cl_steps = 1; }
+                cluster_wait();  // (A) every CTA of the cluster has finished reading its weight ring
+                cl_steps = 2;
                 if (tid == 0) stamp(p, 10);
-                {
-                    // rows gi, gi + 2, ...: owner j % cluster and its local row index j / cluster, stepped without
-                    // divisions (this code runs once per launch: its size, not its arithmetic, is what costs)
-                    uint32_t dst = smem_u32(part) + ((my_rank * rows_cap) * kTileRows + rt) * 4;
-                    const uint32_t red_bar = smem_u32(&ctrl->red);
-                    uint32_t owner = static_cast<uint32_t>(gi);
-#pragma unroll 2
-                    for (int j = gi; j < m_rows; j += 2) {
-                        if (owner != my_rank)
-                            st_async_cluster_f32(mapa_shared_cluster(dst, owner), stage_acc[j * kTileRows + rt],
-                                                 mapa_shared_cluster(red_bar, owner));
-                        owner += 2;
-                        if (owner >= csz) { owner -= csz; dst += kTileRows * 4; }
+                if (warp == 0 && lane < static_cast<int>(csz)) {  // lane r sends the block owned by CTA r
+                    int nr = m_rows - lane * static_cast<int>(rows_cap);
+                    nr = nr > static_cast<int>(rows_cap) ? static_cast<int>(rows_cap) : nr;
+                    if (nr > 0) {
+                        const uint32_t dst = smem_u32(part) + (my_rank * rows_cap) * (kTileRows * 4);
+                        bulk_copy_to_cluster(mapa_shared_cluster(dst, lane),
+                                             smem_u32(stage_acc) + lane * rows_cap * (kTileRows * 4), nr * (kTileRows * 4),
+                                             mapa_shared_cluster(smem_u32(&ctrl->red), lane));
                     }
                 }
                 if (tid == 0) stamp(p, 11);
                 if (!mbar_wait(smem_u32(&ctrl->red), 0u, abort_flag)) { ok = false; break; }
+                // (B) this CTA has all its incoming rows, so the senders' sources may go away; waited for at exit
+                cluster_arrive();
+                cl_steps = 3;
                 if (tid == 0) stamp(p, 7);
                 {
-                    // this CTA's rows rank, rank + cluster, ...; the two threads of a tile row take every other one
+                    // this CTA's block of rows; the two threads of a tile row take every other one
                     const bool direct = !p.swiglu && valid;
-                    OutT* y = static_cast<OutT*>(sg.y) + my_row;
                     const long long ldy = sg.ldy;
                     const float bias = (direct && sg.bias) ? sg.bias[my_row] : 0.f;
-                    const float* pp0 = part + gi * kTileRows + rt;
+                    const uint32_t jfirst = my_rank * rows_cap;
+                    uint32_t jlast = jfirst + rows_cap;
+                    jlast = jlast > static_cast<uint32_t>(m_rows) ? static_cast<uint32_t>(m_rows) : jlast;
+                    uint32_t j = jfirst + gi;
+                    OutT* yp = static_cast<OutT*>(sg.y) + my_row + static_cast<long long>(j) * ldy;
+                    uint32_t pa = smem_u32(part) + (gi * kTileRows + rt) * 4;
+                    const uint32_t rstep = rows_cap * (kTileRows * 4);
+                    float* sa = stage_acc + j * kTileRows + rt;
 #pragma unroll 1
-                    for (uint32_t j = my_rank + gi * csz; j < static_cast<uint32_t>(m_rows); j += 2 * csz, pp0 += 2 * kTileRows) {
+                    for (; j < jlast; j += 2, pa += 2 * kTileRows * 4, yp += 2 * ldy, sa += 2 * kTileRows) {
                         float sum = 0.f;
-                        const float* pp = pp0;
+                        uint32_t a = pa;
 #pragma unroll 2
-                        for (uint32_t r = 0; r < csz; ++r, pp += rows_cap * kTileRows)
-                            sum += (r == my_rank) ? stage_acc[j * kTileRows + rt] : *pp;
-                        if (direct) store_out<OutT>(y + static_cast<long long>(j) * ldy, sum + bias);
-                        else stage_acc[j * kTileRows + rt] = sum;
+                        for (uint32_t r = 0; r < csz; ++r, a += rstep) sum += lds_f32(a);
+                        if (direct) store_out<OutT>(yp, sum + bias);
+                        else *sa = sum;
                     }
+                    j0 = static_cast<int>(jfirst) + gi;
+                    jend = static_cast<int>(jlast);
                     finish = p.swiglu != 0;  // plain projections are already written
                 }
                 if (tid == 0) stamp(p, 12);
-                j0 = static_cast<int>(my_rank + gi * csz);
-                jstep = static_cast<int>(2 * csz);
             } else if (!whole) {
                 // tiles that straddle CTAs (one CTA per SM, units cut evenly): partials go through the scratch
                 // buffer and the last CTA to arrive sums them in CTA order
@@ -692,7 +700,7 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
                         OutT* y = static_cast<OutT*>(p.seg[0].y) + my_row;
                         const long long ldy = p.seg[0].ldy;
 #pragma unroll 4
-                        for (int j = j0; j < m_rows; j += jstep) {
+                        for (int j = j0; j < jend; j += jstep) {
                             const float g = stage_acc[j * kTileRows + t];
                             const float up = stage_acc[j * kTileRows + kHalfRows + t];
                             store_out<OutT>(y + static_cast<long long>(j) * ldy, (g / (1.0f + expf(-g))) * up);
@@ -703,18 +711,20 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
                     const long long ldy = sg.ldy;
                     const float b = sg.bias ? sg.bias[my_row] : 0.f;
 #pragma unroll 4
-                    for (int j = j0; j < m_rows; j += jstep)
+                    for (int j = j0; j < jend; j += jstep)
                         store_out<OutT>(y + static_cast<long long>(j) * ldy, stage_acc[j * kTileRows + rt] + b);
                 }
             }
             if (tid == 0) stamp(p, 4);
             u += (s1 - s0);
         }
-        // every thread of a cluster arrives at and waits for the cluster barrier exactly once, also when a wait gave up
+        // every thread of a cluster passes both cluster barriers exactly once, also when a wait gave up
         if (p.cluster > 1) {
             __syncwarp();
-            if (!cl_arrived) cluster_arrive();
-            if (!cl_waited) cluster_wait();
+            for (; cl_steps < 4; ++cl_steps) {
+                if (cl_steps & 1) cluster_wait();
+                else cluster_arrive();
+            }
         }
     }
 
