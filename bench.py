@@ -286,6 +286,108 @@ def gemv_bench(args):
         dist.destroy_process_group()
 
 
+def tp_gemv_bench(args):
+    """N-split tensor-parallel form of one projection: every rank streams 1/g of the weight rows with the same
+    kernel, then one NCCL all-gather restores the [M, N] activation on every rank.  value = whole-projection
+    algorithmic bytes per (max over ranks) time; the compute-only time is reported beside it."""
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    import xinfer_b200.ops as ops
+    from xinfer_b200 import lib
+    from xinfer_b200.tp import ColumnShardedLinear, shard_rows
+    assert lib().xinfer_b200_init(local_rank) == 0, lib().xinfer_last_cuda_error()
+
+    K, N = LAYER_SHAPES[args.shape]
+    M = args.m
+    n0, n1 = shard_rows(N, world, rank)
+    X, W, S = synth(M, K, N, 0)
+    Wl, Sl = W[n0:n1], S[n0:n1]
+    per_launch = alg_bytes(M, K, N, 2)
+    slice_bytes = Wl.nbytes + Sl.nbytes
+    n_buf = max(2, -(-2 * L2_BYTES // slice_bytes) + 1)
+    Xd = torch.from_numpy(X).cuda()
+    lins = [ColumnShardedLinear(torch.from_numpy(np.roll(Wl, i, axis=0)).cuda(), torch.from_numpy(np.roll(Sl, i, axis=0)).cuda(),
+                                None, N, K, rank=rank, world=world, sliced=True) for i in range(n_buf)]
+    Y = torch.empty((M, N), dtype=torch.float16, device="cuda")
+    launches = args.launches
+
+    def run(gather):
+        for i in range(launches):
+            lin = lins[i % n_buf]
+            lin.compute_local(Xd, M)
+            if gather:
+                lin.unstage(lin.gather(M), Y)
+
+    def timed(gather):
+        run(gather)
+        torch.cuda.synchronize()
+        graph = None
+        try:  # the launch loop as one CUDA graph (NCCL is capturable); eager if the capture is refused
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                run(gather)
+            graph = g
+        except Exception:
+            torch.cuda.synchronize()
+        step = graph.replay if graph is not None else (lambda: run(gather))
+        for _ in range(max(3, args.warmup)):
+            step()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record()
+        for _ in range(args.steps):
+            step()
+        ev1.record()
+        torch.cuda.synchronize()
+        ms = ev0.elapsed_time(ev1)
+        if world > 1:
+            t = torch.tensor([ms], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms, graph is not None
+
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    ms_c, _ = timed(False)
+    ms_g, graphed = timed(True)
+    clocks = sampler.stop()
+    assert ops.device_status(local_rank) == 0
+    total = args.steps * launches
+    us_c, us_g = ms_c * 1e3 / total, ms_g * 1e3 / total
+    value = per_launch / (us_g * 1e-6) / 1e9
+    peak, peak_kind = measured_peak()
+    line = {
+        "metric": "int4_gemv_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+        "warmup": max(3, args.warmup), "ms_per_step": ms_g / args.steps, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "int4 weights x fp16 activations, fp32 accumulate", "data": "synthetic",
+        "config": {"workload": f"INT4-G128 W4A16 linear M={M} K={K} N={N} ({args.shape}), N-split over {world} GPU(s) + "
+                               f"all-gather of [M,N] fp16, {launches} launches/step" + (" in one CUDA graph" if graphed else ", eager"),
+                   "M": M, "K": K, "N": N, "parallelism": f"tp{world}",
+                   "l2": f"rotates over {n_buf} distinct weight shards ({n_buf * slice_bytes >> 20} MiB > 2x L2 per GPU)"},
+        "roofline": {"bound": "hbm", "achieved": value, "peak": peak * world, "unit": "GB/s", "frac": value / (peak * world),
+                     "peak_kind": f"of {peak_kind} x {world} GPUs", "traffic": None, "us_per_launch": us_g,
+                     "us_per_launch_compute_only": us_c,
+                     "gbs_compute_only": per_launch / (us_c * 1e-6) / 1e9},
+        "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
+                "note": "device-resident operands; the end-to-end form of this metric is the gemv workload"},
+        "gpu_launches": total, "clocks": clocks,
+    }
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def sweep(args):
     import torch
     import xinfer_b200.ops as ops
@@ -515,7 +617,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="step", choices=["step", "gemv", "sweep"])
+    ap.add_argument("--workload", default="step", choices=["step", "gemv", "sweep", "tp_gemv"])
     ap.add_argument("--layers", type=int, default=64)
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--k", type=int, default=3)
@@ -536,6 +638,8 @@ def main():
     if args.impl == "reference":
         run_reference_arm(args, cfg)
         return
+    if args.workload == "tp_gemv":
+        return tp_gemv_bench(args)
     if args.workload == "sweep":
         sweep(args)
         return
