@@ -70,7 +70,7 @@ __global__ void embed_kernel(__half* out, const uint16_t* table_bf16, const long
 // `out` may have a wider row (ld_out) and a column offset so that two norms can fill one concatenated row.
 __global__ void __launch_bounds__(256) rmsnorm_kernel(__half* out, long long ld_out, __half* x, const __half* delta,
                                                       const float* w, int hidden, float eps) {
-    griddep_prologue();
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     __shared__ float red[32];
     const long long row = blockIdx.x;
     __half* xr = x + row * hidden;
@@ -81,6 +81,18 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(__half* out, long long ld_
                         ((reinterpret_cast<uintptr_t>(orow) & 15) == 0) &&
                         (!dr || (reinterpret_cast<uintptr_t>(dr) & 15) == 0);
     if (vec_ok) {
+        // The norm weights do not depend on the previous kernel in the stream: they are fetched before waiting
+        // for it, so that only the activations' latency is left on the critical path.
+        float4 wv[4][2];
+#pragma unroll
+        for (int it = 0; it < 4; ++it) {
+            const int i = threadIdx.x + it * 256;
+            if (i < nvec) {
+                wv[it][0] = __ldg(reinterpret_cast<const float4*>(w + i * 8));
+                wv[it][1] = __ldg(reinterpret_cast<const float4*>(w + i * 8 + 4));
+            }
+        }
+        asm volatile("griddepcontrol.wait;" ::: "memory");
         // one pass: each thread keeps its (up to four) 8-element vectors in registers
         uint4 v[4];
         float ss = 0.f;
@@ -114,8 +126,7 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(__half* out, long long ld_
             const int i = threadIdx.x + it * 256;
             if (i < nvec) {
                 const __half2* h = reinterpret_cast<const __half2*>(&v[it]);
-                const float4 w0 = *reinterpret_cast<const float4*>(w + i * 8);
-                const float4 w1 = *reinterpret_cast<const float4*>(w + i * 8 + 4);
+                const float4 w0 = wv[it][0], w1 = wv[it][1];
                 const float ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
                 uint4 o;
                 __half2* oh = reinterpret_cast<__half2*>(&o);
@@ -129,6 +140,7 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(__half* out, long long ld_
         }
         return;
     }
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     float ss = 0.f;
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
         float v = __half2float(xr[i]);

@@ -78,7 +78,6 @@ __global__ void __launch_bounds__(kThreads) logits_partials_kernel(const float* 
     __shared__ float s_v[kThreads / 32];
     __shared__ int s_i[kThreads / 32];
     __shared__ float s_f[kThreads / 32];
-    __shared__ float s_bcast;
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) {
         const float ov = __shfl_xor_sync(0xffffffffu, best, off);
@@ -97,7 +96,7 @@ __global__ void __launch_bounds__(kThreads) logits_partials_kernel(const float* 
             const int oi = __shfl_xor_sync(0xffffffffu, i, off);
             better(v, i, ov, oi);
         }
-        if (lane == 0) { s_v[0] = v; s_i[0] = i; s_bcast = v * inv_t; }
+        if (lane == 0) { s_v[0] = v; s_i[0] = i; }
     }
     __syncthreads();
     Partial res;

@@ -12,21 +12,27 @@
 // 128-k group, then one multiply by the group's scale.
 //
 // Mapping to the hardware.  The weights sit on the MMA's M side: a CTA owns 256 output rows as two
-// 128-row halves, one per consumer warpgroup, and thread t of a warpgroup owns row t of its half.
-// That thread reads its row's packed bytes from the TMA-staged tile (128B-swizzled, conflict free),
-// unpacks them to exact fp16 integers in registers, and writes them with tcgen05.st into TMEM lane
-// t, where they are the A operand (128 x 16 per MMA).  The <= 32 activation rows are the MMA's N
-// side: their K slice arrives as TMA boxes of 64 k per row in the 128-byte-swizzled K-major layout
-// and is the B operand from shared memory.  Each 128-k group accumulates into a fresh TMEM
-// tile D[128 x NMMA]; its owner thread reads lane t back (tcgen05.ld) and folds it into fp32
-// register accumulators with its own row's scale.  Nothing about a row ever leaves its thread.
+// 128-row halves.  Sixteen consumer warps, four per scheduler: warp (half, group, quarter) owns 32 rows
+// of its half and, in every 256-k stage, one of the stage's two 128-k groups.  Its thread reads 64
+// packed bytes of its row from the TMA-staged tile (128B-swizzled, conflict free), unpacks them to
+// exact fp16 integers in registers, and writes them with tcgen05.st into TMEM lane t, where they are
+// the A operand (128 x 16 per MMA).  The <= 32 activation rows are the MMA's N side: their K slice
+// arrives as TMA boxes of 64 k per row in the 128-byte-swizzled K-major layout, in a ring of its own,
+// and is the B operand from shared memory.  Each 128-k group accumulates into a fresh TMEM tile
+// D[128 x NMMA]; the thread that unpacked the group reads lane t back (tcgen05.ld) one stage later and
+// folds it into fp32 register accumulators with its own row's scale.  The two threads of a row add
+// their partial sums in the epilogue.
 //
-// The unpack yields k in the order (0,4,1,5,2,6,3,7) inside each 8-k block; a dedicated warp
-// permutes the staged activations in place to the same order before the MMA reads them.
+// Helper warpgroup: a TMA producer warp, two MMA-issuing warps (one per half; the warp computes
+// warp-uniformly, one elected lane issues) and a warp that rewrites the staged activations in the k
+// order of the unpack, (0,4,1,5,2,6,3,7) inside each 8-k block.  The register file is re-split
+// between the helper warpgroup and the consumers with setmaxnreg.
 //
-// Work is cut stream-K style: the (tile, 256-k stage) units are split evenly over one CTA per SM;
-// a tile finished by several CTAs is summed by the last one to arrive, in CTA order, from fp32
-// partials in a scratch buffer (deterministic, no float atomics).
+// Work is cut stream-K style when there is at least one tile per SM: the (tile, 256-k stage) units are
+// split evenly over one CTA per SM; a tile finished by several CTAs is summed by the last one to
+// arrive, in CTA order, from fp32 partials in a scratch buffer (deterministic, no float atomics).
+// With fewer tiles, each tile's K range is split over a thread-block cluster that sums through
+// distributed shared memory (bulk copies that count bytes on the receiver's mbarrier).
 #include <cuda.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
@@ -51,7 +57,7 @@ constexpr int kXBoxesPerStage = kStageK / 64;                // activation boxes
 constexpr int kConsumerThreads = 512;  // warps 0..15
 constexpr int kProducerWarp = 16;
 constexpr int kMmaWarp = 17;  // issues the MMAs of half 0 and owns the TMEM allocation; warp 18 issues half 1
-constexpr int kReorderWarp = 19;  // rewrites the staged activations in the k order of the unpack
+// warp 19 rewrites the staged activations in the k order of the unpack
 constexpr int kThreads = 640;
 // Register re-split between warpgroups.  The kernel starts with kLaunchRegs per thread (what 640 threads leave
 // of the 64K file); the helper warpgroup releases down to kHelperRegs and the four consumer warpgroups grow
@@ -536,19 +542,31 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
 #pragma unroll
                 for (int c = 0; c < 4; ++c) v[c] = lds128(stage + w_off[c]);
 
-                // The previous stage's MMAs of this group must be done before its A buffer is overwritten.
+                // The first kPre of the four 16-register chunks are unpacked before waiting for the previous
+                // stage's MMAs of this group (their A buffer is about to be overwritten): the hand-off latency
+                // of the tensor pipe is then covered by ALU work instead of a stalled warp.
+                constexpr int kPre = (NREAD <= 16) ? 4 : 2;
+                uint32_t a[4][16];
+#pragma unroll
+                for (int c = 0; c < kPre; ++c) {
+                    dequant_word(v[c].x, a[c] + 0);
+                    dequant_word(v[c].y, a[c] + 4);
+                    dequant_word(v[c].z, a[c] + 8);
+                    dequant_word(v[c].w, a[c] + 12);
+                }
                 if (have_prev) {
                     if (!mbar_wait(dfull, (n - 1) & 1u, abort_flag)) { ok = false; break; }
                     tc_fence_after_sync();
                 }
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
-                    uint32_t a[16];
-                    dequant_word(v[c].x, a + 0);
-                    dequant_word(v[c].y, a + 4);
-                    dequant_word(v[c].z, a + 8);
-                    dequant_word(v[c].w, a + 12);
-                    tmem_st16(a_t + c * 16, a);
+                    if (c >= kPre) {
+                        dequant_word(v[c].x, a[c] + 0);
+                        dequant_word(v[c].y, a[c] + 4);
+                        dequant_word(v[c].z, a[c] + 8);
+                        dequant_word(v[c].w, a[c] + 12);
+                    }
+                    tmem_st16(a_t + c * 16, a[c]);
                 }
                 // this warp has read its weights of the stage
                 __syncwarp();
