@@ -623,7 +623,7 @@ def main():
     ap.add_argument("--k", type=int, default=3)
     ap.add_argument("--context", type=int, default=8192)
     ap.add_argument("--shape", default="gate_up", choices=sorted(LAYER_SHAPES))
-    ap.add_argument("--m", type=int, default=1)
+    ap.add_argument("--m", "--rows", dest="m", type=int, default=1)  # activation rows M (--rows: torchrun parses --m itself)
     ap.add_argument("--launches", type=int, default=64)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
