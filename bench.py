@@ -604,8 +604,13 @@ def step_reference_arm(args):
     line = {"impl": "reference", "metric": "accepted_tok_per_s", "value": val, "unit": "tok/s", "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_s * 1e3, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "int4 weights, fp32 accumulate", "data": "synthetic",
-            "config": {"workload": f"27B-shape hybrid, MTP k={k}, batch {B}: CPU oracle port, sampled and extrapolated",
-                       "batch": B, "k": k, "context": args.context},
+            "config": {"workload": f"27B-shape hybrid ({args.layers} layers: Gated-DeltaNet + full attention, hidden 5120, "
+                                   f"FFN 17408, vocab 151936, INT4-G128), MTP k={k}, batch {B}, context {args.context}, greedy; "
+                                   f"one step = {k} MTP draft passes + one {B * (k + 1)}-row verify pass + acceptance + commit",
+                       "layers": args.layers, "batch": B, "k": k, "context": args.context,
+                       "note": "CPU arm: the oracle's port of the reference's linear_int4_naive on all host cores over a "
+                               "bounded row sample of every projection shape; the step time is extrapolated by weight "
+                               "bytes (the linears are 88 % of the reference's own step)"},
             "cpu_baseline": dict(res[0], value=val),
             "e2e": {"value": val, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line), flush=True)
