@@ -508,7 +508,8 @@ __global__ void __launch_bounds__(512, 2) gdn_spec_kernel(__half* out, const __h
                                                           const int* n_commit, int rows_per_seq, int prev_rows, int hv,
                                                           int hk) {
     griddep_prologue();
-    __shared__ float sh_q[8][128], sh_k[8][128], sh_beta[8], sh_eg[8], red[2][16];
+    __shared__ __align__(16) float sh_q[8][128], sh_k[8][128];
+    __shared__ float sh_beta[8], sh_eg[8], red[2][16];
     __shared__ float part_sum[2][4][128], attn_all[8][4][128];
     const int h = blockIdx.x, b = blockIdx.y;
     const int j = threadIdx.x & 127, part = threadIdx.x >> 7;  // part doubles as the token group in phases 0 and 2
@@ -579,11 +580,18 @@ __global__ void __launch_bounds__(512, 2) gdn_spec_kernel(__half* out, const __h
         const float v = __half2float(qkv[row * channels + 2 * hk * 128 + h * 128 + j]);
         const float eg = sh_eg[t];
         float kv_mem = 0.f;
+        const float4* k4 = reinterpret_cast<const float4*>(&sh_k[t][i0]);  // 16-byte broadcast reads
+        const float4* q4 = reinterpret_cast<const float4*>(&sh_q[t][i0]);
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-            const float sv = col[i] * eg;
-            col[i] = sv;
-            kv_mem += sv * sh_k[t][i0 + i];
+        for (int m = 0; m < 8; ++m) {
+            const float4 kk = k4[m];
+            const float kv[4] = {kk.x, kk.y, kk.z, kk.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float sv = col[m * 4 + e] * eg;
+                col[m * 4 + e] = sv;
+                kv_mem += sv * kv[e];
+            }
         }
         part_sum[t & 1][part][j] = kv_mem;
         __syncthreads();
@@ -591,10 +599,15 @@ __global__ void __launch_bounds__(512, 2) gdn_spec_kernel(__half* out, const __h
         const float delta = (v - (((ps[0] + ps[128]) + ps[256]) + ps[384])) * sh_beta[t];
         float attn = 0.f;
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-            const float ns = col[i] + sh_k[t][i0 + i] * delta;
-            col[i] = ns;
-            attn += ns * sh_q[t][i0 + i];
+        for (int m = 0; m < 8; ++m) {
+            const float4 kk = k4[m], qq = q4[m];
+            const float kv[4] = {kk.x, kk.y, kk.z, kk.w}, qv[4] = {qq.x, qq.y, qq.z, qq.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float ns = col[m * 4 + e] + kv[e] * delta;
+                col[m * 4 + e] = ns;
+                attn += ns * qv[e];
+            }
         }
         attn_all[t][part][j] = attn;
         if (part == 0) {
