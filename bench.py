@@ -632,6 +632,10 @@ def main():
     ap.add_argument("--launches", type=int, default=64)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
+    if args.impl == "reference":
+        # torchrun exports OMP_NUM_THREADS=1 to its workers; the CPU arm is meant to use every host thread,
+        # so restore the default before the OpenMP runtime of the oracle library is loaded
+        os.environ["OMP_NUM_THREADS"] = str(os.cpu_count() or 1)
     K, N = LAYER_SHAPES[args.shape]
     cfg = {"workload": f"INT4-G128 W4A16 linear M={args.m} K={K} N={N} ({args.shape})", "M": args.m, "K": K, "N": N}
     if args.workload == "step":
