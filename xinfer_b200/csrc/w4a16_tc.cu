@@ -542,31 +542,21 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
 #pragma unroll
                 for (int c = 0; c < 4; ++c) v[c] = lds128(stage + w_off[c]);
 
-                // The first kPre of the four 16-register chunks are unpacked before waiting for the previous
-                // stage's MMAs of this group (their A buffer is about to be overwritten): the hand-off latency
-                // of the tensor pipe is then covered by ALU work instead of a stalled warp.
-                constexpr int kPre = (NREAD <= 16) ? 4 : 2;
-                uint32_t a[4][16];
-#pragma unroll
-                for (int c = 0; c < kPre; ++c) {
-                    dequant_word(v[c].x, a[c] + 0);
-                    dequant_word(v[c].y, a[c] + 4);
-                    dequant_word(v[c].z, a[c] + 8);
-                    dequant_word(v[c].w, a[c] + 12);
-                }
+                // The previous stage's MMAs of this group must be done before its A buffer is overwritten.
+                // (Unpacking ahead of this wait was tried: the compiler re-reads and re-unpacks part of the words
+                // after the wait to stay within the register budget, 20 % more instructions for no gain.)
                 if (have_prev) {
                     if (!mbar_wait(dfull, (n - 1) & 1u, abort_flag)) { ok = false; break; }
                     tc_fence_after_sync();
                 }
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
-                    if (c >= kPre) {
-                        dequant_word(v[c].x, a[c] + 0);
-                        dequant_word(v[c].y, a[c] + 4);
-                        dequant_word(v[c].z, a[c] + 8);
-                        dequant_word(v[c].w, a[c] + 12);
-                    }
-                    tmem_st16(a_t + c * 16, a[c]);
+                    uint32_t a[16];
+                    dequant_word(v[c].x, a + 0);
+                    dequant_word(v[c].y, a + 4);
+                    dequant_word(v[c].z, a + 8);
+                    dequant_word(v[c].w, a + 12);
+                    tmem_st16(a_t + c * 16, a);
                 }
                 // this warp has read its weights of the stage
                 __syncwarp();
