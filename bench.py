@@ -40,7 +40,7 @@ L2_BYTES = 126 * 1024 * 1024
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum over algorithmic bytes of w4a16_tc_kernel, from the ncu capture
-# summarised in profiles/w4a16_tc_kernel_gate_up_m32_lm_head_m8.md (the kernel reads every weight byte once).
+# summarised under profiles/ (the kernel reads every weight byte once).
 NCU_TRAFFIC_RATIO = 0.98
 
 
