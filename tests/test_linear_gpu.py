@@ -198,7 +198,10 @@ def test_lm_head_fp32_logits_rows_sampled(cuda):
 
 # ------------------------------------------------------------------ edge cases
 @pytest.mark.parametrize("M,K,N", [(1, 128, 1), (2, 128, 3), (5, 256, 47), (32, 384, 129), (17, 640, 257),
-                                   (31, 1152, 513), (1, 5120, 48), (9, 128, 1000)])
+                                   (31, 1152, 513), (1, 5120, 48), (9, 128, 1000),
+                                   # K splits over clusters of 7, 6 and 8 CTAs with activation-row blocks that do
+                                   # not divide evenly (some CTAs of the cluster finish no row at all)
+                                   (3, 17408, 5120), (13, 6144, 5120), (29, 17408, 2560)])
 @pytest.mark.parametrize("path", [TC, SIMT])
 def test_ragged_shapes_with_bias(cuda, M, K, N, path):
     X, W, S, _ = synth_linear(M, K, N, seed=M + N)
