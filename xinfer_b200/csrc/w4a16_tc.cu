@@ -671,7 +671,7 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
                 const int first_tile = static_cast<int>(u_begin / S);
                 const int wslot = blockIdx.x * 2 + (tile == first_tile ? 0 : 1);
                 float* ws = p.workspace + static_cast<long long>(wslot) * (32 * kTileRows);
-#pragma unroll 1
+#pragma unroll 4
                 for (int j = gi; j < m_rows; j += 2) ws[j * kTileRows + rt] = stage_acc[j * kTileRows + rt];
                 __threadfence();
                 if (!consumer_sync()) break;
@@ -686,18 +686,24 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
                 finish = ctrl->is_last != 0;
                 if (finish) {
                     __threadfence();
+                    // This thread's rows gi, gi + 2, ...: the partials of one CTA are fetched for all of them at
+                    // once (independent loads in flight together), CTA after CTA in fixed order, so every sum is
+                    // deterministic and the loop costs one memory latency per CTA instead of one per row.
+                    float sums[NREAD / 2];
+#pragma unroll
+                    for (int q = 0; q < NREAD / 2; ++q) sums[q] = 0.f;
 #pragma unroll 1
-                    for (int j = gi; j < m_rows; j += 2) {
-                        float sum = 0.f;
-#pragma unroll 1
-                        for (int c = c_lo; c <= c_hi; ++c) {  // fixed CTA order: deterministic sum
-                            const int c_first_tile = static_cast<int>(unit_begin(c, p.total_units, ctas) / S);
-                            const float* src = p.workspace + static_cast<long long>(c * 2 + (tile == c_first_tile ? 0 : 1)) *
-                                                                 (32 * kTileRows);
-                            sum += __ldcg(src + j * kTileRows + rt);
-                        }
-                        stage_acc[j * kTileRows + rt] = sum;
+                    for (int c = c_lo; c <= c_hi; ++c) {
+                        const int c_first_tile = static_cast<int>(unit_begin(c, p.total_units, ctas) / S);
+                        const float* src = p.workspace + static_cast<long long>(c * 2 + (tile == c_first_tile ? 0 : 1)) *
+                                                             (32 * kTileRows) + rt;
+#pragma unroll
+                        for (int q = 0; q < NREAD / 2; ++q)
+                            if (gi + 2 * q < m_rows) sums[q] += __ldcg(src + (gi + 2 * q) * kTileRows);
                     }
+#pragma unroll
+                    for (int q = 0; q < NREAD / 2; ++q)
+                        if (gi + 2 * q < m_rows) stage_acc[(gi + 2 * q) * kTileRows + rt] = sums[q];
                     if (tid == 0) p.counters[tile] = 0;
                 }
             }
