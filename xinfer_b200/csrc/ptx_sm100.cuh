@@ -236,6 +236,12 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* map, uint3
         : "r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y), "l"(policy)
         : "memory");
 }
+// Pulls one box of a tiled tensor into L2 without a destination in shared memory (nothing to wait for).
+__device__ __forceinline__ void tma_prefetch_l2_2d(const void* map, int x, int y) {
+    asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(reinterpret_cast<uint64_t>(map)),
+                 "r"(x), "r"(y)
+                 : "memory");
+}
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const void* map, uint32_t bar, int x, int y, int z,
                                             uint64_t policy) {
     asm volatile(

@@ -25,6 +25,7 @@
 
 #include "../../include/xinfer_b200.h"
 #include "mixers.h"
+#include "w4a16.h"
 #include "sampling.h"
 
 namespace {
@@ -352,6 +353,7 @@ int enqueue_step(Dec* d, cudaStream_t s) {
     d->launches_per_step = 0;
     d->linear_launches = 0;
     d->linear_bytes = 0;
+    xb::tc_plan_rewind();  // the step's linears come in the recorded order (if a plan was recorded at capture)
     for (int i = 0; i < k; ++i) CK(draft_pass(d, s, i));
     if (d->override_armed && !d->linears_only)
         cudaMemcpyAsync(d->draft, d->draft_override, static_cast<size_t>(B) * k * sizeof(long long), cudaMemcpyDeviceToDevice, s);
@@ -469,6 +471,7 @@ int xinfer_spec_decoder_create(const xinfer_model_config* cfg, int batch, int k,
 
 void xinfer_spec_decoder_destroy(xinfer_spec_decoder* d) {
     if (!d) return;
+    xb::tc_plan_clear();  // the recorded plan points into this decoder's weights
     if (d->graph_exec) cudaGraphExecDestroy(d->graph_exec);
     if (d->graph) cudaGraphDestroy(d->graph);
     for (void* p : d->allocs) cudaFree(p);
@@ -530,8 +533,12 @@ int xinfer_spec_decoder_capture(xinfer_spec_decoder* d, xinfer_stream_t stream) 
     if (d->graph_exec) return XINFER_OK;
     // The lazy state commit reads the previous pass's row count, a host constant baked into the graph:
     // run one eager step first so that every replay sees prev_rows = k + 1.
+    // The same eager step records the order of the tensor-core launches, so that in the captured step
+    // every linear can ask L2 for the first weight stages of the one after it.
     if (d->prev_rows != d->k + 1) {
+        xb::tc_plan_record_begin();
         int rc = enqueue_step(d, s);
+        xb::tc_plan_record_end();
         if (rc < 0) return rc;
         if (cudaStreamSynchronize(s) != cudaSuccess) return XINFER_ERR_CUDA;
     }

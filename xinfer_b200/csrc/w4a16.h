@@ -25,6 +25,12 @@ void tc_set_trace(long long* dev_ptr);
 // attribute and call griddepcontrol.wait before they touch data of the previous kernel.
 bool pdl_enabled();
 bool tc_eligible(const void* x, const TcProj* proj, int num, bool swiglu, long long m, long long k, int group_size);
+// Launch plan (a hint for L2 prefetching of the next launch's weights): record one round of the caller's
+// fixed launch sequence between record_begin/record_end, then rewind at the start of every further round.
+void tc_plan_record_begin();
+void tc_plan_record_end();
+void tc_plan_rewind();
+void tc_plan_clear();
 int tc_launch(cudaStream_t stream, const void* x, const TcProj* proj, int num, bool swiglu, bool out_f32,
               long long m, long long k, int num_sms, float* workspace, int* counters, int counter_capacity,
               int* status);

@@ -40,6 +40,8 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include <vector>
+
 #include "ptx_sm100.cuh"
 #include "w4a16.h"
 
@@ -110,7 +112,16 @@ struct Params {
     int* counters;    // [total_tiles], zero between launches
     int* status;      // device status word
     int cluster;      // CTAs per thread-block cluster = K splits per tile summed through distributed shared memory (1: none)
-    long long* trace; // optional [ctas][8] globaltimer stamps (debug aid, null in production)
+    long long* trace; // optional [ctas][16] globaltimer stamps (debug aid, null in production)
+    // Optional: the first weight stages of the NEXT tensor-core launch in the stream, pulled into L2 while this
+    // launch drains, so that launch's pipeline fills from L2 instead of HBM.  pf_ctas = 0: nothing to prefetch.
+    CUtensorMap pf_map[kMaxSegs];
+    int pf_tile_begin[kMaxSegs];
+    int pf_num_segs;
+    int pf_swiglu;
+    int pf_stages;            // stage units per tile of that launch
+    int pf_ctas;              // its grid size
+    long long pf_total_units;
 };
 
 struct Ctrl {
@@ -321,6 +332,26 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
             if (ok && nx < total_mine) {
                 ok = mbar_wait_parked(smem_u32(&ctrl->x_empty[nx % C::kXStages]), ((nx / C::kXStages) & 1u) ^ 1u, abort_flag);
                 if (ok) issue_x(nx++);
+            }
+        }
+        if (leader && p.pf_ctas > 0) {
+            // this CTA's own stream is fully requested: ask L2 for what CTA blockIdx.x (+ k * gridDim.x) of the
+            // next launch will request first (its first two stages, same unit arithmetic as above)
+            for (int c = blockIdx.x; c < p.pf_ctas; c += gridDim.x) {
+                const long long pu0 = unit_begin(c, p.pf_total_units, p.pf_ctas);
+                const long long pu1 = unit_begin(c + 1, p.pf_total_units, p.pf_ctas);
+                for (int i = 0; i < 2 && pu0 + i < pu1; ++i) {
+                    const int ptile = static_cast<int>((pu0 + i) / p.pf_stages);
+                    const int ps = static_cast<int>((pu0 + i) - static_cast<long long>(ptile) * p.pf_stages);
+                    int pseg = 0;
+                    if (!p.pf_swiglu)
+                        for (int q = 1; q < kMaxSegs; ++q)
+                            if (q < p.pf_num_segs && ptile >= p.pf_tile_begin[q]) pseg = q;
+                    const int prow = (ptile - p.pf_tile_begin[pseg]) * (p.pf_swiglu ? kHalfRows : kTileRows);
+                    tma_prefetch_l2_2d(&p.pf_map[pseg], ps * kStageRowBytes, prow);
+                    tma_prefetch_l2_2d(&p.pf_map[p.pf_swiglu ? 1 : pseg], ps * kStageRowBytes,
+                                       p.pf_swiglu ? prow : prow + kHalfRows);
+                }
             }
         }
         if (*abort_flag) {
@@ -800,8 +831,27 @@ bool encode_x_map(CUtensorMap* map, const __half* x, long long m, long long k, i
 // tiles every tile is split into the same whole number of K ranges and those CTAs form a thread-block
 // cluster that sums its partials through distributed shared memory; the split count is the largest one
 // (at most 8, the portable cluster size) whose clusters are all co-resident in one wave.
+struct Decomp {
+    int ctas;
+    int cluster;
+};
+
+// `max_clusters[cs]`: how many clusters of cs CTAs of the kernel can be resident at once.
+Decomp choose_grid(int tiles, int stages, int num_sms, const int* max_clusters) {
+    Decomp d{num_sms, 1};
+    if (tiles >= num_sms) return d;
+    int best = tiles;  // one CTA per tile, no split
+    for (int cs = 2; cs <= 8 && cs <= stages; ++cs) {
+        if (max_clusters[cs] < tiles) continue;  // would need a second wave
+        if (tiles * cs > best && tiles * cs <= num_sms) { best = tiles * cs; d.cluster = cs; }
+    }
+    d.ctas = tiles * d.cluster;
+    return d;
+}
+
+// One-time set-up of a kernel instantiation on the current device; returns its cluster occupancy table.
 template <int NMMA, int NREAD, typename OutT>
-cudaError_t launch(Params& p, int tiles, int num_sms, cudaStream_t stream) {
+cudaError_t configure(const int** table) {
     auto kern = w4a16_tc_kernel<NMMA, NREAD, OutT>;
     static int configured_dev = -1;
     static int max_clusters[9];
@@ -834,17 +884,30 @@ cudaError_t launch(Params& p, int tiles, int num_sms, cudaStream_t stream) {
         }
         configured_dev = dev;
     }
-    int ctas, cluster = 1;
-    if (tiles >= num_sms) {
-        ctas = num_sms;
-    } else {
-        int best = tiles;  // one CTA per tile, no split
-        for (int cs = 2; cs <= 8 && cs <= p.stages; ++cs) {
-            if (max_clusters[cs] < tiles) continue;  // would need a second wave
-            if (tiles * cs > best && tiles * cs <= num_sms) { best = tiles * cs; cluster = cs; }
-        }
-        ctas = tiles * cluster;
-    }
+    *table = max_clusters;
+    return cudaSuccess;
+}
+
+// The decomposition launch() would choose for a problem of `m` activation rows (which picks the instantiation).
+cudaError_t decomp_for(long long m, bool out_f32, int tiles, int stages, int num_sms, Decomp* out) {
+    const int* table = nullptr;
+    cudaError_t e;
+    if (m <= 8) e = out_f32 ? configure<16, 8, float>(&table) : configure<16, 8, __half>(&table);
+    else if (m <= 16) e = out_f32 ? configure<16, 16, float>(&table) : configure<16, 16, __half>(&table);
+    else e = out_f32 ? configure<32, 32, float>(&table) : configure<32, 32, __half>(&table);
+    if (e != cudaSuccess) return e;
+    *out = choose_grid(tiles, stages, num_sms, table);
+    return cudaSuccess;
+}
+
+template <int NMMA, int NREAD, typename OutT>
+cudaError_t launch(Params& p, int tiles, int num_sms, cudaStream_t stream) {
+    auto kern = w4a16_tc_kernel<NMMA, NREAD, OutT>;
+    const int* table = nullptr;
+    cudaError_t ce = configure<NMMA, NREAD, OutT>(&table);
+    if (ce != cudaSuccess) return ce;
+    const Decomp d = choose_grid(tiles, p.stages, num_sms, table);
+    const int ctas = d.ctas, cluster = d.cluster;
     p.cluster = cluster;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(ctas);
@@ -872,6 +935,86 @@ bool pdl_enabled() {
 
 static long long* g_trace = nullptr;
 void tc_set_trace(long long* dev_ptr) { g_trace = dev_ptr; }
+
+// ------------------------------------------------------------------------------------ launch plan
+// A caller that issues the same sequence of tensor-core launches over and over (the speculative step) records
+// it once; afterwards every launch of the sequence knows which weights the next one will stream and asks L2
+// for that launch's first stages while it drains.  The plan is only a hint: a call that does not match the
+// recorded sequence switches it off.
+namespace {
+struct PlanEntry {
+    TcProj proj[kMaxSegs];
+    int num;
+    bool swiglu, out_f32;
+    long long m, k;
+};
+std::vector<PlanEntry> g_plan;
+bool g_plan_recording = false, g_plan_active = false;
+size_t g_plan_cursor = 0;
+
+PlanEntry make_entry(const TcProj* proj, int num, bool swiglu, bool out_f32, long long m, long long k) {
+    PlanEntry e;
+    memset(&e, 0, sizeof(e));
+    const int cnt = swiglu ? 2 : num;
+    for (int i = 0; i < cnt && i < kMaxSegs; ++i) e.proj[i] = proj[i];
+    e.num = num;
+    e.swiglu = swiglu;
+    e.out_f32 = out_f32;
+    e.m = m;
+    e.k = k;
+    return e;
+}
+bool same_launch(const PlanEntry& a, const PlanEntry& b) {
+    return a.proj[0].w == b.proj[0].w && a.num == b.num && a.swiglu == b.swiglu && a.m == b.m && a.k == b.k;
+}
+}  // namespace
+
+void tc_plan_record_begin() {
+    g_plan.clear();
+    g_plan_recording = true;
+    g_plan_active = false;
+    g_plan_cursor = 0;
+}
+void tc_plan_record_end() {
+    g_plan_recording = false;
+    g_plan_active = !g_plan.empty();
+    g_plan_cursor = 0;
+}
+void tc_plan_rewind() { g_plan_cursor = 0; }
+void tc_plan_clear() {
+    g_plan.clear();
+    g_plan_recording = g_plan_active = false;
+    g_plan_cursor = 0;
+}
+
+namespace {
+// Describes the first stages of `next` to the kernel of the current launch (Params::pf_*).
+void fill_prefetch(Params& p, const PlanEntry& next, int num_sms) {
+    p.pf_ctas = 0;
+    if (next.m < 1 || next.m > 32 || next.k < 128 || (next.k % 128) != 0) return;
+    const int cnt = next.swiglu ? 2 : next.num;
+    int tiles = 0;
+    for (int i = 0; i < cnt; ++i) {
+        if (reinterpret_cast<uintptr_t>(next.proj[i].w) & 15) return;
+        if (!encode_w_map(&p.pf_map[i], next.proj[i].w, next.proj[i].n, next.k)) return;
+        p.pf_tile_begin[i] = tiles;
+        if (next.swiglu) {
+            if (i == 0) tiles += static_cast<int>((next.proj[0].n + kHalfRows - 1) / kHalfRows);
+            else p.pf_tile_begin[i] = 0;
+        } else {
+            tiles += static_cast<int>((next.proj[i].n + kTileRows - 1) / kTileRows);
+        }
+    }
+    const int stages = static_cast<int>((next.k / 128 + 1) / 2);
+    Decomp d;
+    if (decomp_for(next.m, next.out_f32, tiles, stages, num_sms, &d) != cudaSuccess) return;
+    p.pf_num_segs = next.swiglu ? 1 : next.num;
+    p.pf_swiglu = next.swiglu ? 1 : 0;
+    p.pf_stages = stages;
+    p.pf_total_units = static_cast<long long>(tiles) * stages;
+    p.pf_ctas = d.ctas;
+}
+}  // namespace
 
 size_t tc_workspace_bytes(int ctas) { return static_cast<size_t>(ctas) * 2 * 32 * kTileRows * sizeof(float); }
 
@@ -926,6 +1069,18 @@ int tc_launch(cudaStream_t stream, const void* x, const TcProj* proj, int num, b
     p.counters = counters;
     p.status = status;
     p.trace = g_trace;
+    if (g_plan_recording) {
+        g_plan.push_back(make_entry(proj, num, swiglu, out_f32, m, k));
+    } else if (g_plan_active) {
+        const PlanEntry cur = make_entry(proj, num, swiglu, out_f32, m, k);
+        if (g_plan_cursor < g_plan.size() && same_launch(g_plan[g_plan_cursor], cur)) {
+            // (the last launch of the sequence looks ahead to the first one of the next round)
+            fill_prefetch(p, g_plan[(g_plan_cursor + 1) % g_plan.size()], num_sms);
+            ++g_plan_cursor;
+        } else {
+            g_plan_active = false;  // not the recorded sequence: no more hints
+        }
+    }
     cudaError_t e;
     if (m <= 8) e = out_f32 ? launch<16, 8, float>(p, tiles, num_sms, stream) : launch<16, 8, __half>(p, tiles, num_sms, stream);
     else if (m <= 16) e = out_f32 ? launch<16, 16, float>(p, tiles, num_sms, stream) : launch<16, 16, __half>(p, tiles, num_sms, stream);
