@@ -72,6 +72,7 @@ static_assert(kConsumerThreads * (kConsumerRegs - kLaunchRegs) <= (kThreads - kC
               "consumer register request exceeds what the helper warpgroup releases");
 constexpr uint32_t kTmemCols = 512;
 constexpr int kMaxSegs = 4;
+constexpr int kPrefetchStages = 4;  // stages of the next launch that each CTA asks L2 for
 
 template <int NMMA>
 struct Cfg {
@@ -340,7 +341,7 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
             for (int c = blockIdx.x; c < p.pf_ctas; c += gridDim.x) {
                 const long long pu0 = unit_begin(c, p.pf_total_units, p.pf_ctas);
                 const long long pu1 = unit_begin(c + 1, p.pf_total_units, p.pf_ctas);
-                for (int i = 0; i < 2 && pu0 + i < pu1; ++i) {
+                for (int i = 0; i < kPrefetchStages && pu0 + i < pu1; ++i) {
                     const int ptile = static_cast<int>((pu0 + i) / p.pf_stages);
                     const int ps = static_cast<int>((pu0 + i) - static_cast<long long>(ptile) * p.pf_stages);
                     int pseg = 0;
