@@ -119,6 +119,18 @@ XINFER_EXPORT int xinfer_linear_int4_f16f16_noalloc(xinfer_stream_t s, void* Y_f
                                                     const uint8_t* W_int4, const void* scales_f16, const float* bias,
                                                     int64_t M, int64_t N, int64_t K, int group_size);
 
+/* Launch plan for callers that issue the same sequence of fp16-activation linears again and again (a decode or
+ * verify pass).  Record one round of the sequence between record_begin() and record_end(); call rewind() at the
+ * start of every later round.  Each launch of a recorded round then also asks the L2 cache for the first weight
+ * tiles of the launch that follows it, so that launch starts from L2 instead of HBM.  The plan is a hint: results
+ * are unchanged, and a call that does not match the recorded sequence switches the hints off until the next
+ * recording.  One plan per process; clear() drops it (call it before freeing the recorded weights).
+ * No counterpart in the reference (its queue has no cross-kernel prefetch). */
+XINFER_EXPORT void xinfer_linear_plan_record_begin(void);
+XINFER_EXPORT void xinfer_linear_plan_record_end(void);
+XINFER_EXPORT void xinfer_linear_plan_rewind(void);
+XINFER_EXPORT void xinfer_linear_plan_clear(void);
+
 /* ---- sampling ---------------------------------------------------------------------------------- */
 /* Replaces xinfer::ops::argmax_scratch_size, src/ops/sampling.h:11-15. */
 XINFER_EXPORT size_t xinfer_argmax_scratch_size(int64_t vocab_size);

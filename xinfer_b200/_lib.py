@@ -64,6 +64,10 @@ SIGNATURES = {
     "xinfer_last_linear_path": (_i32, []),
     "xinfer_set_linear_path": (None, [_i32]),
     "xinfer_debug_set_trace": (None, [_vp]),
+    "xinfer_linear_plan_record_begin": (None, []),
+    "xinfer_linear_plan_record_end": (None, []),
+    "xinfer_linear_plan_rewind": (None, []),
+    "xinfer_linear_plan_clear": (None, []),
     "xinfer_linear_int4_f16f16": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i32]),
     "xinfer_linear_int4_f16f32": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i32]),
     "xinfer_linear_int4_f32f32": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i32]),

@@ -178,6 +178,11 @@ const char* xinfer_last_cuda_error(void) { return g_last_error.c_str(); }
 const char* xinfer_b200_version(void) { return "xinfer_b200 0.1 (sm_100a)"; }
 int xinfer_last_linear_path(void) { return g_last_path; }
 void xinfer_debug_set_trace(void* dev_ptr) { xb::tc_set_trace(static_cast<long long*>(dev_ptr)); }
+
+void xinfer_linear_plan_record_begin(void) { xb::tc_plan_record_begin(); }
+void xinfer_linear_plan_record_end(void) { xb::tc_plan_record_end(); }
+void xinfer_linear_plan_rewind(void) { xb::tc_plan_rewind(); }
+void xinfer_linear_plan_clear(void) { xb::tc_plan_clear(); }
 void xinfer_set_linear_path(int path) { g_forced_path = path; }
 
 int xinfer_linear_int4_f16f16(xinfer_stream_t s, void* Y, const void* X, const uint8_t* W, const void* scales,

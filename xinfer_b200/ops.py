@@ -66,6 +66,33 @@ def linear_int4_noalloc(Y: torch.Tensor, X, W_int4, scales, bias, M: int, N: int
                                                          _ptr(bias), M, N, K, group_size), "linear_int4_noalloc")
 
 
+class LinearPlan:
+    """Launch plan for a fixed sequence of fp16 ``linear_int4`` / fused / SwiGLU calls (one decode or verify pass).
+
+    ``with plan.record(): run_the_sequence()`` once, then ``plan.rewind()`` before every later round: each launch
+    of a round also pulls the first weight tiles of the next launch into L2.  Results are unchanged; a call
+    outside the recorded order switches the hints off.  One plan per process."""
+
+    class _Rec:
+        def __enter__(self):
+            lib().xinfer_linear_plan_record_begin()
+
+        def __exit__(self, *exc):
+            lib().xinfer_linear_plan_record_end()
+            return False
+
+    def record(self):
+        return LinearPlan._Rec()
+
+    @staticmethod
+    def rewind() -> None:
+        lib().xinfer_linear_plan_rewind()
+
+    @staticmethod
+    def clear() -> None:
+        lib().xinfer_linear_plan_clear()
+
+
 def linear_int4_fused(X: torch.Tensor, descs: Sequence[dict], M: int, K: int, group_size: int = 128) -> int:
     """``xinfer::ops::linear_int4_fused`` (src/ops/linear.h:96-111).
 
