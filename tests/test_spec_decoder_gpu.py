@@ -216,3 +216,25 @@ def test_graph_replay_equals_eager(small):
         assert np.array_equal(ee, eg) and np.array_equal(ce, cg)
     eager.close()
     graph.close()
+
+
+def test_reduced_stack_at_full_layer_shapes():
+    """The reduced-stack configuration with the 27B layer shapes (8 layers = 6 Gated-DeltaNet + 2 GQA 24q/4kv,
+    hidden 5120, FFN 17408, k=3, batch 1, context 2048): every projection runs through the decomposition it
+    gets in the benchmark (cluster split-K, fused 3- and 4-way launches, SwiGLU pairs).  The vocabulary is
+    cut to 8192 to keep the CPU oracle to seconds."""
+    from xinfer_b200.spec import Shape, SpecDecoder
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    shape_cfg = Shape(hidden_size=5120, intermediate_size=17408, num_hidden_layers=8, num_attention_heads=24,
+                      num_key_value_heads=4, vocab_size=8192, linear_num_v_heads=48, linear_num_k_heads=16)
+    dec = SpecDecoder(shape_cfg, batch=1, k=3, max_seq=2100, seed=21)
+    dec.reset(2048, seed=7)
+    model = pull_model(dec, shape_cfg, dec.k)
+    seqs = pull_state(dec, model, shape_cfg, dec.batch, dec.max_seq)
+    compare_step(dec, model, seqs, shape_cfg, tag="cfg3-plain")
+    cont = model.greedy_continuation(seqs[0], 3)
+    accepted = compare_step(dec, model, seqs, shape_cfg, [cont], tag="cfg3-accept-all")
+    assert accepted == [3]
+    compare_step(dec, model, seqs, shape_cfg, tag="cfg3-after")
+    dec.close()
