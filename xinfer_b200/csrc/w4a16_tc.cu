@@ -149,8 +149,6 @@ __device__ __forceinline__ int unit_owner(long long unit, long long total, long 
     return static_cast<int>(((unit + 1) * ctas + total - 1) / total - 1);
 }
 
-constexpr int kScalePrefetchStages = 10;
-__device__ __forceinline__ void prefetch_l1(const void* ptr) { asm volatile("prefetch.global.L1 [%0];" ::"l"(ptr)); }
 // Non-blocking L2 prefetch of [ptr, ptr + bytes), one request per 32-byte sector.
 __device__ __forceinline__ void prefetch_l2_range(const void* ptr, int bytes) {
     const uintptr_t lo = reinterpret_cast<uintptr_t>(ptr) & ~uintptr_t(31);
@@ -547,28 +545,28 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
 
             // The scale of this warp's group is fetched two stages ahead as a raw 16-bit value and only
             // converted when its stage starts, so the load latency never sits in the loop's critical path.
-            const unsigned short* raw_scales = reinterpret_cast<const unsigned short*>(my_scales);
-            auto load_scale = [&](int s) -> uint32_t {
-                const int g = 2 * s + gi;
-                return g < gmax ? static_cast<uint32_t>(__ldg(raw_scales + g)) : 0u;
-            };
+            // The loop's bookkeeping is kept to running pointers and counters: the SM is issue-bound here and
+            // every instruction of a consumer warp is paid sixteen-fold.
+            const unsigned short* sp = reinterpret_cast<const unsigned short*>(my_scales) + 2 * s0 + gi;  // this stage's scale
+            // stages [s0, s_lim) have a scale for this thread (none for rows beyond N; K/128 odd: group 1 of the last)
+            const int s_lim = min(s1, (gmax - gi + 1) >> 1);
             float sc_pend = 0.f;
-            uint32_t q0 = load_scale(s0);
-            uint32_t q1 = (s0 + 1 < s1) ? load_scale(s0 + 1) : 0u;
+            uint32_t q0 = (s0 < s_lim) ? static_cast<uint32_t>(__ldg(sp)) : 0u;
+            uint32_t q1 = (s0 + 1 < s_lim) ? static_cast<uint32_t>(__ldg(sp + 2)) : 0u;
             bool have_prev = false;
+            uint32_t slot = n % C::kStages;                 // weight-ring slot and phase of stage n
+            uint32_t full_phase = (n / C::kStages) & 1u;
+            uint32_t dfull_phase = (n - 1) & 1u;            // phase of the previous stage's MMA completion
+            const int s_last = (p.cluster > 1) ? s1 - 1 : -1;  // stage after which the cluster barrier is arrived at
 
-            for (int s = s0; s < s1 && ok; ++s, ++n) {
-                const uint32_t slot = n % C::kStages;
+            for (int s = s0; s < s1; ++s, ++n) {
                 const float sc_cur = __half2float(__ushort_as_half(static_cast<unsigned short>(q0)));
                 q0 = q1;
-                if (s + 2 < s1) q1 = load_scale(s + 2);
-                // Behind the weight stream's queue of requests a miss of this SM takes several stages to come
-                // back: ask for the scale's sector many stages early, so the load above finds it in L1.
-                if (s + kScalePrefetchStages < s1 && 2 * (s + kScalePrefetchStages) + gi < gmax)
-                    prefetch_l1(raw_scales + 2 * (s + kScalePrefetchStages) + gi);
+                q1 = 0u;
+                if (s + 2 < s_lim) q1 = static_cast<uint32_t>(__ldg(sp + 4));
+                sp += 2;
 
-                if (!mbar_wait(full0 + slot * 8, (n / C::kStages) & 1u, abort_flag)) { ok = false; break; }
-                if (tid == 0 && n == 0) stamp(p, 2);
+                if (!mbar_wait(full0 + slot * 8, full_phase, abort_flag)) { ok = false; break; }
                 const uint32_t stage = smem_base + slot * kWStageBytes;
                 uint4 v[4];
 #pragma unroll
@@ -578,9 +576,12 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
                 // (Unpacking ahead of this wait was tried: the compiler re-reads and re-unpacks part of the words
                 // after the wait to stay within the register budget, 20 % more instructions for no gain.)
                 if (have_prev) {
-                    if (!mbar_wait(dfull, (n - 1) & 1u, abort_flag)) { ok = false; break; }
+                    if (!mbar_wait(dfull, dfull_phase, abort_flag)) { ok = false; break; }
                     tc_fence_after_sync();
+                } else if (tid == 0 && n == 0) {
+                    stamp(p, 2);
                 }
+                dfull_phase ^= 1u;
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
                     uint32_t a[16];
@@ -593,7 +594,8 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
                 // this warp has read its weights of the stage
                 __syncwarp();
                 if (lane == 0) mbar_arrive(empty0 + slot * 8);
-                if (p.cluster > 1 && s + 1 == s1) {
+                if (++slot == C::kStages) { slot = 0; full_phase ^= 1u; }
+                if (s == s_last) {
                     // Last stage of this CTA's K range: its weight ring may now be overwritten by the other CTAs
                     // of the cluster.  Arriving here, not at the exchange, lets the read-out below overlap with
                     // waiting for them.
