@@ -80,7 +80,7 @@ struct Cfg {
     // only when the MMAs that read it have completed, about a stage later.  Keeping them apart lets the
     // weight stream (the HBM traffic) run as far ahead as its own ring allows.
     static constexpr int kXStageBytes = NMMA * kStageK * 2;
-    static constexpr int kStages = (NMMA == 32) ? 4 : 5;   // weight ring, 32 KiB per slot
+    static constexpr int kStages = (NMMA == 32) ? 3 : 4;   // weight ring, 32 KiB per slot
     static constexpr int kXStages = (NMMA == 32) ? 4 : 6;  // activation ring
     static constexpr int kWRingBytes = kStages * kWStageBytes;
     static constexpr int kXRingBytes = kXStages * kXStageBytes;
