@@ -80,6 +80,10 @@ struct Cfg {
     // only when the MMAs that read it have completed, about a stage later.  Keeping them apart lets the
     // weight stream (the HBM traffic) run as far ahead as its own ring allows.
     static constexpr int kXStageBytes = NMMA * kStageK * 2;
+    // Depth is not what limits the stream (3, 4 and 5 weight slots run at the same rate); the total is: L1 is
+    // what shared memory leaves of the SM's 256 KB, and the consumers' strided 2-byte scale loads live in L1.
+    // Both configurations stay under the 196 KB carve-out (about 60 KB of L1); at 224 KB the scale lines
+    // thrashed (LM head 3 % slower at M <= 8, 15 % at M = 32).
     static constexpr int kStages = (NMMA == 32) ? 3 : 4;   // weight ring, 32 KiB per slot
     static constexpr int kXStages = (NMMA == 32) ? 4 : 6;  // activation ring
     static constexpr int kWRingBytes = kStages * kWStageBytes;
@@ -87,6 +91,7 @@ struct Cfg {
     static constexpr int kXchgBytes = kTileRows * NMMA * 4;  // accumulators parked for the epilogue
     static constexpr int kCtrlBytes = 512;
     static constexpr int kSmemBytes = kWRingBytes + kXRingBytes + kXchgBytes + kCtrlBytes + 1024;  // + align slack
+    static_assert(kSmemBytes <= 196 * 1024, "rings sized to leave L1 for the scale loads");
 };
 
 struct Seg {
