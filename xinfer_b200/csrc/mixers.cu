@@ -212,22 +212,30 @@ __global__ void __launch_bounds__(256) attn_prep_kernel(__half* q_out, __half* k
 }
 
 // ------------------------------------------------------------------------------- split-KV GQA attention
-// Grid (splits, Hkv, B), 256 threads, two CTAs per SM.  The G * R query rows that share one KV head
-// (G = Hq / Hkv, at most 32 rows) form the M side of mma.sync m16n8k16 tiles; keys stream through shared
-// memory in chunks of 32 via cp.async, double buffered.  Warp (mt, wq) owns the 16-row tile mt and, per
-// chunk, the keys [8 wq, 8 wq + 8) of S = Q K^T and the output dims [64 wq, 64 wq + 64) of O += P V.
+// Grid (splits, Hkv, B), 256 threads, two CTAs per SM.  Keys stream through shared memory in chunks of 32 via
+// cp.async, double buffered, and both products are computed transposed so that the G * R query rows that share
+// one KV head (G = Hq / Hkv, at most 32 rows) sit on the N side of mma.sync m16n8k16, eight rows per tile, and
+// nothing is padded to 16:
+//   S^T = K Q^T   warp (kq, kt) owns the keys [16 kt, 16 kt + 16) of the chunk and the head dims
+//                 [64 kq, 64 kq + 64); its slice of Q stays in registers as B fragments for the whole kernel,
+//                 so a chunk costs one read of K from shared memory and no read of Q; the four partial sums
+//                 over kq meet in shared memory, where the softmax threads add them;
+//   O^T += V^T P^T  warp w owns the output dims [32 w, 32 w + 32); V is read once per chunk (ldmatrix.trans).
+// The kernel is bound by shared-memory bandwidth (two CTAs per SM share it): per 32 KB chunk this layout moves
+// about 100 KB through shared memory where the untransposed one moved 165 KB.
 // Each CTA writes an unnormalised partial (max, sum, O) per row.
 constexpr int kAttnChunk = 32;
-constexpr int kAttnStages = 2;
+constexpr int kAttnStages = 2;  // the loop below is written for exactly two slots
 constexpr int kAttnThreads = 256;
 constexpr int kAttnLd = 264;  // padded row of 256 halves (528 B): conflict-free ldmatrix
 constexpr int kAttnRows = 32;
+constexpr int kAttnSpLd = 41;  // odd row pitch: the softmax threads (4 rows x 8 key parts per warp) read conflict-free
 
 struct AttnSmem {
     __half q[kAttnRows][kAttnLd];
     __half k[kAttnStages][kAttnChunk][kAttnLd];
     __half v[kAttnStages][kAttnChunk][kAttnLd];
-    float s[kAttnRows][kAttnChunk + 1];
+    float sp[4][kAttnChunk][kAttnSpLd];  // S^T partial sums over the four dim quarters, [key][row]
     __half p[kAttnRows][kAttnChunk + 8];
     float row_max[kAttnRows];
     float row_sum[kAttnRows];
@@ -251,6 +259,11 @@ __device__ __forceinline__ void ldmatrix_x2(uint32_t* r, const void* p) {
     const uint32_t a = static_cast<uint32_t>(__cvta_generic_to_shared(p));
     asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0, %1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(a));
 }
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t* r, const void* p) {
+    const uint32_t a = static_cast<uint32_t>(__cvta_generic_to_shared(p));
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
 __device__ __forceinline__ void ldmatrix_x2_trans(uint32_t* r, const void* p) {
     const uint32_t a = static_cast<uint32_t>(__cvta_generic_to_shared(p));
     asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0, %1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(a));
@@ -272,9 +285,10 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_split_kernel(float* part
     AttnSmem& sm = *reinterpret_cast<AttnSmem*>(attn_smem_raw);
     const int split = blockIdx.x, nsplit = gridDim.x, kvh = blockIdx.y, b = blockIdx.z;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int mt = warp >> 2, wq = warp & 3;
+    const int kq = warp >> 1, kt = warp & 1;  // S^T role: dim quarter, 16-key tile
     const int G = hq / hkv;
     const int nrows = G * rows_per_seq;  // valid query rows, row = g * R + i
+    const int ntiles = (nrows + 7) >> 3;  // 8-row tiles that hold query rows
     const int ctx_b = ctx[b];
     long long total_keys = static_cast<long long>(ctx_b) + rows_per_seq;
     if (total_keys > max_seq) total_keys = max_seq;
@@ -298,8 +312,7 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_split_kernel(float* part
         sm.row_sum[tid] = 0.f;
     }
 
-    // one cp.async group per chunk slot, also when the slot lies past the split's end (an empty group), so that
-    // "all but the newest kAttnStages - 1 groups have landed" always means "chunk c has landed"
+    // one cp.async group per chunk (an empty one past the split's end)
     auto load_chunk = [&](int c, int buf) {
         const long long key0 = static_cast<long long>(c) * kAttnChunk;
         if (c < c_end)
@@ -314,35 +327,60 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_split_kernel(float* part
         cp_async_commit();
     };
 
-    float o_acc[8][4];
+    // O^T accumulators: [16-dim tile][8-row tile]; element e of a tile is (dim g4 + 8 (e >> 1), row 2 t4 + (e & 1))
+    float o_acc[2][4][4];
 #pragma unroll
-    for (int nt = 0; nt < 8; ++nt)
+    for (int mi = 0; mi < 2; ++mi)
 #pragma unroll
-        for (int e = 0; e < 4; ++e) o_acc[nt][e] = 0.f;
+        for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) o_acc[mi][nt][e] = 0.f;
 
     for (int i = 0; i < kAttnStages - 1; ++i) load_chunk(c_begin + i, i);
+
+    // this warp's slice of Q (all rows, dims [64 kq, 64 kq + 64)) as B fragments, read once
+    __syncthreads();
+    uint32_t qf[4][4][2];
+#pragma unroll
+    for (int ks = 0; ks < 4; ++ks)
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt)
+            ldmatrix_x2(qf[ks][nt], &sm.q[nt * 8 + (lane & 7)][kq * 64 + ks * 16 + ((lane >> 3) & 1) * 8]);
+
     for (int c = c_begin; c < c_end; ++c) {
         const int buf = (c - c_begin) % kAttnStages;
-        // the slot refilled here was read in the previous iteration, which ended with a barrier
-        load_chunk(c + kAttnStages - 1, (c - c_begin + kAttnStages - 1) % kAttnStages);
-        cp_async_wait<kAttnStages - 1>();
+        // Chunk c has landed for every thread after this barrier, and every warp has finished the previous
+        // chunk's P V: the other slot may be refilled.  (Three barriers per chunk; requesting the next chunk
+        // before the wait instead would need a fourth one at the end of the iteration.)
+        cp_async_wait<0>();
         __syncthreads();
+        load_chunk(c + 1, (c - c_begin + 1) % kAttnStages);
 
-        // S = Q K^T for this warp's 16 rows and 8 keys
+        // S^T = K Q^T for this warp's 16 keys, summed over its 64 dims
         {
-            float s_acc[4] = {0.f, 0.f, 0.f, 0.f};
+            float s_acc[4][4];
 #pragma unroll
-            for (int ks = 0; ks < 16; ++ks) {
-                uint32_t bfr[2], afr[4];
-                ldmatrix_x2(bfr, &sm.k[buf][wq * 8 + (lane & 7)][ks * 16 + ((lane >> 3) & 1) * 8]);
-                ldmatrix_x4(afr, &sm.q[mt * 16 + (lane & 15)][ks * 16 + (lane >> 4) * 8]);
-                mma16816(s_acc, afr, bfr);
+            for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) s_acc[nt][e] = 0.f;
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks) {
+                uint32_t afr[4];
+                ldmatrix_x4(afr, &sm.k[buf][kt * 16 + (lane & 15)][kq * 64 + ks * 16 + (lane >> 4) * 8]);
+#pragma unroll
+                for (int nt = 0; nt < 4; ++nt)
+                    if (nt < ntiles) mma16816(s_acc[nt], afr, qf[ks][nt]);
             }
             const int g4 = lane >> 2, t4 = lane & 3;
-            sm.s[mt * 16 + g4][wq * 8 + t4 * 2] = s_acc[0];
-            sm.s[mt * 16 + g4][wq * 8 + t4 * 2 + 1] = s_acc[1];
-            sm.s[mt * 16 + g4 + 8][wq * 8 + t4 * 2] = s_acc[2];
-            sm.s[mt * 16 + g4 + 8][wq * 8 + t4 * 2 + 1] = s_acc[3];
+            float* sp0 = &sm.sp[kq][kt * 16 + g4][t4 * 2];
+#pragma unroll
+            for (int nt = 0; nt < 4; ++nt)
+                if (nt < ntiles) {
+                    sp0[nt * 8] = s_acc[nt][0];
+                    sp0[nt * 8 + 1] = s_acc[nt][1];
+                    sp0[8 * kAttnSpLd + nt * 8] = s_acc[nt][2];
+                    sp0[8 * kAttnSpLd + nt * 8 + 1] = s_acc[nt][3];
+                }
         }
         __syncthreads();
 
@@ -357,7 +395,8 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_split_kernel(float* part
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 const bool vis = (r < nrows) && (key0 + j < limit) && (key0 + j < total_keys);
-                sc[j] = vis ? sm.s[r][part * 4 + j] * scale : -INFINITY;
+                const int kk = part * 4 + j;
+                sc[j] = vis ? ((sm.sp[0][kk][r] + sm.sp[1][kk][r]) + (sm.sp[2][kk][r] + sm.sp[3][kk][r])) * scale : -INFINITY;
                 mx = fmaxf(mx, sc[j]);
             }
             mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
@@ -385,43 +424,56 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_split_kernel(float* part
         }
         __syncthreads();
 
-        // O = alpha * O + P V for this warp's 16 rows and 64 output dims
+        // O^T = alpha * O^T + V^T P^T for this warp's 32 output dims
         {
-            const int g4 = lane >> 2;
-            const float a0 = sm.row_alpha[mt * 16 + g4], a1 = sm.row_alpha[mt * 16 + g4 + 8];
+            const int t4 = lane & 3;
 #pragma unroll
-            for (int nt = 0; nt < 8; ++nt) {
-                o_acc[nt][0] *= a0;
-                o_acc[nt][1] *= a0;
-                o_acc[nt][2] *= a1;
-                o_acc[nt][3] *= a1;
+            for (int nt = 0; nt < 4; ++nt) {
+                const float a0 = sm.row_alpha[nt * 8 + t4 * 2], a1 = sm.row_alpha[nt * 8 + t4 * 2 + 1];
+#pragma unroll
+                for (int mi = 0; mi < 2; ++mi) {
+                    o_acc[mi][nt][0] *= a0;
+                    o_acc[mi][nt][1] *= a1;
+                    o_acc[mi][nt][2] *= a0;
+                    o_acc[mi][nt][3] *= a1;
+                }
             }
 #pragma unroll
             for (int ks = 0; ks < kAttnChunk / 16; ++ks) {
-                uint32_t afr[4];
-                ldmatrix_x4(afr, &sm.p[mt * 16 + (lane & 15)][ks * 16 + (lane >> 4) * 8]);
+                uint32_t pfr[4][2];
 #pragma unroll
-                for (int nt = 0; nt < 8; ++nt) {
-                    uint32_t bfr[2];
-                    ldmatrix_x2_trans(bfr, &sm.v[buf][ks * 16 + (lane & 15)][wq * 64 + nt * 8]);
-                    mma16816(o_acc[nt], afr, bfr);
+                for (int nt = 0; nt < 4; ++nt)
+                    if (nt < ntiles) ldmatrix_x2(pfr[nt], &sm.p[nt * 8 + (lane & 7)][ks * 16 + ((lane >> 3) & 1) * 8]);
+#pragma unroll
+                for (int mi = 0; mi < 2; ++mi) {
+                    // A = V^T: matrix j = lane >> 3 of the four 8x8 blocks is (dims + 8 (j & 1), keys + 8 (j >> 1)),
+                    // stored key-major, hence the transposing load
+                    uint32_t afr[4];
+                    const int j = lane >> 3;
+                    ldmatrix_x4_trans(afr, &sm.v[buf][ks * 16 + (j >> 1) * 8 + (lane & 7)][warp * 32 + mi * 16 + (j & 1) * 8]);
+#pragma unroll
+                    for (int nt = 0; nt < 4; ++nt)
+                        if (nt < ntiles) mma16816(o_acc[mi][nt], afr, pfr[nt]);
                 }
             }
         }
-        __syncthreads();
     }
+    cp_async_wait<0>();
 
     // write the partial: O [rows][256] fp32, (max, sum) per row
     const long long pbase = (static_cast<long long>(b) * hkv + kvh) * nsplit + split;
     float* po = part_o + pbase * (kAttnRows * 256);
     const int g4 = lane >> 2, t4 = lane & 3;
 #pragma unroll
-    for (int nt = 0; nt < 8; ++nt) {
-        const int col = wq * 64 + nt * 8 + t4 * 2;
-        const int r0 = mt * 16 + g4;
-        if (r0 < nrows) *reinterpret_cast<float2*>(po + r0 * 256 + col) = make_float2(o_acc[nt][0], o_acc[nt][1]);
-        if (r0 + 8 < nrows) *reinterpret_cast<float2*>(po + (r0 + 8) * 256 + col) = make_float2(o_acc[nt][2], o_acc[nt][3]);
-    }
+    for (int mi = 0; mi < 2; ++mi)
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int r = nt * 8 + t4 * 2 + (e & 1);
+                const int col = warp * 32 + mi * 16 + g4 + (e >> 1) * 8;
+                if (r < nrows) po[r * 256 + col] = o_acc[mi][nt][e];
+            }
     if (tid < nrows) {
         part_ml[pbase * (kAttnRows * 2) + tid * 2] = sm.row_max[tid];
         part_ml[pbase * (kAttnRows * 2) + tid * 2 + 1] = sm.row_sum[tid];
