@@ -413,7 +413,7 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
                             const uint32_t kk = gi * 8 + i;
                             const uint32_t lo = xlo + (((kk >> 2) * (NMMA * 128) + (kk & 3) * 32) >> 4);
                             const uint64_t bdesc = (static_cast<uint64_t>(desc_hi) << 32) | lo;
-                            umma_ts_f16(d_t0 + gi * 32, a_t0 + gi * 64 + i * 8, bdesc, idesc, i > 0 ? 1u : 0u);
+                            umma_ts_f16(d_t0 + (n & 1u) * 128 + gi * 32, a_t0 + gi * 64 + i * 8, bdesc, idesc, i > 0 ? 1u : 0u);
                         }
                         umma_commit(dfull0 + gi * 8);
                         // the stage's activations are no longer read once both groups' MMAs have completed
@@ -499,10 +499,13 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
         };
 
         // acc += scale * D: the accumulator tile of this warp's group, 16 columns at a time
-        auto fold = [&](const float scale) {
+        // (D alternates between two accumulator tiles, 128 columns apart, so that the tile of stage n - 1 can
+        // still be read out while the MMAs of stage n run)
+        auto fold = [&](const float scale, const uint32_t buf) {
+            const uint32_t d_tb = d_t + buf * 128;
             if constexpr (NREAD == 8) {
                 uint32_t d[8];
-                tmem_ld8(d_t, d);
+                tmem_ld8(d_tb, d);
                 tmem_wait_ld();
 #pragma unroll
                 for (int j = 0; j < 8; ++j) acc[j] = fmaf(__uint_as_float(d[j]), scale, acc[j]);
@@ -510,7 +513,7 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
 #pragma unroll
                 for (int c = 0; c < NREAD / 16; ++c) {
                     uint32_t d[16];
-                    tmem_ld16(d_t + c * 16, d);
+                    tmem_ld16(d_tb + c * 16, d);
                     tmem_wait_ld();
 #pragma unroll
                     for (int j = 0; j < 16; ++j) acc[c * 16 + j] = fmaf(__uint_as_float(d[j]), scale, acc[c * 16 + j]);
@@ -607,11 +610,12 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
                     cluster_arrive();
                     cl_steps = 1;
                 }
-                if (have_prev) fold(sc_pend);  // previous stage's accumulator, before its D buffer is reused
                 tmem_wait_st();
                 tc_fence_before_sync();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(afull);
+                // previous stage's accumulator tile, read out while the MMA warp picks up this stage
+                if (have_prev) fold(sc_pend, dfull_phase ^ 1u);
                 sc_pend = sc_cur;
                 have_prev = true;
             }
@@ -619,7 +623,7 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
             // drain the tile's last stage (n already counts it)
             if (!mbar_wait(dfull, (n - 1) & 1u, abort_flag)) { ok = false; break; }
             tc_fence_after_sync();
-            fold(sc_pend);
+            fold(sc_pend, (n - 1) & 1u);
 
             if (tid == 0) stamp(p, 3);
             // ---------------------------------------------------------------- tile epilogue
