@@ -594,13 +594,11 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
                 for (int c = 0; c < 4; ++c) {
                     uint32_t a[16];
                     dequant_word(v[c].x, a + 0);
-                    tmem_st4(a_t + c * 16, a);
                     dequant_word(v[c].y, a + 4);
-                    tmem_st4(a_t + c * 16 + 4, a + 4);
+                    tmem_st8(a_t + c * 16, a);
                     dequant_word(v[c].z, a + 8);
-                    tmem_st4(a_t + c * 16 + 8, a + 8);
                     dequant_word(v[c].w, a + 12);
-                    tmem_st4(a_t + c * 16 + 12, a + 12);
+                    tmem_st8(a_t + c * 16 + 8, a + 8);
                 }
                 // this warp has read its weights of the stage
                 __syncwarp();
