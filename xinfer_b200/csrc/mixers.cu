@@ -276,6 +276,8 @@ __device__ __forceinline__ void mma16816(float* c, const uint32_t* a, const uint
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
 }
 
+// NT = number of 8-row tiles that hold query rows (1..4): arrays and loops are sized for it at compile time.
+template <int NT>
 __global__ void __launch_bounds__(kAttnThreads, 2) attn_split_kernel(float* part_o, float* part_ml, const __half* q,
                                                          const __half* k_cache, const __half* v_cache, const int* ctx,
                                                          int rows_per_seq, int hq, int hkv, long long max_seq,
@@ -288,7 +290,6 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_split_kernel(float* part
     const int kq = warp >> 1, kt = warp & 1;  // S^T role: dim quarter, 16-key tile
     const int G = hq / hkv;
     const int nrows = G * rows_per_seq;  // valid query rows, row = g * R + i
-    const int ntiles = (nrows + 7) >> 3;  // 8-row tiles that hold query rows
     const int ctx_b = ctx[b];
     long long total_keys = static_cast<long long>(ctx_b) + rows_per_seq;
     if (total_keys > max_seq) total_keys = max_seq;
@@ -328,11 +329,11 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_split_kernel(float* part
     };
 
     // O^T accumulators: [16-dim tile][8-row tile]; element e of a tile is (dim g4 + 8 (e >> 1), row 2 t4 + (e & 1))
-    float o_acc[2][4][4];
+    float o_acc[2][NT][4];
 #pragma unroll
     for (int mi = 0; mi < 2; ++mi)
 #pragma unroll
-        for (int nt = 0; nt < 4; ++nt)
+        for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
             for (int e = 0; e < 4; ++e) o_acc[mi][nt][e] = 0.f;
 
@@ -340,11 +341,11 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_split_kernel(float* part
 
     // this warp's slice of Q (all rows, dims [64 kq, 64 kq + 64)) as B fragments, read once
     __syncthreads();
-    uint32_t qf[4][4][2];
+    uint32_t qf[4][NT][2];
 #pragma unroll
     for (int ks = 0; ks < 4; ++ks)
 #pragma unroll
-        for (int nt = 0; nt < 4; ++nt)
+        for (int nt = 0; nt < NT; ++nt)
             ldmatrix_x2(qf[ks][nt], &sm.q[nt * 8 + (lane & 7)][kq * 64 + ks * 16 + ((lane >> 3) & 1) * 8]);
 
     for (int c = c_begin; c < c_end; ++c) {
@@ -358,9 +359,9 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_split_kernel(float* part
 
         // S^T = K Q^T for this warp's 16 keys, summed over its 64 dims
         {
-            float s_acc[4][4];
+            float s_acc[NT][4];
 #pragma unroll
-            for (int nt = 0; nt < 4; ++nt)
+            for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
                 for (int e = 0; e < 4; ++e) s_acc[nt][e] = 0.f;
 #pragma unroll
@@ -368,14 +369,14 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_split_kernel(float* part
                 uint32_t afr[4];
                 ldmatrix_x4(afr, &sm.k[buf][kt * 16 + (lane & 15)][kq * 64 + ks * 16 + (lane >> 4) * 8]);
 #pragma unroll
-                for (int nt = 0; nt < 4; ++nt)
-                    if (nt < ntiles) mma16816(s_acc[nt], afr, qf[ks][nt]);
+                for (int nt = 0; nt < NT; ++nt)
+                    mma16816(s_acc[nt], afr, qf[ks][nt]);
             }
             const int g4 = lane >> 2, t4 = lane & 3;
             float* sp0 = &sm.sp[kq][kt * 16 + g4][t4 * 2];
 #pragma unroll
-            for (int nt = 0; nt < 4; ++nt)
-                if (nt < ntiles) {
+            for (int nt = 0; nt < NT; ++nt)
+                {
                     sp0[nt * 8] = s_acc[nt][0];
                     sp0[nt * 8 + 1] = s_acc[nt][1];
                     sp0[8 * kAttnSpLd + nt * 8] = s_acc[nt][2];
@@ -428,7 +429,7 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_split_kernel(float* part
         {
             const int t4 = lane & 3;
 #pragma unroll
-            for (int nt = 0; nt < 4; ++nt) {
+            for (int nt = 0; nt < NT; ++nt) {
                 const float a0 = sm.row_alpha[nt * 8 + t4 * 2], a1 = sm.row_alpha[nt * 8 + t4 * 2 + 1];
 #pragma unroll
                 for (int mi = 0; mi < 2; ++mi) {
@@ -440,10 +441,10 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_split_kernel(float* part
             }
 #pragma unroll
             for (int ks = 0; ks < kAttnChunk / 16; ++ks) {
-                uint32_t pfr[4][2];
+                uint32_t pfr[NT][2];
 #pragma unroll
-                for (int nt = 0; nt < 4; ++nt)
-                    if (nt < ntiles) ldmatrix_x2(pfr[nt], &sm.p[nt * 8 + (lane & 7)][ks * 16 + ((lane >> 3) & 1) * 8]);
+                for (int nt = 0; nt < NT; ++nt)
+                    ldmatrix_x2(pfr[nt], &sm.p[nt * 8 + (lane & 7)][ks * 16 + ((lane >> 3) & 1) * 8]);
 #pragma unroll
                 for (int mi = 0; mi < 2; ++mi) {
                     // A = V^T: matrix j = lane >> 3 of the four 8x8 blocks is (dims + 8 (j & 1), keys + 8 (j >> 1)),
@@ -452,8 +453,8 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_split_kernel(float* part
                     const int j = lane >> 3;
                     ldmatrix_x4_trans(afr, &sm.v[buf][ks * 16 + (j >> 1) * 8 + (lane & 7)][warp * 32 + mi * 16 + (j & 1) * 8]);
 #pragma unroll
-                    for (int nt = 0; nt < 4; ++nt)
-                        if (nt < ntiles) mma16816(o_acc[mi][nt], afr, pfr[nt]);
+                    for (int nt = 0; nt < NT; ++nt)
+                        mma16816(o_acc[mi][nt], afr, pfr[nt]);
                 }
             }
         }
@@ -467,7 +468,7 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_split_kernel(float* part
 #pragma unroll
     for (int mi = 0; mi < 2; ++mi)
 #pragma unroll
-        for (int nt = 0; nt < 4; ++nt)
+        for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const int r = nt * 8 + t4 * 2 + (e & 1);
@@ -780,16 +781,24 @@ int attn_decode(cudaStream_t s, __half* out, const __half* q, const __half* q_ga
     if (hq % hkv != 0 || (hq / hkv) * rows_per_seq > kAttnRows) return -2;
     static bool configured = false;
     if (!configured) {
-        if (cudaFuncSetAttribute(attn_split_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 static_cast<int>(sizeof(AttnSmem))) != cudaSuccess)
+        const int bytes = static_cast<int>(sizeof(AttnSmem));
+        if (cudaFuncSetAttribute(attn_split_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess ||
+            cudaFuncSetAttribute(attn_split_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess ||
+            cudaFuncSetAttribute(attn_split_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess ||
+            cudaFuncSetAttribute(attn_split_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess)
             return -1;
         configured = true;
     }
     float* part_o = scratch;
     float* part_ml = scratch + static_cast<size_t>(batch) * hkv * nsplit * (kAttnRows * 256);
     dim3 grid(nsplit, hkv, batch);
-    launch_pdl(attn_split_kernel, dim3(grid), dim3(kAttnThreads), sizeof(AttnSmem), s, part_o, part_ml, q, k_cache, v_cache, ctx, rows_per_seq, hq,
-                                                          hkv, max_seq, 1.0f / sqrtf(256.0f));
+    const float scale = 1.0f / sqrtf(256.0f);
+    switch (((hq / hkv) * rows_per_seq + 7) / 8) {
+        case 1: launch_pdl(attn_split_kernel<1>, dim3(grid), dim3(kAttnThreads), sizeof(AttnSmem), s, part_o, part_ml, q, k_cache, v_cache, ctx, rows_per_seq, hq, hkv, max_seq, scale); break;
+        case 2: launch_pdl(attn_split_kernel<2>, dim3(grid), dim3(kAttnThreads), sizeof(AttnSmem), s, part_o, part_ml, q, k_cache, v_cache, ctx, rows_per_seq, hq, hkv, max_seq, scale); break;
+        case 3: launch_pdl(attn_split_kernel<3>, dim3(grid), dim3(kAttnThreads), sizeof(AttnSmem), s, part_o, part_ml, q, k_cache, v_cache, ctx, rows_per_seq, hq, hkv, max_seq, scale); break;
+        default: launch_pdl(attn_split_kernel<4>, dim3(grid), dim3(kAttnThreads), sizeof(AttnSmem), s, part_o, part_ml, q, k_cache, v_cache, ctx, rows_per_seq, hq, hkv, max_seq, scale); break;
+    }
     dim3 grid2((hq / hkv) * rows_per_seq, hkv, batch);
     launch_pdl(attn_combine_kernel, dim3(grid2), dim3(256), 0, s, out, part_o, part_ml, q_gate, nsplit, rows_per_seq, hq, hkv);
     return XB_LAUNCH_OK();
