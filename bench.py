@@ -475,6 +475,131 @@ def cpu_step_sample(batch, k, budget_s=15.0):
             "extrapolated_step_s": step_s}
 
 
+def cpu_gemv_and_acceptance(budget_s=6.0):
+    """The other two CPU figures beside the step: the config-0 GEMV at full size (the oracle's port of
+    linear_int4_naive, OpenMP over N, median of >= 5 runs) and the acceptance oracle (literal restatement of
+    speculative_accept_reject, one thread, as the reference runs it on the host) on the acceptance configuration
+    (batch 8, k = 3, vocab 151936, stochastic rule at T = 0.7)."""
+    import oracle
+    K, N = LAYER_SHAPES["gate_up"]
+    X, W, S = synth(1, K, N, 0)
+    Xf = X.astype(np.float32)
+    oracle.linear_int4_naive_f32(Xf, W, S)
+    times = []
+    t_end = time.perf_counter() + budget_s
+    while len(times) < 5 or (time.perf_counter() < t_end and len(times) < 40):
+        t0 = time.perf_counter()
+        oracle.linear_int4_naive_f32(Xf, W, S)
+        times.append(time.perf_counter() - t0)
+    med = statistics.median(times)
+    B, k, V = 8, 3, 151936
+    rng = np.random.default_rng(0)
+    target = rng.normal(0, 3, size=(B, k, V)).astype(np.float32)
+    toks = rng.integers(0, V, size=(B, k)).astype(np.int64)
+    probs = np.full((B, k), 1e-5, np.float32)
+    uni = rng.random(size=(B, k)).astype(np.float32)
+    acc = []
+    for _ in range(5):
+        t0 = time.perf_counter()
+        for b in range(B):
+            oracle.speculative_accept_reject(toks[b], target[b], probs[b], uni[b], inv_temperature=1.0 / 0.7)
+        acc.append(time.perf_counter() - t0)
+    return {"gemv": {"value": alg_bytes(1, K, N) / med / 1e9, "unit": "GB/s", "us": med * 1e6, "cores": oracle.num_threads(),
+                     "sample": f"{len(times)} runs of the full M=1 K={K} N={N} GEMV, median"},
+            "acceptance": {"us": statistics.median(acc) * 1e6, "cores": 1,
+                           "sample": f"batch {B} x k {k} x vocab {V}, stochastic rule, 5 runs, median"}}
+
+
+def gemv_object(ops, torch, tp=None, dist=None, shape="gate_up", M=1, launches=64, reps=5):
+    """INT4 GEMV HBM GB/s on the shape the metric is quoted on (M = 1, 5120 -> 17408): `launches` launches in one
+    CUDA graph rotating over distinct weight buffers (> 2x L2 in total), event-timed.  With a tensor-parallel group
+    every rank streams its 1/g of the rows and stores its slice into every rank's output from the kernel's
+    epilogue; the figure is then whole-projection bytes over the slowest rank's time."""
+    K, N = LAYER_SHAPES[shape]
+    world = 1 if tp is None else tp.world
+    rank = 0 if tp is None else tp.rank
+    nl = N // world
+    _, W, S = synth(M, K, N, 0)
+    Wl, Sl = W[rank * nl:(rank + 1) * nl], S[rank * nl:(rank + 1) * nl]
+    w_bytes = Wl.nbytes + Sl.nbytes
+    n_buf = max(2, -(-2 * L2_BYTES // w_bytes) + 1)
+    Ws = [torch.from_numpy(np.roll(Wl, i, axis=0)).cuda() for i in range(n_buf)]
+    Ss = [torch.from_numpy(np.roll(Sl, i, axis=0)).cuda() for i in range(n_buf)]
+    X = torch.randn((M, K), device="cuda").half()
+    if tp is None:
+        Y = torch.empty((M, N), dtype=torch.float16, device="cuda")
+        def launch(j):
+            ops.linear_int4(Y, X, Ws[j], Ss[j], None, M, N, K)
+    else:
+        y_off = tp.alloc(M * N * 2)
+        def launch(j):
+            tp.linear(y_off, N, rank * nl, X, Ws[j], Ss[j], None, M, nl, K)
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        for i in range(2):
+            launch(i % n_buf)
+        stream.synchronize()
+        if dist is not None:
+            dist.barrier()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream):
+            for i in range(launches):
+                launch(i % n_buf)
+        for _ in range(3):
+            g.replay()
+        stream.synchronize()
+        if dist is not None:
+            dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(reps):
+            g.replay()
+        e1.record(stream)
+        stream.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / (reps * launches)
+    if dist is not None:
+        t = torch.tensor([us], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        us = float(t.item())
+    gbs = alg_bytes(M, K, N) / us / 1e3
+    peak, kind = measured_peak()
+    return {"shape": f"M={M} K={K} N={N}", "us": us, "value": gbs, "unit": "GB/s", "frac_of_measured": gbs / (peak * world),
+            "frac_of_nominal_8000": gbs / (8000.0 * world), "peak_kind": f"of {kind}" + (f" x {world} GPUs" if world > 1 else ""),
+            "parallelism": "one GPU" if world == 1 else f"N-split over {world} GPUs, slices stored into every rank's output "
+                           "by the GEMM epilogue (peer stores + flags)",
+            "l2": f"rotates over {n_buf} distinct weight buffers per GPU"}
+
+
+def acceptance_object(ops, torch, launches=20, reps=5):
+    """Device time of the acceptance configuration: batch 8, k = 3, vocab 151936 fp32 logits, stochastic rule at
+    T = 0.7 with device-resident draft probabilities and uniforms; one call = partials kernel + finish kernel."""
+    B, k, V = 8, 3, 151936
+    logits = [torch.randn((B, k, V), device="cuda") * 3 for _ in range(4)]   # 58 MB in rotation (L2 holds it: noted)
+    toks = torch.randint(0, V, (B, k), device="cuda")
+    probs = torch.full((B, k), 1e-5, device="cuda")
+    uni = torch.rand((B, k), device="cuda")
+    out = torch.zeros(B * ops.ACCEPT_RECORD_BYTES, dtype=torch.uint8, device="cuda")
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        ops.speculative_accept_reject_batched(toks, logits[0], probs, uni, out, inv_temperature=1.0 / 0.7)
+        stream.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream):
+            for i in range(launches):
+                ops.speculative_accept_reject_batched(toks, logits[i % 4], probs, uni, out, inv_temperature=1.0 / 0.7)
+        g.replay()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(reps):
+            g.replay()
+        e1.record(stream)
+        stream.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / (reps * launches)
+    bytes_ = B * k * V * 4
+    return {"us": us, "logit_bytes": bytes_, "gbs": bytes_ / us / 1e3,
+            "config": f"batch {B}, k {k}, vocab {V}, stochastic rule T=0.7; logits rotate over 4 buffers (58 MB, L2-resident)"}
+
+
 def step_bench(args):
     import torch
     import torch.distributed as dist
@@ -490,10 +615,21 @@ def step_bench(args):
     from xinfer_b200.spec import Shape, SpecDecoder
     assert lib().xinfer_b200_init(local_rank) == 0, lib().xinfer_last_cuda_error()
 
+    from xinfer_b200.tp import TpGroup
     shape = Shape(num_hidden_layers=args.layers)
     B, k, ctx0 = args.batch, args.k, args.context
-    dec = SpecDecoder(shape, batch=B, k=k, max_seq=ctx0 + 1024, seed=rank)
-    dec.reset(ctx0, seed=rank)
+    # More than one GPU: the SAME job (one batch-B step) with every projection N-split over the ranks and the
+    # per-sequence state split by sequence; --parallel replicas runs N independent copies instead.
+    use_tp = world > 1 and args.parallel == "tp"
+    tp = None
+    if use_tp:
+        tp = TpGroup(SpecDecoder.exchange_bytes(shape, B, k, world) + (8 << 20))
+        dec = SpecDecoder(shape, batch=B, k=k, max_seq=ctx0 + 1024, seed=0, tp=tp)
+        dec.reset(ctx0, seed=0)
+        dist.barrier()
+    else:
+        dec = SpecDecoder(shape, batch=B, k=k, max_seq=ctx0 + 1024, seed=rank)
+        dec.reset(ctx0, seed=rank)
     stream = torch.cuda.Stream()
     steps, warm = args.steps, max(3, args.warmup)
     with torch.cuda.stream(stream):
@@ -550,23 +686,61 @@ def step_bench(args):
         e2e_s = time.perf_counter() - t0
         e2e_tokens = int(dec.tensor(-1, "ctx", np.int32).astype(np.int64).sum() - ctx_a)
     assert ops.device_status(local_rank) == 0
-    (ms, e2e_s), (tokens, e2e_tokens) = reduce_over_ranks([ms, e2e_s], [tokens, e2e_tokens], device="cuda")
+    if tp is not None:
+        assert tp.status() == 0, "an inter-rank exchange wait ran out"
+    exchanges = dec.info(6)
+    if use_tp:
+        # one job: every rank holds the same token counts; the job is as slow as its slowest rank
+        (ms, e2e_s, lin_ms), _ = reduce_over_ranks([ms, e2e_s, lin_ms], [0], device="cuda")
+    else:
+        (ms, e2e_s), (tokens, e2e_tokens) = reduce_over_ranks([ms, e2e_s], [tokens, e2e_tokens], device="cuda")
     tokens, e2e_tokens = int(tokens), int(e2e_tokens)
     value = tokens / (ms * 1e-3)
+    # the other half of the metric, and the acceptance kernel, on the same GPUs
+    gemv = gemv_object(ops, torch, tp=tp, dist=dist if world > 1 and use_tp else None) if (world == 1 or use_tp) else None
+    acceptance = acceptance_object(ops, torch) if rank == 0 else None
+    replicas = None
+    if use_tp and args.with_replicas:
+        # the same GPUs as N independent copies of the job (weak scaling), for comparison
+        dec.close()
+        dec = SpecDecoder(shape, batch=B, k=k, max_seq=ctx0 + 1024, seed=rank)
+        dec.reset(ctx0, seed=rank)
+        with torch.cuda.stream(stream):
+            dec.capture(stream)
+            for _ in range(warm):
+                dec.step()
+            stream.synchronize()
+            c0 = dec.tensor(-1, "ctx", np.int32).astype(np.int64).sum()
+            dist.barrier()
+            r0, r1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            r0.record(stream)
+            for _ in range(steps):
+                dec.step()
+            r1.record(stream)
+            torch.cuda.synchronize()
+            rtok = int(dec.tensor(-1, "ctx", np.int32).astype(np.int64).sum() - c0)
+        (rms,), (rtok,) = reduce_over_ranks([r0.elapsed_time(r1)], [rtok], device="cuda")
+        replicas = {"value": rtok / (rms * 1e-3), "unit": "tok/s", "ms_per_step": rms / steps, "scaling": "weak",
+                    "note": f"{world} independent batch-{B} jobs, one per GPU, no inter-GPU traffic"}
     peak, peak_kind = measured_peak()
     lin_gbs = lin_bytes / (lin_ms * 1e-3) / 1e9
     line = {
         "metric": "accepted_tok_per_s", "value": value, "unit": "tok/s", "n_gpus": world, "steps": steps, "warmup": warm,
-        "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "strong" if use_tp else "weak", "vs_baseline": None,
         "dtype": "int4 weights x fp16 activations, fp32 accumulate", "data": "synthetic",
         "config": {"workload": f"27B-shape hybrid ({args.layers} layers: Gated-DeltaNet + full attention, hidden 5120, "
                                f"FFN 17408, vocab 151936, INT4-G128), MTP k={k}, batch {B}, context {ctx0}, greedy; "
                                f"one step = {k} MTP draft passes + one {B * (k + 1)}-row verify pass + acceptance + "
                                f"commit, replayed as one CUDA graph",
                    "layers": args.layers, "batch": B, "k": k, "context": ctx0,
-                   "parallelism": f"{world} independent replica(s), one per GPU",
+                   "parallelism": (f"tp{world}: every projection N-split over {world} GPUs, KV cache and recurrent state split "
+                                   f"by sequence, LM head split by vocabulary") if use_tp
+                                  else f"{world} independent replica(s), one per GPU",
+                   "collective": (f"{exchanges} exchanges per step inside the CUDA graph: the GEMM epilogue stores its slice "
+                                  "into every rank's activation buffer with plain peer stores over NVLink, one flag per "
+                                  "(receiver, sender), bounded waits; no NCCL on the data path") if use_tp else "none",
                    "l2": "inputs larger than L2: every step streams %.1f GB of weights" % (dec.info(0) / 1e9),
-                   "accepted_per_step_per_seq": tokens / max(1, steps * B * world),
+                   "accepted_per_step_per_seq": tokens / max(1, steps * B * (1 if use_tp else world)),
                    "note": "random-init weights: the draft head and the target agree only by chance, so almost "
                            "every step emits the bonus token alone"},
         "roofline": {"bound": "hbm", "achieved": lin_gbs, "peak": peak, "unit": "GB/s", "frac": lin_gbs / peak,
@@ -582,11 +756,24 @@ def step_bench(args):
                 "d2h_bytes_per_step": B * (k + 1) * 8 + B * 4, "ms_per_step": e2e_s / e2e_steps * 1e3},
         "gpu_launches": launches * steps, "clocks": clocks,
     }
+    if clocks.get("sm_mhz"):
+        # clock-normalised reading: the same step at another SM clock takes about this many ms x MHz / that clock
+        line["ms_per_step_x_sm_mhz"] = ms / steps * clocks["sm_mhz"]
+    if gemv is not None:
+        line["gemv"] = gemv
+    if acceptance is not None:
+        line["acceptance"] = acceptance
+    if replicas is not None:
+        line["replicas"] = replicas
     if rank == 0:
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_step_sample(B, k)
+            line["cpu_baseline"].update(cpu_gemv_and_acceptance())
         print(json.dumps(line), flush=True)
     dec.close()
+    if tp is not None:
+        dist.barrier()
+        tp.close()
     if world > 1:
         dist.destroy_process_group()
 
@@ -611,7 +798,7 @@ def step_reference_arm(args):
                        "note": "CPU arm: the oracle's port of the reference's linear_int4_naive on all host cores over a "
                                "bounded row sample of every projection shape; the step time is extrapolated by weight "
                                "bytes (the linears are 88 % of the reference's own step)"},
-            "cpu_baseline": dict(res[0], value=val),
+            "cpu_baseline": dict(res[0], value=val, **cpu_gemv_and_acceptance()),
             "e2e": {"value": val, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line), flush=True)
 
@@ -631,6 +818,9 @@ def main():
     ap.add_argument("--m", "--rows", dest="m", type=int, default=1)  # activation rows M (--rows: torchrun parses --m itself)
     ap.add_argument("--launches", type=int, default=64)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--parallel", default="tp", choices=["tp", "replicas"],
+                    help="with more than one GPU: the one job N-split over the GPUs (default), or N independent copies")
+    ap.add_argument("--with-replicas", action="store_true", help="tp runs also measure the replica form on the same GPUs")
     args = ap.parse_args()
     if args.impl == "reference":
         # torchrun exports OMP_NUM_THREADS=1 to its workers; the CPU arm is meant to use every host thread,

@@ -41,17 +41,23 @@ enum {
  * Called implicitly by the first compute call on a device; call it explicitly before any stream
  * capture, because it allocates.  No counterpart in the reference (SYCL USM is allocated per call there). */
 XINFER_EXPORT int xinfer_b200_init(int device);
-/* 0 when no bounded device-side wait has given up on `device` since the last call, else the code. */
+XINFER_EXPORT int xinfer_b200_init_current(void); /* the same for the calling thread's current device */
+/* 0 when no bounded device-side wait has given up on `device` since the last call, else
+ * XINFER_ERR_DEVICE_TIMEOUT.  Covers every entry point, xinfer_linear_int4_f16f16_noalloc included; reading
+ * clears the record.  The output of a launch that reported a timeout is undefined. */
 XINFER_EXPORT int xinfer_device_status(int device);
 XINFER_EXPORT const char* xinfer_last_cuda_error(void);
 XINFER_EXPORT const char* xinfer_b200_version(void);
 /* Which kernel family the last linear call on this thread used: 0 none, 1 tcgen05, 2 CUDA cores. */
 XINFER_EXPORT int xinfer_last_linear_path(void);
-/* Debug aid: when non-NULL, every CTA of the tcgen05 linear kernel writes eight %globaltimer stamps
- * (start, set-up done, first tile landed, main loop done, epilogue done, teardown) to dev_ptr[cta*8+i]. */
-XINFER_EXPORT void xinfer_debug_set_trace(void* dev_ptr);
-/* Force a kernel family for the linear entry points: 0 = automatic, 1 = tcgen05 when eligible
- * (default for fp16 activations), 2 = CUDA cores only.  For measurements and tests. */
+/* Test hook for the bounded device-side waits of the tcgen05 linear kernel.  limit_clocks: SM clocks after
+ * which a wait gives up (<= 0 restores the default, about one second).  withhold_x_from_stage >= 0: the
+ * kernel's loader never requests the activation stages from that index on, so the waits for them run out,
+ * the kernel returns through its abort path and xinfer_device_status reports the timeout (-1: off).
+ * Process-wide; applies to launches enqueued afterwards.  No counterpart in the reference. */
+XINFER_EXPORT void xinfer_debug_set_wait_hooks(int64_t limit_clocks, int withhold_x_from_stage);
+/* Force a kernel family for the linear entry points on the current device: 0 = automatic, 1 = tcgen05 when
+ * eligible (default for fp16 activations), 2 = CUDA cores only.  For measurements and tests. */
 XINFER_EXPORT void xinfer_set_linear_path(int path);
 
 /* ---- INT4-G128-SYM W4A16 linear:  Y[M,N] = X[M,K] * W^T + bias ---------------------------------
@@ -111,10 +117,13 @@ XINFER_EXPORT int xinfer_linear_int4_f16f16_ld(xinfer_stream_t s, void* Y_f16, i
  * in the reference.
  *   - Limits: 1 <= M <= 32, K a multiple of 128, group_size 128, 16-byte aligned X and W, N <= 2,097,152,
  *     at most 160 SMs.  Anything else returns XINFER_ERR_INVALID_ARGUMENT (there is no fallback path).
- *   - The first call on a device resolves the array's device address and configures the kernel; make that
- *     first call before any stream capture.  Later calls only enqueue work on `s`.
+ *   - The first call on a device resolves the array's device address and configures the kernel (all three
+ *     row-count variants); make that first call before any stream capture.  Later calls only enqueue work
+ *     on `s`.
  *   - Every call uses the same array.  Counters are cleared at the start of each call, on `s`; two calls
- *     that overlap on the GPU (different streams, or graphs replayed concurrently) race on it. */
+ *     that overlap on the GPU (different streams, or graphs replayed concurrently) race on it.
+ *   - A bounded wait that gives up inside this entry point is reported by xinfer_device_status(), like
+ *     any other launch's; the record is kept across later calls until it has been read. */
 XINFER_EXPORT int xinfer_linear_int4_f16f16_noalloc(xinfer_stream_t s, void* Y_f16, const void* X_f16,
                                                     const uint8_t* W_int4, const void* scales_f16, const float* bias,
                                                     int64_t M, int64_t N, int64_t K, int group_size);
@@ -124,7 +133,8 @@ XINFER_EXPORT int xinfer_linear_int4_f16f16_noalloc(xinfer_stream_t s, void* Y_f
  * start of every later round.  Each launch of a recorded round then also asks the L2 cache for the first weight
  * tiles of the launch that follows it, so that launch starts from L2 instead of HBM.  The plan is a hint: results
  * are unchanged, and a call that does not match the recorded sequence switches the hints off until the next
- * recording.  One plan per process; clear() drops it (call it before freeing the recorded weights).
+ * recording.  These four calls act on the process-wide plan (a decoder object keeps a plan of its own);
+ * clear() drops it (call it before freeing the recorded weights).
  * No counterpart in the reference (its queue has no cross-kernel prefetch). */
 XINFER_EXPORT void xinfer_linear_plan_record_begin(void);
 XINFER_EXPORT void xinfer_linear_plan_record_end(void);
@@ -226,7 +236,9 @@ XINFER_EXPORT void xinfer_spec_decoder_destroy(xinfer_spec_decoder* d);
 /* Synthetic context of `context_len` positions per sequence: random KV cache and recurrent state. */
 XINFER_EXPORT int xinfer_spec_decoder_reset(xinfer_spec_decoder* d, int64_t context_len, uint64_t seed);
 XINFER_EXPORT int xinfer_spec_decoder_set_tokens(xinfer_spec_decoder* d, const int64_t* cur_tokens_host);
-/* Enqueues one speculative step (replays the captured graph when there is one). */
+/* Enqueues one speculative step (replays the captured graph when there is one).  Returns
+ * XINFER_ERR_INVALID_ARGUMENT, enqueuing nothing, when another step could run past max_seq (the reference's
+ * KVCache throws when it is full). */
 XINFER_EXPORT int xinfer_spec_decoder_step(xinfer_spec_decoder* d, xinfer_stream_t stream);
 XINFER_EXPORT int xinfer_spec_decoder_capture(xinfer_spec_decoder* d, xinfer_stream_t stream);
 /* Synchronous: emitted_host [batch][k+1] (accepted drafts, then the bonus token, then -1), counts_host [batch]. */
@@ -238,10 +250,101 @@ XINFER_EXPORT int xinfer_spec_decoder_override_drafts(xinfer_spec_decoder* d, co
 /* Measurement entry: enqueues only the W4A16 linear launches of one step (same order, same weights). */
 XINFER_EXPORT int xinfer_spec_decoder_enqueue_linears(xinfer_spec_decoder* d, xinfer_stream_t stream);
 /* what: 0 weight bytes, 1 state bytes, 2 kernel launches per step, 3 graph captured,
- * 4 algorithmic bytes of the step's linear launches, 5 number of linear launches per step */
+ * 4 algorithmic bytes of the step's linear launches (this rank's), 5 number of linear launches per step,
+ * 6 inter-rank exchanges per step, 7 bytes of the decoder's one device block */
 XINFER_EXPORT int64_t xinfer_spec_decoder_info(const xinfer_spec_decoder* d, int what);
 XINFER_EXPORT void* xinfer_spec_decoder_tensor(xinfer_spec_decoder* d, int layer, const char* name, int64_t* bytes);
 XINFER_EXPORT const char* xinfer_spec_decoder_error(const xinfer_spec_decoder* d);
+
+/* ---- per-layer mixer ops (fp16 overloads of the reference's ops; head_dim 256) -----------------------
+ * The kernels the speculative step uses between its projections, exported one by one so that each can be
+ * checked against the reference's own op tests.  They keep the reference's fp16 rounding points; reductions
+ * are fp32.  The stateful ones allocate a small per-device scratch on their first call (make it before any
+ * stream capture). */
+/* out = in * rsqrt(mean(in^2) + eps) * weight.  Replaces ops::rmsnorm (half), src/ops/rmsnorm.h:17-23. */
+XINFER_EXPORT int xinfer_rmsnorm_f16(xinfer_stream_t s, void* out_f16, const void* in_f16, const float* weight,
+                                     int64_t num_tokens, int64_t hidden_size, float eps);
+/* residual += in (fp16); out = rmsnorm(residual).  Replaces ops::rmsnorm_residual (half), rmsnorm.h:35-42. */
+XINFER_EXPORT int xinfer_rmsnorm_residual_f16(xinfer_stream_t s, void* out_f16, void* residual_f16, const void* in_f16,
+                                              const float* weight, int64_t num_tokens, int64_t hidden_size, float eps);
+/* In-place partial rotary embedding of Q [tokens][q_heads][256] and K [tokens][kv_heads][256]: pairs
+ * (p, p + rotary_dim/2) of the first rotary_dim dims, angle = position * theta^(-2p/rotary_dim); positions is a
+ * DEVICE array [tokens].  Replaces ops::rope (half), src/ops/rope.h:25-34. */
+XINFER_EXPORT int xinfer_rope_f16(xinfer_stream_t s, void* q_f16, void* k_f16, int64_t num_tokens, int64_t num_q_heads,
+                                  int64_t num_kv_heads, int64_t head_dim, const int64_t* positions_dev, float theta,
+                                  int64_t rotary_dim);
+/* Copies K, V rows into the fp16 cache [pos][kv_head][256] at start_pos...  Rows that do not fit a bounded
+ * cache (max_seq_len > 0) are an error, as in the reference.  Replaces ops::attention_write_kv_cache (half),
+ * src/ops/attention.h:49-58. */
+XINFER_EXPORT int xinfer_attention_write_kv_cache_f16(xinfer_stream_t s, void* k_cache_f16, void* v_cache_f16,
+                                                      const void* K_in_f16, const void* V_in_f16, int64_t start_pos,
+                                                      int64_t num_tokens, int64_t num_kv_heads, int64_t head_dim,
+                                                      int64_t max_seq_len);
+/* Causal GQA attention of num_q_tokens query rows at positions start_pos... over the cache: row i sees keys
+ * 0 .. start_pos + i.  scale <= 0 means 1/sqrt(head_dim).  Replaces ops::sdpa_causal_cached (half),
+ * src/ops/attention.h:102-113 (also the body of sdpa_causal_verify). */
+XINFER_EXPORT int xinfer_sdpa_causal_cached_f16(xinfer_stream_t s, void* out_f16, const void* Q_f16,
+                                                const void* k_cache_f16, const void* v_cache_f16, int64_t start_pos,
+                                                int64_t num_q_tokens, int64_t num_q_heads, int64_t num_kv_heads,
+                                                int64_t head_dim, float scale, int64_t max_seq_len);
+/* Depthwise causal conv (width 4) + SiLU over [seq_len][channels]; conv_state [3][channels] fp32 holds the last
+ * three inputs and is updated by the call (NULL: zeros for the past, nothing kept).  Replaces
+ * targets::qwen3_8::causal_conv1d_silu (half), src/targets/qwen3_8/linear_attn.h:15-21. */
+XINFER_EXPORT int xinfer_causal_conv1d_silu_f16(xinfer_stream_t s, void* out_f16, const void* in_f16, const float* conv_w,
+                                                int64_t seq_len, float* conv_state, int64_t num_channels);
+/* Gated delta rule + gated RMSNorm, head dims 128, state [v_heads][128][128] fp32 updated by the call.
+ * Replaces targets::qwen3_8::recurrent_gated_delta_net (half), src/targets/qwen3_8/linear_attn.h:41-58. */
+XINFER_EXPORT int xinfer_recurrent_gated_delta_net_f16(xinfer_stream_t s, void* out_f16, const void* qkv_f16,
+                                                       const void* z_f16, const void* b_f16, const void* a_f16,
+                                                       const float* A_log, const float* dt_bias, const float* norm_weight,
+                                                       float* state_buffer, int64_t seq_len, int zero_state,
+                                                       int64_t num_v_heads, int64_t num_k_heads);
+
+/* ---- N-split tensor parallelism over the GPUs of one box (one process per GPU) -------------------------
+ * No counterpart in the reference (it has no multi-GPU code).  Rank r holds the output rows
+ * [r N/g, (r+1) N/g) of every split projection, computes that slice for all activation rows and stores it
+ * into every rank's activation buffer straight from the GEMM epilogue (plain peer stores over NVLink), then
+ * one flag per (receiver, sender); device-side waits are bounded and report through xinfer_tp_status.
+ *
+ * Every rank owns an exchange region of `bytes` (the same on all ranks).  Set-up: create -> handle ->
+ * all-gather the xinfer_tp_handle_bytes()-sized blobs among the ranks by any means -> connect. */
+typedef struct xinfer_tp xinfer_tp;
+XINFER_EXPORT int xinfer_tp_create(int rank, int world, size_t bytes, xinfer_tp** out);
+XINFER_EXPORT void xinfer_tp_destroy(xinfer_tp* tp);
+XINFER_EXPORT size_t xinfer_tp_handle_bytes(void);
+XINFER_EXPORT int xinfer_tp_handle(xinfer_tp* tp, void* out_blob);
+/* all_handles: world blobs in rank order (this rank's own is ignored). */
+XINFER_EXPORT int xinfer_tp_connect(xinfer_tp* tp, const void* all_handles);
+XINFER_EXPORT int xinfer_tp_rank(const xinfer_tp* tp);
+XINFER_EXPORT int xinfer_tp_world(const xinfer_tp* tp);
+/* Carves `bytes` out of the region (256-byte aligned).  Ranks that allocate in the same order get the same
+ * offsets, and an offset names the same logical buffer on every rank. */
+XINFER_EXPORT int xinfer_tp_alloc(xinfer_tp* tp, size_t bytes, size_t* offset_out);
+XINFER_EXPORT void* xinfer_tp_ptr(xinfer_tp* tp, size_t offset);
+/* Y[M][ldy] lives at y_offset of every rank's region; this rank computes the columns [col0, col0 + N_local)
+ * from its slice of W / scales and stores them into EVERY rank's Y (rows_per_rank == 0), or row j only into
+ * rank j / rows_per_rank's Y (the rank that owns the row's sequence).  When the launch completes on a
+ * rank, every rank's columns have arrived there.  Shapes the tcgen05 kernel does not take are refused. */
+XINFER_EXPORT int xinfer_tp_linear_int4_f16f16(xinfer_tp* tp, xinfer_stream_t s, size_t y_offset, int64_t ldy,
+                                               int64_t col0, const void* X_f16, const uint8_t* W_int4,
+                                               const void* scales_f16, const float* bias, int64_t M, int64_t N_local,
+                                               int64_t K, int group_size, int rows_per_rank);
+/* Copies [offset, offset + bytes) of this rank's region to the same place on every other rank, then the same
+ * handshake (an all-gather when every rank pushes its own part of a buffer).  16-byte granularity. */
+XINFER_EXPORT int xinfer_tp_push(xinfer_tp* tp, xinfer_stream_t s, size_t offset, size_t bytes);
+XINFER_EXPORT int xinfer_tp_barrier(xinfer_tp* tp, xinfer_stream_t s);
+/* Clock limit of the exchange waits (<= 0: the default, about one second), and whether one has run out
+ * since the last call (XINFER_ERR_DEVICE_TIMEOUT; the data of that exchange is incomplete). */
+XINFER_EXPORT void xinfer_tp_set_wait_limit(xinfer_tp* tp, int64_t limit_clocks);
+XINFER_EXPORT int xinfer_tp_status(xinfer_tp* tp);
+
+/* The speculative decoder over `tp` (connected): projections N-split, KV caches and recurrent state split by
+ * sequence (batch % world == 0), LM head split by vocabulary with (max, index) partials exchanged, the whole
+ * step one CUDA graph per rank.  Every rank must create its decoder with the same arguments and run the
+ * same calls.  tp == NULL or world 1: the single-GPU decoder.  exchange_bytes: region size it needs. */
+XINFER_EXPORT size_t xinfer_spec_decoder_exchange_bytes(const xinfer_model_config* cfg, int batch, int k, int world);
+XINFER_EXPORT int xinfer_spec_decoder_create_tp(const xinfer_model_config* cfg, int batch, int k, int64_t max_seq,
+                                                uint64_t seed, xinfer_tp* tp, xinfer_spec_decoder** out);
 
 /* ---- device arena ------------------------------------------------------------------------------
  * cudaMalloc-backed bump allocator.  Replaces xinfer::core::DeviceArena, src/core/arena.h:14-66
@@ -259,11 +362,15 @@ XINFER_EXPORT size_t xinfer_arena_capacity(const xinfer_arena* a);
 XINFER_EXPORT size_t xinfer_arena_allocated_bytes(const xinfer_arena* a);
 XINFER_EXPORT size_t xinfer_arena_remaining_bytes(const xinfer_arena* a);
 XINFER_EXPORT size_t xinfer_arena_peak_allocated_bytes(const xinfer_arena* a);
-XINFER_EXPORT void* xinfer_arena_base_ptr(xinfer_arena* a);
+XINFER_EXPORT void* xinfer_arena_base_ptr(const xinfer_arena* a);
 
-/* Synchronous copies between host memory and raw device pointers handed out by this library (arena blocks,
- * decoder tensors).  The reference's counterpart is DeviceContext::copy_host_to_device /
- * copy_device_to_host, src/core/device.h:26-72. */
+/* Plain device memory, streams and synchronous copies for hosts that do not link the CUDA runtime
+ * themselves.  The reference's counterparts are members of DeviceContext, src/core/device.h:26-72. */
+XINFER_EXPORT int xinfer_device_alloc(size_t bytes, void** out);   /* DeviceContext::allocate_device */
+XINFER_EXPORT void xinfer_device_free(void* dev_ptr);              /* DeviceContext::free_device */
+XINFER_EXPORT int xinfer_stream_create(xinfer_stream_t* out);      /* stands in for DeviceContext::queue() */
+XINFER_EXPORT void xinfer_stream_destroy(xinfer_stream_t s);
+XINFER_EXPORT int xinfer_stream_synchronize(xinfer_stream_t s);    /* DeviceContext::synchronize */
 XINFER_EXPORT int xinfer_copy_device_to_host(void* dst_host, const void* src_dev, size_t bytes);
 XINFER_EXPORT int xinfer_copy_host_to_device(void* dst_dev, const void* src_host, size_t bytes);
 

@@ -82,6 +82,24 @@ class OracleModel:
         logits = oracle.linear_int4_f64(normed.astype(np.float32), self.top["lm_head.w"], self.top["lm_head.s"])
         return x[0], logits[0]
 
+    def draft_fill(self, tok, h_prev, pos, seq_state):
+        """The head's pass for `tok` at `pos` up to its attention layer's KV write (no attention, MLP or logits):
+        fills the slot the next step's first draft pass attends to when all k drafts are accepted."""
+        s = self.s
+        w = self.mtp_layer.w
+        e = oracle.embed(self.top["embed"], [tok], s.vocab_size)
+        cat = np.concatenate([oracle.rmsnorm_f16(e, self.top["mtp_enorm"], s.rms_norm_eps),
+                              oracle.rmsnorm_f16(h_prev[None], self.top["mtp_hnorm"], s.rms_norm_eps)], axis=1)
+        x = linear16(cat, self.top["mtp_fc.w"], self.top["mtp_fc.s"])
+        normed = oracle.rmsnorm_f16(x, w["input_norm"], s.rms_norm_eps)
+        hkv = s.num_key_value_heads
+        kk = linear16(normed, w["k_proj.w"], w["k_proj.s"])
+        vv = linear16(normed, w["v_proj.w"], w["v_proj.s"])
+        kk = oracle.rmsnorm_f16(kk.reshape(hkv, 256), w["k_norm"], s.rms_norm_eps).reshape(1, hkv, 256)
+        _, kk = oracle.rope_f16(np.zeros((1, 1, 256), np.float16), kk, np.array([pos], np.int64), s.rope_theta, s.rope_dim)
+        st = seq_state["mtp"]
+        oracle.kv_write(st["k_cache"], st["v_cache"], kk, vv.reshape(1, hkv, 256), pos)
+
     def greedy_continuation(self, seq_state, n):
         """The n tokens the target itself would emit after cur_tok (state is left untouched)."""
         import copy
@@ -106,6 +124,7 @@ class OracleModel:
             drafts.append(tok)
             draft_logits.append(lg)
         mtp_drafts = list(drafts)
+        self.draft_fill(tok, h, ctx + k, seq_state)
         if draft_override is not None:
             drafts = [int(t) for t in draft_override]
         # verify: save recurrent state, run k+1 rows

@@ -154,6 +154,18 @@ def main() -> None:
          "out": oracle.philox4x32_10([0x243F6A88, 0x85A308D3, 0x13198A2E, 0x03707344], [0xA4093822, 0x299F31D0])},
     ]
 
+    # Input streams of the reference's mixer op tests (tests/test_ops_oracle.cpp:50-285, 797-906): regenerated at
+    # test time by tests/ref_recipes.py, pinned here by length and CRC-64.
+    sys.path.insert(0, os.path.dirname(HERE))
+    import ref_recipes
+    streams = {}
+    for name, case in (("rmsnorm", ref_recipes.rmsnorm_case), ("rope", ref_recipes.rope_case), ("sdpa", ref_recipes.sdpa_case)):
+        st = case()[-1]
+        streams[name] = {"n": int(st.size), "crc64": f"{oracle.crc64(st.tobytes()):016x}", "first": float(st[0]),
+                         "last": float(st[-1])}
+    with open(os.path.join(HERE, "mixer_streams.json"), "w") as f:
+        json.dump(streams, f, indent=1, sort_keys=True)
+
     np.savez_compressed(os.path.join(HERE, "ref_vectors.npz"), **arrays)
     with open(os.path.join(HERE, "ref_vectors.json"), "w") as f:
         json.dump(meta, f, indent=1, sort_keys=True)

@@ -311,3 +311,28 @@ def test_column_slice_output_for_tensor_parallel(cuda):
                                    M, half, K) == 0
     torch.cuda.synchronize()
     assert np.array_equal(Y.float().cpu().numpy(), full)
+
+
+# ------------------------------------------------------------------ bounded waits
+def test_device_side_wait_runs_out_and_is_reported(cuda):
+    """Every device-side wait of the tcgen05 kernel is bounded.  The test hook shortens the limit to a few
+    milliseconds and makes the kernel's loader withhold the activations of a one-stage, one-CTA problem (K = 256,
+    N = 256: no cluster), so the waits for them run out: the launch must return (no hang, no fault), the device
+    status must report the timeout once, and the next ordinary launch must be correct."""
+    from xinfer_b200 import _lib
+    M, K, N = 4, 256, 256
+    X, W, S, _ = synth_linear(M, K, N, seed=3)
+    Xd, Wd, Sd = dev(X), dev(W), dev(S)
+    Y = torch.zeros((M, N), dtype=torch.float16, device="cuda")
+    good, path = run_linear(cuda, X, W, S, out_dtype=torch.float16)
+    assert path == TC
+    cuda.set_wait_hooks(8_000_000, 0)          # about 4 ms at 1.9 GHz; activation stage 0 is never requested
+    try:
+        assert cuda.linear_int4(Y, Xd, Wd, Sd, None, M, N, K) == 0
+        torch.cuda.synchronize()               # returns: the kernel gave up instead of spinning
+    finally:
+        cuda.set_wait_hooks(0, -1)
+    assert cuda.device_status(0) == _lib.ERR_DEVICE_TIMEOUT
+    assert cuda.device_status(0) == 0          # reading clears the record
+    again, _ = run_linear(cuda, X, W, S, out_dtype=torch.float16)
+    assert np.array_equal(again, good)

@@ -191,3 +191,54 @@ def test_philox_uniform_bit_exact(cuda):
         out = torch.empty(n, dtype=torch.float32, device="cuda")
         assert cuda.philox_uniform(out, seed=seed, subsequence=sub) == 0
         assert np.array_equal(out.cpu().numpy(), oracle.philox_uniform(n, seed, sub))
+
+
+def test_stochastic_margin_run_200_seeds(cuda):
+    """The device sums exp() in parallel fp32, the reference sequentially on the host (src/ops/sampling.cpp:144-147),
+    so p_target can differ in its last bits and a decision r < p_target / p_draft can flip only where r is within
+    rounding of the ratio.  200 seeds of the acceptance configuration (batch 8, k = 3, vocab 151936, T = 0.7):
+    every sequence's accepted count is compared with the literal fp32-sequential oracle; where they differ, the
+    diverging decision's margin |r - ratio| / ratio (ratio from the fp64 oracle) must lie inside 1e-6.  The test
+    also reports the smallest margin seen."""
+    B, k, V, T = 8, 3, 151936, 0.7
+    inv_t = np.float32(1.0 / T)
+    flips_inside, min_margin, decisions = 0, np.inf, 0
+    out = torch.zeros(B * cuda.ACCEPT_RECORD_BYTES, dtype=torch.uint8, device="cuda")
+    for seed in range(200):
+        rng = np.random.default_rng(50_000 + seed)
+        draft = rng.normal(0, 3, size=(B, k, V)).astype(np.float32)
+        target = (draft + rng.normal(0, 1, size=(B, k, V)).astype(np.float32)).astype(np.float32)
+        pick = oracle.philox_uniform(B * k, seed=9000 + seed, subsequence=0).reshape(B, k)
+        uni = oracle.philox_uniform(B * k, seed=9000 + seed, subsequence=1).reshape(B, k)
+        z = draft.astype(np.float64) * np.float64(inv_t)
+        p = np.exp(z - z.max(axis=-1, keepdims=True))
+        p /= p.sum(axis=-1, keepdims=True)
+        c = np.cumsum(p, axis=-1)
+        toks = np.zeros((B, k), np.int64)
+        for b in range(B):
+            for i in range(k):
+                toks[b, i] = min(int(np.searchsorted(c[b, i], pick[b, i] * c[b, i, -1], side="right")), V - 1)
+        probs = np.take_along_axis(p, toks[..., None], axis=-1)[..., 0].astype(np.float32)
+        assert cuda.speculative_accept_reject_batched(dev(toks), dev(target), dev(probs), dev(uni), out,
+                                                      inv_temperature=float(inv_t)) == 0
+        recs = cuda.decode_accept_records(out)
+        for b in range(B):
+            want = oracle.speculative_accept_reject(toks[b], target[b], probs[b], uni[b], inv_temperature=float(inv_t))
+            na_gpu, na_cpu = recs[b]["num_accepted"], want["num_accepted"]
+            last = min(max(na_gpu, na_cpu), k - 1)
+            for i in range(last + 1):                 # the decisions that were actually taken
+                ratio = oracle.token_prob_f64(target[b, i] * inv_t, toks[b, i]) / float(probs[b, i])
+                if ratio > 0:
+                    min_margin = min(min_margin, abs(float(uni[b, i]) - ratio) / ratio)
+                decisions += 1
+            if na_gpu != na_cpu:
+                i = min(na_gpu, na_cpu)               # the decision on which the two sides part
+                ratio = oracle.token_prob_f64(target[b, i] * inv_t, toks[b, i]) / float(probs[b, i])
+                margin = abs(float(uni[b, i]) - ratio) / ratio
+                assert margin < 1e-6, (seed, b, i, margin, na_gpu, na_cpu)
+                flips_inside += 1
+            else:
+                assert recs[b]["bonus_or_resampled_token"] == want["bonus_or_resampled_token"], (seed, b)
+    print(f"stochastic margin run: {decisions} decisions, {flips_inside} flips inside the 1e-6 band, "
+          f"smallest margin {min_margin:.3e}")
+    assert decisions >= 200 * B

@@ -221,13 +221,13 @@ def test_graph_replay_equals_eager(small):
 def test_reduced_stack_at_full_layer_shapes():
     """The reduced-stack configuration with the 27B layer shapes (8 layers = 6 Gated-DeltaNet + 2 GQA 24q/4kv,
     hidden 5120, FFN 17408, k=3, batch 1, context 2048): every projection runs through the decomposition it
-    gets in the benchmark (cluster split-K, fused 3- and 4-way launches, SwiGLU pairs).  The vocabulary is
-    cut to 8192 to keep the CPU oracle to seconds."""
+    gets in the benchmark (cluster split-K, fused 3- and 4-way launches, SwiGLU pairs), LM head at the full
+    vocabulary of 151936."""
     from xinfer_b200.spec import Shape, SpecDecoder
     if not torch.cuda.is_available():
         pytest.skip("no CUDA device")
     shape_cfg = Shape(hidden_size=5120, intermediate_size=17408, num_hidden_layers=8, num_attention_heads=24,
-                      num_key_value_heads=4, vocab_size=8192, linear_num_v_heads=48, linear_num_k_heads=16)
+                      num_key_value_heads=4, vocab_size=151936, linear_num_v_heads=48, linear_num_k_heads=16)
     dec = SpecDecoder(shape_cfg, batch=1, k=3, max_seq=2100, seed=21)
     dec.reset(2048, seed=7)
     model = pull_model(dec, shape_cfg, dec.k)
@@ -238,3 +238,55 @@ def test_reduced_stack_at_full_layer_shapes():
     assert accepted == [3]
     compare_step(dec, model, seqs, shape_cfg, tag="cfg3-after")
     dec.close()
+
+
+def test_batch8_context8192_at_full_layer_shapes():
+    """The benchmark's extents for the mixers: batch 8, context 8192, k = 3 (32 verify rows, the 9-split attention
+    grid over 8 sequences, the DeltaNet grid over 8 x 48 heads), on a 2-layer stack (one Gated-DeltaNet, one GQA
+    layer) at the 27B layer shapes.  Hidden rows are bounded per row by their largest element, not by an RMS
+    over the tensor; tokens, counts and context lengths must match exactly."""
+    from xinfer_b200.spec import Shape, SpecDecoder
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    shape_cfg = Shape(hidden_size=5120, intermediate_size=17408, num_hidden_layers=2, num_attention_heads=24,
+                      num_key_value_heads=4, vocab_size=8192, linear_num_v_heads=48, linear_num_k_heads=16,
+                      full_attention_interval=2)
+    B, k = 8, 3
+    dec = SpecDecoder(shape_cfg, batch=B, k=k, max_seq=8192 + 64, seed=33)
+    dec.reset(8192, seed=9)
+    model = pull_model(dec, shape_cfg, k)
+    seqs = pull_state(dec, model, shape_cfg, B, dec.max_seq)
+    for step in range(2):
+        dec.step()
+        emitted, counts = dec.results()
+        x_gpu = dec.tensor(-1, "x", np.float16).reshape(B, k + 1, shape_cfg.hidden_size).astype(np.float64)
+        ctx_gpu = dec.tensor(-1, "ctx", np.int32)
+        worst = 0.0
+        for b in range(B):
+            want, dbg = model.step(seqs[b])
+            ref = dbg["hidden"].astype(np.float64)
+            per_row = np.abs(x_gpu[b] - ref).max(axis=1) / np.abs(ref).max(axis=1)
+            worst = max(worst, float(per_row.max()))
+            assert counts[b] == len(want) and emitted[b, :counts[b]].tolist() == want, (step, b)
+            assert ctx_gpu[b] == seqs[b]["ctx"]
+        assert worst < 1e-2, worst     # a few fp16 roundings of the row's largest element
+    dec.close()
+
+
+def test_step_refuses_to_run_past_the_cache(small):
+    """The context lengths advance on the device; the host keeps an upper bound and returns an error instead of
+    letting a step drop its newest keys (the reference's KV cache throws when full)."""
+    from xinfer_b200 import _lib
+    dec, _ = small
+    k = dec.k
+    room = 3
+    dec.reset(dec.max_seq - (room + 2) * (k + 1), seed=1)     # reset itself needs two steps of headroom
+    for _ in range(room + 2):
+        dec.step()
+    torch.cuda.synchronize()
+    with pytest.raises(_lib.XInferError) as e:
+        dec.step()
+    assert e.value.code == _lib.ERR_INVALID_ARGUMENT
+    dec.reset(0, seed=1)
+    dec.step()                                                # usable again after a reset
+    dec.results()

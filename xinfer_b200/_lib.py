@@ -58,12 +58,13 @@ _vp, _i64, _i32, _f32, _u64, _sz = C.c_void_p, C.c_int64, C.c_int, C.c_float, C.
 # name -> (restype, argtypes); the list is also what the symbol-export test checks.
 SIGNATURES = {
     "xinfer_b200_init": (_i32, [_i32]),
+    "xinfer_b200_init_current": (_i32, []),
     "xinfer_device_status": (_i32, [_i32]),
     "xinfer_last_cuda_error": (C.c_char_p, []),
     "xinfer_b200_version": (C.c_char_p, []),
     "xinfer_last_linear_path": (_i32, []),
     "xinfer_set_linear_path": (None, [_i32]),
-    "xinfer_debug_set_trace": (None, [_vp]),
+    "xinfer_debug_set_wait_hooks": (None, [_i64, _i32]),
     "xinfer_linear_plan_record_begin": (None, []),
     "xinfer_linear_plan_record_end": (None, []),
     "xinfer_linear_plan_rewind": (None, []),
@@ -96,6 +97,29 @@ SIGNATURES = {
     "xinfer_spec_decoder_info": (_i64, [_vp, _i32]),
     "xinfer_spec_decoder_tensor": (_vp, [_vp, _i32, C.c_char_p, C.POINTER(_i64)]),
     "xinfer_spec_decoder_error": (C.c_char_p, [_vp]),
+    "xinfer_rmsnorm_f16": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _f32]),
+    "xinfer_rmsnorm_residual_f16": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _f32]),
+    "xinfer_rope_f16": (_i32, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _f32, _i64]),
+    "xinfer_attention_write_kv_cache_f16": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64]),
+    "xinfer_sdpa_causal_cached_f16": (_i32, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _f32, _i64]),
+    "xinfer_causal_conv1d_silu_f16": (_i32, [_vp, _vp, _vp, _vp, _i64, _vp, _i64]),
+    "xinfer_recurrent_gated_delta_net_f16": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i32, _i64, _i64]),
+    "xinfer_tp_create": (_i32, [_i32, _i32, _sz, C.POINTER(_vp)]),
+    "xinfer_tp_destroy": (None, [_vp]),
+    "xinfer_tp_handle_bytes": (_sz, []),
+    "xinfer_tp_handle": (_i32, [_vp, _vp]),
+    "xinfer_tp_connect": (_i32, [_vp, _vp]),
+    "xinfer_tp_rank": (_i32, [_vp]),
+    "xinfer_tp_world": (_i32, [_vp]),
+    "xinfer_tp_alloc": (_i32, [_vp, _sz, C.POINTER(_sz)]),
+    "xinfer_tp_ptr": (_vp, [_vp, _sz]),
+    "xinfer_tp_linear_int4_f16f16": (_i32, [_vp, _vp, _sz, _i64, _i64, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i32, _i32]),
+    "xinfer_tp_push": (_i32, [_vp, _vp, _sz, _sz]),
+    "xinfer_tp_barrier": (_i32, [_vp, _vp]),
+    "xinfer_tp_set_wait_limit": (None, [_vp, _i64]),
+    "xinfer_tp_status": (_i32, [_vp]),
+    "xinfer_spec_decoder_exchange_bytes": (_sz, [_vp, _i32, _i32, _i32]),
+    "xinfer_spec_decoder_create_tp": (_i32, [_vp, _i32, _i32, _i64, _u64, _vp, C.POINTER(_vp)]),
     "xinfer_arena_create": (_i32, [_sz, _sz, C.POINTER(_vp)]),
     "xinfer_arena_destroy": (None, [_vp]),
     "xinfer_arena_allocate": (_i32, [_vp, _sz, _sz, C.POINTER(_vp)]),
@@ -107,6 +131,11 @@ SIGNATURES = {
     "xinfer_arena_remaining_bytes": (_sz, [_vp]),
     "xinfer_arena_peak_allocated_bytes": (_sz, [_vp]),
     "xinfer_arena_base_ptr": (_vp, [_vp]),
+    "xinfer_device_alloc": (_i32, [_sz, C.POINTER(_vp)]),
+    "xinfer_device_free": (None, [_vp]),
+    "xinfer_stream_create": (_i32, [C.POINTER(_vp)]),
+    "xinfer_stream_destroy": (None, [_vp]),
+    "xinfer_stream_synchronize": (_i32, [_vp]),
     "xinfer_copy_device_to_host": (_i32, [_vp, _vp, _sz]),
     "xinfer_copy_host_to_device": (_i32, [_vp, _vp, _sz]),
     "xinfer_crc64": (_u64, [_vp, _sz]),

@@ -113,6 +113,6 @@ size_t xinfer_arena_remaining_bytes(const xinfer_arena* a) {
     return (a && a->offset < a->capacity) ? a->capacity - a->offset : 0;
 }
 size_t xinfer_arena_peak_allocated_bytes(const xinfer_arena* a) { return a ? a->peak : 0; }
-void* xinfer_arena_base_ptr(xinfer_arena* a) { return a ? a->base : nullptr; }
+void* xinfer_arena_base_ptr(const xinfer_arena* a) { return a ? a->base : nullptr; }
 
 }  // extern "C"

@@ -11,6 +11,7 @@
 
 #include "../../include/xinfer_b200.h"
 #include "sampling.h"
+#include "tp_host.h"
 #include "w4a16.h"
 
 namespace {
@@ -28,13 +29,13 @@ struct DeviceCtx {
     void* sampling = nullptr;     // (row, chunk) partials
     long long* small_dev = nullptr;   // staging for the synchronous sampling calls
     long long* small_host = nullptr;  // pinned
+    int forced_path = 0;              // xinfer_set_linear_path, per device
 };
 
 DeviceCtx g_ctx[kMaxDevices];
 std::mutex g_mutex;
 thread_local std::string g_last_error;
 thread_local int g_last_path = 0;
-int g_forced_path = 0;
 
 constexpr size_t kSmallBytes = 64 * 1024;
 
@@ -82,7 +83,7 @@ int run_linear(xinfer_stream_t s, const void* x, xb::ActType in, bool out_f32, c
     int rc = get_ctx(&c);
     if (rc != XINFER_OK) return rc;
     cudaStream_t stream = static_cast<cudaStream_t>(s);
-    const bool want_tc = (g_forced_path != 2) && in == xb::ActType::F16 &&
+    const bool want_tc = (c->forced_path != 2) && in == xb::ActType::F16 &&
                          xb::tc_eligible(x, proj, num, swiglu, m, k, group_size);
     if (want_tc) {
         int r = xb::tc_launch(stream, x, proj, num, swiglu, out_f32, m, k, c->num_sms, c->workspace, c->counters,
@@ -149,6 +150,23 @@ uint64_t crc_update(uint64_t crc, const void* data, size_t n) {
 
 }  // namespace
 
+namespace xb {
+void set_last_error(const char* msg) { g_last_error = msg ? msg : ""; }
+
+int run_tc_linear(cudaStream_t s, const void* x, const TcProj* proj, int num, bool swiglu, bool out_f32, long long m,
+                  long long k, int group_size, const TpLink* tp) {
+    DeviceCtx* c = nullptr;
+    int rc = get_ctx(&c);
+    if (rc != XINFER_OK) return rc;
+    if (!tc_eligible(x, proj, num, swiglu, m, k, group_size)) return XINFER_ERR_INVALID_ARGUMENT;
+    const int r = tc_launch(s, x, proj, num, swiglu, out_f32, m, k, c->num_sms, c->workspace, c->counters,
+                            kCounterCapacity, c->status, tp);
+    if (r == 0) { g_last_path = 1; return XINFER_OK; }
+    if (r == -1) return fail_cuda(cudaGetLastError());
+    return XINFER_ERR_INVALID_ARGUMENT;
+}
+}  // namespace xb
+
 extern "C" {
 
 int xinfer_b200_init(int device) {
@@ -162,28 +180,44 @@ int xinfer_b200_init(int device) {
     return rc;
 }
 
+int xinfer_b200_init_current(void) {
+    DeviceCtx* c = nullptr;
+    return get_ctx(&c);
+}
+
 int xinfer_device_status(int device) {
-    if (device < 0 || device >= kMaxDevices || !g_ctx[device].ready) return 0;
+    if (device < 0 || device >= kMaxDevices) return 0;
     int cur = 0, v = 0;
     cudaGetDevice(&cur);
     cudaSetDevice(device);
-    cudaError_t e = cudaMemcpy(&v, g_ctx[device].status, sizeof(int), cudaMemcpyDeviceToHost);
-    if (e == cudaSuccess && v != 0) cudaMemset(g_ctx[device].status, 0, sizeof(int));
+    cudaError_t e = cudaSuccess;
+    if (g_ctx[device].ready) {
+        e = cudaMemcpy(&v, g_ctx[device].status, sizeof(int), cudaMemcpyDeviceToHost);
+        if (e == cudaSuccess && v != 0) cudaMemset(g_ctx[device].status, 0, sizeof(int));
+    }
+    // the allocation-free entry point keeps its own status word (in its in-library array)
+    const int v2 = xb::tc_noalloc_take_status(device);
     cudaSetDevice(cur);
     if (e != cudaSuccess) return fail_cuda(e);
-    return v == 0 ? 0 : XINFER_ERR_DEVICE_TIMEOUT;
+    if (v2 < 0) return fail_cuda(cudaGetLastError());
+    return (v == 0 && v2 == 0) ? 0 : XINFER_ERR_DEVICE_TIMEOUT;
 }
 
 const char* xinfer_last_cuda_error(void) { return g_last_error.c_str(); }
 const char* xinfer_b200_version(void) { return "xinfer_b200 0.1 (sm_100a)"; }
 int xinfer_last_linear_path(void) { return g_last_path; }
-void xinfer_debug_set_trace(void* dev_ptr) { xb::tc_set_trace(static_cast<long long*>(dev_ptr)); }
+void xinfer_debug_set_wait_hooks(int64_t limit_clocks, int withhold_x_from_stage) {
+    xb::tc_set_wait_hooks(limit_clocks, withhold_x_from_stage);
+}
 
 void xinfer_linear_plan_record_begin(void) { xb::tc_plan_record_begin(); }
 void xinfer_linear_plan_record_end(void) { xb::tc_plan_record_end(); }
 void xinfer_linear_plan_rewind(void) { xb::tc_plan_rewind(); }
 void xinfer_linear_plan_clear(void) { xb::tc_plan_clear(); }
-void xinfer_set_linear_path(int path) { g_forced_path = path; }
+void xinfer_set_linear_path(int path) {
+    DeviceCtx* c = nullptr;
+    if (get_ctx(&c) == XINFER_OK) c->forced_path = path;
+}
 
 int xinfer_linear_int4_f16f16(xinfer_stream_t s, void* Y, const void* X, const uint8_t* W, const void* scales,
                               const float* bias, int64_t M, int64_t N, int64_t K, int group_size) {

@@ -26,6 +26,8 @@
 #include <math.h>
 #include <stdint.h>
 
+#include <mutex>
+
 #include "launch.cuh"
 #include "mixers.h"
 
@@ -160,11 +162,16 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(__half* out, long long ld_
 // ------------------------------------------------------------------------------- attention prologue
 // One block per (row, head slot); head slots 0..Hq-1 are query heads, Hq..Hq+Hkv-1 key heads,
 // Hq+Hkv..Hq+2Hkv-1 value heads.  256 threads = head_dim.
+// Generalisations used by the stand-alone op entry points: `q_head_stride` is the distance between query
+// heads in q_in (512 for the interleaved [q | gate] block, 256 for plain queries); a null norm weight skips
+// that head norm; `positions` (one per row) overrides ctx[b] + i; a null ctx means context length ctx_base; a
+// null cache pointer skips the write (the rotated key then goes to k_out, if given).
 __global__ void __launch_bounds__(256) attn_prep_kernel(__half* q_out, __half* k_cache, __half* v_cache,
                                                         const __half* q_gate, const __half* k_in, const __half* v_in,
                                                         const float* q_norm_w, const float* k_norm_w, const int* ctx,
                                                         int rows_per_seq, int hq, int hkv, long long max_seq,
-                                                        float eps, float log_theta, int rope_dim) {
+                                                        float eps, float log_theta, int rope_dim, int q_head_stride,
+                                                        const long long* positions, int ctx_base, __half* k_out) {
     griddep_prologue();
     __shared__ float red[32];
     __shared__ float vals[256];
@@ -172,11 +179,11 @@ __global__ void __launch_bounds__(256) attn_prep_kernel(__half* q_out, __half* k
     const int slot = blockIdx.y;
     const int d = threadIdx.x;
     const int b = row / rows_per_seq, i = row % rows_per_seq;
-    const long long pos = static_cast<long long>(ctx[b]) + i;
+    const long long pos = positions ? positions[row] : static_cast<long long>(ctx ? ctx[b] : ctx_base) + i;
     const bool in_cache = pos >= 0 && pos < max_seq;
     if (slot >= hq + hkv) {  // value head: plain copy into the cache
         const int h = slot - hq - hkv;
-        if (in_cache)
+        if (in_cache && v_cache && v_in)
             v_cache[((static_cast<long long>(b) * max_seq + pos) * hkv + h) * 256 + d] =
                 v_in[(static_cast<long long>(row) * hkv + h) * 256 + d];
         return;
@@ -184,13 +191,16 @@ __global__ void __launch_bounds__(256) attn_prep_kernel(__half* q_out, __half* k
     const bool is_q = slot < hq;
     const int h = is_q ? slot : slot - hq;
     // the reference first copies q out of the interleaved [q | gate] head block (fp16, exact)
-    const float x = is_q ? __half2float(q_gate[(static_cast<long long>(row) * hq + h) * 512 + d])
+    const float x = is_q ? __half2float(q_gate[(static_cast<long long>(row) * hq + h) * q_head_stride + d])
                          : __half2float(k_in[(static_cast<long long>(row) * hkv + h) * 256 + d]);
-    const float total = block_sum(x * x, red);
-    const float r = 1.0f / sqrtf(total / 256.0f + eps);
     const float* w = is_q ? q_norm_w : k_norm_w;
-    // rounding point: the head RMSNorm writes fp16
-    const float normed = __half2float(__float2half_rn(x * r * w[d]));
+    float normed = x;
+    if (w) {
+        const float total = block_sum(x * x, red);
+        const float r = 1.0f / sqrtf(total / 256.0f + eps);
+        // rounding point: the head RMSNorm writes fp16
+        normed = __half2float(__float2half_rn(x * r * w[d]));
+    }
     vals[d] = normed;
     __syncthreads();
     float outv = normed;
@@ -206,8 +216,10 @@ __global__ void __launch_bounds__(256) attn_prep_kernel(__half* q_out, __half* k
     const __half o = __float2half_rn(outv);
     if (is_q) {
         q_out[(static_cast<long long>(row) * hq + h) * 256 + d] = o;
-    } else if (in_cache) {
-        k_cache[((static_cast<long long>(b) * max_seq + pos) * hkv + h) * 256 + d] = o;
+    } else if (k_cache) {
+        if (in_cache) k_cache[((static_cast<long long>(b) * max_seq + pos) * hkv + h) * 256 + d] = o;
+    } else if (k_out) {
+        k_out[(static_cast<long long>(row) * hkv + h) * 256 + d] = o;
     }
 }
 
@@ -281,7 +293,7 @@ template <int NT>
 __global__ void __launch_bounds__(kAttnThreads, 2) attn_split_kernel(float* part_o, float* part_ml, const __half* q,
                                                          const __half* k_cache, const __half* v_cache, const int* ctx,
                                                          int rows_per_seq, int hq, int hkv, long long max_seq,
-                                                         float scale) {
+                                                         float scale, int ctx_base) {
     griddep_prologue();
     extern __shared__ __align__(16) uint8_t attn_smem_raw[];
     AttnSmem& sm = *reinterpret_cast<AttnSmem*>(attn_smem_raw);
@@ -290,7 +302,7 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_split_kernel(float* part
     const int kq = warp >> 1, kt = warp & 1;  // S^T role: dim quarter, 16-key tile
     const int G = hq / hkv;
     const int nrows = G * rows_per_seq;  // valid query rows, row = g * R + i
-    const int ctx_b = ctx[b];
+    const int ctx_b = ctx ? ctx[b] : ctx_base;  // (null: the stand-alone entry point's host-side start position)
     long long total_keys = static_cast<long long>(ctx_b) + rows_per_seq;
     if (total_keys > max_seq) total_keys = max_seq;
     const int nchunks = static_cast<int>((total_keys + kAttnChunk - 1) / kAttnChunk);
@@ -506,6 +518,10 @@ __global__ void __launch_bounds__(256) attn_combine_kernel(__half* out, const fl
     const int h = kvh * G + g;
     // rounding point: the reference's SDPA writes fp16, the gate then multiplies in fp32
     const float attn = __half2float(__float2half_rn(acc * inv));
+    if (!q_gate) {  // plain SDPA (the stand-alone entry point): no output gate
+        out[(row * hq + h) * 256 + d] = __float2half_rn(acc * inv);
+        return;
+    }
     const float gate = __half2float(q_gate[(row * hq + h) * 512 + 256 + d]);
     const float sig = 1.0f / (1.0f + expf(-gate));
     out[(row * hq + h) * 256 + d] = __float2half_rn(attn * sig);
@@ -515,7 +531,7 @@ __global__ void __launch_bounds__(256) attn_combine_kernel(__half* out, const fl
 // One thread per (sequence, channel).  state [B][3][C] holds the last three committed inputs; pending
 // [B][Rmax][C] the raw inputs of the previous step, of which the first n_commit[b] were accepted.
 __global__ void conv1d_spec_kernel(__half* out, const __half* in, const float* conv_w, float* state, float* pending,
-                                   const int* n_commit, int rows_per_seq, int prev_rows, int channels) {
+                                   const int* n_commit, int rows_per_seq, int prev_rows, int channels, int nc_base) {
     griddep_prologue();
     const int c = blockIdx.x * blockDim.x + threadIdx.x;
     const int b = blockIdx.y;
@@ -523,7 +539,7 @@ __global__ void conv1d_spec_kernel(__half* out, const __half* in, const float* c
     float* st = state + static_cast<long long>(b) * 3 * channels;
     float* pd = pending + static_cast<long long>(b) * 8 * channels;
     float s0 = st[c], s1 = st[channels + c], s2 = st[2 * channels + c];
-    int nc = n_commit ? n_commit[b] : 0;
+    int nc = n_commit ? n_commit[b] : nc_base;
     if (nc > prev_rows) nc = prev_rows;
     for (int i = 0; i < nc; ++i) {  // replay the accepted inputs of the previous step
         s0 = s1;
@@ -559,7 +575,7 @@ __global__ void __launch_bounds__(512, 2) gdn_spec_kernel(__half* out, const __h
                                                           const float* dt_bias, const float* norm_w, float* state,
                                                           float* pend_k, float* pend_d, float* pend_g,
                                                           const int* n_commit, int rows_per_seq, int prev_rows, int hv,
-                                                          int hk) {
+                                                          int hk, int nc_base) {
     griddep_prologue();
     __shared__ __align__(16) float sh_q[8][128], sh_k[8][128];
     __shared__ float sh_beta[8], sh_eg[8], red[2][16];
@@ -609,7 +625,7 @@ __global__ void __launch_bounds__(512, 2) gdn_spec_kernel(__half* out, const __h
     }
 
     // ---- replay of the previous step's accepted updates, then write the committed state
-    int nc = n_commit ? n_commit[b] : 0;
+    int nc = n_commit ? n_commit[b] : nc_base;
     if (nc > prev_rows) nc = prev_rows;
     if (nc > 0) {
         for (int t = 0; t < nc; ++t) {
@@ -765,9 +781,17 @@ int add_rmsnorm_rows(cudaStream_t s, __half* out, __half* x, const __half* delta
 int attn_prep(cudaStream_t s, __half* q_out, __half* k_cache, __half* v_cache, const __half* q_gate, const __half* k_in,
               const __half* v_in, const float* q_norm_w, const float* k_norm_w, const int* ctx, int batch,
               int rows_per_seq, int hq, int hkv, long long max_seq, float eps, float rope_theta, int rope_dim) {
+    return attn_prep_ex(s, q_out, k_cache, v_cache, q_gate, k_in, v_in, q_norm_w, k_norm_w, ctx, batch, rows_per_seq, hq, hkv,
+                        max_seq, eps, rope_theta, rope_dim, 512, nullptr, 0, nullptr);
+}
+
+int attn_prep_ex(cudaStream_t s, __half* q_out, __half* k_cache, __half* v_cache, const __half* q_in, const __half* k_in,
+                 const __half* v_in, const float* q_norm_w, const float* k_norm_w, const int* ctx, int batch,
+                 int rows_per_seq, int hq, int hkv, long long max_seq, float eps, float rope_theta, int rope_dim,
+                 int q_head_stride, const long long* positions, int ctx_base, __half* k_out) {
     dim3 grid(batch * rows_per_seq, hq + 2 * hkv);
-    launch_pdl(attn_prep_kernel, dim3(grid), dim3(256), 0, s, q_out, k_cache, v_cache, q_gate, k_in, v_in, q_norm_w, k_norm_w, ctx,
-                                          rows_per_seq, hq, hkv, max_seq, eps, logf(rope_theta), rope_dim);
+    launch_pdl(attn_prep_kernel, dim3(grid), dim3(256), 0, s, q_out, k_cache, v_cache, q_in, k_in, v_in, q_norm_w, k_norm_w, ctx,
+               rows_per_seq, hq, hkv, max_seq, eps, logf(rope_theta), rope_dim, q_head_stride, positions, ctx_base, k_out);
     return XB_LAUNCH_OK();
 }
 
@@ -778,26 +802,37 @@ size_t attn_scratch_bytes(int batch, int hkv, int nsplit) {
 int attn_decode(cudaStream_t s, __half* out, const __half* q, const __half* q_gate, const __half* k_cache,
                 const __half* v_cache, const int* ctx, int batch, int rows_per_seq, int hq, int hkv, long long max_seq,
                 int nsplit, float* scratch) {
+    return attn_decode_ex(s, out, q, q_gate, k_cache, v_cache, ctx, batch, rows_per_seq, hq, hkv, max_seq, nsplit, scratch,
+                          1.0f / sqrtf(256.0f), 0);
+}
+
+int attn_decode_ex(cudaStream_t s, __half* out, const __half* q, const __half* q_gate, const __half* k_cache,
+                   const __half* v_cache, const int* ctx, int batch, int rows_per_seq, int hq, int hkv, long long max_seq,
+                   int nsplit, float* scratch, float scale, int ctx_base) {
     if (hq % hkv != 0 || (hq / hkv) * rows_per_seq > kAttnRows) return -2;
-    static bool configured = false;
-    if (!configured) {
+    // the shared-memory attribute belongs to the device's context: set it once per device
+    static bool configured_dev[64];
+    static std::mutex configured_mu;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -1;
+    std::lock_guard<std::mutex> lock(configured_mu);
+    if (!configured_dev[dev]) {
         const int bytes = static_cast<int>(sizeof(AttnSmem));
         if (cudaFuncSetAttribute(attn_split_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess ||
             cudaFuncSetAttribute(attn_split_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess ||
             cudaFuncSetAttribute(attn_split_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess ||
             cudaFuncSetAttribute(attn_split_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess)
             return -1;
-        configured = true;
+        configured_dev[dev] = true;
     }
     float* part_o = scratch;
     float* part_ml = scratch + static_cast<size_t>(batch) * hkv * nsplit * (kAttnRows * 256);
     dim3 grid(nsplit, hkv, batch);
-    const float scale = 1.0f / sqrtf(256.0f);
     switch (((hq / hkv) * rows_per_seq + 7) / 8) {
-        case 1: launch_pdl(attn_split_kernel<1>, dim3(grid), dim3(kAttnThreads), sizeof(AttnSmem), s, part_o, part_ml, q, k_cache, v_cache, ctx, rows_per_seq, hq, hkv, max_seq, scale); break;
-        case 2: launch_pdl(attn_split_kernel<2>, dim3(grid), dim3(kAttnThreads), sizeof(AttnSmem), s, part_o, part_ml, q, k_cache, v_cache, ctx, rows_per_seq, hq, hkv, max_seq, scale); break;
-        case 3: launch_pdl(attn_split_kernel<3>, dim3(grid), dim3(kAttnThreads), sizeof(AttnSmem), s, part_o, part_ml, q, k_cache, v_cache, ctx, rows_per_seq, hq, hkv, max_seq, scale); break;
-        default: launch_pdl(attn_split_kernel<4>, dim3(grid), dim3(kAttnThreads), sizeof(AttnSmem), s, part_o, part_ml, q, k_cache, v_cache, ctx, rows_per_seq, hq, hkv, max_seq, scale); break;
+        case 1: launch_pdl(attn_split_kernel<1>, dim3(grid), dim3(kAttnThreads), sizeof(AttnSmem), s, part_o, part_ml, q, k_cache, v_cache, ctx, rows_per_seq, hq, hkv, max_seq, scale, ctx_base); break;
+        case 2: launch_pdl(attn_split_kernel<2>, dim3(grid), dim3(kAttnThreads), sizeof(AttnSmem), s, part_o, part_ml, q, k_cache, v_cache, ctx, rows_per_seq, hq, hkv, max_seq, scale, ctx_base); break;
+        case 3: launch_pdl(attn_split_kernel<3>, dim3(grid), dim3(kAttnThreads), sizeof(AttnSmem), s, part_o, part_ml, q, k_cache, v_cache, ctx, rows_per_seq, hq, hkv, max_seq, scale, ctx_base); break;
+        default: launch_pdl(attn_split_kernel<4>, dim3(grid), dim3(kAttnThreads), sizeof(AttnSmem), s, part_o, part_ml, q, k_cache, v_cache, ctx, rows_per_seq, hq, hkv, max_seq, scale, ctx_base); break;
     }
     dim3 grid2((hq / hkv) * rows_per_seq, hkv, batch);
     launch_pdl(attn_combine_kernel, dim3(grid2), dim3(256), 0, s, out, part_o, part_ml, q_gate, nsplit, rows_per_seq, hq, hkv);
@@ -805,18 +840,18 @@ int attn_decode(cudaStream_t s, __half* out, const __half* q, const __half* q_ga
 }
 
 int conv1d_spec(cudaStream_t s, __half* out, const __half* in, const float* conv_w, float* state, float* pending,
-                const int* n_commit, int batch, int rows_per_seq, int prev_rows, int channels) {
+                const int* n_commit, int batch, int rows_per_seq, int prev_rows, int channels, int nc_base) {
     dim3 grid((channels + 255) / 256, batch);
-    launch_pdl(conv1d_spec_kernel, dim3(grid), dim3(256), 0, s, out, in, conv_w, state, pending, n_commit, rows_per_seq, prev_rows, channels);
+    launch_pdl(conv1d_spec_kernel, dim3(grid), dim3(256), 0, s, out, in, conv_w, state, pending, n_commit, rows_per_seq, prev_rows, channels, nc_base);
     return XB_LAUNCH_OK();
 }
 
 int gdn_spec(cudaStream_t s, __half* out, const __half* qkv, const __half* z, const __half* b, const __half* a,
              const float* A_log, const float* dt_bias, const float* norm_w, float* state, float* pend_k, float* pend_d,
-             float* pend_g, const int* n_commit, int batch, int rows_per_seq, int prev_rows, int hv, int hk) {
+             float* pend_g, const int* n_commit, int batch, int rows_per_seq, int prev_rows, int hv, int hk, int nc_base) {
     dim3 grid(hv, batch);
     launch_pdl(gdn_spec_kernel, dim3(grid), dim3(512), 0, s, out, qkv, z, b, a, A_log, dt_bias, norm_w, state, pend_k, pend_d, pend_g,
-                                         n_commit, rows_per_seq, prev_rows, hv, hk);
+                                         n_commit, rows_per_seq, prev_rows, hv, hk, nc_base);
     return XB_LAUNCH_OK();
 }
 

@@ -20,19 +20,32 @@ int add_rmsnorm_rows(cudaStream_t s, __half* out, __half* x, const __half* delta
 int attn_prep(cudaStream_t s, __half* q_out, __half* k_cache, __half* v_cache, const __half* q_gate, const __half* k_in,
               const __half* v_in, const float* q_norm_w, const float* k_norm_w, const int* ctx, int batch,
               int rows_per_seq, int hq, int hkv, long long max_seq, float eps, float rope_theta, int rope_dim);
+// The same kernel with its optional pieces spelled out (the stand-alone op entry points): query heads
+// `q_head_stride` halves apart in q_in, null norm weights skip the head norm, `positions` (per row) or `ctx_base`
+// (when ctx is null) give the positions, null caches skip the write and the rotated keys go to `k_out`.
+int attn_prep_ex(cudaStream_t s, __half* q_out, __half* k_cache, __half* v_cache, const __half* q_in, const __half* k_in,
+                 const __half* v_in, const float* q_norm_w, const float* k_norm_w, const int* ctx, int batch,
+                 int rows_per_seq, int hq, int hkv, long long max_seq, float eps, float rope_theta, int rope_dim,
+                 int q_head_stride, const long long* positions, int ctx_base, __half* k_out);
 size_t attn_scratch_bytes(int batch, int hkv, int nsplit);
 // causal GQA attention over the cache (row i of sequence b sees keys below ctx[b] + i + 1), then * sigmoid(gate)
 int attn_decode(cudaStream_t s, __half* out, const __half* q, const __half* q_gate, const __half* k_cache,
                 const __half* v_cache, const int* ctx, int batch, int rows_per_seq, int hq, int hkv, long long max_seq,
                 int nsplit, float* scratch);
+// with an explicit softmax scale, a host-side context length when ctx is null, and no output gate when q_gate is null
+int attn_decode_ex(cudaStream_t s, __half* out, const __half* q, const __half* q_gate, const __half* k_cache,
+                   const __half* v_cache, const int* ctx, int batch, int rows_per_seq, int hq, int hkv, long long max_seq,
+                   int nsplit, float* scratch, float scale, int ctx_base);
 
-// state [batch][3][channels], pending [batch][8][channels] fp32
+// state [batch][3][channels], pending [batch][8][channels] fp32.  The first min(n_commit[b], prev_rows) pending
+// inputs of the previous call are committed to the state before the new rows are processed (n_commit null:
+// nc_base of them).  rows_per_seq = 0 only commits.
 int conv1d_spec(cudaStream_t s, __half* out, const __half* in, const float* conv_w, float* state, float* pending,
-                const int* n_commit, int batch, int rows_per_seq, int prev_rows, int channels);
+                const int* n_commit, int batch, int rows_per_seq, int prev_rows, int channels, int nc_base = 0);
 // state [batch][hv][128][128], pend_k / pend_d [batch][hv][8][128], pend_g [batch][hv][8] fp32
 int gdn_spec(cudaStream_t s, __half* out, const __half* qkv, const __half* z, const __half* b, const __half* a,
              const float* A_log, const float* dt_bias, const float* norm_w, float* state, float* pend_k, float* pend_d,
-             float* pend_g, const int* n_commit, int batch, int rows_per_seq, int prev_rows, int hv, int hk);
+             float* pend_g, const int* n_commit, int batch, int rows_per_seq, int prev_rows, int hv, int hk, int nc_base = 0);
 
 int spec_commit(cudaStream_t s, const void* accept_records, const long long* draft_tokens, int batch, int k,
                 int rows_per_seq, int* ctx, int* n_commit, long long* cur_tok, long long* emitted, int* emitted_n,

@@ -1,0 +1,237 @@
+// C-ABI entry points for the per-layer mixer ops, with the reference's own op signatures (fp16 overloads,
+// cudaStream_t for sycl::queue&), so that each kernel of mixers.cu can be checked on its own against the
+// cases the reference's tests hold:
+//   rmsnorm, rmsnorm_residual       src/ops/rmsnorm.h:9-42
+//   rope                            src/ops/rope.h:14-34
+//   attention_write_kv_cache        src/ops/attention.h:38-58
+//   sdpa_causal_cached              src/ops/attention.h:89-113
+//   causal_conv1d_silu              src/targets/qwen3_8/linear_attn.h:15-21
+//   recurrent_gated_delta_net       src/targets/qwen3_8/linear_attn.h:41-58
+// They run the product kernels (the ones the speculative step launches), not separate test kernels: the
+// stateful ops go through the same pending-update / commit mechanism as the step, with the commit applied
+// before the call returns to the stream, which gives the reference's "state is updated by the call" contract.
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <math.h>
+#include <stdint.h>
+
+#include <mutex>
+
+#include "../../include/xinfer_b200.h"
+#include "mixers.h"
+#include "w4a16.h"
+
+namespace {
+
+constexpr int kMaxDevices = 64;
+constexpr int kSdpaSplits = 8;
+
+// Scratch of the stand-alone entry points, per device, grown on demand (the speculative decoder has its own).
+struct MixerScratch {
+    float* buf = nullptr;
+    size_t bytes = 0;
+};
+MixerScratch g_scratch[kMaxDevices];
+std::mutex g_mu;
+
+int scratch(size_t bytes, float** out) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return XINFER_ERR_NO_DEVICE;
+    std::lock_guard<std::mutex> lock(g_mu);
+    MixerScratch& m = g_scratch[dev];
+    if (m.bytes < bytes) {
+        // a larger request: the old block may still be in use by work already enqueued, so wait for it first
+        if (m.buf) {
+            cudaDeviceSynchronize();
+            cudaFree(m.buf);
+            m.buf = nullptr;
+            m.bytes = 0;
+        }
+        if (cudaMalloc(reinterpret_cast<void**>(&m.buf), bytes) != cudaSuccess) {
+            cudaGetLastError();
+            return XINFER_ERR_OUT_OF_MEMORY;
+        }
+        m.bytes = bytes;
+    }
+    *out = m.buf;
+    return XINFER_OK;
+}
+
+int ok_or_cuda(int rc) {
+    if (rc == 0) return XINFER_OK;
+    xb::set_last_error(cudaGetErrorString(cudaGetLastError()));
+    return rc == -2 ? XINFER_ERR_INVALID_ARGUMENT : XINFER_ERR_CUDA;
+}
+
+}  // namespace
+
+extern "C" {
+
+int xinfer_rmsnorm_f16(xinfer_stream_t s, void* out, const void* in, const float* weight, int64_t num_tokens,
+                       int64_t hidden_size, float eps) {
+    if (num_tokens <= 0 || hidden_size <= 0) return XINFER_NOOP_INVALID_SHAPE;
+    if (!out || !in || !weight) return XINFER_ERR_INVALID_ARGUMENT;
+    return ok_or_cuda(xb::rmsnorm_rows(static_cast<cudaStream_t>(s), static_cast<__half*>(out), hidden_size,
+                                       static_cast<const __half*>(in), weight, static_cast<int>(num_tokens),
+                                       static_cast<int>(hidden_size), eps));
+}
+
+int xinfer_rmsnorm_residual_f16(xinfer_stream_t s, void* out, void* residual, const void* in, const float* weight,
+                                int64_t num_tokens, int64_t hidden_size, float eps) {
+    if (num_tokens <= 0 || hidden_size <= 0) return XINFER_NOOP_INVALID_SHAPE;
+    if (!out || !residual || !in || !weight) return XINFER_ERR_INVALID_ARGUMENT;
+    return ok_or_cuda(xb::add_rmsnorm_rows(static_cast<cudaStream_t>(s), static_cast<__half*>(out), static_cast<__half*>(residual),
+                                           static_cast<const __half*>(in), weight, static_cast<int>(num_tokens),
+                                           static_cast<int>(hidden_size), eps));
+}
+
+int xinfer_rope_f16(xinfer_stream_t s, void* q_ptr, void* k_ptr, int64_t num_tokens, int64_t num_q_heads,
+                    int64_t num_kv_heads, int64_t head_dim, const int64_t* positions_dev, float theta, int64_t rotary_dim) {
+    if (num_tokens <= 0 || num_q_heads < 0 || num_kv_heads < 0 || num_q_heads + num_kv_heads == 0) return XINFER_NOOP_INVALID_SHAPE;
+    if (head_dim != 256 || rotary_dim < 0 || rotary_dim > 256 || rotary_dim % 2 || !positions_dev || !(theta > 0.f) ||
+        (num_q_heads > 0 && !q_ptr) || (num_kv_heads > 0 && !k_ptr))
+        return XINFER_ERR_INVALID_ARGUMENT;
+    // in place: each (row, head) block reads its 256 values before it writes them
+    return ok_or_cuda(xb::attn_prep_ex(static_cast<cudaStream_t>(s), static_cast<__half*>(q_ptr), nullptr, nullptr,
+                                       static_cast<const __half*>(q_ptr), static_cast<const __half*>(k_ptr), nullptr, nullptr,
+                                       nullptr, nullptr, 1, static_cast<int>(num_tokens), static_cast<int>(num_q_heads),
+                                       static_cast<int>(num_kv_heads), 1ll << 40, 0.f, theta, static_cast<int>(rotary_dim), 256,
+                                       reinterpret_cast<const long long*>(positions_dev), 0, static_cast<__half*>(k_ptr)));
+}
+
+int xinfer_attention_write_kv_cache_f16(xinfer_stream_t s, void* k_cache, void* v_cache, const void* K_in, const void* V_in,
+                                        int64_t start_pos, int64_t num_tokens, int64_t num_kv_heads, int64_t head_dim,
+                                        int64_t max_seq_len) {
+    if (num_tokens <= 0 || num_kv_heads <= 0) return XINFER_NOOP_INVALID_SHAPE;
+    if (!k_cache || !v_cache || !K_in || !V_in || head_dim != 256 || start_pos < 0 || start_pos > INT32_MAX)
+        return XINFER_ERR_INVALID_ARGUMENT;
+    // the reference throws std::out_of_range when the rows do not fit a bounded cache (src/ops/attention.cpp:95-99)
+    if (max_seq_len > 0 && start_pos + num_tokens > max_seq_len) return XINFER_ERR_INVALID_ARGUMENT;
+    const long long cap = max_seq_len > 0 ? max_seq_len : (1ll << 40);
+    return ok_or_cuda(xb::attn_prep_ex(static_cast<cudaStream_t>(s), nullptr, static_cast<__half*>(k_cache),
+                                       static_cast<__half*>(v_cache), nullptr, static_cast<const __half*>(K_in),
+                                       static_cast<const __half*>(V_in), nullptr, nullptr, nullptr, 1,
+                                       static_cast<int>(num_tokens), 0, static_cast<int>(num_kv_heads), cap, 0.f, 1.0e7f, 0, 256,
+                                       nullptr, static_cast<int>(start_pos), nullptr));
+}
+
+int xinfer_sdpa_causal_cached_f16(xinfer_stream_t s, void* out, const void* Q, const void* k_cache, const void* v_cache,
+                                  int64_t start_pos, int64_t num_q_tokens, int64_t num_q_heads, int64_t num_kv_heads,
+                                  int64_t head_dim, float scale, int64_t max_seq_len) {
+    if (num_q_tokens <= 0 || num_q_heads <= 0 || num_kv_heads <= 0) return XINFER_NOOP_INVALID_SHAPE;
+    if (!out || !Q || !k_cache || !v_cache || head_dim != 256 || num_q_heads % num_kv_heads || start_pos < 0 ||
+        start_pos + num_q_tokens > INT32_MAX)
+        return XINFER_ERR_INVALID_ARGUMENT;
+    if (max_seq_len > 0 && start_pos + num_q_tokens > max_seq_len) return XINFER_ERR_INVALID_ARGUMENT;
+    const int hq = static_cast<int>(num_q_heads), hkv = static_cast<int>(num_kv_heads);
+    const int group = hq / hkv;
+    if (group > 32) return XINFER_ERR_INVALID_ARGUMENT;
+    const int rows_max = 32 / group;  // query rows that share a KV head fill at most 32 MMA columns per launch
+    float* scr = nullptr;
+    int rc = scratch(xb::attn_scratch_bytes(1, hkv, kSdpaSplits), &scr);
+    if (rc != XINFER_OK) return rc;
+    const float sc = scale > 0.f ? scale : 1.0f / sqrtf(256.0f);  // src/ops/attention.cpp:165-167
+    const long long cap = max_seq_len > 0 ? max_seq_len : (1ll << 40);
+    const __half* q = static_cast<const __half*>(Q);
+    __half* o = static_cast<__half*>(out);
+    // the kernel takes the tokens of one launch as "rows of one sequence"; longer inputs go chunk by chunk
+    for (int64_t t0 = 0; t0 < num_q_tokens; t0 += rows_max) {
+        const int rows = static_cast<int>(num_q_tokens - t0 < rows_max ? num_q_tokens - t0 : rows_max);
+        rc = xb::attn_decode_ex(static_cast<cudaStream_t>(s), o + t0 * hq * 256, q + t0 * hq * 256, nullptr,
+                                static_cast<const __half*>(k_cache), static_cast<const __half*>(v_cache), nullptr, 1, rows, hq,
+                                hkv, cap, kSdpaSplits, scr, sc, static_cast<int>(start_pos + t0));
+        if (rc != 0) return ok_or_cuda(rc);
+    }
+    return XINFER_OK;
+}
+
+int xinfer_causal_conv1d_silu_f16(xinfer_stream_t s, void* out_qkv, const void* in_qkv, const float* conv_w, int64_t seq_len,
+                                  float* conv_state, int64_t num_channels) {
+    if (seq_len <= 0 || num_channels <= 0) return XINFER_NOOP_INVALID_SHAPE;
+    if (!out_qkv || !in_qkv || !conv_w || num_channels > INT32_MAX) return XINFER_ERR_INVALID_ARGUMENT;
+    const int ch = static_cast<int>(num_channels);
+    // pending inputs [8][ch], and a zero state [3][ch] for callers without one ("assumes zeros for past")
+    float* scr = nullptr;
+    int rc = scratch(static_cast<size_t>(11) * ch * sizeof(float), &scr);
+    if (rc != XINFER_OK) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(s);
+    float* state = conv_state;
+    if (!state) {
+        state = scr + static_cast<size_t>(8) * ch;
+        if (cudaMemsetAsync(state, 0, static_cast<size_t>(3) * ch * sizeof(float), st) != cudaSuccess) return ok_or_cuda(-1);
+    }
+    const __half* in = static_cast<const __half*>(in_qkv);
+    __half* out = static_cast<__half*>(out_qkv);
+    int prev = 0;
+    for (int64_t t0 = 0; t0 < seq_len; t0 += 8) {
+        const int rows = static_cast<int>(seq_len - t0 < 8 ? seq_len - t0 : 8);
+        rc = xb::conv1d_spec(st, out + t0 * ch, in + t0 * ch, conv_w, state, scr, nullptr, 1, rows, prev, ch, prev);
+        if (rc != 0) return ok_or_cuda(rc);
+        prev = rows;
+    }
+    // commit the last chunk's inputs to the state
+    return ok_or_cuda(xb::conv1d_spec(st, out, in, conv_w, state, scr, nullptr, 1, 0, prev, ch, prev));
+}
+
+int xinfer_recurrent_gated_delta_net_f16(xinfer_stream_t s, void* out, const void* qkv, const void* z, const void* b,
+                                         const void* a, const float* A_log, const float* dt_bias, const float* norm_weight,
+                                         float* state_buffer, int64_t seq_len, int zero_state, int64_t num_v_heads,
+                                         int64_t num_k_heads) {
+    if (seq_len <= 0 || num_v_heads <= 0 || num_k_heads <= 0) return XINFER_NOOP_INVALID_SHAPE;
+    if (!out || !qkv || !z || !b || !a || !A_log || !dt_bias || !norm_weight || !state_buffer || num_v_heads % num_k_heads)
+        return XINFER_ERR_INVALID_ARGUMENT;
+    const int hv = static_cast<int>(num_v_heads), hk = static_cast<int>(num_k_heads);
+    const size_t pk = static_cast<size_t>(hv) * 8 * 128;
+    float* scr = nullptr;
+    int rc = scratch((2 * pk + static_cast<size_t>(hv) * 8) * sizeof(float), &scr);
+    if (rc != XINFER_OK) return rc;
+    float *pend_k = scr, *pend_d = scr + pk, *pend_g = scr + 2 * pk;
+    cudaStream_t st = static_cast<cudaStream_t>(s);
+    if (zero_state &&
+        cudaMemsetAsync(state_buffer, 0, static_cast<size_t>(hv) * 128 * 128 * sizeof(float), st) != cudaSuccess)
+        return ok_or_cuda(-1);
+    const int64_t ch = 2 * static_cast<int64_t>(hk) * 128 + static_cast<int64_t>(hv) * 128, vd = static_cast<int64_t>(hv) * 128;
+    const __half *q = static_cast<const __half*>(qkv), *zz = static_cast<const __half*>(z), *bb = static_cast<const __half*>(b),
+                 *aa = static_cast<const __half*>(a);
+    __half* o = static_cast<__half*>(out);
+    int prev = 0;
+    for (int64_t t0 = 0; t0 < seq_len; t0 += 8) {
+        const int rows = static_cast<int>(seq_len - t0 < 8 ? seq_len - t0 : 8);
+        rc = xb::gdn_spec(st, o + t0 * vd, q + t0 * ch, zz + t0 * vd, bb + t0 * hv, aa + t0 * hv, A_log, dt_bias, norm_weight,
+                          state_buffer, pend_k, pend_d, pend_g, nullptr, 1, rows, prev, hv, hk, prev);
+        if (rc != 0) return ok_or_cuda(rc);
+        prev = rows;
+    }
+    return ok_or_cuda(xb::gdn_spec(st, o, q, zz, bb, aa, A_log, dt_bias, norm_weight, state_buffer, pend_k, pend_d, pend_g, nullptr,
+                                   1, 0, prev, hv, hk, prev));
+}
+
+/* ---- plain device memory and streams, for hosts that do not link the CUDA runtime themselves --------------- */
+int xinfer_device_alloc(size_t bytes, void** out) {
+    if (!out) return XINFER_ERR_INVALID_ARGUMENT;
+    *out = nullptr;
+    if (bytes == 0) return XINFER_OK;
+    if (cudaMalloc(out, bytes) != cudaSuccess) {
+        cudaGetLastError();
+        return XINFER_ERR_OUT_OF_MEMORY;
+    }
+    return XINFER_OK;
+}
+void xinfer_device_free(void* p) {
+    if (p) cudaFree(p);
+}
+int xinfer_stream_create(xinfer_stream_t* out) {
+    if (!out) return XINFER_ERR_INVALID_ARGUMENT;
+    cudaStream_t st = nullptr;
+    if (cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking) != cudaSuccess) return ok_or_cuda(-1);
+    *out = st;
+    return XINFER_OK;
+}
+void xinfer_stream_destroy(xinfer_stream_t s) {
+    if (s) cudaStreamDestroy(static_cast<cudaStream_t>(s));
+}
+int xinfer_stream_synchronize(xinfer_stream_t s) {
+    return cudaStreamSynchronize(static_cast<cudaStream_t>(s)) == cudaSuccess ? XINFER_OK : ok_or_cuda(-1);
+}
+
+}  // extern "C"

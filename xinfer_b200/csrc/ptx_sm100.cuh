@@ -9,9 +9,20 @@
 
 namespace xb {
 
-// Every device-side wait gives up after this many SM clocks (about one second at 1.9 GHz).  A wait
-// that gives up sets the CTA's abort flag, the kernel records an error status and returns.
+// Default limit of every device-side wait, in SM clocks (about one second at 1.9 GHz).  A wait that
+// gives up sets the CTA's abort flag, the kernel records an error status and returns.  The limit a
+// kernel actually uses is a launch parameter (WaitState::limit).
 constexpr long long kWaitLimitClocks = 2000000000LL;
+
+// Shared by all waits of one CTA (lives in shared memory).  `dep_ready` is set once the CTA has seen the
+// previous kernel of the stream complete (griddepcontrol.wait returned): a wait that runs out before
+// that restarts its clock instead of giving up, so a long predecessor under programmatic dependent
+// launch cannot cause a false timeout.
+struct WaitState {
+    int abort_flag;
+    int dep_ready;
+    long long limit;
+};
 
 enum DeviceStatus : int {
     kStatusOk = 0,
@@ -81,16 +92,17 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // Bounded wait.  Returns false when the CTA is aborting (this wait ran out, or another one did).
 // The poll loop is kept to the try_wait and one counter: every instruction it issues competes with the
 // warps that have work, so the clock and the abort flag are only looked at every 256 polls.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile WaitState* ws) {
     if (mbar_try_wait(bar, parity)) return true;
-    const long long t0 = clock64();
+    long long t0 = clock64();
     while (true) {
 #pragma unroll 1
         for (int spins = 0; spins < 256; ++spins)
             if (mbar_try_wait(bar, parity)) return true;
-        if (*abort_flag) return false;
-        if (clock64() - t0 > kWaitLimitClocks) {
-            *abort_flag = 1;
+        if (ws->abort_flag) return false;
+        if (clock64() - t0 > ws->limit) {
+            if (!ws->dep_ready) { t0 = clock64(); continue; }
+            ws->abort_flag = 1;
             return false;
         }
     }
@@ -112,14 +124,15 @@ __device__ __forceinline__ bool mbar_try_wait_parked(uint32_t bar, uint32_t pari
         : "memory");
     return ok != 0;
 }
-__device__ __forceinline__ bool mbar_wait_parked(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool mbar_wait_parked(uint32_t bar, uint32_t parity, volatile WaitState* ws) {
     if (mbar_try_wait_parked(bar, parity)) return true;
-    const long long t0 = clock64();
+    long long t0 = clock64();
     while (true) {
         if (mbar_try_wait_parked(bar, parity)) return true;
-        if (*abort_flag) return false;
-        if (clock64() - t0 > kWaitLimitClocks) {
-            *abort_flag = 1;
+        if (ws->abort_flag) return false;
+        if (clock64() - t0 > ws->limit) {
+            if (!ws->dep_ready) { t0 = clock64(); continue; }
+            ws->abort_flag = 1;
             return false;
         }
     }

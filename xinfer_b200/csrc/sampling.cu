@@ -45,7 +45,7 @@ __device__ __forceinline__ void better(float& v, int& i, float ov, int oi) {
 // grid = (chunks, rows).  `row_stride` is the distance between logit rows in floats.
 __global__ void __launch_bounds__(kThreads) logits_partials_kernel(const float* __restrict__ logits, long long row_stride,
                                                                    int vocab, float inv_t, int want_sum,
-                                                                   Partial* __restrict__ out, int chunks) {
+                                                                   Partial* __restrict__ out, int chunks, int idx_offset) {
     const int row = blockIdx.y;
     const int chunk = blockIdx.x;
     const float* l = logits + static_cast<long long>(row) * row_stride;
@@ -101,7 +101,7 @@ __global__ void __launch_bounds__(kThreads) logits_partials_kernel(const float* 
     __syncthreads();
     Partial res;
     res.max_raw = s_v[0];
-    res.idx = s_i[0];
+    res.idx = s_i[0] < 0 ? -1 : s_i[0] + idx_offset;  // vocabulary slice of an N-split LM head: global token id
     res.max_scaled = 0.f;
     res.sum_exp = 0.f;
     if (want_sum) {
@@ -151,12 +151,14 @@ __global__ void publish_partials_kernel(const Partial* in, int chunks, float* pa
     }
 }
 
-__device__ __forceinline__ void merge_row(const Partial* p, int chunks, int lane, float& mx, int& idx, float& ms,
-                                          float& se) {
+// `p` points at the row's chunk partials of the first vocabulary slice; slice r's are r * slice_stride entries
+// further (one slice per rank of an N-split LM head; nslices = 1 otherwise).
+__device__ __forceinline__ void merge_row(const Partial* p, int chunks, int nslices, long long slice_stride, int lane,
+                                          float& mx, int& idx, float& ms, float& se) {
     // one warp merges the chunk partials of one row
     mx = -INFINITY; idx = -1; ms = -INFINITY; se = 0.f;
-    for (int c = lane; c < chunks; c += 32) {
-        const Partial q = p[c];
+    for (int c = lane; c < chunks * nslices; c += 32) {
+        const Partial q = p[static_cast<long long>(c / chunks) * slice_stride + (c % chunks)];
         better(mx, idx, q.max_raw, q.idx);
         if (q.max_scaled > ms) { se = se * expf(ms - q.max_scaled) + q.sum_exp; ms = q.max_scaled; }
         else if (q.sum_exp > 0.f) se += q.sum_exp * expf(q.max_scaled - ms);
@@ -176,16 +178,18 @@ __device__ __forceinline__ void merge_row(const Partial* p, int chunks, int lane
     }
 }
 
-__global__ void argmax_finish_kernel(const Partial* partials, int chunks, long long* out) {
+__global__ void argmax_finish_kernel(const Partial* partials, int chunks, int nslices, long long slice_stride,
+                                     long long* out) {
     const int row = blockIdx.x;
     float mx, ms, se;
     int idx;
-    merge_row(partials + static_cast<long long>(row) * chunks, chunks, threadIdx.x, mx, idx, ms, se);
+    merge_row(partials + static_cast<long long>(row) * chunks, chunks, nslices, slice_stride, threadIdx.x, mx, idx, ms, se);
     if (threadIdx.x == 0) out[row] = idx < 0 ? 0 : idx;
 }
 
 // One warp per sequence.  Rows of sequence b are b * rows_per_seq + i.
-__global__ void accept_finish_kernel(const Partial* partials, int chunks, const float* logits, long long row_stride,
+__global__ void accept_finish_kernel(const Partial* partials, int chunks, int nslices, long long slice_stride,
+                                     const float* logits, long long row_stride,
                                      int vocab, float inv_t, const long long* draft_tokens, const float* draft_probs,
                                      const float* uniforms, int num_draft, int rows_per_seq, int bonus_row,
                                      AcceptOut* out) {
@@ -204,7 +208,7 @@ __global__ void accept_finish_kernel(const Partial* partials, int chunks, const 
         const long long row = static_cast<long long>(b) * rows_per_seq + i;
         float mx, ms, se;
         int t;
-        merge_row(partials + row * chunks, chunks, lane, mx, t, ms, se);
+        merge_row(partials + row * chunks, chunks, nslices, slice_stride, lane, mx, t, ms, se);
         const long long d = draft_tokens[static_cast<long long>(b) * num_draft + i];
         bool accepted;
         if (!draft_probs) {
@@ -238,7 +242,7 @@ __global__ void accept_finish_kernel(const Partial* partials, int chunks, const 
         const long long row = static_cast<long long>(b) * rows_per_seq + bonus_row;
         float mx, ms, se;
         int t;
-        merge_row(partials + row * chunks, chunks, lane, mx, t, ms, se);
+        merge_row(partials + row * chunks, chunks, nslices, slice_stride, lane, mx, t, ms, se);
         r.bonus_or_resampled_token = t;
     }
     if (lane == 0) out[b] = r;
@@ -277,16 +281,40 @@ size_t sampling_scratch_bytes(long long rows, long long vocab) {
     return static_cast<size_t>(rows) * sampling_chunks(vocab) * sizeof(Partial);
 }
 
+int sampling_partials(cudaStream_t stream, const float* logits, long long row_stride, int rows, long long vocab,
+                      float inv_temperature, bool want_sum, long long idx_offset, void* partials_out) {
+    const int chunks = sampling_chunks(vocab);
+    logits_partials_kernel<<<dim3(chunks, rows), kThreads, 0, stream>>>(
+        logits, row_stride, static_cast<int>(vocab), inv_temperature, want_sum ? 1 : 0, static_cast<Partial*>(partials_out),
+        chunks, static_cast<int>(idx_offset));
+    return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+int argmax_finish(cudaStream_t stream, const void* partials, int chunks, int nslices, long long slice_stride, int rows,
+                  long long* out_dev) {
+    argmax_finish_kernel<<<rows, 32, 0, stream>>>(static_cast<const Partial*>(partials), chunks, nslices, slice_stride, out_dev);
+    return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+int accept_finish(cudaStream_t stream, const void* partials, int chunks, int nslices, long long slice_stride,
+                  const float* logits, long long row_stride, long long vocab, float inv_temperature,
+                  const long long* draft_tokens, const float* draft_probs, const float* uniforms, int batch,
+                  int num_draft, int rows_per_seq, int bonus_row, AcceptOut* out_dev) {
+    if (nslices > 1 && draft_probs) return -2;  // the stochastic rule reads the draft token's logit: one slice only
+    accept_finish_kernel<<<batch, 32, 0, stream>>>(static_cast<const Partial*>(partials), chunks, nslices, slice_stride, logits,
+                                                   row_stride, static_cast<int>(vocab), inv_temperature, draft_tokens,
+                                                   draft_probs, uniforms, num_draft, rows_per_seq, bonus_row, out_dev);
+    return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
 int argmax_rows(cudaStream_t stream, const float* logits, long long row_stride, int rows, long long vocab,
                 void* scratch, long long* out_dev, float* partial_max, long long* partial_idx) {
     const int chunks = sampling_chunks(vocab);
     Partial* part = static_cast<Partial*>(scratch);
-    logits_partials_kernel<<<dim3(chunks, rows), kThreads, 0, stream>>>(logits, row_stride, static_cast<int>(vocab),
-                                                                        1.0f, 0, part, chunks);
+    if (sampling_partials(stream, logits, row_stride, rows, vocab, 1.0f, false, 0, part) != 0) return -1;
     if (partial_max && partial_idx && rows == 1)
         publish_partials_kernel<<<(chunks + 127) / 128, 128, 0, stream>>>(part, chunks, partial_max, partial_idx);
-    argmax_finish_kernel<<<rows, 32, 0, stream>>>(part, chunks, out_dev);
-    return cudaGetLastError() == cudaSuccess ? 0 : -1;
+    return argmax_finish(stream, part, chunks, 1, 0, rows, out_dev);
 }
 
 int accept_reject_batched(cudaStream_t stream, const float* logits, long long row_stride, long long vocab,
@@ -294,14 +322,11 @@ int accept_reject_batched(cudaStream_t stream, const float* logits, long long ro
                           const float* uniforms, int batch, int num_draft, int rows_per_seq, int bonus_row,
                           void* scratch, AcceptOut* out_dev) {
     const int chunks = sampling_chunks(vocab);
-    Partial* part = static_cast<Partial*>(scratch);
     const int rows = batch * rows_per_seq;
-    logits_partials_kernel<<<dim3(chunks, rows), kThreads, 0, stream>>>(
-        logits, row_stride, static_cast<int>(vocab), inv_temperature, draft_probs ? 1 : 0, part, chunks);
-    accept_finish_kernel<<<batch, 32, 0, stream>>>(part, chunks, logits, row_stride, static_cast<int>(vocab),
-                                                   inv_temperature, draft_tokens, draft_probs, uniforms, num_draft,
-                                                   rows_per_seq, bonus_row, out_dev);
-    return cudaGetLastError() == cudaSuccess ? 0 : -1;
+    if (sampling_partials(stream, logits, row_stride, rows, vocab, inv_temperature, draft_probs != nullptr, 0, scratch) != 0)
+        return -1;
+    return accept_finish(stream, scratch, chunks, 1, 0, logits, row_stride, vocab, inv_temperature, draft_tokens,
+                         draft_probs, uniforms, batch, num_draft, rows_per_seq, bonus_row, out_dev);
 }
 
 int philox_uniform(cudaStream_t stream, float* out, long long n, unsigned long long seed, unsigned long long subseq) {

@@ -23,6 +23,18 @@ struct AcceptOut {
 int sampling_chunks(long long vocab);
 size_t sampling_scratch_bytes(long long rows, long long vocab);
 
+// The two halves of the calls below, for an LM head whose vocabulary is split over ranks: every rank runs
+// sampling_partials over its slice (idx_offset = first token id of the slice), the partial blocks are
+// exchanged, and the finish kernels merge `nslices` blocks that lie `slice_stride` entries apart.
+int sampling_partials(cudaStream_t stream, const float* logits, long long row_stride, int rows, long long vocab,
+                      float inv_temperature, bool want_sum, long long idx_offset, void* partials_out);
+int argmax_finish(cudaStream_t stream, const void* partials, int chunks, int nslices, long long slice_stride, int rows,
+                  long long* out_dev);
+int accept_finish(cudaStream_t stream, const void* partials, int chunks, int nslices, long long slice_stride,
+                  const float* logits, long long row_stride, long long vocab, float inv_temperature,
+                  const long long* draft_tokens, const float* draft_probs, const float* uniforms, int batch,
+                  int num_draft, int rows_per_seq, int bonus_row, AcceptOut* out_dev);
+
 int argmax_rows(cudaStream_t stream, const float* logits, long long row_stride, int rows, long long vocab,
                 void* scratch, long long* out_dev, float* partial_max, long long* partial_idx);
 

@@ -25,8 +25,9 @@
 
 #include "../../include/xinfer_b200.h"
 #include "mixers.h"
-#include "w4a16.h"
 #include "sampling.h"
+#include "tp_host.h"
+#include "w4a16.h"
 
 namespace {
 
@@ -42,24 +43,26 @@ __device__ __forceinline__ float normal01(uint64_t seed, uint64_t i) {
     const float u1 = u01(seed, 2 * i), u2 = u01(seed, 2 * i + 1);
     return sqrtf(-2.0f * logf(u1)) * cosf(6.28318530718f * u2);
 }
-__global__ void init_bytes_kernel(uint8_t* p, size_t n, uint64_t seed) {
+// Every initialiser hashes the element's GLOBAL index (`off` + local index), so a rank that holds only a slice
+// of a tensor (N-split weights, the sequences it owns) gets exactly the values of the unsharded tensor.
+__global__ void init_bytes_kernel(uint8_t* p, size_t n, uint64_t seed, size_t off) {
     size_t i = (static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x) * 4;
     if (i + 3 < n) {
-        *reinterpret_cast<uint32_t*>(p + i) = mix32(seed * 0x9E3779B97F4A7C15ULL + i);
+        *reinterpret_cast<uint32_t*>(p + i) = mix32(seed * 0x9E3779B97F4A7C15ULL + off + i);
     } else {
-        for (; i < n; ++i) p[i] = static_cast<uint8_t>(mix32(seed * 0x9E3779B97F4A7C15ULL + i));
+        for (; i < n; ++i) p[i] = static_cast<uint8_t>(mix32(seed * 0x9E3779B97F4A7C15ULL + off + i));
     }
 }
 // mode 0: |N(0, sigma)| / 7 (int4 group scales)   mode 1: mean + N(0, sigma)
-__global__ void init_half_kernel(__half* p, size_t n, uint64_t seed, int mode, float mean, float sigma) {
+__global__ void init_half_kernel(__half* p, size_t n, uint64_t seed, int mode, float mean, float sigma, size_t off) {
     const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (i >= n) return;
-    const float z = normal01(seed, i);
+    const float z = normal01(seed, off + i);
     p[i] = __float2half_rn(mode == 0 ? fabsf(z * sigma) / 7.0f : mean + z * sigma);
 }
-__global__ void init_float_kernel(float* p, size_t n, uint64_t seed, float mean, float sigma) {
+__global__ void init_float_kernel(float* p, size_t n, uint64_t seed, float mean, float sigma, size_t off) {
     const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-    if (i < n) p[i] = mean + normal01(seed, i) * sigma;
+    if (i < n) p[i] = mean + normal01(seed, off + i) * sigma;
 }
 __global__ void init_bf16_kernel(uint16_t* p, size_t n, uint64_t seed, float sigma) {
     const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -74,10 +77,18 @@ __global__ void add_int_kernel(int* out, const int* in, int n, int v) {
     if (i < n) out[i] = in[i] + v;
 }
 
+// A projection as this rank holds it: `n` output rows starting at row `row0` of the full [n_full][k] matrix
+// (n == n_full, row0 == 0 when it is not split).
 struct Linear {
     uint8_t* w = nullptr;
     __half* s = nullptr;
-    int64_t n = 0, k = 0;
+    int64_t n = 0, k = 0, n_full = 0, row0 = 0;
+};
+
+// An activation buffer; `off` is its byte offset in the exchange region when other ranks write into it.
+struct XBuf {
+    __half* p = nullptr;
+    size_t off = 0;
 };
 
 struct Layer {
@@ -102,71 +113,110 @@ struct xinfer_spec_decoder {
     int64_t max_seq = 0;
     uint64_t seed = 0;
     int device = 0;
-    std::vector<void*> allocs;
+    // N-split tensor parallelism (world == 1: none).  This rank owns the sequences [b0, b0 + bl).
+    xinfer_tp* tp = nullptr;
+    int rank = 0, world = 1, bl = 0, b0 = 0;
+    // one device block for weights, state and activations
+    xinfer_arena* arena = nullptr;
+    bool sizing = false;
+    size_t need_bytes = 0;
     std::vector<Layer> layers;
     Layer mtp_layer;
     Linear mtp_fc, lm_head;
     float *mtp_enorm = nullptr, *mtp_hnorm = nullptr, *final_norm = nullptr;
     uint16_t* embed = nullptr;
-    // sequence state
+    // sequence state (all sequences, replicated on every rank)
     int *ctx = nullptr, *ctx_draft = nullptr, *n_commit = nullptr, *n_commit_zero = nullptr;
     long long *cur_tok = nullptr, *draft = nullptr, *verify_tokens = nullptr, *argmax_out = nullptr, *emitted = nullptr;
     int* emitted_n = nullptr;
     __half *h_last = nullptr, *mtp_hidden = nullptr;
     xinfer_accept_record* records = nullptr;
-    // activations (rows up to batch * (k + 1))
-    __half *x = nullptr, *normed = nullptr, *proj_out = nullptr, *mlp = nullptr, *q_gate = nullptr, *qbuf = nullptr,
-           *kbuf = nullptr, *vbuf = nullptr, *attn_out = nullptr, *qkv_raw = nullptr, *qkv_conv = nullptr, *zbuf = nullptr,
-           *bbuf = nullptr, *abuf = nullptr, *delta_out = nullptr, *cat = nullptr;
+    // activations (rows up to batch * (k + 1)); XBufs are written by other ranks under tensor parallelism
+    __half *x = nullptr, *emb = nullptr, *normed = nullptr, *qbuf = nullptr, *qkv_conv = nullptr, *bbuf = nullptr,
+           *abuf = nullptr, *cat = nullptr;
+    XBuf x_mtp, proj_out, mlp, q_gate, kbuf, vbuf, attn_out, qkv_raw, zbuf, delta_out, partials;
     float *logits = nullptr, *attn_scratch = nullptr;
+    int64_t vocab_local = 0;
     // pinned result staging
     long long* h_emitted = nullptr;
     int* h_emitted_n = nullptr;
     long long* draft_override = nullptr;  // test hook: when armed, the verify pass checks these tokens instead
     bool override_armed = false;
     int prev_rows = 0;       // rows of the previous target pass (for the lazy state commit)
+    int64_t ctx_upper = 0;   // host-side upper bound of every sequence's context length
     cudaGraphExec_t graph_exec = nullptr;
     cudaGraph_t graph = nullptr;
+    xb::TcPlan* plan = nullptr;  // this decoder's launch plan (next-launch prefetch hints)
     std::string error;
     size_t weight_bytes = 0, state_bytes = 0;
     long long launches_per_step = 0;
     bool linears_only = false;   // measurement mode: enqueue only the W4A16 launches of a step
     long long linear_launches = 0;
-    double linear_bytes = 0;     // algorithmic bytes of those launches
+    double linear_bytes = 0;     // algorithmic bytes of those launches (this rank's share)
+    long long exchanges_per_step = 0;
 };
 
 namespace {
 
 using Dec = xinfer_spec_decoder;
 
+constexpr size_t kAlign = 256;
+
+// Sizing pass: only adds up.  Real pass: carves the arena.
 template <typename T>
 T* dalloc(Dec* d, size_t count, bool is_state = false) {
-    void* p = nullptr;
     if (count == 0) count = 1;
-    if (cudaMalloc(&p, count * sizeof(T)) != cudaSuccess) throw std::bad_alloc();
-    d->allocs.push_back(p);
-    (is_state ? d->state_bytes : d->weight_bytes) += count * sizeof(T);
+    const size_t bytes = (count * sizeof(T) + kAlign - 1) & ~(kAlign - 1);
+    (is_state ? d->state_bytes : d->weight_bytes) += d->sizing ? 0 : count * sizeof(T);
+    if (d->sizing) {
+        d->need_bytes += bytes;
+        return nullptr;
+    }
+    void* p = nullptr;
+    if (xinfer_arena_allocate(d->arena, bytes, kAlign, &p) != XINFER_OK || !p) throw std::bad_alloc();
     return static_cast<T*>(p);
+}
+
+// An activation buffer that other ranks store into: from the exchange region when there are other ranks.
+XBuf xalloc(Dec* d, size_t halves) {
+    XBuf b;
+    if (d->world <= 1) {
+        b.p = dalloc<__half>(d, halves, true);
+        return b;
+    }
+    if (d->sizing) return b;
+    if (xinfer_tp_alloc(d->tp, halves * sizeof(__half), &b.off) != XINFER_OK) throw std::bad_alloc();
+    b.p = static_cast<__half*>(xinfer_tp_ptr(d->tp, b.off));
+    d->state_bytes += halves * sizeof(__half);
+    return b;
 }
 
 unsigned blocks_for(size_t n, int per) { return static_cast<unsigned>((n + per - 1) / per); }
 
 uint64_t next_seed(Dec* d) { return d->seed = d->seed * 6364136223846793005ULL + 1442695040888963407ULL; }
 
-Linear make_linear(Dec* d, int64_t n, int64_t k) {
+// `split`: under tensor parallelism this rank holds the output rows [rank n/world, (rank + 1) n/world).
+Linear make_linear(Dec* d, int64_t n, int64_t k, bool split) {
     Linear l;
-    l.n = n;
+    l.n_full = n;
     l.k = k;
-    const size_t wb = static_cast<size_t>(n) * (k / 2), sc = static_cast<size_t>(n) * (k / 128);
+    const bool sp = split && d->world > 1;
+    l.n = sp ? n / d->world : n;
+    l.row0 = sp ? d->rank * l.n : 0;
+    const size_t wb = static_cast<size_t>(l.n) * (k / 2), sc = static_cast<size_t>(l.n) * (k / 128);
     l.w = dalloc<uint8_t>(d, wb);
     l.s = dalloc<__half>(d, sc);
-    init_bytes_kernel<<<blocks_for((wb + 3) / 4, 256), 256>>>(l.w, wb, next_seed(d));
-    init_half_kernel<<<blocks_for(sc, 256), 256>>>(l.s, sc, next_seed(d), 0, 0.f, 0.02f);
+    const uint64_t sw = next_seed(d), ss = next_seed(d);
+    if (!d->sizing) {
+        init_bytes_kernel<<<blocks_for((wb + 3) / 4, 256), 256>>>(l.w, wb, sw, static_cast<size_t>(l.row0) * (k / 2));
+        init_half_kernel<<<blocks_for(sc, 256), 256>>>(l.s, sc, ss, 0, 0.f, 0.02f, static_cast<size_t>(l.row0) * (k / 128));
+    }
     return l;
 }
 float* make_floats(Dec* d, size_t n, float mean, float sigma) {
     float* p = dalloc<float>(d, n);
-    init_float_kernel<<<blocks_for(n, 256), 256>>>(p, n, next_seed(d), mean, sigma);
+    const uint64_t sd = next_seed(d);
+    if (!d->sizing) init_float_kernel<<<blocks_for(n, 256), 256>>>(p, n, sd, mean, sigma, 0);
     return p;
 }
 
@@ -176,38 +226,109 @@ void make_layer(Dec* d, Layer& L, bool full) {
     L.full = full;
     L.input_norm = make_floats(d, H, 1.0f, 0.02f);
     L.post_norm = make_floats(d, H, 1.0f, 0.02f);
-    L.gate = make_linear(d, F, H);
-    L.up = make_linear(d, F, H);
-    L.down = make_linear(d, H, F);
+    L.gate = make_linear(d, F, H, true);
+    L.up = make_linear(d, F, H, true);
+    L.down = make_linear(d, H, F, true);
     if (full) {
-        L.q_proj = make_linear(d, c.num_attention_heads * 512, H);
-        L.k_proj = make_linear(d, c.num_key_value_heads * 256, H);
-        L.v_proj = make_linear(d, c.num_key_value_heads * 256, H);
-        L.o_proj = make_linear(d, H, c.num_attention_heads * 256);
+        L.q_proj = make_linear(d, c.num_attention_heads * 512, H, true);
+        L.k_proj = make_linear(d, c.num_key_value_heads * 256, H, true);
+        L.v_proj = make_linear(d, c.num_key_value_heads * 256, H, true);
+        L.o_proj = make_linear(d, H, c.num_attention_heads * 256, true);
         L.q_norm = make_floats(d, 256, 1.0f, 0.02f);
         L.k_norm = make_floats(d, 256, 1.0f, 0.02f);
-        const size_t kv = static_cast<size_t>(d->batch) * d->max_seq * c.num_key_value_heads * 256;
+        const size_t kv = static_cast<size_t>(d->bl) * d->max_seq * c.num_key_value_heads * 256;
         L.k_cache = dalloc<__half>(d, kv, true);
         L.v_cache = dalloc<__half>(d, kv, true);
     } else {
         const int64_t hv = c.linear_num_v_heads, hk = c.linear_num_k_heads;
         const int64_t ch = 2 * hk * 128 + hv * 128;
-        L.in_qkv = make_linear(d, ch, H);
-        L.in_z = make_linear(d, hv * 128, H);
-        L.in_b = make_linear(d, hv, H);
-        L.in_a = make_linear(d, hv, H);
-        L.out_proj = make_linear(d, H, hv * 128);
+        L.in_qkv = make_linear(d, ch, H, true);
+        L.in_z = make_linear(d, hv * 128, H, true);
+        L.in_b = make_linear(d, hv, H, false);  // tiny projections: every rank computes them whole
+        L.in_a = make_linear(d, hv, H, false);
+        L.out_proj = make_linear(d, H, hv * 128, true);
         L.conv_w = make_floats(d, ch * 4, 0.0f, 0.5f);
         L.A_log = make_floats(d, hv, 0.5f, 0.5f);
         L.dt_bias = make_floats(d, hv, 0.0f, 0.5f);
         L.gdn_norm = make_floats(d, 128, 1.0f, 0.02f);
-        L.S = dalloc<float>(d, static_cast<size_t>(d->batch) * hv * 128 * 128, true);
-        L.pend_k = dalloc<float>(d, static_cast<size_t>(d->batch) * hv * 8 * 128, true);
-        L.pend_d = dalloc<float>(d, static_cast<size_t>(d->batch) * hv * 8 * 128, true);
-        L.pend_g = dalloc<float>(d, static_cast<size_t>(d->batch) * hv * 8, true);
-        L.conv_state = dalloc<float>(d, static_cast<size_t>(d->batch) * 3 * ch, true);
-        L.conv_pend = dalloc<float>(d, static_cast<size_t>(d->batch) * 8 * ch, true);
+        L.S = dalloc<float>(d, static_cast<size_t>(d->bl) * hv * 128 * 128, true);
+        L.pend_k = dalloc<float>(d, static_cast<size_t>(d->bl) * hv * 8 * 128, true);
+        L.pend_d = dalloc<float>(d, static_cast<size_t>(d->bl) * hv * 8 * 128, true);
+        L.pend_g = dalloc<float>(d, static_cast<size_t>(d->bl) * hv * 8, true);
+        L.conv_state = dalloc<float>(d, static_cast<size_t>(d->bl) * 3 * ch, true);
+        L.conv_pend = dalloc<float>(d, static_cast<size_t>(d->bl) * 8 * ch, true);
     }
+}
+
+// Everything the decoder keeps on the device, in a fixed order (run once to size the arena, once for real).
+void build_all(Dec* d) {
+    const auto& c = d->cfg;
+    const int64_t H = c.hidden_size, V = c.vocab_size;
+    const int batch = d->batch, k = d->k;
+    const int M = batch * (k + 1);
+    const uint64_t seed0 = d->seed;
+    d->layers.assign(static_cast<size_t>(c.num_hidden_layers), Layer());
+    const int interval = c.full_attention_interval > 0 ? c.full_attention_interval : 4;
+    for (int64_t l = 0; l < c.num_hidden_layers; ++l) make_layer(d, d->layers[l], (l % interval) == interval - 1);
+    make_layer(d, d->mtp_layer, true);
+    d->mtp_fc = make_linear(d, H, 2 * H, true);
+    d->lm_head = make_linear(d, V, H, true);
+    d->vocab_local = d->lm_head.n;
+    d->mtp_enorm = make_floats(d, H, 1.0f, 0.02f);
+    d->mtp_hnorm = make_floats(d, H, 1.0f, 0.02f);
+    d->final_norm = make_floats(d, H, 1.0f, 0.02f);
+    d->embed = dalloc<uint16_t>(d, static_cast<size_t>(V) * H);
+    const uint64_t se = next_seed(d);
+    if (!d->sizing)
+        init_bf16_kernel<<<blocks_for(static_cast<size_t>(V) * H, 256), 256>>>(d->embed, static_cast<size_t>(V) * H, se, 1.0f);
+    d->ctx = dalloc<int>(d, batch, true);
+    d->ctx_draft = dalloc<int>(d, batch, true);
+    d->n_commit = dalloc<int>(d, batch, true);
+    d->n_commit_zero = dalloc<int>(d, batch, true);
+    d->cur_tok = dalloc<long long>(d, batch, true);
+    d->draft = dalloc<long long>(d, static_cast<size_t>(batch) * k, true);
+    d->verify_tokens = dalloc<long long>(d, M, true);
+    d->argmax_out = dalloc<long long>(d, M, true);
+    d->emitted = dalloc<long long>(d, M, true);
+    d->emitted_n = dalloc<int>(d, batch, true);
+    d->h_last = dalloc<__half>(d, static_cast<size_t>(batch) * H, true);
+    d->mtp_hidden = dalloc<__half>(d, static_cast<size_t>(batch) * H, true);
+    d->records = dalloc<xinfer_accept_record>(d, batch, true);
+    d->draft_override = dalloc<long long>(d, static_cast<size_t>(batch) * k, true);
+    const int64_t hv = c.linear_num_v_heads, hk = c.linear_num_k_heads, ch = 2 * hk * 128 + hv * 128;
+    d->x = dalloc<__half>(d, static_cast<size_t>(M) * H, true);
+    d->emb = dalloc<__half>(d, static_cast<size_t>(batch) * H, true);
+    d->normed = dalloc<__half>(d, static_cast<size_t>(M) * H, true);
+    d->qbuf = dalloc<__half>(d, static_cast<size_t>(M) * c.num_attention_heads * 256, true);
+    d->qkv_conv = dalloc<__half>(d, static_cast<size_t>(M) * ch, true);
+    d->bbuf = dalloc<__half>(d, static_cast<size_t>(M) * hv, true);
+    d->abuf = dalloc<__half>(d, static_cast<size_t>(M) * hv, true);
+    d->cat = dalloc<__half>(d, static_cast<size_t>(batch) * 2 * H, true);
+    d->logits = dalloc<float>(d, static_cast<size_t>(M) * d->vocab_local, true);
+    // buffers that other ranks store into (same order on every rank: an offset names the same buffer everywhere)
+    d->x_mtp = xalloc(d, static_cast<size_t>(batch) * H);
+    d->proj_out = xalloc(d, static_cast<size_t>(M) * H);
+    d->mlp = xalloc(d, static_cast<size_t>(M) * c.intermediate_size);
+    d->q_gate = xalloc(d, static_cast<size_t>(M) * c.num_attention_heads * 512);
+    d->kbuf = xalloc(d, static_cast<size_t>(M) * c.num_key_value_heads * 256);
+    d->vbuf = xalloc(d, static_cast<size_t>(M) * c.num_key_value_heads * 256);
+    d->attn_out = xalloc(d, static_cast<size_t>(M) * c.num_attention_heads * 256);
+    d->qkv_raw = xalloc(d, static_cast<size_t>(M) * ch);
+    d->zbuf = xalloc(d, static_cast<size_t>(M) * hv * 128);
+    d->delta_out = xalloc(d, static_cast<size_t>(M) * hv * 128);
+    // (row, chunk) partials of the sampling kernels, one block per vocabulary slice
+    d->partials = xalloc(d, static_cast<size_t>(d->world) * xb::sampling_scratch_bytes(M, d->vocab_local) / sizeof(__half));
+    {
+        // KV splits: with one attention CTA per SM, two waves of CTAs over (split, kv head, sequence)
+        int sms = 148;
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, d->device);
+        const int units = d->bl * static_cast<int>(c.num_key_value_heads);
+        int splits = (2 * sms) / (units > 0 ? units : 1);
+        d->attn_splits = splits < 1 ? 1 : (splits > 16 ? 16 : splits);
+    }
+    d->attn_scratch = dalloc<float>(
+        d, xb::attn_scratch_bytes(d->bl, static_cast<int>(c.num_key_value_heads), d->attn_splits) / sizeof(float), true);
+    if (d->sizing) d->seed = seed0;  // the real pass draws the same seeds again
 }
 
 #define NL(expr)                                                        \
@@ -224,114 +345,207 @@ void make_layer(Dec* d, Layer& L, bool full) {
         }                                                               \
     } while (0)
 
+#define CKCUDA(expr)                                                    \
+    do {                                                                \
+        if ((expr) != cudaSuccess) {                                    \
+            d->error = std::string(#expr) + " failed";                  \
+            cudaGetLastError();                                         \
+            return XINFER_ERR_CUDA;                                     \
+        }                                                               \
+    } while (0)
+
 void account(Dec* d, const Linear& l, int M, int out_bytes, bool count_x) {
     d->linear_bytes += static_cast<double>(l.n) * (l.k / 2) + static_cast<double>(l.n) * (l.k / 128) * 2 +
                        (count_x ? static_cast<double>(M) * l.k * 2 : 0.0) + static_cast<double>(M) * l.n * out_bytes;
 }
 
-int lin(Dec* d, cudaStream_t s, __half* y, const __half* x, const Linear& l, int M) {
-    ++d->launches_per_step;
-    ++d->linear_launches;
-    account(d, l, M, 2, true);
-    return xinfer_linear_int4_f16f16(s, y, x, l.w, l.s, nullptr, M, l.n, l.k, 128);
+// How an N-split projection's output travels: to every rank, or only to the rank that owns the row's sequence.
+enum Push { kLocal = 0, kAll = 1, kOwner = 2 };
+
+// One projection of a (possibly fused) launch as this rank runs it: its slice of W writes the columns
+// [row0, row0 + n) of the full-width output `y` (row stride n_full), on this rank and - push - on the others.
+xb::TcProj make_proj(const Dec* d, const Linear& l, const XBuf& y, int push) {
+    xb::TcProj p;
+    p.w = l.w;
+    p.scales = l.s;
+    p.bias = nullptr;
+    p.n = l.n;
+    p.ldy = l.n_full;
+    p.y = y.p + l.row0;
+    if (d->world > 1 && push != kLocal) xb::tp_fill_proj(d->tp, &p, y.off + static_cast<size_t>(l.row0) * sizeof(__half), push);
+    return p;
+}
+xb::TcProj make_proj_local(const Linear& l, void* y) {
+    xb::TcProj p;
+    p.w = l.w;
+    p.scales = l.s;
+    p.bias = nullptr;
+    p.n = l.n;
+    p.ldy = l.n;
+    p.y = y;
+    return p;
 }
 
-// One decoder layer on M = batch * R rows; `x` is updated in place (the second residual add is folded
-// into the next layer's norm by the caller through `pending_delta`).
-int layer_forward(Dec* d, cudaStream_t s, Layer& L, int R, const int* ctx, const int* n_commit, int prev_rows,
-                  bool first, const float* next_norm_unused) {
-    (void)next_norm_unused;
+// Launches `num` projections sharing X (or a gate/up pair) on the tensor-core kernel; with other ranks around
+// the launch ends with the exchange handshake, so when it completes every rank's slice has arrived here.
+int run_lin(Dec* d, cudaStream_t s, const void* x, xb::TcProj* pr, int num, bool swiglu, bool out_f32, int M, int64_t K,
+            int rows_per_rank, bool exchange) {
+    ++d->launches_per_step;
+    ++d->linear_launches;
+    if (d->world > 1 && exchange) {
+        ++d->exchanges_per_step;
+        const xb::TpLink link = xb::tp_link(d->tp, rows_per_rank);
+        return xb::run_tc_linear(s, x, pr, num, swiglu, out_f32, M, K, 128, &link);
+    }
+    return xb::run_tc_linear(s, x, pr, num, swiglu, out_f32, M, K, 128, nullptr);
+}
+
+int lin(Dec* d, cudaStream_t s, const XBuf& y, const __half* x, const Linear& l, int M, int push) {
+    account(d, l, M, 2, true);
+    xb::TcProj p = make_proj(d, l, y, push);
+    return run_lin(d, s, x, &p, 1, false, false, M, l.k, 1, push != kLocal);
+}
+
+// All-gather by rows of a buffer whose rows [row0, row0 + rows) this rank has just produced.
+int gather_rows(Dec* d, cudaStream_t s, const XBuf& b, int row0, int rows, int64_t width) {
+    if (d->world <= 1 || d->linears_only) return 0;
+    ++d->launches_per_step;
+    ++d->exchanges_per_step;
+    const size_t rb = static_cast<size_t>(width) * sizeof(__half);
+    return xb::tp_push(d->tp, s, b.off + static_cast<size_t>(row0) * rb, static_cast<size_t>(rows) * rb) == 0 ? 0 : XINFER_ERR_CUDA;
+}
+
+// One decoder layer on M = batch * R rows; the residual stream `xr` is updated in place (the second residual
+// add is folded into the next norm by the caller).  Projections run on all M rows (N-split over the ranks);
+// the mixer runs on the rows of this rank's own sequences.
+int layer_forward(Dec* d, cudaStream_t s, Layer& L, int R, __half* xr, const XBuf* pending, const int* ctx,
+                  const int* n_commit, int prev_rows) {
     const auto& c = d->cfg;
     const int B = d->batch, M = B * R;
+    const int Bl = d->bl, Ml = Bl * R, row0 = d->b0 * R;
     const int H = static_cast<int>(c.hidden_size);
     // x += previous layer's MLP output (none for the first layer), then input RMSNorm
-    if (first) NL(xb::rmsnorm_rows(s, d->normed, H, d->x, L.input_norm, M, H, c.rms_norm_eps));
-    else NL(xb::add_rmsnorm_rows(s, d->normed, d->x, d->proj_out, L.input_norm, M, H, c.rms_norm_eps));
+    if (!pending) NL(xb::rmsnorm_rows(s, d->normed, H, xr, L.input_norm, M, H, c.rms_norm_eps));
+    else NL(xb::add_rmsnorm_rows(s, d->normed, xr, pending->p, L.input_norm, M, H, c.rms_norm_eps));
     ++d->launches_per_step;
     if (L.full) {
-        xinfer_fused_desc fd[3] = {{d->q_gate, L.q_proj.w, L.q_proj.s, nullptr, L.q_proj.n},
-                                   {d->kbuf, L.k_proj.w, L.k_proj.s, nullptr, L.k_proj.n},
-                                   {d->vbuf, L.v_proj.w, L.v_proj.s, nullptr, L.v_proj.n}};
-        CK(xinfer_linear_int4_fused_f16(s, d->normed, fd, 3, M, H, 128));
-        ++d->linear_launches;
+        const int hq = static_cast<int>(c.num_attention_heads), hkv = static_cast<int>(c.num_key_value_heads);
+        xb::TcProj fd[3] = {make_proj(d, L.q_proj, d->q_gate, kOwner), make_proj(d, L.k_proj, d->kbuf, kOwner),
+                            make_proj(d, L.v_proj, d->vbuf, kOwner)};
         account(d, L.q_proj, M, 2, true);
         account(d, L.k_proj, M, 2, false);
         account(d, L.v_proj, M, 2, false);
-        NL(xb::attn_prep(s, d->qbuf, L.k_cache, L.v_cache, d->q_gate, d->kbuf, d->vbuf, L.q_norm, L.k_norm, ctx, B, R,
-                         static_cast<int>(c.num_attention_heads), static_cast<int>(c.num_key_value_heads), d->max_seq,
-                         c.rms_norm_eps, c.rope_theta, c.rope_dim));
-        NL(xb::attn_decode(s, d->attn_out, d->qbuf, d->q_gate, L.k_cache, L.v_cache, ctx, B, R,
-                           static_cast<int>(c.num_attention_heads), static_cast<int>(c.num_key_value_heads), d->max_seq,
-                           d->attn_splits, d->attn_scratch));
-        d->launches_per_step += 4;
-        CK(lin(d, s, d->proj_out, d->attn_out, L.o_proj, M));
+        CK(run_lin(d, s, d->normed, fd, 3, false, false, M, H, Ml, true));
+        NL(xb::attn_prep(s, d->qbuf + static_cast<size_t>(row0) * hq * 256, L.k_cache, L.v_cache,
+                         d->q_gate.p + static_cast<size_t>(row0) * hq * 512, d->kbuf.p + static_cast<size_t>(row0) * hkv * 256,
+                         d->vbuf.p + static_cast<size_t>(row0) * hkv * 256, L.q_norm, L.k_norm, ctx + d->b0, Bl, R, hq, hkv,
+                         d->max_seq, c.rms_norm_eps, c.rope_theta, c.rope_dim));
+        NL(xb::attn_decode(s, d->attn_out.p + static_cast<size_t>(row0) * hq * 256, d->qbuf + static_cast<size_t>(row0) * hq * 256,
+                           d->q_gate.p + static_cast<size_t>(row0) * hq * 512, L.k_cache, L.v_cache, ctx + d->b0, Bl, R, hq,
+                           hkv, d->max_seq, d->attn_splits, d->attn_scratch));
+        d->launches_per_step += 3;
+        CK(gather_rows(d, s, d->attn_out, row0, Ml, static_cast<int64_t>(hq) * 256));
+        CK(lin(d, s, d->proj_out, d->attn_out.p, L.o_proj, M, kAll));
     } else {
         const int hv = static_cast<int>(c.linear_num_v_heads), hk = static_cast<int>(c.linear_num_k_heads);
         const int ch = 2 * hk * 128 + hv * 128;
-        xinfer_fused_desc fd[4] = {{d->qkv_raw, L.in_qkv.w, L.in_qkv.s, nullptr, L.in_qkv.n},
-                                   {d->zbuf, L.in_z.w, L.in_z.s, nullptr, L.in_z.n},
-                                   {d->bbuf, L.in_b.w, L.in_b.s, nullptr, L.in_b.n},
-                                   {d->abuf, L.in_a.w, L.in_a.s, nullptr, L.in_a.n}};
-        CK(xinfer_linear_int4_fused_f16(s, d->normed, fd, 4, M, H, 128));
-        ++d->linear_launches;
+        xb::TcProj fd[4] = {make_proj(d, L.in_qkv, d->qkv_raw, kOwner), make_proj(d, L.in_z, d->zbuf, kOwner),
+                            make_proj_local(L.in_b, d->bbuf), make_proj_local(L.in_a, d->abuf)};
         account(d, L.in_qkv, M, 2, true);
         account(d, L.in_z, M, 2, false);
         account(d, L.in_b, M, 2, false);
         account(d, L.in_a, M, 2, false);
-        NL(xb::conv1d_spec(s, d->qkv_conv, d->qkv_raw, L.conv_w, L.conv_state, L.conv_pend, n_commit, B, R, prev_rows, ch));
-        NL(xb::gdn_spec(s, d->delta_out, d->qkv_conv, d->zbuf, d->bbuf, d->abuf, L.A_log, L.dt_bias, L.gdn_norm, L.S,
-                        L.pend_k, L.pend_d, L.pend_g, n_commit, B, R, prev_rows, hv, hk));
-        d->launches_per_step += 3;
-        CK(lin(d, s, d->proj_out, d->delta_out, L.out_proj, M));
+        CK(run_lin(d, s, d->normed, fd, 4, false, false, M, H, Ml, true));
+        NL(xb::conv1d_spec(s, d->qkv_conv + static_cast<size_t>(row0) * ch, d->qkv_raw.p + static_cast<size_t>(row0) * ch,
+                           L.conv_w, L.conv_state, L.conv_pend, n_commit + d->b0, Bl, R, prev_rows, ch));
+        NL(xb::gdn_spec(s, d->delta_out.p + static_cast<size_t>(row0) * hv * 128, d->qkv_conv + static_cast<size_t>(row0) * ch,
+                        d->zbuf.p + static_cast<size_t>(row0) * hv * 128, d->bbuf + static_cast<size_t>(row0) * hv,
+                        d->abuf + static_cast<size_t>(row0) * hv, L.A_log, L.dt_bias, L.gdn_norm, L.S, L.pend_k, L.pend_d,
+                        L.pend_g, n_commit + d->b0, Bl, R, prev_rows, hv, hk));
+        d->launches_per_step += 2;
+        CK(gather_rows(d, s, d->delta_out, row0, Ml, static_cast<int64_t>(hv) * 128));
+        CK(lin(d, s, d->proj_out, d->delta_out.p, L.out_proj, M, kAll));
     }
     // x += mixer output, post-attention RMSNorm
-    NL(xb::add_rmsnorm_rows(s, d->normed, d->x, d->proj_out, L.post_norm, M, H, c.rms_norm_eps));
-    CK(xinfer_mlp_gate_up_swiglu_int4_f16(s, d->mlp, d->normed, L.gate.w, L.gate.s, L.up.w, L.up.s, M, L.gate.n, H, 128));
-    ++d->linear_launches;
-    account(d, L.gate, M, 2, true);
-    d->linear_bytes += static_cast<double>(L.up.n) * (L.up.k / 2) + static_cast<double>(L.up.n) * (L.up.k / 128) * 2;
-    d->launches_per_step += 2;
-    CK(lin(d, s, d->proj_out, d->mlp, L.down, M));  // the caller adds proj_out into x
+    NL(xb::add_rmsnorm_rows(s, d->normed, xr, d->proj_out.p, L.post_norm, M, H, c.rms_norm_eps));
+    ++d->launches_per_step;
+    {
+        xb::TcProj gu[2] = {make_proj(d, L.gate, d->mlp, kAll), make_proj_local(L.up, nullptr)};
+        account(d, L.gate, M, 2, true);
+        d->linear_bytes += static_cast<double>(L.up.n) * (L.up.k / 2) + static_cast<double>(L.up.n) * (L.up.k / 128) * 2;
+        CK(run_lin(d, s, d->normed, gu, 2, true, false, M, H, 1, true));
+    }
+    CK(lin(d, s, d->proj_out, d->mlp.p, L.down, M, kAll));  // the caller adds proj_out into the residual stream
     return 0;
 }
 
-// final: x += last MLP output, final RMSNorm, LM head -> fp32 logits
-int head_forward(Dec* d, cudaStream_t s, int M) {
-    const auto& c = d->cfg;
-    const int H = static_cast<int>(c.hidden_size);
-    NL(xb::add_rmsnorm_rows(s, d->normed, d->x, d->proj_out, d->final_norm, M, H, c.rms_norm_eps));
-    CK(xinfer_linear_int4_f16f32(s, d->logits, d->normed, d->lm_head.w, d->lm_head.s, nullptr, M, d->lm_head.n,
-                                 d->lm_head.k, 128));
-    ++d->linear_launches;
+// LM head on M rows -> this rank's slice of the fp32 logits, then the (row, chunk) partials of the sampling
+// kernels over that slice; under tensor parallelism the partial blocks are exchanged so that every rank can
+// finish argmax / acceptance over the whole vocabulary.
+int lm_head_and_partials(Dec* d, cudaStream_t s, int M) {
+    xb::TcProj p = make_proj_local(d->lm_head, d->logits);
     account(d, d->lm_head, M, 4, true);
-    d->launches_per_step += 2;
+    CK(run_lin(d, s, d->normed, &p, 1, false, true, M, d->lm_head.k, 1, false));
+    if (d->linears_only) return 0;
+    const size_t block = xb::sampling_scratch_bytes(M, d->vocab_local);
+    uint8_t* mine = reinterpret_cast<uint8_t*>(d->partials.p) + static_cast<size_t>(d->rank) * block;
+    CK(xb::sampling_partials(s, d->logits, d->vocab_local, M, d->vocab_local, 1.0f, false, d->lm_head.row0, mine));
+    ++d->launches_per_step;
+    if (d->world > 1) {
+        ++d->launches_per_step;
+        ++d->exchanges_per_step;
+        if (xb::tp_push(d->tp, s, d->partials.off + static_cast<size_t>(d->rank) * block, block) != 0) return XINFER_ERR_CUDA;
+    }
     return 0;
 }
+long long partial_slice_stride(const Dec* d, int M) {
+    return static_cast<long long>(xb::sampling_scratch_bytes(M, d->vocab_local) / 16);  // in (row, chunk) entries
+}
 
-int draft_pass(Dec* d, cudaStream_t s, int i) {
+// The MTP head up to (and including) its attention layer's KV write for the token at position ctx + i.
+// `full`: the whole head (attention, MLP, final norm, LM head, argmax -> draft token i).  Otherwise only the
+// part that fills the head's KV slot: after k accepted drafts the next step's first draft pass attends to
+// position ctx + k, which no draft pass of this step has written.
+int draft_pass(Dec* d, cudaStream_t s, int i, bool full) {
     const auto& c = d->cfg;
     const int B = d->batch, H = static_cast<int>(c.hidden_size);
     const long long* tok = (i == 0) ? d->cur_tok : d->argmax_out;
     const __half* hprev = (i == 0) ? d->h_last : d->mtp_hidden;
     // cat = [rmsnorm(embed(tok)) ; rmsnorm(h_prev)]  ->  fc  ->  x
-    NL(xb::embed_rows(s, d->x, d->embed, tok, B, H, c.vocab_size));
-    NL(xb::rmsnorm_rows(s, d->cat, 2 * H, d->x, d->mtp_enorm, B, H, c.rms_norm_eps));
+    NL(xb::embed_rows(s, d->emb, d->embed, tok, B, H, c.vocab_size));
+    NL(xb::rmsnorm_rows(s, d->cat, 2 * H, d->emb, d->mtp_enorm, B, H, c.rms_norm_eps));
     NL(xb::rmsnorm_rows(s, d->cat + H, 2 * H, hprev, d->mtp_hnorm, B, H, c.rms_norm_eps));
-    CK(lin(d, s, d->x, d->cat, d->mtp_fc, B));
+    CK(lin(d, s, d->x_mtp, d->cat, d->mtp_fc, B, kAll));
     if (!d->linears_only) add_int_kernel<<<1, 64, 0, s>>>(d->ctx_draft, d->ctx, B, i);
     d->launches_per_step += 4;
-    CK(layer_forward(d, s, d->mtp_layer, 1, d->ctx_draft, d->n_commit_zero, 0, true, nullptr));
+    if (!full) {
+        // input norm -> k, v projections of the head's layer -> head norm, RoPE, cache write
+        Layer& L = d->mtp_layer;
+        const int hq = static_cast<int>(c.num_attention_heads), hkv = static_cast<int>(c.num_key_value_heads);
+        const int Bl = d->bl, row0 = d->b0;
+        NL(xb::rmsnorm_rows(s, d->normed, H, d->x_mtp.p, L.input_norm, B, H, c.rms_norm_eps));
+        // (the query projection is not needed: the prologue kernel is told there are no query heads)
+        xb::TcProj fd[2] = {make_proj(d, L.k_proj, d->kbuf, kOwner), make_proj(d, L.v_proj, d->vbuf, kOwner)};
+        account(d, L.k_proj, B, 2, true);
+        account(d, L.v_proj, B, 2, false);
+        CK(run_lin(d, s, d->normed, fd, 2, false, false, B, H, Bl, true));
+        (void)hq;
+        NL(xb::attn_prep(s, d->qbuf, L.k_cache, L.v_cache, d->q_gate.p, d->kbuf.p + static_cast<size_t>(row0) * hkv * 256,
+                         d->vbuf.p + static_cast<size_t>(row0) * hkv * 256, L.q_norm, L.k_norm, d->ctx_draft + d->b0, Bl, 1, 0,
+                         hkv, d->max_seq, c.rms_norm_eps, c.rope_theta, c.rope_dim));
+        d->launches_per_step += 2;
+        return 0;
+    }
+    CK(layer_forward(d, s, d->mtp_layer, 1, d->x_mtp.p, nullptr, d->ctx_draft, d->n_commit_zero, 0));
     // keep the head's output hidden for the next draft pass: x + proj_out (pre final norm)
-    NL(xb::add_rmsnorm_rows(s, d->normed, d->x, d->proj_out, d->final_norm, B, H, c.rms_norm_eps));
+    NL(xb::add_rmsnorm_rows(s, d->normed, d->x_mtp.p, d->proj_out.p, d->final_norm, B, H, c.rms_norm_eps));
     if (!d->linears_only)
-        cudaMemcpyAsync(d->mtp_hidden, d->x, static_cast<size_t>(B) * H * sizeof(__half), cudaMemcpyDeviceToDevice, s);
-    CK(xinfer_linear_int4_f16f32(s, d->logits, d->normed, d->lm_head.w, d->lm_head.s, nullptr, B, d->lm_head.n,
-                                 d->lm_head.k, 128));
-    ++d->linear_launches;
-    account(d, d->lm_head, B, 4, true);
-    NL(xinfer_argmax_rows(s, d->logits, c.vocab_size, B, c.vocab_size, reinterpret_cast<int64_t*>(d->argmax_out)));
+        CKCUDA(cudaMemcpyAsync(d->mtp_hidden, d->x_mtp.p, static_cast<size_t>(B) * H * sizeof(__half), cudaMemcpyDeviceToDevice, s));
+    CK(lm_head_and_partials(d, s, B));
+    NL(xb::argmax_finish(s, d->partials.p, xb::sampling_chunks(d->vocab_local), d->world, partial_slice_stride(d, B), B,
+                         d->argmax_out));
     NL(xb::copy_token_column(s, d->draft, d->argmax_out, B, d->k, i));
-    d->launches_per_step += 6;
+    d->launches_per_step += 4;
     return 0;
 }
 
@@ -341,8 +555,11 @@ int target_pass(Dec* d, cudaStream_t s, int R, const long long* tokens) {
     NL(xb::embed_rows(s, d->x, d->embed, tokens, M, H, c.vocab_size));
     ++d->launches_per_step;
     for (size_t l = 0; l < d->layers.size(); ++l)
-        CK(layer_forward(d, s, d->layers[l], R, d->ctx, d->n_commit, d->prev_rows, l == 0, nullptr));
-    CK(head_forward(d, s, M));
+        CK(layer_forward(d, s, d->layers[l], R, d->x, l == 0 ? nullptr : &d->proj_out, d->ctx, d->n_commit, d->prev_rows));
+    // final: x += last MLP output, final RMSNorm, LM head -> fp32 logits
+    NL(xb::add_rmsnorm_rows(s, d->normed, d->x, d->proj_out.p, d->final_norm, M, H, c.rms_norm_eps));
+    ++d->launches_per_step;
+    CK(lm_head_and_partials(d, s, M));
     if (!d->linears_only) d->prev_rows = R;
     return 0;
 }
@@ -353,27 +570,49 @@ int enqueue_step(Dec* d, cudaStream_t s) {
     d->launches_per_step = 0;
     d->linear_launches = 0;
     d->linear_bytes = 0;
+    d->exchanges_per_step = 0;
+    xb::TcPlan* prev_plan = xb::tc_plan_bind(d->plan);
     xb::tc_plan_rewind();  // the step's linears come in the recorded order (if a plan was recorded at capture)
-    for (int i = 0; i < k; ++i) CK(draft_pass(d, s, i));
-    if (d->override_armed && !d->linears_only)
-        cudaMemcpyAsync(d->draft, d->draft_override, static_cast<size_t>(B) * k * sizeof(long long), cudaMemcpyDeviceToDevice, s);
-    NL(xb::build_verify_tokens(s, d->verify_tokens, d->cur_tok, d->draft, B, k));
-    CK(target_pass(d, s, R, d->verify_tokens));
-    NL(xinfer_speculative_accept_reject_batched(s, reinterpret_cast<const int64_t*>(d->draft), d->logits, c.vocab_size,
-                                                c.vocab_size, nullptr, nullptr, 1.0f, B, k, R, k, d->records));
-    // x still holds the pre-norm hidden rows of the verify pass (head_forward added the last MLP output)
-    NL(xb::spec_commit(s, d->records, d->draft, B, k, R, d->ctx, d->n_commit, d->cur_tok, d->emitted, d->emitted_n,
-                       d->h_last, d->x, static_cast<int>(c.hidden_size)));
-    d->launches_per_step += 5;
-    return 0;
+    int rc = [&]() -> int {
+        for (int i = 0; i < k; ++i) CK(draft_pass(d, s, i, true));
+        CK(draft_pass(d, s, k, false));  // the head's KV slot at ctx + k
+        if (d->override_armed && !d->linears_only)
+            CKCUDA(cudaMemcpyAsync(d->draft, d->draft_override, static_cast<size_t>(B) * k * sizeof(long long),
+                                   cudaMemcpyDeviceToDevice, s));
+        NL(xb::build_verify_tokens(s, d->verify_tokens, d->cur_tok, d->draft, B, k));
+        CK(target_pass(d, s, R, d->verify_tokens));
+        NL(xb::accept_finish(s, d->partials.p, xb::sampling_chunks(d->vocab_local), d->world,
+                             partial_slice_stride(d, B * R), d->logits, d->vocab_local, d->vocab_local, 1.0f, d->draft, nullptr,
+                             nullptr, B, k, R, k, reinterpret_cast<xb::AcceptOut*>(d->records)));
+        // x still holds the pre-norm hidden rows of the verify pass (the final norm added the last MLP output)
+        NL(xb::spec_commit(s, d->records, d->draft, B, k, R, d->ctx, d->n_commit, d->cur_tok, d->emitted, d->emitted_n,
+                           d->h_last, d->x, static_cast<int>(c.hidden_size)));
+        d->launches_per_step += 4;
+        return 0;
+    }();
+    xb::tc_plan_bind(prev_plan);
+    return rc;
 }
 
 }  // namespace
 
 extern "C" {
 
-int xinfer_spec_decoder_create(const xinfer_model_config* cfg, int batch, int k, int64_t max_seq, uint64_t seed,
-                               xinfer_spec_decoder** out) {
+size_t xinfer_spec_decoder_exchange_bytes(const xinfer_model_config* cfg, int batch, int k, int world) {
+    if (!cfg || batch < 1 || k < 1 || world < 1) return 0;
+    const auto& c = *cfg;
+    const size_t M = static_cast<size_t>(batch) * (k + 1);
+    const size_t ch = static_cast<size_t>(2 * c.linear_num_k_heads * 128 + c.linear_num_v_heads * 128);
+    size_t halves = static_cast<size_t>(batch) * c.hidden_size + M * c.hidden_size + M * c.intermediate_size +
+                    M * c.num_attention_heads * 512 + 2 * M * c.num_key_value_heads * 256 + M * c.num_attention_heads * 256 +
+                    M * ch + 2 * M * c.linear_num_v_heads * 128;
+    const size_t vl = static_cast<size_t>(c.vocab_size) / world + 1;
+    const size_t part = static_cast<size_t>(world) * xb::sampling_scratch_bytes(static_cast<long long>(M), static_cast<long long>(vl));
+    return halves * 2 + part + 16 * 256;  // + alignment slack of the eleven buffers
+}
+
+int xinfer_spec_decoder_create_tp(const xinfer_model_config* cfg, int batch, int k, int64_t max_seq, uint64_t seed,
+                                  xinfer_tp* tp, xinfer_spec_decoder** out) {
     if (!cfg || !out || batch < 1 || k < 1 || k > 7 || max_seq < 8) return XINFER_ERR_INVALID_ARGUMENT;
     *out = nullptr;
     const auto& c = *cfg;
@@ -382,6 +621,17 @@ int xinfer_spec_decoder_create(const xinfer_model_config* cfg, int batch, int k,
         c.linear_num_k_heads < 1 || c.linear_num_v_heads % c.linear_num_k_heads || batch * (k + 1) > 32 ||
         c.rope_dim > 256 || c.rope_dim % 2)
         return XINFER_ERR_INVALID_ARGUMENT;
+    const int world = tp ? xinfer_tp_world(tp) : 1;
+    const int rank = tp ? xinfer_tp_rank(tp) : 0;
+    if (world > 1) {
+        // every split extent must divide evenly, and keep whole row pairs (and the 16-byte row alignment of TMA)
+        const int64_t ch = 2 * c.linear_num_k_heads * 128 + c.linear_num_v_heads * 128;
+        const int64_t split[] = {c.intermediate_size, c.hidden_size, c.num_attention_heads * 512, c.num_key_value_heads * 256,
+                                 ch, c.linear_num_v_heads * 128, c.vocab_size};
+        for (int64_t n : split)
+            if (n % world || (n / world) % 8) return XINFER_ERR_INVALID_ARGUMENT;
+        if (batch % world || !tp->connected) return XINFER_ERR_INVALID_ARGUMENT;
+    }
     {
         int dev = 0;
         if (cudaGetDevice(&dev) != cudaSuccess) return XINFER_ERR_NO_DEVICE;
@@ -395,64 +645,22 @@ int xinfer_spec_decoder_create(const xinfer_model_config* cfg, int batch, int k,
     d->k = k;
     d->max_seq = max_seq;
     d->seed = seed * 2654435761ULL + 12345;
+    d->tp = world > 1 ? tp : nullptr;
+    d->world = world;
+    d->rank = rank;
+    d->bl = batch / world;
+    d->b0 = rank * d->bl;
     cudaGetDevice(&d->device);
+    d->plan = xb::tc_plan_new();
     try {
-        const int64_t H = c.hidden_size, V = c.vocab_size;
+        if (!d->plan) throw std::bad_alloc();
         const int M = batch * (k + 1);
-        d->layers.resize(static_cast<size_t>(c.num_hidden_layers));
-        const int interval = c.full_attention_interval > 0 ? c.full_attention_interval : 4;
-        for (int64_t l = 0; l < c.num_hidden_layers; ++l) make_layer(d, d->layers[l], (l % interval) == interval - 1);
-        make_layer(d, d->mtp_layer, true);
-        d->mtp_fc = make_linear(d, H, 2 * H);
-        d->lm_head = make_linear(d, V, H);
-        d->mtp_enorm = make_floats(d, H, 1.0f, 0.02f);
-        d->mtp_hnorm = make_floats(d, H, 1.0f, 0.02f);
-        d->final_norm = make_floats(d, H, 1.0f, 0.02f);
-        d->embed = dalloc<uint16_t>(d, static_cast<size_t>(V) * H);
-        init_bf16_kernel<<<blocks_for(static_cast<size_t>(V) * H, 256), 256>>>(d->embed, static_cast<size_t>(V) * H,
-                                                                                next_seed(d), 1.0f);
-        d->ctx = dalloc<int>(d, batch, true);
-        d->ctx_draft = dalloc<int>(d, batch, true);
-        d->n_commit = dalloc<int>(d, batch, true);
-        d->n_commit_zero = dalloc<int>(d, batch, true);
-        d->cur_tok = dalloc<long long>(d, batch, true);
-        d->draft = dalloc<long long>(d, static_cast<size_t>(batch) * k, true);
-        d->verify_tokens = dalloc<long long>(d, M, true);
-        d->argmax_out = dalloc<long long>(d, M, true);
-        d->emitted = dalloc<long long>(d, M, true);
-        d->emitted_n = dalloc<int>(d, batch, true);
-        d->h_last = dalloc<__half>(d, static_cast<size_t>(batch) * H, true);
-        d->mtp_hidden = dalloc<__half>(d, static_cast<size_t>(batch) * H, true);
-        d->records = dalloc<xinfer_accept_record>(d, batch, true);
-        d->draft_override = dalloc<long long>(d, static_cast<size_t>(batch) * k, true);
-        const int64_t hv = c.linear_num_v_heads, hk = c.linear_num_k_heads, ch = 2 * hk * 128 + hv * 128;
-        d->x = dalloc<__half>(d, static_cast<size_t>(M) * H, true);
-        d->normed = dalloc<__half>(d, static_cast<size_t>(M) * H, true);
-        d->proj_out = dalloc<__half>(d, static_cast<size_t>(M) * H, true);
-        d->mlp = dalloc<__half>(d, static_cast<size_t>(M) * c.intermediate_size, true);
-        d->q_gate = dalloc<__half>(d, static_cast<size_t>(M) * c.num_attention_heads * 512, true);
-        d->qbuf = dalloc<__half>(d, static_cast<size_t>(M) * c.num_attention_heads * 256, true);
-        d->kbuf = dalloc<__half>(d, static_cast<size_t>(M) * c.num_key_value_heads * 256, true);
-        d->vbuf = dalloc<__half>(d, static_cast<size_t>(M) * c.num_key_value_heads * 256, true);
-        d->attn_out = dalloc<__half>(d, static_cast<size_t>(M) * c.num_attention_heads * 256, true);
-        d->qkv_raw = dalloc<__half>(d, static_cast<size_t>(M) * ch, true);
-        d->qkv_conv = dalloc<__half>(d, static_cast<size_t>(M) * ch, true);
-        d->zbuf = dalloc<__half>(d, static_cast<size_t>(M) * hv * 128, true);
-        d->bbuf = dalloc<__half>(d, static_cast<size_t>(M) * hv, true);
-        d->abuf = dalloc<__half>(d, static_cast<size_t>(M) * hv, true);
-        d->delta_out = dalloc<__half>(d, static_cast<size_t>(M) * hv * 128, true);
-        d->cat = dalloc<__half>(d, static_cast<size_t>(batch) * 2 * H, true);
-        d->logits = dalloc<float>(d, static_cast<size_t>(M) * V, true);
-        {
-            // KV splits: with one attention CTA per SM, two waves of CTAs over (split, kv head, sequence)
-            int sms = 148;
-            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, d->device);
-            const int units = batch * static_cast<int>(c.num_key_value_heads);
-            int splits = (2 * sms) / (units > 0 ? units : 1);
-            d->attn_splits = splits < 1 ? 1 : (splits > 16 ? 16 : splits);
-        }
-        d->attn_scratch = dalloc<float>(
-            d, xb::attn_scratch_bytes(batch, static_cast<int>(c.num_key_value_heads), d->attn_splits) / sizeof(float), true);
+        // first pass adds up what the decoder needs, the arena is created with exactly that, second pass carves it
+        d->sizing = true;
+        build_all(d);
+        d->sizing = false;
+        if (xinfer_arena_create(d->need_bytes + kAlign, kAlign, &d->arena) != XINFER_OK) throw std::bad_alloc();
+        build_all(d);
         if (cudaMallocHost(&d->h_emitted, static_cast<size_t>(M) * sizeof(long long)) != cudaSuccess ||
             cudaMallocHost(&d->h_emitted_n, static_cast<size_t>(batch) * sizeof(int)) != cudaSuccess)
             throw std::bad_alloc();
@@ -469,12 +677,18 @@ int xinfer_spec_decoder_create(const xinfer_model_config* cfg, int batch, int k,
     return xinfer_spec_decoder_reset(d, 0, seed);
 }
 
+int xinfer_spec_decoder_create(const xinfer_model_config* cfg, int batch, int k, int64_t max_seq, uint64_t seed,
+                               xinfer_spec_decoder** out) {
+    return xinfer_spec_decoder_create_tp(cfg, batch, k, max_seq, seed, nullptr, out);
+}
+
 void xinfer_spec_decoder_destroy(xinfer_spec_decoder* d) {
     if (!d) return;
-    xb::tc_plan_clear();  // the recorded plan points into this decoder's weights
+    cudaDeviceSynchronize();
     if (d->graph_exec) cudaGraphExecDestroy(d->graph_exec);
     if (d->graph) cudaGraphDestroy(d->graph);
-    for (void* p : d->allocs) cudaFree(p);
+    if (d->plan) xb::tc_plan_delete(d->plan);  // the recorded plan points into this decoder's weights
+    if (d->arena) xinfer_arena_destroy(d->arena);
     if (d->h_emitted) cudaFreeHost(d->h_emitted);
     if (d->h_emitted_n) cudaFreeHost(d->h_emitted_n);
     delete d;
@@ -483,25 +697,28 @@ void xinfer_spec_decoder_destroy(xinfer_spec_decoder* d) {
 int xinfer_spec_decoder_reset(xinfer_spec_decoder* d, int64_t context_len, uint64_t seed) {
     if (!d || context_len < 0 || context_len + 2 * (d->k + 1) > d->max_seq) return XINFER_ERR_INVALID_ARGUMENT;
     const auto& c = d->cfg;
-    const int B = d->batch;
+    const int B = d->batch, Bl = d->bl, b0 = d->b0;
     uint64_t sd = seed * 0x9E3779B97F4A7C15ULL + 777;
     auto nxt = [&]() { return sd = sd * 6364136223846793005ULL + 1442695040888963407ULL; };
+    // state tensors are [sequence][...]: this rank fills the slices of its own sequences with the values the
+    // unsharded decoder would hold there
     auto fill_layer = [&](Layer& L) {
         if (L.full) {
-            const size_t kv = static_cast<size_t>(B) * d->max_seq * c.num_key_value_heads * 256;
-            init_half_kernel<<<blocks_for(kv, 256), 256>>>(L.k_cache, kv, nxt(), 1, 0.f, 1.0f);
-            init_half_kernel<<<blocks_for(kv, 256), 256>>>(L.v_cache, kv, nxt(), 1, 0.f, 1.0f);
+            const size_t per = static_cast<size_t>(d->max_seq) * c.num_key_value_heads * 256;
+            init_half_kernel<<<blocks_for(Bl * per, 256), 256>>>(L.k_cache, Bl * per, nxt(), 1, 0.f, 1.0f, b0 * per);
+            init_half_kernel<<<blocks_for(Bl * per, 256), 256>>>(L.v_cache, Bl * per, nxt(), 1, 0.f, 1.0f, b0 * per);
         } else {
             const int64_t hv = c.linear_num_v_heads, hk = c.linear_num_k_heads, ch = 2 * hk * 128 + hv * 128;
-            const size_t sn = static_cast<size_t>(B) * hv * 128 * 128;
+            const size_t per = static_cast<size_t>(hv) * 128 * 128;
             const float sig = context_len > 0 ? 0.05f : 0.0f;  // an empty context starts from zero state
-            init_float_kernel<<<blocks_for(sn, 256), 256>>>(L.S, sn, nxt(), 0.f, sig);
-            init_float_kernel<<<blocks_for(static_cast<size_t>(B) * 3 * ch, 256), 256>>>(
-                L.conv_state, static_cast<size_t>(B) * 3 * ch, nxt(), 0.f, context_len > 0 ? 1.0f : 0.0f);
-            cudaMemset(L.pend_k, 0, static_cast<size_t>(B) * hv * 8 * 128 * sizeof(float));
-            cudaMemset(L.pend_d, 0, static_cast<size_t>(B) * hv * 8 * 128 * sizeof(float));
-            cudaMemset(L.pend_g, 0, static_cast<size_t>(B) * hv * 8 * sizeof(float));
-            cudaMemset(L.conv_pend, 0, static_cast<size_t>(B) * 8 * ch * sizeof(float));
+            init_float_kernel<<<blocks_for(Bl * per, 256), 256>>>(L.S, Bl * per, nxt(), 0.f, sig, b0 * per);
+            const size_t cper = static_cast<size_t>(3) * ch;
+            init_float_kernel<<<blocks_for(Bl * cper, 256), 256>>>(L.conv_state, Bl * cper, nxt(), 0.f,
+                                                                    context_len > 0 ? 1.0f : 0.0f, b0 * cper);
+            cudaMemset(L.pend_k, 0, static_cast<size_t>(Bl) * hv * 8 * 128 * sizeof(float));
+            cudaMemset(L.pend_d, 0, static_cast<size_t>(Bl) * hv * 8 * 128 * sizeof(float));
+            cudaMemset(L.pend_g, 0, static_cast<size_t>(Bl) * hv * 8 * sizeof(float));
+            cudaMemset(L.conv_pend, 0, static_cast<size_t>(Bl) * 8 * ch * sizeof(float));
         }
     };
     for (auto& L : d->layers) fill_layer(L);
@@ -511,20 +728,28 @@ int xinfer_spec_decoder_reset(xinfer_spec_decoder* d, int64_t context_len, uint6
     xb::fill_int(nullptr, d->n_commit_zero, B, 0);
     init_tokens_kernel<<<1, 64>>>(d->cur_tok, B, nxt(), c.vocab_size);
     init_half_kernel<<<blocks_for(static_cast<size_t>(B) * c.hidden_size, 256), 256>>>(
-        d->h_last, static_cast<size_t>(B) * c.hidden_size, nxt(), 1, 0.f, 1.0f);
+        d->h_last, static_cast<size_t>(B) * c.hidden_size, nxt(), 1, 0.f, 1.0f, 0);
     d->prev_rows = 0;
+    d->ctx_upper = context_len;
     return cudaDeviceSynchronize() == cudaSuccess ? XINFER_OK : XINFER_ERR_CUDA;
 }
 
 int xinfer_spec_decoder_step(xinfer_spec_decoder* d, xinfer_stream_t stream) {
     if (!d) return XINFER_ERR_INVALID_ARGUMENT;
-    cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (d->graph_exec) {
-        return cudaGraphLaunch(d->graph_exec, s) == cudaSuccess ? XINFER_OK : XINFER_ERR_CUDA;
+    // A step writes cache positions up to ctx + k.  The context lengths advance on the device; the host keeps an
+    // upper bound (every step adds at most k + 1) and refuses a step that could run past the caches, where the
+    // kernels would drop the newest keys silently (the reference's KVCache throws when it is full,
+    // src/core/kv_cache.cpp advance()).
+    if (d->ctx_upper + (d->k + 1) > d->max_seq) {
+        d->error = "context would exceed max_seq";
+        return XINFER_ERR_INVALID_ARGUMENT;
     }
-    const int prev = d->prev_rows;
-    (void)prev;
-    return enqueue_step(d, s);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    int rc;
+    if (d->graph_exec) rc = cudaGraphLaunch(d->graph_exec, s) == cudaSuccess ? XINFER_OK : XINFER_ERR_CUDA;
+    else rc = enqueue_step(d, s);
+    if (rc >= 0) d->ctx_upper += d->k + 1;
+    return rc;
 }
 
 int xinfer_spec_decoder_capture(xinfer_spec_decoder* d, xinfer_stream_t stream) {
@@ -536,10 +761,15 @@ int xinfer_spec_decoder_capture(xinfer_spec_decoder* d, xinfer_stream_t stream) 
     // The same eager step records the order of the tensor-core launches, so that in the captured step
     // every linear can ask L2 for the first weight stages of the one after it.
     if (d->prev_rows != d->k + 1) {
+        if (d->ctx_upper + (d->k + 1) > d->max_seq) return XINFER_ERR_INVALID_ARGUMENT;
+        xb::TcPlan* prev_plan = xb::tc_plan_bind(d->plan);
         xb::tc_plan_record_begin();
         int rc = enqueue_step(d, s);
+        xb::tc_plan_bind(d->plan);  // (enqueue_step restored the previous binding)
         xb::tc_plan_record_end();
+        xb::tc_plan_bind(prev_plan);
         if (rc < 0) return rc;
+        d->ctx_upper += d->k + 1;
         if (cudaStreamSynchronize(s) != cudaSuccess) return XINFER_ERR_CUDA;
     }
     if (cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal) != cudaSuccess) return XINFER_ERR_CUDA;
@@ -563,9 +793,12 @@ int xinfer_spec_decoder_results(xinfer_spec_decoder* d, xinfer_stream_t stream, 
     if (!d || !emitted_host || !counts_host) return XINFER_ERR_INVALID_ARGUMENT;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const int M = d->batch * (d->k + 1);
-    cudaMemcpyAsync(d->h_emitted, d->emitted, static_cast<size_t>(M) * sizeof(long long), cudaMemcpyDeviceToHost, s);
-    cudaMemcpyAsync(d->h_emitted_n, d->emitted_n, static_cast<size_t>(d->batch) * sizeof(int), cudaMemcpyDeviceToHost, s);
-    if (cudaStreamSynchronize(s) != cudaSuccess) return XINFER_ERR_CUDA;
+    if (cudaMemcpyAsync(d->h_emitted, d->emitted, static_cast<size_t>(M) * sizeof(long long), cudaMemcpyDeviceToHost, s) != cudaSuccess ||
+        cudaMemcpyAsync(d->h_emitted_n, d->emitted_n, static_cast<size_t>(d->batch) * sizeof(int), cudaMemcpyDeviceToHost, s) != cudaSuccess ||
+        cudaStreamSynchronize(s) != cudaSuccess) {
+        cudaGetLastError();
+        return XINFER_ERR_CUDA;
+    }
     memcpy(emitted_host, d->h_emitted, static_cast<size_t>(M) * sizeof(long long));
     memcpy(counts_host, d->h_emitted_n, static_cast<size_t>(d->batch) * sizeof(int));
     return XINFER_OK;
@@ -605,6 +838,8 @@ int64_t xinfer_spec_decoder_info(const xinfer_spec_decoder* d, int what) {
         case 3: return d->graph_exec ? 1 : 0;
         case 4: return static_cast<int64_t>(d->linear_bytes);
         case 5: return d->linear_launches;
+        case 6: return d->exchanges_per_step;
+        case 7: return d->arena ? static_cast<int64_t>(xinfer_arena_capacity(d->arena)) : 0;
         default: return -1;
     }
 }
@@ -620,6 +855,7 @@ void* xinfer_spec_decoder_tensor(xinfer_spec_decoder* d, int layer, const char* 
     auto lin_w = [&](const Linear& l) { nb = l.n * (l.k / 2); return static_cast<void*>(l.w); };
     auto lin_s = [&](const Linear& l) { nb = l.n * (l.k / 128) * 2; return static_cast<void*>(l.s); };
     const int64_t H = c.hidden_size, B = d->batch, M = B * (d->k + 1);
+    const int64_t Bl = d->bl;  // state tensors hold this rank's own sequences only
     if (layer < 0) {
         if (n == "embed") { nb = c.vocab_size * H * 2; return d->embed; }
         if (n == "final_norm") { nb = H * 4; return d->final_norm; }
@@ -634,7 +870,7 @@ void* xinfer_spec_decoder_tensor(xinfer_spec_decoder* d, int layer, const char* 
         if (n == "cur_tok") { nb = B * 8; return d->cur_tok; }
         if (n == "draft") { nb = B * d->k * 8; return d->draft; }
         if (n == "h_last") { nb = B * H * 2; return d->h_last; }
-        if (n == "logits") { nb = M * c.vocab_size * 4; return d->logits; }
+        if (n == "logits") { nb = M * d->vocab_local * 4; return d->logits; }
         if (n == "x") { nb = M * H * 2; return d->x; }
         if (n == "records") { nb = B * static_cast<int64_t>(sizeof(xinfer_accept_record)); return d->records; }
         return nullptr;
@@ -653,7 +889,7 @@ void* xinfer_spec_decoder_tensor(xinfer_spec_decoder* d, int layer, const char* 
     if (n == "down.w") return lin_w(L->down);
     if (n == "down.s") return lin_s(L->down);
     if (L->full) {
-        const int64_t kv = B * d->max_seq * c.num_key_value_heads * 256 * 2;
+        const int64_t kv = Bl * d->max_seq * c.num_key_value_heads * 256 * 2;
         if (n == "q_proj.w") return lin_w(L->q_proj);
         if (n == "q_proj.s") return lin_s(L->q_proj);
         if (n == "k_proj.w") return lin_w(L->k_proj);
@@ -682,8 +918,8 @@ void* xinfer_spec_decoder_tensor(xinfer_spec_decoder* d, int layer, const char* 
         if (n == "A_log") { nb = hv * 4; return L->A_log; }
         if (n == "dt_bias") { nb = hv * 4; return L->dt_bias; }
         if (n == "gdn_norm") { nb = 128 * 4; return L->gdn_norm; }
-        if (n == "S") { nb = B * hv * 128 * 128 * 4; return L->S; }
-        if (n == "conv_state") { nb = B * 3 * ch * 4; return L->conv_state; }
+        if (n == "S") { nb = Bl * hv * 128 * 128 * 4; return L->S; }
+        if (n == "conv_state") { nb = Bl * 3 * ch * 4; return L->conv_state; }
     }
     return nullptr;
 }

@@ -5,10 +5,16 @@
 #include <stddef.h>
 #include <stdint.h>
 
+#include "tp.cuh"
+
 namespace xb {
 
 // One projection of a (possibly fused) launch.  `w` is [n][k/2] packed int4 (low nibble = even k),
 // `scales` is [n][k/group] fp16, `bias` is [n] fp32 or null, `y` is [m][ldy] (ldy = 0 means n).
+// N-split tensor parallelism: with push != 0 the kernel stores every output element straight into the
+// buffers of other ranks, `y_peer[r]` being rank r's address of the element `y` points to (y_peer[own
+// rank] == y).  push 1: every rank gets every row; push 2: row j goes only to rank j / rows_per_rank
+// (its sequence's owner).  push 0 (and y_peer unused): local store only.
 struct TcProj {
     void* y;
     const uint8_t* w;
@@ -16,24 +22,39 @@ struct TcProj {
     const float* bias;
     long long n;
     long long ldy;
+    int push = 0;
+    void* y_peer[kTpMaxWorld] = {};
 };
 
 // ---- tcgen05 path (w4a16_tc.cu): fp16 activations, 1 <= m <= 32, k % 128 == 0
 size_t tc_workspace_bytes(int ctas);
-void tc_set_trace(long long* dev_ptr);
+// Test hooks for the bounded device-side waits: their clock limit (<= 0 restores the one-second default)
+// and the first activation stage that the producer never requests (-1: all are requested).
+void tc_set_wait_hooks(long long limit_clocks, int withhold_x_from_stage);
+// Status word of the allocation-free entry point on `device` (which must be current): read and cleared.
+int tc_noalloc_take_status(int device);
+// Records a message for xinfer_last_cuda_error() on the calling thread (c_api.cu).
+void set_last_error(const char* msg);
 // Programmatic dependent launch (on unless XINFER_PDL=0): kernels are launched with the stream-serialization
 // attribute and call griddepcontrol.wait before they touch data of the previous kernel.
 bool pdl_enabled();
 bool tc_eligible(const void* x, const TcProj* proj, int num, bool swiglu, long long m, long long k, int group_size);
 // Launch plan (a hint for L2 prefetching of the next launch's weights): record one round of the caller's
 // fixed launch sequence between record_begin/record_end, then rewind at the start of every further round.
+struct TcPlan;
+TcPlan* tc_plan_new();
+void tc_plan_delete(TcPlan* p);
+// Binds a plan to the calling thread (null: the process-wide default); returns the previous binding.
+TcPlan* tc_plan_bind(TcPlan* p);
 void tc_plan_record_begin();
 void tc_plan_record_end();
 void tc_plan_rewind();
 void tc_plan_clear();
+// `tp` (may be null): the exchange this launch takes part in; its last CTA then signals the peers and waits
+// for theirs before the kernel completes.
 int tc_launch(cudaStream_t stream, const void* x, const TcProj* proj, int num, bool swiglu, bool out_f32,
               long long m, long long k, int num_sms, float* workspace, int* counters, int counter_capacity,
-              int* status);
+              int* status, const TpLink* tp = nullptr);
 
 // ---- CUDA-core path (w4a16_simt.cu): any m, fp16 or fp32 activations, any shape the reference accepts
 enum class ActType { F16, F32 };

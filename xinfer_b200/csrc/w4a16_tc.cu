@@ -40,6 +40,8 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include <mutex>
+#include <new>
 #include <vector>
 
 #include "ptx_sm100.cuh"
@@ -101,6 +103,8 @@ struct Seg {
     long long ldy;  // row stride of y in elements
     int n;          // output features of this projection
     int tile_begin; // first tile index of this projection
+    int push;       // 0: y only; 1: the same element in every rank's buffer; 2: in the row owner's buffer
+    void* y_peer[kTpMaxWorld];
 };
 
 struct Params {
@@ -118,7 +122,9 @@ struct Params {
     int* counters;    // [total_tiles], zero between launches
     int* status;      // device status word
     int cluster;      // CTAs per thread-block cluster = K splits per tile summed through distributed shared memory (1: none)
-    long long* trace; // optional [ctas][16] globaltimer stamps (debug aid, null in production)
+    long long wait_limit;  // SM clocks after which a device-side wait gives up
+    int x_stage_limit;     // test hook: activation stages beyond this index are never requested (-1: off)
+    TpLink tp;             // N-split exchange (world <= 1: none)
     // Optional: the first weight stages of the NEXT tensor-core launch in the stream, pulled into L2 while this
     // launch drains, so that launch's pipeline fills from L2 instead of HBM.  pf_ctas = 0: nothing to prefetch.
     CUtensorMap pf_map[kMaxSegs];
@@ -141,8 +147,8 @@ struct Ctrl {
     uint64_t epi;         // epilogue barrier of the consumer warps
     uint64_t red;         // counts the bytes of split-K partials that other CTAs of the cluster store here
     uint32_t tmem_base;
-    int abort_flag;
     int is_last;
+    WaitState ws;
 };
 static_assert(sizeof(Ctrl) <= 512, "control block");
 
@@ -186,11 +192,17 @@ __device__ __forceinline__ TileInfo locate_tile(const Params& p, int tile) {
     return ti;
 }
 
-__device__ __forceinline__ void stamp(const Params& p, int slot) {
-    if (p.trace) {
-        long long t;
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-        p.trace[blockIdx.x * 16 + slot] = t;
+// Stores output element (activation row j, element offset `off` from the projection's y) where it belongs:
+// locally, or - N-split tensor parallelism - with plain peer stores into the other ranks' buffers as well.
+template <typename OutT>
+__device__ __forceinline__ void store_row(const Params& p, const Seg& sg, long long off, int j, float v) {
+    if (sg.push == 0) {
+        store_out<OutT>(static_cast<OutT*>(sg.y) + off, v);
+    } else if (sg.push == 2) {
+        store_out<OutT>(static_cast<OutT*>(sg.y_peer[j / p.tp.rows_per_rank]) + off, v);
+    } else {
+#pragma unroll 1
+        for (int r = 0; r < p.tp.world; ++r) store_out<OutT>(static_cast<OutT*>(sg.y_peer[r]) + off, v);
     }
 }
 
@@ -209,8 +221,7 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
     const int lane = tid & 31;
-    volatile int* abort_flag = &ctrl->abort_flag;
-    if (tid == 0) stamp(p, 0);
+    volatile WaitState* abort_flag = &ctrl->ws;  // shared by every bounded wait of the CTA
     griddep_launch_dependents();
 
     if (tid == 0) {
@@ -240,7 +251,9 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
             owned = owned < 0 ? 0 : (owned > rows_cap ? rows_cap : owned);
             mbar_arrive_expect_tx(smem_u32(&ctrl->red), static_cast<uint32_t>(p.cluster * owned * kTileRows * 4));
         }
-        ctrl->abort_flag = 0;
+        ctrl->ws.abort_flag = 0;
+        ctrl->ws.dep_ready = 0;
+        ctrl->ws.limit = p.wait_limit;
         ctrl->is_last = 0;
         mbar_fence_init();
     }
@@ -252,7 +265,6 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = ctrl->tmem_base;
-    if (tid == 0) stamp(p, 1);
 
     const long long ctas = gridDim.x;
     const long long u_begin = unit_begin(blockIdx.x, p.total_units, ctas);
@@ -314,13 +326,18 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
         // ring of weight tiles is requested before waiting for that kernel, so the weight stream is
         // already in flight while it drains (programmatic dependent launch).
         const uint32_t pre_w = total_mine < C::kStages ? total_mine : C::kStages;
-        const uint32_t pre_x = total_mine < C::kXStages ? total_mine : C::kXStages;
+        // (test hook: with x_stage_limit >= 0 the activation stages from that index on are never requested, so
+        // the waits for them run out and the kernel leaves through its abort path)
+        const uint32_t x_total = (p.x_stage_limit >= 0 && static_cast<uint32_t>(p.x_stage_limit) < total_mine)
+                                     ? static_cast<uint32_t>(p.x_stage_limit) : total_mine;
+        const uint32_t pre_x = x_total < C::kXStages ? x_total : C::kXStages;
         // All CTAs start together: were every CTA to request its whole ring at once, the first stages would
         // come back interleaved with the deeper ones and the consumers would sit idle for the whole burst.
         // Two stages go out first; the rest of the ring follows once the first stage has landed.
         const uint32_t pre_a = pre_w < 2u ? pre_w : 2u;
         for (uint32_t n = 0; n < pre_a; ++n) issue_w(n);
         griddep_wait();
+        if (leader) abort_flag->dep_ready = 1;  // from here on a wait that runs out is a real timeout
         for (uint32_t n = 0; n < pre_x; ++n) issue_x(n);
         bool ok = true;
         if (pre_w > pre_a) {
@@ -328,12 +345,12 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
             for (uint32_t n = pre_a; ok && n < pre_w; ++n) issue_w(n);
         }
         uint32_t nw = pre_w, nx = pre_x;
-        while (ok && (nw < total_mine || nx < total_mine)) {
+        while (ok && (nw < total_mine || nx < x_total)) {
             if (nw < total_mine) {
                 ok = mbar_wait_parked(smem_u32(&ctrl->empty[nw % C::kStages]), ((nw / C::kStages) & 1u) ^ 1u, abort_flag);
                 if (ok) issue_w(nw++);
             }
-            if (ok && nx < total_mine) {
+            if (ok && nx < x_total) {
                 ok = mbar_wait_parked(smem_u32(&ctrl->x_empty[nx % C::kXStages]), ((nx / C::kXStages) & 1u) ^ 1u, abort_flag);
                 if (ok) issue_x(nx++);
             }
@@ -358,19 +375,19 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
                 }
             }
         }
-        if (*abort_flag) {
+        if (abort_flag->abort_flag) {
             // give the copies still in flight a bounded chance to land before the CTA exits
             const long long t0 = clock64();
             for (int i = 0; i < C::kStages && i < static_cast<int>(nw); ++i) {
                 const uint32_t k = nw - 1 - i;
                 while (!mbar_try_wait(smem_u32(&ctrl->full[k % C::kStages]), (k / C::kStages) & 1u) &&
-                       clock64() - t0 < kWaitLimitClocks / 8) {
+                       clock64() - t0 < p.wait_limit / 8) {
                 }
             }
             for (int i = 0; i < C::kXStages && i < static_cast<int>(nx); ++i) {
                 const uint32_t k = nx - 1 - i;
                 while (!mbar_try_wait(smem_u32(&ctrl->x_full[k % C::kXStages]), (k / C::kXStages) & 1u) &&
-                       clock64() - t0 < kWaitLimitClocks / 8) {
+                       clock64() - t0 < p.wait_limit / 8) {
                 }
             }
         }
@@ -586,8 +603,6 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
                 if (have_prev) {
                     if (!mbar_wait(dfull, dfull_phase, abort_flag)) { ok = false; break; }
                     tc_fence_after_sync();
-                } else if (tid == 0 && n == 0) {
-                    stamp(p, 2);
                 }
                 dfull_phase ^= 1u;
 #pragma unroll
@@ -626,7 +641,6 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
             tc_fence_after_sync();
             fold(sc_pend, (n - 1) & 1u);
 
-            if (tid == 0) stamp(p, 3);
             // ---------------------------------------------------------------- tile epilogue
             // Runs once per tile, so its instructions are cold in the instruction caches: the accumulators
             // are parked in shared memory and everything after that is written as rolled loops (a fully
@@ -638,16 +652,13 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
 #pragma unroll
                 for (int j = 0; j < NREAD; ++j) stage_acc[j * kTileRows + rt] = acc[j];
             }
-            if (tid == 0) stamp(p, 8);
             if (!consumer_sync()) break;
-            if (tid == 0) stamp(p, 9);
             if (gi == 1) {
 #pragma unroll
                 for (int j = 0; j < NREAD; ++j) stage_acc[j * kTileRows + rt] += acc[j];
             }
             fence_proxy_async_smem();  // the copy engine may read the parked rows (split-K exchange)
             if (!consumer_sync()) break;
-            if (tid == 0) stamp(p, 6);
             const int m_rows = p.m < NREAD ? p.m : NREAD;
             const bool whole = (s0 == 0 && s1 == S);
             bool finish = whole;
@@ -665,7 +676,6 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
                 if (cl_steps == 0) { cluster_arrive(); cl_steps = 1; }
                 cluster_wait();  // (A) every CTA of the cluster has finished reading its weight ring
                 cl_steps = 2;
-                if (tid == 0) stamp(p, 10);
                 if (warp == 0 && lane < static_cast<int>(csz)) {  // lane r sends the block owned by CTA r
                     int nr = m_rows - lane * static_cast<int>(rows_cap);
                     nr = nr > static_cast<int>(rows_cap) ? static_cast<int>(rows_cap) : nr;
@@ -676,12 +686,10 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
                                              mapa_shared_cluster(smem_u32(&ctrl->red), lane));
                     }
                 }
-                if (tid == 0) stamp(p, 11);
                 if (!mbar_wait(smem_u32(&ctrl->red), 0u, abort_flag)) { ok = false; break; }
                 // (B) this CTA has all its incoming rows, so the senders' sources may go away; waited for at exit
                 cluster_arrive();
                 cl_steps = 3;
-                if (tid == 0) stamp(p, 7);
                 {
                     // this CTA's block of rows; the two threads of a tile row take every other one
                     const bool direct = !p.swiglu && valid;
@@ -691,24 +699,23 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
                     uint32_t jlast = jfirst + rows_cap;
                     jlast = jlast > static_cast<uint32_t>(m_rows) ? static_cast<uint32_t>(m_rows) : jlast;
                     uint32_t j = jfirst + gi;
-                    OutT* yp = static_cast<OutT*>(sg.y) + my_row + static_cast<long long>(j) * ldy;
+                    long long yoff = my_row + static_cast<long long>(j) * ldy;
                     uint32_t pa = smem_u32(part) + (gi * kTileRows + rt) * 4;
                     const uint32_t rstep = rows_cap * (kTileRows * 4);
                     float* sa = stage_acc + j * kTileRows + rt;
 #pragma unroll 1
-                    for (; j < jlast; j += 2, pa += 2 * kTileRows * 4, yp += 2 * ldy, sa += 2 * kTileRows) {
+                    for (; j < jlast; j += 2, pa += 2 * kTileRows * 4, yoff += 2 * ldy, sa += 2 * kTileRows) {
                         float sum = 0.f;
                         uint32_t a = pa;
 #pragma unroll 2
                         for (uint32_t r = 0; r < csz; ++r, a += rstep) sum += lds_f32(a);
-                        if (direct) store_out<OutT>(yp, sum + bias);
+                        if (direct) store_row<OutT>(p, sg, yoff, static_cast<int>(j), sum + bias);
                         else *sa = sum;
                     }
                     j0 = static_cast<int>(jfirst) + gi;
                     jend = static_cast<int>(jlast);
                     finish = p.swiglu != 0;  // plain projections are already written
                 }
-                if (tid == 0) stamp(p, 12);
             } else if (!whole) {
                 // tiles that straddle CTAs (one CTA per SM, units cut evenly): partials go through the scratch
                 // buffer and the last CTA to arrive sums them in CTA order
@@ -755,25 +762,23 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
                 if (p.swiglu) {
                     if (!consumer_sync()) break;  // the up half's values are visible to the gate half
                     if (wg == 0 && valid) {
-                        OutT* y = static_cast<OutT*>(p.seg[0].y) + my_row;
                         const long long ldy = p.seg[0].ldy;
 #pragma unroll 4
                         for (int j = j0; j < jend; j += jstep) {
                             const float g = stage_acc[j * kTileRows + t];
                             const float up = stage_acc[j * kTileRows + kHalfRows + t];
-                            store_out<OutT>(y + static_cast<long long>(j) * ldy, (g / (1.0f + expf(-g))) * up);
+                            store_row<OutT>(p, p.seg[0], my_row + static_cast<long long>(j) * ldy, j,
+                                            (g / (1.0f + expf(-g))) * up);
                         }
                     }
                 } else if (valid) {
-                    OutT* y = static_cast<OutT*>(sg.y) + my_row;
                     const long long ldy = sg.ldy;
                     const float b = sg.bias ? sg.bias[my_row] : 0.f;
 #pragma unroll 4
                     for (int j = j0; j < jend; j += jstep)
-                        store_out<OutT>(y + static_cast<long long>(j) * ldy, stage_acc[j * kTileRows + rt] + b);
+                        store_row<OutT>(p, sg, my_row + static_cast<long long>(j) * ldy, j, stage_acc[j * kTileRows + rt] + b);
                 }
             }
-            if (tid == 0) stamp(p, 4);
             u += (s1 - s0);
         }
         // every thread of a cluster passes both cluster barriers exactly once, also when a wait gave up
@@ -789,8 +794,10 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
     // ---------------------------------------------------------------------- teardown
     tc_fence_before_sync();
     __syncthreads();
-    if (tid == 0) stamp(p, 5);
-    if (tid == 0 && ctrl->abort_flag) atomicExch(p.status, kStatusWaitTimeout);
+    if (tid == 0 && ctrl->ws.abort_flag) atomicExch(p.status, kStatusWaitTimeout);
+    // N-split exchange: every store of this CTA is ordered before the barrier above; the grid's last CTA
+    // publishes the launch to the peers and waits for theirs
+    if (p.tp.world > 1 && tid == 0) tp_finish_exchange(p.tp, gridDim.x);
     if (warp == kMmaWarp) {
         __syncwarp();
         tc_fence_after_sync();
@@ -863,14 +870,22 @@ Decomp choose_grid(int tiles, int stages, int num_sms, const int* max_clusters) 
 }
 
 // One-time set-up of a kernel instantiation on the current device; returns its cluster occupancy table.
+constexpr int kMaxDevices = 64;
+
 template <int NMMA, int NREAD, typename OutT>
 cudaError_t configure(const int** table) {
     auto kern = w4a16_tc_kernel<NMMA, NREAD, OutT>;
-    static int configured_dev = -1;
-    static int max_clusters[9];
+    // per device: the function attributes live in that device's context, and so does the occupancy table
+    static bool configured[kMaxDevices];
+    static int clusters[kMaxDevices][9];
+    static std::mutex mu;
     int dev = 0;
-    cudaGetDevice(&dev);
-    if (configured_dev != dev) {
+    cudaError_t ge = cudaGetDevice(&dev);
+    if (ge != cudaSuccess) return ge;
+    if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+    std::lock_guard<std::mutex> lock(mu);
+    int* max_clusters = clusters[dev];
+    if (!configured[dev]) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<NMMA>::kSmemBytes);
         if (e != cudaSuccess) return e;
         // The in-kernel register re-split is balanced for exactly kLaunchRegs per thread at launch: with any
@@ -895,7 +910,7 @@ cudaError_t configure(const int** table) {
             if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess) { n = 0; cudaGetLastError(); }
             max_clusters[cs] = n;
         }
-        configured_dev = dev;
+        configured[dev] = true;
     }
     *table = max_clusters;
     return cudaSuccess;
@@ -946,14 +961,21 @@ bool pdl_enabled() {
     return on;
 }
 
-static long long* g_trace = nullptr;
-void tc_set_trace(long long* dev_ptr) { g_trace = dev_ptr; }
+// Test hooks: the clock limit of the device-side waits, and an activation stage index from which on the
+// producer requests nothing (the kernel then leaves through its abort path).  Defaults: one second, off.
+static long long g_wait_limit = kWaitLimitClocks;
+static int g_x_stage_limit = -1;
+void tc_set_wait_hooks(long long limit_clocks, int withhold_x_from_stage) {
+    g_wait_limit = limit_clocks > 0 ? limit_clocks : kWaitLimitClocks;
+    g_x_stage_limit = withhold_x_from_stage;
+}
 
 // ------------------------------------------------------------------------------------ launch plan
 // A caller that issues the same sequence of tensor-core launches over and over (the speculative step) records
 // it once; afterwards every launch of the sequence knows which weights the next one will stream and asks L2
 // for that launch's first stages while it drains.  The plan is only a hint: a call that does not match the
-// recorded sequence switches it off.
+// recorded sequence switches it off.  A plan is an object: each decoder owns one and binds it to the calling
+// thread around its launches; callers of the bare entry points share the process-wide default plan.
 namespace {
 struct PlanEntry {
     TcProj proj[kMaxSegs];
@@ -961,9 +983,16 @@ struct PlanEntry {
     bool swiglu, out_f32;
     long long m, k;
 };
-std::vector<PlanEntry> g_plan;
-bool g_plan_recording = false, g_plan_active = false;
-size_t g_plan_cursor = 0;
+}  // namespace
+struct TcPlan {
+    std::vector<PlanEntry> entries;
+    bool recording = false, active = false;
+    size_t cursor = 0;
+};
+namespace {
+TcPlan g_default_plan;
+thread_local TcPlan* t_plan = nullptr;
+TcPlan& cur_plan() { return t_plan ? *t_plan : g_default_plan; }
 
 PlanEntry make_entry(const TcProj* proj, int num, bool swiglu, bool out_f32, long long m, long long k) {
     PlanEntry e;
@@ -982,22 +1011,35 @@ bool same_launch(const PlanEntry& a, const PlanEntry& b) {
 }
 }  // namespace
 
+TcPlan* tc_plan_new() { return new (std::nothrow) TcPlan(); }
+void tc_plan_delete(TcPlan* p) {
+    if (t_plan == p) t_plan = nullptr;
+    delete p;
+}
+TcPlan* tc_plan_bind(TcPlan* p) {
+    TcPlan* prev = t_plan;
+    t_plan = p;
+    return prev;
+}
 void tc_plan_record_begin() {
-    g_plan.clear();
-    g_plan_recording = true;
-    g_plan_active = false;
-    g_plan_cursor = 0;
+    TcPlan& pl = cur_plan();
+    pl.entries.clear();
+    pl.recording = true;
+    pl.active = false;
+    pl.cursor = 0;
 }
 void tc_plan_record_end() {
-    g_plan_recording = false;
-    g_plan_active = !g_plan.empty();
-    g_plan_cursor = 0;
+    TcPlan& pl = cur_plan();
+    pl.recording = false;
+    pl.active = !pl.entries.empty();
+    pl.cursor = 0;
 }
-void tc_plan_rewind() { g_plan_cursor = 0; }
+void tc_plan_rewind() { cur_plan().cursor = 0; }
 void tc_plan_clear() {
-    g_plan.clear();
-    g_plan_recording = g_plan_active = false;
-    g_plan_cursor = 0;
+    TcPlan& pl = cur_plan();
+    pl.entries.clear();
+    pl.recording = pl.active = false;
+    pl.cursor = 0;
 }
 
 namespace {
@@ -1048,7 +1090,7 @@ bool tc_eligible(const void* x, const TcProj* proj, int num, bool swiglu, long l
 // problem cannot be described to the kernel (the caller then uses the CUDA-core path).
 int tc_launch(cudaStream_t stream, const void* x, const TcProj* proj, int num, bool swiglu, bool out_f32,
               long long m, long long k, int num_sms, float* workspace, int* counters, int counter_capacity,
-              int* status) {
+              int* status, const TpLink* tp) {
     Params p;
     memset(&p, 0, sizeof(p));
     const int nmma = (m <= 16) ? 16 : 32;
@@ -1066,6 +1108,8 @@ int tc_launch(cudaStream_t stream, const void* x, const TcProj* proj, int num, b
         p.seg[i].y = proj[i].y;
         p.seg[i].ldy = proj[i].ldy > 0 ? proj[i].ldy : proj[i].n;
         p.seg[i].n = static_cast<int>(proj[i].n);
+        p.seg[i].push = (tp && tp->world > 1) ? proj[i].push : 0;
+        for (int r = 0; r < kTpMaxWorld; ++r) p.seg[i].y_peer[r] = proj[i].y_peer[r];
         p.seg[i].tile_begin = tiles;
         if (swiglu) {
             if (i == 0) tiles += static_cast<int>((proj[0].n + kHalfRows - 1) / kHalfRows);
@@ -1081,17 +1125,25 @@ int tc_launch(cudaStream_t stream, const void* x, const TcProj* proj, int num, b
     p.workspace = workspace;
     p.counters = counters;
     p.status = status;
-    p.trace = g_trace;
-    if (g_plan_recording) {
-        g_plan.push_back(make_entry(proj, num, swiglu, out_f32, m, k));
-    } else if (g_plan_active) {
+    p.wait_limit = g_wait_limit;
+    if (tp && tp->world > 1) {
+        if (tp->world > kTpMaxWorld || tp->rows_per_rank < 1) return -2;
+        p.tp = *tp;
+        if (!p.tp.status) p.tp.status = status;
+        if (p.tp.wait_limit <= 0) p.tp.wait_limit = g_wait_limit;
+    }
+    p.x_stage_limit = g_x_stage_limit;
+    TcPlan& pl = cur_plan();
+    if (pl.recording) {
+        pl.entries.push_back(make_entry(proj, num, swiglu, out_f32, m, k));
+    } else if (pl.active) {
         const PlanEntry cur = make_entry(proj, num, swiglu, out_f32, m, k);
-        if (g_plan_cursor < g_plan.size() && same_launch(g_plan[g_plan_cursor], cur)) {
+        if (pl.cursor < pl.entries.size() && same_launch(pl.entries[pl.cursor], cur)) {
             // (the last launch of the sequence looks ahead to the first one of the next round)
-            fill_prefetch(p, g_plan[(g_plan_cursor + 1) % g_plan.size()], num_sms);
-            ++g_plan_cursor;
+            fill_prefetch(p, pl.entries[(pl.cursor + 1) % pl.entries.size()], num_sms);
+            ++pl.cursor;
         } else {
-            g_plan_active = false;  // not the recorded sequence: no more hints
+            pl.active = false;  // not the recorded sequence: no more hints
         }
     }
     cudaError_t e;
@@ -1128,9 +1180,57 @@ struct NoAllocDevice {
     NoAllocScratch* ptr = nullptr;
     int num_sms = 0;
 };
-NoAllocDevice g_noalloc_dev[64];
+NoAllocDevice g_noalloc_dev[kMaxDevices];
+std::mutex g_noalloc_mutex;
+
+// Once per device, with that device current: resolves the array's device address and configures the three
+// fp16-output instantiations, so that later calls only enqueue work.
+int noalloc_setup(int dev, NoAllocDevice** out) {
+    NoAllocDevice& nd = g_noalloc_dev[dev];
+    std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+    if (!nd.ptr) {
+        void* p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+        if (e != cudaSuccess || !p) {
+            set_last_error(e != cudaSuccess ? cudaGetErrorString(e) : "cudaGetSymbolAddress returned no address");
+            cudaGetLastError();
+            return -1;
+        }
+        int sms = 0;
+        if ((e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) {
+            set_last_error(cudaGetErrorString(e));
+            return -1;
+        }
+        const int* table = nullptr;
+        if ((e = configure<16, 8, __half>(&table)) != cudaSuccess || (e = configure<16, 16, __half>(&table)) != cudaSuccess ||
+            (e = configure<32, 32, __half>(&table)) != cudaSuccess) {
+            set_last_error(cudaGetErrorString(e));
+            return -1;
+        }
+        nd.num_sms = sms;
+        nd.ptr = static_cast<NoAllocScratch*>(p);
+    }
+    *out = &nd;
+    return 0;
+}
 
 }  // namespace
+
+// Reads and clears the status word of the allocation-free entry point on `device` (0 when that entry point
+// has not been used there).  The caller has made `device` current.
+int tc_noalloc_take_status(int device) {
+    if (device < 0 || device >= kMaxDevices) return 0;
+    NoAllocScratch* ptr = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+        ptr = g_noalloc_dev[device].ptr;
+    }
+    if (!ptr) return 0;
+    int v = 0;
+    if (cudaMemcpy(&v, &ptr->status, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+    if (v != 0) cudaMemset(&ptr->status, 0, sizeof(int));
+    return v;
+}
 }  // namespace xb
 
 extern "C" __attribute__((visibility("default"))) int xinfer_linear_int4_f16f16_noalloc(
@@ -1140,20 +1240,10 @@ extern "C" __attribute__((visibility("default"))) int xinfer_linear_int4_f16f16_
     if (M <= 0 || N <= 0 || K <= 0) return 1;  // XINFER_NOOP_INVALID_SHAPE, as the allocating entry point
     if (!Y_f16 || !X_f16 || !W_int4 || !scales_f16) return -2;
     int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -6;
-    NoAllocDevice& nd = g_noalloc_dev[dev];
-    if (!nd.ptr) {
-        // once per device, with that device current: resolve the array's device address
-        void* p = nullptr;
-        if (cudaGetSymbolAddress(&p, g_noalloc_scratch) != cudaSuccess || !p) {
-            cudaGetLastError();
-            return -1;
-        }
-        int sms = 0;
-        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return -1;
-        nd.num_sms = sms;
-        nd.ptr = static_cast<NoAllocScratch*>(p);
-    }
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return -6;
+    NoAllocDevice* ndp = nullptr;
+    if (noalloc_setup(dev, &ndp) != 0) return -1;
+    NoAllocDevice& nd = *ndp;
     TcProj proj{Y_f16, W_int4, scales_f16, bias, N, 0};
     // sizes beyond the fixed scratch, or shapes the tensor-core kernel does not take, are refused: this entry
     // point has no second code path to fall back on
@@ -1162,10 +1252,13 @@ extern "C" __attribute__((visibility("default"))) int xinfer_linear_int4_f16f16_
     const long long tiles = (N + kTileRows - 1) / kTileRows;
     if (tiles > kNoAllocMaxTiles) return -2;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    // the array keeps whatever the last call left: the counters (and the status word) must start at zero
-    if (cudaMemsetAsync(nd.ptr->counters, 0, static_cast<size_t>(tiles) * sizeof(int), s) != cudaSuccess) return -1;
-    if (cudaMemsetAsync(&nd.ptr->status, 0, sizeof(int), s) != cudaSuccess) return -1;
+    // The array keeps whatever the last call left.  The tile counters must start at zero (a call that ended in
+    // a timeout may have left some set); the status word is NOT cleared here: it keeps a timeout on record
+    // until xinfer_device_status() has reported it.
+    cudaError_t e = cudaMemsetAsync(nd.ptr->counters, 0, static_cast<size_t>(tiles) * sizeof(int), s);
+    if (e != cudaSuccess) { set_last_error(cudaGetErrorString(e)); return -1; }
     const int rc = tc_launch(s, X_f16, &proj, 1, false, false, M, K, nd.num_sms, nd.ptr->partials, nd.ptr->counters,
                              kNoAllocMaxTiles, &nd.ptr->status);
+    if (rc == -1) set_last_error(cudaGetErrorString(cudaGetLastError()));
     return rc == 0 ? 0 : (rc == -1 ? -1 : -2);
 }

@@ -204,6 +204,64 @@ def device_status(device: int = 0) -> int:
     return int(lib().xinfer_device_status(device))
 
 
+def set_wait_hooks(limit_clocks: int = 0, withhold_x_from_stage: int = -1) -> None:
+    """Test hook for the bounded device-side waits of the tcgen05 linear kernel (0 / -1 restore the defaults)."""
+    lib().xinfer_debug_set_wait_hooks(limit_clocks, withhold_x_from_stage)
+
+
+# ---- per-layer mixer ops (fp16 overloads of the reference's ops) -------------------------------------------
+def rmsnorm(out: torch.Tensor, inp: torch.Tensor, weight: torch.Tensor, num_tokens: int, hidden_size: int,
+            eps: float = 1e-6) -> int:
+    """``xinfer::ops::rmsnorm`` (src/ops/rmsnorm.h:17-23), fp16 in/out, fp32 weight."""
+    return check(lib().xinfer_rmsnorm_f16(_stream(), _ptr(out), _ptr(inp), _ptr(weight), num_tokens, hidden_size, eps),
+                 "rmsnorm")
+
+
+def rmsnorm_residual(out, residual, inp, weight, num_tokens: int, hidden_size: int, eps: float = 1e-6) -> int:
+    """``xinfer::ops::rmsnorm_residual`` (src/ops/rmsnorm.h:35-42): residual += in; out = rmsnorm(residual)."""
+    return check(lib().xinfer_rmsnorm_residual_f16(_stream(), _ptr(out), _ptr(residual), _ptr(inp), _ptr(weight),
+                                                   num_tokens, hidden_size, eps), "rmsnorm_residual")
+
+
+def rope(q: Optional[torch.Tensor], k: Optional[torch.Tensor], num_tokens: int, num_q_heads: int, num_kv_heads: int,
+         head_dim: int, positions: torch.Tensor, theta: float = 1.0e7, rotary_dim: int = 64) -> int:
+    """``xinfer::ops::rope`` (src/ops/rope.h:25-34), in place; positions is a device int64 tensor."""
+    return check(lib().xinfer_rope_f16(_stream(), _ptr(q), _ptr(k), num_tokens, num_q_heads, num_kv_heads, head_dim,
+                                       _ptr(positions), theta, rotary_dim), "rope")
+
+
+def attention_write_kv_cache(k_cache, v_cache, K_in, V_in, start_pos: int, num_tokens: int, num_kv_heads: int,
+                             head_dim: int, max_seq_len: int = 0) -> int:
+    """``xinfer::ops::attention_write_kv_cache`` (src/ops/attention.h:49-58)."""
+    return check(lib().xinfer_attention_write_kv_cache_f16(_stream(), _ptr(k_cache), _ptr(v_cache), _ptr(K_in), _ptr(V_in),
+                                                           start_pos, num_tokens, num_kv_heads, head_dim, max_seq_len),
+                 "attention_write_kv_cache")
+
+
+def sdpa_causal_cached(out, Q, k_cache, v_cache, start_pos: int, num_q_tokens: int, num_q_heads: int, num_kv_heads: int,
+                       head_dim: int, scale: float = 0.0, max_seq_len: int = 0) -> int:
+    """``xinfer::ops::sdpa_causal_cached`` (src/ops/attention.h:102-113)."""
+    return check(lib().xinfer_sdpa_causal_cached_f16(_stream(), _ptr(out), _ptr(Q), _ptr(k_cache), _ptr(v_cache), start_pos,
+                                                     num_q_tokens, num_q_heads, num_kv_heads, head_dim, scale, max_seq_len),
+                 "sdpa_causal_cached")
+
+
+def causal_conv1d_silu(out_qkv, in_qkv, conv_w, seq_len: int, conv_state: Optional[torch.Tensor] = None,
+                       num_channels: int = 10240) -> int:
+    """``targets::qwen3_8::causal_conv1d_silu`` (src/targets/qwen3_8/linear_attn.h:15-21)."""
+    return check(lib().xinfer_causal_conv1d_silu_f16(_stream(), _ptr(out_qkv), _ptr(in_qkv), _ptr(conv_w), seq_len,
+                                                     _ptr(conv_state), num_channels), "causal_conv1d_silu")
+
+
+def recurrent_gated_delta_net(out, qkv, z, b, a, A_log, dt_bias, norm_weight, state_buffer, seq_len: int,
+                              zero_state: bool = False, num_v_heads: int = 48, num_k_heads: int = 16) -> int:
+    """``targets::qwen3_8::recurrent_gated_delta_net`` (src/targets/qwen3_8/linear_attn.h:41-58)."""
+    return check(lib().xinfer_recurrent_gated_delta_net_f16(_stream(), _ptr(out), _ptr(qkv), _ptr(z), _ptr(b), _ptr(a),
+                                                            _ptr(A_log), _ptr(dt_bias), _ptr(norm_weight), _ptr(state_buffer),
+                                                            seq_len, 1 if zero_state else 0, num_v_heads, num_k_heads),
+                 "recurrent_gated_delta_net")
+
+
 def last_linear_path() -> int:
     return int(lib().xinfer_last_linear_path())
 

@@ -41,17 +41,27 @@ _DTYPES = {"w": np.uint8, "s": np.float16}
 
 
 class SpecDecoder:
-    def __init__(self, shape: Shape, batch: int = 8, k: int = 3, max_seq: int = 8448, seed: int = 0):
+    def __init__(self, shape: Shape, batch: int = 8, k: int = 3, max_seq: int = 8448, seed: int = 0, tp=None):
+        """``tp``: a connected ``xinfer_b200.tp.TpGroup`` for the N-split step (every rank creates its decoder with the
+        same arguments), None for one GPU."""
         self.shape, self.batch, self.k, self.max_seq = shape, batch, k, max_seq
+        self.tp = tp
         h = C.c_void_p()
         cfg = shape.to_c()
-        code = lib().xinfer_spec_decoder_create(C.byref(cfg), batch, k, max_seq, seed, C.byref(h))
+        code = lib().xinfer_spec_decoder_create_tp(C.byref(cfg), batch, k, max_seq, seed,
+                                                   None if tp is None else tp.handle, C.byref(h))
         if code == _lib.ERR_OUT_OF_MEMORY:
             raise MemoryError("SpecDecoder: device allocation failed")
         check(code, "spec_decoder_create")
         self._h = h
         self._emitted = np.zeros((batch, k + 1), np.int64)
         self._counts = np.zeros(batch, np.int32)
+
+    @staticmethod
+    def exchange_bytes(shape: Shape, batch: int, k: int, world: int) -> int:
+        """Size of the exchange region a ``TpGroup`` needs for this decoder."""
+        cfg = shape.to_c()
+        return int(lib().xinfer_spec_decoder_exchange_bytes(C.byref(cfg), batch, k, world))
 
     def close(self):
         if getattr(self, "_h", None):

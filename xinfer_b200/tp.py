@@ -8,11 +8,15 @@ fp16 restores the full activation on every rank.  One process per GPU; the colle
 ``[g][M][N/g]`` staging buffer, the all-gather runs in place on that buffer, and ``unstage`` turns it into
 row-major ``[M][N]``.
 
-Stateful mixers (KV cache, DeltaNet state) do not shard this way; the speculative step as a whole runs as
-independent replicas (see ``bench.py``).
+``ColumnShardedLinear`` is the plain NCCL form (the baseline).  ``TpGroup`` is the product path: every rank owns an
+exchange region mapped into all processes (CUDA IPC), the linear kernel's epilogue stores its slice straight into
+every rank's activation buffer over NVLink and a flag per (receiver, sender) completes the exchange inside the
+same launch; ``xinfer_b200.spec.SpecDecoder(tp=group)`` runs the whole speculative step that way (projections
+N-split, KV cache and recurrent state split by sequence).
 """
 from __future__ import annotations
 
+import ctypes as C
 from typing import Callable, Optional, Tuple
 
 import torch
@@ -102,3 +106,95 @@ class ColumnShardedLinear:
     def forward(self, X: torch.Tensor, M: int, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         self.compute_local(X, M)
         return self.unstage(self.gather(M), out)
+
+
+class TpGroup:
+    """This rank's end of the N-split exchange (``xinfer_tp_*`` in the C-ABI).
+
+    Creates the rank's exchange region, all-gathers the IPC handles over ``torch.distributed`` (any backend: the
+    blobs travel as CPU or CUDA byte tensors) and maps the peers' regions.  The current CUDA device must be the
+    rank's own.  ``world == 1`` needs no process group.
+    """
+
+    def __init__(self, region_bytes: int, rank: Optional[int] = None, world: Optional[int] = None, group=None):
+        from ._lib import check, lib
+        self.group = group
+        self.world = (dist.get_world_size(group) if dist.is_initialized() else 1) if world is None else world
+        self.rank = (dist.get_rank(group) if dist.is_initialized() else 0) if rank is None else rank
+        h = C.c_void_p()
+        check(lib().xinfer_tp_create(self.rank, self.world, region_bytes, C.byref(h)), "tp_create")
+        self._h = h
+        if self.world > 1:
+            nb = int(lib().xinfer_tp_handle_bytes())
+            blob = (C.c_ubyte * nb)()
+            check(lib().xinfer_tp_handle(self._h, blob), "tp_handle")
+            mine = torch.tensor(list(bytes(blob)), dtype=torch.uint8)
+            if dist.get_backend(group) == "nccl":
+                mine = mine.cuda()
+            gathered = [torch.empty_like(mine) for _ in range(self.world)]
+            dist.all_gather(gathered, mine, group=group)
+            allb = b"".join(bytes(t.cpu().numpy().tobytes()) for t in gathered)
+            buf = C.create_string_buffer(allb, len(allb))
+            check(lib().xinfer_tp_connect(self._h, C.cast(buf, C.c_void_p)), "tp_connect")
+        else:
+            check(lib().xinfer_tp_connect(self._h, None), "tp_connect")
+
+    @property
+    def handle(self):
+        return self._h
+
+    def close(self):
+        from ._lib import lib
+        if getattr(self, "_h", None):
+            lib().xinfer_tp_destroy(self._h)
+            self._h = None
+
+    def alloc(self, nbytes: int) -> int:
+        """Byte offset of a new buffer in the region (same on every rank when all allocate in the same order)."""
+        from ._lib import check, lib
+        off = C.c_size_t()
+        check(lib().xinfer_tp_alloc(self._h, nbytes, C.byref(off)), "tp_alloc")
+        return int(off.value)
+
+    def read(self, offset: int, nbytes: int):
+        """Host copy (numpy uint8) of ``nbytes`` of this rank's region at ``offset``; synchronises the device."""
+        import numpy as np
+        from ._lib import check, lib
+        torch.cuda.synchronize()
+        out = np.empty(nbytes, np.uint8)
+        check(lib().xinfer_copy_device_to_host(out.ctypes.data_as(C.c_void_p), lib().xinfer_tp_ptr(self._h, offset), nbytes),
+              "copy_device_to_host")
+        return out
+
+    def write(self, offset: int, array) -> None:
+        import numpy as np
+        from ._lib import check, lib
+        a = np.ascontiguousarray(array)
+        torch.cuda.synchronize()
+        check(lib().xinfer_copy_host_to_device(lib().xinfer_tp_ptr(self._h, offset), a.ctypes.data_as(C.c_void_p), a.nbytes),
+              "copy_host_to_device")
+
+    def linear(self, y_offset: int, ldy: int, col0: int, X, W_local, scales_local, bias_local, M: int, n_local: int, K: int,
+               rows_per_rank: int = 0, group_size: int = 128) -> int:
+        """This rank's slice of ``linear_int4`` stored into every rank's Y (or the row owner's, rows_per_rank > 0)."""
+        from ._lib import check, lib
+        return check(lib().xinfer_tp_linear_int4_f16f16(
+            self._h, torch.cuda.current_stream().cuda_stream, y_offset, ldy, col0, X.data_ptr(), W_local.data_ptr(),
+            scales_local.data_ptr(), None if bias_local is None else bias_local.data_ptr(), M, n_local, K, group_size,
+            rows_per_rank), "tp_linear_int4")
+
+    def push(self, offset: int, nbytes: int) -> int:
+        from ._lib import check, lib
+        return check(lib().xinfer_tp_push(self._h, torch.cuda.current_stream().cuda_stream, offset, nbytes), "tp_push")
+
+    def barrier(self) -> int:
+        from ._lib import check, lib
+        return check(lib().xinfer_tp_barrier(self._h, torch.cuda.current_stream().cuda_stream), "tp_barrier")
+
+    def set_wait_limit(self, clocks: int) -> None:
+        from ._lib import lib
+        lib().xinfer_tp_set_wait_limit(self._h, clocks)
+
+    def status(self) -> int:
+        from ._lib import lib
+        return int(lib().xinfer_tp_status(self._h))
