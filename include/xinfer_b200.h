@@ -380,6 +380,42 @@ XINFER_EXPORT int xinfer_copy_host_to_device(void* dst_dev, const void* src_host
  * file variant reads at most max_bytes (0 = whole file), unreadable file -> 0. */
 XINFER_EXPORT uint64_t xinfer_crc64(const void* data, size_t length);
 XINFER_EXPORT uint64_t xinfer_crc64_file(const char* filepath, uint64_t max_bytes);
+/* Incremental form of the same CRC for data that arrives in pieces: start from state ~0 (all ones), feed the
+ * pieces in order, complement the final state; xinfer_crc64(d, n) == ~xinfer_crc64_update(~0, d, n).  No
+ * counterpart in the C-ABI of the reference (its Crc64 class is C++ only, src/artifact/checksum.h). */
+XINFER_EXPORT uint64_t xinfer_crc64_update(uint64_t state, const void* data, size_t length);
+
+/* ---- `.xinfer` artifacts ------------------------------------------------------------------------------
+ * Reader of the reference's container (docs/artifact-format.md; src/artifact/container.h:20-63) and loader of
+ * its tensors into device memory.  open() applies the checks of ArtifactReader::open (src/artifact/reader.cpp:
+ * 59-196: magics, version, header size, file size, bounds of metadata / section table / every section) and,
+ * on request, the whole-file CRC-64 (reader.cpp:266-310).  Section payloads stream through pinned staging
+ * buffers; their CRC-64 is checked while they stream.  XINFER_ERR_CONTRACT = checksum mismatch. */
+typedef struct xinfer_artifact xinfer_artifact;
+XINFER_EXPORT int xinfer_artifact_open(const char* path, int verify_file_checksum, xinfer_artifact** out);
+XINFER_EXPORT void xinfer_artifact_close(xinfer_artifact* a);
+XINFER_EXPORT int xinfer_artifact_section_count(const xinfer_artifact* a);
+XINFER_EXPORT int xinfer_artifact_find(const xinfer_artifact* a, const char* name); /* index, or -1 */
+XINFER_EXPORT int xinfer_artifact_section_info(const xinfer_artifact* a, int index, const char** name, uint32_t* type_tag,
+                                               uint64_t* offset, uint64_t* size, uint64_t* checksum);
+XINFER_EXPORT const char* xinfer_artifact_metadata(const xinfer_artifact* a, uint64_t* size); /* the JSON block */
+XINFER_EXPORT const char* xinfer_artifact_error(const xinfer_artifact* a);
+/* Whole section into host memory, checksum verified.  Replaces ArtifactReader::read_section, reader.h:44-47. */
+XINFER_EXPORT int xinfer_artifact_read_section(xinfer_artifact* a, const char* name, void* dst_host, uint64_t capacity);
+/* Bytes [offset, offset + bytes) of a section into device memory (synchronous).  verify != 0 reads the whole
+ * section and checks its CRC-64 even when only a part is kept. */
+XINFER_EXPORT int xinfer_artifact_load_section(xinfer_artifact* a, const char* name, uint64_t offset, uint64_t bytes,
+                                               void* dst_dev, int verify);
+/* One INT4 projection: sections `weight_name` ([out][in/2] bytes) and `weight_name`.scales ([out][in/group]
+ * fp16) with the size checks of load_linear (src/targets/qwen3_8_27b/weights.cpp:252-304); rows
+ * [row0, row0 + rows) of both go to the device: the whole projection, or the N-split shard of one rank. */
+XINFER_EXPORT int xinfer_artifact_load_linear(xinfer_artifact* a, const char* weight_name, int64_t out_features,
+                                              int64_t in_features, int group_size, int64_t row0, int64_t rows,
+                                              void* dst_weights_dev, void* dst_scales_dev, int verify);
+/* A BF16 vector as fp32 on the device, with the checkpoint's "1 + w" RMSNorm convention when add_unit_offset
+ * (src/targets/qwen3_8_27b/weights.cpp:319-347). */
+XINFER_EXPORT int xinfer_artifact_load_bf16_as_f32(xinfer_artifact* a, const char* name, int64_t num_elements,
+                                                   int add_unit_offset, float* dst_dev);
 
 #ifdef __cplusplus
 }

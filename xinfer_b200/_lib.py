@@ -140,6 +140,19 @@ SIGNATURES = {
     "xinfer_copy_host_to_device": (_i32, [_vp, _vp, _sz]),
     "xinfer_crc64": (_u64, [_vp, _sz]),
     "xinfer_crc64_file": (_u64, [C.c_char_p, _u64]),
+    "xinfer_crc64_update": (_u64, [_u64, _vp, _sz]),
+    "xinfer_artifact_open": (_i32, [C.c_char_p, _i32, C.POINTER(_vp)]),
+    "xinfer_artifact_close": (None, [_vp]),
+    "xinfer_artifact_section_count": (_i32, [_vp]),
+    "xinfer_artifact_find": (_i32, [_vp, C.c_char_p]),
+    "xinfer_artifact_section_info": (_i32, [_vp, _i32, C.POINTER(C.c_char_p), C.POINTER(C.c_uint32), C.POINTER(_u64),
+                                            C.POINTER(_u64), C.POINTER(_u64)]),
+    "xinfer_artifact_metadata": (C.c_char_p, [_vp, C.POINTER(_u64)]),
+    "xinfer_artifact_error": (C.c_char_p, [_vp]),
+    "xinfer_artifact_read_section": (_i32, [_vp, C.c_char_p, _vp, _u64]),
+    "xinfer_artifact_load_section": (_i32, [_vp, C.c_char_p, _u64, _u64, _vp, _i32]),
+    "xinfer_artifact_load_linear": (_i32, [_vp, C.c_char_p, _i64, _i64, _i32, _i64, _i64, _vp, _vp, _i32]),
+    "xinfer_artifact_load_bf16_as_f32": (_i32, [_vp, C.c_char_p, _i64, _i32, _vp]),
 }
 
 

@@ -397,6 +397,11 @@ uint64_t xinfer_crc64(const void* data, size_t length) {
     return ~crc_update(~0ull, data, length);
 }
 
+uint64_t xinfer_crc64_update(uint64_t state, const void* data, size_t length) {
+    if (!data || length == 0) return state;
+    return crc_update(state, data, length);
+}
+
 uint64_t xinfer_crc64_file(const char* filepath, uint64_t max_bytes) {
     if (!filepath) return 0ull;
     FILE* f = fopen(filepath, "rb");
