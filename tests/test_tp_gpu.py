@@ -226,21 +226,23 @@ def _decoder_worker(rank, world, port, out):
         dec = SpecDecoder(shape, batch=B, k=k, max_seq=max_seq, seed=5, tp=tp)
         dec.reset(37, seed=4)
         dist.barrier()
-        ok_tokens, worst_x = True, 0.0
+        ok_tokens, worst_x, per_step = True, 0.0, []
         stream = torch.cuda.Stream()
         with torch.cuda.stream(stream):
             for i in range(5):
                 if i == 2:
-                    dec.capture(stream)       # runs one eager step (the third), then replays from the fourth on
-                else:
-                    dec.step()
+                    dec.capture(stream)       # records the step as a CUDA graph (no step runs: two have run already)
+                dec.step()                    # eager for i < 2, graph replays from here on
                 e, c = dec.results()
                 ctx = dec.tensor(-1, "ctx", np.int32)
                 x = dec.tensor(-1, "x", np.float16).astype(np.float32)
-                ok_tokens &= bool(np.array_equal(e, want[i][0]) and np.array_equal(c, want[i][1]) and
-                                  np.array_equal(ctx, want[i][2]))
-                worst_x = max(worst_x, float(np.sqrt(np.mean((x - want[i][3]) ** 2)) /
-                                             (np.sqrt(np.mean(want[i][3] ** 2)) + 1e-30)))
+                same = bool(np.array_equal(e, want[i][0]) and np.array_equal(c, want[i][1]) and
+                            np.array_equal(ctx, want[i][2]))
+                rel = float(np.sqrt(np.mean((x - want[i][3]) ** 2)) / (np.sqrt(np.mean(want[i][3] ** 2)) + 1e-30))
+                per_step.append((same, rel, e.tolist(), want[i][0].tolist()))
+                ok_tokens &= same
+                worst_x = max(worst_x, rel)
+        out[f"steps{rank}"] = per_step
         out[rank] = (ok_tokens, worst_x, dec.info(3), dec.info(6), tp.status())
         dist.barrier()
         dec.close()
@@ -252,7 +254,7 @@ def _decoder_worker(rank, world, port, out):
 def test_tp_decoder_matches_single_gpu_decoder(cuda):
     """Projections N-split over the ranks, KV cache and recurrent state split by sequence, LM head split by
     vocabulary: emitted tokens, counts and context lengths equal the single-GPU decoder's on the same seeds over
-    five steps (two eager, one inside capture, two graph replays); hidden rows agree to fp16 rounding (the
+    five steps (two eager, three graph replays); hidden rows agree to fp16 rounding (the
     K-split summation order differs between a slice and the whole projection)."""
     n = torch.cuda.device_count()
     if n < 2:
@@ -261,6 +263,6 @@ def test_tp_decoder_matches_single_gpu_decoder(cuda):
     out = _spawn(_decoder_worker, world)
     for r in range(world):
         ok_tokens, worst_x, captured, exchanges, status = out[r]
-        assert ok_tokens, r
+        assert ok_tokens, (r, [(st[0], st[1]) for st in out[f"steps{r}"]], out[f"steps{r}"])
         assert worst_x < 2e-2, worst_x
         assert captured == 1 and exchanges > 0 and status == 0

@@ -531,8 +531,13 @@ __global__ void __launch_bounds__(256) attn_combine_kernel(__half* out, const fl
 // One thread per (sequence, channel).  state [B][3][C] holds the last three committed inputs; pending
 // [B][Rmax][C] the raw inputs of the previous step, of which the first n_commit[b] were accepted.
 __global__ void conv1d_spec_kernel(__half* out, const __half* in, const float* conv_w, float* state, float* pending,
-                                   const int* n_commit, int rows_per_seq, int prev_rows, int channels, int nc_base) {
-    griddep_prologue();
+                                   const int* n_commit, int rows_per_seq, int prev_rows, int channels, int nc_base,
+                                   int early_state) {
+    // state, pending inputs and weights do not depend on the kernel in front of this one: they are read, and the
+    // committed state written, before waiting for it (only `in` comes from that kernel).  early_state = 0: the
+    // caller's previous launch wrote them, so everything waits.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    if (!early_state) asm volatile("griddepcontrol.wait;" ::: "memory");
     const int c = blockIdx.x * blockDim.x + threadIdx.x;
     const int b = blockIdx.y;
     if (c >= channels) return;
@@ -550,6 +555,7 @@ __global__ void conv1d_spec_kernel(__half* out, const __half* in, const float* c
     st[channels + c] = s1;
     st[2 * channels + c] = s2;
     const float w0 = conv_w[c * 4], w1 = conv_w[c * 4 + 1], w2 = conv_w[c * 4 + 2], w3 = conv_w[c * 4 + 3];
+    if (early_state) asm volatile("griddepcontrol.wait;" ::: "memory");
     for (int i = 0; i < rows_per_seq; ++i) {
         const long long row = static_cast<long long>(b) * rows_per_seq + i;
         const float x = __half2float(in[row * channels + c]);
@@ -575,8 +581,15 @@ __global__ void __launch_bounds__(512, 2) gdn_spec_kernel(__half* out, const __h
                                                           const float* dt_bias, const float* norm_w, float* state,
                                                           float* pend_k, float* pend_d, float* pend_g,
                                                           const int* n_commit, int rows_per_seq, int prev_rows, int hv,
-                                                          int hk, int nc_base) {
-    griddep_prologue();
+                                                          int hk, int nc_base, int early_state) {
+    // The recurrent state, the previous step's pending updates and the per-head constants were written many
+    // launches ago (by this layer's kernel of the previous pass, and by the commit at the end of the previous step):
+    // they are fetched BEFORE waiting for the kernel in front of this one, so that the bulk of this kernel's memory
+    // traffic overlaps the projection and convolution that precede it.  Only q/k/v/z/b/a come from those.
+    // (early_state = 0: the caller's previous launch wrote the state - the stand-alone op entry point chaining
+    // chunks of one sequence - so everything waits.)
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    if (!early_state) asm volatile("griddepcontrol.wait;" ::: "memory");
     __shared__ __align__(16) float sh_q[8][128], sh_k[8][128];
     __shared__ float sh_beta[8], sh_eg[8], red[2][16];
     __shared__ float part_sum[2][4][128], attn_all[8][4][128];
@@ -592,10 +605,13 @@ __global__ void __launch_bounds__(512, 2) gdn_spec_kernel(__half* out, const __h
     float col[32];
 #pragma unroll
     for (int i = 0; i < 32; ++i) col[i] = S[(i0 + i) * 128 + j];
-
-    // ---- phase 0: per-token quantities that do not depend on the state (token tt handled by thread group tt % 4)
     const float exp_a_log = expf(A_log[h]);
     const float dtb = dt_bias[h];
+    int nc = n_commit ? n_commit[b] : nc_base;
+    if (nc > prev_rows) nc = prev_rows;
+    if (early_state) asm volatile("griddepcontrol.wait;" ::: "memory");
+
+    // ---- phase 0: per-token quantities that do not depend on the state (token tt handled by thread group tt % 4)
     for (int t0 = 0; t0 < rows_per_seq; t0 += 4) {
         const int tt = t0 + part;
         float raw_q = 0.f, raw_k = 0.f;
@@ -625,8 +641,6 @@ __global__ void __launch_bounds__(512, 2) gdn_spec_kernel(__half* out, const __h
     }
 
     // ---- replay of the previous step's accepted updates, then write the committed state
-    int nc = n_commit ? n_commit[b] : nc_base;
-    if (nc > prev_rows) nc = prev_rows;
     if (nc > 0) {
         for (int t = 0; t < nc; ++t) {
             const float eg = pend_g[pbase + t];
@@ -840,18 +854,19 @@ int attn_decode_ex(cudaStream_t s, __half* out, const __half* q, const __half* q
 }
 
 int conv1d_spec(cudaStream_t s, __half* out, const __half* in, const float* conv_w, float* state, float* pending,
-                const int* n_commit, int batch, int rows_per_seq, int prev_rows, int channels, int nc_base) {
+                const int* n_commit, int batch, int rows_per_seq, int prev_rows, int channels, int nc_base, int early_state) {
     dim3 grid((channels + 255) / 256, batch);
-    launch_pdl(conv1d_spec_kernel, dim3(grid), dim3(256), 0, s, out, in, conv_w, state, pending, n_commit, rows_per_seq, prev_rows, channels, nc_base);
+    launch_pdl(conv1d_spec_kernel, dim3(grid), dim3(256), 0, s, out, in, conv_w, state, pending, n_commit, rows_per_seq, prev_rows, channels, nc_base, early_state);
     return XB_LAUNCH_OK();
 }
 
 int gdn_spec(cudaStream_t s, __half* out, const __half* qkv, const __half* z, const __half* b, const __half* a,
              const float* A_log, const float* dt_bias, const float* norm_w, float* state, float* pend_k, float* pend_d,
-             float* pend_g, const int* n_commit, int batch, int rows_per_seq, int prev_rows, int hv, int hk, int nc_base) {
+             float* pend_g, const int* n_commit, int batch, int rows_per_seq, int prev_rows, int hv, int hk, int nc_base,
+             int early_state) {
     dim3 grid(hv, batch);
     launch_pdl(gdn_spec_kernel, dim3(grid), dim3(512), 0, s, out, qkv, z, b, a, A_log, dt_bias, norm_w, state, pend_k, pend_d, pend_g,
-                                         n_commit, rows_per_seq, prev_rows, hv, hk, nc_base);
+                                         n_commit, rows_per_seq, prev_rows, hv, hk, nc_base, early_state);
     return XB_LAUNCH_OK();
 }
 

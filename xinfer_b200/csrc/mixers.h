@@ -39,13 +39,17 @@ int attn_decode_ex(cudaStream_t s, __half* out, const __half* q, const __half* q
 
 // state [batch][3][channels], pending [batch][8][channels] fp32.  The first min(n_commit[b], prev_rows) pending
 // inputs of the previous call are committed to the state before the new rows are processed (n_commit null:
-// nc_base of them).  rows_per_seq = 0 only commits.
+// nc_base of them).  rows_per_seq = 0 only commits.  early_state = 1 (both kernels): state, pending updates and
+// weights were NOT written by the launch directly in front of this one in the stream, so the kernel may fetch
+// them while that launch is still running (programmatic dependent launch).
 int conv1d_spec(cudaStream_t s, __half* out, const __half* in, const float* conv_w, float* state, float* pending,
-                const int* n_commit, int batch, int rows_per_seq, int prev_rows, int channels, int nc_base = 0);
+                const int* n_commit, int batch, int rows_per_seq, int prev_rows, int channels, int nc_base = 0,
+                int early_state = 0);
 // state [batch][hv][128][128], pend_k / pend_d [batch][hv][8][128], pend_g [batch][hv][8] fp32
 int gdn_spec(cudaStream_t s, __half* out, const __half* qkv, const __half* z, const __half* b, const __half* a,
              const float* A_log, const float* dt_bias, const float* norm_w, float* state, float* pend_k, float* pend_d,
-             float* pend_g, const int* n_commit, int batch, int rows_per_seq, int prev_rows, int hv, int hk, int nc_base = 0);
+             float* pend_g, const int* n_commit, int batch, int rows_per_seq, int prev_rows, int hv, int hk, int nc_base = 0,
+             int early_state = 0);
 
 int spec_commit(cudaStream_t s, const void* accept_records, const long long* draft_tokens, int batch, int k,
                 int rows_per_seq, int* ctx, int* n_commit, long long* cur_tok, long long* emitted, int* emitted_n,

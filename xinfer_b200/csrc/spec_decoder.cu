@@ -17,6 +17,7 @@
 #include <cuda_runtime.h>
 #include <math.h>
 #include <stdint.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include <new>
@@ -415,19 +416,29 @@ int gather_rows(Dec* d, cudaStream_t s, const XBuf& b, int row0, int rows, int64
     return xb::tp_push(d->tp, s, b.off + static_cast<size_t>(row0) * rb, static_cast<size_t>(rows) * rb) == 0 ? 0 : XINFER_ERR_CUDA;
 }
 
-// One decoder layer on M = batch * R rows; the residual stream `xr` is updated in place (the second residual
-// add is folded into the next norm by the caller).  Projections run on all M rows (N-split over the ranks);
-// the mixer runs on the rows of this rank's own sequences.
-int layer_forward(Dec* d, cudaStream_t s, Layer& L, int R, __half* xr, const XBuf* pending, const int* ctx,
+// y = projection(x_in);  xr = half(xr + y);  normed = rmsnorm(xr) * w.
+// (Running the add + norm as a tail of the projection kernel, by the CTA that completes a block of rows last,
+// was measured slower than the separate launch: under programmatic dependent launch the next projection's
+// weight stream already overlaps the norm kernel.)
+int lin_add_norm(Dec* d, cudaStream_t s, const XBuf& y, const __half* x_in, const Linear& l, int M, __half* xr,
+                 const float* w) {
+    const auto& c = d->cfg;
+    CK(lin(d, s, y, x_in, l, M, kAll));
+    NL(xb::add_rmsnorm_rows(s, d->normed, xr, y.p, w, M, static_cast<int>(l.n_full), c.rms_norm_eps));
+    ++d->launches_per_step;
+    return 0;
+}
+
+// One decoder layer on M = batch * R rows.  On entry `normed` holds the layer's input norm of the residual stream
+// `xr`; on exit `xr` has both residual adds applied and `normed` holds its norm under `next_norm_w` (the next
+// layer's input norm, or the final norm).  Projections run on all M rows (N-split over the ranks); the mixer runs
+// on the rows of this rank's own sequences.
+int layer_forward(Dec* d, cudaStream_t s, Layer& L, int R, __half* xr, const float* next_norm_w, const int* ctx,
                   const int* n_commit, int prev_rows) {
     const auto& c = d->cfg;
     const int B = d->batch, M = B * R;
     const int Bl = d->bl, Ml = Bl * R, row0 = d->b0 * R;
     const int H = static_cast<int>(c.hidden_size);
-    // x += previous layer's MLP output (none for the first layer), then input RMSNorm
-    if (!pending) NL(xb::rmsnorm_rows(s, d->normed, H, xr, L.input_norm, M, H, c.rms_norm_eps));
-    else NL(xb::add_rmsnorm_rows(s, d->normed, xr, pending->p, L.input_norm, M, H, c.rms_norm_eps));
-    ++d->launches_per_step;
     if (L.full) {
         const int hq = static_cast<int>(c.num_attention_heads), hkv = static_cast<int>(c.num_key_value_heads);
         xb::TcProj fd[3] = {make_proj(d, L.q_proj, d->q_gate, kOwner), make_proj(d, L.k_proj, d->kbuf, kOwner),
@@ -445,7 +456,8 @@ int layer_forward(Dec* d, cudaStream_t s, Layer& L, int R, __half* xr, const XBu
                            hkv, d->max_seq, d->attn_splits, d->attn_scratch));
         d->launches_per_step += 3;
         CK(gather_rows(d, s, d->attn_out, row0, Ml, static_cast<int64_t>(hq) * 256));
-        CK(lin(d, s, d->proj_out, d->attn_out.p, L.o_proj, M, kAll));
+        // x += mixer output, post-attention RMSNorm
+        CK(lin_add_norm(d, s, d->proj_out, d->attn_out.p, L.o_proj, M, xr, L.post_norm));
     } else {
         const int hv = static_cast<int>(c.linear_num_v_heads), hk = static_cast<int>(c.linear_num_k_heads);
         const int ch = 2 * hk * 128 + hv * 128;
@@ -457,25 +469,23 @@ int layer_forward(Dec* d, cudaStream_t s, Layer& L, int R, __half* xr, const XBu
         account(d, L.in_a, M, 2, false);
         CK(run_lin(d, s, d->normed, fd, 4, false, false, M, H, Ml, true));
         NL(xb::conv1d_spec(s, d->qkv_conv + static_cast<size_t>(row0) * ch, d->qkv_raw.p + static_cast<size_t>(row0) * ch,
-                           L.conv_w, L.conv_state, L.conv_pend, n_commit + d->b0, Bl, R, prev_rows, ch));
+                           L.conv_w, L.conv_state, L.conv_pend, n_commit + d->b0, Bl, R, prev_rows, ch, 0, 1));
         NL(xb::gdn_spec(s, d->delta_out.p + static_cast<size_t>(row0) * hv * 128, d->qkv_conv + static_cast<size_t>(row0) * ch,
                         d->zbuf.p + static_cast<size_t>(row0) * hv * 128, d->bbuf + static_cast<size_t>(row0) * hv,
                         d->abuf + static_cast<size_t>(row0) * hv, L.A_log, L.dt_bias, L.gdn_norm, L.S, L.pend_k, L.pend_d,
-                        L.pend_g, n_commit + d->b0, Bl, R, prev_rows, hv, hk));
+                        L.pend_g, n_commit + d->b0, Bl, R, prev_rows, hv, hk, 0, 1));
         d->launches_per_step += 2;
         CK(gather_rows(d, s, d->delta_out, row0, Ml, static_cast<int64_t>(hv) * 128));
-        CK(lin(d, s, d->proj_out, d->delta_out.p, L.out_proj, M, kAll));
+        CK(lin_add_norm(d, s, d->proj_out, d->delta_out.p, L.out_proj, M, xr, L.post_norm));
     }
-    // x += mixer output, post-attention RMSNorm
-    NL(xb::add_rmsnorm_rows(s, d->normed, xr, d->proj_out.p, L.post_norm, M, H, c.rms_norm_eps));
-    ++d->launches_per_step;
     {
         xb::TcProj gu[2] = {make_proj(d, L.gate, d->mlp, kAll), make_proj_local(L.up, nullptr)};
         account(d, L.gate, M, 2, true);
         d->linear_bytes += static_cast<double>(L.up.n) * (L.up.k / 2) + static_cast<double>(L.up.n) * (L.up.k / 128) * 2;
         CK(run_lin(d, s, d->normed, gu, 2, true, false, M, H, 1, true));
     }
-    CK(lin(d, s, d->proj_out, d->mlp.p, L.down, M, kAll));  // the caller adds proj_out into the residual stream
+    // x += MLP output, then the norm the next consumer of the residual stream needs
+    CK(lin_add_norm(d, s, d->proj_out, d->mlp.p, L.down, M, xr, next_norm_w));
     return 0;
 }
 
@@ -536,9 +546,10 @@ int draft_pass(Dec* d, cudaStream_t s, int i, bool full) {
         d->launches_per_step += 2;
         return 0;
     }
-    CK(layer_forward(d, s, d->mtp_layer, 1, d->x_mtp.p, nullptr, d->ctx_draft, d->n_commit_zero, 0));
-    // keep the head's output hidden for the next draft pass: x + proj_out (pre final norm)
-    NL(xb::add_rmsnorm_rows(s, d->normed, d->x_mtp.p, d->proj_out.p, d->final_norm, B, H, c.rms_norm_eps));
+    NL(xb::rmsnorm_rows(s, d->normed, H, d->x_mtp.p, d->mtp_layer.input_norm, B, H, c.rms_norm_eps));
+    ++d->launches_per_step;
+    CK(layer_forward(d, s, d->mtp_layer, 1, d->x_mtp.p, d->final_norm, d->ctx_draft, d->n_commit_zero, 0));
+    // keep the head's output hidden (pre final norm) for the next draft pass
     if (!d->linears_only)
         CKCUDA(cudaMemcpyAsync(d->mtp_hidden, d->x_mtp.p, static_cast<size_t>(B) * H * sizeof(__half), cudaMemcpyDeviceToDevice, s));
     CK(lm_head_and_partials(d, s, B));
@@ -553,12 +564,13 @@ int target_pass(Dec* d, cudaStream_t s, int R, const long long* tokens) {
     const auto& c = d->cfg;
     const int M = d->batch * R, H = static_cast<int>(c.hidden_size);
     NL(xb::embed_rows(s, d->x, d->embed, tokens, M, H, c.vocab_size));
-    ++d->launches_per_step;
-    for (size_t l = 0; l < d->layers.size(); ++l)
-        CK(layer_forward(d, s, d->layers[l], R, d->x, l == 0 ? nullptr : &d->proj_out, d->ctx, d->n_commit, d->prev_rows));
-    // final: x += last MLP output, final RMSNorm, LM head -> fp32 logits
-    NL(xb::add_rmsnorm_rows(s, d->normed, d->x, d->proj_out.p, d->final_norm, M, H, c.rms_norm_eps));
-    ++d->launches_per_step;
+    NL(xb::rmsnorm_rows(s, d->normed, H, d->x, d->layers[0].input_norm, M, H, c.rms_norm_eps));
+    d->launches_per_step += 2;
+    const size_t nl = d->layers.size();
+    for (size_t l = 0; l < nl; ++l)
+        CK(layer_forward(d, s, d->layers[l], R, d->x, l + 1 < nl ? d->layers[l + 1].input_norm : d->final_norm, d->ctx,
+                         d->n_commit, d->prev_rows));
+    // `normed` now holds the final norm of the residual stream: LM head -> fp32 logits
     CK(lm_head_and_partials(d, s, M));
     if (!d->linears_only) d->prev_rows = R;
     return 0;
@@ -616,7 +628,7 @@ int xinfer_spec_decoder_create_tp(const xinfer_model_config* cfg, int batch, int
     if (!cfg || !out || batch < 1 || k < 1 || k > 7 || max_seq < 8) return XINFER_ERR_INVALID_ARGUMENT;
     *out = nullptr;
     const auto& c = *cfg;
-    if (c.hidden_size % 128 || c.intermediate_size % 128 || c.num_key_value_heads < 1 ||
+    if (c.num_hidden_layers < 1 || c.hidden_size % 128 || c.intermediate_size % 128 || c.num_key_value_heads < 1 ||
         c.num_attention_heads % c.num_key_value_heads || (c.num_attention_heads / c.num_key_value_heads) * (k + 1) > 32 ||
         c.linear_num_k_heads < 1 || c.linear_num_v_heads % c.linear_num_k_heads || batch * (k + 1) > 32 ||
         c.rope_dim > 256 || c.rope_dim % 2)

@@ -28,13 +28,13 @@ namespace xb {
 
 namespace {
 
-constexpr size_t kHeaderBytes = 4096;  // flags [8] u64 | epoch u64 | done u32 | ... ; buffers start after it
+constexpr size_t kHeaderBytes = 16384;  // flag matrix | exchange count; buffers start after it
 
 struct Header {
-    unsigned long long flags[kTpMaxWorld];
+    unsigned long long flags[kTpMaxWorld][kTpMaxCtas];
     unsigned long long epoch;
-    unsigned int done;
 };
+static_assert(sizeof(Header) <= kHeaderBytes, "exchange header");
 
 // Copies [off, off + bytes) of this rank's region to the same offsets of every peer (16-byte vectors),
 // then runs the exchange handshake.  bytes == 0: handshake only (a barrier among the ranks).
@@ -54,7 +54,7 @@ __global__ void __launch_bounds__(256) tp_push_kernel(TpLink tp, uint8_t* local_
             if (r < tp.world && r != tp.rank) reinterpret_cast<uint4*>(peers[r] + off)[i] = v;
     }
     __syncthreads();
-    if (threadIdx.x == 0) tp_finish_exchange(tp, gridDim.x);
+    if (threadIdx.x < 32) tp_finish_exchange(tp, gridDim.x, blockIdx.x);
 }
 
 }  // namespace
@@ -70,11 +70,10 @@ TpLink tp_link(const TpComm* c, int rows_per_rank) {
     l.rank = c->rank;
     l.rows_per_rank = rows_per_rank;
     for (int r = 0; r < c->world; ++r)
-        l.flags_peer[r] = reinterpret_cast<unsigned long long*>(c->peer_base[r]) + 0;  // Header::flags
+        l.flags_peer[r] = reinterpret_cast<unsigned long long*>(c->peer_base[r]);  // Header::flags
     Header* h = reinterpret_cast<Header*>(c->peer_base[c->rank]);
-    l.flags_local = h->flags;
+    l.flags_local = &h->flags[0][0];
     l.epoch = &h->epoch;
-    l.done = &h->done;
     l.status = c->status;
     l.wait_limit = c->wait_limit;
     return l;

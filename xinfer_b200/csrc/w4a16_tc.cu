@@ -795,9 +795,9 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
     tc_fence_before_sync();
     __syncthreads();
     if (tid == 0 && ctrl->ws.abort_flag) atomicExch(p.status, kStatusWaitTimeout);
-    // N-split exchange: every store of this CTA is ordered before the barrier above; the grid's last CTA
-    // publishes the launch to the peers and waits for theirs
-    if (p.tp.world > 1 && tid == 0) tp_finish_exchange(p.tp, gridDim.x);
+    // N-split exchange: every store of this CTA is ordered before the barrier above; warp 0 publishes the CTA to
+    // the peers, and in CTA 0 waits for theirs
+    if (p.tp.world > 1 && warp == 0) tp_finish_exchange(p.tp, gridDim.x, blockIdx.x);
     if (warp == kMmaWarp) {
         __syncwarp();
         tc_fence_after_sync();
@@ -1127,7 +1127,7 @@ int tc_launch(cudaStream_t stream, const void* x, const TcProj* proj, int num, b
     p.status = status;
     p.wait_limit = g_wait_limit;
     if (tp && tp->world > 1) {
-        if (tp->world > kTpMaxWorld || tp->rows_per_rank < 1) return -2;
+        if (tp->world > kTpMaxWorld || tp->rows_per_rank < 1 || num_sms > kTpMaxCtas) return -2;
         p.tp = *tp;
         if (!p.tp.status) p.tp.status = status;
         if (p.tp.wait_limit <= 0) p.tp.wait_limit = g_wait_limit;
