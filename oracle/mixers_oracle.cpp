@@ -2,11 +2,15 @@
 // header of xinfer_oracle.cpp).  Literal single-sequence restatements of the reference's kernels, with
 // `_Float16` for sycl::half and every fp16 rounding point kept.
 //
-// Parity status: each function restates one reference kernel that the reference's own tests pin only
-// against inline oracles computed at run time (tests/test_ops_oracle.cpp:50-285, 797-906,
-// tests/test_decode_graph.cpp:208-284); no stored vectors exist for them.  The speculative batching and
-// the lazy state commit around them are additions of this repository and are checked against these
-// functions applied sequence by sequence, token by token.
+// Parity status: pinned.  Each function restates one reference kernel; the reference's own tests for those
+// kernels (tests/test_ops_oracle.cpp:50-285, 797-906; tests/test_decode_graph.cpp:208-284; tests/test_kv_cache.cpp:
+// 286-314) hold no stored vectors, they recompute inline fp64 expectations from seeded inputs, so the pin is the
+// same recipe: tests/test_mixer_oracle_pins.py regenerates those inputs (std::mt19937 streams, checked by CRC-64
+// against tests/golden/mixer_streams.json), recomputes the expectations with the tests' own formulas
+// (tests/ref_recipes.py) and holds these functions to the reference's tolerances.  For the gated delta rule the
+// reference tests argument validation only (tests/test_decode_graph.cpp:37-49); its arithmetic here is a
+// line-by-line restatement of src/targets/qwen3_8/linear_attn.cpp:144-343.  The speculative batching and the lazy state commit around these ops are
+// additions of this repository and are checked against these functions applied sequence by sequence, token by token.
 #include <algorithm>
 #include <cmath>
 #include <cstdint>

@@ -178,3 +178,15 @@ def test_gated_delta_net_matches_oracle(cuda, seq_len, zero):
     # fp32 sums in a different order than the oracle's: a few fp16 steps on outputs, 1e-5 relative on the state
     assert np.max(np.abs(got - ref) / (np.abs(ref) + 0.05)) < 5e-3
     assert np.max(np.abs(host(S_d) - S_ref)) <= 1e-5 * max(1.0, float(np.abs(S_ref).max()))
+
+
+def test_shape_validation_like_the_reference(cuda):
+    """tests/test_decode_graph.cpp:23-49: conv1d refuses num_channels <= 0, the delta rule refuses head counts it was
+    not built for (here: v heads not a multiple of k heads); both before touching any pointer."""
+    from xinfer_b200 import _lib
+    with pytest.raises(_lib.XInferError) as e:
+        cuda.causal_conv1d_silu(None, None, None, 1, None, 0)
+    assert e.value.code == _lib.ERR_INVALID_ARGUMENT
+    with pytest.raises(_lib.XInferError) as e:
+        cuda.recurrent_gated_delta_net(None, None, None, None, None, None, None, None, None, 1, False, 32, 5)
+    assert e.value.code == _lib.ERR_INVALID_ARGUMENT

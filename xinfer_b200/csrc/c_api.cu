@@ -154,13 +154,13 @@ namespace xb {
 void set_last_error(const char* msg) { g_last_error = msg ? msg : ""; }
 
 int run_tc_linear(cudaStream_t s, const void* x, const TcProj* proj, int num, bool swiglu, bool out_f32, long long m,
-                  long long k, int group_size, const TpLink* tp) {
+                  long long k, int group_size, const TpLink* tp, int layout_flags) {
     DeviceCtx* c = nullptr;
     int rc = get_ctx(&c);
     if (rc != XINFER_OK) return rc;
     if (!tc_eligible(x, proj, num, swiglu, m, k, group_size)) return XINFER_ERR_INVALID_ARGUMENT;
     const int r = tc_launch(s, x, proj, num, swiglu, out_f32, m, k, c->num_sms, c->workspace, c->counters,
-                            kCounterCapacity, c->status, tp);
+                            kCounterCapacity, c->status, tp, layout_flags);
     if (r == 0) { g_last_path = 1; return XINFER_OK; }
     if (r == -1) return fail_cuda(cudaGetLastError());
     return XINFER_ERR_INVALID_ARGUMENT;

@@ -41,6 +41,23 @@ __device__ __forceinline__ float warp_sum(float v) {
     return v;
 }
 
+// Outputs that feed a W4A16 projection can be written with every block of eight features in the order the int4
+// unpack yields them, (0,4,1,5,2,6,3,7), which saves the projection kernel its in-flight rewrite of the staged
+// activations.  perm8: where feature n goes;  perm8_vec: eight consecutive features (one 16-byte vector) reordered.
+__device__ __forceinline__ int perm8(int n) {
+    const int k = n & 7;
+    return (n & ~7) | ((k < 4) ? 2 * k : 2 * (k - 4) + 1);
+}
+__device__ __forceinline__ uint4 perm8_vec(const uint4& v) {
+    // halves (h0 h1 | h2 h3 | h4 h5 | h6 h7) -> (h0 h4 | h1 h5 | h2 h6 | h3 h7)
+    uint4 o;
+    o.x = __byte_perm(v.x, v.z, 0x5410);
+    o.y = __byte_perm(v.x, v.z, 0x7632);
+    o.z = __byte_perm(v.y, v.w, 0x5410);
+    o.w = __byte_perm(v.y, v.w, 0x7632);
+    return o;
+}
+
 // block-wide sum for up to 1024 threads; every thread gets the result
 __device__ __forceinline__ float block_sum(float v, float* smem) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
@@ -71,7 +88,7 @@ __global__ void embed_kernel(__half* out, const uint16_t* table_bf16, const long
 // mode 1: x = half(float(x) + float(delta)); out = rmsnorm(x) * w   (residual add, then norm)
 // `out` may have a wider row (ld_out) and a column offset so that two norms can fill one concatenated row.
 __global__ void __launch_bounds__(256) rmsnorm_kernel(__half* out, long long ld_out, __half* x, const __half* delta,
-                                                      const float* w, int hidden, float eps) {
+                                                      const float* w, int hidden, float eps, int perm_out) {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     __shared__ float red[32];
     const long long row = blockIdx.x;
@@ -137,7 +154,7 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(__half* out, long long ld_
                     const float2 a = __half22float2(h[j]);
                     oh[j] = __halves2half2(__float2half_rn(a.x * r * ww[2 * j]), __float2half_rn(a.y * r * ww[2 * j + 1]));
                 }
-                *reinterpret_cast<uint4*>(orow + i * 8) = o;
+                *reinterpret_cast<uint4*>(orow + i * 8) = perm_out ? perm8_vec(o) : o;
             }
         }
         return;
@@ -156,7 +173,7 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(__half* out, long long ld_
     const float total = block_sum(ss, red);
     const float r = 1.0f / sqrtf(total / static_cast<float>(hidden) + eps);
     for (int i = threadIdx.x; i < hidden; i += blockDim.x)
-        orow[i] = __float2half_rn(__half2float(xr[i]) * r * w[i]);
+        orow[(perm_out && (hidden & 7) == 0) ? perm8(i) : i] = __float2half_rn(__half2float(xr[i]) * r * w[i]);
 }
 
 // ------------------------------------------------------------------------------- attention prologue
@@ -497,7 +514,7 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_split_kernel(float* part
 // Grid (G * R, Hkv, B), 256 threads = head_dim.
 __global__ void __launch_bounds__(256) attn_combine_kernel(__half* out, const float* part_o, const float* part_ml,
                                                            const __half* q_gate, int nsplit, int rows_per_seq, int hq,
-                                                           int hkv) {
+                                                           int hkv, int perm_out) {
     griddep_prologue();
     const int r = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z, d = threadIdx.x;
     const int G = hq / hkv;
@@ -524,7 +541,7 @@ __global__ void __launch_bounds__(256) attn_combine_kernel(__half* out, const fl
     }
     const float gate = __half2float(q_gate[(row * hq + h) * 512 + 256 + d]);
     const float sig = 1.0f / (1.0f + expf(-gate));
-    out[(row * hq + h) * 256 + d] = __float2half_rn(attn * sig);
+    out[(row * hq + h) * 256 + (perm_out ? perm8(d) : d)] = __float2half_rn(attn * sig);
 }
 
 // ------------------------------------------------------------------------------- causal conv1d + SiLU
@@ -581,7 +598,7 @@ __global__ void __launch_bounds__(512, 2) gdn_spec_kernel(__half* out, const __h
                                                           const float* dt_bias, const float* norm_w, float* state,
                                                           float* pend_k, float* pend_d, float* pend_g,
                                                           const int* n_commit, int rows_per_seq, int prev_rows, int hv,
-                                                          int hk, int nc_base, int early_state) {
+                                                          int hk, int nc_base, int early_state, int perm_out) {
     // The recurrent state, the previous step's pending updates and the per-head constants were written many
     // launches ago (by this layer's kernel of the previous pass, and by the commit at the end of the previous step):
     // they are fetched BEFORE waiting for the kernel in front of this one, so that the bulk of this kernel's memory
@@ -716,7 +733,7 @@ __global__ void __launch_bounds__(512, 2) gdn_spec_kernel(__half* out, const __h
             const long long row = static_cast<long long>(b) * rows_per_seq + tt;
             const float zv = __half2float(z[row * value_dim + h * 128 + j]);
             const float silu_z = zv / (1.0f + expf(-zv));
-            out[row * value_dim + h * 128 + j] = __float2half_rn(attn * inv_std * norm_w[j] * silu_z);
+            out[row * value_dim + h * 128 + (perm_out ? perm8(j) : j)] = __float2half_rn(attn * inv_std * norm_w[j] * silu_z);
         }
     }
 }
@@ -781,14 +798,14 @@ int embed_rows(cudaStream_t s, __half* out, const void* table_bf16, const long l
 }
 
 int rmsnorm_rows(cudaStream_t s, __half* out, long long ld_out, const __half* in, const float* w, int rows, int hidden,
-                 float eps) {
-    launch_pdl(rmsnorm_kernel, dim3(rows), dim3(256), 0, s, out, ld_out, const_cast<__half*>(in), nullptr, w, hidden, eps);
+                 float eps, int perm_out) {
+    launch_pdl(rmsnorm_kernel, dim3(rows), dim3(256), 0, s, out, ld_out, const_cast<__half*>(in), nullptr, w, hidden, eps, perm_out);
     return XB_LAUNCH_OK();
 }
 
 int add_rmsnorm_rows(cudaStream_t s, __half* out, __half* x, const __half* delta, const float* w, int rows, int hidden,
-                     float eps) {
-    launch_pdl(rmsnorm_kernel, dim3(rows), dim3(256), 0, s, out, hidden, x, delta, w, hidden, eps);
+                     float eps, int perm_out) {
+    launch_pdl(rmsnorm_kernel, dim3(rows), dim3(256), 0, s, out, hidden, x, delta, w, hidden, eps, perm_out);
     return XB_LAUNCH_OK();
 }
 
@@ -817,12 +834,12 @@ int attn_decode(cudaStream_t s, __half* out, const __half* q, const __half* q_ga
                 const __half* v_cache, const int* ctx, int batch, int rows_per_seq, int hq, int hkv, long long max_seq,
                 int nsplit, float* scratch) {
     return attn_decode_ex(s, out, q, q_gate, k_cache, v_cache, ctx, batch, rows_per_seq, hq, hkv, max_seq, nsplit, scratch,
-                          1.0f / sqrtf(256.0f), 0);
+                          1.0f / sqrtf(256.0f), 0, 0);
 }
 
 int attn_decode_ex(cudaStream_t s, __half* out, const __half* q, const __half* q_gate, const __half* k_cache,
                    const __half* v_cache, const int* ctx, int batch, int rows_per_seq, int hq, int hkv, long long max_seq,
-                   int nsplit, float* scratch, float scale, int ctx_base) {
+                   int nsplit, float* scratch, float scale, int ctx_base, int perm_out) {
     if (hq % hkv != 0 || (hq / hkv) * rows_per_seq > kAttnRows) return -2;
     // the shared-memory attribute belongs to the device's context: set it once per device
     static bool configured_dev[64];
@@ -849,7 +866,8 @@ int attn_decode_ex(cudaStream_t s, __half* out, const __half* q, const __half* q
         default: launch_pdl(attn_split_kernel<4>, dim3(grid), dim3(kAttnThreads), sizeof(AttnSmem), s, part_o, part_ml, q, k_cache, v_cache, ctx, rows_per_seq, hq, hkv, max_seq, scale, ctx_base); break;
     }
     dim3 grid2((hq / hkv) * rows_per_seq, hkv, batch);
-    launch_pdl(attn_combine_kernel, dim3(grid2), dim3(256), 0, s, out, part_o, part_ml, q_gate, nsplit, rows_per_seq, hq, hkv);
+    launch_pdl(attn_combine_kernel, dim3(grid2), dim3(256), 0, s, out, part_o, part_ml, q_gate, nsplit, rows_per_seq, hq, hkv,
+               (q_gate && perm_out) ? 1 : 0);
     return XB_LAUNCH_OK();
 }
 
@@ -863,10 +881,10 @@ int conv1d_spec(cudaStream_t s, __half* out, const __half* in, const float* conv
 int gdn_spec(cudaStream_t s, __half* out, const __half* qkv, const __half* z, const __half* b, const __half* a,
              const float* A_log, const float* dt_bias, const float* norm_w, float* state, float* pend_k, float* pend_d,
              float* pend_g, const int* n_commit, int batch, int rows_per_seq, int prev_rows, int hv, int hk, int nc_base,
-             int early_state) {
+             int early_state, int perm_out) {
     dim3 grid(hv, batch);
     launch_pdl(gdn_spec_kernel, dim3(grid), dim3(512), 0, s, out, qkv, z, b, a, A_log, dt_bias, norm_w, state, pend_k, pend_d, pend_g,
-                                         n_commit, rows_per_seq, prev_rows, hv, hk, nc_base, early_state);
+                                         n_commit, rows_per_seq, prev_rows, hv, hk, nc_base, early_state, perm_out);
     return XB_LAUNCH_OK();
 }
 

@@ -10,11 +10,14 @@ namespace xb {
 
 int embed_rows(cudaStream_t s, __half* out, const void* table_bf16, const long long* tokens, int rows, int hidden,
                long long vocab);
+// perm_out (here and below): write the output with every block of eight features in the order the int4 unpack of
+// the W4A16 kernel yields them, (0,4,1,5,2,6,3,7): such a buffer is only good as the X of a projection launched
+// with kTcXPermuted (w4a16.h).
 int rmsnorm_rows(cudaStream_t s, __half* out, long long ld_out, const __half* in, const float* w, int rows, int hidden,
-                 float eps);
+                 float eps, int perm_out = 0);
 // x = half(x + delta) in place, out = rmsnorm(x) * w
 int add_rmsnorm_rows(cudaStream_t s, __half* out, __half* x, const __half* delta, const float* w, int rows, int hidden,
-                     float eps);
+                     float eps, int perm_out = 0);
 
 // q/k head RMSNorm + partial RoPE + KV-cache write.  Caches are [batch][max_seq][hkv][256] fp16.
 int attn_prep(cudaStream_t s, __half* q_out, __half* k_cache, __half* v_cache, const __half* q_gate, const __half* k_in,
@@ -35,7 +38,7 @@ int attn_decode(cudaStream_t s, __half* out, const __half* q, const __half* q_ga
 // with an explicit softmax scale, a host-side context length when ctx is null, and no output gate when q_gate is null
 int attn_decode_ex(cudaStream_t s, __half* out, const __half* q, const __half* q_gate, const __half* k_cache,
                    const __half* v_cache, const int* ctx, int batch, int rows_per_seq, int hq, int hkv, long long max_seq,
-                   int nsplit, float* scratch, float scale, int ctx_base);
+                   int nsplit, float* scratch, float scale, int ctx_base, int perm_out = 0);
 
 // state [batch][3][channels], pending [batch][8][channels] fp32.  The first min(n_commit[b], prev_rows) pending
 // inputs of the previous call are committed to the state before the new rows are processed (n_commit null:
@@ -49,7 +52,7 @@ int conv1d_spec(cudaStream_t s, __half* out, const __half* in, const float* conv
 int gdn_spec(cudaStream_t s, __half* out, const __half* qkv, const __half* z, const __half* b, const __half* a,
              const float* A_log, const float* dt_bias, const float* norm_w, float* state, float* pend_k, float* pend_d,
              float* pend_g, const int* n_commit, int batch, int rows_per_seq, int prev_rows, int hv, int hk, int nc_base = 0,
-             int early_state = 0);
+             int early_state = 0, int perm_out = 0);
 
 int spec_commit(cudaStream_t s, const void* accept_records, const long long* draft_tokens, int batch, int k,
                 int rows_per_seq, int* ctx, int* n_commit, long long* cur_tok, long long* emitted, int* emitted_n,

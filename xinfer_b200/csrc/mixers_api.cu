@@ -147,8 +147,11 @@ int xinfer_sdpa_causal_cached_f16(xinfer_stream_t s, void* out, const void* Q, c
 
 int xinfer_causal_conv1d_silu_f16(xinfer_stream_t s, void* out_qkv, const void* in_qkv, const float* conv_w, int64_t seq_len,
                                   float* conv_state, int64_t num_channels) {
-    if (seq_len <= 0 || num_channels <= 0) return XINFER_NOOP_INVALID_SHAPE;
-    if (!out_qkv || !in_qkv || !conv_w || num_channels > INT32_MAX) return XINFER_ERR_INVALID_ARGUMENT;
+    // the reference throws std::invalid_argument on num_channels <= 0 before it looks at anything else
+    // (src/targets/qwen3_8/linear_attn.cpp, causal_conv1d_silu; tests/test_decode_graph.cpp:27-35)
+    if (num_channels <= 0 || num_channels > INT32_MAX) return XINFER_ERR_INVALID_ARGUMENT;
+    if (seq_len <= 0) return XINFER_NOOP_INVALID_SHAPE;
+    if (!out_qkv || !in_qkv || !conv_w) return XINFER_ERR_INVALID_ARGUMENT;
     const int ch = static_cast<int>(num_channels);
     // pending inputs [8][ch], and a zero state [3][ch] for callers without one ("assumes zeros for past")
     float* scr = nullptr;
@@ -177,9 +180,12 @@ int xinfer_recurrent_gated_delta_net_f16(xinfer_stream_t s, void* out, const voi
                                          const void* a, const float* A_log, const float* dt_bias, const float* norm_weight,
                                          float* state_buffer, int64_t seq_len, int zero_state, int64_t num_v_heads,
                                          int64_t num_k_heads) {
-    if (seq_len <= 0 || num_v_heads <= 0 || num_k_heads <= 0) return XINFER_NOOP_INVALID_SHAPE;
-    if (!out || !qkv || !z || !b || !a || !A_log || !dt_bias || !norm_weight || !state_buffer || num_v_heads % num_k_heads)
-        return XINFER_ERR_INVALID_ARGUMENT;
+    if (seq_len <= 0) return XINFER_NOOP_INVALID_SHAPE;
+    // The reference refuses every shape but its compiled one (48 v heads, 16 k heads, 128 x 128 state;
+    // src/targets/qwen3_8/linear_attn.cpp:163-181, tests/test_decode_graph.cpp:37-49); the kernel here takes any
+    // head counts with v_heads a multiple of k_heads and refuses the rest the same way.
+    if (num_v_heads <= 0 || num_k_heads <= 0 || num_v_heads % num_k_heads) return XINFER_ERR_INVALID_ARGUMENT;
+    if (!out || !qkv || !z || !b || !a || !A_log || !dt_bias || !norm_weight || !state_buffer) return XINFER_ERR_INVALID_ARGUMENT;
     const int hv = static_cast<int>(num_v_heads), hk = static_cast<int>(num_k_heads);
     const size_t pk = static_cast<size_t>(hv) * 8 * 128;
     float* scr = nullptr;

@@ -389,16 +389,26 @@ xb::TcProj make_proj_local(const Linear& l, void* y) {
 
 // Launches `num` projections sharing X (or a gate/up pair) on the tensor-core kernel; with other ranks around
 // the launch ends with the exchange handshake, so when it completes every rank's slice has arrived here.
+// Every activation buffer that feeds a projection (normed, cat, attn_out, delta_out, mlp) is written by its producer
+// with each block of eight features in the order the int4 unpack yields them, so the projection kernel does not
+// rewrite its staged activation tiles: all launches below pass kTcXPermuted, and the gate/up launch, whose output
+// is the down projection's input, also kTcYPermuted.  Set XINFER_XPERM=0 to run everything in natural order.
+bool xperm_on() {
+    static const bool on = [] { const char* e = getenv("XINFER_XPERM"); return !(e && atoi(e) == 0); }();
+    return on;
+}
+
 int run_lin(Dec* d, cudaStream_t s, const void* x, xb::TcProj* pr, int num, bool swiglu, bool out_f32, int M, int64_t K,
             int rows_per_rank, bool exchange) {
     ++d->launches_per_step;
     ++d->linear_launches;
+    const int flags = xperm_on() ? (xb::kTcXPermuted | (swiglu ? xb::kTcYPermuted : 0)) : 0;
     if (d->world > 1 && exchange) {
         ++d->exchanges_per_step;
         const xb::TpLink link = xb::tp_link(d->tp, rows_per_rank);
-        return xb::run_tc_linear(s, x, pr, num, swiglu, out_f32, M, K, 128, &link);
+        return xb::run_tc_linear(s, x, pr, num, swiglu, out_f32, M, K, 128, &link, flags);
     }
-    return xb::run_tc_linear(s, x, pr, num, swiglu, out_f32, M, K, 128, nullptr);
+    return xb::run_tc_linear(s, x, pr, num, swiglu, out_f32, M, K, 128, nullptr, flags);
 }
 
 int lin(Dec* d, cudaStream_t s, const XBuf& y, const __half* x, const Linear& l, int M, int push) {
@@ -424,7 +434,7 @@ int lin_add_norm(Dec* d, cudaStream_t s, const XBuf& y, const __half* x_in, cons
                  const float* w) {
     const auto& c = d->cfg;
     CK(lin(d, s, y, x_in, l, M, kAll));
-    NL(xb::add_rmsnorm_rows(s, d->normed, xr, y.p, w, M, static_cast<int>(l.n_full), c.rms_norm_eps));
+    NL(xb::add_rmsnorm_rows(s, d->normed, xr, y.p, w, M, static_cast<int>(l.n_full), c.rms_norm_eps, xperm_on()));
     ++d->launches_per_step;
     return 0;
 }
@@ -451,9 +461,10 @@ int layer_forward(Dec* d, cudaStream_t s, Layer& L, int R, __half* xr, const flo
                          d->q_gate.p + static_cast<size_t>(row0) * hq * 512, d->kbuf.p + static_cast<size_t>(row0) * hkv * 256,
                          d->vbuf.p + static_cast<size_t>(row0) * hkv * 256, L.q_norm, L.k_norm, ctx + d->b0, Bl, R, hq, hkv,
                          d->max_seq, c.rms_norm_eps, c.rope_theta, c.rope_dim));
-        NL(xb::attn_decode(s, d->attn_out.p + static_cast<size_t>(row0) * hq * 256, d->qbuf + static_cast<size_t>(row0) * hq * 256,
-                           d->q_gate.p + static_cast<size_t>(row0) * hq * 512, L.k_cache, L.v_cache, ctx + d->b0, Bl, R, hq,
-                           hkv, d->max_seq, d->attn_splits, d->attn_scratch));
+        NL(xb::attn_decode_ex(s, d->attn_out.p + static_cast<size_t>(row0) * hq * 256,
+                              d->qbuf + static_cast<size_t>(row0) * hq * 256, d->q_gate.p + static_cast<size_t>(row0) * hq * 512,
+                              L.k_cache, L.v_cache, ctx + d->b0, Bl, R, hq, hkv, d->max_seq, d->attn_splits, d->attn_scratch,
+                              1.0f / sqrtf(256.0f), 0, xperm_on()));
         d->launches_per_step += 3;
         CK(gather_rows(d, s, d->attn_out, row0, Ml, static_cast<int64_t>(hq) * 256));
         // x += mixer output, post-attention RMSNorm
@@ -473,7 +484,7 @@ int layer_forward(Dec* d, cudaStream_t s, Layer& L, int R, __half* xr, const flo
         NL(xb::gdn_spec(s, d->delta_out.p + static_cast<size_t>(row0) * hv * 128, d->qkv_conv + static_cast<size_t>(row0) * ch,
                         d->zbuf.p + static_cast<size_t>(row0) * hv * 128, d->bbuf + static_cast<size_t>(row0) * hv,
                         d->abuf + static_cast<size_t>(row0) * hv, L.A_log, L.dt_bias, L.gdn_norm, L.S, L.pend_k, L.pend_d,
-                        L.pend_g, n_commit + d->b0, Bl, R, prev_rows, hv, hk, 0, 1));
+                        L.pend_g, n_commit + d->b0, Bl, R, prev_rows, hv, hk, 0, 1, xperm_on()));
         d->launches_per_step += 2;
         CK(gather_rows(d, s, d->delta_out, row0, Ml, static_cast<int64_t>(hv) * 128));
         CK(lin_add_norm(d, s, d->proj_out, d->delta_out.p, L.out_proj, M, xr, L.post_norm));
@@ -523,8 +534,8 @@ int draft_pass(Dec* d, cudaStream_t s, int i, bool full) {
     const __half* hprev = (i == 0) ? d->h_last : d->mtp_hidden;
     // cat = [rmsnorm(embed(tok)) ; rmsnorm(h_prev)]  ->  fc  ->  x
     NL(xb::embed_rows(s, d->emb, d->embed, tok, B, H, c.vocab_size));
-    NL(xb::rmsnorm_rows(s, d->cat, 2 * H, d->emb, d->mtp_enorm, B, H, c.rms_norm_eps));
-    NL(xb::rmsnorm_rows(s, d->cat + H, 2 * H, hprev, d->mtp_hnorm, B, H, c.rms_norm_eps));
+    NL(xb::rmsnorm_rows(s, d->cat, 2 * H, d->emb, d->mtp_enorm, B, H, c.rms_norm_eps, xperm_on()));
+    NL(xb::rmsnorm_rows(s, d->cat + H, 2 * H, hprev, d->mtp_hnorm, B, H, c.rms_norm_eps, xperm_on()));
     CK(lin(d, s, d->x_mtp, d->cat, d->mtp_fc, B, kAll));
     if (!d->linears_only) add_int_kernel<<<1, 64, 0, s>>>(d->ctx_draft, d->ctx, B, i);
     d->launches_per_step += 4;
@@ -533,7 +544,7 @@ int draft_pass(Dec* d, cudaStream_t s, int i, bool full) {
         Layer& L = d->mtp_layer;
         const int hq = static_cast<int>(c.num_attention_heads), hkv = static_cast<int>(c.num_key_value_heads);
         const int Bl = d->bl, row0 = d->b0;
-        NL(xb::rmsnorm_rows(s, d->normed, H, d->x_mtp.p, L.input_norm, B, H, c.rms_norm_eps));
+        NL(xb::rmsnorm_rows(s, d->normed, H, d->x_mtp.p, L.input_norm, B, H, c.rms_norm_eps, xperm_on()));
         // (the query projection is not needed: the prologue kernel is told there are no query heads)
         xb::TcProj fd[2] = {make_proj(d, L.k_proj, d->kbuf, kOwner), make_proj(d, L.v_proj, d->vbuf, kOwner)};
         account(d, L.k_proj, B, 2, true);
@@ -546,7 +557,7 @@ int draft_pass(Dec* d, cudaStream_t s, int i, bool full) {
         d->launches_per_step += 2;
         return 0;
     }
-    NL(xb::rmsnorm_rows(s, d->normed, H, d->x_mtp.p, d->mtp_layer.input_norm, B, H, c.rms_norm_eps));
+    NL(xb::rmsnorm_rows(s, d->normed, H, d->x_mtp.p, d->mtp_layer.input_norm, B, H, c.rms_norm_eps, xperm_on()));
     ++d->launches_per_step;
     CK(layer_forward(d, s, d->mtp_layer, 1, d->x_mtp.p, d->final_norm, d->ctx_draft, d->n_commit_zero, 0));
     // keep the head's output hidden (pre final norm) for the next draft pass
@@ -564,7 +575,7 @@ int target_pass(Dec* d, cudaStream_t s, int R, const long long* tokens) {
     const auto& c = d->cfg;
     const int M = d->batch * R, H = static_cast<int>(c.hidden_size);
     NL(xb::embed_rows(s, d->x, d->embed, tokens, M, H, c.vocab_size));
-    NL(xb::rmsnorm_rows(s, d->normed, H, d->x, d->layers[0].input_norm, M, H, c.rms_norm_eps));
+    NL(xb::rmsnorm_rows(s, d->normed, H, d->x, d->layers[0].input_norm, M, H, c.rms_norm_eps, xperm_on()));
     d->launches_per_step += 2;
     const size_t nl = d->layers.size();
     for (size_t l = 0; l < nl; ++l)

@@ -39,6 +39,6 @@ inline void tp_fill_proj(const TpComm* c, TcProj* p, size_t off, int push) {
 // tcgen05 linear on the current device's scratch with an optional exchange; no CUDA-core fallback: returns
 // XINFER_ERR_INVALID_ARGUMENT for shapes the tensor-core kernel does not take (c_api.cu).
 int run_tc_linear(cudaStream_t s, const void* x, const TcProj* proj, int num, bool swiglu, bool out_f32, long long m,
-                  long long k, int group_size, const TpLink* tp);
+                  long long k, int group_size, const TpLink* tp, int layout_flags = 0);
 
 }  // namespace xb

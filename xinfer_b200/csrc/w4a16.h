@@ -54,7 +54,13 @@ void tc_plan_clear();
 // for theirs before the kernel completes.
 int tc_launch(cudaStream_t stream, const void* x, const TcProj* proj, int num, bool swiglu, bool out_f32,
               long long m, long long k, int num_sms, float* workspace, int* counters, int counter_capacity,
-              int* status, const TpLink* tp = nullptr);
+              int* status, const TpLink* tp = nullptr, int layout_flags = 0);
+// layout_flags.  The int4 unpack yields the k of each block of eight in the order (0,4,1,5,2,6,3,7); the kernel
+// normally rewrites every staged activation tile into that order itself.  A caller that owns the producer of X can
+// have it written in that order once (kTcXPermuted) and skip the rewrite; kTcYPermuted makes this launch such a
+// producer: its output columns are written in that order.  Permuted buffers are private to such a chain.
+constexpr int kTcXPermuted = 1;
+constexpr int kTcYPermuted = 2;
 
 // ---- CUDA-core path (w4a16_simt.cu): any m, fp16 or fp32 activations, any shape the reference accepts
 enum class ActType { F16, F32 };

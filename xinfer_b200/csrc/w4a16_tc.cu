@@ -125,6 +125,8 @@ struct Params {
     long long wait_limit;  // SM clocks after which a device-side wait gives up
     int x_stage_limit;     // test hook: activation stages beyond this index are never requested (-1: off)
     TpLink tp;             // N-split exchange (world <= 1: none)
+    int x_perm;            // X is stored in the unpack's k order already: no in-kernel reorder of the staged activations
+    int y_perm;            // write Y with its columns in that order (it is the X of another such launch)
     // Optional: the first weight stages of the NEXT tensor-core launch in the stream, pulled into L2 while this
     // launch drains, so that launch's pipeline fills from L2 instead of HBM.  pf_ctas = 0: nothing to prefetch.
     CUtensorMap pf_map[kMaxSegs];
@@ -194,6 +196,13 @@ __device__ __forceinline__ TileInfo locate_tile(const Params& p, int tile) {
 
 // Stores output element (activation row j, element offset `off` from the projection's y) where it belongs:
 // locally, or - N-split tensor parallelism - with plain peer stores into the other ranks' buffers as well.
+// Position of output feature n inside its block of eight when Y is written in the unpack's k order
+// (0,4,1,5,2,6,3,7): feature k < 4 of a block goes to 2k, feature k >= 4 to 2(k - 4) + 1.
+__device__ __forceinline__ int perm8(int n) {
+    const int k = n & 7;
+    return (n & ~7) | ((k < 4) ? 2 * k : 2 * (k - 4) + 1);
+}
+
 template <typename OutT>
 __device__ __forceinline__ void store_row(const Params& p, const Seg& sg, long long off, int j, float v) {
     if (sg.push == 0) {
@@ -407,7 +416,8 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
             constexpr uint32_t desc_lo_const = 1u << 16;  // leading-dimension offset: unused for swizzled K-major
             // (in a cluster launch a shared-window address carries the CTA's rank in its upper bits: keep 14 bits)
             const uint32_t xring_lo = (smem_u32(xring) >> 4) & 0x3FFFu;
-            const uint32_t xready0 = smem_u32(&ctrl->x_ready[0]);
+            // pre-permuted activations are usable as they land (x_full); otherwise once the reorder warp is done (x_ready)
+            const uint32_t xready0 = p.x_perm ? smem_u32(&ctrl->x_full[0]) : smem_u32(&ctrl->x_ready[0]);
             const uint32_t xempty0 = smem_u32(&ctrl->x_empty[0]);
             const uint32_t afull0 = smem_u32(&ctrl->a_full[w][0]);
             const uint32_t dfull0 = smem_u32(&ctrl->d_full[w][0]);
@@ -450,7 +460,8 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
         const uint32_t xready0 = smem_u32(&ctrl->x_ready[0]);
         const uint32_t total_mine = static_cast<uint32_t>(u_end - u_begin);
         constexpr int kChunksPerLane = C::kXStageBytes / 16 / 32;
-        for (uint32_t n = 0; n < total_mine; ++n) {
+        // (nothing to do when the caller's X is in that order already)
+        for (uint32_t n = 0; n < (p.x_perm ? 0u : total_mine); ++n) {
             const uint32_t xslot = n % C::kXStages;
             if (!mbar_wait_parked(xfull0 + xslot * 8, (n / C::kXStages) & 1u, abort_flag)) break;
             const uint32_t base = xring_base + xslot * C::kXStageBytes + lane * 16;
@@ -547,6 +558,7 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
             const Seg& sg = p.seg[p.swiglu ? wg : ti.seg];
             const int my_row = p.swiglu ? ti.row0 + t : ti.row0 + rt;
             const bool valid = my_row < sg.n;
+            const int my_col = p.y_perm ? perm8(my_row) : my_row;  // where this feature's outputs go within a Y row
             const __half* my_scales = sg.scales + static_cast<long long>(valid ? my_row : 0) * p.groups;
             const int gmax = valid ? p.groups : 0;  // scale index limit; rows beyond N use scale 0
             // A row's scales are 2 bytes per 128 k, far apart from its neighbours': behind a saturated weight
@@ -699,7 +711,7 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
                     uint32_t jlast = jfirst + rows_cap;
                     jlast = jlast > static_cast<uint32_t>(m_rows) ? static_cast<uint32_t>(m_rows) : jlast;
                     uint32_t j = jfirst + gi;
-                    long long yoff = my_row + static_cast<long long>(j) * ldy;
+                    long long yoff = my_col + static_cast<long long>(j) * ldy;
                     uint32_t pa = smem_u32(part) + (gi * kTileRows + rt) * 4;
                     const uint32_t rstep = rows_cap * (kTileRows * 4);
                     float* sa = stage_acc + j * kTileRows + rt;
@@ -767,7 +779,7 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
                         for (int j = j0; j < jend; j += jstep) {
                             const float g = stage_acc[j * kTileRows + t];
                             const float up = stage_acc[j * kTileRows + kHalfRows + t];
-                            store_row<OutT>(p, p.seg[0], my_row + static_cast<long long>(j) * ldy, j,
+                            store_row<OutT>(p, p.seg[0], my_col + static_cast<long long>(j) * ldy, j,
                                             (g / (1.0f + expf(-g))) * up);
                         }
                     }
@@ -776,7 +788,7 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
                     const float b = sg.bias ? sg.bias[my_row] : 0.f;
 #pragma unroll 4
                     for (int j = j0; j < jend; j += jstep)
-                        store_row<OutT>(p, sg, my_row + static_cast<long long>(j) * ldy, j, stage_acc[j * kTileRows + rt] + b);
+                        store_row<OutT>(p, sg, my_col + static_cast<long long>(j) * ldy, j, stage_acc[j * kTileRows + rt] + b);
                 }
             }
             u += (s1 - s0);
@@ -1090,7 +1102,7 @@ bool tc_eligible(const void* x, const TcProj* proj, int num, bool swiglu, long l
 // problem cannot be described to the kernel (the caller then uses the CUDA-core path).
 int tc_launch(cudaStream_t stream, const void* x, const TcProj* proj, int num, bool swiglu, bool out_f32,
               long long m, long long k, int num_sms, float* workspace, int* counters, int counter_capacity,
-              int* status, const TpLink* tp) {
+              int* status, const TpLink* tp, int layout_flags) {
     Params p;
     memset(&p, 0, sizeof(p));
     const int nmma = (m <= 16) ? 16 : 32;
@@ -1126,6 +1138,11 @@ int tc_launch(cudaStream_t stream, const void* x, const TcProj* proj, int num, b
     p.counters = counters;
     p.status = status;
     p.wait_limit = g_wait_limit;
+    p.x_perm = (layout_flags & kTcXPermuted) ? 1 : 0;
+    p.y_perm = (layout_flags & kTcYPermuted) ? 1 : 0;
+    if (p.y_perm)
+        for (int i = 0; i < (swiglu ? 1 : num); ++i)
+            if (proj[i].n & 7) return -2;  // whole blocks of eight features only
     if (tp && tp->world > 1) {
         if (tp->world > kTpMaxWorld || tp->rows_per_rank < 1 || num_sms > kTpMaxCtas) return -2;
         p.tp = *tp;
