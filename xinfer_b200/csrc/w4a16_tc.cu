@@ -228,7 +228,10 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
     float* xchg = reinterpret_cast<float*>(xchg_raw);
 
     const int tid = threadIdx.x;
-    const int warp = tid >> 5;
+    // (the broadcast tells the compiler that the warp index, and every role, row block, tensor-memory address and
+    // barrier address derived from it, is the same in all lanes: they then live in uniform registers instead of
+    // being moved there before each tcgen05 or barrier instruction)
+    const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);
     const int lane = tid & 31;
     volatile WaitState* abort_flag = &ctrl->ws;  // shared by every bounded wait of the CTA
     griddep_launch_dependents();
