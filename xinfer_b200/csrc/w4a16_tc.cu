@@ -125,6 +125,7 @@ struct Params {
     long long wait_limit;  // SM clocks after which a device-side wait gives up
     int x_stage_limit;     // test hook: activation stages beyond this index are never requested (-1: off)
     TpLink tp;             // N-split exchange (world <= 1: none)
+    int xchg_direct;       // cluster split-K partials go by plain remote stores (1) or by bulk copies (0)
     int x_perm;            // X is stored in the unpack's k order already: no in-kernel reorder of the staged activations
     int y_perm;            // write Y with its columns in that order (it is the X of another such launch)
     // Optional: the first weight stages of the NEXT tensor-core launch in the stream, pulled into L2 while this
@@ -662,6 +663,10 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
             // unrolled epilogue cost ~10 us in instruction fetches alone).  The two threads of a row first
             // add their groups' partial sums there; afterwards they split the activation rows by parity.
             float* stage_acc = xchg;  // [NREAD][256] fp32, row rt's values at [j][rt]
+            const int m_rows = p.m < NREAD ? p.m : NREAD;
+            const bool whole = (s0 == 0 && s1 == S);
+            const bool direct_xchg = !whole && p.cluster > 1 && p.xchg_direct;
+            if (!direct_xchg) {
             if (!consumer_sync()) break;  // previous tile's readers of stage_acc are done
             if (gi == 0) {
 #pragma unroll
@@ -674,11 +679,69 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_tc_kernel(const __grid_cons
             }
             fence_proxy_async_smem();  // the copy engine may read the parked rows (split-K exchange)
             if (!consumer_sync()) break;
-            const int m_rows = p.m < NREAD ? p.m : NREAD;
-            const bool whole = (s0 == 0 && s1 == S);
+            }
             bool finish = whole;
             int j0 = gi, jstep = 2, jend = m_rows;  // activation rows this thread finishes: j0, j0 + jstep, ... < jend
-            if (!whole && p.cluster > 1) {
+            if (direct_xchg) {
+                // K splits of one tile form a thread-block cluster.  CTA r of the cluster finishes a contiguous block
+                // of activation rows (ceil(m / cluster) of them).  Every thread stores its fp32 partials straight from
+                // its registers into the owner's shared memory (the weight ring, free once every CTA has arrived at
+                // barrier A): [sender][group][row of the block][256 features].  One cluster barrier later the owner
+                // adds the two groups of every sender and then the senders in rank order (deterministic).
+                float* part = reinterpret_cast<float*>(smem);
+                const uint32_t my_rank = cluster_ctarank();
+                const uint32_t csz = static_cast<uint32_t>(p.cluster);
+                const uint32_t rows_cap = (static_cast<uint32_t>(m_rows) + csz - 1) / csz;
+                if (cl_steps == 0) { cluster_arrive(); cl_steps = 1; }
+                cluster_wait();  // (A) every CTA of the cluster has finished reading its weight ring
+                cl_steps = 2;
+                {
+                    const uint32_t local = smem_u32(part) + (((my_rank * 2 + gi) * rows_cap) * kTileRows + rt) * 4;
+                    uint32_t owner = 0, jl = 0;
+                    uint32_t dst = mapa_shared_cluster(local, 0);
+#pragma unroll
+                    for (int j = 0; j < NREAD; ++j) {
+                        if (j < m_rows) {
+                            st_shared_cluster_f32(dst, acc[j]);
+                            dst += kTileRows * 4;
+                            if (++jl == rows_cap) {
+                                jl = 0;
+                                ++owner;
+                                dst = mapa_shared_cluster(local, owner < csz ? owner : 0);
+                            }
+                        }
+                    }
+                }
+                cluster_arrive();  // (B) releases this thread's stores ...
+                cl_steps = 3;
+                cluster_wait();    // ... and acquires everyone's: this CTA's block is complete
+                cl_steps = 4;
+                {
+                    const bool direct = !p.swiglu && valid;
+                    const long long ldy = sg.ldy;
+                    const float bias = (direct && sg.bias) ? sg.bias[my_row] : 0.f;
+                    const uint32_t jfirst = my_rank * rows_cap;
+                    uint32_t jlast = jfirst + rows_cap;
+                    jlast = jlast > static_cast<uint32_t>(m_rows) ? static_cast<uint32_t>(m_rows) : jlast;
+                    uint32_t j = jfirst + gi;
+                    long long yoff = my_col + static_cast<long long>(j) * ldy;
+                    uint32_t pa = smem_u32(part) + (gi * kTileRows + rt) * 4;  // row gi of the block, sender 0, group 0
+                    const uint32_t gstep = rows_cap * (kTileRows * 4);           // group 0 -> group 1 of one sender
+                    float* sa = stage_acc + j * kTileRows + rt;
+#pragma unroll 1
+                    for (; j < jlast; j += 2, pa += 2 * kTileRows * 4, yoff += 2 * ldy, sa += 2 * kTileRows) {
+                        float sum = 0.f;
+                        uint32_t a = pa;
+#pragma unroll 2
+                        for (uint32_t r = 0; r < csz; ++r, a += 2 * gstep) sum += lds_f32(a) + lds_f32(a + gstep);
+                        if (direct) store_row<OutT>(p, sg, yoff, static_cast<int>(j), sum + bias);
+                        else *sa = sum;
+                    }
+                    j0 = static_cast<int>(jfirst) + gi;
+                    jend = static_cast<int>(jlast);
+                    finish = p.swiglu != 0;  // plain projections are already written
+                }
+            } else if (!whole && p.cluster > 1) {
                 // K splits of one tile form a thread-block cluster.  CTA r of the cluster finishes a contiguous
                 // block of activation rows (ceil(m / cluster) of them): every CTA sends its fp32 partials of
                 // that block, contiguous in the parked accumulators, into r's shared memory with ONE bulk copy
@@ -1153,6 +1216,9 @@ int tc_launch(cudaStream_t stream, const void* x, const TcProj* proj, int num, b
         if (p.tp.wait_limit <= 0) p.tp.wait_limit = g_wait_limit;
     }
     p.x_stage_limit = g_x_stage_limit;
+    // few activation rows: the partials go by plain remote stores (less latency than parking them and starting a
+    // bulk copy per peer); more rows: the copy engine moves them (fewer instructions per CTA)
+    p.xchg_direct = m <= 8 ? 1 : 0;
     TcPlan& pl = cur_plan();
     if (pl.recording) {
         pl.entries.push_back(make_entry(proj, num, swiglu, out_f32, m, k));
