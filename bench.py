@@ -88,26 +88,42 @@ class ClockSampler:
     def __init__(self, gpu_index):
         self.gpu_index = gpu_index
         self.proc = None
+        self.lines = []
+        self.reader = None
 
     def start(self):
+        import threading
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
                  "-i", str(self.gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
+            return
+
+        def pump():
+            for line in self.proc.stdout:
+                self.lines.append(line)
+        self.reader = threading.Thread(target=pump, daemon=True)
+        self.reader.start()
+
+    def samples(self):
+        """Samples received so far (nvidia-smi takes a few hundred ms to deliver its first one on a box with many
+        GPUs: a caller whose timed region is shorter keeps the same load running until one has arrived)."""
+        return len(self.lines)
 
     def stop(self):
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
         try:
-            out, _ = self.proc.communicate(timeout=5)
+            self.proc.wait(timeout=5)
         except subprocess.TimeoutExpired:
             self.proc.kill()
-            out, _ = self.proc.communicate()
+        if self.reader is not None:
+            self.reader.join(timeout=2)
         sm, mx, reasons = [], [], set()
-        for line in out.strip().splitlines():
+        for line in list(self.lines):
             f = [x.strip() for x in line.split(",")]
             if len(f) < 9:
                 continue
@@ -649,8 +665,24 @@ def step_bench(args):
             dec.step()
         ev1.record(stream)
         torch.cuda.synchronize()
-        clocks = sampler.stop()
         ms = ev0.elapsed_time(ev1)
+        # the clock record must hold at least one sample taken under this load: keep the same steps running
+        # (untimed) until nvidia-smi has delivered one
+        extra = 0
+        while extra < 400:
+            more = 1 if (sampler.samples() == 0 and sampler.proc is not None) else 0
+            if world > 1:  # every rank runs the same number of steps (the N-split step needs all of them): rank 0 decides
+                flag = torch.tensor([more], device="cuda", dtype=torch.int32)
+                dist.broadcast(flag, src=0)
+                more = int(flag.item())
+            if not more:
+                break
+            dec.step()
+            stream.synchronize()
+            extra += 1
+        clocks = sampler.stop()
+        if extra:
+            clocks["note"] = f"first sample arrived during {extra} untimed steps of the same load right after the timed region"
         tokens = int(dec.tensor(-1, "ctx", np.int32).astype(np.int64).sum() - ctx_before)
         launches = dec.info(2)
 

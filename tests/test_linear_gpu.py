@@ -227,7 +227,7 @@ def test_invalid_shapes_are_noops(cuda):
 def test_large_m_and_other_group_size_use_cuda_cores(cuda):
     X, W, S, _ = synth_linear(40, 512, 96, seed=4)
     ref = oracle.linear_int4_f64(X.astype(np.float32), W, S)
-    got, used = run_linear(cuda, X, W, S)
+    got, used = run_linear(cuda, X, W, S, path=SIMT)
     assert used == SIMT and rel_err(got, ref) <= 2e-5
     # group size 64: only the naive path of the reference honours it (src/ops/linear.cpp:703-722)
     rng = np.random.default_rng(6)
@@ -237,6 +237,81 @@ def test_large_m_and_other_group_size_use_cuda_cores(cuda):
     assert cuda.linear_int4(Y, dev(X), dev(W), dev(S64), None, 40, 96, 512, 64) == 0
     torch.cuda.synchronize()
     assert rel_err(Y.cpu().numpy(), ref64) <= 2e-5
+
+
+# ------------------------------------------------------------------ prefill chunks: the tcgen05 GEMM (M > 32)
+GEMM = 3
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("M,K,N", [(33, 128, 16), (64, 512, 96), (256, 1024, 1000), (300, 5120, 1024), (512, 5120, 6144),
+                                   (512, 17408, 5120), (513, 256, 300)])
+def test_prefill_gemm_against_oracle(cuda, M, K, N):
+    """More than 32 rows go to the tensor-core GEMM (scale * weight enters the MMA as an exact hi + lo pair of fp16
+    operands; sums in fp32 over all of K): same bound as the decode kernels."""
+    X, W, S, _ = synth_linear(M, K, N, seed=M + N)
+    bias = np.random.default_rng(1).normal(0, 0.1, size=N).astype(np.float32)
+    ref = oracle.linear_int4_f64(X.astype(np.float32), W, S, bias)
+    got, used = run_linear(cuda, X, W, S, bias=bias)
+    assert used == GEMM
+    # (one tensor-core accumulation over all of K instead of one per 128-k group; its fp32 adds truncate, so the
+    # error grows with K: 3.7e-5 measured at K = 5120, 1.3e-4 at K = 17408; the stated bound is 1e-3 relative)
+    assert rel_err(got, ref) <= 3e-4
+    got16, used = run_linear(cuda, X, W, S, bias=bias, out_dtype=torch.float16)
+    assert used == GEMM
+    assert rel_err(got16, ref) <= 1.5e-3  # the fp16 rounding of the output
+    # the CUDA-core path of the same call agrees
+    simt, used = run_linear(cuda, X, W, S, bias=bias, path=SIMT)
+    assert used == SIMT and rel_err(got, simt) <= 3e-4
+
+
+@pytest.mark.gpu
+def test_prefill_gemm_unpack_bit_exact_via_one_hot(cuda):
+    """One-hot activations with unit scales read the unpacked weights out exactly (every nibble position, both
+    128-row halves, a ragged last tile)."""
+    K, N, M = 256, 300, 256
+    rng = np.random.default_rng(3)
+    q = rng.integers(-8, 8, size=(N, K), dtype=np.int8)
+    W = ((q[:, 0::2] & 0xF) | ((q[:, 1::2] & 0xF) << 4)).astype(np.uint8)
+    S = np.ones((N, K // 128), np.float16)
+    X = np.zeros((M, K), np.float16)
+    X[np.arange(M), np.arange(M) % K] = 1.0
+    got, used = run_linear(cuda, X, W, S)
+    assert used == GEMM
+    assert np.array_equal(got, q[:, np.arange(M) % K].T.astype(np.float32))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("M", [64, 512])
+def test_prefill_swiglu_and_fused_projections(cuda, M):
+    K, N = 1024, 1280
+    rng = np.random.default_rng(M)
+    X = rng.normal(0, 1, size=(M, K)).astype(np.float16)
+    _, Wg, Sg, _ = synth_linear(1, K, N, seed=1)
+    _, Wu, Su, _ = synth_linear(1, K, N, seed=2)
+    g = oracle.linear_int4_f64(X.astype(np.float32), Wg, Sg)
+    u = oracle.linear_int4_f64(X.astype(np.float32), Wu, Su)
+    ref = g / (1.0 + np.exp(-g)) * u
+    Y = torch.empty((M, N), dtype=torch.float16, device="cuda")
+    assert cuda.mlp_gate_up_swiglu_int4(Y, dev(X), dev(Wg), dev(Sg), dev(Wu), dev(Su), M, N, K) == 0
+    torch.cuda.synchronize()
+    assert cuda.last_linear_path() == GEMM and cuda.device_status(0) == 0
+    assert rel_err(Y.float().cpu().numpy(), ref) <= 3e-3
+    # fused descriptors: one launch per projection behind the same call
+    Ns = [640, 130, 48]
+    Ws, Ss, Ys = [], [], []
+    for i, n in enumerate(Ns):
+        _, w, sc, _ = synth_linear(1, K, n, seed=10 + i)
+        Ws.append(w)
+        Ss.append(sc)
+        Ys.append(torch.empty((M, n), dtype=torch.float16, device="cuda"))
+    descs = [{"Y": Ys[i], "W_int4": dev(Ws[i]), "scales": dev(Ss[i]), "bias": None, "N": Ns[i]} for i in range(3)]
+    assert cuda.linear_int4_fused(dev(X), descs, M, K) == 0
+    torch.cuda.synchronize()
+    assert cuda.last_linear_path() == GEMM and cuda.device_status(0) == 0
+    for i in range(3):
+        ref = oracle.linear_int4_f64(X.astype(np.float32), Ws[i], Ss[i])
+        assert rel_err(Ys[i].float().cpu().numpy(), ref) <= 2e-3
 
 
 # ------------------------------------------------------------------ fused launches at layer shapes

@@ -83,6 +83,12 @@ int run_linear(xinfer_stream_t s, const void* x, xb::ActType in, bool out_f32, c
     int rc = get_ctx(&c);
     if (rc != XINFER_OK) return rc;
     cudaStream_t stream = static_cast<cudaStream_t>(s);
+    if (c->forced_path != 2 && in == xb::ActType::F16 && xb::gemm_eligible(x, proj, num, swiglu, m, k, group_size)) {
+        // more than 32 rows (prefill chunks): the compute-bound tcgen05 GEMM
+        const int r = xb::gemm_launch(stream, x, proj, num, swiglu, out_f32, m, k, c->status, xb::tc_wait_limit());
+        if (r == 0) { g_last_path = 3; return XINFER_OK; }
+        if (r == -1) return fail_cuda(cudaGetLastError());
+    }
     const bool want_tc = (c->forced_path != 2) && in == xb::ActType::F16 &&
                          xb::tc_eligible(x, proj, num, swiglu, m, k, group_size);
     if (want_tc) {

@@ -39,6 +39,9 @@ struct TpLink {
 __device__ __forceinline__ void st_release_sys_u64(unsigned long long* p, unsigned long long v) {
     asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
+__device__ __forceinline__ void st_relaxed_sys_u64(unsigned long long* p, unsigned long long v) {
+    asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
 __device__ __forceinline__ unsigned long long ld_acquire_sys_u64(const unsigned long long* p) {
     unsigned long long v;
     asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
@@ -59,9 +62,13 @@ __device__ __forceinline__ void tp_finish_exchange(const TpLink& tp, unsigned in
     const unsigned int lane = threadIdx.x & 31u;
     const unsigned long long e = *tp.epoch + 1;  // written by CTA 0 of the previous exchange, long complete
     if (lane == 0) {
+        // One release fence at system scope (the CTA's data stores, ordered before this point by the CTA barrier, are
+        // performed before any flag below becomes visible), then one plain store per rank: the flag writes leave
+        // together instead of each waiting for the one before it.
         // (this rank's own matrix included: CTA 0 must not advance the count while a CTA of its own grid has yet to
         // read it)
-        for (int r = 0; r < tp.world; ++r) st_release_sys_u64(tp.flags_peer[r] + tp.rank * kTpMaxCtas + cta, e);
+        asm volatile("fence.acq_rel.sys;" ::: "memory");
+        for (int r = 0; r < tp.world; ++r) st_relaxed_sys_u64(tp.flags_peer[r] + tp.rank * kTpMaxCtas + cta, e);
     }
     if (cta != 0) return;
     const long long t0 = clock64();

@@ -1042,6 +1042,7 @@ bool pdl_enabled() {
 // Test hooks: the clock limit of the device-side waits, and an activation stage index from which on the
 // producer requests nothing (the kernel then leaves through its abort path).  Defaults: one second, off.
 static long long g_wait_limit = kWaitLimitClocks;
+long long tc_wait_limit() { return g_wait_limit; }
 static int g_x_stage_limit = -1;
 void tc_set_wait_hooks(long long limit_clocks, int withhold_x_from_stage) {
     g_wait_limit = limit_clocks > 0 ? limit_clocks : kWaitLimitClocks;
