@@ -302,6 +302,134 @@ def gemv_bench(args):
         dist.destroy_process_group()
 
 
+def prefill_bench(args):
+    """One prefill chunk (M = --rows, default 512) through the linears of one Gated-DeltaNet layer and one attention
+    layer of the 27B shape, i.e. the `M > 32` side of the same entry points: useful TFLOP/s (2*M*N*K per projection)
+    against the measured dense bf16 peak.  The kernel feeds scale * weight to the MMA as an exact hi + lo pair, so
+    the tensor pipe does twice the useful work; `roofline.frac` counts useful flops only."""
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    import xinfer_b200.ops as ops
+    from xinfer_b200 import lib
+    assert lib().xinfer_b200_init(local_rank) == 0, lib().xinfer_last_cuda_error()
+    M = args.m if args.m > 32 else 512
+    H, F = 5120, 17408
+    rng = np.random.default_rng(0)
+
+    def weights(K, N):
+        W = rng.integers(0, 256, size=(N, K // 2), dtype=np.uint8)
+        S = (np.abs(rng.normal(0, 0.02, size=(N, K // 128))) / 7).astype(np.float16)
+        return torch.from_numpy(W).cuda(), torch.from_numpy(S).cuda()
+
+    X = torch.randn((M, H), device="cuda").half()
+    Xo = torch.randn((M, 6144), device="cuda").half()
+    Xf = torch.randn((M, F), device="cuda").half()
+    projs = {n: weights(H, n) for n in (10240, 6144, 48, 12288, 1024)}
+    w48b, w1024b = weights(H, 48), weights(H, 1024)
+    w_out, w_o = weights(6144, H), weights(6144, H)
+    w_gate, w_up, w_down = weights(H, F), weights(H, F), weights(F, H)
+    outs = {n: torch.empty((M, n), dtype=torch.float16, device="cuda") for n in (10240, 6144, 48, 12288, 1024, H, F)}
+    o48b = torch.empty((M, 48), dtype=torch.float16, device="cuda")
+    o1024b = torch.empty((M, 1024), dtype=torch.float16, device="cuda")
+    flops = 0
+
+    def d(y, ws, n):
+        return {"Y": y, "W_int4": ws[0], "scales": ws[1], "bias": None, "N": n}
+
+    def chunk():
+        # Gated-DeltaNet layer: in-projection (4 outputs), out-projection, gate/up + SwiGLU, down
+        ops.linear_int4_fused(X, [d(outs[10240], projs[10240], 10240), d(outs[6144], projs[6144], 6144),
+                                  d(outs[48], projs[48], 48), d(o48b, w48b, 48)], M, H)
+        ops.linear_int4(outs[H], Xo, w_out[0], w_out[1], None, M, H, 6144)
+        ops.mlp_gate_up_swiglu_int4(outs[F], X, w_gate[0], w_gate[1], w_up[0], w_up[1], M, F, H)
+        ops.linear_int4(outs[H], Xf, w_down[0], w_down[1], None, M, H, F)
+        # attention layer: q+gate / k / v, o-projection, the same MLP
+        ops.linear_int4_fused(X, [d(outs[12288], projs[12288], 12288), d(outs[1024], projs[1024], 1024),
+                                  d(o1024b, w1024b, 1024)], M, H)
+        ops.linear_int4(outs[H], Xo, w_o[0], w_o[1], None, M, H, 6144)
+        ops.mlp_gate_up_swiglu_int4(outs[F], X, w_gate[0], w_gate[1], w_up[0], w_up[1], M, F, H)
+        ops.linear_int4(outs[H], Xf, w_down[0], w_down[1], None, M, H, F)
+
+    flops = 2.0 * M * (H * (10240 + 6144 + 96) + 6144 * H + 2 * H * F + F * H
+                       + H * (12288 + 2048) + 6144 * H + 2 * H * F + F * H)
+    launches_per_chunk = 4 + 1 + 1 + 1 + 3 + 1 + 1 + 1
+    stream = torch.cuda.Stream()
+    steps, warm = args.steps, max(3, args.warmup)
+    with torch.cuda.stream(stream):
+        for _ in range(warm):
+            chunk()
+        stream.synchronize()
+        assert ops.last_linear_path() == 3, "the M > 32 path did not run"
+        if world > 1:
+            dist.barrier()
+        sampler = ClockSampler(local_rank)
+        sampler.start()
+        torch.cuda.synchronize()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record(stream)
+        for _ in range(steps):
+            chunk()
+        ev1.record(stream)
+        torch.cuda.synchronize()
+        ms = ev0.elapsed_time(ev1)
+        extra = 0
+        while sampler.samples() == 0 and sampler.proc is not None and extra < 200:
+            chunk()
+            stream.synchronize()
+            extra += 1
+        clocks = sampler.stop()
+        # end to end: the chunk's activations from pinned host memory, the last projection's output back
+        Xh = X.cpu().pin_memory()
+        Yh = torch.empty((M, H), dtype=torch.float16).pin_memory()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            X.copy_(Xh, non_blocking=True)
+            chunk()
+            Yh.copy_(outs[H], non_blocking=True)
+            stream.synchronize()
+        e2e_s = time.perf_counter() - t0
+    assert ops.device_status(local_rank) == 0
+    if world > 1:
+        t = torch.tensor([ms, e2e_s], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, e2e_s = float(t[0].item()), float(t[1].item())
+    tf_gpu = flops * steps / (ms * 1e-3) / 1e12
+    peaks = {}
+    try:
+        with open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "MEASURED_PEAKS.json")) as f:
+            peaks = json.load(f)
+    except OSError:
+        pass
+    peak = float(peaks.get("bf16_tflops_sustained", 1400.0))
+    line = {
+        "metric": "prefill_w4a16_gemm_tflops", "value": tf_gpu * world, "unit": "TFLOP/s", "n_gpus": world, "steps": steps,
+        "warmup": warm, "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "int4 weights x fp16 activations, fp32 accumulate", "data": "synthetic",
+        "config": {"workload": f"one prefill chunk of M={M} rows through the linears of one Gated-DeltaNet and one "
+                               f"attention layer of the 27B shape (hidden 5120, FFN 17408, INT4-G128): "
+                               f"{launches_per_chunk} launches, {flops / 1e9:.0f} GFLOP useful", "M": M,
+                   "l2": "1.1 GB of distinct weights per chunk (> 2x L2)"},
+        "roofline": {"bound": "tensor", "achieved": tf_gpu, "peak": peak, "unit": "TFLOP/s", "frac": tf_gpu / peak,
+                     "peak_kind": "of measured (sustained cuBLAS bf16)" if peaks else "of fallback", "traffic": None,
+                     "note": "useful flops; the kernel issues two MMAs per k step (exact hi + lo split of scale * weight)"},
+        "e2e": {"value": flops * steps / e2e_s / 1e12 * world, "unit": "TFLOP/s", "h2d_bytes_per_step": M * H * 2,
+                "d2h_bytes_per_step": M * H * 2},
+        "gpu_launches": steps * launches_per_chunk, "clocks": clocks,
+    }
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def tp_gemv_bench(args):
     """N-split tensor-parallel form of one projection: every rank streams 1/g of the weight rows with the same
     kernel, then one NCCL all-gather restores the [M, N] activation on every rank.  value = whole-projection
@@ -841,7 +969,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="step", choices=["step", "gemv", "sweep", "tp_gemv"])
+    ap.add_argument("--workload", default="step", choices=["step", "gemv", "sweep", "tp_gemv", "prefill"])
     ap.add_argument("--layers", type=int, default=64)
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--k", type=int, default=3)
@@ -871,6 +999,8 @@ def main():
         return
     if args.workload == "tp_gemv":
         return tp_gemv_bench(args)
+    if args.workload == "prefill":
+        return prefill_bench(args)
     if args.workload == "sweep":
         sweep(args)
         return
