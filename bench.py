@@ -285,7 +285,7 @@ def gemv_bench(args):
         "config": {"workload": f"INT4-G128 W4A16 linear M={M} K={K} N={N} ({args.shape}), {launches} launches/step "
                                f"in one CUDA graph", "M": M, "K": K, "N": N,
                    "l2": f"rotates over {n_buf} distinct weight buffers ({n_buf * w_bytes >> 20} MiB > 2x L2)",
-                   "kernel_path": {1: "tcgen05", 2: "cuda-core"}.get(path, "none")},
+                   "kernel_path": {1: "tcgen05", 2: "cuda-core", 3: "tcgen05 gemm (M > 32)"}.get(path, "none")},
         "roofline": {"bound": "hbm", "achieved": gbs_per_gpu, "peak": peak, "unit": "GB/s", "frac": gbs_per_gpu / peak,
                      "peak_kind": f"of {peak_kind}", "frac_of_nominal_8000": gbs_per_gpu / 8000.0,
                      "traffic": NCU_TRAFFIC_RATIO * per_launch,

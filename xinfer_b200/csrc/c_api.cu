@@ -19,6 +19,7 @@ namespace {
 constexpr int kMaxDevices = 64;
 constexpr int kCounterCapacity = 8192;
 constexpr size_t kSamplingScratchBytes = 4u << 20;  // rows * chunks * 16 B
+constexpr size_t kGemmPartialBytes = 96u << 20;     // K-split partials of the prefill GEMM
 
 struct DeviceCtx {
     bool ready = false;
@@ -30,6 +31,8 @@ struct DeviceCtx {
     long long* small_dev = nullptr;   // staging for the synchronous sampling calls
     long long* small_host = nullptr;  // pinned
     int forced_path = 0;              // xinfer_set_linear_path, per device
+    float* gemm_partials = nullptr;   // fp32 partial sums of the prefill GEMM's K splits (taken at its first use)
+    bool gemm_partials_tried = false;
 };
 
 DeviceCtx g_ctx[kMaxDevices];
@@ -85,7 +88,21 @@ int run_linear(xinfer_stream_t s, const void* x, xb::ActType in, bool out_f32, c
     cudaStream_t stream = static_cast<cudaStream_t>(s);
     if (c->forced_path != 2 && in == xb::ActType::F16 && xb::gemm_eligible(x, proj, num, swiglu, m, k, group_size)) {
         // more than 32 rows (prefill chunks): the compute-bound tcgen05 GEMM
-        const int r = xb::gemm_launch(stream, x, proj, num, swiglu, out_f32, m, k, c->status, xb::tc_wait_limit());
+        // scratch for K splits of the GEMM: taken once per device, outside any stream capture (a failed or refused
+        // allocation just means no K split)
+        if (!c->gemm_partials && !c->gemm_partials_tried) {
+            c->gemm_partials_tried = true;
+            cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+            if (cudaStreamIsCapturing(stream, &cap) == cudaSuccess && cap == cudaStreamCaptureStatusNone) {
+                void* ptr = nullptr;
+                if (cudaMalloc(&ptr, kGemmPartialBytes) == cudaSuccess) c->gemm_partials = static_cast<float*>(ptr);
+                else cudaGetLastError();
+            } else {
+                c->gemm_partials_tried = false;  // try again on a call that is not being captured
+            }
+        }
+        const int r = xb::gemm_launch(stream, x, proj, num, swiglu, out_f32, m, k, c->status, xb::tc_wait_limit(), c->num_sms,
+                                      c->gemm_partials, c->gemm_partials ? kGemmPartialBytes : 0);
         if (r == 0) { g_last_path = 3; return XINFER_OK; }
         if (r == -1) return fail_cuda(cudaGetLastError());
     }

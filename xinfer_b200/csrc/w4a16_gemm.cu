@@ -82,6 +82,7 @@ struct GemmParams {
     int out_f32;
     long long wait_limit;
     int* status;
+    float* partials;  // K split over gridDim.z: fp32 partial sums [split][m][n] (summed by a second kernel); else null
 };
 
 // D[tmem] (+)= A[smem descriptor] * B[smem descriptor], kind::f16, one CTA.  Issued by one thread.
@@ -156,7 +157,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1) w4a16_gemm_kernel(const __gri
     tc_fence_after_sync();
     const uint32_t tmem_base = ctrl->tmem_base;
 
-    const int S = p.stages;
+    // this CTA's stages: all of K, or its share when K is split over gridDim.z
+    const int s_begin = static_cast<int>(static_cast<long long>(blockIdx.z) * p.stages / gridDim.z);
+    const int s_end = static_cast<int>(static_cast<long long>(blockIdx.z + 1) * p.stages / gridDim.z);
+    const int S = s_end - s_begin;  // ring slots and phases count from the CTA's first stage
     const int tile_n = blockIdx.x, m0 = blockIdx.y * kGemmTileM;
     // first weight row of each half
     const int row_base0 = p.swiglu ? tile_n * 128 : tile_n * kGemmTileN;
@@ -178,8 +182,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) w4a16_gemm_kernel(const __gri
             const uint32_t dst = smem_u32(w_ring) + slot * kWSlotBytes;
             if (leader) {
                 mbar_arrive_expect_tx(full, kWSlotBytes);
-                tma_load_2d(dst, &p.w_map[0], full, s * (kGemmStageK / 2), row_base0, pol_w);
-                tma_load_2d(dst + kWSlotBytes / 2, &p.w_map[1], full, s * (kGemmStageK / 2), row_base1, pol_w);
+                tma_load_2d(dst, &p.w_map[0], full, (s_begin + s) * (kGemmStageK / 2), row_base0, pol_w);
+                tma_load_2d(dst + kWSlotBytes / 2, &p.w_map[1], full, (s_begin + s) * (kGemmStageK / 2), row_base1, pol_w);
             }
         };
         auto issue_x = [&](int s) {
@@ -187,7 +191,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) w4a16_gemm_kernel(const __gri
             const uint32_t full = smem_u32(&ctrl->x_full[slot]);
             if (leader) {
                 mbar_arrive_expect_tx(full, kXSlotBytes);
-                tma_load_2d(smem_u32(x_ring) + slot * kXSlotBytes, &p.x_map, full, s * kGemmStageK, m0, pol_x);
+                tma_load_2d(smem_u32(x_ring) + slot * kXSlotBytes, &p.x_map, full, (s_begin + s) * kGemmStageK, m0, pol_x);
             }
         };
         // the weights do not depend on the kernel in front of this one, the activations do
@@ -266,14 +270,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1) w4a16_gemm_kernel(const __gri
         const uint32_t a_off = static_cast<uint32_t>(h * (kAPartBytes / 2) + (r >> 3) * 1024 + (r & 7) * 128);
         const uint32_t sw = static_cast<uint32_t>(r & 7);
         bool ok = true;
-        uint32_t q_next = valid ? static_cast<uint32_t>(__ldg(sp)) : 0u;
-        uint32_t sc2 = 0;
+        // the scale of the stage's 128-k group (two stages per group), fetched one stage ahead
+        uint32_t q_next = (valid && S > 0) ? static_cast<uint32_t>(__ldg(sp + (s_begin >> 1))) : 0u;
         for (int s = 0; s < S; ++s) {
-            if ((s & 1) == 0) {  // a new 128-k group: its scale, as a pair
-                sc2 = q_next | (q_next << 16);
-                const int g = (s >> 1) + 1;
-                q_next = (valid && g < p.groups) ? static_cast<uint32_t>(__ldg(sp + g)) : 0u;
-            }
+            const uint32_t sc2 = q_next | (q_next << 16);
+            if (s + 1 < S) q_next = valid ? static_cast<uint32_t>(__ldg(sp + ((s_begin + s + 1) >> 1))) : 0u;
             const uint32_t wslot = static_cast<uint32_t>(s % kWSlots), aslot = static_cast<uint32_t>(s % kASlots);
             if (!mbar_wait(smem_u32(&ctrl->w_full[wslot]), (s / kWSlots) & 1u, ws)) { ok = false; break; }
             const uint32_t wsrc = smem_u32(w_ring) + wslot * kWSlotBytes + w_off;
@@ -319,10 +320,19 @@ __global__ void __launch_bounds__(kGemmThreads, 1) w4a16_gemm_kernel(const __gri
                     tmem_ld16(tmem_base + lane_sel + h * 256 + c * 16, d);
                     tmem_wait_ld();
                     if (valid) {
+                        if (p.partials) {
+                            float* ws_out = p.partials + static_cast<long long>(blockIdx.z) * p.m * p.n;
 #pragma unroll
-                        for (int j = 0; j < 16; ++j) {
-                            const int m = m0 + c * 16 + j;
-                            if (m < p.m) store_out<OutT>(p.y, static_cast<long long>(m) * p.ldy + row, __uint_as_float(d[j]) + bias);
+                            for (int j = 0; j < 16; ++j) {
+                                const int m = m0 + c * 16 + j;
+                                if (m < p.m) ws_out[static_cast<long long>(m) * p.n + row] = __uint_as_float(d[j]);
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) {
+                                const int m = m0 + c * 16 + j;
+                                if (m < p.m) store_out<OutT>(p.y, static_cast<long long>(m) * p.ldy + row, __uint_as_float(d[j]) + bias);
+                            }
                         }
                     }
                 }
@@ -362,6 +372,22 @@ __global__ void __launch_bounds__(kGemmThreads, 1) w4a16_gemm_kernel(const __gri
         __syncwarp();
         tc_fence_after_sync();
         tmem_dealloc(tmem_base, kGemmTmemCols);
+    }
+}
+
+// Sums the K splits in split order (deterministic), adds the bias and converts.
+template <typename OutT>
+__global__ void __launch_bounds__(256) gemm_splitk_reduce_kernel(void* y, long long ldy, const float* partials, int splits,
+                                                                 int m, int n, const float* bias) {
+    griddep_prologue();
+    const long long total = static_cast<long long>(m) * n;
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        float sum = 0.f;
+        for (int z = 0; z < splits; ++z) sum += __ldcg(partials + z * total + i);
+        const int row = static_cast<int>(i / n), col = static_cast<int>(i - static_cast<long long>(row) * n);
+        if (bias) sum += bias[col];
+        store_out<OutT>(y, static_cast<long long>(row) * ldy + col, sum);
     }
 }
 
@@ -441,7 +467,7 @@ bool gemm_eligible(const void* x, const TcProj* proj, int num, bool swiglu, long
 // One launch per projection (gate and up of the fused MLP share one).  Returns 0, -1 on a launch error, -2 when
 // the problem cannot be described to the kernel.
 int gemm_launch(cudaStream_t stream, const void* x, const TcProj* proj, int num, bool swiglu, bool out_f32, long long m,
-                long long k, int* status, long long wait_limit) {
+                long long k, int* status, long long wait_limit, int num_sms, float* partials, size_t partial_bytes) {
     const int launches = swiglu ? 1 : num;
     for (int i = 0; i < launches; ++i) {
         GemmParams p;
@@ -465,8 +491,31 @@ int gemm_launch(cudaStream_t stream, const void* x, const TcProj* proj, int num,
         p.status = status;
         const int rows_per_cta = swiglu ? 128 : kGemmTileN;
         dim3 grid(static_cast<unsigned>((a.n + rows_per_cta - 1) / rows_per_cta), static_cast<unsigned>((m + kGemmTileM - 1) / kGemmTileM));
-        const cudaError_t e = out_f32 ? gemm_configure_and_launch<float>(p, grid, stream) : gemm_configure_and_launch<__half>(p, grid, stream);
+        // Few tiles (N = 5120 at M = 512 is 40): K is split over gridDim.z so that about two CTAs per SM's worth of
+        // work exists, the fp32 partials go through a scratch buffer and a second kernel adds them in split order.
+        int splits = 1;
+        const long long tiles = static_cast<long long>(grid.x) * grid.y;
+        if (!swiglu && partials && tiles * 2 <= num_sms) {
+            splits = static_cast<int>((2LL * num_sms) / tiles);
+            if (splits > 8) splits = 8;
+            if (splits > p.stages / 8) splits = p.stages / 8;
+            const long long per_split = static_cast<long long>(m) * a.n * 4;
+            if (per_split * splits > static_cast<long long>(partial_bytes)) splits = static_cast<int>(partial_bytes / per_split);
+            if (splits < 2) splits = 1;
+        }
+        grid.z = static_cast<unsigned>(splits);
+        p.partials = splits > 1 ? partials : nullptr;
+        cudaError_t e = out_f32 ? gemm_configure_and_launch<float>(p, grid, stream) : gemm_configure_and_launch<__half>(p, grid, stream);
         if (e != cudaSuccess) return -1;
+        if (splits > 1) {
+            const long long total = m * a.n;
+            const unsigned blocks = static_cast<unsigned>(total / 1024 + 1 < 4096 ? total / 1024 + 1 : 4096);
+            e = out_f32 ? launch_pdl(gemm_splitk_reduce_kernel<float>, dim3(blocks), dim3(256), 0, stream, p.y, p.ldy,
+                                     static_cast<const float*>(partials), splits, p.m, p.n, p.bias)
+                        : launch_pdl(gemm_splitk_reduce_kernel<__half>, dim3(blocks), dim3(256), 0, stream, p.y, p.ldy,
+                                     static_cast<const float*>(partials), splits, p.m, p.n, p.bias);
+            if (e != cudaSuccess) return -1;
+        }
     }
     return 0;
 }
