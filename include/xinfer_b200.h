@@ -48,7 +48,9 @@ XINFER_EXPORT int xinfer_b200_init_current(void); /* the same for the calling th
 XINFER_EXPORT int xinfer_device_status(int device);
 XINFER_EXPORT const char* xinfer_last_cuda_error(void);
 XINFER_EXPORT const char* xinfer_b200_version(void);
-/* Which kernel family the last linear call on this thread used: 0 none, 1 tcgen05, 2 CUDA cores. */
+/* Which kernel family the last linear call on this thread used: 0 none, 1 tcgen05 (M <= 32, the decode and verify
+ * kernel), 2 CUDA cores (fp32 activations, odd shapes), 3 tcgen05 GEMM (M > 32: prefill chunks through the same entry
+ * points, forward_prefill_chunk of src/targets/qwen3_8/forward.cpp:402-554). */
 XINFER_EXPORT int xinfer_last_linear_path(void);
 /* Test hook for the bounded device-side waits of the tcgen05 linear kernel.  limit_clocks: SM clocks after
  * which a wait gives up (<= 0 restores the default, about one second).  withhold_x_from_stage >= 0: the
