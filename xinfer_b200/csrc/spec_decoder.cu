@@ -867,6 +867,83 @@ int64_t xinfer_spec_decoder_info(const xinfer_spec_decoder* d, int what) {
     }
 }
 
+// Replaces the decoder's synthetic weights by the tensors of a `.xinfer` artifact, under the section names the
+// reference's loader uses (src/targets/qwen3_8_27b/weights.cpp:358-640): `model.language_model.embed_tokens.weight`
+// (BF16 table, kept as BF16), `model.language_model.norm.weight`, `lm_head.weight` (+ `.scales`), and per layer
+// `model.language_model.layers.<l>.{input_layernorm,post_attention_layernorm}.weight`, `.mlp.{gate,up,down}_proj.weight`,
+// `.self_attn.{q,k,v,o}_proj.weight`, `.self_attn.{q,k}_norm.weight` or `.linear_attn.{in_proj_qkv,in_proj_z,in_proj_b,
+// in_proj_a,out_proj}.weight`, `.linear_attn.{conv1d.weight,A_log,dt_bias,norm.weight}`.  RMSNorm vectors follow the
+// checkpoint's "1 + w" convention except the gated norm of the linear-attention block (weights.cpp:306-318).  Under
+// tensor parallelism every rank loads its own row range of every split projection.  The layer kind found in the file
+// must be the one this decoder was built with.  The MTP head is not part of the reference's artifacts: its tensors
+// (`mtp.fc.weight`, `mtp.pre_fc_norm_embedding.weight`, `mtp.pre_fc_norm_hidden.weight`, `mtp.layers.0.*` named like a
+// full-attention layer) are loaded when present and left as they are otherwise.
+int xinfer_spec_decoder_load_artifact(xinfer_spec_decoder* d, xinfer_artifact* a, int verify) {
+    if (!d || !a) return XINFER_ERR_INVALID_ARGUMENT;
+    const auto& c = d->cfg;
+    DeviceGuard guard(d->device);
+    int rc = XINFER_OK;
+    auto lin = [&](const std::string& name, Linear& l) {
+        if (rc != XINFER_OK) return;
+        rc = xinfer_artifact_load_linear(a, name.c_str(), l.n_full, l.k, 128, l.row0, l.n, l.w, l.s, verify);
+        if (rc != XINFER_OK) xb::set_last_error((name + ": " + xinfer_artifact_error(a)).c_str());
+    };
+    auto vec = [&](const std::string& name, float* dst, int64_t count, int unit_offset) {
+        if (rc != XINFER_OK) return;
+        rc = xinfer_artifact_load_bf16_as_f32(a, name.c_str(), count, unit_offset, dst);
+        if (rc != XINFER_OK) xb::set_last_error((name + ": " + xinfer_artifact_error(a)).c_str());
+    };
+    auto has = [&](const std::string& name) { return xinfer_artifact_find(a, name.c_str()) >= 0; };
+    auto layer = [&](const std::string& prefix, Layer& L) {
+        const bool file_full = has(prefix + ".self_attn.q_proj.weight");
+        const bool file_lin = has(prefix + ".linear_attn.in_proj_qkv.weight");
+        if (rc == XINFER_OK && (file_full == file_lin || file_full != L.full)) {
+            xb::set_last_error((prefix + ": the artifact's layer kind is not the one this decoder was built with").c_str());
+            rc = XINFER_ERR_CONTRACT;
+            return;
+        }
+        vec(prefix + ".input_layernorm.weight", L.input_norm, c.hidden_size, 1);
+        vec(prefix + ".post_attention_layernorm.weight", L.post_norm, c.hidden_size, 1);
+        lin(prefix + ".mlp.gate_proj.weight", L.gate);
+        lin(prefix + ".mlp.up_proj.weight", L.up);
+        lin(prefix + ".mlp.down_proj.weight", L.down);
+        if (L.full) {
+            lin(prefix + ".self_attn.q_proj.weight", L.q_proj);
+            lin(prefix + ".self_attn.k_proj.weight", L.k_proj);
+            lin(prefix + ".self_attn.v_proj.weight", L.v_proj);
+            lin(prefix + ".self_attn.o_proj.weight", L.o_proj);
+            vec(prefix + ".self_attn.q_norm.weight", L.q_norm, 256, 1);
+            vec(prefix + ".self_attn.k_norm.weight", L.k_norm, 256, 1);
+        } else {
+            const int64_t hv = c.linear_num_v_heads, hk = c.linear_num_k_heads, ch = 2 * hk * 128 + hv * 128;
+            lin(prefix + ".linear_attn.in_proj_qkv.weight", L.in_qkv);
+            lin(prefix + ".linear_attn.in_proj_z.weight", L.in_z);
+            lin(prefix + ".linear_attn.in_proj_b.weight", L.in_b);
+            lin(prefix + ".linear_attn.in_proj_a.weight", L.in_a);
+            lin(prefix + ".linear_attn.out_proj.weight", L.out_proj);
+            vec(prefix + ".linear_attn.conv1d.weight", L.conv_w, ch * 4, 0);
+            vec(prefix + ".linear_attn.A_log", L.A_log, hv, 0);
+            vec(prefix + ".linear_attn.dt_bias", L.dt_bias, hv, 0);
+            vec(prefix + ".linear_attn.norm.weight", L.gdn_norm, 128, 0);
+        }
+    };
+    const std::string embed_name = "model.language_model.embed_tokens.weight";
+    rc = xinfer_artifact_load_section(a, embed_name.c_str(), 0, static_cast<uint64_t>(c.vocab_size) * c.hidden_size * 2, d->embed, verify);
+    if (rc != XINFER_OK) xb::set_last_error((embed_name + ": " + xinfer_artifact_error(a)).c_str());
+    vec("model.language_model.norm.weight", d->final_norm, c.hidden_size, 1);
+    lin("lm_head.weight", d->lm_head);
+    for (size_t l = 0; l < d->layers.size() && rc == XINFER_OK; ++l)
+        layer("model.language_model.layers." + std::to_string(l), d->layers[l]);
+    if (rc == XINFER_OK && has("mtp.fc.weight")) {
+        lin("mtp.fc.weight", d->mtp_fc);
+        vec("mtp.pre_fc_norm_embedding.weight", d->mtp_enorm, c.hidden_size, 1);
+        vec("mtp.pre_fc_norm_hidden.weight", d->mtp_hnorm, c.hidden_size, 1);
+        layer("mtp.layers.0", d->mtp_layer);
+    }
+    if (cudaDeviceSynchronize() != cudaSuccess && rc == XINFER_OK) rc = XINFER_ERR_CUDA;
+    return rc;
+}
+
 // Device pointer of a named tensor, for tests that mirror weights and state on the host.
 // layer = -1 addresses the model-level tensors, layer = num_hidden_layers the MTP head's layer.
 void* xinfer_spec_decoder_tensor(xinfer_spec_decoder* d, int layer, const char* name, int64_t* bytes) {
