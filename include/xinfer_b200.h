@@ -414,6 +414,12 @@ XINFER_EXPORT int xinfer_artifact_load_section(xinfer_artifact* a, const char* n
 XINFER_EXPORT int xinfer_artifact_load_linear(xinfer_artifact* a, const char* weight_name, int64_t out_features,
                                               int64_t in_features, int group_size, int64_t row0, int64_t rows,
                                               void* dst_weights_dev, void* dst_scales_dev, int verify);
+/* Replaces a decoder's (synthetic) weights by the tensors of an artifact, under the section names of the reference's
+ * loader (src/targets/qwen3_8_27b/weights.cpp:358-640); under tensor parallelism every rank loads its own row range of
+ * each split projection.  The MTP head's tensors (`mtp.fc.weight`, `mtp.pre_fc_norm_{embedding,hidden}.weight`,
+ * `mtp.layers.0.*`) are loaded when the file has them.  Call between create and the first step / capture.
+ * XINFER_ERR_CONTRACT: a layer's kind in the file differs from the decoder's, or a checksum mismatch. */
+XINFER_EXPORT int xinfer_spec_decoder_load_artifact(xinfer_spec_decoder* d, xinfer_artifact* a, int verify);
 /* A BF16 vector as fp32 on the device, with the checkpoint's "1 + w" RMSNorm convention when add_unit_offset
  * (src/targets/qwen3_8_27b/weights.cpp:319-347). */
 XINFER_EXPORT int xinfer_artifact_load_bf16_as_f32(xinfer_artifact* a, const char* name, int64_t num_elements,

@@ -163,3 +163,96 @@ def test_load_linear_whole_and_as_shards_then_run(tmp_path, cuda):
     ref = oracle.linear_int4_f64(X.astype(np.float32), packed, scales)
     assert np.max(np.abs(Y.cpu().numpy() - ref)) <= 1e-4 * max(1.0, float(np.abs(ref).max()))
     r.close()
+
+
+# ------------------------------------------------------------------ a whole model through the artifact
+_LIN = {"gate": "mlp.gate_proj", "up": "mlp.up_proj", "down": "mlp.down_proj", "q_proj": "self_attn.q_proj",
+        "k_proj": "self_attn.k_proj", "v_proj": "self_attn.v_proj", "o_proj": "self_attn.o_proj",
+        "in_qkv": "linear_attn.in_proj_qkv", "in_z": "linear_attn.in_proj_z", "in_b": "linear_attn.in_proj_b",
+        "in_a": "linear_attn.in_proj_a", "out_proj": "linear_attn.out_proj"}
+# decoder tensor -> (section, the checkpoint stores w - 1)
+_VEC = {"input_norm": ("input_layernorm.weight", True), "post_norm": ("post_attention_layernorm.weight", True),
+        "q_norm": ("self_attn.q_norm.weight", True), "k_norm": ("self_attn.k_norm.weight", True),
+        "conv_w": ("linear_attn.conv1d.weight", False), "A_log": ("linear_attn.A_log", False),
+        "dt_bias": ("linear_attn.dt_bias", False), "gdn_norm": ("linear_attn.norm.weight", False)}
+
+
+def _bf16_bits(x):
+    """fp32 -> bf16 bits, round to nearest even (what a converter stores)."""
+    u = np.ascontiguousarray(x, np.float32).view(np.uint32).astype(np.uint64)
+    return (((u + 0x7FFF + ((u >> 16) & 1)) >> 16) & 0xFFFF).astype(np.uint16)
+
+
+def _bf16_to_f32(bits):
+    return (bits.astype(np.uint32) << 16).view(np.float32)
+
+
+def _export_layer(dec, idx, prefix, secs):
+    """Appends the sections of one decoder layer; rewrites the decoder's fp32 vectors to what the file can hold."""
+    full = dec.is_full(idx)
+    lins = ["gate", "up", "down"] + (["q_proj", "k_proj", "v_proj", "o_proj"] if full else ["in_qkv", "in_z", "in_b", "in_a", "out_proj"])
+    vecs = ["input_norm", "post_norm"] + (["q_norm", "k_norm"] if full else ["conv_w", "A_log", "dt_bias", "gdn_norm"])
+    for v in vecs:
+        sec, unit = _VEC[v]
+        w = dec.tensor(idx, v, np.float32)
+        bits = _bf16_bits(w - np.float32(1.0) if unit else w)
+        held = _bf16_to_f32(bits) + np.float32(1.0) if unit else _bf16_to_f32(bits)
+        dec.write_tensor(idx, v, held.astype(np.float32))
+        secs.append((f"{prefix}.{sec}", RAW_BLOB, bits.tobytes()))
+    for l in lins:
+        secs.append((f"{prefix}.{_LIN[l]}.weight", TENSOR_WEIGHTS, dec.tensor(idx, l + ".w", np.uint8).tobytes()))
+        secs.append((f"{prefix}.{_LIN[l]}.weight.scales", TENSOR_SCALES, dec.tensor(idx, l + ".s", np.float16).tobytes()))
+
+
+@pytest.mark.gpu
+def test_decoder_loads_its_weights_from_an_artifact(tmp_path, cuda):
+    """A decoder's synthetic weights are written out under the reference loader's section names
+    (src/targets/qwen3_8_27b/weights.cpp:358-640), a second decoder built from another seed loads the file, and the
+    two then emit the same tokens and hold the same hidden states, bit for bit."""
+    import torch
+    from xinfer_b200.spec import Shape, SpecDecoder
+    shape_cfg = Shape(hidden_size=1024, intermediate_size=2048, num_hidden_layers=4, num_attention_heads=4,
+                      num_key_value_heads=2, vocab_size=4096, linear_num_v_heads=6, linear_num_k_heads=2)
+    a = SpecDecoder(shape_cfg, batch=2, k=3, max_seq=96, seed=5)
+    secs = [("model.language_model.embed_tokens.weight", RAW_BLOB, a.tensor(-1, "embed", np.uint16).tobytes())]
+    for name, sec in (("final_norm", "model.language_model.norm.weight"), ("mtp_enorm", "mtp.pre_fc_norm_embedding.weight"),
+                      ("mtp_hnorm", "mtp.pre_fc_norm_hidden.weight")):
+        bits = _bf16_bits(a.tensor(-1, name, np.float32) - np.float32(1.0))
+        a.write_tensor(-1, name, (_bf16_to_f32(bits) + np.float32(1.0)).astype(np.float32))
+        secs.append((sec, RAW_BLOB, bits.tobytes()))
+    for name, sec in (("lm_head", "lm_head.weight"), ("mtp_fc", "mtp.fc.weight")):
+        secs.append((sec, TENSOR_WEIGHTS, a.tensor(-1, name + ".w", np.uint8).tobytes()))
+        secs.append((sec + ".scales", TENSOR_SCALES, a.tensor(-1, name + ".s", np.float16).tobytes()))
+    L = shape_cfg.num_hidden_layers
+    for i in range(L):
+        _export_layer(a, i, f"model.language_model.layers.{i}", secs)
+    _export_layer(a, L, "mtp.layers.0", secs)
+    path = str(tmp_path / "model.xinfer")
+    write_artifact(path, json.dumps({"format": "xinfer", "note": "synthetic"}), secs)
+
+    b = SpecDecoder(shape_cfg, batch=2, k=3, max_seq=96, seed=77)   # other weights until the file is loaded
+    r = ArtifactReader(path)
+    b.load_artifact(r)
+    for i in list(range(L + 1)):
+        for n in ("gate.w", "down.s", "input_norm"):
+            assert np.array_equal(a.tensor(i, n, np.uint8), b.tensor(i, n, np.uint8)), (i, n)
+    a.reset(30, seed=3)
+    b.reset(30, seed=3)
+    for step in range(3):
+        a.step()
+        b.step()
+        ea, ca = a.results()
+        eb, cb = b.results()
+        assert np.array_equal(ea, eb) and np.array_equal(ca, cb), step
+        assert np.array_equal(a.tensor(-1, "x", np.uint16), b.tensor(-1, "x", np.uint16)), step
+    # a file whose layer kinds do not fit the decoder is refused
+    wrong = [(n.replace("layers.0.linear_attn", "layers.0.self_attn_x"), t, d) for n, t, d in secs]
+    path2 = str(tmp_path / "wrong.xinfer")
+    write_artifact(path2, "{}", wrong)
+    r2 = ArtifactReader(path2)
+    with pytest.raises(_lib.XInferError):
+        b.load_artifact(r2)
+    r2.close()
+    r.close()
+    a.close()
+    b.close()

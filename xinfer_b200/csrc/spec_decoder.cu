@@ -881,8 +881,7 @@ int64_t xinfer_spec_decoder_info(const xinfer_spec_decoder* d, int what) {
 int xinfer_spec_decoder_load_artifact(xinfer_spec_decoder* d, xinfer_artifact* a, int verify) {
     if (!d || !a) return XINFER_ERR_INVALID_ARGUMENT;
     const auto& c = d->cfg;
-    DeviceGuard guard(d->device);
-    int rc = XINFER_OK;
+    int rc = XINFER_OK;  // (the caller's current device is the decoder's, as for every other call on it)
     auto lin = [&](const std::string& name, Linear& l) {
         if (rc != XINFER_OK) return;
         rc = xinfer_artifact_load_linear(a, name.c_str(), l.n_full, l.k, 128, l.row0, l.n, l.w, l.s, verify);

@@ -63,6 +63,11 @@ class SpecDecoder:
         cfg = shape.to_c()
         return int(lib().xinfer_spec_decoder_exchange_bytes(C.byref(cfg), batch, k, world))
 
+    def load_artifact(self, reader, verify: bool = True) -> None:
+        """Replaces the synthetic weights by the tensors of an open ``xinfer_b200.artifact.ArtifactReader``
+        (section names of the reference's loader, src/targets/qwen3_8_27b/weights.cpp:358-640)."""
+        check(lib().xinfer_spec_decoder_load_artifact(self._h, reader._h, 1 if verify else 0), "spec_decoder_load_artifact")
+
     def close(self):
         if getattr(self, "_h", None):
             lib().xinfer_spec_decoder_destroy(self._h)
