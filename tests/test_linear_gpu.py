@@ -411,3 +411,26 @@ def test_device_side_wait_runs_out_and_is_reported(cuda):
     assert cuda.device_status(0) == 0          # reading clears the record
     again, _ = run_linear(cuda, X, W, S, out_dtype=torch.float16)
     assert np.array_equal(again, good)
+
+
+def test_prefill_gemm_wait_runs_out_and_is_reported(cuda):
+    """The same for the M > 32 GEMM: its loader withholds the activations from stage 1 on, the MMA warp's wait for them
+    runs out, every role leaves through the bounded path (tensor memory released), the status word reports it, and
+    the next launch is correct."""
+    from xinfer_b200 import _lib
+    M, K, N = 64, 512, 256
+    X, W, S, _ = synth_linear(M, K, N, seed=9)
+    Xd, Wd, Sd = dev(X), dev(W), dev(S)
+    Y = torch.zeros((M, N), dtype=torch.float16, device="cuda")
+    good, path = run_linear(cuda, X, W, S, out_dtype=torch.float16)
+    assert path == GEMM
+    cuda.set_wait_hooks(8_000_000, 1)
+    try:
+        assert cuda.linear_int4(Y, Xd, Wd, Sd, None, M, N, K) == 0
+        torch.cuda.synchronize()
+    finally:
+        cuda.set_wait_hooks(0, -1)
+    assert cuda.device_status(0) == _lib.ERR_DEVICE_TIMEOUT
+    assert cuda.device_status(0) == 0
+    again, _ = run_linear(cuda, X, W, S, out_dtype=torch.float16)
+    assert np.array_equal(again, good)

@@ -101,7 +101,7 @@ int run_linear(xinfer_stream_t s, const void* x, xb::ActType in, bool out_f32, c
                 c->gemm_partials_tried = false;  // try again on a call that is not being captured
             }
         }
-        const int r = xb::gemm_launch(stream, x, proj, num, swiglu, out_f32, m, k, c->status, xb::tc_wait_limit(), c->num_sms,
+        const int r = xb::gemm_launch(stream, x, proj, num, swiglu, out_f32, m, k, c->status, xb::tc_wait_limit(), xb::tc_x_stage_limit(), c->num_sms,
                                       c->gemm_partials, c->gemm_partials ? kGemmPartialBytes : 0);
         if (r == 0) { g_last_path = 3; return XINFER_OK; }
         if (r == -1) return fail_cuda(cudaGetLastError());

@@ -34,13 +34,14 @@ void tc_set_wait_hooks(long long limit_clocks, int withhold_x_from_stage);
 // Status word of the allocation-free entry point on `device` (which must be current): read and cleared.
 int tc_noalloc_take_status(int device);
 long long tc_wait_limit();  // clocks after which a device-side wait gives up (tc_set_wait_hooks)
+int tc_x_stage_limit();     // test hook of tc_set_wait_hooks: first activation stage that is never requested (-1: off)
 
 // Dense GEMM for more than 32 activation rows (prefill chunks) on tcgen05, both operands from shared memory
 // (w4a16_gemm.cu).  One launch per projection; gate and up of the fused MLP share one.
 bool gemm_eligible(const void* x, const TcProj* proj, int num, bool swiglu, long long m, long long k, int group_size);
 // `partials` / `partial_bytes`: scratch for the fp32 partial sums of a K split (null: never split).
 int gemm_launch(cudaStream_t stream, const void* x, const TcProj* proj, int num, bool swiglu, bool out_f32, long long m,
-                long long k, int* status, long long wait_limit, int num_sms, float* partials, size_t partial_bytes);
+                long long k, int* status, long long wait_limit, int x_stage_limit, int num_sms, float* partials, size_t partial_bytes);
 // Records a message for xinfer_last_cuda_error() on the calling thread (c_api.cu).
 void set_last_error(const char* msg);
 // Programmatic dependent launch (on unless XINFER_PDL=0): kernels are launched with the stream-serialization

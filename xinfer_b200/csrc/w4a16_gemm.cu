@@ -82,6 +82,7 @@ struct GemmParams {
     int out_f32;
     long long wait_limit;
     int* status;
+    int x_stage_limit;  // test hook: activation stages from this index on are never requested (-1: off)
     float* partials;  // K split over gridDim.z: fp32 partial sums [split][m][n] (summed by a second kernel); else null
 };
 
@@ -195,18 +196,21 @@ __global__ void __launch_bounds__(kGemmThreads, 1) w4a16_gemm_kernel(const __gri
             }
         };
         // the weights do not depend on the kernel in front of this one, the activations do
+        // (test hook: with x_stage_limit >= 0 the activation stages from that index on are never requested, so the
+        // waits for them run out and the kernel leaves through its abort path)
+        const int SX = (p.x_stage_limit >= 0 && p.x_stage_limit < S) ? p.x_stage_limit : S;
         int nw = 0, nx = 0;
         for (; nw < kWSlots && nw < S; ++nw) issue_w(nw);
         griddep_wait();
         if (leader) ws->dep_ready = 1;
-        for (; nx < kXSlots && nx < S; ++nx) issue_x(nx);
+        for (; nx < kXSlots && nx < SX; ++nx) issue_x(nx);
         bool ok = true;
-        while (ok && (nw < S || nx < S)) {
+        while (ok && (nw < S || nx < SX)) {
             if (nw < S) {
                 ok = mbar_wait_parked(smem_u32(&ctrl->w_empty[nw % kWSlots]), ((nw / kWSlots) & 1u) ^ 1u, ws);
                 if (ok) issue_w(nw++);
             }
-            if (ok && nx < S) {
+            if (ok && nx < SX) {
                 ok = mbar_wait_parked(smem_u32(&ctrl->x_empty[nx % kXSlots]), ((nx / kXSlots) & 1u) ^ 1u, ws);
                 if (ok) issue_x(nx++);
             }
@@ -467,7 +471,7 @@ bool gemm_eligible(const void* x, const TcProj* proj, int num, bool swiglu, long
 // One launch per projection (gate and up of the fused MLP share one).  Returns 0, -1 on a launch error, -2 when
 // the problem cannot be described to the kernel.
 int gemm_launch(cudaStream_t stream, const void* x, const TcProj* proj, int num, bool swiglu, bool out_f32, long long m,
-                long long k, int* status, long long wait_limit, int num_sms, float* partials, size_t partial_bytes) {
+                long long k, int* status, long long wait_limit, int x_stage_limit, int num_sms, float* partials, size_t partial_bytes) {
     const int launches = swiglu ? 1 : num;
     for (int i = 0; i < launches; ++i) {
         GemmParams p;
@@ -488,6 +492,7 @@ int gemm_launch(cudaStream_t stream, const void* x, const TcProj* proj, int num,
         p.swiglu = swiglu ? 1 : 0;
         p.out_f32 = out_f32 ? 1 : 0;
         p.wait_limit = wait_limit;
+        p.x_stage_limit = x_stage_limit;
         p.status = status;
         const int rows_per_cta = swiglu ? 128 : kGemmTileN;
         dim3 grid(static_cast<unsigned>((a.n + rows_per_cta - 1) / rows_per_cta), static_cast<unsigned>((m + kGemmTileM - 1) / kGemmTileM));

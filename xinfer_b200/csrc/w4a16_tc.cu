@@ -1044,6 +1044,7 @@ bool pdl_enabled() {
 static long long g_wait_limit = kWaitLimitClocks;
 long long tc_wait_limit() { return g_wait_limit; }
 static int g_x_stage_limit = -1;
+int tc_x_stage_limit() { return g_x_stage_limit; }
 void tc_set_wait_hooks(long long limit_clocks, int withhold_x_from_stage) {
     g_wait_limit = limit_clocks > 0 ? limit_clocks : kWaitLimitClocks;
     g_x_stage_limit = withhold_x_from_stage;
