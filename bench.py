@@ -794,6 +794,7 @@ def step_bench(args):
         ev1.record(stream)
         torch.cuda.synchronize()
         ms = ev0.elapsed_time(ev1)
+        tokens = int(dec.tensor(-1, "ctx", np.int32).astype(np.int64).sum() - ctx_before)   # of the timed steps only
         # the clock record must hold at least one sample taken under this load: keep the same steps running
         # (untimed) until nvidia-smi has delivered one
         extra = 0
@@ -811,7 +812,6 @@ def step_bench(args):
         clocks = sampler.stop()
         if extra:
             clocks["note"] = f"first sample arrived during {extra} untimed steps of the same load right after the timed region"
-        tokens = int(dec.tensor(-1, "ctx", np.int32).astype(np.int64).sum() - ctx_before)
         launches = dec.info(2)
 
         # the dominant kernel alone: the step's W4A16 launches, same order and weights, event-timed
@@ -882,6 +882,31 @@ def step_bench(args):
         (rms,), (rtok,) = reduce_over_ranks([r0.elapsed_time(r1)], [rtok], device="cuda")
         replicas = {"value": rtok / (rms * 1e-3), "unit": "tok/s", "ms_per_step": rms / steps, "scaling": "weak",
                     "note": f"{world} independent batch-{B} jobs, one per GPU, no inter-GPU traffic"}
+    batch_split = None
+    if use_tp and args.with_replicas and B % world == 0:
+        # the SAME batch-B job with its sequences divided over the GPUs (each rank the whole model and B / N
+        # sequences; sequences are independent, so nothing crosses NVLink): strong scaling without a collective
+        dec.close()
+        Bl = B // world
+        dec = SpecDecoder(shape, batch=Bl, k=k, max_seq=ctx0 + 1024, seed=rank)
+        dec.reset(ctx0, seed=rank)
+        with torch.cuda.stream(stream):
+            dec.capture(stream)
+            for _ in range(warm):
+                dec.step()
+            stream.synchronize()
+            c0 = dec.tensor(-1, "ctx", np.int32).astype(np.int64).sum()
+            dist.barrier()
+            r0, r1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            r0.record(stream)
+            for _ in range(steps):
+                dec.step()
+            r1.record(stream)
+            torch.cuda.synchronize()
+            btok = int(dec.tensor(-1, "ctx", np.int32).astype(np.int64).sum() - c0)
+        (bms,), (btok,) = reduce_over_ranks([r0.elapsed_time(r1)], [btok], device="cuda")
+        batch_split = {"value": btok / (bms * 1e-3), "unit": "tok/s", "ms_per_step": bms / steps, "scaling": "strong",
+                       "note": f"the same batch-{B} job, {Bl} sequence(s) per GPU, whole model on every GPU, no inter-GPU traffic"}
     peak, peak_kind = measured_peak()
     lin_gbs = lin_bytes / (lin_ms * 1e-3) / 1e9
     line = {
@@ -925,6 +950,8 @@ def step_bench(args):
         line["acceptance"] = acceptance
     if replicas is not None:
         line["replicas"] = replicas
+    if batch_split is not None:
+        line["batch_split"] = batch_split
     if rank == 0:
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_step_sample(B, k)
