@@ -414,6 +414,14 @@ XINFER_EXPORT int xinfer_artifact_load_section(xinfer_artifact* a, const char* n
 XINFER_EXPORT int xinfer_artifact_load_linear(xinfer_artifact* a, const char* weight_name, int64_t out_features,
                                               int64_t in_features, int group_size, int64_t row0, int64_t rows,
                                               void* dst_weights_dev, void* dst_scales_dev, int verify);
+/* Builds the context from a prompt, tokens[batch][T] on the host (every sequence the same length), starting from the
+ * empty context of xinfer_spec_decoder_reset(d, 0, seed): positions 0 .. T-2 go through the target in chunks of k + 1
+ * rows with every row kept, the MTP head's KV slots of those positions are filled, the last prompt token becomes the
+ * current token; ctx = T - 1 afterwards and xinfer_spec_decoder_step continues from there.  Stands where the
+ * reference's prefill loop does (forward_prefill_chunk, src/targets/qwen3_8/forward.cpp:402-554; engine.cpp:330-398)
+ * but runs at the decode kernels' row count.  Synchronous; one GPU only. */
+XINFER_EXPORT int xinfer_spec_decoder_prefill(xinfer_spec_decoder* d, xinfer_stream_t stream, const int64_t* prompt_host,
+                                              int64_t T);
 /* Replaces a decoder's (synthetic) weights by the tensors of an artifact, under the section names of the reference's
  * loader (src/targets/qwen3_8_27b/weights.cpp:358-640); under tensor parallelism every rank loads its own row range of
  * each split projection.  The MTP head's tensors (`mtp.fc.weight`, `mtp.pre_fc_norm_{embedding,hidden}.weight`,

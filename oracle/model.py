@@ -100,6 +100,27 @@ class OracleModel:
         st = seq_state["mtp"]
         oracle.kv_write(st["k_cache"], st["v_cache"], kk, vv.reshape(1, hkv, 256), pos)
 
+    def prefill(self, seq_state, tokens):
+        """Builds the context of one sequence from a prompt, starting from the empty state: positions 0 .. T-2 go
+        through the target (every row kept), the head's KV slot of position p is filled from (token p, hidden state of
+        position p - 1; zeros in front of position 0), the last prompt token becomes the current token."""
+        tokens = [int(t) for t in tokens]
+        assert seq_state["ctx"] == 0 and len(tokens) >= 1
+        h_prev = np.zeros(self.s.hidden_size, np.float16)
+        R = self.k + 1
+        body = tokens[:-1]
+        pos = 0
+        while pos < len(body):
+            chunk = body[pos:pos + R]
+            x, _ = self.target(chunk, pos, seq_state)
+            for i, t in enumerate(chunk):
+                self.draft_fill(t, h_prev if i == 0 else x[i - 1], pos + i, seq_state)
+            h_prev = x[len(chunk) - 1]
+            pos += len(chunk)
+        seq_state["ctx"] = len(body)
+        seq_state["cur_tok"] = tokens[-1]
+        seq_state["h_last"] = h_prev.copy()
+
     def greedy_continuation(self, seq_state, n):
         """The n tokens the target itself would emit after cur_tok (state is left untouched)."""
         import copy

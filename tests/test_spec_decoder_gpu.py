@@ -191,6 +191,36 @@ def test_long_context_attention_splits():
     dec.close()
 
 
+def test_prefill_from_a_prompt_then_steps(small):
+    """A prompt of 11 tokens per sequence (chunks of 4, 4 and 2 rows through the target, every row kept) builds the
+    context from the empty state; the oracle does the same sequence by sequence; then speculative steps must emit the
+    same tokens on both sides, with forced full acceptance first (which reads the MTP head's prompt slots)."""
+    dec, shape_cfg = small
+    B, k = dec.batch, dec.k
+    dec.reset(0, seed=9)
+    model = pull_model(dec, shape_cfg, k)
+    seqs = pull_state(dec, model, shape_cfg, B, dec.max_seq)
+    assert all(s["ctx"] == 0 for s in seqs)
+    prompt = np.random.default_rng(4).integers(0, shape_cfg.vocab_size, size=(B, 11)).astype(np.int64)
+    dec.prefill(prompt)
+    for b in range(B):
+        model.prefill(seqs[b], prompt[b])
+    assert dec.tensor(-1, "ctx", np.int32).tolist() == [10] * B
+    assert dec.tensor(-1, "cur_tok", np.int64).tolist() == prompt[:, -1].tolist()
+    h_gpu = dec.tensor(-1, "h_last", np.float16).reshape(B, shape_cfg.hidden_size)
+    for b in range(B):
+        assert rel_rms(h_gpu[b], seqs[b]["h_last"]) < 2e-2
+    cont = [model.greedy_continuation(seqs[b], k) for b in range(B)]
+    compare_step(dec, model, seqs, shape_cfg, cont, tag="prefill-accept-all")
+    compare_step(dec, model, seqs, shape_cfg, None, tag="prefill-free")
+    compare_step(dec, model, seqs, shape_cfg, None, tag="prefill-free2")
+    # a second prefill without a reset is refused
+    from xinfer_b200 import _lib
+    with pytest.raises(_lib.XInferError):
+        dec.prefill(prompt)
+    dec.reset(30, seed=3)   # leave the shared decoder as the other tests expect it
+
+
 def test_graph_replay_equals_eager(small):
     dec, shape_cfg = small
     B, k = dec.batch, dec.k

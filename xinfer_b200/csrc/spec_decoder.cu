@@ -77,6 +77,31 @@ __global__ void add_int_kernel(int* out, const int* in, int n, int v) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) out[i] = in[i] + v;
 }
+// Prompt handling.  rows[b * R + i] = prompt[b][c0 + i]
+__global__ void gather_prompt_kernel(long long* rows, const long long* prompt, int batch, long long T, long long c0, int R) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < batch * R) rows[i] = prompt[static_cast<long long>(i / R) * T + c0 + (i % R)];
+}
+// The hidden state in front of every row of a chunk: row (b, 0) <- h_last[b], row (b, i) <- x[b, i - 1].
+__global__ void shift_hidden_kernel(__half* out, const __half* h_last, const __half* x, int batch, int R, int H) {
+    const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= static_cast<long long>(batch) * R * H) return;
+    const int col = static_cast<int>(i % H);
+    const long long row = i / H;
+    const int b = static_cast<int>(row / R), r = static_cast<int>(row % R);
+    out[i] = r == 0 ? h_last[static_cast<long long>(b) * H + col] : x[(row - 1) * H + col];
+}
+// h_last[b] <- x[b, R - 1]
+__global__ void take_last_hidden_kernel(__half* h_last, const __half* x, int batch, int R, int H) {
+    const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= static_cast<long long>(batch) * H) return;
+    const int b = static_cast<int>(i / H), col = static_cast<int>(i % H);
+    h_last[i] = x[(static_cast<long long>(b) * R + R - 1) * H + col];
+}
+__global__ void last_prompt_token_kernel(long long* cur_tok, const long long* prompt, int batch, long long T) {
+    const int b = blockIdx.x * blockDim.x + threadIdx.x;
+    if (b < batch) cur_tok[b] = prompt[static_cast<long long>(b) * T + T - 1];
+}
 
 // A projection as this rank holds it: `n` output rows starting at row `row0` of the full [n_full][k] matrix
 // (n == n_full, row0 == 0 when it is not split).
@@ -571,7 +596,7 @@ int draft_pass(Dec* d, cudaStream_t s, int i, bool full) {
     return 0;
 }
 
-int target_pass(Dec* d, cudaStream_t s, int R, const long long* tokens) {
+int target_pass(Dec* d, cudaStream_t s, int R, const long long* tokens, bool with_logits = true) {
     const auto& c = d->cfg;
     const int M = d->batch * R, H = static_cast<int>(c.hidden_size);
     NL(xb::embed_rows(s, d->x, d->embed, tokens, M, H, c.vocab_size));
@@ -582,8 +607,32 @@ int target_pass(Dec* d, cudaStream_t s, int R, const long long* tokens) {
         CK(layer_forward(d, s, d->layers[l], R, d->x, l + 1 < nl ? d->layers[l + 1].input_norm : d->final_norm, d->ctx,
                          d->n_commit, d->prev_rows));
     // `normed` now holds the final norm of the residual stream: LM head -> fp32 logits
-    CK(lm_head_and_partials(d, s, M));
+    if (with_logits) CK(lm_head_and_partials(d, s, M));
     if (!d->linears_only) d->prev_rows = R;
+    return 0;
+}
+
+// The MTP head's KV slots of the R positions a prompt chunk has just gone through the target at: for every row the
+// head's pass up to its attention layer's cache write, from (token of the row, hidden state in front of the row).
+// One GPU only; the scratch rows live in activation buffers the target pass has finished with.
+int mtp_fill_rows(Dec* d, cudaStream_t s, int R, const long long* tokens, const __half* hprev_rows) {
+    const auto& c = d->cfg;
+    const int B = d->batch, M = B * R, H = static_cast<int>(c.hidden_size);
+    const int hkv = static_cast<int>(c.num_key_value_heads);
+    Layer& L = d->mtp_layer;
+    __half* emb = d->proj_out.p;
+    __half* cat = d->mlp.p;
+    XBuf xm;
+    xm.p = d->attn_out.p;
+    CK(xb::embed_rows(s, emb, d->embed, tokens, M, H, c.vocab_size));
+    CK(xb::rmsnorm_rows(s, cat, 2 * H, emb, d->mtp_enorm, M, H, c.rms_norm_eps, xperm_on()));
+    CK(xb::rmsnorm_rows(s, cat + H, 2 * H, hprev_rows, d->mtp_hnorm, M, H, c.rms_norm_eps, xperm_on()));
+    CK(lin(d, s, xm, cat, d->mtp_fc, M, kAll));
+    CK(xb::rmsnorm_rows(s, d->normed, H, xm.p, L.input_norm, M, H, c.rms_norm_eps, xperm_on()));
+    xb::TcProj fd[2] = {make_proj(d, L.k_proj, d->kbuf, kOwner), make_proj(d, L.v_proj, d->vbuf, kOwner)};
+    CK(run_lin(d, s, d->normed, fd, 2, false, false, M, H, d->bl * R, true));
+    CK(xb::attn_prep(s, d->qbuf, L.k_cache, L.v_cache, d->q_gate.p, d->kbuf.p, d->vbuf.p, L.q_norm, L.k_norm, d->ctx, B, R, 0,
+                     hkv, d->max_seq, c.rms_norm_eps, c.rope_theta, c.rope_dim));
     return 0;
 }
 
@@ -865,6 +914,56 @@ int64_t xinfer_spec_decoder_info(const xinfer_spec_decoder* d, int what) {
         case 7: return d->arena ? static_cast<int64_t>(xinfer_arena_capacity(d->arena)) : 0;
         default: return -1;
     }
+}
+
+// Builds the context from a prompt: tokens [batch][T] (host), all sequences the same length, starting from the empty
+// context of reset(0, seed).  Positions 0 .. T-2 go through the target model in chunks of k + 1 rows (the verify
+// pass's own kernels with every row kept: KV caches, Gated-DeltaNet and convolution state advance as in a step whose
+// drafts were all accepted), the MTP head's KV slots of the same positions are written from (token, hidden state in
+// front of it; zeros in front of position 0), and the last prompt token becomes the current token.  Afterwards
+// ctx = T - 1 and xinfer_spec_decoder_step continues from there.  Stands where the reference's prefill loop does
+// (forward_prefill_chunk, src/targets/qwen3_8/forward.cpp:402-554, called from engine.cpp:330-398) but runs at the
+// decode kernels' row count, not in 512-row chunks.  One GPU only.
+int xinfer_spec_decoder_prefill(xinfer_spec_decoder* d, xinfer_stream_t stream, const int64_t* prompt_host, int64_t T) {
+    if (!d || !prompt_host || T < 1) return XINFER_ERR_INVALID_ARGUMENT;
+    const auto& c = d->cfg;
+    const int B = d->batch, R = d->k + 1, H = static_cast<int>(c.hidden_size);
+    if (d->world > 1) { d->error = "prefill runs on one GPU"; return XINFER_ERR_INVALID_ARGUMENT; }
+    if (d->ctx_upper != 0) { d->error = "prefill starts from the empty context (reset(0, seed))"; return XINFER_ERR_INVALID_ARGUMENT; }
+    if (T - 1 + 2 * R > d->max_seq) { d->error = "prompt does not fit the cache"; return XINFER_ERR_INVALID_ARGUMENT; }
+    if (c.intermediate_size < 2 * c.hidden_size || c.num_attention_heads * 256 < c.hidden_size) {
+        d->error = "prefill borrows activation buffers that this shape makes too small";
+        return XINFER_ERR_INVALID_ARGUMENT;
+    }
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    long long* prompt = nullptr;
+    const size_t pbytes = static_cast<size_t>(B) * T * sizeof(long long);
+    if (cudaMalloc(&prompt, pbytes) != cudaSuccess) { cudaGetLastError(); return XINFER_ERR_OUT_OF_MEMORY; }
+    int rc = [&]() -> int {
+        CKCUDA(cudaMemcpyAsync(prompt, prompt_host, pbytes, cudaMemcpyHostToDevice, s));
+        CKCUDA(cudaMemsetAsync(d->h_last, 0, static_cast<size_t>(B) * H * sizeof(__half), s));
+        CK(xb::fill_int(s, d->n_commit, B, 0));
+        d->prev_rows = 0;
+        __half* hprev_rows = d->q_gate.p;
+        for (long long c0 = 0; c0 < T - 1; c0 += R) {
+            const int Rp = static_cast<int>((T - 1 - c0) < R ? (T - 1 - c0) : R);
+            gather_prompt_kernel<<<blocks_for(static_cast<size_t>(B) * Rp, 64), 64, 0, s>>>(d->verify_tokens, prompt, B, T, c0, Rp);
+            CK(target_pass(d, s, Rp, d->verify_tokens, false));
+            const size_t n = static_cast<size_t>(B) * Rp * H;
+            shift_hidden_kernel<<<blocks_for(n, 256), 256, 0, s>>>(hprev_rows, d->h_last, d->x, B, Rp, H);
+            CK(mtp_fill_rows(d, s, Rp, d->verify_tokens, hprev_rows));
+            take_last_hidden_kernel<<<blocks_for(static_cast<size_t>(B) * H, 256), 256, 0, s>>>(d->h_last, d->x, B, Rp, H);
+            add_int_kernel<<<1, 64, 0, s>>>(d->ctx, d->ctx, B, Rp);
+            CK(xb::fill_int(s, d->n_commit, B, Rp));  // every row of the chunk stays: the next pass replays all of them
+        }
+        last_prompt_token_kernel<<<1, 64, 0, s>>>(d->cur_tok, prompt, B, T);
+        CKCUDA(cudaGetLastError());
+        CKCUDA(cudaStreamSynchronize(s));
+        return XINFER_OK;
+    }();
+    cudaFree(prompt);
+    if (rc == XINFER_OK) d->ctx_upper = T - 1;
+    return rc;
 }
 
 // Replaces the decoder's synthetic weights by the tensors of a `.xinfer` artifact, under the section names the

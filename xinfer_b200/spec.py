@@ -63,6 +63,16 @@ class SpecDecoder:
         cfg = shape.to_c()
         return int(lib().xinfer_spec_decoder_exchange_bytes(C.byref(cfg), batch, k, world))
 
+    def prefill(self, prompt, stream=None) -> None:
+        """Builds the context from ``prompt`` (int64 [batch][T]); call ``reset(0, seed)`` first.  Afterwards the
+        context length is T - 1 and the last prompt token is the current token (``xinfer_spec_decoder_prefill``)."""
+        p = np.ascontiguousarray(prompt, np.int64)
+        assert p.ndim == 2 and p.shape[0] == self.batch
+        s = stream if stream is not None else torch.cuda.current_stream()
+        code = lib().xinfer_spec_decoder_prefill(self._h, C.c_void_p(s.cuda_stream), p.ctypes.data_as(C.c_void_p), p.shape[1])
+        if code != 0:
+            raise _lib.XInferError(code, "spec_decoder_prefill: " + self._err())
+
     def load_artifact(self, reader, verify: bool = True) -> None:
         """Replaces the synthetic weights by the tensors of an open ``xinfer_b200.artifact.ArtifactReader``
         (section names of the reference's loader, src/targets/qwen3_8_27b/weights.cpp:358-640)."""
