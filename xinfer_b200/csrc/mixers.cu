@@ -266,7 +266,7 @@ struct AttnSmem {
     __half v[kAttnStages][kAttnChunk][kAttnLd];
     float sp[4][kAttnChunk][kAttnSpLd];  // S^T partial sums over the four dim quarters, [key][row]
     __half p[kAttnRows][kAttnChunk + 8];
-    float row_max[kAttnRows];
+    float row_max[kAttnRows];   // running maximum of scale * log2(e) * score (the softmax runs in base 2)
     float row_sum[kAttnRows];
     float row_alpha[kAttnRows];
 };
@@ -320,6 +320,7 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_split_kernel(float* part
     const int G = hq / hkv;
     const int nrows = G * rows_per_seq;  // valid query rows, row = g * R + i
     const int ctx_b = ctx ? ctx[b] : ctx_base;  // (null: the stand-alone entry point's host-side start position)
+    const float scale2 = scale * 1.4426950408889634f;  // exp(x) = exp2(x * log2 e)
     long long total_keys = static_cast<long long>(ctx_b) + rows_per_seq;
     if (total_keys > max_seq) total_keys = max_seq;
     const int nchunks = static_cast<int>((total_keys + kAttnChunk - 1) / kAttnChunk);
@@ -426,7 +427,7 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_split_kernel(float* part
             for (int j = 0; j < 4; ++j) {
                 const bool vis = (r < nrows) && (key0 + j < limit) && (key0 + j < total_keys);
                 const int kk = part * 4 + j;
-                sc[j] = vis ? ((sm.sp[0][kk][r] + sm.sp[1][kk][r]) + (sm.sp[2][kk][r] + sm.sp[3][kk][r])) * scale : -INFINITY;
+                sc[j] = vis ? ((sm.sp[0][kk][r] + sm.sp[1][kk][r]) + (sm.sp[2][kk][r] + sm.sp[3][kk][r])) * scale2 : -INFINITY;
                 mx = fmaxf(mx, sc[j]);
             }
             mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
@@ -435,18 +436,25 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_split_kernel(float* part
             const float old_max = sm.row_max[r];
             const float new_max = fmaxf(old_max, mx);
             float sum = 0.f;
+            float pv[4];
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-                const float pv = (sc[j] == -INFINITY) ? 0.f : expf(sc[j] - new_max);
-                sum += pv;
-                sm.p[r][part * 4 + j] = __float2half_rn(pv);
+                pv[j] = (sc[j] == -INFINITY) ? 0.f : exp2f(sc[j] - new_max);
+                sum += pv[j];
+            }
+            {
+                const __half2 p01 = __floats2half2_rn(pv[0], pv[1]), p23 = __floats2half2_rn(pv[2], pv[3]);
+                uint2 packed;
+                packed.x = *reinterpret_cast<const uint32_t*>(&p01);
+                packed.y = *reinterpret_cast<const uint32_t*>(&p23);
+                *reinterpret_cast<uint2*>(&sm.p[r][part * 4]) = packed;
             }
             sum += __shfl_xor_sync(0xffffffffu, sum, 1);
             sum += __shfl_xor_sync(0xffffffffu, sum, 2);
             sum += __shfl_xor_sync(0xffffffffu, sum, 4);
             __syncwarp();
             if (part == 0) {
-                const float alpha = (old_max == -INFINITY) ? 0.f : expf(old_max - new_max);
+                const float alpha = (old_max == -INFINITY) ? 0.f : exp2f(old_max - new_max);
                 sm.row_alpha[r] = alpha;
                 sm.row_sum[r] = sm.row_sum[r] * alpha + sum;
                 sm.row_max[r] = new_max;
@@ -490,7 +498,7 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_split_kernel(float* part
     }
     cp_async_wait<0>();
 
-    // write the partial: O [rows][256] fp32, (max, sum) per row
+    // write the partial: O [rows][256] fp32, (max in base-2 units, sum) per row
     const long long pbase = (static_cast<long long>(b) * hkv + kvh) * nsplit + split;
     float* po = part_o + pbase * (kAttnRows * 256);
     const int g4 = lane >> 2, t4 = lane & 3;
@@ -526,7 +534,7 @@ __global__ void __launch_bounds__(256) attn_combine_kernel(__half* out, const fl
     for (int s = 0; s < nsplit; ++s) {
         const float ms = part_ml[(pbase + s) * (kAttnRows * 2) + r * 2];
         if (ms == -INFINITY) continue;
-        const float w = expf(ms - m);
+        const float w = exp2f(ms - m);  // the partial maxima are in base-2 units
         l += part_ml[(pbase + s) * (kAttnRows * 2) + r * 2 + 1] * w;
         acc += part_o[(pbase + s) * (kAttnRows * 256) + r * 256 + d] * w;
     }
