@@ -414,6 +414,13 @@ XINFER_EXPORT int xinfer_artifact_load_section(xinfer_artifact* a, const char* n
 XINFER_EXPORT int xinfer_artifact_load_linear(xinfer_artifact* a, const char* weight_name, int64_t out_features,
                                               int64_t in_features, int group_size, int64_t row0, int64_t rows,
                                               void* dst_weights_dev, void* dst_scales_dev, int verify);
+/* Sampling mode of the step.  temperature <= 0 (default): greedy drafting and the greedy accept rule, what the
+ * reference's engine runs.  temperature > 0: draft tokens are drawn from softmax(head logits / T) and the verify pass
+ * applies the reference's stochastic rule (src/ops/sampling.cpp:129-171) to target logits / T with the draft token's
+ * probability; uniforms are Philox4x32-10 of (seed, step index) - element b * k + i picks draft i of sequence b,
+ * element batch * k + b * k + i is its acceptance uniform - and the step index lives in device memory, so a replayed
+ * graph draws fresh numbers.  Call before capture.  One GPU only. */
+XINFER_EXPORT int xinfer_spec_decoder_set_sampling(xinfer_spec_decoder* d, float temperature, uint64_t seed);
 /* Builds the context from a prompt, tokens[batch][T] on the host (every sequence the same length), starting from the
  * empty context of xinfer_spec_decoder_reset(d, 0, seed): positions 0 .. T-2 go through the target in chunks of k + 1
  * rows with every row kept, the MTP head's KV slots of those positions are filled, the last prompt token becomes the

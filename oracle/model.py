@@ -24,6 +24,56 @@ def linear16(x16, W, S):
     return oracle.linear_int4_f64(np.asarray(x16, np.float16).astype(np.float32), W, S).astype(np.float16)
 
 
+def sample_token(logits, inv_t, u):
+    """One token from softmax(logits * inv_t) by inverting the cumulative distribution at u * Z, with the two-level
+    summation of the device kernel (chunks of 4096 logits in chunk order; inside the chosen chunk groups of sixteen
+    consecutive logits in group order, then the group's own running sum), all in fp32.  Returns (token, probability)."""
+    f32 = np.float32
+    l = np.asarray(logits, f32) * f32(inv_t)
+    V = l.size
+    nch = (V + 4095) // 4096
+    ms = np.array([l[c * 4096:(c + 1) * 4096].max() for c in range(nch)], f32)
+    se = np.array([np.exp(l[c * 4096:(c + 1) * 4096] - ms[c]).astype(f32).sum(dtype=f32) for c in range(nch)], f32)
+    m = f32(ms.max())
+    wts = (se * np.exp(ms - m).astype(f32)).astype(f32)
+    z = f32(0)
+    for x in wts:
+        z = f32(z + x)
+    target = f32(f32(u) * z)
+    before, pick = f32(0), nch - 1
+    for c in range(nch):
+        if f32(before + wts[c]) > target:
+            pick = c
+            break
+        if c + 1 < nch:
+            before = f32(before + wts[c])
+    rest = f32(target - before)
+    lo, hi = pick * 4096, min(V, (pick + 1) * 4096)
+    e = np.zeros(4096, f32)
+    e[:hi - lo] = np.exp(l[lo:hi] - m).astype(f32)
+    local = np.zeros(256, f32)
+    for t in range(256):
+        acc = f32(0)
+        for j in range(16):
+            acc = f32(acc + e[t * 16 + j])
+        local[t] = acc
+    last = (hi - lo - 1) // 16
+    prefix, th = f32(0), 0
+    for t in range(last + 1):
+        th = t
+        if f32(prefix + local[t]) > rest or t == last:
+            break
+        prefix = f32(prefix + local[t])
+    cum, tok = prefix, -1
+    for j in range(16):
+        if lo + th * 16 + j < hi:
+            tok = j
+            cum = f32(cum + e[th * 16 + j])
+            if cum > rest:
+                break
+    return lo + th * 16 + tok, float(f32(e[th * 16 + tok] / z))
+
+
 class OracleModel:
     def __init__(self, shape, layers, mtp_layer, top, k):
         self.s, self.layers, self.mtp_layer, self.top, self.k = shape, layers, mtp_layer, top, k
@@ -132,16 +182,22 @@ class OracleModel:
             toks.append(tok)
         return toks
 
-    def step(self, seq_state, draft_override=None):
-        """One speculative step of one sequence.  Returns (emitted tokens, debug dict)."""
+    def step(self, seq_state, draft_override=None, sampling=None):
+        """One speculative step of one sequence.  Returns (emitted tokens, debug dict).  `sampling` = dict(inv_t, u_draft[k],
+        u_accept[k]): draft tokens drawn from softmax(head logits * inv_t), the reference's stochastic accept rule."""
         k = self.k
         ctx = seq_state["ctx"]
         tok, h = seq_state["cur_tok"], seq_state["h_last"]
         drafts = []
+        draft_probs = []
         draft_logits = []
         for i in range(k):
             h, lg = self.draft(tok, h, ctx + i, seq_state)
-            tok = oracle.argmax(lg)
+            if sampling is None:
+                tok = oracle.argmax(lg)
+            else:
+                tok, p = sample_token(lg, sampling["inv_t"], sampling["u_draft"][i])
+                draft_probs.append(p)
             drafts.append(tok)
             draft_logits.append(lg)
         mtp_drafts = list(drafts)
@@ -152,7 +208,12 @@ class OracleModel:
         saved = [{n: (v.copy() if n in ("S", "conv_state") else v) for n, v in st.items()} for st in seq_state["layers"]]
         tokens = [seq_state["cur_tok"]] + drafts
         x, logits = self.target(tokens, ctx, seq_state)
-        res = oracle.speculative_accept_reject(np.array(drafts, np.int64), logits[:k])
+        if sampling is None or draft_override is not None:
+            res = oracle.speculative_accept_reject(np.array(drafts, np.int64), logits[:k])
+        else:
+            res = oracle.speculative_accept_reject(np.array(drafts, np.int64), logits[:k], np.array(draft_probs, np.float32),
+                                                   np.array(sampling["u_accept"], np.float32),
+                                                   inv_temperature=float(sampling["inv_t"]))
         na = res["num_accepted"]
         bonus = res["bonus_or_resampled_token"] if res["has_rejected_token"] else oracle.argmax(logits[k])
         if na < k:  # roll the recurrent state back and run the accepted prefix again

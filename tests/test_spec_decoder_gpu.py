@@ -221,6 +221,42 @@ def test_prefill_from_a_prompt_then_steps(small):
     dec.reset(30, seed=3)   # leave the shared decoder as the other tests expect it
 
 
+def test_stochastic_drafting_and_acceptance_inside_the_step():
+    """temperature 0.7: the step draws its draft tokens from the head's distribution and applies the reference's
+    stochastic rule with Philox uniforms of (seed, step index); the oracle regenerates the same uniforms, samples with
+    the same two-level sums and applies the literal rule.  Tokens, counts and contexts must agree over several steps,
+    eagerly and from the captured graph (whose replays must draw fresh numbers)."""
+    from xinfer_b200.spec import Shape, SpecDecoder
+    shape_cfg = Shape(hidden_size=1024, intermediate_size=2048, num_hidden_layers=4, num_attention_heads=4,
+                      num_key_value_heads=2, vocab_size=4096 + 512, linear_num_v_heads=6, linear_num_k_heads=2)
+    B, k, T, seed = 2, 3, 0.7, 1234
+    inv_t = float(np.float32(1.0) / np.float32(T))
+    for graph in (False, True):
+        dec = SpecDecoder(shape_cfg, batch=B, k=k, max_seq=96, seed=5)
+        dec.set_sampling(T, seed)
+        dec.reset(20, seed=3)
+        model = pull_model(dec, shape_cfg, k)
+        seqs = pull_state(dec, model, shape_cfg, B, dec.max_seq)
+        stream = torch.cuda.Stream()
+        accepted_total = 0
+        with torch.cuda.stream(stream):
+            for step in range(5):
+                if graph and step == 0:
+                    dec.capture(stream)       # runs step 0 eagerly, records the graph
+                else:
+                    dec.step()
+                emitted, counts = dec.results()
+                u = oracle.philox_uniform(2 * B * k, seed, step)
+                for b in range(B):
+                    samp = {"inv_t": inv_t, "u_draft": u[b * k:(b + 1) * k], "u_accept": u[B * k + b * k:B * k + (b + 1) * k]}
+                    want, dbg = model.step(seqs[b], None, samp)
+                    assert counts[b] == len(want) and emitted[b, :counts[b]].tolist() == want, (graph, step, b, emitted[b], want)
+                    accepted_total += dbg["num_accepted"]
+                assert dec.tensor(-1, "ctx", np.int32).tolist() == [s["ctx"] for s in seqs]
+        assert accepted_total > 0   # (random weights: about a third of the drafts survive the stochastic rule at T = 0.7)
+        dec.close()
+
+
 def test_graph_replay_equals_eager(small):
     dec, shape_cfg = small
     B, k = dec.batch, dec.k

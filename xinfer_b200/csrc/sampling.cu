@@ -274,6 +274,100 @@ __global__ void philox_uniform_kernel(float* out, long long n, unsigned long lon
         if (blk * 4 + j < n) out[blk * 4 + j] = static_cast<float>(c[j] >> 8) * (1.0f / 16777216.0f);
 }
 
+// The same generator with the subsequence taken from device memory (a step counter that the step's own kernels advance),
+// so that a replayed CUDA graph draws fresh numbers every replay.
+__global__ void philox_uniform_counter_kernel(float* out, long long n, unsigned long long seed,
+                                              const unsigned long long* subseq_dev) {
+    const long long blk = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (blk * 4 >= n) return;
+    const unsigned long long subseq = *subseq_dev;
+    uint32_t c[4] = {static_cast<uint32_t>(blk), static_cast<uint32_t>(static_cast<unsigned long long>(blk) >> 32),
+                     static_cast<uint32_t>(subseq), static_cast<uint32_t>(subseq >> 32)};
+    philox4x32_10(c, static_cast<uint32_t>(seed), static_cast<uint32_t>(seed >> 32));
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+        if (blk * 4 + j < n) out[blk * 4 + j] = static_cast<float>(c[j] >> 8) * (1.0f / 16777216.0f);
+}
+__global__ void add_counter_kernel(unsigned long long* counter, unsigned long long v) { *counter += v; }
+
+// Draws one token per row from softmax(logits * inv_t) by inverting the cumulative distribution at u * Z, in two
+// levels: the chunk (of 4096 logits) from the chunk sums of logits_partials_kernel, taken in chunk order; inside the
+// chunk every thread owns sixteen consecutive logits, the thread is found from the thread sums taken in thread order,
+// the token from the thread's own running sum.  Every sum is a fixed sequence of fp32 additions, so a (logits, u)
+// pair always gives the same token.  Also returns the token's probability exp(l * inv_t - max) / Z (the p_draft of
+// the acceptance rule, src/ops/sampling.cpp:129-156).  One block per row.
+__global__ void __launch_bounds__(kThreads) sample_finish_kernel(const Partial* partials, int chunks, const float* logits,
+                                                                 long long row_stride, int vocab, float inv_t,
+                                                                 const float* uniforms, int u_stride, long long* tok_out,
+                                                                 float* prob_out, int prob_stride) {
+    const int row = blockIdx.x, tid = threadIdx.x;
+    const Partial* P = partials + static_cast<long long>(row) * chunks;
+    const float* l = logits + static_cast<long long>(row) * row_stride;
+    __shared__ float s_m, s_z, s_rest;
+    __shared__ int s_chunk, s_thread;
+    __shared__ float s_local[kThreads], s_prefix;
+    if (tid == 0) {
+        float m = -INFINITY;
+        for (int c = 0; c < chunks; ++c) m = fmaxf(m, P[c].max_scaled);
+        float z = 0.f;
+        for (int c = 0; c < chunks; ++c) z += P[c].sum_exp * expf(P[c].max_scaled - m);
+        const float target = uniforms[static_cast<long long>(row) * u_stride] * z;
+        float before = 0.f;
+        int pick = chunks - 1;
+        for (int c = 0; c < chunks; ++c) {
+            const float w = P[c].sum_exp * expf(P[c].max_scaled - m);
+            if (before + w > target) { pick = c; break; }
+            if (c + 1 < chunks) before += w;
+        }
+        s_m = m; s_z = z; s_chunk = pick; s_rest = target - before;
+    }
+    __syncthreads();
+    const float m = s_m;
+    const int base = s_chunk * kChunk + tid * 16;
+    float e[16];
+    float local = 0.f;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+        e[j] = (base + j < vocab) ? expf(l[base + j] * inv_t - m) : 0.f;
+        local += e[j];
+    }
+    s_local[tid] = local;
+    __syncthreads();
+    if (tid == 0) {
+        const float rest = s_rest;
+        float prefix = 0.f;
+        int pick = 0;
+        // the last thread that holds a logit takes what rounding leaves over
+        int last = (min(vocab, (s_chunk + 1) * kChunk) - 1 - s_chunk * kChunk) / 16;
+        for (int t = 0; t <= last; ++t) {
+            pick = t;
+            if (prefix + s_local[t] > rest || t == last) break;
+            prefix += s_local[t];
+        }
+        s_thread = pick; s_prefix = prefix;
+    }
+    __syncthreads();
+    if (tid == s_thread) {
+        const float rest = s_rest;
+        float cum = s_prefix;
+        int pick = -1;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            if (base + j < vocab) {
+                pick = j;
+                cum += e[j];
+                if (cum > rest) break;
+            }
+        }
+        float pe = 0.f;
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+            if (j == pick) pe = e[j];
+        tok_out[row] = base + pick;
+        prob_out[static_cast<long long>(row) * prob_stride] = pe / s_z;
+    }
+}
+
 }  // namespace
 
 int sampling_chunks(long long vocab) { return static_cast<int>((vocab + kChunk - 1) / kChunk); }
@@ -336,4 +430,26 @@ int philox_uniform(cudaStream_t stream, float* out, long long n, unsigned long l
     return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 
+}  // namespace xb
+
+namespace xb {
+int philox_uniform_counter(cudaStream_t stream, float* out, long long n, unsigned long long seed,
+                           const unsigned long long* subseq_dev) {
+    const long long blocks4 = (n + 3) / 4;
+    if (blocks4 <= 0) return 0;
+    philox_uniform_counter_kernel<<<static_cast<unsigned>((blocks4 + 127) / 128), 128, 0, stream>>>(out, n, seed, subseq_dev);
+    return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+int add_counter(cudaStream_t stream, unsigned long long* counter_dev, unsigned long long v) {
+    add_counter_kernel<<<1, 1, 0, stream>>>(counter_dev, v);
+    return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+int sample_finish(cudaStream_t stream, const void* partials, int chunks, const float* logits, long long row_stride,
+                  long long vocab, float inv_temperature, const float* uniforms, int u_stride, int rows, long long* tok_out,
+                  float* prob_out, int prob_stride) {
+    sample_finish_kernel<<<rows, kThreads, 0, stream>>>(static_cast<const Partial*>(partials), chunks, logits, row_stride,
+                                                        static_cast<int>(vocab), inv_temperature, uniforms, u_stride, tok_out,
+                                                        prob_out, prob_stride);
+    return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
 }  // namespace xb

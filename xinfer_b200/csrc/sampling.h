@@ -44,5 +44,15 @@ int accept_reject_batched(cudaStream_t stream, const float* logits, long long ro
                           void* scratch, AcceptOut* out_dev);
 
 int philox_uniform(cudaStream_t stream, float* out, long long n, unsigned long long seed, unsigned long long subseq);
+// the subsequence read from device memory at run time (a counter that add_counter advances): graph-replay safe
+int philox_uniform_counter(cudaStream_t stream, float* out, long long n, unsigned long long seed,
+                           const unsigned long long* subseq_dev);
+int add_counter(cudaStream_t stream, unsigned long long* counter_dev, unsigned long long v);
+// One token per row from softmax(logits * inv_temperature) at the row's uniform (uniforms[row * u_stride]), from the
+// partials of sampling_partials(..., want_sum = true): token ids to tok_out[row], probabilities to
+// prob_out[row * prob_stride].
+int sample_finish(cudaStream_t stream, const void* partials, int chunks, const float* logits, long long row_stride,
+                  long long vocab, float inv_temperature, const float* uniforms, int u_stride, int rows, long long* tok_out,
+                  float* prob_out, int prob_stride);
 
 }  // namespace xb

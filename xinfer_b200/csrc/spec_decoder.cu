@@ -168,6 +168,12 @@ struct xinfer_spec_decoder {
     int* h_emitted_n = nullptr;
     long long* draft_override = nullptr;  // test hook: when armed, the verify pass checks these tokens instead
     bool override_armed = false;
+    // stochastic drafting and acceptance (temperature > 0): per step 2 * batch * k Philox uniforms - [0, batch * k) pick
+    // the draft tokens, the rest feed the acceptance rule - from (seed, step counter), the counter in device memory
+    float temperature = 0.f;
+    uint64_t sample_seed = 0;
+    unsigned long long* step_counter = nullptr;
+    float *uniforms = nullptr, *draft_probs = nullptr;
     int prev_rows = 0;       // rows of the previous target pass (for the lazy state commit)
     int64_t ctx_upper = 0;   // host-side upper bound of every sequence's context length
     cudaGraphExec_t graph_exec = nullptr;
@@ -321,6 +327,9 @@ void build_all(Dec* d) {
     d->mtp_hidden = dalloc<__half>(d, static_cast<size_t>(batch) * H, true);
     d->records = dalloc<xinfer_accept_record>(d, batch, true);
     d->draft_override = dalloc<long long>(d, static_cast<size_t>(batch) * k, true);
+    d->step_counter = dalloc<unsigned long long>(d, 1, true);
+    d->uniforms = dalloc<float>(d, static_cast<size_t>(2) * batch * k, true);
+    d->draft_probs = dalloc<float>(d, static_cast<size_t>(batch) * k, true);
     const int64_t hv = c.linear_num_v_heads, hk = c.linear_num_k_heads, ch = 2 * hk * 128 + hv * 128;
     d->x = dalloc<__half>(d, static_cast<size_t>(M) * H, true);
     d->emb = dalloc<__half>(d, static_cast<size_t>(batch) * H, true);
@@ -529,13 +538,15 @@ int layer_forward(Dec* d, cudaStream_t s, Layer& L, int R, __half* xr, const flo
 // kernels over that slice; under tensor parallelism the partial blocks are exchanged so that every rank can
 // finish argmax / acceptance over the whole vocabulary.
 int lm_head_and_partials(Dec* d, cudaStream_t s, int M) {
+    const bool stochastic = d->temperature > 0.f;
+    const float inv_t = stochastic ? 1.0f / d->temperature : 1.0f;
     xb::TcProj p = make_proj_local(d->lm_head, d->logits);
     account(d, d->lm_head, M, 4, true);
     CK(run_lin(d, s, d->normed, &p, 1, false, true, M, d->lm_head.k, 1, false));
     if (d->linears_only) return 0;
     const size_t block = xb::sampling_scratch_bytes(M, d->vocab_local);
     uint8_t* mine = reinterpret_cast<uint8_t*>(d->partials.p) + static_cast<size_t>(d->rank) * block;
-    CK(xb::sampling_partials(s, d->logits, d->vocab_local, M, d->vocab_local, 1.0f, false, d->lm_head.row0, mine));
+    CK(xb::sampling_partials(s, d->logits, d->vocab_local, M, d->vocab_local, inv_t, stochastic, d->lm_head.row0, mine));
     ++d->launches_per_step;
     if (d->world > 1) {
         ++d->launches_per_step;
@@ -589,8 +600,14 @@ int draft_pass(Dec* d, cudaStream_t s, int i, bool full) {
     if (!d->linears_only)
         CKCUDA(cudaMemcpyAsync(d->mtp_hidden, d->x_mtp.p, static_cast<size_t>(B) * H * sizeof(__half), cudaMemcpyDeviceToDevice, s));
     CK(lm_head_and_partials(d, s, B));
-    NL(xb::argmax_finish(s, d->partials.p, xb::sampling_chunks(d->vocab_local), d->world, partial_slice_stride(d, B), B,
-                         d->argmax_out));
+    if (d->temperature > 0.f) {
+        // draft token i of every sequence from softmax(logits / T) at its uniform; its probability is the rule's p_draft
+        NL(xb::sample_finish(s, d->partials.p, xb::sampling_chunks(d->vocab_local), d->logits, d->vocab_local, d->vocab_local,
+                             1.0f / d->temperature, d->uniforms + i, d->k, B, d->argmax_out, d->draft_probs + i, d->k));
+    } else {
+        NL(xb::argmax_finish(s, d->partials.p, xb::sampling_chunks(d->vocab_local), d->world, partial_slice_stride(d, B), B,
+                             d->argmax_out));
+    }
     NL(xb::copy_token_column(s, d->draft, d->argmax_out, B, d->k, i));
     d->launches_per_step += 4;
     return 0;
@@ -645,7 +662,12 @@ int enqueue_step(Dec* d, cudaStream_t s) {
     d->exchanges_per_step = 0;
     xb::TcPlan* prev_plan = xb::tc_plan_bind(d->plan);
     xb::tc_plan_rewind();  // the step's linears come in the recorded order (if a plan was recorded at capture)
+    const bool stochastic = d->temperature > 0.f && !d->override_armed;
     int rc = [&]() -> int {
+        if (stochastic) {
+            NL(xb::philox_uniform_counter(s, d->uniforms, 2LL * B * k, d->sample_seed, d->step_counter));
+            ++d->launches_per_step;
+        }
         for (int i = 0; i < k; ++i) CK(draft_pass(d, s, i, true));
         CK(draft_pass(d, s, k, false));  // the head's KV slot at ctx + k
         if (d->override_armed && !d->linears_only)
@@ -653,9 +675,18 @@ int enqueue_step(Dec* d, cudaStream_t s) {
                                    cudaMemcpyDeviceToDevice, s));
         NL(xb::build_verify_tokens(s, d->verify_tokens, d->cur_tok, d->draft, B, k));
         CK(target_pass(d, s, R, d->verify_tokens));
+        // greedy: draft i is kept iff it is the target's argmax of row i.  Stochastic: the reference's rule with the draft
+        // token's probability under the head and this step's acceptance uniforms, logits scaled by 1 / T on both sides
+        // (src/ops/sampling.cpp:129-171; with forced drafts there is no draft probability, so the greedy rule applies)
         NL(xb::accept_finish(s, d->partials.p, xb::sampling_chunks(d->vocab_local), d->world,
-                             partial_slice_stride(d, B * R), d->logits, d->vocab_local, d->vocab_local, 1.0f, d->draft, nullptr,
-                             nullptr, B, k, R, k, reinterpret_cast<xb::AcceptOut*>(d->records)));
+                             partial_slice_stride(d, B * R), d->logits, d->vocab_local, d->vocab_local,
+                             d->temperature > 0.f ? 1.0f / d->temperature : 1.0f, d->draft, stochastic ? d->draft_probs : nullptr,
+                             stochastic ? d->uniforms + static_cast<size_t>(B) * k : nullptr, B, k, R, k,
+                             reinterpret_cast<xb::AcceptOut*>(d->records)));
+        if (d->temperature > 0.f) {
+            NL(xb::add_counter(s, d->step_counter, 1));
+            ++d->launches_per_step;
+        }
         // x still holds the pre-norm hidden rows of the verify pass (the final norm added the last MLP output)
         NL(xb::spec_commit(s, d->records, d->draft, B, k, R, d->ctx, d->n_commit, d->cur_tok, d->emitted, d->emitted_n,
                            d->h_last, d->x, static_cast<int>(c.hidden_size)));
@@ -801,6 +832,7 @@ int xinfer_spec_decoder_reset(xinfer_spec_decoder* d, int64_t context_len, uint6
     init_tokens_kernel<<<1, 64>>>(d->cur_tok, B, nxt(), c.vocab_size);
     init_half_kernel<<<blocks_for(static_cast<size_t>(B) * c.hidden_size, 256), 256>>>(
         d->h_last, static_cast<size_t>(B) * c.hidden_size, nxt(), 1, 0.f, 1.0f, 0);
+    cudaMemset(d->step_counter, 0, sizeof(unsigned long long));
     d->prev_rows = 0;
     d->ctx_upper = context_len;
     return cudaDeviceSynchronize() == cudaSuccess ? XINFER_OK : XINFER_ERR_CUDA;
@@ -914,6 +946,22 @@ int64_t xinfer_spec_decoder_info(const xinfer_spec_decoder* d, int what) {
         case 7: return d->arena ? static_cast<int64_t>(xinfer_arena_capacity(d->arena)) : 0;
         default: return -1;
     }
+}
+
+// temperature <= 0: greedy drafting and acceptance (the default, what the reference's engine runs).  temperature > 0:
+// every draft token is drawn from softmax(head logits / T) and the verify pass applies the reference's stochastic rule
+// (src/ops/sampling.cpp:129-171) to the target's logits / T with the draft's probability; both consume Philox4x32-10
+// uniforms of (seed, step index): element b * k + i picks draft i of sequence b, element batch * k + b * k + i is its
+// acceptance uniform.  The step index lives in device memory (reset sets it to 0), so a captured step draws fresh
+// numbers on every replay.  Call before xinfer_spec_decoder_capture.  One GPU only (the rule reads the draft token's
+// logit, which an N-split LM head holds on one rank).
+int xinfer_spec_decoder_set_sampling(xinfer_spec_decoder* d, float temperature, uint64_t seed) {
+    if (!d) return XINFER_ERR_INVALID_ARGUMENT;
+    if (temperature > 0.f && d->world > 1) { d->error = "stochastic acceptance runs on one GPU"; return XINFER_ERR_INVALID_ARGUMENT; }
+    if (d->graph_exec) { d->error = "set the sampling mode before capture"; return XINFER_ERR_INVALID_ARGUMENT; }
+    d->temperature = temperature > 0.f ? temperature : 0.f;
+    d->sample_seed = seed;
+    return XINFER_OK;
 }
 
 // Builds the context from a prompt: tokens [batch][T] (host), all sequences the same length, starting from the empty

@@ -63,6 +63,13 @@ class SpecDecoder:
         cfg = shape.to_c()
         return int(lib().xinfer_spec_decoder_exchange_bytes(C.byref(cfg), batch, k, world))
 
+    def set_sampling(self, temperature: float, seed: int = 0) -> None:
+        """temperature <= 0: greedy (default).  Otherwise stochastic drafting and the reference's rejection rule with
+        Philox uniforms of (seed, step index); call before ``capture`` (``xinfer_spec_decoder_set_sampling``)."""
+        code = lib().xinfer_spec_decoder_set_sampling(self._h, float(temperature), int(seed))
+        if code != 0:
+            raise _lib.XInferError(code, "spec_decoder_set_sampling: " + self._err())
+
     def prefill(self, prompt, stream=None) -> None:
         """Builds the context from ``prompt`` (int64 [batch][T]); call ``reset(0, seed)`` first.  Afterwards the
         context length is T - 1 and the last prompt token is the current token (``xinfer_spec_decoder_prefill``)."""
