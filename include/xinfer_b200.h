@@ -203,6 +203,15 @@ XINFER_EXPORT int xinfer_speculative_accept_reject_batched(xinfer_stream_t s, co
                                                            int batch, int num_draft, int rows_per_seq, int bonus_row,
                                                            xinfer_accept_record* out_dev);
 
+/* One token per row drawn from softmax(logits * inv_temperature) at the row's uniform in [0, 1) (inverse of the
+ * cumulative distribution, a fixed two-level fp32 summation: the same (logits, u) always gives the same token), and the
+ * token's probability - the draft token and the p_draft that xinfer_speculative_accept_reject_batched takes.  No
+ * counterpart in the reference, whose drafter is greedy (src/runtime/engine.cpp:279-303 rejects temperature).
+ * Asynchronous; all pointers device memory. */
+XINFER_EXPORT int xinfer_sample_tokens(xinfer_stream_t s, const float* logits_dev, int64_t row_stride, int64_t vocab_size,
+                                       int rows, float inv_temperature, const float* rand_uniform_dev, int64_t* tokens_out_dev,
+                                       float* probs_out_dev);
+
 /* Philox4x32-10 uniforms in [0,1): out[i] = (word(i&3) of block(i>>2) >> 8) * 2^-24 with counter
  * {lo(i>>2), hi(i>>2), lo(subsequence), hi(subsequence)} and key {lo(seed), hi(seed)}.  No counterpart
  * in the reference (its acceptance op takes caller-supplied uniforms). */

@@ -242,3 +242,47 @@ def test_stochastic_margin_run_200_seeds(cuda):
     print(f"stochastic margin run: {decisions} decisions, {flips_inside} flips inside the 1e-6 band, "
           f"smallest margin {min_margin:.3e}")
     assert decisions >= 200 * B
+
+
+def test_sample_tokens_against_the_oracle_sampler(cuda):
+    """Draft-token sampling at the acceptance configuration's shape (8 rows, vocab 151936, T = 0.7): the kernel inverts the
+    cumulative distribution with a fixed two-level fp32 summation that `oracle.model.sample_token` restates; tokens
+    must be equal and probabilities within fp32 rounding for every draw of 40 seeds, the probabilities must be the
+    softmax's, and the empirical distribution over a small vocabulary must follow the softmax."""
+    from oracle.model import sample_token
+    B, V, T = 8, 151936, 0.7
+    inv_t = float(np.float32(1.0) / np.float32(T))
+    mismatches = 0
+    for seed in range(40):
+        rng = np.random.default_rng(500 + seed)
+        logits = (rng.standard_normal((B, V)) * 3).astype(np.float32)
+        u = oracle.philox_uniform(B, 4000 + seed, 0)
+        tok = torch.empty(B, dtype=torch.int64, device="cuda")
+        prob = torch.empty(B, dtype=torch.float32, device="cuda")
+        assert cuda.sample_tokens(torch.from_numpy(logits).cuda(), torch.from_numpy(u).cuda(), tok, prob, inv_t) == 0
+        tok, prob = tok.cpu().numpy(), prob.cpu().numpy()
+        for b in range(B):
+            want_t, want_p = sample_token(logits[b], inv_t, u[b])
+            mismatches += int(tok[b] != want_t)
+            if tok[b] == want_t:
+                assert abs(prob[b] - want_p) <= 2e-5 * want_p
+            p64 = oracle.token_prob_f64(logits[b] * np.float32(inv_t), int(tok[b]))
+            assert abs(prob[b] - p64) <= 1e-4 * p64
+    assert mismatches == 0
+    # a small vocabulary (two chunks, ragged): 20000 draws follow the softmax
+    V2 = 4096 + 37
+    l2 = (np.random.default_rng(1).standard_normal(V2) * 2).astype(np.float32)
+    n = 20000
+    u = oracle.philox_uniform(n, 77, 3)
+    rows = torch.from_numpy(np.broadcast_to(l2, (n, V2)).copy()).cuda()
+    tok = torch.empty(n, dtype=torch.int64, device="cuda")
+    prob = torch.empty(n, dtype=torch.float32, device="cuda")
+    for i in range(0, n, 500):    # (the library's sampling scratch bounds rows x chunks per call)
+        assert cuda.sample_tokens(rows[i:i + 500], torch.from_numpy(u[i:i + 500]).cuda(), tok[i:i + 500], prob[i:i + 500], 1.0) == 0
+    tok = tok.cpu().numpy()
+    p = np.exp(l2.astype(np.float64) - l2.max())
+    p /= p.sum()
+    top = np.argsort(-p)[:20]
+    freq = np.bincount(tok, minlength=V2) / n
+    assert tok.min() >= 0 and tok.max() < V2
+    assert np.all(np.abs(freq[top] - p[top]) <= 5 * np.sqrt(p[top] * (1 - p[top]) / n) + 1e-3)

@@ -338,6 +338,23 @@ int xinfer_speculative_accept_reject_batched(xinfer_stream_t s, const int64_t* d
     return XINFER_OK;
 }
 
+int xinfer_sample_tokens(xinfer_stream_t s, const float* logits, int64_t row_stride, int64_t vocab, int rows,
+                         float inv_temperature, const float* uniforms, int64_t* tokens_out, float* probs_out) {
+    if (rows <= 0 || vocab <= 0) return XINFER_NOOP_INVALID_SHAPE;
+    if (!logits || !uniforms || !tokens_out || !probs_out || !(inv_temperature > 0.f) || row_stride < vocab)
+        return XINFER_ERR_INVALID_ARGUMENT;
+    DeviceCtx* c = nullptr;
+    int rc = get_ctx(&c);
+    if (rc != XINFER_OK) return rc;
+    if (xb::sampling_scratch_bytes(rows, vocab) > kSamplingScratchBytes) return XINFER_ERR_INVALID_ARGUMENT;
+    cudaStream_t st = static_cast<cudaStream_t>(s);
+    if (xb::sampling_partials(st, logits, row_stride, rows, vocab, inv_temperature, true, 0, c->sampling) != 0 ||
+        xb::sample_finish(st, c->sampling, xb::sampling_chunks(vocab), logits, row_stride, vocab, inv_temperature, uniforms, 1,
+                          rows, reinterpret_cast<long long*>(tokens_out), probs_out, 1) != 0)
+        return fail_cuda(cudaGetLastError());
+    return XINFER_OK;
+}
+
 int xinfer_speculative_accept_reject(xinfer_stream_t s, const int64_t* draft_tokens, size_t n, const float* logits,
                                      int64_t vocab, const float* draft_probs, const float* rand_uniform,
                                      xinfer_accept_result* out) {

@@ -189,6 +189,15 @@ def speculative_accept_reject_batched(draft_tokens: torch.Tensor, target_logits:
         "speculative_accept_reject_batched")
 
 
+def sample_tokens(logits: torch.Tensor, rand_uniform: torch.Tensor, tokens_out: torch.Tensor, probs_out: torch.Tensor,
+                  inv_temperature: float = 1.0) -> int:
+    """One token per row of ``logits`` [rows, vocab] fp32 from softmax(logits * inv_temperature) at the row's uniform, and
+    its probability (``xinfer_sample_tokens``): the draft token and p_draft of the stochastic acceptance rule."""
+    rows, vocab = logits.shape
+    return check(lib().xinfer_sample_tokens(_stream(), _ptr(logits), logits.stride(0), vocab, rows, inv_temperature,
+                                            _ptr(rand_uniform), _ptr(tokens_out), _ptr(probs_out)), "sample_tokens")
+
+
 def decode_accept_records(out_records: torch.Tensor) -> list:
     raw = out_records.cpu().numpy().tobytes()
     n = len(raw) // ACCEPT_RECORD_BYTES
