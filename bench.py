@@ -773,6 +773,8 @@ def step_bench(args):
         dist.barrier()
     else:
         dec = SpecDecoder(shape, batch=B, k=k, max_seq=ctx0 + 1024, seed=rank)
+        if args.temperature > 0:
+            dec.set_sampling(args.temperature, 12345 + rank)   # stochastic drafting + rejection rule (one GPU per job)
         dec.reset(ctx0, seed=rank)
     stream = torch.cuda.Stream()
     steps, warm = args.steps, max(3, args.warmup)
@@ -914,7 +916,8 @@ def step_bench(args):
         "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "strong" if use_tp else "weak", "vs_baseline": None,
         "dtype": "int4 weights x fp16 activations, fp32 accumulate", "data": "synthetic",
         "config": {"workload": f"27B-shape hybrid ({args.layers} layers: Gated-DeltaNet + full attention, hidden 5120, "
-                               f"FFN 17408, vocab 151936, INT4-G128), MTP k={k}, batch {B}, context {ctx0}, greedy; "
+                               f"FFN 17408, vocab 151936, INT4-G128), MTP k={k}, batch {B}, context {ctx0}, "
+                               + ("greedy; " if args.temperature <= 0 or use_tp else f"stochastic at T={args.temperature}; ") +
                                f"one step = {k} MTP draft passes + one {B * (k + 1)}-row verify pass + acceptance + "
                                f"commit, replayed as one CUDA graph",
                    "layers": args.layers, "batch": B, "k": k, "context": ctx0,
@@ -1001,6 +1004,8 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--k", type=int, default=3)
     ap.add_argument("--context", type=int, default=8192)
+    ap.add_argument("--temperature", type=float, default=0.0,
+                    help="step workload: > 0 runs stochastic drafting and the rejection rule (default 0: greedy, the metric's configuration)")
     ap.add_argument("--shape", default="gate_up", choices=sorted(LAYER_SHAPES))
     ap.add_argument("--m", "--rows", dest="m", type=int, default=1)  # activation rows M (--rows: torchrun parses --m itself)
     ap.add_argument("--launches", type=int, default=64)
