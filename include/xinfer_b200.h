@@ -58,8 +58,9 @@ XINFER_EXPORT int xinfer_last_linear_path(void);
  * the kernel returns through its abort path and xinfer_device_status reports the timeout (-1: off).
  * Process-wide; applies to launches enqueued afterwards.  No counterpart in the reference. */
 XINFER_EXPORT void xinfer_debug_set_wait_hooks(int64_t limit_clocks, int withhold_x_from_stage);
-/* Force a kernel family for the linear entry points on the current device: 0 = automatic, 1 = tcgen05 when
- * eligible (default for fp16 activations), 2 = CUDA cores only.  For measurements and tests. */
+/* Force a kernel family for the linear entry points on the current device: 0 = automatic (fp16 activations: the
+ * tcgen05 decode kernel up to 32 rows, 32-row slices of it up to 128 rows, the tcgen05 GEMM above), 1 = the same,
+ * 2 = CUDA cores only, 3 = the GEMM for every M > 32.  For measurements and tests. */
 XINFER_EXPORT void xinfer_set_linear_path(int path);
 
 /* ---- INT4-G128-SYM W4A16 linear:  Y[M,N] = X[M,K] * W^T + bias ---------------------------------

@@ -252,17 +252,21 @@ def test_prefill_gemm_against_oracle(cuda, M, K, N):
     X, W, S, _ = synth_linear(M, K, N, seed=M + N)
     bias = np.random.default_rng(1).normal(0, 0.1, size=N).astype(np.float32)
     ref = oracle.linear_int4_f64(X.astype(np.float32), W, S, bias)
-    got, used = run_linear(cuda, X, W, S, bias=bias)
+    got, used = run_linear(cuda, X, W, S, bias=bias, path=GEMM)   # (forced: up to 128 rows the default is the decode kernel)
     assert used == GEMM
     # (one tensor-core accumulation over all of K instead of one per 128-k group; its fp32 adds truncate, so the
     # error grows with K: 3.7e-5 measured at K = 5120, 1.3e-4 at K = 17408; the stated bound is 1e-3 relative)
     assert rel_err(got, ref) <= 3e-4
-    got16, used = run_linear(cuda, X, W, S, bias=bias, out_dtype=torch.float16)
+    got16, used = run_linear(cuda, X, W, S, bias=bias, out_dtype=torch.float16, path=GEMM)
     assert used == GEMM
     assert rel_err(got16, ref) <= 1.5e-3  # the fp16 rounding of the output
     # the CUDA-core path of the same call agrees
     simt, used = run_linear(cuda, X, W, S, bias=bias, path=SIMT)
     assert used == SIMT and rel_err(got, simt) <= 3e-4
+    # the default: 32-row slices of the decode kernel up to 128 rows (the reference's association), the GEMM above
+    auto, used = run_linear(cuda, X, W, S, bias=bias)
+    assert used == (TC if M <= 128 else GEMM)
+    assert rel_err(auto, ref) <= (2e-5 if M <= 128 else 3e-4)
 
 
 @pytest.mark.gpu
@@ -279,6 +283,10 @@ def test_prefill_gemm_unpack_bit_exact_via_one_hot(cuda):
     got, used = run_linear(cuda, X, W, S)
     assert used == GEMM
     assert np.array_equal(got, q[:, np.arange(M) % K].T.astype(np.float32))
+    got, used = run_linear(cuda, X[:100], W, S)      # 100 rows: four slices through the decode kernel
+    assert used == TC and np.array_equal(got, q[:, np.arange(100) % K].T.astype(np.float32))
+    got, used = run_linear(cuda, X, W, S)
+    assert np.array_equal(got, q[:, np.arange(M) % K].T.astype(np.float32))
 
 
 @pytest.mark.gpu
@@ -293,7 +301,11 @@ def test_prefill_swiglu_and_fused_projections(cuda, M):
     u = oracle.linear_int4_f64(X.astype(np.float32), Wu, Su)
     ref = g / (1.0 + np.exp(-g)) * u
     Y = torch.empty((M, N), dtype=torch.float16, device="cuda")
-    assert cuda.mlp_gate_up_swiglu_int4(Y, dev(X), dev(Wg), dev(Sg), dev(Wu), dev(Su), M, N, K) == 0
+    cuda.set_linear_path(GEMM)
+    try:
+        assert cuda.mlp_gate_up_swiglu_int4(Y, dev(X), dev(Wg), dev(Sg), dev(Wu), dev(Su), M, N, K) == 0
+    finally:
+        cuda.set_linear_path(0)
     torch.cuda.synchronize()
     assert cuda.last_linear_path() == GEMM and cuda.device_status(0) == 0
     assert rel_err(Y.float().cpu().numpy(), ref) <= 3e-3
@@ -306,9 +318,28 @@ def test_prefill_swiglu_and_fused_projections(cuda, M):
         Ss.append(sc)
         Ys.append(torch.empty((M, n), dtype=torch.float16, device="cuda"))
     descs = [{"Y": Ys[i], "W_int4": dev(Ws[i]), "scales": dev(Ss[i]), "bias": None, "N": Ns[i]} for i in range(3)]
-    assert cuda.linear_int4_fused(dev(X), descs, M, K) == 0
+    cuda.set_linear_path(GEMM)
+    try:
+        assert cuda.linear_int4_fused(dev(X), descs, M, K) == 0
+    finally:
+        cuda.set_linear_path(0)
     torch.cuda.synchronize()
     assert cuda.last_linear_path() == GEMM and cuda.device_status(0) == 0
+    if M <= 128:   # the default for this many rows: slices through the decode kernel, fused and SwiGLU forms included
+        Y2 = torch.empty((M, N), dtype=torch.float16, device="cuda")
+        assert cuda.mlp_gate_up_swiglu_int4(Y2, dev(X), dev(Wg), dev(Sg), dev(Wu), dev(Su), M, N, K) == 0
+        torch.cuda.synchronize()
+        assert cuda.last_linear_path() == TC
+        g = oracle.linear_int4_f64(X.astype(np.float32), Wg, Sg)
+        u = oracle.linear_int4_f64(X.astype(np.float32), Wu, Su)
+        assert rel_err(Y2.float().cpu().numpy(), g / (1.0 + np.exp(-g)) * u) <= 3e-3
+        Ys2 = [torch.empty((M, n), dtype=torch.float16, device="cuda") for n in Ns]
+        descs2 = [{"Y": Ys2[i], "W_int4": dev(Ws[i]), "scales": dev(Ss[i]), "bias": None, "N": Ns[i]} for i in range(3)]
+        assert cuda.linear_int4_fused(dev(X), descs2, M, K) == 0
+        torch.cuda.synchronize()
+        assert cuda.last_linear_path() == TC
+        for i in range(3):
+            assert rel_err(Ys2[i].float().cpu().numpy(), oracle.linear_int4_f64(X.astype(np.float32), Ws[i], Ss[i])) <= 2e-3
     for i in range(3):
         ref = oracle.linear_int4_f64(X.astype(np.float32), Ws[i], Ss[i])
         assert rel_err(Ys[i].float().cpu().numpy(), ref) <= 2e-3
@@ -422,15 +453,17 @@ def test_prefill_gemm_wait_runs_out_and_is_reported(cuda):
     X, W, S, _ = synth_linear(M, K, N, seed=9)
     Xd, Wd, Sd = dev(X), dev(W), dev(S)
     Y = torch.zeros((M, N), dtype=torch.float16, device="cuda")
-    good, path = run_linear(cuda, X, W, S, out_dtype=torch.float16)
+    good, path = run_linear(cuda, X, W, S, out_dtype=torch.float16, path=GEMM)
     assert path == GEMM
     cuda.set_wait_hooks(8_000_000, 1)
+    cuda.set_linear_path(GEMM)
     try:
         assert cuda.linear_int4(Y, Xd, Wd, Sd, None, M, N, K) == 0
         torch.cuda.synchronize()
     finally:
         cuda.set_wait_hooks(0, -1)
+        cuda.set_linear_path(0)
     assert cuda.device_status(0) == _lib.ERR_DEVICE_TIMEOUT
     assert cuda.device_status(0) == 0
-    again, _ = run_linear(cuda, X, W, S, out_dtype=torch.float16)
+    again, _ = run_linear(cuda, X, W, S, out_dtype=torch.float16, path=GEMM)
     assert np.array_equal(again, good)

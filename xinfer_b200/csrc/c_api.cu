@@ -20,6 +20,7 @@ constexpr int kMaxDevices = 64;
 constexpr int kCounterCapacity = 8192;
 constexpr size_t kSamplingScratchBytes = 4u << 20;  // rows * chunks * 16 B
 constexpr size_t kGemmPartialBytes = 96u << 20;     // K-split partials of the prefill GEMM
+constexpr int64_t kSliceRowsMax = 128;             // up to here M > 32 runs as 32-row slices of the decode kernel
 
 struct DeviceCtx {
     bool ready = false;
@@ -86,6 +87,28 @@ int run_linear(xinfer_stream_t s, const void* x, xb::ActType in, bool out_f32, c
     int rc = get_ctx(&c);
     if (rc != XINFER_OK) return rc;
     cudaStream_t stream = static_cast<cudaStream_t>(s);
+    if (c->forced_path != 2 && c->forced_path != 3 && in == xb::ActType::F16 && m > 32 && m <= kSliceRowsMax &&
+        xb::tc_eligible(x, proj, num, swiglu, 32, k, group_size)) {
+        // 33 .. 128 rows: slices of 32 rows through the decode kernel (the reference's association, and cheaper than a
+        // 256-row GEMM tile that would be mostly padding: gate-sized projection 18 us per slice against 88 us)
+        const int cnt = swiglu ? 2 : num;
+        const size_t ybytes = out_f32 ? 4 : 2;
+        for (int64_t r0 = 0; r0 < m; r0 += 32) {
+            xb::TcProj sl[4];
+            for (int i = 0; i < cnt; ++i) {
+                sl[i] = proj[i];
+                const int64_t ld = proj[i].ldy > 0 ? proj[i].ldy : proj[i].n;
+                if (sl[i].y) sl[i].y = static_cast<char*>(sl[i].y) + static_cast<size_t>(r0) * ld * ybytes;
+            }
+            const int64_t rows = m - r0 < 32 ? m - r0 : 32;
+            const int r = xb::tc_launch(stream, static_cast<const char*>(x) + static_cast<size_t>(r0) * k * 2, sl, num, swiglu, out_f32,
+                                        rows, k, c->num_sms, c->workspace, c->counters, kCounterCapacity, c->status);
+            if (r == -1) return fail_cuda(cudaGetLastError());
+            if (r != 0) return XINFER_ERR_INVALID_ARGUMENT;
+        }
+        g_last_path = 1;
+        return XINFER_OK;
+    }
     if (c->forced_path != 2 && in == xb::ActType::F16 && xb::gemm_eligible(x, proj, num, swiglu, m, k, group_size)) {
         // more than 32 rows (prefill chunks): the compute-bound tcgen05 GEMM
         // scratch for K splits of the GEMM: taken once per device, outside any stream capture (a failed or refused
