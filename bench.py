@@ -980,7 +980,9 @@ def step_reference_arm(args):
     val = B / step_s
     line = {"impl": "reference", "metric": "accepted_tok_per_s", "value": val, "unit": "tok/s", "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_s * 1e3, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "int4 weights, fp32 accumulate", "data": "synthetic",
+            # (the same one batch-B job at every N, as the N-split arm it stands beside; replicas: N such jobs)
+            "scaling": "strong" if (args.gpus > 1 and args.parallel == "tp") else "weak", "vs_baseline": None,
+            "dtype": "int4 weights, fp32 accumulate", "data": "synthetic",
             "config": {"workload": f"27B-shape hybrid ({args.layers} layers: Gated-DeltaNet + full attention, hidden 5120, "
                                    f"FFN 17408, vocab 151936, INT4-G128), MTP k={k}, batch {B}, context {args.context}, greedy; "
                                    f"one step = {k} MTP draft passes + one {B * (k + 1)}-row verify pass + acceptance + commit",
