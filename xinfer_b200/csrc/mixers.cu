@@ -258,13 +258,14 @@ constexpr int kAttnStages = 2;  // the loop below is written for exactly two slo
 constexpr int kAttnThreads = 256;
 constexpr int kAttnLd = 264;  // padded row of 256 halves (528 B): conflict-free ldmatrix
 constexpr int kAttnRows = 32;
-constexpr int kAttnSpLd = 41;  // odd row pitch: the softmax threads (4 rows x 8 key parts per warp) read conflict-free
+constexpr int kAttnSpLd = 36;  // row pitch (floats) of the score planes: 2 * 36 = 8 mod 32 makes the MMA threads' stores
+                               // conflict-free, 144-byte rows let a softmax thread fetch its four keys with one 16-byte load
 
 struct AttnSmem {
     __half q[kAttnRows][kAttnLd];
     __half k[kAttnStages][kAttnChunk][kAttnLd];
     __half v[kAttnStages][kAttnChunk][kAttnLd];
-    float sp[4][kAttnChunk][kAttnSpLd];  // S^T partial sums over the four dim quarters, [key][row]
+    float sp[4][kAttnRows][kAttnSpLd];  // score partial sums over the four dim quarters, [query row][key]
     __half p[kAttnRows][kAttnChunk + 8];
     float row_max[kAttnRows];   // running maximum of scale * log2(e) * score (the softmax runs in base 2)
     float row_sum[kAttnRows];
@@ -403,14 +404,15 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_split_kernel(float* part
                     mma16816(s_acc[nt], afr, qf[ks][nt]);
             }
             const int g4 = lane >> 2, t4 = lane & 3;
-            float* sp0 = &sm.sp[kq][kt * 16 + g4][t4 * 2];
+            float* sp0 = &sm.sp[kq][t4 * 2][kt * 16 + g4];
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt)
                 {
-                    sp0[nt * 8] = s_acc[nt][0];
-                    sp0[nt * 8 + 1] = s_acc[nt][1];
-                    sp0[8 * kAttnSpLd + nt * 8] = s_acc[nt][2];
-                    sp0[8 * kAttnSpLd + nt * 8 + 1] = s_acc[nt][3];
+                    // fragment element e: key g4 + 8 (e >> 1), query row 8 nt + 2 t4 + (e & 1)
+                    sp0[(nt * 8) * kAttnSpLd] = s_acc[nt][0];
+                    sp0[(nt * 8 + 1) * kAttnSpLd] = s_acc[nt][1];
+                    sp0[(nt * 8) * kAttnSpLd + 8] = s_acc[nt][2];
+                    sp0[(nt * 8 + 1) * kAttnSpLd + 8] = s_acc[nt][3];
                 }
         }
         __syncthreads();
@@ -423,11 +425,21 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_split_kernel(float* part
             const long long key0 = static_cast<long long>(c) * kAttnChunk + part * 4;
             float sc[4];
             float mx = -INFINITY;
+            {
+                // this thread's four keys of its row, one 16-byte load per dim quarter
+                const float4 q0 = *reinterpret_cast<const float4*>(&sm.sp[0][r][part * 4]);
+                const float4 q1 = *reinterpret_cast<const float4*>(&sm.sp[1][r][part * 4]);
+                const float4 q2 = *reinterpret_cast<const float4*>(&sm.sp[2][r][part * 4]);
+                const float4 q3 = *reinterpret_cast<const float4*>(&sm.sp[3][r][part * 4]);
+                sc[0] = (q0.x + q1.x) + (q2.x + q3.x);
+                sc[1] = (q0.y + q1.y) + (q2.y + q3.y);
+                sc[2] = (q0.z + q1.z) + (q2.z + q3.z);
+                sc[3] = (q0.w + q1.w) + (q2.w + q3.w);
+            }
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 const bool vis = (r < nrows) && (key0 + j < limit) && (key0 + j < total_keys);
-                const int kk = part * 4 + j;
-                sc[j] = vis ? ((sm.sp[0][kk][r] + sm.sp[1][kk][r]) + (sm.sp[2][kk][r] + sm.sp[3][kk][r])) * scale2 : -INFINITY;
+                sc[j] = vis ? sc[j] * scale2 : -INFINITY;
                 mx = fmaxf(mx, sc[j]);
             }
             mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
