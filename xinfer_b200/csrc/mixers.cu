@@ -488,12 +488,18 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_split_kernel(float* part
                     o_acc[mi][nt][3] *= a1;
                 }
             }
+            // P^T as B fragments: one ldmatrix.x4 per 8-row tile fetches the chunk's 32 keys (both 16-key steps)
+            uint32_t pall[NT][4];
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) ldmatrix_x4(pall[nt], &sm.p[nt * 8 + (lane & 7)][(lane >> 3) * 8]);
 #pragma unroll
             for (int ks = 0; ks < kAttnChunk / 16; ++ks) {
                 uint32_t pfr[NT][2];
 #pragma unroll
-                for (int nt = 0; nt < NT; ++nt)
-                    ldmatrix_x2(pfr[nt], &sm.p[nt * 8 + (lane & 7)][ks * 16 + ((lane >> 3) & 1) * 8]);
+                for (int nt = 0; nt < NT; ++nt) {
+                    pfr[nt][0] = pall[nt][2 * ks];
+                    pfr[nt][1] = pall[nt][2 * ks + 1];
+                }
 #pragma unroll
                 for (int mi = 0; mi < 2; ++mi) {
                     // A = V^T: matrix j = lane >> 3 of the four 8x8 blocks is (dims + 8 (j & 1), keys + 8 (j >> 1)),
