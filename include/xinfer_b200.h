@@ -439,6 +439,36 @@ XINFER_EXPORT int xinfer_spec_decoder_set_sampling(xinfer_spec_decoder* d, float
  * but runs at the decode kernels' row count.  Synchronous; one GPU only. */
 XINFER_EXPORT int xinfer_spec_decoder_prefill(xinfer_spec_decoder* d, xinfer_stream_t stream, const int64_t* prompt_host,
                                               int64_t T);
+/* The device side of Engine::generate's speculative loop (src/runtime/engine.cpp:262-560) for `batch` prompts of one
+ * length T (host, [batch][T]): the reference's argument checks (max_new_tokens > 0, temperature >= 0, top_p == 1,
+ * prompt + completion within the cache; messages in xinfer_spec_decoder_error), reset to the empty context, prefill,
+ * then steps until every sequence has stopped.  A sequence stops on eos_token_id / im_end_token_id (a negative id
+ * matches nothing; the stop token is not returned; finish 0 = "stop") or with max_new_tokens tokens (finish 1 =
+ * "length"; also when the cache runs out).  temperature > 0 runs the stochastic step (the reference's engine
+ * refuses it, engine.cpp:285-293; its acceptance rule exists in src/ops/sampling.cpp and is what the step applies).
+ * token_ids_out is [batch][max_new_tokens], generated_out and finish_out are [batch]; stats may be NULL.
+ * Sequences run in lockstep; a stopped one keeps its lane until the last has finished.  Uses the captured graph
+ * when there is one.  Synchronous; one GPU only. */
+typedef struct xinfer_generation_config {   /* GenerationConfig, include/xinfer/engine.h:17-25 */
+    int32_t max_new_tokens;
+    float temperature;          /* 0 = greedy */
+    float top_p;                /* must be 1 */
+    int64_t eos_token_id;
+    int64_t im_end_token_id;
+    uint64_t seed;              /* Philox seed of the stochastic step */
+} xinfer_generation_config;
+typedef struct xinfer_generation_stats {    /* the counters of GenerationResult, include/xinfer/engine.h:44-57 */
+    int64_t prompt_tokens;      /* per sequence */
+    int64_t generated_tokens;   /* over all sequences */
+    int64_t steps;
+    double time_to_first_token_sec;   /* reset + prefill + the first step */
+    double decode_tokens_per_sec;     /* tokens kept after the first step / time after it, all sequences */
+    double total_time_sec;
+} xinfer_generation_stats;
+XINFER_EXPORT int xinfer_spec_decoder_generate(xinfer_spec_decoder* d, xinfer_stream_t stream, const int64_t* prompt_host,
+                                               int64_t T, const xinfer_generation_config* config, int64_t* token_ids_out,
+                                               int32_t* generated_out, int32_t* finish_out,
+                                               xinfer_generation_stats* stats);
 /* Replaces a decoder's (synthetic) weights by the tensors of an artifact, under the section names of the reference's
  * loader (src/targets/qwen3_8_27b/weights.cpp:358-640); under tensor parallelism every rank loads its own row range of
  * each split projection.  The MTP head's tensors (`mtp.fc.weight`, `mtp.pre_fc_norm_{embedding,hidden}.weight`,

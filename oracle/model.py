@@ -171,6 +171,30 @@ class OracleModel:
         seq_state["cur_tok"] = tokens[-1]
         seq_state["h_last"] = h_prev.copy()
 
+    def generate(self, seq_state, prompt, max_new_tokens, eos_token_id=-1, im_end_token_id=-1, max_seq=None):
+        """The speculative generate loop of one sequence (src/runtime/engine.cpp:400-525) over (k+1)-row steps:
+        prefill, then steps; a stop token ends the sequence and is not returned ("stop"), max_new_tokens tokens end
+        it with "length" (tokens a step emits beyond that are dropped), and so does a full cache.
+        Returns (token ids, finish reason)."""
+        self.prefill(seq_state, prompt)
+        out, finish = [], "length"
+        while len(out) < max_new_tokens:
+            if max_seq is not None and seq_state["ctx"] + self.k + 1 > max_seq:
+                break
+            emitted, _ = self.step(seq_state)
+            done = False
+            for t in emitted:
+                if (eos_token_id >= 0 and t == eos_token_id) or (im_end_token_id >= 0 and t == im_end_token_id):
+                    finish, done = "stop", True
+                    break
+                out.append(int(t))
+                if len(out) == max_new_tokens:
+                    done = True
+                    break
+            if done:
+                break
+        return out, finish
+
     def greedy_continuation(self, seq_state, n):
         """The n tokens the target itself would emit after cur_tok (state is left untouched)."""
         import copy

@@ -221,6 +221,56 @@ def test_prefill_from_a_prompt_then_steps(small):
     dec.reset(30, seed=3)   # leave the shared decoder as the other tests expect it
 
 
+def test_generate_loop_against_the_oracle():
+    """xinfer_spec_decoder_generate against the oracle's restatement of the reference's generate loop: a prompt of 11
+    tokens per sequence, then tokens until max_new_tokens ("length") or a stop token ("stop", not returned).  Run
+    eagerly, from the captured graph (the first step after a prefill whose last chunk is short must run eagerly), and
+    with a stop token that ends sequence 0 early while sequence 1 runs on with lane 0 parked."""
+    import copy
+    from xinfer_b200 import _lib
+    from xinfer_b200.spec import Shape, SpecDecoder
+    shape_cfg = Shape(hidden_size=1024, intermediate_size=2048, num_hidden_layers=4, num_attention_heads=4,
+                      num_key_value_heads=2, vocab_size=4096 + 512, linear_num_v_heads=6, linear_num_k_heads=2)
+    B, k, T, cap = 2, 3, 11, 9
+    dec = SpecDecoder(shape_cfg, batch=B, k=k, max_seq=96, seed=5)
+    dec.reset(0, seed=9)
+    model = pull_model(dec, shape_cfg, k)
+    seqs0 = pull_state(dec, model, shape_cfg, B, dec.max_seq)
+    prompt = np.random.default_rng(8).integers(0, shape_cfg.vocab_size, size=(B, T)).astype(np.int64)
+    want = [model.generate(copy.deepcopy(seqs0[b]), prompt[b], cap) for b in range(B)]
+    assert all(f == "length" and len(t) == cap for t, f in want)
+
+    def check(results, expect):
+        for b in range(B):
+            assert results[b].token_ids == expect[b][0], (b, results[b].token_ids, expect[b][0])
+            assert results[b].finish_reason == expect[b][1] and results[b].generated_tokens == len(expect[b][0])
+            assert results[b].prompt_tokens == T
+
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        got = dec.generate(prompt, max_new_tokens=cap, seed=9)
+        check(got, want)
+        assert got[0].steps >= 3 and got[0].total_time_sec > 0 and got[0].decode_tokens_per_sec > 0
+        dec.reset(20, seed=3)
+        dec.capture(stream)
+        assert dec.info(3) == 1
+        check(dec.generate(prompt, max_new_tokens=cap, seed=9), want)
+        # a stop token: the fifth token of sequence 0
+        eos = want[0][0][4]
+        want_eos = [model.generate(copy.deepcopy(seqs0[b]), prompt[b], cap, eos_token_id=eos) for b in range(B)]
+        assert want_eos[0][1] == "stop" and len(want_eos[0][0]) <= 4
+        check(dec.generate(prompt, max_new_tokens=cap, eos_token_id=eos, seed=9), want_eos)
+        check(dec.generate(prompt, max_new_tokens=cap, im_end_token_id=eos, seed=9), want_eos)
+        # the reference's argument checks
+        for bad in ({"max_new_tokens": 0}, {"temperature": -1.0}, {"top_p": 0.9}, {"max_new_tokens": 96}):
+            with pytest.raises(_lib.XInferError):
+                dec.generate(prompt, **bad)
+        # a changed sampling mode is refused once the step is captured
+        with pytest.raises(_lib.XInferError):
+            dec.generate(prompt, max_new_tokens=cap, temperature=0.7)
+    dec.close()
+
+
 def test_stochastic_drafting_and_acceptance_inside_the_step():
     """temperature 0.7: the step draws its draft tokens from the head's distribution and applies the reference's
     stochastic rule with Philox uniforms of (seed, step index); the oracle regenerates the same uniforms, samples with

@@ -20,6 +20,7 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include <chrono>
 #include <new>
 #include <string>
 #include <vector>
@@ -850,7 +851,9 @@ int xinfer_spec_decoder_step(xinfer_spec_decoder* d, xinfer_stream_t stream) {
     }
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     int rc;
-    if (d->graph_exec) rc = cudaGraphLaunch(d->graph_exec, s) == cudaSuccess ? XINFER_OK : XINFER_ERR_CUDA;
+    // The graph holds the previous pass's row count as a constant (k + 1): right after a prefill whose last chunk was
+    // shorter, one step runs eagerly.
+    if (d->graph_exec && d->prev_rows == d->k + 1) rc = cudaGraphLaunch(d->graph_exec, s) == cudaSuccess ? XINFER_OK : XINFER_ERR_CUDA;
     else rc = enqueue_step(d, s);
     if (rc >= 0) d->ctx_upper += d->k + 1;
     return rc;
@@ -1012,6 +1015,93 @@ int xinfer_spec_decoder_prefill(xinfer_spec_decoder* d, xinfer_stream_t stream, 
     cudaFree(prompt);
     if (rc == XINFER_OK) d->ctx_upper = T - 1;
     return rc;
+}
+
+// The device side of Engine::generate's speculative loop (src/runtime/engine.cpp:262-560) for a batch of prompts of one
+// length: argument checks in the reference's order and words, reset to the empty context, prefill, then steps until
+// every sequence has stopped.  A sequence stops on eos_token_id / im_end_token_id (the stop token is not returned,
+// finish reason 0 = "stop", engine.cpp:452-468) or when it holds max_new_tokens tokens (1 = "length"); tokens a step
+// emits beyond that are dropped, where the reference shortens its last draft instead (engine.cpp:420).  The sequences
+// run in lockstep: one that has stopped keeps its lane, its context length is put back after every step so that it
+// cannot run into the end of the cache while the others finish.  Uses the captured graph when there is one.
+int xinfer_spec_decoder_generate(xinfer_spec_decoder* d, xinfer_stream_t stream, const int64_t* prompt_host, int64_t T,
+                                 const xinfer_generation_config* g, int64_t* token_ids_out, int32_t* generated_out,
+                                 int32_t* finish_out, xinfer_generation_stats* stats) {
+    if (!d || !g || !token_ids_out || !generated_out || !finish_out) return XINFER_ERR_INVALID_ARGUMENT;
+    const int B = d->batch, R = d->k + 1;
+    if (g->max_new_tokens <= 0) { d->error = "Invalid max_new_tokens: must be greater than 0"; return XINFER_ERR_INVALID_ARGUMENT; }
+    if (g->temperature < 0.f) { d->error = "Invalid temperature: must be >= 0.0"; return XINFER_ERR_INVALID_ARGUMENT; }
+    if (g->top_p != 1.0f) { d->error = "Nucleus (top-p) sampling is not yet supported."; return XINFER_ERR_INVALID_ARGUMENT; }
+    if (!prompt_host || T < 1) { d->error = "empty prompt"; return XINFER_ERR_INVALID_ARGUMENT; }
+    if (T + g->max_new_tokens + d->k > d->max_seq) {
+        d->error = "This model's maximum context length is " + std::to_string(d->max_seq - d->k) + " tokens. However, you requested " +
+                   std::to_string(T + g->max_new_tokens) + " tokens (" + std::to_string(T) + " in the messages, " +
+                   std::to_string(g->max_new_tokens) + " in the completion).";
+        return XINFER_ERR_INVALID_ARGUMENT;
+    }
+    if (g->temperature != d->temperature || (g->temperature > 0.f && g->seed != d->sample_seed)) {
+        int rc = xinfer_spec_decoder_set_sampling(d, g->temperature, g->seed);
+        if (rc < 0) return rc;
+    }
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const auto t0 = std::chrono::steady_clock::now();
+    int rc = xinfer_spec_decoder_reset(d, 0, g->seed);
+    if (rc < 0) return rc;
+    rc = xinfer_spec_decoder_prefill(d, stream, prompt_host, T);
+    if (rc < 0) return rc;
+    const int64_t cap = g->max_new_tokens;
+    std::vector<int64_t> emitted(static_cast<size_t>(B) * R);
+    std::vector<int> counts(B), ctx(B, static_cast<int>(T - 1));
+    std::vector<char> running(B, 1);
+    for (int b = 0; b < B; ++b) { generated_out[b] = 0; finish_out[b] = 1; }
+    int n_running = B;
+    int64_t steps = 0, first_step_tokens = 0;
+    auto t_first = t0;
+    while (n_running > 0) {
+        int64_t top = 0;
+        for (int b = 0; b < B; ++b) top = ctx[b] > top ? ctx[b] : top;
+        d->ctx_upper = top;                       // exact: the host has read every step's counts
+        if (top + R > d->max_seq) break;          // the reference's "Context length limit reached": the rest end on "length"
+        rc = xinfer_spec_decoder_step(d, stream);
+        if (rc < 0) return rc;
+        rc = xinfer_spec_decoder_results(d, stream, emitted.data(), counts.data());
+        if (rc < 0) return rc;
+        ++steps;
+        for (int b = 0; b < B; ++b) {
+            if (!running[b]) {                    // a parked lane: put its context length back
+                if (cudaMemcpyAsync(d->ctx + b, &ctx[b], sizeof(int), cudaMemcpyHostToDevice, s) != cudaSuccess) return XINFER_ERR_CUDA;
+                continue;
+            }
+            ctx[b] += counts[b];
+            for (int j = 0; j < counts[b] && running[b]; ++j) {
+                const int64_t tok = emitted[static_cast<size_t>(b) * R + j];
+                if ((g->eos_token_id >= 0 && tok == g->eos_token_id) || (g->im_end_token_id >= 0 && tok == g->im_end_token_id)) {
+                    finish_out[b] = 0;
+                    running[b] = 0;
+                } else {
+                    token_ids_out[static_cast<size_t>(b) * cap + generated_out[b]++] = tok;
+                    if (steps == 1) ++first_step_tokens;
+                    if (generated_out[b] == cap) running[b] = 0;   // finish reason stays "length"
+                }
+            }
+            if (!running[b]) --n_running;
+        }
+        if (steps == 1) t_first = std::chrono::steady_clock::now();
+    }
+    if (cudaStreamSynchronize(s) != cudaSuccess) return XINFER_ERR_CUDA;
+    if (stats) {
+        const auto t1 = std::chrono::steady_clock::now();
+        int64_t total = 0;
+        for (int b = 0; b < B; ++b) total += generated_out[b];
+        stats->prompt_tokens = T;
+        stats->steps = steps;
+        stats->generated_tokens = total;
+        stats->time_to_first_token_sec = std::chrono::duration<double>(t_first - t0).count();
+        stats->total_time_sec = std::chrono::duration<double>(t1 - t0).count();
+        const double dt = std::chrono::duration<double>(t1 - t_first).count();
+        stats->decode_tokens_per_sec = steps > 1 && dt > 0 ? static_cast<double>(total - first_step_tokens) / dt : 0.0;
+    }
+    return XINFER_OK;
 }
 
 // Replaces the decoder's synthetic weights by the tensors of a `.xinfer` artifact, under the section names the

@@ -40,6 +40,33 @@ class Shape:
 _DTYPES = {"w": np.uint8, "s": np.float16}
 
 
+class GenerationConfig(C.Structure):
+    """``xinfer_generation_config``."""
+    _fields_ = [("max_new_tokens", C.c_int32), ("temperature", C.c_float), ("top_p", C.c_float),
+                ("eos_token_id", C.c_int64), ("im_end_token_id", C.c_int64), ("seed", C.c_uint64)]
+
+
+class GenerationStats(C.Structure):
+    """``xinfer_generation_stats``."""
+    _fields_ = [("prompt_tokens", C.c_int64), ("generated_tokens", C.c_int64), ("steps", C.c_int64),
+                ("time_to_first_token_sec", C.c_double), ("decode_tokens_per_sec", C.c_double),
+                ("total_time_sec", C.c_double)]
+
+
+@dataclass
+class GenerationResult:
+    """The token-level fields of the reference's ``GenerationResult`` (include/xinfer/engine.h:44-57) for one
+    sequence; text and tokenizer fields are the caller's."""
+    token_ids: list
+    prompt_tokens: int
+    generated_tokens: int
+    finish_reason: str
+    time_to_first_token_sec: float
+    decode_tokens_per_sec: float
+    total_time_sec: float
+    steps: int
+
+
 class SpecDecoder:
     def __init__(self, shape: Shape, batch: int = 8, k: int = 3, max_seq: int = 8448, seed: int = 0, tp=None):
         """``tp``: a connected ``xinfer_b200.tp.TpGroup`` for the N-split step (every rank creates its decoder with the
@@ -79,6 +106,33 @@ class SpecDecoder:
         code = lib().xinfer_spec_decoder_prefill(self._h, C.c_void_p(s.cuda_stream), p.ctypes.data_as(C.c_void_p), p.shape[1])
         if code != 0:
             raise _lib.XInferError(code, "spec_decoder_prefill: " + self._err())
+
+    def generate(self, prompt, max_new_tokens: int = 256, temperature: float = 0.0, top_p: float = 1.0,
+                 eos_token_id: int = -1, im_end_token_id: int = -1, seed: int = 0, stream=None):
+        """The speculative generate loop for ``prompt`` (int64 [batch][T]) with the fields of the reference's
+        ``GenerationConfig`` (include/xinfer/engine.h:17-25): reset, prefill, steps until every sequence has met a stop
+        token or holds ``max_new_tokens`` tokens (``xinfer_spec_decoder_generate``).  Returns one ``GenerationResult``
+        per sequence; the timing fields describe the whole batch."""
+        p = np.ascontiguousarray(prompt, np.int64)
+        assert p.ndim == 2 and p.shape[0] == self.batch
+        cfg = GenerationConfig(int(max_new_tokens), float(temperature), float(top_p), int(eos_token_id),
+                               int(im_end_token_id), int(seed))
+        cap = max(int(max_new_tokens), 1)
+        toks = np.full((self.batch, cap), -1, np.int64)
+        n = np.zeros(self.batch, np.int32)
+        fin = np.zeros(self.batch, np.int32)
+        st = GenerationStats()
+        s = stream if stream is not None else torch.cuda.current_stream()
+        code = lib().xinfer_spec_decoder_generate(self._h, C.c_void_p(s.cuda_stream), p.ctypes.data_as(C.c_void_p), p.shape[1],
+                                                  C.byref(cfg), toks.ctypes.data_as(C.c_void_p), n.ctypes.data_as(C.c_void_p),
+                                                  fin.ctypes.data_as(C.c_void_p), C.byref(st))
+        if code != 0:
+            raise _lib.XInferError(code, "spec_decoder_generate: " + self._err())
+        return [GenerationResult(token_ids=toks[b, :n[b]].tolist(), prompt_tokens=int(st.prompt_tokens),
+                                 generated_tokens=int(n[b]), finish_reason="stop" if fin[b] == 0 else "length",
+                                 time_to_first_token_sec=st.time_to_first_token_sec,
+                                 decode_tokens_per_sec=st.decode_tokens_per_sec, total_time_sec=st.total_time_sec,
+                                 steps=int(st.steps)) for b in range(self.batch)]
 
     def load_artifact(self, reader, verify: bool = True) -> None:
         """Replaces the synthetic weights by the tensors of an open ``xinfer_b200.artifact.ArtifactReader``
