@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the speculative-decode hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload step|gemv|sweep] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload step|gemv|sweep|tp_gemv|prefill|generate] [--impl reference]
 
 Prints ONE JSON line on rank 0.  Workloads:
   step   (default) accepted tokens/s of the 27B-shape speculative decode step: 64-layer random-init
@@ -995,19 +995,73 @@ def step_reference_arm(args):
     print(json.dumps(line), flush=True)
 
 
+def generate_bench(args):
+    """One request batch through `xinfer_spec_decoder_generate` (the reference's Engine::generate loop, device side):
+    `--batch` prompts of `--prompt-len` synthetic tokens, `--max-new` tokens each, on the 27B shape with the step
+    captured as a CUDA graph.  Host buffers in and out; the timers are the call's own (time to first token = reset +
+    prefill + first step, decode tokens/s over the steps after it).  One GPU."""
+    import torch
+    from xinfer_b200 import lib
+    from xinfer_b200.spec import Shape, SpecDecoder
+    torch.cuda.set_device(0)
+    assert lib().xinfer_b200_init(0) == 0, lib().xinfer_last_cuda_error()
+    shape = Shape(num_hidden_layers=args.layers)
+    B, k, T, cap = args.batch, args.k, args.prompt_len, args.max_new
+    dec = SpecDecoder(shape, batch=B, k=k, max_seq=T + cap + 64, seed=0)
+    if args.temperature > 0:
+        dec.set_sampling(args.temperature, 1234)
+    dec.reset(T, seed=0)
+    stream = torch.cuda.Stream()
+    prompt = np.random.default_rng(0).integers(0, shape.vocab_size, size=(B, T)).astype(np.int64)
+    runs = []
+    sampler = ClockSampler(0)
+    with torch.cuda.stream(stream):
+        dec.capture(stream)
+        for i in range(max(1, args.warmup) + max(1, args.steps)):
+            if i == max(1, args.warmup):
+                sampler.start()
+            res = dec.generate(prompt, max_new_tokens=cap, temperature=args.temperature, seed=1234)
+            if i >= max(1, args.warmup):
+                runs.append(res)
+    clocks = sampler.stop()
+    r0 = runs[len(runs) // 2][0]
+    med = lambda f: statistics.median(f(r[0]) for r in runs)
+    generated = sum(x.generated_tokens for x in runs[-1])
+    line = {
+        "metric": "accepted tok/s", "value": med(lambda x: x.decode_tokens_per_sec), "unit": "tok/s", "n_gpus": 1,
+        "steps": len(runs), "warmup": max(1, args.warmup), "ms_per_step": med(lambda x: x.total_time_sec) * 1e3 / max(1, r0.steps),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int4 x fp16, fp32 accumulate",
+        "data": "synthetic", "impl": "ours",
+        "config": {"workload": f"generate: {B} prompts x {T} tokens, {cap} new tokens each, 27B-shape hybrid ({args.layers} layers), "
+                               f"k={k}, temperature {args.temperature}, random-init INT4-G128 weights (no draft is accepted at "
+                               "temperature 0: one token per sequence and step)",
+                   "batch": B, "k": k, "prompt_len": T, "max_new_tokens": cap},
+        "generate": {"time_to_first_token_ms": med(lambda x: x.time_to_first_token_sec) * 1e3,
+                     "total_ms": med(lambda x: x.total_time_sec) * 1e3, "steps_per_request": r0.steps,
+                     "generated_tokens": generated, "finish": sorted({x.finish_reason for x in runs[-1]}),
+                     "prefill_tok_s": B * T / max(1e-9, med(lambda x: x.time_to_first_token_sec)),
+                     "note": "prefill runs k + 1 rows per pass (functional form); the reset that starts a request is inside the first-token time"},
+        "clocks": clocks,
+    }
+    print(json.dumps(line), flush=True)
+    dec.close()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="step", choices=["step", "gemv", "sweep", "tp_gemv", "prefill"])
+    ap.add_argument("--workload", default="step", choices=["step", "gemv", "sweep", "tp_gemv", "prefill", "generate"])
     ap.add_argument("--layers", type=int, default=64)
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--k", type=int, default=3)
     ap.add_argument("--context", type=int, default=8192)
     ap.add_argument("--temperature", type=float, default=0.0,
                     help="step workload: > 0 runs stochastic drafting and the rejection rule (default 0: greedy, the metric's configuration)")
+    ap.add_argument("--prompt-len", type=int, default=64, help="generate workload: prompt tokens per sequence")
+    ap.add_argument("--max-new", type=int, default=64, help="generate workload: tokens to generate per sequence")
     ap.add_argument("--shape", default="gate_up", choices=sorted(LAYER_SHAPES))
     ap.add_argument("--m", "--rows", dest="m", type=int, default=1)  # activation rows M (--rows: torchrun parses --m itself)
     ap.add_argument("--launches", type=int, default=64)
@@ -1035,6 +1089,8 @@ def main():
         return tp_gemv_bench(args)
     if args.workload == "prefill":
         return prefill_bench(args)
+    if args.workload == "generate":
+        return generate_bench(args)
     if args.workload == "sweep":
         sweep(args)
         return
