@@ -1068,7 +1068,9 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--parallel", default="tp", choices=["tp", "replicas"],
                     help="with more than one GPU: the one job N-split over the GPUs (default), or N independent copies")
-    ap.add_argument("--with-replicas", action="store_true", help="tp runs also measure the replica form on the same GPUs")
+    ap.add_argument("--with-replicas", dest="with_replicas", action="store_true", default=True,
+                    help="tp runs also measure, on the same GPUs, N independent replicas and the batch divided by sequence (default)")
+    ap.add_argument("--no-replicas", dest="with_replicas", action="store_false", help="tp runs measure the N-split only")
     args = ap.parse_args()
     if args.impl == "reference":
         # torchrun exports OMP_NUM_THREADS=1 to its workers; the CPU arm is meant to use every host thread,
