@@ -221,6 +221,31 @@ def test_prefill_from_a_prompt_then_steps(small):
     dec.reset(30, seed=3)   # leave the shared decoder as the other tests expect it
 
 
+@pytest.mark.parametrize("batch,k", [(1, 1), (3, 2), (2, 4), (6, 4), (5, 1)])
+def test_other_batch_and_draft_counts(batch, k):
+    """The step at draft counts and batch sizes other than the benchmark's (k = 1, 2, 4; odd batches; 30 verify
+    rows): a free step, a step with every draft forced to the target's own continuation (k accepted), one with the
+    first draft wrong, against the oracle."""
+    from xinfer_b200.spec import Shape, SpecDecoder
+    shape_cfg = Shape(hidden_size=1024, intermediate_size=2048, num_hidden_layers=4, num_attention_heads=4,
+                      num_key_value_heads=2, vocab_size=4096, linear_num_v_heads=6, linear_num_k_heads=2)
+    dec = SpecDecoder(shape_cfg, batch=batch, k=k, max_seq=96, seed=11)
+    dec.reset(17, seed=2)
+    model = pull_model(dec, shape_cfg, k)
+    seqs = pull_state(dec, model, shape_cfg, batch, dec.max_seq)
+    compare_step(dec, model, seqs, shape_cfg, None, tag="free")
+    cont = [model.greedy_continuation(seqs[b], k) for b in range(batch)]
+    acc = compare_step(dec, model, seqs, shape_cfg, cont, tag="accept-all")
+    assert acc == [k] * batch
+    cont = [model.greedy_continuation(seqs[b], k) for b in range(batch)]
+    for b in range(batch):
+        cont[b][0] = (cont[b][0] + 1) % shape_cfg.vocab_size
+    acc = compare_step(dec, model, seqs, shape_cfg, cont, tag="reject-first")
+    assert acc == [0] * batch
+    compare_step(dec, model, seqs, shape_cfg, None, tag="free-after")
+    dec.close()
+
+
 def test_generate_loop_against_the_oracle():
     """xinfer_spec_decoder_generate against the oracle's restatement of the reference's generate loop: a prompt of 11
     tokens per sequence, then tokens until max_new_tokens ("length") or a stop token ("stop", not returned).  Run
