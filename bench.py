@@ -775,6 +775,8 @@ def step_bench(args):
         dec = SpecDecoder(shape, batch=B, k=k, max_seq=ctx0 + 1024, seed=rank)
         if args.temperature > 0:
             dec.set_sampling(args.temperature, 12345 + rank)   # stochastic drafting + rejection rule (one GPU per job)
+            if args.top_p < 1.0:
+                dec.set_top_p(args.top_p)
         dec.reset(ctx0, seed=rank)
     stream = torch.cuda.Stream()
     steps, warm = args.steps, max(3, args.warmup)
@@ -917,7 +919,7 @@ def step_bench(args):
         "dtype": "int4 weights x fp16 activations, fp32 accumulate", "data": "synthetic",
         "config": {"workload": f"27B-shape hybrid ({args.layers} layers: Gated-DeltaNet + full attention, hidden 5120, "
                                f"FFN 17408, vocab 151936, INT4-G128), MTP k={k}, batch {B}, context {ctx0}, "
-                               + ("greedy; " if args.temperature <= 0 or use_tp else f"stochastic at T={args.temperature}; ") +
+                               + ("greedy; " if args.temperature <= 0 or use_tp else f"stochastic at T={args.temperature}" + (f", top-p {args.top_p}" if args.top_p < 1.0 else "") + "; ") +
                                f"one step = {k} MTP draft passes + one {B * (k + 1)}-row verify pass + acceptance + "
                                f"commit, replayed as one CUDA graph",
                    "layers": args.layers, "batch": B, "k": k, "context": ctx0,
@@ -1010,6 +1012,8 @@ def generate_bench(args):
     dec = SpecDecoder(shape, batch=B, k=k, max_seq=T + cap + 64, seed=0)
     if args.temperature > 0:
         dec.set_sampling(args.temperature, 1234)
+        if args.top_p < 1.0:
+            dec.set_top_p(args.top_p)
     dec.reset(T, seed=0)
     stream = torch.cuda.Stream()
     prompt = np.random.default_rng(0).integers(0, shape.vocab_size, size=(B, T)).astype(np.int64)
@@ -1020,7 +1024,7 @@ def generate_bench(args):
         for i in range(max(1, args.warmup) + max(1, args.steps)):
             if i == max(1, args.warmup):
                 sampler.start()
-            res = dec.generate(prompt, max_new_tokens=cap, temperature=args.temperature, seed=1234)
+            res = dec.generate(prompt, max_new_tokens=cap, temperature=args.temperature, top_p=args.top_p, seed=1234)
             if i >= max(1, args.warmup):
                 runs.append(res)
     clocks = sampler.stop()
@@ -1033,7 +1037,7 @@ def generate_bench(args):
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int4 x fp16, fp32 accumulate",
         "data": "synthetic", "impl": "ours",
         "config": {"workload": f"generate: {B} prompts x {T} tokens, {cap} new tokens each, 27B-shape hybrid ({args.layers} layers), "
-                               f"k={k}, temperature {args.temperature}, random-init INT4-G128 weights (no draft is accepted at "
+                               f"k={k}, temperature {args.temperature}, top-p {args.top_p}, random-init INT4-G128 weights (no draft is accepted at "
                                "temperature 0: one token per sequence and step)",
                    "batch": B, "k": k, "prompt_len": T, "max_new_tokens": cap},
         "generate": {"time_to_first_token_ms": med(lambda x: x.time_to_first_token_sec) * 1e3,
@@ -1062,6 +1066,8 @@ def main():
                     help="step workload: > 0 runs stochastic drafting and the rejection rule (default 0: greedy, the metric's configuration)")
     ap.add_argument("--prompt-len", type=int, default=64, help="generate workload: prompt tokens per sequence")
     ap.add_argument("--max-new", type=int, default=64, help="generate workload: tokens to generate per sequence")
+    ap.add_argument("--top-p", dest="top_p", type=float, default=1.0,
+                    help="with --temperature > 0: nucleus sampling on both sides of the rejection rule (default 1: off)")
     ap.add_argument("--shape", default="gate_up", choices=sorted(LAYER_SHAPES))
     ap.add_argument("--m", "--rows", dest="m", type=int, default=1)  # activation rows M (--rows: torchrun parses --m itself)
     ap.add_argument("--launches", type=int, default=64)

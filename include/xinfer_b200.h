@@ -212,6 +212,15 @@ XINFER_EXPORT int xinfer_speculative_accept_reject_batched(xinfer_stream_t s, co
 XINFER_EXPORT int xinfer_sample_tokens(xinfer_stream_t s, const float* logits_dev, int64_t row_stride, int64_t vocab_size,
                                        int rows, float inv_temperature, const float* rand_uniform_dev, int64_t* tokens_out_dev,
                                        float* probs_out_dev);
+/* The same draw from the row's nucleus: the smallest set of highest-probability tokens of softmax(logits *
+ * inv_temperature) whose probabilities reach top_p (ties at the threshold all in), renormalised.  Weights are the
+ * integers rn(exp(s - max) * 2^32), so every sum is exact and order-free; the token is the first, in index order, at which
+ * the running nucleus weight exceeds floor(u * Z_nucleus); probs_out is its weight / Z_nucleus.  0 < top_p <= 1.
+ * GenerationConfig::top_p of the reference (include/xinfer/engine.h:20), which its engine refuses
+ * (src/runtime/engine.cpp:294-303).  Asynchronous; all pointers device memory. */
+XINFER_EXPORT int xinfer_sample_tokens_top_p(xinfer_stream_t s, const float* logits_dev, int64_t row_stride,
+                                             int64_t vocab_size, int rows, float inv_temperature, float top_p,
+                                             const float* uniforms_dev, int64_t* tokens_out_dev, float* probs_out_dev);
 
 /* Philox4x32-10 uniforms in [0,1): out[i] = (word(i&3) of block(i>>2) >> 8) * 2^-24 with counter
  * {lo(i>>2), hi(i>>2), lo(subsequence), hi(subsequence)} and key {lo(seed), hi(seed)}.  No counterpart
@@ -431,6 +440,11 @@ XINFER_EXPORT int xinfer_artifact_load_linear(xinfer_artifact* a, const char* we
  * element batch * k + b * k + i is its acceptance uniform - and the step index lives in device memory, so a replayed
  * graph draws fresh numbers.  Call before capture.  One GPU only. */
 XINFER_EXPORT int xinfer_spec_decoder_set_sampling(xinfer_spec_decoder* d, float temperature, uint64_t seed);
+/* Nucleus sampling inside the stochastic step: with 0 < top_p < 1 (and temperature > 0) the draft tokens are drawn from the
+ * nucleus of the head's distribution (xinfer_sample_tokens_top_p) and the acceptance rule takes the target's probability
+ * inside the target row's own nucleus (zero outside it).  top_p = 1 (default) is the whole distribution.  Call before
+ * capture. */
+XINFER_EXPORT int xinfer_spec_decoder_set_top_p(xinfer_spec_decoder* d, float top_p);
 /* Builds the context from a prompt, tokens[batch][T] on the host (every sequence the same length), starting from the
  * empty context of xinfer_spec_decoder_reset(d, 0, seed): positions 0 .. T-2 go through the target in chunks of k + 1
  * rows with every row kept, the MTP head's KV slots of those positions are filled, the last prompt token becomes the
@@ -440,19 +454,20 @@ XINFER_EXPORT int xinfer_spec_decoder_set_sampling(xinfer_spec_decoder* d, float
 XINFER_EXPORT int xinfer_spec_decoder_prefill(xinfer_spec_decoder* d, xinfer_stream_t stream, const int64_t* prompt_host,
                                               int64_t T);
 /* The device side of Engine::generate's speculative loop (src/runtime/engine.cpp:262-560) for `batch` prompts of one
- * length T (host, [batch][T]): the reference's argument checks (max_new_tokens > 0, temperature >= 0, top_p == 1,
+ * length T (host, [batch][T]): the reference's argument checks (max_new_tokens > 0, temperature >= 0, 0 < top_p <= 1 and top_p < 1 only with temperature > 0,
  * prompt + completion within the cache; messages in xinfer_spec_decoder_error), reset to the empty context, prefill,
  * then steps until every sequence has stopped.  A sequence stops on eos_token_id / im_end_token_id (a negative id
  * matches nothing; the stop token is not returned; finish 0 = "stop") or with max_new_tokens tokens (finish 1 =
  * "length"; also when the cache runs out).  temperature > 0 runs the stochastic step (the reference's engine
- * refuses it, engine.cpp:285-293; its acceptance rule exists in src/ops/sampling.cpp and is what the step applies).
+ * refuses it, engine.cpp:285-293; its acceptance rule exists in src/ops/sampling.cpp and is what the step applies);
+ * top_p < 1 adds nucleus sampling on both sides of that rule (xinfer_spec_decoder_set_top_p).
  * token_ids_out is [batch][max_new_tokens], generated_out and finish_out are [batch]; stats may be NULL.
  * Sequences run in lockstep; a stopped one keeps its lane until the last has finished.  Uses the captured graph
  * when there is one.  Synchronous; one GPU only. */
 typedef struct xinfer_generation_config {   /* GenerationConfig, include/xinfer/engine.h:17-25 */
     int32_t max_new_tokens;
     float temperature;          /* 0 = greedy */
-    float top_p;                /* must be 1 */
+    float top_p;                /* 1 = whole distribution; < 1 needs temperature > 0 */
     int64_t eos_token_id;
     int64_t im_end_token_id;
     uint64_t seed;              /* Philox seed of the stochastic step */

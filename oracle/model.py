@@ -74,6 +74,79 @@ def sample_token(logits, inv_t, u):
     return lo + th * 16 + tok, float(f32(e[th * 16 + tok] / z))
 
 
+def _order_key(s32):
+    """Order-preserving uint32 key of float32 values (negative: all bits flipped; else the sign bit set)."""
+    u = np.ascontiguousarray(s32, np.float32).view(np.uint32)
+    return np.where(u & np.uint32(0x80000000), ~u, u | np.uint32(0x80000000)).astype(np.uint32)
+
+
+def nucleus(logits, inv_t, top_p):
+    """The nucleus of softmax(logits * inv_t) at top_p with the device kernel's integer weights
+    w = rn(exp(s - max) * 2^32), s = logits * inv_t in fp32: the smallest set of highest-s tokens whose weights reach
+    ceil(top_p * Z), all tokens tied with the threshold included.  Returns (keys, weights, threshold key, Z_nucleus)."""
+    import math
+    f32 = np.float32
+    s = (np.asarray(logits, f32) * f32(inv_t)).astype(f32)
+    ms = f32(s.max())
+    e = np.exp((s - ms).astype(f32)).astype(f32)
+    w = np.rint(e.astype(np.float64) * 4294967296.0).astype(np.uint64)
+    key = _order_key(s)
+    z = int(w.sum(dtype=np.uint64))
+    want = math.ceil(float(f32(top_p)) * float(z))
+    target = min(z, 1 if want <= 1 else int(want))
+    uk, inv = np.unique(key, return_inverse=True)
+    sums = np.zeros(len(uk), np.uint64)
+    np.add.at(sums, inv, w)
+    cum = 0
+    thr = int(uk[0])
+    for i in range(len(uk) - 1, -1, -1):
+        cum += int(sums[i])
+        thr = int(uk[i])
+        if cum >= target:
+            break
+    return key, w, thr, cum
+
+
+def sample_token_top_p(logits, inv_t, top_p, u):
+    """One token from the nucleus: the first token, in index order, at which the running nucleus weight exceeds
+    floor(u * Z_nucleus).  Returns (token, probability inside the nucleus)."""
+    import math
+    key, w, thr, z = nucleus(logits, inv_t, top_p)
+    t2 = min(z - 1, max(0, int(math.floor(float(np.float32(u)) * float(z)))))
+    member = key >= np.uint32(thr)
+    cum = np.cumsum(np.where(member, w, np.uint64(0)).astype(np.uint64), dtype=np.uint64)
+    tok = int(np.argmax(member & (cum > np.uint64(t2))))
+    return tok, float(np.float32(float(w[tok]) / float(z)))
+
+
+def accept_reject_top_p(drafts, logits_rows, draft_probs, uniforms, inv_t, top_p):
+    """The reference's stochastic rule (src/ops/sampling.cpp:129-171) with the target's probability taken inside
+    the target row's own nucleus (zero outside it); same result fields as oracle.speculative_accept_reject."""
+    f32 = np.float32
+    n = len(drafts)
+    res = {"num_accepted": 0, "has_rejected_token": False, "bonus_or_resampled_token": -1, "rejected_token": -1}
+    for i in range(n):
+        t = oracle.argmax(logits_rows[i])
+        d = int(drafts[i])
+        p_draft, rr = f32(draft_probs[i]), f32(uniforms[i])
+        if p_draft <= 0:
+            ok = d == t
+        elif d == t and rr <= 0:
+            ok = True
+        else:
+            key, w, thr, z = nucleus(logits_rows[i], inv_t, top_p)
+            p_target = f32(0)
+            if 0 <= d < len(key) and z > 0 and int(key[d]) >= thr:
+                p_target = f32(float(w[d]) / float(z))
+            ok = bool(rr < f32(p_target / p_draft))
+        if ok:
+            res["num_accepted"] += 1
+        else:
+            res.update(has_rejected_token=True, rejected_token=d, bonus_or_resampled_token=t)
+            return res
+    return res
+
+
 class OracleModel:
     def __init__(self, shape, layers, mtp_layer, top, k):
         self.s, self.layers, self.mtp_layer, self.top, self.k = shape, layers, mtp_layer, top, k
@@ -220,7 +293,10 @@ class OracleModel:
             if sampling is None:
                 tok = oracle.argmax(lg)
             else:
-                tok, p = sample_token(lg, sampling["inv_t"], sampling["u_draft"][i])
+                if sampling.get("top_p", 1.0) < 1.0:
+                    tok, p = sample_token_top_p(lg, sampling["inv_t"], sampling["top_p"], sampling["u_draft"][i])
+                else:
+                    tok, p = sample_token(lg, sampling["inv_t"], sampling["u_draft"][i])
                 draft_probs.append(p)
             drafts.append(tok)
             draft_logits.append(lg)
@@ -234,6 +310,9 @@ class OracleModel:
         x, logits = self.target(tokens, ctx, seq_state)
         if sampling is None or draft_override is not None:
             res = oracle.speculative_accept_reject(np.array(drafts, np.int64), logits[:k])
+        elif sampling.get("top_p", 1.0) < 1.0:
+            res = accept_reject_top_p(drafts, logits[:k], np.array(draft_probs, np.float32),
+                                      np.array(sampling["u_accept"], np.float32), float(sampling["inv_t"]), sampling["top_p"])
         else:
             res = oracle.speculative_accept_reject(np.array(drafts, np.int64), logits[:k], np.array(draft_probs, np.float32),
                                                    np.array(sampling["u_accept"], np.float32),

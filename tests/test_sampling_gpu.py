@@ -286,3 +286,75 @@ def test_sample_tokens_against_the_oracle_sampler(cuda):
     freq = np.bincount(tok, minlength=V2) / n
     assert tok.min() >= 0 and tok.max() < V2
     assert np.all(np.abs(freq[top] - p[top]) <= 5 * np.sqrt(p[top] * (1 - p[top]) / n) + 1e-3)
+
+
+def test_sample_tokens_top_p_against_the_oracle(cuda):
+    """Nucleus sampling (vocab 151936, T = 0.7): integer weights make every sum exact, so token and probability must
+    equal the oracle's restatement for every draw (the two sides only have to agree on exp's bits; a token whose draw
+    lands within one part in 10^6 of a boundary of the oracle's cumulative weights is excused and counted).  Properties
+    that need no oracle: the drawn token lies inside the nucleus, top_p = 1 reproduces the whole-distribution
+    probability, a tiny top_p always returns the arg-max with probability 1, and over a small vocabulary the draws
+    follow the renormalised nucleus."""
+    from oracle.model import nucleus, sample_token_top_p
+    B, V, T = 6, 151936, 0.7
+    inv_t = float(np.float32(1.0) / np.float32(T))
+    near, total = 0, 0
+    for seed in range(6):
+        rng = np.random.default_rng(900 + seed)
+        logits = (rng.standard_normal((B, V)) * (1.0 + seed)).astype(np.float32)   # flat to peaked rows
+        u = oracle.philox_uniform(B, 5000 + seed, 0)
+        u[0] = 0.0
+        dl, du = torch.from_numpy(logits).cuda(), torch.from_numpy(u).cuda()
+        for top_p in (0.5, 0.9, 0.999, 1.0):
+            tok = torch.empty(B, dtype=torch.int64, device="cuda")
+            prob = torch.empty(B, dtype=torch.float32, device="cuda")
+            assert cuda.sample_tokens_top_p(dl, du, tok, prob, inv_t, top_p) == 0
+            tok_h, prob_h = tok.cpu().numpy(), prob.cpu().numpy()
+            for b in range(B):
+                key, w, thr, z = nucleus(logits[b], inv_t, top_p)
+                assert int(key[tok_h[b]]) >= thr, (seed, top_p, b)
+                want_t, want_p = sample_token_top_p(logits[b], inv_t, top_p, u[b])
+                total += 1
+                if tok_h[b] != want_t:
+                    # only a draw that sits on a boundary of the cumulative weights may differ
+                    member = key >= np.uint32(thr)
+                    cum = np.cumsum(np.where(member, w, np.uint64(0)).astype(np.uint64), dtype=np.uint64).astype(np.float64)
+                    t2 = np.floor(float(u[b]) * float(z))
+                    assert np.min(np.abs(cum - t2)) <= 1e-6 * z, (seed, top_p, b, tok_h[b], want_t)
+                    near += 1
+                else:
+                    assert abs(prob_h[b] - want_p) <= 1e-5 * want_p
+                if top_p == 1.0:
+                    p64 = oracle.token_prob_f64(logits[b] * np.float32(inv_t), int(tok_h[b]))
+                    assert abs(prob_h[b] - p64) <= 1e-4 * p64 + 2.0 ** -32   # weights are multiples of 2^-32
+    assert near <= max(1, total // 50), (near, total)
+    # a nucleus of one token
+    logits = (np.random.default_rng(3).standard_normal((4, 9000)) * 4).astype(np.float32)
+    u = oracle.philox_uniform(4, 9, 9)
+    tok = torch.empty(4, dtype=torch.int64, device="cuda")
+    prob = torch.empty(4, dtype=torch.float32, device="cuda")
+    assert cuda.sample_tokens_top_p(torch.from_numpy(logits).cuda(), torch.from_numpy(u).cuda(), tok, prob, 1.0, 1e-6) == 0
+    assert tok.cpu().numpy().tolist() == logits.argmax(axis=1).tolist() and np.allclose(prob.cpu().numpy(), 1.0)
+    # distribution over a small vocabulary
+    V2, n, top_p = 4096 + 37, 20000, 0.8
+    l2 = (np.random.default_rng(1).standard_normal(V2) * 2).astype(np.float32)
+    u = oracle.philox_uniform(n, 78, 3)
+    rows = torch.from_numpy(np.broadcast_to(l2, (n, V2)).copy()).cuda()
+    tok = torch.empty(n, dtype=torch.int64, device="cuda")
+    prob = torch.empty(n, dtype=torch.float32, device="cuda")
+    assert cuda.sample_tokens_top_p(rows, torch.from_numpy(u).cuda(), tok, prob, 1.0, top_p) == 0
+    tok = tok.cpu().numpy()
+    key, w, thr, z = nucleus(l2, 1.0, top_p)
+    member = key >= np.uint32(thr)
+    assert member[tok].all()
+    p = np.where(member, w.astype(np.float64), 0.0) / float(z)
+    freq = np.bincount(tok, minlength=V2) / n
+    for t in np.argsort(-p)[:20]:
+        assert abs(freq[t] - p[t]) <= 5 * np.sqrt(p[t] * (1 - p[t]) / n) + 1e-3, (t, freq[t], p[t])
+    # arguments
+    from xinfer_b200 import _lib
+    for bad in (0.0, 1.5, -0.1):
+        with pytest.raises(_lib.XInferError):
+            cuda.sample_tokens_top_p(rows[:2], torch.from_numpy(u[:2]).cuda(), torch.empty(2, dtype=torch.int64, device="cuda"),
+                                     torch.empty(2, dtype=torch.float32, device="cuda"), 1.0, bad)
+

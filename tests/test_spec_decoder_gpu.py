@@ -431,3 +431,55 @@ def test_step_refuses_to_run_past_the_cache(small):
     dec.reset(0, seed=1)
     dec.step()                                                # usable again after a reset
     dec.results()
+
+
+def test_nucleus_sampling_inside_the_step():
+    """temperature 0.7 and top_p 0.8: draft tokens come from the head's nucleus, the rule takes the target's probability
+    inside the target row's nucleus; the oracle regenerates the uniforms and restates both with the same integer
+    weights.  Tokens, counts and contexts must agree, eagerly and from the captured graph, and through generate."""
+    import copy
+    from xinfer_b200.spec import Shape, SpecDecoder
+    shape_cfg = Shape(hidden_size=1024, intermediate_size=2048, num_hidden_layers=4, num_attention_heads=4,
+                      num_key_value_heads=2, vocab_size=4096 + 512, linear_num_v_heads=6, linear_num_k_heads=2)
+    B, k, T, top_p, seed = 2, 3, 0.7, 0.8, 4321
+    inv_t = float(np.float32(1.0) / np.float32(T))
+    for graph in (False, True):
+        dec = SpecDecoder(shape_cfg, batch=B, k=k, max_seq=96, seed=5)
+        dec.set_sampling(T, seed)
+        dec.set_top_p(top_p)
+        dec.reset(20, seed=3)
+        model = pull_model(dec, shape_cfg, k)
+        seqs = pull_state(dec, model, shape_cfg, B, dec.max_seq)
+        stream = torch.cuda.Stream()
+        accepted_total = 0
+        with torch.cuda.stream(stream):
+            for step in range(5):
+                if graph and step == 0:
+                    dec.capture(stream)
+                else:
+                    dec.step()
+                emitted, counts = dec.results()
+                u = oracle.philox_uniform(2 * B * k, seed, step)
+                for b in range(B):
+                    samp = {"inv_t": inv_t, "top_p": top_p, "u_draft": u[b * k:(b + 1) * k],
+                            "u_accept": u[B * k + b * k:B * k + (b + 1) * k]}
+                    want, dbg = model.step(seqs[b], None, samp)
+                    assert counts[b] == len(want) and emitted[b, :counts[b]].tolist() == want, (graph, step, b, emitted[b], want)
+                    accepted_total += dbg["num_accepted"]
+        assert accepted_total > 0
+        from xinfer_b200 import _lib
+        with pytest.raises(_lib.XInferError):
+            dec.set_top_p(0.0)
+        if graph:
+            with pytest.raises(_lib.XInferError):
+                dec.set_top_p(0.5)          # refused once the step is captured
+        else:
+            # generate refuses top_p < 1 without a temperature, and takes it with one
+            prompt = np.random.default_rng(2).integers(0, shape_cfg.vocab_size, size=(B, 7)).astype(np.int64)
+            with torch.cuda.stream(stream):
+                with pytest.raises(_lib.XInferError):
+                    dec.generate(prompt, max_new_tokens=6, top_p=0.9)
+                out = dec.generate(prompt, max_new_tokens=6, temperature=T, top_p=0.9, seed=7)
+            assert all(r.generated_tokens == 6 and r.finish_reason == "length" for r in out)
+        dec.close()
+

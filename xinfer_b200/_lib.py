@@ -123,6 +123,8 @@ SIGNATURES = {
     "xinfer_spec_decoder_prefill": (_i32, [_vp, _vp, _vp, _i64]),
     "xinfer_spec_decoder_set_sampling": (_i32, [_vp, _f32, _u64]),
     "xinfer_spec_decoder_generate": (_i32, [_vp, _vp, _vp, _i64, _vp, _vp, _vp, _vp, _vp]),
+    "xinfer_sample_tokens_top_p": (_i32, [_vp, _vp, _i64, _i64, _i32, _f32, _f32, _vp, _vp, _vp]),
+    "xinfer_spec_decoder_set_top_p": (_i32, [_vp, _f32]),
     "xinfer_sample_tokens": (_i32, [_vp, _vp, _i64, _i64, _i32, _f32, _vp, _vp, _vp]),
     "xinfer_spec_decoder_create_tp": (_i32, [_vp, _i32, _i32, _i64, _u64, _vp, C.POINTER(_vp)]),
     "xinfer_arena_create": (_i32, [_sz, _sz, C.POINTER(_vp)]),

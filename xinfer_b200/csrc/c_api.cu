@@ -378,6 +378,22 @@ int xinfer_sample_tokens(xinfer_stream_t s, const float* logits, int64_t row_str
     return XINFER_OK;
 }
 
+int xinfer_sample_tokens_top_p(xinfer_stream_t s, const float* logits, int64_t row_stride, int64_t vocab, int rows,
+                               float inv_temperature, float top_p, const float* uniforms, int64_t* tokens_out,
+                               float* probs_out) {
+    if (rows <= 0 || vocab <= 0) return XINFER_NOOP_INVALID_SHAPE;
+    if (!logits || !uniforms || !tokens_out || !probs_out || !(inv_temperature > 0.f) || row_stride < vocab ||
+        !(top_p > 0.f) || top_p > 1.f)
+        return XINFER_ERR_INVALID_ARGUMENT;
+    DeviceCtx* c = nullptr;
+    int rc = get_ctx(&c);
+    if (rc != XINFER_OK) return rc;
+    if (xb::nucleus_rows(static_cast<cudaStream_t>(s), logits, row_stride, rows, vocab, inv_temperature, top_p, uniforms, 1,
+                         nullptr, reinterpret_cast<long long*>(tokens_out), probs_out, 1) != 0)
+        return fail_cuda(cudaGetLastError());
+    return XINFER_OK;
+}
+
 int xinfer_speculative_accept_reject(xinfer_stream_t s, const int64_t* draft_tokens, size_t n, const float* logits,
                                      int64_t vocab, const float* draft_probs, const float* rand_uniform,
                                      xinfer_accept_result* out) {

@@ -42,6 +42,22 @@ __device__ __forceinline__ void better(float& v, int& i, float ov, int oi) {
     }
 }
 
+// Top-p bookkeeping (the nucleus kernel further down and the acceptance rule): the order-preserving 32-bit key of a
+// scaled logit, and a token's integer weight rn(exp(s - max) * 2^32).
+__device__ __forceinline__ uint32_t order_key(float x) {
+    const uint32_t u = __float_as_uint(x);
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+// Coarse position of a scaled logit below the row's maximum: 128 buckets per unit, reversed (higher bin = higher
+// logit), everything 32 or more below the maximum in bin 0 (its weight is zero anyway).  Monotone in the logit.
+__device__ __forceinline__ int nucleus_bucket(float scaled, float max_scaled) {
+    const float d = max_scaled - scaled;
+    return d >= 31.99f ? 0 : 4095 - static_cast<int>(d * 128.0f);
+}
+__device__ __forceinline__ unsigned long long nucleus_weight(float scaled, float max_scaled) {
+    return __float2ull_rn(expf(scaled - max_scaled) * 4294967296.0f);
+}
+
 // grid = (chunks, rows).  `row_stride` is the distance between logit rows in floats.
 __global__ void __launch_bounds__(kThreads) logits_partials_kernel(const float* __restrict__ logits, long long row_stride,
                                                                    int vocab, float inv_t, int want_sum,
@@ -192,7 +208,7 @@ __global__ void accept_finish_kernel(const Partial* partials, int chunks, int ns
                                      const float* logits, long long row_stride,
                                      int vocab, float inv_t, const long long* draft_tokens, const float* draft_probs,
                                      const float* uniforms, int num_draft, int rows_per_seq, int bonus_row,
-                                     AcceptOut* out) {
+                                     const Nucleus* nucleus, AcceptOut* out) {
     const int b = blockIdx.x;
     const int lane = threadIdx.x;
     AcceptOut r;
@@ -222,7 +238,18 @@ __global__ void accept_finish_kernel(const Partial* partials, int chunks, int ns
                 accepted = true;
             } else {
                 float p_target = 0.f;
-                if (d >= 0 && d < vocab && se > 0.f) p_target = expf(logits[row * row_stride + d] * inv_t - ms) / se;
+                if (nucleus) {
+                    // the target's distribution cut to its nucleus: zero outside, w / Z_nucleus inside
+                    const Nucleus q = nucleus[row];
+                    if (d >= 0 && d < vocab && q.z > 0) {
+                        const float sv = logits[row * row_stride + d] * inv_t;
+                        if (order_key(sv) >= q.thr_key)
+                            p_target = static_cast<float>(static_cast<double>(nucleus_weight(sv, q.max_scaled)) /
+                                                          static_cast<double>(q.z));
+                    }
+                } else if (d >= 0 && d < vocab && se > 0.f) {
+                    p_target = expf(logits[row * row_stride + d] * inv_t - ms) / se;
+                }
                 accepted = rr < (p_target / p_draft);
             }
         }
@@ -368,6 +395,209 @@ __global__ void __launch_bounds__(kThreads) sample_finish_kernel(const Partial* 
     }
 }
 
+
+// ------------------------------------------------------------------------------------ nucleus (top-p)
+// The nucleus of a row is the smallest set of highest-probability tokens of softmax(l * inv_t) whose probabilities
+// add up to at least top_p; tokens whose scaled logit equals the threshold's are all in.  Sums are integers: a
+// token's weight is w = rn(exp(s - max) * 2^32) with s = l * inv_t in fp32, so every sum is exact, independent of
+// the order of the additions, and the same on any machine that agrees on exp's bits.  The threshold is found by a
+// four-level selection, each level one pass over the row that adds the weights of the still-undecided tokens into a
+// histogram in shared memory and takes the bin in which the sum over all higher bins reaches ceil(top_p * Z): first
+// 4096 buckets over the distance to the row's maximum, then a radix selection on the order-preserving 32-bit key of
+// s (12 + 12 + 8 bits) among the tokens of that bucket.  With a uniform u the kernel also
+// draws the row's token: the first token, in index order, at which the running sum of the nucleus weights exceeds
+// floor(u * Z_nucleus); its probability is w / Z_nucleus.  One block of 1024 threads per row.
+constexpr int kNucThreads = 1024;
+
+__device__ __forceinline__ unsigned long long shfl_u64(unsigned long long v, int src) {
+    return __shfl_sync(0xffffffffu, v, src);
+}
+
+// Warp 0: the bin b (scanning from the highest bin down) at which the running sum first reaches `target`, and the
+// sum of all bins above it.  `nbins` is a multiple of 32; lane l owns the l-th highest block of nbins / 32 bins.
+__device__ void find_bin_desc(const unsigned long long* hist, int nbins, unsigned long long target, int lane,
+                              int* bin_out, unsigned long long* above_out) {
+    const int per = nbins / 32;
+    const int top = nbins - 1 - lane * per;  // highest bin of this lane
+    unsigned long long mine = 0;
+    for (int i = 0; i < per; ++i) mine += hist[top - i];
+    unsigned long long incl = mine;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const unsigned long long up = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += up;
+    }
+    const unsigned reach = __ballot_sync(0xffffffffu, incl >= target);
+    const int who = reach ? __ffs(reach) - 1 : 31;
+    if (lane == who) {
+        unsigned long long cum = incl - mine;
+        int b = top - (per - 1);
+        for (int i = 0; i < per; ++i) {
+            if (cum + hist[top - i] >= target || i == per - 1) { b = top - i; break; }
+            cum += hist[top - i];
+        }
+        *bin_out = b;
+        *above_out = cum;
+    }
+}
+
+__global__ void __launch_bounds__(kNucThreads) nucleus_kernel(const float* logits, long long row_stride, int vocab,
+                                                              float inv_t, float top_p, const float* uniforms, int u_stride,
+                                                              Nucleus* nuc_out, long long* tok_out, float* prob_out,
+                                                              int prob_stride) {
+    __shared__ unsigned long long hist[4096];
+    __shared__ unsigned long long wsum[32];
+    __shared__ float wmax[32];
+    __shared__ unsigned long long s_above, s_z;
+    __shared__ int s_bin;
+    __shared__ float s_ms;
+    const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const float* l = logits + static_cast<long long>(row) * row_stride;
+
+    // maximum of the scaled logits
+    float mx = -INFINITY;
+    for (int i = tid; i < vocab; i += kNucThreads) mx = fmaxf(mx, l[i] * inv_t);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    if (lane == 0) wmax[warp] = mx;
+    for (int i = tid; i < 4096; i += kNucThreads) hist[i] = 0;
+    __syncthreads();
+    if (tid == 0) {
+        float m = wmax[0];
+        for (int w = 1; w < 32; ++w) m = fmaxf(m, wmax[w]);
+        s_ms = m;
+    }
+    __syncthreads();
+    const float ms = s_ms;
+
+    // level 0: total weight and a histogram over the distance to the maximum, 128 buckets per unit of scaled logit
+    // (the keys themselves crowd into a few exponents: their top bits would send every token of the row to a
+    // handful of bins, and shared-memory atomics on one address run one after the other).  The bucket index falls
+    // as the scaled logit grows, so buckets are stored in reverse: a higher bin holds higher logits.
+    unsigned long long z = 0;
+    for (int i = tid; i < vocab; i += kNucThreads) {
+        const float sv = l[i] * inv_t;
+        const unsigned long long w = nucleus_weight(sv, ms);
+        z += w;
+        if (w) atomicAdd(&hist[nucleus_bucket(sv, ms)], w);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) z += shfl_u64(z, lane ^ o);
+    if (lane == 0) wsum[warp] = z;
+    __syncthreads();
+    if (warp == 0) {
+        unsigned long long tot = wsum[lane];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) tot += shfl_u64(tot, lane ^ o);
+        // ceil(top_p * Z), at least one unit of weight and at most all of it
+        double want = ceil(static_cast<double>(top_p) * static_cast<double>(tot));
+        unsigned long long target = want <= 1.0 ? 1ull : static_cast<unsigned long long>(want);
+        if (target > tot) target = tot;
+        if (lane == 0) s_z = target;  // (the target travels in s_z until the nucleus sum replaces it)
+        find_bin_desc(hist, 4096, target, lane, &s_bin, &s_above);
+    }
+    __syncthreads();
+    const int b0 = s_bin;
+    unsigned long long above = s_above;
+    unsigned long long target = s_z - above;
+    __syncthreads();
+
+    // levels 1 to 3: radix selection on the key (12 + 12 + 8 bits) among the tokens of bucket b0 only
+    for (int i = tid; i < 4096; i += kNucThreads) hist[i] = 0;
+    __syncthreads();
+    for (int i = tid; i < vocab; i += kNucThreads) {
+        const float sv = l[i] * inv_t;
+        const unsigned long long w = nucleus_weight(sv, ms);
+        if (w && nucleus_bucket(sv, ms) == b0) atomicAdd(&hist[order_key(sv) >> 20], w);
+    }
+    __syncthreads();
+    if (warp == 0) find_bin_desc(hist, 4096, target, lane, &s_bin, &s_above);
+    __syncthreads();
+    const uint32_t b1 = static_cast<uint32_t>(s_bin);
+    above += s_above;
+    target -= s_above;
+    __syncthreads();
+
+    for (int i = tid; i < 4096; i += kNucThreads) hist[i] = 0;
+    __syncthreads();
+    for (int i = tid; i < vocab; i += kNucThreads) {
+        const float sv = l[i] * inv_t;
+        const uint32_t k = order_key(sv);
+        const unsigned long long w = nucleus_weight(sv, ms);
+        if (w && (k >> 20) == b1 && nucleus_bucket(sv, ms) == b0) atomicAdd(&hist[(k >> 8) & 0xFFFu], w);
+    }
+    __syncthreads();
+    if (warp == 0) find_bin_desc(hist, 4096, target, lane, &s_bin, &s_above);
+    __syncthreads();
+    const uint32_t b2 = static_cast<uint32_t>(s_bin);
+    above += s_above;
+    target -= s_above;
+    __syncthreads();
+
+    for (int i = tid; i < 256; i += kNucThreads) hist[i] = 0;
+    __syncthreads();
+    const uint32_t hi24 = (b1 << 12) | b2;
+    for (int i = tid; i < vocab; i += kNucThreads) {
+        const float sv = l[i] * inv_t;
+        const uint32_t k = order_key(sv);
+        const unsigned long long w = nucleus_weight(sv, ms);
+        if (w && (k >> 8) == hi24 && nucleus_bucket(sv, ms) == b0) atomicAdd(&hist[k & 0xFFu], w);
+    }
+    __syncthreads();
+    if (warp == 0) find_bin_desc(hist, 256, target, lane, &s_bin, &s_above);
+    __syncthreads();
+    const uint32_t thr = (hi24 << 8) | static_cast<uint32_t>(s_bin);
+    const unsigned long long z_nuc = above + s_above + hist[s_bin];
+    if (tid == 0 && nuc_out) {
+        Nucleus q;
+        q.z = z_nuc;
+        q.max_scaled = ms;
+        q.thr_key = thr;
+        nuc_out[row] = q;
+    }
+    if (!uniforms) return;
+
+    // draw: every thread sums the nucleus weights of its contiguous block of token ids
+    const int per = (vocab + kNucThreads - 1) / kNucThreads;
+    const int i0 = tid * per, i1 = min(vocab, i0 + per);
+    unsigned long long mine = 0;
+    for (int i = i0; i < i1; ++i) {
+        const float sv = l[i] * inv_t;
+        if (order_key(sv) >= thr) mine += nucleus_weight(sv, ms);
+    }
+    unsigned long long incl = mine;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const unsigned long long up = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += up;
+    }
+    __syncthreads();  // (wsum is reused)
+    if (lane == 31) wsum[warp] = incl;
+    __syncthreads();
+    unsigned long long before = incl - mine;
+    for (int w = 0; w < warp; ++w) before += wsum[w];
+    double pos = floor(static_cast<double>(uniforms[static_cast<long long>(row) * u_stride]) * static_cast<double>(z_nuc));
+    unsigned long long t2 = pos <= 0.0 ? 0ull : static_cast<unsigned long long>(pos);
+    if (t2 >= z_nuc) t2 = z_nuc - 1;
+    if (mine > 0 && before <= t2 && t2 < before + mine) {
+        unsigned long long cum = before, wtok = 0;
+        int tok = i0;
+        for (int i = i0; i < i1; ++i) {
+            const float sv = l[i] * inv_t;
+            if (order_key(sv) >= thr) {
+                const unsigned long long w = nucleus_weight(sv, ms);
+                cum += w;
+                tok = i;
+                wtok = w;
+                if (cum > t2) break;
+            }
+        }
+        tok_out[row] = tok;
+        prob_out[static_cast<long long>(row) * prob_stride] =
+            static_cast<float>(static_cast<double>(wtok) / static_cast<double>(z_nuc));
+    }
+}
+
 }  // namespace
 
 int sampling_chunks(long long vocab) { return static_cast<int>((vocab + kChunk - 1) / kChunk); }
@@ -393,11 +623,11 @@ int argmax_finish(cudaStream_t stream, const void* partials, int chunks, int nsl
 int accept_finish(cudaStream_t stream, const void* partials, int chunks, int nslices, long long slice_stride,
                   const float* logits, long long row_stride, long long vocab, float inv_temperature,
                   const long long* draft_tokens, const float* draft_probs, const float* uniforms, int batch,
-                  int num_draft, int rows_per_seq, int bonus_row, AcceptOut* out_dev) {
+                  int num_draft, int rows_per_seq, int bonus_row, AcceptOut* out_dev, const Nucleus* nucleus) {
     if (nslices > 1 && draft_probs) return -2;  // the stochastic rule reads the draft token's logit: one slice only
     accept_finish_kernel<<<batch, 32, 0, stream>>>(static_cast<const Partial*>(partials), chunks, nslices, slice_stride, logits,
                                                    row_stride, static_cast<int>(vocab), inv_temperature, draft_tokens,
-                                                   draft_probs, uniforms, num_draft, rows_per_seq, bonus_row, out_dev);
+                                                   draft_probs, uniforms, num_draft, rows_per_seq, bonus_row, nucleus, out_dev);
     return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 
@@ -450,6 +680,14 @@ int sample_finish(cudaStream_t stream, const void* partials, int chunks, const f
     sample_finish_kernel<<<rows, kThreads, 0, stream>>>(static_cast<const Partial*>(partials), chunks, logits, row_stride,
                                                         static_cast<int>(vocab), inv_temperature, uniforms, u_stride, tok_out,
                                                         prob_out, prob_stride);
+    return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+int nucleus_rows(cudaStream_t stream, const float* logits, long long row_stride, int rows, long long vocab,
+                 float inv_temperature, float top_p, const float* uniforms, int u_stride, Nucleus* nucleus_out,
+                 long long* tok_out, float* prob_out, int prob_stride) {
+    if (rows <= 0) return 0;
+    nucleus_kernel<<<rows, kNucThreads, 0, stream>>>(logits, row_stride, static_cast<int>(vocab), inv_temperature, top_p,
+                                                     uniforms, u_stride, nucleus_out, tok_out, prob_out, prob_stride);
     return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 }  // namespace xb

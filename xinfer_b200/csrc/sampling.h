@@ -20,6 +20,14 @@ struct AcceptOut {
     int pad;
 };
 
+// What the acceptance rule needs to know of a row's nucleus (top-p): the order-preserving key of the smallest scaled
+// logit inside it, the row's maximum scaled logit, and the sum of the integer weights rn(exp(s - max) * 2^32) inside.
+struct Nucleus {
+    unsigned long long z;
+    float max_scaled;
+    uint32_t thr_key;
+};
+
 int sampling_chunks(long long vocab);
 size_t sampling_scratch_bytes(long long rows, long long vocab);
 
@@ -33,7 +41,13 @@ int argmax_finish(cudaStream_t stream, const void* partials, int chunks, int nsl
 int accept_finish(cudaStream_t stream, const void* partials, int chunks, int nslices, long long slice_stride,
                   const float* logits, long long row_stride, long long vocab, float inv_temperature,
                   const long long* draft_tokens, const float* draft_probs, const float* uniforms, int batch,
-                  int num_draft, int rows_per_seq, int bonus_row, AcceptOut* out_dev);
+                  int num_draft, int rows_per_seq, int bonus_row, AcceptOut* out_dev, const Nucleus* nucleus = nullptr);
+// Per row: the nucleus of softmax(logits * inv_temperature) at top_p (nucleus_out, may be null) and, with uniforms,
+// one token drawn from it (token ids to tok_out[row], its probability inside the nucleus to
+// prob_out[row * prob_stride]).
+int nucleus_rows(cudaStream_t stream, const float* logits, long long row_stride, int rows, long long vocab,
+                 float inv_temperature, float top_p, const float* uniforms, int u_stride, Nucleus* nucleus_out,
+                 long long* tok_out, float* prob_out, int prob_stride);
 
 int argmax_rows(cudaStream_t stream, const float* logits, long long row_stride, int rows, long long vocab,
                 void* scratch, long long* out_dev, float* partial_max, long long* partial_idx);

@@ -175,6 +175,8 @@ struct xinfer_spec_decoder {
     uint64_t sample_seed = 0;
     unsigned long long* step_counter = nullptr;
     float *uniforms = nullptr, *draft_probs = nullptr;
+    float top_p = 1.0f;               // < 1: nucleus sampling on both sides of the stochastic rule
+    xb::Nucleus* nucleus = nullptr;   // [batch * (k + 1)] nuclei of the verify rows
     int prev_rows = 0;       // rows of the previous target pass (for the lazy state commit)
     int64_t ctx_upper = 0;   // host-side upper bound of every sequence's context length
     cudaGraphExec_t graph_exec = nullptr;
@@ -331,6 +333,7 @@ void build_all(Dec* d) {
     d->step_counter = dalloc<unsigned long long>(d, 1, true);
     d->uniforms = dalloc<float>(d, static_cast<size_t>(2) * batch * k, true);
     d->draft_probs = dalloc<float>(d, static_cast<size_t>(batch) * k, true);
+    d->nucleus = dalloc<xb::Nucleus>(d, static_cast<size_t>(M), true);
     const int64_t hv = c.linear_num_v_heads, hk = c.linear_num_k_heads, ch = 2 * hk * 128 + hv * 128;
     d->x = dalloc<__half>(d, static_cast<size_t>(M) * H, true);
     d->emb = dalloc<__half>(d, static_cast<size_t>(batch) * H, true);
@@ -603,6 +606,10 @@ int draft_pass(Dec* d, cudaStream_t s, int i, bool full) {
     CK(lm_head_and_partials(d, s, B));
     if (d->temperature > 0.f) {
         // draft token i of every sequence from softmax(logits / T) at its uniform; its probability is the rule's p_draft
+        if (d->top_p < 1.0f)
+            NL(xb::nucleus_rows(s, d->logits, d->vocab_local, B, d->vocab_local, 1.0f / d->temperature, d->top_p, d->uniforms + i,
+                                d->k, nullptr, d->argmax_out, d->draft_probs + i, d->k));
+        else
         NL(xb::sample_finish(s, d->partials.p, xb::sampling_chunks(d->vocab_local), d->logits, d->vocab_local, d->vocab_local,
                              1.0f / d->temperature, d->uniforms + i, d->k, B, d->argmax_out, d->draft_probs + i, d->k));
     } else {
@@ -679,11 +686,18 @@ int enqueue_step(Dec* d, cudaStream_t s) {
         // greedy: draft i is kept iff it is the target's argmax of row i.  Stochastic: the reference's rule with the draft
         // token's probability under the head and this step's acceptance uniforms, logits scaled by 1 / T on both sides
         // (src/ops/sampling.cpp:129-171; with forced drafts there is no draft probability, so the greedy rule applies)
+        const bool nucleus_on = stochastic && d->top_p < 1.0f;
+        if (nucleus_on) {
+            // the nucleus of every verify row's own distribution: the rule takes the target's probability inside it
+            NL(xb::nucleus_rows(s, d->logits, d->vocab_local, B * R, d->vocab_local, 1.0f / d->temperature, d->top_p, nullptr, 0,
+                                d->nucleus, nullptr, nullptr, 0));
+            ++d->launches_per_step;
+        }
         NL(xb::accept_finish(s, d->partials.p, xb::sampling_chunks(d->vocab_local), d->world,
                              partial_slice_stride(d, B * R), d->logits, d->vocab_local, d->vocab_local,
                              d->temperature > 0.f ? 1.0f / d->temperature : 1.0f, d->draft, stochastic ? d->draft_probs : nullptr,
                              stochastic ? d->uniforms + static_cast<size_t>(B) * k : nullptr, B, k, R, k,
-                             reinterpret_cast<xb::AcceptOut*>(d->records)));
+                             reinterpret_cast<xb::AcceptOut*>(d->records), nucleus_on ? d->nucleus : nullptr));
         if (d->temperature > 0.f) {
             NL(xb::add_counter(s, d->step_counter, 1));
             ++d->launches_per_step;
@@ -967,6 +981,14 @@ int xinfer_spec_decoder_set_sampling(xinfer_spec_decoder* d, float temperature, 
     return XINFER_OK;
 }
 
+int xinfer_spec_decoder_set_top_p(xinfer_spec_decoder* d, float top_p) {
+    if (!d || !(top_p > 0.f) || top_p > 1.f) return XINFER_ERR_INVALID_ARGUMENT;
+    if (d->graph_exec) { d->error = "set the sampling mode before capture"; return XINFER_ERR_INVALID_ARGUMENT; }
+    if (top_p < 1.f && d->world > 1) { d->error = "stochastic acceptance runs on one GPU"; return XINFER_ERR_INVALID_ARGUMENT; }
+    d->top_p = top_p;
+    return XINFER_OK;
+}
+
 // Builds the context from a prompt: tokens [batch][T] (host), all sequences the same length, starting from the empty
 // context of reset(0, seed).  Positions 0 .. T-2 go through the target model in chunks of k + 1 rows (the verify
 // pass's own kernels with every row kept: KV caches, Gated-DeltaNet and convolution state advance as in a step whose
@@ -1031,7 +1053,11 @@ int xinfer_spec_decoder_generate(xinfer_spec_decoder* d, xinfer_stream_t stream,
     const int B = d->batch, R = d->k + 1;
     if (g->max_new_tokens <= 0) { d->error = "Invalid max_new_tokens: must be greater than 0"; return XINFER_ERR_INVALID_ARGUMENT; }
     if (g->temperature < 0.f) { d->error = "Invalid temperature: must be >= 0.0"; return XINFER_ERR_INVALID_ARGUMENT; }
-    if (g->top_p != 1.0f) { d->error = "Nucleus (top-p) sampling is not yet supported."; return XINFER_ERR_INVALID_ARGUMENT; }
+    if (!(g->top_p > 0.f) || g->top_p > 1.0f) { d->error = "Invalid top_p: must be in (0, 1]"; return XINFER_ERR_INVALID_ARGUMENT; }
+    if (g->top_p < 1.0f && !(g->temperature > 0.f)) {
+        d->error = "top_p < 1 needs temperature > 0 (greedy decoding takes the arg-max of the whole distribution)";
+        return XINFER_ERR_INVALID_ARGUMENT;
+    }
     if (!prompt_host || T < 1) { d->error = "empty prompt"; return XINFER_ERR_INVALID_ARGUMENT; }
     if (T + g->max_new_tokens + d->k > d->max_seq) {
         d->error = "This model's maximum context length is " + std::to_string(d->max_seq - d->k) + " tokens. However, you requested " +
@@ -1041,6 +1067,10 @@ int xinfer_spec_decoder_generate(xinfer_spec_decoder* d, xinfer_stream_t stream,
     }
     if (g->temperature != d->temperature || (g->temperature > 0.f && g->seed != d->sample_seed)) {
         int rc = xinfer_spec_decoder_set_sampling(d, g->temperature, g->seed);
+        if (rc < 0) return rc;
+    }
+    if (g->top_p != d->top_p) {
+        int rc = xinfer_spec_decoder_set_top_p(d, g->top_p);
         if (rc < 0) return rc;
     }
     cudaStream_t s = static_cast<cudaStream_t>(stream);

@@ -198,6 +198,15 @@ def sample_tokens(logits: torch.Tensor, rand_uniform: torch.Tensor, tokens_out: 
                                             _ptr(rand_uniform), _ptr(tokens_out), _ptr(probs_out)), "sample_tokens")
 
 
+def sample_tokens_top_p(logits: torch.Tensor, rand_uniform: torch.Tensor, tokens_out: torch.Tensor, probs_out: torch.Tensor,
+                        inv_temperature: float, top_p: float) -> int:
+    """``sample_tokens`` restricted to each row's nucleus at ``top_p`` (``xinfer_sample_tokens_top_p``)."""
+    rows, vocab = logits.shape
+    return check(lib().xinfer_sample_tokens_top_p(_stream(), _ptr(logits), logits.stride(0), vocab, rows, inv_temperature,
+                                                  top_p, _ptr(rand_uniform), _ptr(tokens_out), _ptr(probs_out)),
+                 "sample_tokens_top_p")
+
+
 def decode_accept_records(out_records: torch.Tensor) -> list:
     raw = out_records.cpu().numpy().tobytes()
     n = len(raw) // ACCEPT_RECORD_BYTES

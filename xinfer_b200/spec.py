@@ -97,6 +97,12 @@ class SpecDecoder:
         if code != 0:
             raise _lib.XInferError(code, "spec_decoder_set_sampling: " + self._err())
 
+    def set_top_p(self, top_p: float) -> None:
+        """Nucleus sampling on both sides of the stochastic rule (``xinfer_spec_decoder_set_top_p``); 1 = off."""
+        code = lib().xinfer_spec_decoder_set_top_p(self._h, float(top_p))
+        if code != 0:
+            raise _lib.XInferError(code, "spec_decoder_set_top_p: " + self._err())
+
     def prefill(self, prompt, stream=None) -> None:
         """Builds the context from ``prompt`` (int64 [batch][T]); call ``reset(0, seed)`` first.  Afterwards the
         context length is T - 1 and the last prompt token is the current token (``xinfer_spec_decoder_prefill``)."""
