@@ -328,6 +328,20 @@ def test_sample_tokens_top_p_against_the_oracle(cuda):
                     p64 = oracle.token_prob_f64(logits[b] * np.float32(inv_t), int(tok_h[b]))
                     assert abs(prob_h[b] - p64) <= 1e-4 * p64 + 2.0 ** -32   # weights are multiples of 2^-32
     assert near <= max(1, total // 50), (near, total)
+    # rows of heavily tied logits: the threshold's bucket holds far more tokens than the kernel's candidate list, so
+    # the selection runs over the row itself; ties at the threshold are all inside the nucleus
+    rng = np.random.default_rng(17)
+    tied = np.stack([rng.integers(0, 4, V).astype(np.float32) * np.float32(0.001),
+                     rng.integers(0, 3, V).astype(np.float32) * np.float32(0.25),
+                     np.zeros(V, np.float32)])
+    u = oracle.philox_uniform(3, 6000, 1)
+    for top_p in (0.3, 0.9):
+        tok = torch.empty(3, dtype=torch.int64, device="cuda")
+        prob = torch.empty(3, dtype=torch.float32, device="cuda")
+        assert cuda.sample_tokens_top_p(torch.from_numpy(tied).cuda(), torch.from_numpy(u).cuda(), tok, prob, 1.0, top_p) == 0
+        for b in range(3):
+            want_t, want_p = sample_token_top_p(tied[b], 1.0, top_p, u[b])
+            assert int(tok[b]) == want_t and abs(float(prob[b]) - want_p) <= 1e-5 * want_p, (top_p, b)
     # a nucleus of one token
     logits = (np.random.default_rng(3).standard_normal((4, 9000)) * 4).astype(np.float32)
     u = oracle.philox_uniform(4, 9, 9)

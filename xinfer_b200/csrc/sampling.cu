@@ -48,11 +48,15 @@ __device__ __forceinline__ uint32_t order_key(float x) {
     const uint32_t u = __float_as_uint(x);
     return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
 }
-// Coarse position of a scaled logit below the row's maximum: 128 buckets per unit, reversed (higher bin = higher
+// Coarse position of a scaled logit below the row's maximum: 64 buckets per unit, reversed (higher bin = higher
 // logit), everything 32 or more below the maximum in bin 0 (its weight is zero anyway).  Monotone in the logit.
+constexpr int kNucBuckets = 2048;
 __device__ __forceinline__ int nucleus_bucket(float scaled, float max_scaled) {
     const float d = max_scaled - scaled;
-    return d >= 31.99f ? 0 : 4095 - static_cast<int>(d * 128.0f);
+    return d >= 31.99f ? 0 : (kNucBuckets - 1) - static_cast<int>(d * 64.0f);
+}
+__device__ __forceinline__ float key_to_float(uint32_t k) {
+    return __uint_as_float((k & 0x80000000u) ? (k ^ 0x80000000u) : ~k);
 }
 __device__ __forceinline__ unsigned long long nucleus_weight(float scaled, float max_scaled) {
     return __float2ull_rn(expf(scaled - max_scaled) * 4294967296.0f);
@@ -403,8 +407,8 @@ __global__ void __launch_bounds__(kThreads) sample_finish_kernel(const Partial* 
 // the order of the additions, and the same on any machine that agrees on exp's bits.  The threshold is found by a
 // four-level selection, each level one pass over the row that adds the weights of the still-undecided tokens into a
 // histogram in shared memory and takes the bin in which the sum over all higher bins reaches ceil(top_p * Z): first
-// 4096 buckets over the distance to the row's maximum, then a radix selection on the order-preserving 32-bit key of
-// s (12 + 12 + 8 bits) among the tokens of that bucket.  With a uniform u the kernel also
+// 2048 buckets over the distance to the row's maximum (one pass over the row), then a radix selection on the
+// order-preserving 32-bit key of s among the tokens of that bucket, which are gathered into shared memory first.  With a uniform u the kernel also
 // draws the row's token: the first token, in index order, at which the running sum of the nucleus weights exceeds
 // floor(u * Z_nucleus); its probability is w / Z_nucleus.  One block of 1024 threads per row.
 constexpr int kNucThreads = 1024;
@@ -414,13 +418,15 @@ __device__ __forceinline__ unsigned long long shfl_u64(unsigned long long v, int
 }
 
 // Warp 0: the bin b (scanning from the highest bin down) at which the running sum first reaches `target`, and the
-// sum of all bins above it.  `nbins` is a multiple of 32; lane l owns the l-th highest block of nbins / 32 bins.
-__device__ void find_bin_desc(const unsigned long long* hist, int nbins, unsigned long long target, int lane,
-                              int* bin_out, unsigned long long* above_out) {
+// sum of all bins above it.  `hist(b)` returns bin b; `nbins` is a multiple of 32; lane l owns the l-th highest block
+// of nbins / 32 bins.
+template <typename G>
+__device__ __forceinline__ void find_bin_desc(G hist, int nbins, unsigned long long target, int lane, int* bin_out,
+                                              unsigned long long* above_out) {
     const int per = nbins / 32;
     const int top = nbins - 1 - lane * per;  // highest bin of this lane
     unsigned long long mine = 0;
-    for (int i = 0; i < per; ++i) mine += hist[top - i];
+    for (int i = 0; i < per; ++i) mine += hist(top - i);
     unsigned long long incl = mine;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
@@ -433,11 +439,31 @@ __device__ void find_bin_desc(const unsigned long long* hist, int nbins, unsigne
         unsigned long long cum = incl - mine;
         int b = top - (per - 1);
         for (int i = 0; i < per; ++i) {
-            if (cum + hist[top - i] >= target || i == per - 1) { b = top - i; break; }
-            cum += hist[top - i];
+            if (cum + hist(top - i) >= target || i == per - 1) { b = top - i; break; }
+            cum += hist(top - i);
         }
         *bin_out = b;
         *above_out = cum;
+    }
+}
+
+// f(i, scaled logit) for every token of the row: eight coalesced loads per thread are issued before the first of them
+// is used, so that a pass is not one L2 round trip per element (the histogram atomics in f would otherwise keep the
+// compiler from moving any load ahead of them).
+template <typename F>
+__device__ __forceinline__ void nucleus_for_each(const float* l, int vocab, float inv_t, int tid, F f) {
+    for (int base = 0; base < vocab; base += 8 * kNucThreads) {
+        float v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int i = base + j * kNucThreads + tid;
+            v[j] = i < vocab ? __ldg(l + i) : 0.f;
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int i = base + j * kNucThreads + tid;
+            if (i < vocab) f(i, v[j] * inv_t);
+        }
     }
 }
 
@@ -449,14 +475,14 @@ __global__ void __launch_bounds__(kNucThreads) nucleus_kernel(const float* logit
     __shared__ unsigned long long wsum[32];
     __shared__ float wmax[32];
     __shared__ unsigned long long s_above, s_z;
-    __shared__ int s_bin;
+    __shared__ int s_bin, s_count;
     __shared__ float s_ms;
     const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const float* l = logits + static_cast<long long>(row) * row_stride;
 
     // maximum of the scaled logits
     float mx = -INFINITY;
-    for (int i = tid; i < vocab; i += kNucThreads) mx = fmaxf(mx, l[i] * inv_t);
+    nucleus_for_each(l, vocab, inv_t, tid, [&](int, float sv) { mx = fmaxf(mx, sv); });
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
     if (lane == 0) wmax[warp] = mx;
@@ -470,17 +496,30 @@ __global__ void __launch_bounds__(kNucThreads) nucleus_kernel(const float* logit
     __syncthreads();
     const float ms = s_ms;
 
-    // level 0: total weight and a histogram over the distance to the maximum, 128 buckets per unit of scaled logit
+    // level 0: total weight and a histogram over the distance to the maximum, 64 buckets per unit of scaled logit
     // (the keys themselves crowd into a few exponents: their top bits would send every token of the row to a
     // handful of bins, and shared-memory atomics on one address run one after the other).  The bucket index falls
     // as the scaled logit grows, so buckets are stored in reverse: a higher bin holds higher logits.
     unsigned long long z = 0;
-    for (int i = tid; i < vocab; i += kNucThreads) {
-        const float sv = l[i] * inv_t;
+    // (64-bit adds on shared memory are compare-and-swap loops; a weight is below 2^33, so it goes in as three 11-bit
+    // limbs with native 32-bit adds - a limb's sum over a whole row stays below 2^32 - and a bin is read back as
+    // l0 + (l1 << 11) + (l2 << 22))
+    uint32_t* limb = reinterpret_cast<uint32_t*>(hist);
+    nucleus_for_each(l, vocab, inv_t, tid, [&](int, float sv) {
         const unsigned long long w = nucleus_weight(sv, ms);
         z += w;
-        if (w) atomicAdd(&hist[nucleus_bucket(sv, ms)], w);
-    }
+        if (w) {
+            const int bk = nucleus_bucket(sv, ms);
+            const uint32_t lo = static_cast<uint32_t>(w);
+            atomicAdd(&limb[bk], lo & 0x7FFu);
+            if (w >> 11) atomicAdd(&limb[kNucBuckets + bk], static_cast<uint32_t>(w >> 11) & 0x7FFu);
+            if (w >> 22) atomicAdd(&limb[2 * kNucBuckets + bk], static_cast<uint32_t>(w >> 22));
+        }
+    });
+    auto bucket_sum = [&](int bk) -> unsigned long long {
+        return static_cast<unsigned long long>(limb[bk]) + (static_cast<unsigned long long>(limb[kNucBuckets + bk]) << 11) +
+               (static_cast<unsigned long long>(limb[2 * kNucBuckets + bk]) << 22);
+    };
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) z += shfl_u64(z, lane ^ o);
     if (lane == 0) wsum[warp] = z;
@@ -494,7 +533,7 @@ __global__ void __launch_bounds__(kNucThreads) nucleus_kernel(const float* logit
         unsigned long long target = want <= 1.0 ? 1ull : static_cast<unsigned long long>(want);
         if (target > tot) target = tot;
         if (lane == 0) s_z = target;  // (the target travels in s_z until the nucleus sum replaces it)
-        find_bin_desc(hist, 4096, target, lane, &s_bin, &s_above);
+        find_bin_desc(bucket_sum, kNucBuckets, target, lane, &s_bin, &s_above);
     }
     __syncthreads();
     const int b0 = s_bin;
@@ -502,52 +541,65 @@ __global__ void __launch_bounds__(kNucThreads) nucleus_kernel(const float* logit
     unsigned long long target = s_z - above;
     __syncthreads();
 
-    // levels 1 to 3: radix selection on the key (12 + 12 + 8 bits) among the tokens of bucket b0 only
-    for (int i = tid; i < 4096; i += kNucThreads) hist[i] = 0;
+    // The tokens of bucket b0 (a few dozen of a 150 000-token row, unless many logits are equal) are gathered into a
+    // list of keys in shared memory; the exact threshold is then a radix selection on the keys of the list (four
+    // levels of 8 bits), which costs no further pass over the row.  A bucket that does not fit the list is selected
+    // from the row itself (12 + 12 + 8 bits, three passes).
+    constexpr int kCand = 4096;
+    uint32_t* cand = reinterpret_cast<uint32_t*>(hist);   // 16 KB; the list's 256-bin histogram sits behind it
+    if (tid == 0) s_count = 0;
     __syncthreads();
-    for (int i = tid; i < vocab; i += kNucThreads) {
-        const float sv = l[i] * inv_t;
-        const unsigned long long w = nucleus_weight(sv, ms);
-        if (w && nucleus_bucket(sv, ms) == b0) atomicAdd(&hist[order_key(sv) >> 20], w);
+    nucleus_for_each(l, vocab, inv_t, tid, [&](int, float sv) {
+        if (nucleus_bucket(sv, ms) == b0 && nucleus_weight(sv, ms)) {
+            const int pos = atomicAdd(&s_count, 1);
+            if (pos < kCand) cand[pos] = order_key(sv);
+        }
+    });
+    __syncthreads();
+    const int count = s_count;
+    uint32_t prefix = 0;           // the key bits decided so far
+    unsigned long long last = 0;   // weight of the threshold's own bin at the last level
+    // one level: histogram of the weights of the candidates that match the decided bits, over the next `bits` bits
+    auto level = [&](auto each, unsigned long long* hh, int nb, int shift, uint32_t mask) {
+        for (int i = tid; i < nb; i += kNucThreads) hh[i] = 0;
+        __syncthreads();
+        each([&](float sv) {
+            const uint32_t k = order_key(sv);
+            if ((k & mask) == prefix) {
+                const unsigned long long w = nucleus_weight(sv, ms);
+                if (w) atomicAdd(&hh[(k >> shift) & static_cast<uint32_t>(nb - 1)], w);
+            }
+        });
+        __syncthreads();
+        if (warp == 0) find_bin_desc([&](int bin) { return hh[bin]; }, nb, target, lane, &s_bin, &s_above);
+        __syncthreads();
+        prefix |= static_cast<uint32_t>(s_bin) << shift;
+        above += s_above;
+        target -= s_above;
+        last = hh[s_bin];
+        __syncthreads();
+    };
+    if (count <= kCand) {
+        unsigned long long* hh = hist + kCand / 2;   // behind the 4096 keys
+        auto each = [&](auto f) {
+            for (int q = tid; q < count; q += kNucThreads) f(key_to_float(cand[q]));
+        };
+        level(each, hh, 256, 24, 0u);
+        level(each, hh, 256, 16, 0xFF000000u);
+        level(each, hh, 256, 8, 0xFFFF0000u);
+        level(each, hh, 256, 0, 0xFFFFFF00u);
+    } else {
+        auto each = [&](auto f) {
+            nucleus_for_each(l, vocab, inv_t, tid, [&](int, float sv) {
+                if (nucleus_bucket(sv, ms) == b0) f(sv);
+            });
+        };
+        level(each, hist, 4096, 20, 0u);
+        level(each, hist, 4096, 8, 0xFFF00000u);
+        level(each, hist, 256, 0, 0xFFFFFF00u);
     }
-    __syncthreads();
-    if (warp == 0) find_bin_desc(hist, 4096, target, lane, &s_bin, &s_above);
-    __syncthreads();
-    const uint32_t b1 = static_cast<uint32_t>(s_bin);
-    above += s_above;
-    target -= s_above;
-    __syncthreads();
-
-    for (int i = tid; i < 4096; i += kNucThreads) hist[i] = 0;
-    __syncthreads();
-    for (int i = tid; i < vocab; i += kNucThreads) {
-        const float sv = l[i] * inv_t;
-        const uint32_t k = order_key(sv);
-        const unsigned long long w = nucleus_weight(sv, ms);
-        if (w && (k >> 20) == b1 && nucleus_bucket(sv, ms) == b0) atomicAdd(&hist[(k >> 8) & 0xFFFu], w);
-    }
-    __syncthreads();
-    if (warp == 0) find_bin_desc(hist, 4096, target, lane, &s_bin, &s_above);
-    __syncthreads();
-    const uint32_t b2 = static_cast<uint32_t>(s_bin);
-    above += s_above;
-    target -= s_above;
-    __syncthreads();
-
-    for (int i = tid; i < 256; i += kNucThreads) hist[i] = 0;
-    __syncthreads();
-    const uint32_t hi24 = (b1 << 12) | b2;
-    for (int i = tid; i < vocab; i += kNucThreads) {
-        const float sv = l[i] * inv_t;
-        const uint32_t k = order_key(sv);
-        const unsigned long long w = nucleus_weight(sv, ms);
-        if (w && (k >> 8) == hi24 && nucleus_bucket(sv, ms) == b0) atomicAdd(&hist[k & 0xFFu], w);
-    }
-    __syncthreads();
-    if (warp == 0) find_bin_desc(hist, 256, target, lane, &s_bin, &s_above);
-    __syncthreads();
-    const uint32_t thr = (hi24 << 8) | static_cast<uint32_t>(s_bin);
-    const unsigned long long z_nuc = above + s_above + hist[s_bin];
+    const uint32_t thr = prefix;
+    const unsigned long long z_nuc = above + last;
     if (tid == 0 && nuc_out) {
         Nucleus q;
         q.z = z_nuc;
@@ -557,44 +609,63 @@ __global__ void __launch_bounds__(kNucThreads) nucleus_kernel(const float* logit
     }
     if (!uniforms) return;
 
-    // draw: every thread sums the nucleus weights of its contiguous block of token ids
-    const int per = (vocab + kNucThreads - 1) / kNucThreads;
-    const int i0 = tid * per, i1 = min(vocab, i0 + per);
+    // draw: warp w owns the contiguous span [w * span, (w + 1) * span) of token ids and first adds up its nucleus
+    // weights (lanes interleaved, loads coalesced); the one warp whose range of the running sum holds floor(u * Z)
+    // then walks its span 32 tokens at a time with a warp scan, which visits the tokens in index order.
+    const int span = ((vocab + 31) / 32 + 31) & ~31;
+    const int w0 = warp * span, w1 = min(vocab, w0 + span);
     unsigned long long mine = 0;
-    for (int i = i0; i < i1; ++i) {
-        const float sv = l[i] * inv_t;
-        if (order_key(sv) >= thr) mine += nucleus_weight(sv, ms);
-    }
-    unsigned long long incl = mine;
+    for (int base = w0; base < w1; base += 8 * 32) {
+        float v[8];
 #pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-        const unsigned long long up = __shfl_up_sync(0xffffffffu, incl, o);
-        if (lane >= o) incl += up;
+        for (int j = 0; j < 8; ++j) {
+            const int i = base + j * 32 + lane;
+            v[j] = i < w1 ? __ldg(l + i) : 0.f;
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int i = base + j * 32 + lane;
+            const float sv = v[j] * inv_t;
+            if (i < w1 && order_key(sv) >= thr) mine += nucleus_weight(sv, ms);
+        }
     }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mine += shfl_u64(mine, lane ^ o);
     __syncthreads();  // (wsum is reused)
-    if (lane == 31) wsum[warp] = incl;
+    if (lane == 0) wsum[warp] = mine;
     __syncthreads();
-    unsigned long long before = incl - mine;
+    unsigned long long before = 0;
     for (int w = 0; w < warp; ++w) before += wsum[w];
     double pos = floor(static_cast<double>(uniforms[static_cast<long long>(row) * u_stride]) * static_cast<double>(z_nuc));
     unsigned long long t2 = pos <= 0.0 ? 0ull : static_cast<unsigned long long>(pos);
     if (t2 >= z_nuc) t2 = z_nuc - 1;
-    if (mine > 0 && before <= t2 && t2 < before + mine) {
-        unsigned long long cum = before, wtok = 0;
-        int tok = i0;
-        for (int i = i0; i < i1; ++i) {
-            const float sv = l[i] * inv_t;
-            if (order_key(sv) >= thr) {
-                const unsigned long long w = nucleus_weight(sv, ms);
-                cum += w;
-                tok = i;
-                wtok = w;
-                if (cum > t2) break;
+    if (mine > 0 && before <= t2 && t2 < before + mine) {   // warp-uniform: exactly one warp
+        unsigned long long cum = before;
+        for (int base = w0; base < w1; base += 32) {
+            const int i = base + lane;
+            unsigned long long w = 0;
+            if (i < w1) {
+                const float sv = __ldg(l + i) * inv_t;
+                if (order_key(sv) >= thr) w = nucleus_weight(sv, ms);
             }
+            unsigned long long incl = w;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const unsigned long long up = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += up;
+            }
+            const unsigned hit = __ballot_sync(0xffffffffu, w > 0 && cum + incl > t2);
+            if (hit) {
+                const int src = __ffs(hit) - 1;
+                if (lane == src) {
+                    tok_out[row] = i;
+                    prob_out[static_cast<long long>(row) * prob_stride] =
+                        static_cast<float>(static_cast<double>(w) / static_cast<double>(z_nuc));
+                }
+                break;
+            }
+            cum += shfl_u64(incl, 31);
         }
-        tok_out[row] = tok;
-        prob_out[static_cast<long long>(row) * prob_stride] =
-            static_cast<float>(static_cast<double>(wtok) / static_cast<double>(z_nuc));
     }
 }
 
