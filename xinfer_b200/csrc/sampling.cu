@@ -13,6 +13,7 @@
 // sum of exp(l * inv_temperature - chunk_max); a second tiny kernel merges the chunks per row
 // (online-softmax merge), evaluates p_target and runs the accept scan for every sequence of the batch.
 // Nothing returns to the host until the caller asks for the result.
+#include <cooperative_groups.h>
 #include <cuda_runtime.h>
 #include <math.h>
 #include <stdint.h>
@@ -410,7 +411,7 @@ __global__ void __launch_bounds__(kThreads) sample_finish_kernel(const Partial* 
 // 2048 buckets over the distance to the row's maximum (one pass over the row), then a radix selection on the
 // order-preserving 32-bit key of s among the tokens of that bucket, which are gathered into shared memory first.  With a uniform u the kernel also
 // draws the row's token: the first token, in index order, at which the running sum of the nucleus weights exceeds
-// floor(u * Z_nucleus); its probability is w / Z_nucleus.  One block of 1024 threads per row.
+// floor(u * Z_nucleus); its probability is w / Z_nucleus.  A cluster of eight 1024-thread CTAs per row.
 constexpr int kNucThreads = 1024;
 
 __device__ __forceinline__ unsigned long long shfl_u64(unsigned long long v, int src) {
@@ -447,173 +448,226 @@ __device__ __forceinline__ void find_bin_desc(G hist, int nbins, unsigned long l
     }
 }
 
-// f(i, scaled logit) for every token of the row: eight coalesced loads per thread are issued before the first of them
+// f(i, scaled logit) for every token of [i0, i1): eight coalesced loads per thread are issued before the first of them
 // is used, so that a pass is not one L2 round trip per element (the histogram atomics in f would otherwise keep the
 // compiler from moving any load ahead of them).
 template <typename F>
-__device__ __forceinline__ void nucleus_for_each(const float* l, int vocab, float inv_t, int tid, F f) {
-    for (int base = 0; base < vocab; base += 8 * kNucThreads) {
+__device__ __forceinline__ void nucleus_for_each(const float* l, int i0, int i1, float inv_t, int tid, F f) {
+    for (int base = i0; base < i1; base += 8 * kNucThreads) {
         float v[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
             const int i = base + j * kNucThreads + tid;
-            v[j] = i < vocab ? __ldg(l + i) : 0.f;
+            v[j] = i < i1 ? __ldg(l + i) : 0.f;
         }
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
             const int i = base + j * kNucThreads + tid;
-            if (i < vocab) f(i, v[j] * inv_t);
+            if (i < i1) f(i, v[j] * inv_t);
         }
     }
 }
 
-__global__ void __launch_bounds__(kNucThreads) nucleus_kernel(const float* logits, long long row_stride, int vocab,
-                                                              float inv_t, float top_p, const float* uniforms, int u_stride,
-                                                              Nucleus* nuc_out, long long* tok_out, float* prob_out,
-                                                              int prob_stride) {
-    __shared__ unsigned long long hist[4096];
-    __shared__ unsigned long long wsum[32];
-    __shared__ float wmax[32];
-    __shared__ unsigned long long s_above, s_z;
-    __shared__ int s_bin, s_count;
-    __shared__ float s_ms;
-    const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+// A row is shared by the eight CTAs of a thread-block cluster, each with a contiguous eighth of the token ids; CTA 0
+// of the cluster (the leader) holds what the others contribute through distributed shared memory: the eight partial
+// maxima and sums, the merged bucket histogram, the candidate list, and the results it hands back.  Every CTA passes
+// every cluster barrier.
+constexpr int kNucCluster = 8;
+constexpr int kNucCand = 4096;
+
+struct NucShared {
+    unsigned long long hist[4096];   // bucket limbs (24 KB) / candidate keys (16 KB) + list histogram / row histograms
+    unsigned long long wsum[32];
+    unsigned long long csum[kNucCluster];   // leader: per-CTA sums
+    float cmax[kNucCluster];                // leader: per-CTA maxima
+    float wmax[32];
+    unsigned long long above, target, z_nuc;   // leader: results of a level / of the selection
+    int bin, count;
+    uint32_t thr;
+};
+
+__global__ void __cluster_dims__(kNucCluster, 1, 1) __launch_bounds__(kNucThreads)
+nucleus_kernel(const float* logits, long long row_stride, int vocab, float inv_t, float top_p, const float* uniforms,
+               int u_stride, Nucleus* nuc_out, long long* tok_out, float* prob_out, int prob_stride) {
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
+    __shared__ NucShared sh;
+    const int crank = static_cast<int>(cluster.block_rank());
+    const int row = blockIdx.x / kNucCluster, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const float* l = logits + static_cast<long long>(row) * row_stride;
+    NucShared* lead = cluster.map_shared_rank(&sh, 0);
+    // this CTA's token ids
+    const int cspan = (((vocab + kNucCluster - 1) / kNucCluster) + 31) & ~31;
+    const int c0 = min(vocab, crank * cspan), c1 = min(vocab, c0 + cspan);
 
     // maximum of the scaled logits
     float mx = -INFINITY;
-    nucleus_for_each(l, vocab, inv_t, tid, [&](int, float sv) { mx = fmaxf(mx, sv); });
+    nucleus_for_each(l, c0, c1, inv_t, tid, [&](int, float sv) { mx = fmaxf(mx, sv); });
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-    if (lane == 0) wmax[warp] = mx;
-    for (int i = tid; i < 4096; i += kNucThreads) hist[i] = 0;
+    if (lane == 0) sh.wmax[warp] = mx;
+    for (int i = tid; i < 4096; i += kNucThreads) sh.hist[i] = 0;
+    if (tid == 0) sh.count = 0;
     __syncthreads();
     if (tid == 0) {
-        float m = wmax[0];
-        for (int w = 1; w < 32; ++w) m = fmaxf(m, wmax[w]);
-        s_ms = m;
+        float m = sh.wmax[0];
+        for (int w = 1; w < 32; ++w) m = fmaxf(m, sh.wmax[w]);
+        lead->cmax[crank] = m;
     }
-    __syncthreads();
-    const float ms = s_ms;
+    cluster.sync();
+    float ms = lead->cmax[0];
+#pragma unroll
+    for (int r = 1; r < kNucCluster; ++r) ms = fmaxf(ms, lead->cmax[r]);
 
     // level 0: total weight and a histogram over the distance to the maximum, 64 buckets per unit of scaled logit
     // (the keys themselves crowd into a few exponents: their top bits would send every token of the row to a
     // handful of bins, and shared-memory atomics on one address run one after the other).  The bucket index falls
     // as the scaled logit grows, so buckets are stored in reverse: a higher bin holds higher logits.
-    unsigned long long z = 0;
     // (64-bit adds on shared memory are compare-and-swap loops; a weight is below 2^33, so it goes in as three 11-bit
     // limbs with native 32-bit adds - a limb's sum over a whole row stays below 2^32 - and a bin is read back as
     // l0 + (l1 << 11) + (l2 << 22))
-    uint32_t* limb = reinterpret_cast<uint32_t*>(hist);
-    nucleus_for_each(l, vocab, inv_t, tid, [&](int, float sv) {
+    unsigned long long z = 0;
+    uint32_t* limb = reinterpret_cast<uint32_t*>(sh.hist);
+    nucleus_for_each(l, c0, c1, inv_t, tid, [&](int, float sv) {
         const unsigned long long w = nucleus_weight(sv, ms);
         z += w;
         if (w) {
             const int bk = nucleus_bucket(sv, ms);
-            const uint32_t lo = static_cast<uint32_t>(w);
-            atomicAdd(&limb[bk], lo & 0x7FFu);
+            atomicAdd(&limb[bk], static_cast<uint32_t>(w) & 0x7FFu);
             if (w >> 11) atomicAdd(&limb[kNucBuckets + bk], static_cast<uint32_t>(w >> 11) & 0x7FFu);
             if (w >> 22) atomicAdd(&limb[2 * kNucBuckets + bk], static_cast<uint32_t>(w >> 22));
         }
     });
-    auto bucket_sum = [&](int bk) -> unsigned long long {
-        return static_cast<unsigned long long>(limb[bk]) + (static_cast<unsigned long long>(limb[kNucBuckets + bk]) << 11) +
-               (static_cast<unsigned long long>(limb[2 * kNucBuckets + bk]) << 22);
-    };
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) z += shfl_u64(z, lane ^ o);
-    if (lane == 0) wsum[warp] = z;
+    if (lane == 0) sh.wsum[warp] = z;
     __syncthreads();
-    if (warp == 0) {
-        unsigned long long tot = wsum[lane];
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) tot += shfl_u64(tot, lane ^ o);
-        // ceil(top_p * Z), at least one unit of weight and at most all of it
-        double want = ceil(static_cast<double>(top_p) * static_cast<double>(tot));
-        unsigned long long target = want <= 1.0 ? 1ull : static_cast<unsigned long long>(want);
-        if (target > tot) target = tot;
-        if (lane == 0) s_z = target;  // (the target travels in s_z until the nucleus sum replaces it)
-        find_bin_desc(bucket_sum, kNucBuckets, target, lane, &s_bin, &s_above);
+    if (tid == 0) {
+        unsigned long long tot = 0;
+        for (int w = 0; w < 32; ++w) tot += sh.wsum[w];
+        lead->csum[crank] = tot;
     }
-    __syncthreads();
-    const int b0 = s_bin;
-    unsigned long long above = s_above;
-    unsigned long long target = s_z - above;
-    __syncthreads();
+    cluster.sync();
+    if (crank == 0) {
+        // the leader adds the other CTAs' limbs to its own, then finds the bucket in which ceil(top_p * Z) is reached
+        for (int i = tid; i < 3 * kNucBuckets; i += kNucThreads) {
+            uint32_t acc = limb[i];
+            for (int r = 1; r < kNucCluster; ++r)
+                acc += reinterpret_cast<const uint32_t*>(cluster.map_shared_rank(&sh, r)->hist)[i];
+            limb[i] = acc;
+        }
+        __syncthreads();
+        if (warp == 0) {
+            unsigned long long tot = 0;
+            for (int r = 0; r < kNucCluster; ++r) tot += sh.csum[r];
+            double want = ceil(static_cast<double>(top_p) * static_cast<double>(tot));
+            unsigned long long target = want <= 1.0 ? 1ull : static_cast<unsigned long long>(want);
+            if (target > tot) target = tot;
+            if (lane == 0) sh.target = target;
+            find_bin_desc(
+                [&](int bk) -> unsigned long long {
+                    return static_cast<unsigned long long>(limb[bk]) + (static_cast<unsigned long long>(limb[kNucBuckets + bk]) << 11) +
+                           (static_cast<unsigned long long>(limb[2 * kNucBuckets + bk]) << 22);
+                },
+                kNucBuckets, target, lane, &sh.bin, &sh.above);
+        }
+    }
+    cluster.sync();
+    const int b0 = lead->bin;
+    unsigned long long above = lead->above;
+    unsigned long long target = lead->target - above;
+    cluster.sync();   // (every CTA has read the leader's results and the leader has read every histogram)
 
     // The tokens of bucket b0 (a few dozen of a 150 000-token row, unless many logits are equal) are gathered into a
-    // list of keys in shared memory; the exact threshold is then a radix selection on the keys of the list (four
-    // levels of 8 bits), which costs no further pass over the row.  A bucket that does not fit the list is selected
-    // from the row itself (12 + 12 + 8 bits, three passes).
-    constexpr int kCand = 4096;
-    uint32_t* cand = reinterpret_cast<uint32_t*>(hist);   // 16 KB; the list's 256-bin histogram sits behind it
-    if (tid == 0) s_count = 0;
-    __syncthreads();
-    nucleus_for_each(l, vocab, inv_t, tid, [&](int, float sv) {
+    // list of keys in the leader's shared memory; the exact threshold is then a radix selection on the keys of the
+    // list (four levels of 8 bits), which costs no further pass over the row.  A bucket that does not fit the list is
+    // selected from the row itself (12 + 12 + 8 bits, three passes, every CTA adding into the leader's histogram).
+    uint32_t* cand = reinterpret_cast<uint32_t*>(lead->hist);
+    nucleus_for_each(l, c0, c1, inv_t, tid, [&](int, float sv) {
         if (nucleus_bucket(sv, ms) == b0 && nucleus_weight(sv, ms)) {
-            const int pos = atomicAdd(&s_count, 1);
-            if (pos < kCand) cand[pos] = order_key(sv);
+            const int pos = atomicAdd(&lead->count, 1);
+            if (pos < kNucCand) cand[pos] = order_key(sv);
         }
     });
-    __syncthreads();
-    const int count = s_count;
+    cluster.sync();
+    const int count = lead->count;
     uint32_t prefix = 0;           // the key bits decided so far
     unsigned long long last = 0;   // weight of the threshold's own bin at the last level
-    // one level: histogram of the weights of the candidates that match the decided bits, over the next `bits` bits
-    auto level = [&](auto each, unsigned long long* hh, int nb, int shift, uint32_t mask) {
-        for (int i = tid; i < nb; i += kNucThreads) hh[i] = 0;
-        __syncthreads();
-        each([&](float sv) {
-            const uint32_t k = order_key(sv);
-            if ((k & mask) == prefix) {
-                const unsigned long long w = nucleus_weight(sv, ms);
-                if (w) atomicAdd(&hh[(k >> shift) & static_cast<uint32_t>(nb - 1)], w);
+    if (count <= kNucCand) {
+        if (crank == 0) {
+            unsigned long long* hh = sh.hist + kNucCand / 2;   // behind the 4096 keys
+            const uint32_t* keys = reinterpret_cast<const uint32_t*>(sh.hist);
+            for (int lvl = 0; lvl < 4; ++lvl) {
+                const int shift = 24 - 8 * lvl;
+                const uint32_t mask = lvl == 0 ? 0u : ~0u << (shift + 8);
+                for (int i = tid; i < 256; i += kNucThreads) hh[i] = 0;
+                __syncthreads();
+                for (int q = tid; q < count; q += kNucThreads) {
+                    const uint32_t k = keys[q];
+                    if ((k & mask) == prefix) {
+                        const unsigned long long w = nucleus_weight(key_to_float(k), ms);
+                        if (w) atomicAdd(&hh[(k >> shift) & 0xFFu], w);
+                    }
+                }
+                __syncthreads();
+                if (warp == 0) find_bin_desc([&](int bin) { return hh[bin]; }, 256, target, lane, &sh.bin, &sh.above);
+                __syncthreads();
+                prefix |= static_cast<uint32_t>(sh.bin) << shift;
+                above += sh.above;
+                target -= sh.above;
+                last = hh[sh.bin];
+                __syncthreads();
             }
-        });
-        __syncthreads();
-        if (warp == 0) find_bin_desc([&](int bin) { return hh[bin]; }, nb, target, lane, &s_bin, &s_above);
-        __syncthreads();
-        prefix |= static_cast<uint32_t>(s_bin) << shift;
-        above += s_above;
-        target -= s_above;
-        last = hh[s_bin];
-        __syncthreads();
-    };
-    if (count <= kCand) {
-        unsigned long long* hh = hist + kCand / 2;   // behind the 4096 keys
-        auto each = [&](auto f) {
-            for (int q = tid; q < count; q += kNucThreads) f(key_to_float(cand[q]));
-        };
-        level(each, hh, 256, 24, 0u);
-        level(each, hh, 256, 16, 0xFF000000u);
-        level(each, hh, 256, 8, 0xFFFF0000u);
-        level(each, hh, 256, 0, 0xFFFFFF00u);
+            if (tid == 0) { sh.thr = prefix; sh.z_nuc = above + last; }
+        }
+        cluster.sync();
     } else {
-        auto each = [&](auto f) {
-            nucleus_for_each(l, vocab, inv_t, tid, [&](int, float sv) {
-                if (nucleus_bucket(sv, ms) == b0) f(sv);
+        const int shifts[3] = {20, 8, 0}, nbs[3] = {4096, 4096, 256};
+        for (int lvl = 0; lvl < 3; ++lvl) {
+            const int shift = shifts[lvl], nb = nbs[lvl];
+            const uint32_t mask = lvl == 0 ? 0u : (lvl == 1 ? 0xFFF00000u : 0xFFFFFF00u);
+            if (crank == 0)
+                for (int i = tid; i < nb; i += kNucThreads) sh.hist[i] = 0;
+            cluster.sync();
+            nucleus_for_each(l, c0, c1, inv_t, tid, [&](int, float sv) {
+                const uint32_t k = order_key(sv);
+                if ((k & mask) == prefix && nucleus_bucket(sv, ms) == b0) {
+                    const unsigned long long w = nucleus_weight(sv, ms);
+                    if (w) atomicAdd(&lead->hist[(k >> shift) & static_cast<uint32_t>(nb - 1)], w);
+                }
             });
-        };
-        level(each, hist, 4096, 20, 0u);
-        level(each, hist, 4096, 8, 0xFFF00000u);
-        level(each, hist, 256, 0, 0xFFFFFF00u);
+            cluster.sync();
+            if (crank == 0 && warp == 0)
+                find_bin_desc([&](int bin) { return sh.hist[bin]; }, nb, target, lane, &sh.bin, &sh.above);
+            cluster.sync();
+            prefix |= static_cast<uint32_t>(lead->bin) << shift;
+            above += lead->above;
+            target -= lead->above;
+            last = lead->hist[lead->bin];
+            cluster.sync();
+        }
+        if (crank == 0 && tid == 0) { sh.thr = prefix; sh.z_nuc = above + last; }
+        cluster.sync();
     }
-    const uint32_t thr = prefix;
-    const unsigned long long z_nuc = above + last;
-    if (tid == 0 && nuc_out) {
+    const uint32_t thr = lead->thr;
+    const unsigned long long z_nuc = lead->z_nuc;
+    if (crank == 0 && tid == 0 && nuc_out) {
         Nucleus q;
         q.z = z_nuc;
         q.max_scaled = ms;
         q.thr_key = thr;
         nuc_out[row] = q;
     }
-    if (!uniforms) return;
+    if (!uniforms) {
+        cluster.sync();   // nobody leaves while the leader's shared memory is still being read
+        return;
+    }
 
-    // draw: warp w owns the contiguous span [w * span, (w + 1) * span) of token ids and first adds up its nucleus
-    // weights (lanes interleaved, loads coalesced); the one warp whose range of the running sum holds floor(u * Z)
-    // then walks its span 32 tokens at a time with a warp scan, which visits the tokens in index order.
-    const int span = ((vocab + 31) / 32 + 31) & ~31;
-    const int w0 = warp * span, w1 = min(vocab, w0 + span);
+    // draw: inside a CTA warp w owns the contiguous span [c0 + w * span, ...) of token ids and first adds up its nucleus
+    // weights (lanes interleaved, loads coalesced); the one warp of the one CTA whose range of the running sum holds
+    // floor(u * Z) then walks its span 32 tokens at a time with a warp scan, which visits the tokens in index order.
+    const int span = (((c1 - c0) + 31) / 32 + 31) & ~31;
+    const int w0 = min(c1, c0 + warp * span), w1 = min(c1, w0 + span);
     unsigned long long mine = 0;
     for (int base = w0; base < w1; base += 8 * 32) {
         float v[8];
@@ -631,15 +685,22 @@ __global__ void __launch_bounds__(kNucThreads) nucleus_kernel(const float* logit
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) mine += shfl_u64(mine, lane ^ o);
-    __syncthreads();  // (wsum is reused)
-    if (lane == 0) wsum[warp] = mine;
     __syncthreads();
+    if (lane == 0) sh.wsum[warp] = mine;
+    __syncthreads();
+    if (tid == 0) {
+        unsigned long long tot = 0;
+        for (int w = 0; w < 32; ++w) tot += sh.wsum[w];
+        lead->csum[crank] = tot;
+    }
+    cluster.sync();
     unsigned long long before = 0;
-    for (int w = 0; w < warp; ++w) before += wsum[w];
+    for (int r = 0; r < crank; ++r) before += lead->csum[r];
+    for (int w = 0; w < warp; ++w) before += sh.wsum[w];
     double pos = floor(static_cast<double>(uniforms[static_cast<long long>(row) * u_stride]) * static_cast<double>(z_nuc));
     unsigned long long t2 = pos <= 0.0 ? 0ull : static_cast<unsigned long long>(pos);
     if (t2 >= z_nuc) t2 = z_nuc - 1;
-    if (mine > 0 && before <= t2 && t2 < before + mine) {   // warp-uniform: exactly one warp
+    if (mine > 0 && before <= t2 && t2 < before + mine) {   // warp-uniform: exactly one warp of one CTA
         unsigned long long cum = before;
         for (int base = w0; base < w1; base += 32) {
             const int i = base + lane;
@@ -667,6 +728,7 @@ __global__ void __launch_bounds__(kNucThreads) nucleus_kernel(const float* logit
             cum += shfl_u64(incl, 31);
         }
     }
+    cluster.sync();   // nobody leaves while the leader's shared memory is still being read
 }
 
 }  // namespace
@@ -757,7 +819,7 @@ int nucleus_rows(cudaStream_t stream, const float* logits, long long row_stride,
                  float inv_temperature, float top_p, const float* uniforms, int u_stride, Nucleus* nucleus_out,
                  long long* tok_out, float* prob_out, int prob_stride) {
     if (rows <= 0) return 0;
-    nucleus_kernel<<<rows, kNucThreads, 0, stream>>>(logits, row_stride, static_cast<int>(vocab), inv_temperature, top_p,
+    nucleus_kernel<<<rows * kNucCluster, kNucThreads, 0, stream>>>(logits, row_stride, static_cast<int>(vocab), inv_temperature, top_p,
                                                      uniforms, u_stride, nucleus_out, tok_out, prob_out, prob_stride);
     return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
