@@ -446,11 +446,12 @@ XINFER_EXPORT int xinfer_spec_decoder_set_sampling(xinfer_spec_decoder* d, float
  * capture. */
 XINFER_EXPORT int xinfer_spec_decoder_set_top_p(xinfer_spec_decoder* d, float top_p);
 /* Builds the context from a prompt, tokens[batch][T] on the host (every sequence the same length), starting from the
- * empty context of xinfer_spec_decoder_reset(d, 0, seed): positions 0 .. T-2 go through the target in chunks of k + 1
- * rows with every row kept, the MTP head's KV slots of those positions are filled, the last prompt token becomes the
- * current token; ctx = T - 1 afterwards and xinfer_spec_decoder_step continues from there.  Stands where the
- * reference's prefill loop does (forward_prefill_chunk, src/targets/qwen3_8/forward.cpp:402-554; engine.cpp:330-398)
- * but runs at the decode kernels' row count.  Synchronous; one GPU only. */
+ * empty context of xinfer_spec_decoder_reset(d, 0, seed): positions 0 .. T-2 go through the target in chunks of up to
+ * 512 rows over all sequences (the projections of a chunk run as one M = 512 GEMM each, the attention and Gated-DeltaNet
+ * kernels take it four positions at a time), the MTP head's KV slots of those positions are filled, the last prompt
+ * token becomes the current token; ctx = T - 1 afterwards and xinfer_spec_decoder_step continues from there.  Stands
+ * where the reference's chunked prefill does (forward_prefill_chunk, src/targets/qwen3_8/forward.cpp:402-554;
+ * prefill_chunk_size = 512, include/xinfer/engine.h:34; engine.cpp:330-398).  Synchronous; one GPU only. */
 XINFER_EXPORT int xinfer_spec_decoder_prefill(xinfer_spec_decoder* d, xinfer_stream_t stream, const int64_t* prompt_host,
                                               int64_t T);
 /* The device side of Engine::generate's speculative loop (src/runtime/engine.cpp:262-560) for `batch` prompts of one

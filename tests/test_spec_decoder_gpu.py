@@ -296,6 +296,41 @@ def test_generate_loop_against_the_oracle():
     dec.close()
 
 
+def test_long_prompt_prefill_runs_in_chunks():
+    """A prompt of 278 tokens per sequence, batch 2: the first chunk is 256 positions x 2 sequences = 512 rows (the
+    projections run on the prefill GEMM), the second 21 positions (42 rows, 32-row slices of the decode kernel); the
+    mixers take both four positions at a time.  Context, current token and last hidden state against the oracle's
+    sequential prefill, then speculative steps must emit the oracle's tokens (forced full acceptance first, which
+    reads the MTP head's cache slots that the prefill wrote)."""
+    from xinfer_b200.spec import Shape, SpecDecoder
+    shape_cfg = Shape(hidden_size=1024, intermediate_size=2048, num_hidden_layers=4, num_attention_heads=4,
+                      num_key_value_heads=2, vocab_size=4096, linear_num_v_heads=6, linear_num_k_heads=2)
+    import xinfer_b200.ops as ops
+    B, k, T = 2, 3, 278
+    dec = SpecDecoder(shape_cfg, batch=B, k=k, max_seq=400, seed=21)
+    # (a prompt whose last chunk is 160 rows as well: the last projection of the prefill ran on the GEMM)
+    dec.reset(0, seed=4)
+    dec.prefill(np.random.default_rng(5).integers(0, shape_cfg.vocab_size, size=(B, 1 + 256 + 80)).astype(np.int64))
+    assert ops.last_linear_path() == 3
+    dec.reset(0, seed=4)
+    model = pull_model(dec, shape_cfg, k)
+    seqs = pull_state(dec, model, shape_cfg, B, dec.max_seq)
+    prompt = np.random.default_rng(6).integers(0, shape_cfg.vocab_size, size=(B, T)).astype(np.int64)
+    dec.prefill(prompt)
+    for b in range(B):
+        model.prefill(seqs[b], prompt[b])
+    assert dec.tensor(-1, "ctx", np.int32).tolist() == [T - 1] * B
+    assert dec.tensor(-1, "cur_tok", np.int64).tolist() == prompt[:, -1].tolist()
+    h_gpu = dec.tensor(-1, "h_last", np.float16).reshape(B, shape_cfg.hidden_size)
+    for b in range(B):
+        assert rel_rms(h_gpu[b], seqs[b]["h_last"]) < 2e-2
+    cont = [model.greedy_continuation(seqs[b], k) for b in range(B)]
+    compare_step(dec, model, seqs, shape_cfg, cont, tag="chunked-accept-all")
+    compare_step(dec, model, seqs, shape_cfg, None, tag="chunked-free")
+    compare_step(dec, model, seqs, shape_cfg, None, tag="chunked-free2")
+    dec.close()
+
+
 def test_stochastic_drafting_and_acceptance_inside_the_step():
     """temperature 0.7: the step draws its draft tokens from the head's distribution and applies the reference's
     stochastic rule with Philox uniforms of (seed, step index); the oracle regenerates the same uniforms, samples with

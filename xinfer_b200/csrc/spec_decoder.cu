@@ -78,30 +78,41 @@ __global__ void add_int_kernel(int* out, const int* in, int n, int v) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) out[i] = in[i] + v;
 }
-// Prompt handling.  rows[b * R + i] = prompt[b][c0 + i]
-__global__ void gather_prompt_kernel(long long* rows, const long long* prompt, int batch, long long T, long long c0, int R) {
-    const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < batch * R) rows[i] = prompt[static_cast<long long>(i / R) * T + c0 + (i % R)];
-}
-// The hidden state in front of every row of a chunk: row (b, 0) <- h_last[b], row (b, i) <- x[b, i - 1].
-__global__ void shift_hidden_kernel(__half* out, const __half* h_last, const __half* x, int batch, int R, int H) {
-    const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
-    if (i >= static_cast<long long>(batch) * R * H) return;
-    const int col = static_cast<int>(i % H);
-    const long long row = i / H;
-    const int b = static_cast<int>(row / R), r = static_cast<int>(row % R);
-    out[i] = r == 0 ? h_last[static_cast<long long>(b) * H + col] : x[(row - 1) * H + col];
-}
-// h_last[b] <- x[b, R - 1]
-__global__ void take_last_hidden_kernel(__half* h_last, const __half* x, int batch, int R, int H) {
-    const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
-    if (i >= static_cast<long long>(batch) * H) return;
-    const int b = static_cast<int>(i / H), col = static_cast<int>(i % H);
-    h_last[i] = x[(static_cast<long long>(b) * R + R - 1) * H + col];
-}
 __global__ void last_prompt_token_kernel(long long* cur_tok, const long long* prompt, int batch, long long T) {
     const int b = blockIdx.x * blockDim.x + threadIdx.x;
     if (b < batch) cur_tok[b] = prompt[static_cast<long long>(b) * T + T - 1];
+}
+
+// Rows of a prefill chunk of Rc positions per sequence.  The mixer kernels take at most a few rows per sequence and
+// launch, laid out [sequence][row]; a projection does not care about the order of its rows.  So the chunk's rows are
+// stored group by group: group j holds positions 4j .. 4j+3 of every sequence as one contiguous [sequence][row] block,
+// which a mixer launch takes as it is.  Row of (position p, sequence b):
+__host__ __device__ inline long long chunk_row(int p, int b, int batch, int Rc) {
+    const int j = p >> 2, i = p & 3;
+    const int rj = (Rc - 4 * j) < 4 ? (Rc - 4 * j) : 4;
+    return static_cast<long long>(j) * batch * 4 + static_cast<long long>(b) * rj + i;
+}
+__global__ void gather_prompt_chunk_kernel(long long* rows, const long long* prompt, int batch, long long T, long long c0, int Rc) {
+    const int t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= batch * Rc) return;
+    const int b = t / Rc, p = t % Rc;
+    rows[chunk_row(p, b, batch, Rc)] = prompt[static_cast<long long>(b) * T + c0 + p];
+}
+// The hidden state in front of every row of a chunk: position 0 <- h_last[b], position p <- x at position p - 1.
+__global__ void shift_hidden_chunk_kernel(__half* out, const __half* h_last, const __half* x, int batch, int Rc, int H) {
+    const long long t = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (t >= static_cast<long long>(batch) * Rc * H) return;
+    const int col = static_cast<int>(t % H);
+    const long long bp = t / H;
+    const int b = static_cast<int>(bp / Rc), p = static_cast<int>(bp % Rc);
+    out[chunk_row(p, b, batch, Rc) * H + col] =
+        p == 0 ? h_last[static_cast<long long>(b) * H + col] : x[chunk_row(p - 1, b, batch, Rc) * H + col];
+}
+__global__ void take_last_hidden_chunk_kernel(__half* h_last, const __half* x, int batch, int Rc, int H) {
+    const long long t = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (t >= static_cast<long long>(batch) * H) return;
+    const int b = static_cast<int>(t / H), col = static_cast<int>(t % H);
+    h_last[t] = x[chunk_row(Rc - 1, b, batch, Rc) * H + col];
 }
 
 // A projection as this rank holds it: `n` output rows starting at row `row0` of the full [n_full][k] matrix
@@ -175,6 +186,14 @@ struct xinfer_spec_decoder {
     uint64_t sample_seed = 0;
     unsigned long long* step_counter = nullptr;
     float *uniforms = nullptr, *draft_probs = nullptr;
+    // activation rows of a prefill chunk (allocated by the first long prompt, freed with the decoder)
+    struct ChunkBufs {
+        int rows = 0;
+        __half *x = nullptr, *normed = nullptr, *proj_out = nullptr, *mlp = nullptr, *wide = nullptr, *wide2 = nullptr,
+               *qbuf = nullptr, *kbuf = nullptr, *vbuf = nullptr, *mix_out = nullptr, *zbuf = nullptr, *bbuf = nullptr,
+               *abuf = nullptr, *cat = nullptr, *hprev = nullptr;
+        long long* tokens = nullptr;
+    } chunk;
     float top_p = 1.0f;               // < 1: nucleus sampling on both sides of the stochastic rule
     xb::Nucleus* nucleus = nullptr;   // [batch * (k + 1)] nuclei of the verify rows
     int prev_rows = 0;       // rows of the previous target pass (for the lazy state commit)
@@ -621,7 +640,7 @@ int draft_pass(Dec* d, cudaStream_t s, int i, bool full) {
     return 0;
 }
 
-int target_pass(Dec* d, cudaStream_t s, int R, const long long* tokens, bool with_logits = true) {
+int target_pass(Dec* d, cudaStream_t s, int R, const long long* tokens) {
     const auto& c = d->cfg;
     const int M = d->batch * R, H = static_cast<int>(c.hidden_size);
     NL(xb::embed_rows(s, d->x, d->embed, tokens, M, H, c.vocab_size));
@@ -632,34 +651,146 @@ int target_pass(Dec* d, cudaStream_t s, int R, const long long* tokens, bool wit
         CK(layer_forward(d, s, d->layers[l], R, d->x, l + 1 < nl ? d->layers[l + 1].input_norm : d->final_norm, d->ctx,
                          d->n_commit, d->prev_rows));
     // `normed` now holds the final norm of the residual stream: LM head -> fp32 logits
-    if (with_logits) CK(lm_head_and_partials(d, s, M));
+    CK(lm_head_and_partials(d, s, M));
     if (!d->linears_only) d->prev_rows = R;
     return 0;
 }
 
-// The MTP head's KV slots of the R positions a prompt chunk has just gone through the target at: for every row the
-// head's pass up to its attention layer's cache write, from (token of the row, hidden state in front of the row).
-// One GPU only; the scratch rows live in activation buffers the target pass has finished with.
-int mtp_fill_rows(Dec* d, cudaStream_t s, int R, const long long* tokens, const __half* hprev_rows) {
+// ---------------------------------------------------------------------------------------------- prefill chunks
+// A prompt goes through the model in chunks of up to 512 rows (all sequences together), so that the projections see
+// M = hundreds of rows and run on the prefill GEMM; between them the mixers take the chunk four positions at a time
+// (their own row limit), which the row order of a chunk (chunk_row) makes contiguous blocks.  Natural feature order
+// everywhere (the permuted order of the decode step is a property of its 32-row kernel).
+
+int ensure_chunk_bufs(Dec* d, int rows) {
+    auto& cb = d->chunk;
+    if (cb.rows >= rows) return 0;
     const auto& c = d->cfg;
-    const int B = d->batch, M = B * R, H = static_cast<int>(c.hidden_size);
-    const int hkv = static_cast<int>(c.num_key_value_heads);
-    Layer& L = d->mtp_layer;
-    __half* emb = d->proj_out.p;
-    __half* cat = d->mlp.p;
-    XBuf xm;
-    xm.p = d->attn_out.p;
-    CK(xb::embed_rows(s, emb, d->embed, tokens, M, H, c.vocab_size));
-    CK(xb::rmsnorm_rows(s, cat, 2 * H, emb, d->mtp_enorm, M, H, c.rms_norm_eps, xperm_on()));
-    CK(xb::rmsnorm_rows(s, cat + H, 2 * H, hprev_rows, d->mtp_hnorm, M, H, c.rms_norm_eps, xperm_on()));
-    CK(lin(d, s, xm, cat, d->mtp_fc, M, kAll));
-    CK(xb::rmsnorm_rows(s, d->normed, H, xm.p, L.input_norm, M, H, c.rms_norm_eps, xperm_on()));
-    xb::TcProj fd[2] = {make_proj(d, L.k_proj, d->kbuf, kOwner), make_proj(d, L.v_proj, d->vbuf, kOwner)};
-    CK(run_lin(d, s, d->normed, fd, 2, false, false, M, H, d->bl * R, true));
-    CK(xb::attn_prep(s, d->qbuf, L.k_cache, L.v_cache, d->q_gate.p, d->kbuf.p, d->vbuf.p, L.q_norm, L.k_norm, d->ctx, B, R, 0,
-                     hkv, d->max_seq, c.rms_norm_eps, c.rope_theta, c.rope_dim));
+    const size_t H = static_cast<size_t>(c.hidden_size), F = static_cast<size_t>(c.intermediate_size);
+    const size_t hq = static_cast<size_t>(c.num_attention_heads), hkv = static_cast<size_t>(c.num_key_value_heads);
+    const size_t hv = static_cast<size_t>(c.linear_num_v_heads), hk = static_cast<size_t>(c.linear_num_k_heads);
+    const size_t ch = 2 * hk * 128 + hv * 128;
+    auto mx = [](size_t a, size_t b2) { return a > b2 ? a : b2; };
+    const size_t wide = mx(hq * 512, ch), mix = mx(mx(hq * 256, hv * 128), H);
+    const size_t per_row = 3 * H + F + wide + ch + hq * 256 + 2 * hkv * 256 + mix + hv * 128 + 2 * hv + 2 * H + H;
+    const size_t halves = (per_row + 64) * static_cast<size_t>(rows);
+    if (cb.x) { cudaFree(cb.x); cb = Dec::ChunkBufs(); }
+    __half* base = nullptr;
+    if (cudaMalloc(&base, halves * sizeof(__half) + static_cast<size_t>(rows) * sizeof(long long) + 256) != cudaSuccess) {
+        cudaGetLastError();
+        return XINFER_ERR_OUT_OF_MEMORY;
+    }
+    size_t off = 0;
+    auto take = [&](size_t per) {
+        __half* ptr = base + off;
+        off += (per * static_cast<size_t>(rows) + 63) & ~static_cast<size_t>(63);   // 128-byte aligned (TMA, vector loads)
+        return ptr;
+    };
+    cb.x = take(H); cb.normed = take(H); cb.proj_out = take(H); cb.mlp = take(F); cb.wide = take(wide); cb.wide2 = take(ch);
+    cb.qbuf = take(hq * 256); cb.kbuf = take(hkv * 256); cb.vbuf = take(hkv * 256); cb.mix_out = take(mix);
+    cb.zbuf = take(hv * 128); cb.bbuf = take(hv); cb.abuf = take(hv); cb.cat = take(2 * H); cb.hprev = take(H);
+    cb.tokens = reinterpret_cast<long long*>(base + ((off + 63) & ~static_cast<size_t>(63)));
+    cb.rows = rows;
     return 0;
 }
+
+#define LIN(expr)                                                        \
+    do {                                                                 \
+        const int lrc_ = (expr);                                         \
+        if (lrc_ < 0) { d->error = "prefill: a projection failed"; return lrc_; } \
+    } while (0)
+
+// One chunk: positions c0 .. c0 + Rc - 1 of every sequence through the target model and into the MTP head's cache.
+// `prev_r`: rows per sequence of the mixer launch in front of this chunk's first one (0 at the start of a prompt).
+int prefill_chunk(Dec* d, cudaStream_t s, const long long* prompt, int64_t T, int64_t c0, int Rc, int* prev_r) {
+    const auto& c = d->cfg;
+    auto& cb = d->chunk;
+    const int B = d->batch, M = B * Rc, H = static_cast<int>(c.hidden_size), F = static_cast<int>(c.intermediate_size);
+    const int hq = static_cast<int>(c.num_attention_heads), hkv = static_cast<int>(c.num_key_value_heads);
+    const int hv = static_cast<int>(c.linear_num_v_heads), hk = static_cast<int>(c.linear_num_k_heads);
+    const int ch = 2 * hk * 128 + hv * 128, groups = (Rc + 3) / 4;
+    const float eps = c.rms_norm_eps;
+    void* st = s;
+    auto desc = [](void* y, const Linear& l) {
+        xinfer_fused_desc f;
+        f.Y = y; f.W_int4 = l.w; f.scales = l.s; f.bias = nullptr; f.N = l.n;
+        return f;
+    };
+    gather_prompt_chunk_kernel<<<blocks_for(static_cast<size_t>(M), 128), 128, 0, s>>>(cb.tokens, prompt, B, T, c0, Rc);
+    NL(xb::embed_rows(s, cb.x, d->embed, cb.tokens, M, H, c.vocab_size));
+    NL(xb::rmsnorm_rows(s, cb.normed, H, cb.x, d->layers[0].input_norm, M, H, eps, 0));
+    const size_t nl = d->layers.size();
+    int last_r = *prev_r;
+    for (size_t l = 0; l < nl; ++l) {
+        Layer& L = d->layers[l];
+        if (L.full) {
+            const xinfer_fused_desc fd[3] = {desc(cb.wide, L.q_proj), desc(cb.kbuf, L.k_proj), desc(cb.vbuf, L.v_proj)};
+            LIN(xinfer_linear_int4_fused_f16(st, cb.normed, fd, 3, M, H, 128));
+            for (int j = 0; j < groups; ++j) {
+                const int rj = Rc - 4 * j < 4 ? Rc - 4 * j : 4;
+                const size_t r0 = static_cast<size_t>(j) * B * 4;
+                const int pos0 = static_cast<int>(c0) + 4 * j;
+                NL(xb::attn_prep_ex(s, cb.qbuf + r0 * hq * 256, L.k_cache, L.v_cache, cb.wide + r0 * hq * 512, cb.kbuf + r0 * hkv * 256,
+                                    cb.vbuf + r0 * hkv * 256, L.q_norm, L.k_norm, nullptr, B, rj, hq, hkv, d->max_seq, eps,
+                                    c.rope_theta, c.rope_dim, 512, nullptr, pos0, nullptr));
+                NL(xb::attn_decode_ex(s, cb.mix_out + r0 * hq * 256, cb.qbuf + r0 * hq * 256, cb.wide + r0 * hq * 512, L.k_cache,
+                                      L.v_cache, nullptr, B, rj, hq, hkv, d->max_seq, d->attn_splits, d->attn_scratch,
+                                      1.0f / sqrtf(256.0f), pos0, 0));
+            }
+            LIN(xinfer_linear_int4_f16f16(st, cb.proj_out, cb.mix_out, L.o_proj.w, L.o_proj.s, nullptr, M, L.o_proj.n, L.o_proj.k, 128));
+        } else {
+            const xinfer_fused_desc fd[4] = {desc(cb.wide, L.in_qkv), desc(cb.zbuf, L.in_z), desc(cb.bbuf, L.in_b), desc(cb.abuf, L.in_a)};
+            LIN(xinfer_linear_int4_fused_f16(st, cb.normed, fd, 4, M, H, 128));
+            int pr = *prev_r;
+            for (int j = 0; j < groups; ++j) {
+                const int rj = Rc - 4 * j < 4 ? Rc - 4 * j : 4;
+                const size_t r0 = static_cast<size_t>(j) * B * 4;
+                // every row of the launch in front stays: it is committed to the state before these rows run
+                NL(xb::conv1d_spec(s, cb.wide2 + r0 * ch, cb.wide + r0 * ch, L.conv_w, L.conv_state, L.conv_pend, nullptr, B, rj, pr,
+                                   ch, pr, 0));
+                NL(xb::gdn_spec(s, cb.mix_out + r0 * hv * 128, cb.wide2 + r0 * ch, cb.zbuf + r0 * hv * 128, cb.bbuf + r0 * hv,
+                                cb.abuf + r0 * hv, L.A_log, L.dt_bias, L.gdn_norm, L.S, L.pend_k, L.pend_d, L.pend_g, nullptr, B, rj,
+                                pr, hv, hk, pr, 0, 0));
+                pr = rj;
+            }
+            last_r = pr;
+            LIN(xinfer_linear_int4_f16f16(st, cb.proj_out, cb.mix_out, L.out_proj.w, L.out_proj.s, nullptr, M, L.out_proj.n,
+                                          L.out_proj.k, 128));
+        }
+        NL(xb::add_rmsnorm_rows(s, cb.normed, cb.x, cb.proj_out, L.post_norm, M, H, eps, 0));
+        LIN(xinfer_mlp_gate_up_swiglu_int4_f16(st, cb.mlp, cb.normed, L.gate.w, L.gate.s, L.up.w, L.up.s, M, L.gate.n, H, 128));
+        LIN(xinfer_linear_int4_f16f16(st, cb.proj_out, cb.mlp, L.down.w, L.down.s, nullptr, M, L.down.n, F, 128));
+        NL(xb::add_rmsnorm_rows(s, cb.normed, cb.x, cb.proj_out, l + 1 < nl ? d->layers[l + 1].input_norm : d->final_norm, M, H, eps, 0));
+    }
+    {
+        const int rl = Rc - 4 * (groups - 1);
+        *prev_r = rl < 4 ? rl : 4;
+        (void)last_r;
+    }
+    // the MTP head's KV slots of the same positions: (token of the row, hidden state in front of the row) -> fc ->
+    // input norm -> k, v projections -> head norm, RoPE, cache write
+    Layer& ML = d->mtp_layer;
+    const size_t nH = static_cast<size_t>(M) * H;
+    shift_hidden_chunk_kernel<<<blocks_for(nH, 256), 256, 0, s>>>(cb.hprev, d->h_last, cb.x, B, Rc, H);
+    NL(xb::embed_rows(s, cb.proj_out, d->embed, cb.tokens, M, H, c.vocab_size));
+    NL(xb::rmsnorm_rows(s, cb.cat, 2 * H, cb.proj_out, d->mtp_enorm, M, H, eps, 0));
+    NL(xb::rmsnorm_rows(s, cb.cat + H, 2 * H, cb.hprev, d->mtp_hnorm, M, H, eps, 0));
+    LIN(xinfer_linear_int4_f16f16(st, cb.mix_out, cb.cat, d->mtp_fc.w, d->mtp_fc.s, nullptr, M, d->mtp_fc.n, d->mtp_fc.k, 128));
+    NL(xb::rmsnorm_rows(s, cb.normed, H, cb.mix_out, ML.input_norm, M, H, eps, 0));
+    const xinfer_fused_desc kv[2] = {desc(cb.kbuf, ML.k_proj), desc(cb.vbuf, ML.v_proj)};
+    LIN(xinfer_linear_int4_fused_f16(st, cb.normed, kv, 2, M, H, 128));
+    for (int j = 0; j < groups; ++j) {
+        const int rj = Rc - 4 * j < 4 ? Rc - 4 * j : 4;
+        const size_t r0 = static_cast<size_t>(j) * B * 4;
+        NL(xb::attn_prep_ex(s, cb.qbuf, ML.k_cache, ML.v_cache, cb.wide, cb.kbuf + r0 * hkv * 256, cb.vbuf + r0 * hkv * 256, ML.q_norm,
+                            ML.k_norm, nullptr, B, rj, 0, hkv, d->max_seq, eps, c.rope_theta, c.rope_dim, 512, nullptr,
+                            static_cast<int>(c0) + 4 * j, nullptr));
+    }
+    take_last_hidden_chunk_kernel<<<blocks_for(static_cast<size_t>(B) * H, 256), 256, 0, s>>>(d->h_last, cb.x, B, Rc, H);
+    CKCUDA(cudaGetLastError());
+    return 0;
+}
+#undef LIN
 
 int enqueue_step(Dec* d, cudaStream_t s) {
     const auto& c = d->cfg;
@@ -807,6 +938,7 @@ void xinfer_spec_decoder_destroy(xinfer_spec_decoder* d) {
     if (d->graph) cudaGraphDestroy(d->graph);
     if (d->plan) xb::tc_plan_delete(d->plan);  // the recorded plan points into this decoder's weights
     if (d->arena) xinfer_arena_destroy(d->arena);
+    if (d->chunk.x) cudaFree(d->chunk.x);
     if (d->h_emitted) cudaFreeHost(d->h_emitted);
     if (d->h_emitted_n) cudaFreeHost(d->h_emitted_n);
     delete d;
@@ -990,52 +1122,52 @@ int xinfer_spec_decoder_set_top_p(xinfer_spec_decoder* d, float top_p) {
 }
 
 // Builds the context from a prompt: tokens [batch][T] (host), all sequences the same length, starting from the empty
-// context of reset(0, seed).  Positions 0 .. T-2 go through the target model in chunks of k + 1 rows (the verify
-// pass's own kernels with every row kept: KV caches, Gated-DeltaNet and convolution state advance as in a step whose
-// drafts were all accepted), the MTP head's KV slots of the same positions are written from (token, hidden state in
-// front of it; zeros in front of position 0), and the last prompt token becomes the current token.  Afterwards
-// ctx = T - 1 and xinfer_spec_decoder_step continues from there.  Stands where the reference's prefill loop does
-// (forward_prefill_chunk, src/targets/qwen3_8/forward.cpp:402-554, called from engine.cpp:330-398) but runs at the
-// decode kernels' row count, not in 512-row chunks.  One GPU only.
+// context of reset(0, seed).  Positions 0 .. T-2 go through the target model in chunks of up to 512 rows over all
+// sequences (prefill_chunk: projections on the prefill GEMM, mixers four positions at a time with every row kept,
+// so KV caches, Gated-DeltaNet and convolution state advance as in steps whose drafts were all accepted), the MTP
+// head's KV slots of the same positions are written from (token, hidden state in front of it; zeros in front of
+// position 0), and the last prompt token becomes the current token.  Afterwards ctx = T - 1 and
+// xinfer_spec_decoder_step continues from there.  Stands where the reference's chunked prefill does
+// (forward_prefill_chunk, src/targets/qwen3_8/forward.cpp:402-554, called from engine.cpp:330-398).  One GPU only.
 int xinfer_spec_decoder_prefill(xinfer_spec_decoder* d, xinfer_stream_t stream, const int64_t* prompt_host, int64_t T) {
     if (!d || !prompt_host || T < 1) return XINFER_ERR_INVALID_ARGUMENT;
-    const auto& c = d->cfg;
-    const int B = d->batch, R = d->k + 1, H = static_cast<int>(c.hidden_size);
+    const int B = d->batch, R = d->k + 1, H = static_cast<int>(d->cfg.hidden_size);
     if (d->world > 1) { d->error = "prefill runs on one GPU"; return XINFER_ERR_INVALID_ARGUMENT; }
     if (d->ctx_upper != 0) { d->error = "prefill starts from the empty context (reset(0, seed))"; return XINFER_ERR_INVALID_ARGUMENT; }
     if (T - 1 + 2 * R > d->max_seq) { d->error = "prompt does not fit the cache"; return XINFER_ERR_INVALID_ARGUMENT; }
-    if (c.intermediate_size < 2 * c.hidden_size || c.num_attention_heads * 256 < c.hidden_size) {
-        d->error = "prefill borrows activation buffers that this shape makes too small";
-        return XINFER_ERR_INVALID_ARGUMENT;
-    }
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // positions per sequence and chunk: 512 rows over all sequences, a multiple of the mixers' four
+    int Cp = (512 / B) & ~3;
+    if (Cp < 4) Cp = 4;
+    if (T - 1 < Cp) Cp = static_cast<int>(((T - 1) + 3) & ~3LL);
+    if (Cp > 0) {
+        int rc0 = ensure_chunk_bufs(d, B * Cp);
+        if (rc0 < 0) return rc0;
+    }
     long long* prompt = nullptr;
     const size_t pbytes = static_cast<size_t>(B) * T * sizeof(long long);
     if (cudaMalloc(&prompt, pbytes) != cudaSuccess) { cudaGetLastError(); return XINFER_ERR_OUT_OF_MEMORY; }
+    int prev_r = 0;
     int rc = [&]() -> int {
         CKCUDA(cudaMemcpyAsync(prompt, prompt_host, pbytes, cudaMemcpyHostToDevice, s));
         CKCUDA(cudaMemsetAsync(d->h_last, 0, static_cast<size_t>(B) * H * sizeof(__half), s));
-        CK(xb::fill_int(s, d->n_commit, B, 0));
-        d->prev_rows = 0;
-        __half* hprev_rows = d->q_gate.p;
-        for (long long c0 = 0; c0 < T - 1; c0 += R) {
-            const int Rp = static_cast<int>((T - 1 - c0) < R ? (T - 1 - c0) : R);
-            gather_prompt_kernel<<<blocks_for(static_cast<size_t>(B) * Rp, 64), 64, 0, s>>>(d->verify_tokens, prompt, B, T, c0, Rp);
-            CK(target_pass(d, s, Rp, d->verify_tokens, false));
-            const size_t n = static_cast<size_t>(B) * Rp * H;
-            shift_hidden_kernel<<<blocks_for(n, 256), 256, 0, s>>>(hprev_rows, d->h_last, d->x, B, Rp, H);
-            CK(mtp_fill_rows(d, s, Rp, d->verify_tokens, hprev_rows));
-            take_last_hidden_kernel<<<blocks_for(static_cast<size_t>(B) * H, 256), 256, 0, s>>>(d->h_last, d->x, B, Rp, H);
-            add_int_kernel<<<1, 64, 0, s>>>(d->ctx, d->ctx, B, Rp);
-            CK(xb::fill_int(s, d->n_commit, B, Rp));  // every row of the chunk stays: the next pass replays all of them
+        for (long long c0 = 0; c0 < T - 1; c0 += Cp) {
+            const int Rc = static_cast<int>((T - 1 - c0) < Cp ? (T - 1 - c0) : Cp);
+            CK(prefill_chunk(d, s, prompt, T, c0, Rc, &prev_r));
         }
+        // as after a step whose rows were all kept: the last mixer launch's rows are replayed by the next pass
+        CK(xb::fill_int(s, d->ctx, B, static_cast<int>(T - 1)));
+        CK(xb::fill_int(s, d->n_commit, B, prev_r));
         last_prompt_token_kernel<<<1, 64, 0, s>>>(d->cur_tok, prompt, B, T);
         CKCUDA(cudaGetLastError());
         CKCUDA(cudaStreamSynchronize(s));
         return XINFER_OK;
     }();
     cudaFree(prompt);
-    if (rc == XINFER_OK) d->ctx_upper = T - 1;
+    if (rc == XINFER_OK) {
+        d->prev_rows = prev_r;
+        d->ctx_upper = T - 1;
+    }
     return rc;
 }
 
