@@ -764,6 +764,152 @@ __global__ void __launch_bounds__(512, 2) gdn_spec_kernel(__half* out, const __h
     }
 }
 
+// ------------------------------------------------------------------------------- the same two mixers over a prompt chunk
+// Prefill keeps every row, so there is nothing to replay or to hold back: one launch walks all `rc` positions of a
+// chunk with the state in registers and writes the state back once (the step kernels above would need rc / 4 launches,
+// each re-reading and re-writing the state).  Rows are found through chunk_row (the chunk's group-by-group row
+// order).  Per token the arithmetic is the step kernels', operation by operation, so the results are bit-identical.
+__global__ void conv1d_chunk_kernel(__half* out, const __half* in, const float* conv_w, float* state, int rc, int channels) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    const int b = blockIdx.y, batch = gridDim.y;
+    if (c >= channels) return;
+    float* st = state + static_cast<long long>(b) * 3 * channels;
+    float s0 = st[c], s1 = st[channels + c], s2 = st[2 * channels + c];
+    const float w0 = conv_w[c * 4], w1 = conv_w[c * 4 + 1], w2 = conv_w[c * 4 + 2], w3 = conv_w[c * 4 + 3];
+    for (int p = 0; p < rc; ++p) {
+        const long long row = chunk_row(p, b, batch, rc);
+        const float x = __half2float(in[row * channels + c]);
+        const float sum = w0 * s0 + w1 * s1 + w2 * s2 + w3 * x;
+        out[row * channels + c] = __float2half_rn(sum / (1.0f + expf(-sum)));
+        s0 = s1;
+        s1 = s2;
+        s2 = x;
+    }
+    st[c] = s0;
+    st[channels + c] = s1;
+    st[2 * channels + c] = s2;
+}
+
+__global__ void __launch_bounds__(512, 2) gdn_chunk_kernel(__half* out, const __half* qkv, const __half* z,
+                                                           const __half* bb, const __half* aa, const float* A_log,
+                                                           const float* dt_bias, const float* norm_w, float* state, int rc,
+                                                           int hv, int hk) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    __shared__ __align__(16) float sh_q[8][128], sh_k[8][128];
+    __shared__ float sh_beta[8], sh_eg[8], red[2][16];
+    __shared__ float part_sum[2][4][128], attn_all[8][4][128];
+    const int h = blockIdx.x, b = blockIdx.y, batch = gridDim.y;
+    const int j = threadIdx.x & 127, part = threadIdx.x >> 7;
+    const int lane = threadIdx.x & 31, wig = (threadIdx.x >> 5) & 3;
+    const int i0 = part * 32;
+    const int h_k = h / (hv / hk);
+    const int channels = 2 * hk * 128 + hv * 128;
+    const int value_dim = hv * 128;
+    float* S = state + (static_cast<long long>(b) * hv + h) * (128 * 128);
+    float col[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) col[i] = S[(i0 + i) * 128 + j];
+    const float exp_a_log = expf(A_log[h]);
+    const float dtb = dt_bias[h];
+
+    for (int p0 = 0; p0 < rc; p0 += 8) {
+        const int nb = rc - p0 < 8 ? rc - p0 : 8;
+        // ---- phase 0: per-token quantities that do not depend on the state (token tt handled by thread group tt % 4)
+        for (int t0 = 0; t0 < nb; t0 += 4) {
+            const int tt = t0 + part;
+            float raw_q = 0.f, raw_k = 0.f;
+            if (tt < nb) {
+                const __half* cur = qkv + chunk_row(p0 + tt, b, batch, rc) * channels;
+                raw_q = __half2float(cur[h_k * 128 + j]);
+                raw_k = __half2float(cur[hk * 128 + h_k * 128 + j]);
+            }
+            const float wq = warp_sum(raw_q * raw_q), wk = warp_sum(raw_k * raw_k);
+            __syncthreads();
+            if (lane == 0) { red[0][part * 4 + wig] = wq; red[1][part * 4 + wig] = wk; }
+            __syncthreads();
+            if (tt < nb) {
+                const float q_sq = ((red[0][part * 4] + red[0][part * 4 + 1]) + red[0][part * 4 + 2]) + red[0][part * 4 + 3];
+                const float k_sq = ((red[1][part * 4] + red[1][part * 4 + 1]) + red[1][part * 4 + 2]) + red[1][part * 4 + 3];
+                sh_q[tt][j] = (raw_q * (1.0f / sqrtf(q_sq + 1e-6f))) * 0.08838834764f;
+                sh_k[tt][j] = raw_k * (1.0f / sqrtf(k_sq + 1e-6f));
+                if (j == 0) {
+                    const long long row = chunk_row(p0 + tt, b, batch, rc);
+                    const float b_val = __half2float(bb[row * hv + h]);
+                    sh_beta[tt] = 1.0f / (1.0f + expf(-b_val));
+                    const float a_val = __half2float(aa[row * hv + h]) + dtb;
+                    const float softplus = (a_val > 20.0f) ? a_val : logf(1.0f + expf(a_val));
+                    sh_eg[tt] = expf(-exp_a_log * softplus);
+                }
+            }
+        }
+        __syncthreads();
+
+        // ---- phase 1: the recurrence
+        for (int t = 0; t < nb; ++t) {
+            const long long row = chunk_row(p0 + t, b, batch, rc);
+            const float v = __half2float(qkv[row * channels + 2 * hk * 128 + h * 128 + j]);
+            const float eg = sh_eg[t];
+            float kv_mem = 0.f;
+            const float4* k4 = reinterpret_cast<const float4*>(&sh_k[t][i0]);
+            const float4* q4 = reinterpret_cast<const float4*>(&sh_q[t][i0]);
+#pragma unroll
+            for (int m = 0; m < 8; ++m) {
+                const float4 kk = k4[m];
+                const float kv[4] = {kk.x, kk.y, kk.z, kk.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float sv = col[m * 4 + e] * eg;
+                    col[m * 4 + e] = sv;
+                    kv_mem += sv * kv[e];
+                }
+            }
+            part_sum[t & 1][part][j] = kv_mem;
+            __syncthreads();
+            const float* ps = &part_sum[t & 1][0][j];
+            const float delta = (v - (((ps[0] + ps[128]) + ps[256]) + ps[384])) * sh_beta[t];
+            float attn = 0.f;
+#pragma unroll
+            for (int m = 0; m < 8; ++m) {
+                const float4 kk = k4[m], qq = q4[m];
+                const float kv[4] = {kk.x, kk.y, kk.z, kk.w}, qv[4] = {qq.x, qq.y, qq.z, qq.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float ns = col[m * 4 + e] + kv[e] * delta;
+                    col[m * 4 + e] = ns;
+                    attn += ns * qv[e];
+                }
+            }
+            attn_all[t][part][j] = attn;
+        }
+        __syncthreads();
+
+        // ---- phase 2: gated RMSNorm of every token's output (token tt handled by thread group tt % 4)
+        for (int t0 = 0; t0 < nb; t0 += 4) {
+            const int tt = t0 + part;
+            float attn = 0.f;
+            if (tt < nb) attn = ((attn_all[tt][0][j] + attn_all[tt][1][j]) + attn_all[tt][2][j]) + attn_all[tt][3][j];
+            const float wsq = warp_sum(attn * attn);
+            __syncthreads();
+            if (lane == 0) red[0][part * 4 + wig] = wsq;
+            __syncthreads();
+            if (tt < nb) {
+                const float sq = ((red[0][part * 4] + red[0][part * 4 + 1]) + red[0][part * 4 + 2]) + red[0][part * 4 + 3];
+                const float inv_std = 1.0f / sqrtf(sq / 128.0f + 1e-6f);
+                const long long row = chunk_row(p0 + tt, b, batch, rc);
+                const float zv = __half2float(z[row * value_dim + h * 128 + j]);
+                const float silu_z = zv / (1.0f + expf(-zv));
+                out[row * value_dim + h * 128 + j] = __float2half_rn(attn * inv_std * norm_w[j] * silu_z);
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 32; ++i) S[(i0 + i) * 128 + j] = col[i];
+}
+
 // ------------------------------------------------------------------------------- speculative bookkeeping
 struct AcceptRec {
     long long bonus;
@@ -911,6 +1057,20 @@ int gdn_spec(cudaStream_t s, __half* out, const __half* qkv, const __half* z, co
     dim3 grid(hv, batch);
     launch_pdl(gdn_spec_kernel, dim3(grid), dim3(512), 0, s, out, qkv, z, b, a, A_log, dt_bias, norm_w, state, pend_k, pend_d, pend_g,
                                          n_commit, rows_per_seq, prev_rows, hv, hk, nc_base, early_state, perm_out);
+    return XB_LAUNCH_OK();
+}
+
+int conv1d_chunk(cudaStream_t s, __half* out, const __half* in, const float* conv_w, float* state, int batch, int rc,
+                 int channels) {
+    dim3 grid((channels + 255) / 256, batch);
+    launch_pdl(conv1d_chunk_kernel, dim3(grid), dim3(256), 0, s, out, in, conv_w, state, rc, channels);
+    return XB_LAUNCH_OK();
+}
+
+int gdn_chunk(cudaStream_t s, __half* out, const __half* qkv, const __half* z, const __half* b, const __half* a,
+              const float* A_log, const float* dt_bias, const float* norm_w, float* state, int batch, int rc, int hv, int hk) {
+    dim3 grid(hv, batch);
+    launch_pdl(gdn_chunk_kernel, dim3(grid), dim3(512), 0, s, out, qkv, z, b, a, A_log, dt_bias, norm_w, state, rc, hv, hk);
     return XB_LAUNCH_OK();
 }
 

@@ -54,6 +54,22 @@ int gdn_spec(cudaStream_t s, __half* out, const __half* qkv, const __half* z, co
              float* pend_g, const int* n_commit, int batch, int rows_per_seq, int prev_rows, int hv, int hk, int nc_base = 0,
              int early_state = 0, int perm_out = 0);
 
+// Row of (position p, sequence b) in a prefill chunk of rc positions per sequence.  The step's mixer kernels take at
+// most a few rows per sequence and launch, laid out [sequence][row]; a projection does not care about the order of its
+// rows.  So a chunk's rows are stored group by group: group j holds positions 4j .. 4j+3 of every sequence as one
+// contiguous [sequence][row] block, which such a launch takes as it is.
+__host__ __device__ inline long long chunk_row(int p, int b, int batch, int rc) {
+    const int j = p >> 2, i = p & 3;
+    const int rj = (rc - 4 * j) < 4 ? (rc - 4 * j) : 4;
+    return static_cast<long long>(j) * batch * 4 + static_cast<long long>(b) * rj + i;
+}
+// The convolution and the gated delta rule over all rc positions of a prefill chunk in one launch each (rows in
+// chunk_row order, every row kept, the state read once and written back once; nothing pending afterwards).
+int conv1d_chunk(cudaStream_t s, __half* out, const __half* in, const float* conv_w, float* state, int batch, int rc,
+                 int channels);
+int gdn_chunk(cudaStream_t s, __half* out, const __half* qkv, const __half* z, const __half* b, const __half* a,
+              const float* A_log, const float* dt_bias, const float* norm_w, float* state, int batch, int rc, int hv, int hk);
+
 int spec_commit(cudaStream_t s, const void* accept_records, const long long* draft_tokens, int batch, int k,
                 int rows_per_seq, int* ctx, int* n_commit, long long* cur_tok, long long* emitted, int* emitted_n,
                 __half* h_last, const __half* hidden_rows, int hidden);

@@ -83,20 +83,12 @@ __global__ void last_prompt_token_kernel(long long* cur_tok, const long long* pr
     if (b < batch) cur_tok[b] = prompt[static_cast<long long>(b) * T + T - 1];
 }
 
-// Rows of a prefill chunk of Rc positions per sequence.  The mixer kernels take at most a few rows per sequence and
-// launch, laid out [sequence][row]; a projection does not care about the order of its rows.  So the chunk's rows are
-// stored group by group: group j holds positions 4j .. 4j+3 of every sequence as one contiguous [sequence][row] block,
-// which a mixer launch takes as it is.  Row of (position p, sequence b):
-__host__ __device__ inline long long chunk_row(int p, int b, int batch, int Rc) {
-    const int j = p >> 2, i = p & 3;
-    const int rj = (Rc - 4 * j) < 4 ? (Rc - 4 * j) : 4;
-    return static_cast<long long>(j) * batch * 4 + static_cast<long long>(b) * rj + i;
-}
+// Prefill chunks: rows in chunk_row order (mixers.h).
 __global__ void gather_prompt_chunk_kernel(long long* rows, const long long* prompt, int batch, long long T, long long c0, int Rc) {
     const int t = blockIdx.x * blockDim.x + threadIdx.x;
     if (t >= batch * Rc) return;
     const int b = t / Rc, p = t % Rc;
-    rows[chunk_row(p, b, batch, Rc)] = prompt[static_cast<long long>(b) * T + c0 + p];
+    rows[xb::chunk_row(p, b, batch, Rc)] = prompt[static_cast<long long>(b) * T + c0 + p];
 }
 // The hidden state in front of every row of a chunk: position 0 <- h_last[b], position p <- x at position p - 1.
 __global__ void shift_hidden_chunk_kernel(__half* out, const __half* h_last, const __half* x, int batch, int Rc, int H) {
@@ -105,14 +97,14 @@ __global__ void shift_hidden_chunk_kernel(__half* out, const __half* h_last, con
     const int col = static_cast<int>(t % H);
     const long long bp = t / H;
     const int b = static_cast<int>(bp / Rc), p = static_cast<int>(bp % Rc);
-    out[chunk_row(p, b, batch, Rc) * H + col] =
-        p == 0 ? h_last[static_cast<long long>(b) * H + col] : x[chunk_row(p - 1, b, batch, Rc) * H + col];
+    out[xb::chunk_row(p, b, batch, Rc) * H + col] =
+        p == 0 ? h_last[static_cast<long long>(b) * H + col] : x[xb::chunk_row(p - 1, b, batch, Rc) * H + col];
 }
 __global__ void take_last_hidden_chunk_kernel(__half* h_last, const __half* x, int batch, int Rc, int H) {
     const long long t = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (t >= static_cast<long long>(batch) * H) return;
     const int b = static_cast<int>(t / H), col = static_cast<int>(t % H);
-    h_last[t] = x[chunk_row(Rc - 1, b, batch, Rc) * H + col];
+    h_last[t] = x[xb::chunk_row(Rc - 1, b, batch, Rc) * H + col];
 }
 
 // A projection as this rank holds it: `n` output rows starting at row `row0` of the full [n_full][k] matrix
@@ -658,9 +650,10 @@ int target_pass(Dec* d, cudaStream_t s, int R, const long long* tokens) {
 
 // ---------------------------------------------------------------------------------------------- prefill chunks
 // A prompt goes through the model in chunks of up to 512 rows (all sequences together), so that the projections see
-// M = hundreds of rows and run on the prefill GEMM; between them the mixers take the chunk four positions at a time
-// (their own row limit), which the row order of a chunk (chunk_row) makes contiguous blocks.  Natural feature order
-// everywhere (the permuted order of the decode step is a property of its 32-row kernel).
+// M = hundreds of rows and run on the prefill GEMM.  Between them the attention kernels take the chunk four positions
+// at a time (their own row limit), which the row order of a chunk (chunk_row) makes contiguous blocks; the convolution
+// and the gated delta rule walk the whole chunk in one launch each (conv1d_chunk, gdn_chunk).  Natural feature
+// order everywhere (the permuted order of the decode step is a property of its 32-row kernel).
 
 int ensure_chunk_bufs(Dec* d, int rows) {
     auto& cb = d->chunk;
@@ -701,7 +694,7 @@ int ensure_chunk_bufs(Dec* d, int rows) {
     } while (0)
 
 // One chunk: positions c0 .. c0 + Rc - 1 of every sequence through the target model and into the MTP head's cache.
-// `prev_r`: rows per sequence of the mixer launch in front of this chunk's first one (0 at the start of a prompt).
+// `prev_r` comes back as the number of recurrent updates left pending for the next pass (none).
 int prefill_chunk(Dec* d, cudaStream_t s, const long long* prompt, int64_t T, int64_t c0, int Rc, int* prev_r) {
     const auto& c = d->cfg;
     auto& cb = d->chunk;
@@ -720,7 +713,6 @@ int prefill_chunk(Dec* d, cudaStream_t s, const long long* prompt, int64_t T, in
     NL(xb::embed_rows(s, cb.x, d->embed, cb.tokens, M, H, c.vocab_size));
     NL(xb::rmsnorm_rows(s, cb.normed, H, cb.x, d->layers[0].input_norm, M, H, eps, 0));
     const size_t nl = d->layers.size();
-    int last_r = *prev_r;
     for (size_t l = 0; l < nl; ++l) {
         Layer& L = d->layers[l];
         if (L.full) {
@@ -741,19 +733,8 @@ int prefill_chunk(Dec* d, cudaStream_t s, const long long* prompt, int64_t T, in
         } else {
             const xinfer_fused_desc fd[4] = {desc(cb.wide, L.in_qkv), desc(cb.zbuf, L.in_z), desc(cb.bbuf, L.in_b), desc(cb.abuf, L.in_a)};
             LIN(xinfer_linear_int4_fused_f16(st, cb.normed, fd, 4, M, H, 128));
-            int pr = *prev_r;
-            for (int j = 0; j < groups; ++j) {
-                const int rj = Rc - 4 * j < 4 ? Rc - 4 * j : 4;
-                const size_t r0 = static_cast<size_t>(j) * B * 4;
-                // every row of the launch in front stays: it is committed to the state before these rows run
-                NL(xb::conv1d_spec(s, cb.wide2 + r0 * ch, cb.wide + r0 * ch, L.conv_w, L.conv_state, L.conv_pend, nullptr, B, rj, pr,
-                                   ch, pr, 0));
-                NL(xb::gdn_spec(s, cb.mix_out + r0 * hv * 128, cb.wide2 + r0 * ch, cb.zbuf + r0 * hv * 128, cb.bbuf + r0 * hv,
-                                cb.abuf + r0 * hv, L.A_log, L.dt_bias, L.gdn_norm, L.S, L.pend_k, L.pend_d, L.pend_g, nullptr, B, rj,
-                                pr, hv, hk, pr, 0, 0));
-                pr = rj;
-            }
-            last_r = pr;
+            NL(xb::conv1d_chunk(s, cb.wide2, cb.wide, L.conv_w, L.conv_state, B, Rc, ch));
+            NL(xb::gdn_chunk(s, cb.mix_out, cb.wide2, cb.zbuf, cb.bbuf, cb.abuf, L.A_log, L.dt_bias, L.gdn_norm, L.S, B, Rc, hv, hk));
             LIN(xinfer_linear_int4_f16f16(st, cb.proj_out, cb.mix_out, L.out_proj.w, L.out_proj.s, nullptr, M, L.out_proj.n,
                                           L.out_proj.k, 128));
         }
@@ -762,11 +743,7 @@ int prefill_chunk(Dec* d, cudaStream_t s, const long long* prompt, int64_t T, in
         LIN(xinfer_linear_int4_f16f16(st, cb.proj_out, cb.mlp, L.down.w, L.down.s, nullptr, M, L.down.n, F, 128));
         NL(xb::add_rmsnorm_rows(s, cb.normed, cb.x, cb.proj_out, l + 1 < nl ? d->layers[l + 1].input_norm : d->final_norm, M, H, eps, 0));
     }
-    {
-        const int rl = Rc - 4 * (groups - 1);
-        *prev_r = rl < 4 ? rl : 4;
-        (void)last_r;
-    }
+    *prev_r = 0;   // the chunk kernels leave nothing pending
     // the MTP head's KV slots of the same positions: (token of the row, hidden state in front of the row) -> fc ->
     // input norm -> k, v projections -> head norm, RoPE, cache write
     Layer& ML = d->mtp_layer;
