@@ -1044,7 +1044,7 @@ def generate_bench(args):
                      "total_ms": med(lambda x: x.total_time_sec) * 1e3, "steps_per_request": r0.steps,
                      "generated_tokens": generated, "finish": sorted({x.finish_reason for x in runs[-1]}),
                      "prefill_tok_s": B * T / max(1e-9, med(lambda x: x.time_to_first_token_sec)),
-                     "note": "prefill runs 512-row chunks (projections on the M = 512 GEMM, attention four positions per launch, convolution and delta rule a chunk per launch); the reset that starts a request is inside the first-token time"},
+                     "note": "prefill runs 512-row chunks (projections on the M = 512 GEMM, each mixer one launch per chunk); the reset that starts a request is inside the first-token time"},
         "clocks": clocks,
     }
     print(json.dumps(line), flush=True)

@@ -447,8 +447,8 @@ XINFER_EXPORT int xinfer_spec_decoder_set_sampling(xinfer_spec_decoder* d, float
 XINFER_EXPORT int xinfer_spec_decoder_set_top_p(xinfer_spec_decoder* d, float top_p);
 /* Builds the context from a prompt, tokens[batch][T] on the host (every sequence the same length), starting from the
  * empty context of xinfer_spec_decoder_reset(d, 0, seed): positions 0 .. T-2 go through the target in chunks of up to
- * 512 rows over all sequences (the projections of a chunk run as one M = 512 GEMM each, the attention kernels take it
- * four positions at a time, the convolution and the gated delta rule in one launch each), the MTP head's KV slots of those positions are filled, the last prompt
+ * 512 rows over all sequences (the projections of a chunk run as one M = 512 GEMM each, attention, convolution and the
+ * gated delta rule take it in one launch each), the MTP head's KV slots of those positions are filled, the last prompt
  * token becomes the current token; ctx = T - 1 afterwards and xinfer_spec_decoder_step continues from there.  Stands
  * where the reference's chunked prefill does (forward_prefill_chunk, src/targets/qwen3_8/forward.cpp:402-554;
  * prefill_chunk_size = 512, include/xinfer/engine.h:34; engine.cpp:330-398).  Synchronous; one GPU only. */

@@ -188,7 +188,8 @@ __global__ void __launch_bounds__(256) attn_prep_kernel(__half* q_out, __half* k
                                                         const float* q_norm_w, const float* k_norm_w, const int* ctx,
                                                         int rows_per_seq, int hq, int hkv, long long max_seq,
                                                         float eps, float log_theta, int rope_dim, int q_head_stride,
-                                                        const long long* positions, int ctx_base, __half* k_out) {
+                                                        const long long* positions, int ctx_base, __half* k_out,
+                                                        int cache_batch) {
     griddep_prologue();
     __shared__ float red[32];
     __shared__ float vals[256];
@@ -196,12 +197,13 @@ __global__ void __launch_bounds__(256) attn_prep_kernel(__half* q_out, __half* k
     const int slot = blockIdx.y;
     const int d = threadIdx.x;
     const int b = row / rows_per_seq, i = row % rows_per_seq;
+    const int bc = cache_batch > 0 ? b % cache_batch : b;  // the sequence whose cache this entry writes (see attn_decode_ex)
     const long long pos = positions ? positions[row] : static_cast<long long>(ctx ? ctx[b] : ctx_base) + i;
     const bool in_cache = pos >= 0 && pos < max_seq;
     if (slot >= hq + hkv) {  // value head: plain copy into the cache
         const int h = slot - hq - hkv;
         if (in_cache && v_cache && v_in)
-            v_cache[((static_cast<long long>(b) * max_seq + pos) * hkv + h) * 256 + d] =
+            v_cache[((static_cast<long long>(bc) * max_seq + pos) * hkv + h) * 256 + d] =
                 v_in[(static_cast<long long>(row) * hkv + h) * 256 + d];
         return;
     }
@@ -234,7 +236,7 @@ __global__ void __launch_bounds__(256) attn_prep_kernel(__half* q_out, __half* k
     if (is_q) {
         q_out[(static_cast<long long>(row) * hq + h) * 256 + d] = o;
     } else if (k_cache) {
-        if (in_cache) k_cache[((static_cast<long long>(b) * max_seq + pos) * hkv + h) * 256 + d] = o;
+        if (in_cache) k_cache[((static_cast<long long>(bc) * max_seq + pos) * hkv + h) * 256 + d] = o;
     } else if (k_out) {
         k_out[(static_cast<long long>(row) * hkv + h) * 256 + d] = o;
     }
@@ -311,7 +313,7 @@ template <int NT>
 __global__ void __launch_bounds__(kAttnThreads, 2) attn_split_kernel(float* part_o, float* part_ml, const __half* q,
                                                          const __half* k_cache, const __half* v_cache, const int* ctx,
                                                          int rows_per_seq, int hq, int hkv, long long max_seq,
-                                                         float scale, int ctx_base) {
+                                                         float scale, int ctx_base, int cache_batch) {
     griddep_prologue();
     extern __shared__ __align__(16) uint8_t attn_smem_raw[];
     AttnSmem& sm = *reinterpret_cast<AttnSmem*>(attn_smem_raw);
@@ -321,6 +323,7 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_split_kernel(float* part
     const int G = hq / hkv;
     const int nrows = G * rows_per_seq;  // valid query rows, row = g * R + i
     const int ctx_b = ctx ? ctx[b] : ctx_base;  // (null: the stand-alone entry point's host-side start position)
+    const int bc = cache_batch > 0 ? b % cache_batch : b;
     const float scale2 = scale * 1.4426950408889634f;  // exp(x) = exp2(x * log2 e)
     long long total_keys = static_cast<long long>(ctx_b) + rows_per_seq;
     if (total_keys > max_seq) total_keys = max_seq;
@@ -352,7 +355,7 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attn_split_kernel(float* part
             const int r = idx >> 5, seg = idx & 31;
             long long key = key0 + r;
             if (key >= total_keys) key = total_keys - 1;  // clamped rows are masked out below
-            const long long off = ((static_cast<long long>(b) * max_seq + key) * hkv + kvh) * 256 + seg * 8;
+            const long long off = ((static_cast<long long>(bc) * max_seq + key) * hkv + kvh) * 256 + seg * 8;
             cp_async16(&sm.k[buf][r][seg * 8], k_cache + off);
             cp_async16(&sm.v[buf][r][seg * 8], v_cache + off);
         }
@@ -991,10 +994,10 @@ int attn_prep(cudaStream_t s, __half* q_out, __half* k_cache, __half* v_cache, c
 int attn_prep_ex(cudaStream_t s, __half* q_out, __half* k_cache, __half* v_cache, const __half* q_in, const __half* k_in,
                  const __half* v_in, const float* q_norm_w, const float* k_norm_w, const int* ctx, int batch,
                  int rows_per_seq, int hq, int hkv, long long max_seq, float eps, float rope_theta, int rope_dim,
-                 int q_head_stride, const long long* positions, int ctx_base, __half* k_out) {
+                 int q_head_stride, const long long* positions, int ctx_base, __half* k_out, int cache_batch) {
     dim3 grid(batch * rows_per_seq, hq + 2 * hkv);
     launch_pdl(attn_prep_kernel, dim3(grid), dim3(256), 0, s, q_out, k_cache, v_cache, q_in, k_in, v_in, q_norm_w, k_norm_w, ctx,
-               rows_per_seq, hq, hkv, max_seq, eps, logf(rope_theta), rope_dim, q_head_stride, positions, ctx_base, k_out);
+               rows_per_seq, hq, hkv, max_seq, eps, logf(rope_theta), rope_dim, q_head_stride, positions, ctx_base, k_out, cache_batch);
     return XB_LAUNCH_OK();
 }
 
@@ -1011,7 +1014,7 @@ int attn_decode(cudaStream_t s, __half* out, const __half* q, const __half* q_ga
 
 int attn_decode_ex(cudaStream_t s, __half* out, const __half* q, const __half* q_gate, const __half* k_cache,
                    const __half* v_cache, const int* ctx, int batch, int rows_per_seq, int hq, int hkv, long long max_seq,
-                   int nsplit, float* scratch, float scale, int ctx_base, int perm_out) {
+                   int nsplit, float* scratch, float scale, int ctx_base, int perm_out, int cache_batch) {
     if (hq % hkv != 0 || (hq / hkv) * rows_per_seq > kAttnRows) return -2;
     // the shared-memory attribute belongs to the device's context: set it once per device
     static bool configured_dev[64];
@@ -1032,10 +1035,10 @@ int attn_decode_ex(cudaStream_t s, __half* out, const __half* q, const __half* q
     float* part_ml = scratch + static_cast<size_t>(batch) * hkv * nsplit * (kAttnRows * 256);
     dim3 grid(nsplit, hkv, batch);
     switch (((hq / hkv) * rows_per_seq + 7) / 8) {
-        case 1: launch_pdl(attn_split_kernel<1>, dim3(grid), dim3(kAttnThreads), sizeof(AttnSmem), s, part_o, part_ml, q, k_cache, v_cache, ctx, rows_per_seq, hq, hkv, max_seq, scale, ctx_base); break;
-        case 2: launch_pdl(attn_split_kernel<2>, dim3(grid), dim3(kAttnThreads), sizeof(AttnSmem), s, part_o, part_ml, q, k_cache, v_cache, ctx, rows_per_seq, hq, hkv, max_seq, scale, ctx_base); break;
-        case 3: launch_pdl(attn_split_kernel<3>, dim3(grid), dim3(kAttnThreads), sizeof(AttnSmem), s, part_o, part_ml, q, k_cache, v_cache, ctx, rows_per_seq, hq, hkv, max_seq, scale, ctx_base); break;
-        default: launch_pdl(attn_split_kernel<4>, dim3(grid), dim3(kAttnThreads), sizeof(AttnSmem), s, part_o, part_ml, q, k_cache, v_cache, ctx, rows_per_seq, hq, hkv, max_seq, scale, ctx_base); break;
+        case 1: launch_pdl(attn_split_kernel<1>, dim3(grid), dim3(kAttnThreads), sizeof(AttnSmem), s, part_o, part_ml, q, k_cache, v_cache, ctx, rows_per_seq, hq, hkv, max_seq, scale, ctx_base, cache_batch); break;
+        case 2: launch_pdl(attn_split_kernel<2>, dim3(grid), dim3(kAttnThreads), sizeof(AttnSmem), s, part_o, part_ml, q, k_cache, v_cache, ctx, rows_per_seq, hq, hkv, max_seq, scale, ctx_base, cache_batch); break;
+        case 3: launch_pdl(attn_split_kernel<3>, dim3(grid), dim3(kAttnThreads), sizeof(AttnSmem), s, part_o, part_ml, q, k_cache, v_cache, ctx, rows_per_seq, hq, hkv, max_seq, scale, ctx_base, cache_batch); break;
+        default: launch_pdl(attn_split_kernel<4>, dim3(grid), dim3(kAttnThreads), sizeof(AttnSmem), s, part_o, part_ml, q, k_cache, v_cache, ctx, rows_per_seq, hq, hkv, max_seq, scale, ctx_base, cache_batch); break;
     }
     dim3 grid2((hq / hkv) * rows_per_seq, hkv, batch);
     launch_pdl(attn_combine_kernel, dim3(grid2), dim3(256), 0, s, out, part_o, part_ml, q_gate, nsplit, rows_per_seq, hq, hkv,

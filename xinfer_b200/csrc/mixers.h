@@ -29,16 +29,18 @@ int attn_prep(cudaStream_t s, __half* q_out, __half* k_cache, __half* v_cache, c
 int attn_prep_ex(cudaStream_t s, __half* q_out, __half* k_cache, __half* v_cache, const __half* q_in, const __half* k_in,
                  const __half* v_in, const float* q_norm_w, const float* k_norm_w, const int* ctx, int batch,
                  int rows_per_seq, int hq, int hkv, long long max_seq, float eps, float rope_theta, int rope_dim,
-                 int q_head_stride, const long long* positions, int ctx_base, __half* k_out);
+                 int q_head_stride, const long long* positions, int ctx_base, __half* k_out, int cache_batch = 0);
 size_t attn_scratch_bytes(int batch, int hkv, int nsplit);
 // causal GQA attention over the cache (row i of sequence b sees keys below ctx[b] + i + 1), then * sigmoid(gate)
 int attn_decode(cudaStream_t s, __half* out, const __half* q, const __half* q_gate, const __half* k_cache,
                 const __half* v_cache, const int* ctx, int batch, int rows_per_seq, int hq, int hkv, long long max_seq,
                 int nsplit, float* scratch);
-// with an explicit softmax scale, a host-side context length when ctx is null, and no output gate when q_gate is null
+// with an explicit softmax scale, a host-side context length when ctx is null, and no output gate when q_gate is null.
+// cache_batch > 0 (here and in attn_prep_ex): entry e of the `batch` entries works on the cache of sequence
+// e % cache_batch with its own ctx[e], so one launch can take several row groups of every sequence (prefill).
 int attn_decode_ex(cudaStream_t s, __half* out, const __half* q, const __half* q_gate, const __half* k_cache,
                    const __half* v_cache, const int* ctx, int batch, int rows_per_seq, int hq, int hkv, long long max_seq,
-                   int nsplit, float* scratch, float scale, int ctx_base, int perm_out = 0);
+                   int nsplit, float* scratch, float scale, int ctx_base, int perm_out = 0, int cache_batch = 0);
 
 // state [batch][3][channels], pending [batch][8][channels] fp32.  The first min(n_commit[b], prev_rows) pending
 // inputs of the previous call are committed to the state before the new rows are processed (n_commit null:

@@ -100,6 +100,11 @@ __global__ void shift_hidden_chunk_kernel(__half* out, const __half* h_last, con
     out[xb::chunk_row(p, b, batch, Rc) * H + col] =
         p == 0 ? h_last[static_cast<long long>(b) * H + col] : x[xb::chunk_row(p - 1, b, batch, Rc) * H + col];
 }
+// entry e = group * batch + sequence of a chunk that starts at position c0: the keys in front of its first row
+__global__ void chunk_entry_ctx_kernel(int* entry_ctx, int entries, int batch, int c0) {
+    const int e = blockIdx.x * blockDim.x + threadIdx.x;
+    if (e < entries) entry_ctx[e] = c0 + 4 * (e / batch);
+}
 __global__ void take_last_hidden_chunk_kernel(__half* h_last, const __half* x, int batch, int Rc, int H) {
     const long long t = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (t >= static_cast<long long>(batch) * H) return;
@@ -185,6 +190,9 @@ struct xinfer_spec_decoder {
                *qbuf = nullptr, *kbuf = nullptr, *vbuf = nullptr, *mix_out = nullptr, *zbuf = nullptr, *bbuf = nullptr,
                *abuf = nullptr, *cat = nullptr, *hprev = nullptr;
         long long* tokens = nullptr;
+        int* entry_ctx = nullptr;        // context length in front of every (group, sequence) entry of a chunk
+        float* attn_scratch = nullptr;   // split partials of one attention launch over all entries
+        int attn_splits = 1;
     } chunk;
     float top_p = 1.0f;               // < 1: nucleus sampling on both sides of the stochastic rule
     xb::Nucleus* nucleus = nullptr;   // [batch * (k + 1)] nuclei of the verify rows
@@ -651,7 +659,8 @@ int target_pass(Dec* d, cudaStream_t s, int R, const long long* tokens) {
 // ---------------------------------------------------------------------------------------------- prefill chunks
 // A prompt goes through the model in chunks of up to 512 rows (all sequences together), so that the projections see
 // M = hundreds of rows and run on the prefill GEMM.  Between them the attention kernels take the chunk four positions
-// at a time (their own row limit), which the row order of a chunk (chunk_row) makes contiguous blocks; the convolution
+// at a time (their own row limit; the row order of a chunk, chunk_row, makes every such group a contiguous block, and
+// one launch takes all groups of all sequences as separate entries); the convolution
 // and the gated delta rule walk the whole chunk in one launch each (conv1d_chunk, gdn_chunk).  Natural feature
 // order everywhere (the permuted order of the decode step is a property of its 32-row kernel).
 
@@ -667,9 +676,9 @@ int ensure_chunk_bufs(Dec* d, int rows) {
     const size_t wide = mx(hq * 512, ch), mix = mx(mx(hq * 256, hv * 128), H);
     const size_t per_row = 3 * H + F + wide + ch + hq * 256 + 2 * hkv * 256 + mix + hv * 128 + 2 * hv + 2 * H + H;
     const size_t halves = (per_row + 64) * static_cast<size_t>(rows);
-    if (cb.x) { cudaFree(cb.x); cb = Dec::ChunkBufs(); }
+    if (cb.x) { cudaFree(cb.x); cudaFree(cb.attn_scratch); cb = Dec::ChunkBufs(); }
     __half* base = nullptr;
-    if (cudaMalloc(&base, halves * sizeof(__half) + static_cast<size_t>(rows) * sizeof(long long) + 256) != cudaSuccess) {
+    if (cudaMalloc(&base, halves * sizeof(__half) + static_cast<size_t>(rows) * (sizeof(long long) + sizeof(int)) + 256) != cudaSuccess) {
         cudaGetLastError();
         return XINFER_ERR_OUT_OF_MEMORY;
     }
@@ -683,6 +692,19 @@ int ensure_chunk_bufs(Dec* d, int rows) {
     cb.qbuf = take(hq * 256); cb.kbuf = take(hkv * 256); cb.vbuf = take(hkv * 256); cb.mix_out = take(mix);
     cb.zbuf = take(hv * 128); cb.bbuf = take(hv); cb.abuf = take(hv); cb.cat = take(2 * H); cb.hprev = take(H);
     cb.tokens = reinterpret_cast<long long*>(base + ((off + 63) & ~static_cast<size_t>(63)));
+    cb.entry_ctx = reinterpret_cast<int*>(cb.tokens + rows);
+    // one attention launch takes every full group of four positions of every sequence as an entry of its own: enough
+    // entries fill the GPU without splitting the keys, few entries are split as in the step
+    const int entries = (rows + 3) / 4;
+    int ns = (2 * 148 + entries * static_cast<int>(hkv) - 1) / (entries * static_cast<int>(hkv));
+    ns = ns < 1 ? 1 : (ns > d->attn_splits ? d->attn_splits : ns);
+    cb.attn_splits = ns;
+    if (cudaMalloc(&cb.attn_scratch, xb::attn_scratch_bytes(entries, static_cast<int>(hkv), ns)) != cudaSuccess) {
+        cudaGetLastError();
+        cudaFree(base);
+        cb = Dec::ChunkBufs();
+        return XINFER_ERR_OUT_OF_MEMORY;
+    }
     cb.rows = rows;
     return 0;
 }
@@ -709,7 +731,11 @@ int prefill_chunk(Dec* d, cudaStream_t s, const long long* prompt, int64_t T, in
         f.Y = y; f.W_int4 = l.w; f.scales = l.s; f.bias = nullptr; f.N = l.n;
         return f;
     };
+    const int full_groups = Rc / 4;
     gather_prompt_chunk_kernel<<<blocks_for(static_cast<size_t>(M), 128), 128, 0, s>>>(cb.tokens, prompt, B, T, c0, Rc);
+    if (full_groups > 0)
+        chunk_entry_ctx_kernel<<<blocks_for(static_cast<size_t>(full_groups) * B, 128), 128, 0, s>>>(cb.entry_ctx, full_groups * B, B,
+                                                                                                 static_cast<int>(c0));
     NL(xb::embed_rows(s, cb.x, d->embed, cb.tokens, M, H, c.vocab_size));
     NL(xb::rmsnorm_rows(s, cb.normed, H, cb.x, d->layers[0].input_norm, M, H, eps, 0));
     const size_t nl = d->layers.size();
@@ -718,10 +744,19 @@ int prefill_chunk(Dec* d, cudaStream_t s, const long long* prompt, int64_t T, in
         if (L.full) {
             const xinfer_fused_desc fd[3] = {desc(cb.wide, L.q_proj), desc(cb.kbuf, L.k_proj), desc(cb.vbuf, L.v_proj)};
             LIN(xinfer_linear_int4_fused_f16(st, cb.normed, fd, 3, M, H, 128));
-            for (int j = 0; j < groups; ++j) {
-                const int rj = Rc - 4 * j < 4 ? Rc - 4 * j : 4;
-                const size_t r0 = static_cast<size_t>(j) * B * 4;
-                const int pos0 = static_cast<int>(c0) + 4 * j;
+            // every full group of four positions of every sequence is one entry (rows [entry][4], its own context length,
+            // the cache of sequence entry % B): one launch each for the prologue, the split attention and the combine;
+            // a last short group goes through the same kernels on its own
+            if (full_groups > 0) {
+                NL(xb::attn_prep_ex(s, cb.qbuf, L.k_cache, L.v_cache, cb.wide, cb.kbuf, cb.vbuf, L.q_norm, L.k_norm, cb.entry_ctx,
+                                    full_groups * B, 4, hq, hkv, d->max_seq, eps, c.rope_theta, c.rope_dim, 512, nullptr, 0, nullptr, B));
+                NL(xb::attn_decode_ex(s, cb.mix_out, cb.qbuf, cb.wide, L.k_cache, L.v_cache, cb.entry_ctx, full_groups * B, 4, hq, hkv,
+                                      d->max_seq, cb.attn_splits, cb.attn_scratch, 1.0f / sqrtf(256.0f), 0, 0, B));
+            }
+            if (full_groups < groups) {
+                const int rj = Rc - 4 * full_groups;
+                const size_t r0 = static_cast<size_t>(full_groups) * B * 4;
+                const int pos0 = static_cast<int>(c0) + 4 * full_groups;
                 NL(xb::attn_prep_ex(s, cb.qbuf + r0 * hq * 256, L.k_cache, L.v_cache, cb.wide + r0 * hq * 512, cb.kbuf + r0 * hkv * 256,
                                     cb.vbuf + r0 * hkv * 256, L.q_norm, L.k_norm, nullptr, B, rj, hq, hkv, d->max_seq, eps,
                                     c.rope_theta, c.rope_dim, 512, nullptr, pos0, nullptr));
@@ -756,12 +791,14 @@ int prefill_chunk(Dec* d, cudaStream_t s, const long long* prompt, int64_t T, in
     NL(xb::rmsnorm_rows(s, cb.normed, H, cb.mix_out, ML.input_norm, M, H, eps, 0));
     const xinfer_fused_desc kv[2] = {desc(cb.kbuf, ML.k_proj), desc(cb.vbuf, ML.v_proj)};
     LIN(xinfer_linear_int4_fused_f16(st, cb.normed, kv, 2, M, H, 128));
-    for (int j = 0; j < groups; ++j) {
-        const int rj = Rc - 4 * j < 4 ? Rc - 4 * j : 4;
-        const size_t r0 = static_cast<size_t>(j) * B * 4;
+    if (full_groups > 0)
+        NL(xb::attn_prep_ex(s, cb.qbuf, ML.k_cache, ML.v_cache, cb.wide, cb.kbuf, cb.vbuf, ML.q_norm, ML.k_norm, cb.entry_ctx,
+                            full_groups * B, 4, 0, hkv, d->max_seq, eps, c.rope_theta, c.rope_dim, 512, nullptr, 0, nullptr, B));
+    if (full_groups < groups) {
+        const size_t r0 = static_cast<size_t>(full_groups) * B * 4;
         NL(xb::attn_prep_ex(s, cb.qbuf, ML.k_cache, ML.v_cache, cb.wide, cb.kbuf + r0 * hkv * 256, cb.vbuf + r0 * hkv * 256, ML.q_norm,
-                            ML.k_norm, nullptr, B, rj, 0, hkv, d->max_seq, eps, c.rope_theta, c.rope_dim, 512, nullptr,
-                            static_cast<int>(c0) + 4 * j, nullptr));
+                            ML.k_norm, nullptr, B, Rc - 4 * full_groups, 0, hkv, d->max_seq, eps, c.rope_theta, c.rope_dim, 512,
+                            nullptr, static_cast<int>(c0) + 4 * full_groups, nullptr));
     }
     take_last_hidden_chunk_kernel<<<blocks_for(static_cast<size_t>(B) * H, 256), 256, 0, s>>>(d->h_last, cb.x, B, Rc, H);
     CKCUDA(cudaGetLastError());
@@ -915,7 +952,7 @@ void xinfer_spec_decoder_destroy(xinfer_spec_decoder* d) {
     if (d->graph) cudaGraphDestroy(d->graph);
     if (d->plan) xb::tc_plan_delete(d->plan);  // the recorded plan points into this decoder's weights
     if (d->arena) xinfer_arena_destroy(d->arena);
-    if (d->chunk.x) cudaFree(d->chunk.x);
+    if (d->chunk.x) { cudaFree(d->chunk.x); cudaFree(d->chunk.attn_scratch); }
     if (d->h_emitted) cudaFreeHost(d->h_emitted);
     if (d->h_emitted_n) cudaFreeHost(d->h_emitted_n);
     delete d;
