@@ -696,7 +696,9 @@ int ensure_chunk_bufs(Dec* d, int rows) {
     // one attention launch takes every full group of four positions of every sequence as an entry of its own: enough
     // entries fill the GPU without splitting the keys, few entries are split as in the step
     const int entries = (rows + 3) / 4;
-    int ns = (2 * 148 + entries * static_cast<int>(hkv) - 1) / (entries * static_cast<int>(hkv));
+    int sms = 148;
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, d->device);
+    int ns = (2 * sms + entries * static_cast<int>(hkv) - 1) / (entries * static_cast<int>(hkv));
     ns = ns < 1 ? 1 : (ns > d->attn_splits ? d->attn_splits : ns);
     cb.attn_splits = ns;
     if (cudaMalloc(&cb.attn_scratch, xb::attn_scratch_bytes(entries, static_cast<int>(hkv), ns)) != cudaSuccess) {
