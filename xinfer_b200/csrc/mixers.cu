@@ -768,31 +768,45 @@ __global__ void __launch_bounds__(512, 2) gdn_spec_kernel(__half* out, const __h
 }
 
 // ------------------------------------------------------------------------------- the same two mixers over a prompt chunk
-// Prefill keeps every row, so there is nothing to replay or to hold back: one launch walks all `rc` positions of a
-// chunk with the state in registers and writes the state back once (the step kernels above would need rc / 4 launches,
-// each re-reading and re-writing the state).  Rows are found through chunk_row (the chunk's group-by-group row
+// Prefill keeps every row, so there is nothing to replay or to hold back: the delta rule walks all `rc` positions of a
+// chunk in one launch with the state in registers and writes the state back once (the step kernels above would need
+// rc / 4 launches, each re-reading and re-writing the state).  Rows are found through chunk_row (the chunk's group-by-group row
 // order).  Per token the arithmetic is the step kernels', operation by operation, so the results are bit-identical.
-__global__ void conv1d_chunk_kernel(__half* out, const __half* in, const float* conv_w, float* state, int rc, int channels) {
+// The convolution has no recurrence on its outputs (y_p needs the inputs p-3 .. p only), so every (position, channel)
+// is a thread of its own; inputs in front of the chunk come from the state.  A second, tiny launch then moves the
+// chunk's last three inputs into the state (it must not run while the first one still reads the old state).
+__global__ void conv1d_chunk_kernel(__half* out, const __half* in, const float* conv_w, const float* state, int rc, int channels) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    const int b = blockIdx.y, batch = gridDim.y, p = blockIdx.z;
+    if (c >= channels) return;
+    const float* st = state + static_cast<long long>(b) * 3 * channels;
+    float x[4];
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+        const int q = p - 3 + t;   // input position; negative: the state's slot 3 + q
+        x[t] = q >= 0 ? __half2float(in[chunk_row(q, b, batch, rc) * channels + c]) : st[(3 + q) * channels + c];
+    }
+    const float w0 = conv_w[c * 4], w1 = conv_w[c * 4 + 1], w2 = conv_w[c * 4 + 2], w3 = conv_w[c * 4 + 3];
+    const float sum = w0 * x[0] + w1 * x[1] + w2 * x[2] + w3 * x[3];
+    out[chunk_row(p, b, batch, rc) * channels + c] = __float2half_rn(sum / (1.0f + expf(-sum)));
+}
+__global__ void conv1d_chunk_state_kernel(const __half* in, float* state, int rc, int channels) {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const int c = blockIdx.x * blockDim.x + threadIdx.x;
     const int b = blockIdx.y, batch = gridDim.y;
     if (c >= channels) return;
     float* st = state + static_cast<long long>(b) * 3 * channels;
-    float s0 = st[c], s1 = st[channels + c], s2 = st[2 * channels + c];
-    const float w0 = conv_w[c * 4], w1 = conv_w[c * 4 + 1], w2 = conv_w[c * 4 + 2], w3 = conv_w[c * 4 + 3];
-    for (int p = 0; p < rc; ++p) {
-        const long long row = chunk_row(p, b, batch, rc);
-        const float x = __half2float(in[row * channels + c]);
-        const float sum = w0 * s0 + w1 * s1 + w2 * s2 + w3 * x;
-        out[row * channels + c] = __float2half_rn(sum / (1.0f + expf(-sum)));
-        s0 = s1;
-        s1 = s2;
-        s2 = x;
+    float s[3];
+#pragma unroll
+    for (int t = 0; t < 3; ++t) {
+        const int q = rc - 3 + t;   // the new slot t holds the input at position rc - 3 + t
+        s[t] = q >= 0 ? __half2float(in[chunk_row(q, b, batch, rc) * channels + c]) : st[(3 + q) * channels + c];
     }
-    st[c] = s0;
-    st[channels + c] = s1;
-    st[2 * channels + c] = s2;
+#pragma unroll
+    for (int t = 0; t < 3; ++t) st[t * channels + c] = s[t];
 }
 
 __global__ void __launch_bounds__(512, 2) gdn_chunk_kernel(__half* out, const __half* qkv, const __half* z,
@@ -1065,8 +1079,11 @@ int gdn_spec(cudaStream_t s, __half* out, const __half* qkv, const __half* z, co
 
 int conv1d_chunk(cudaStream_t s, __half* out, const __half* in, const float* conv_w, float* state, int batch, int rc,
                  int channels) {
-    dim3 grid((channels + 255) / 256, batch);
-    launch_pdl(conv1d_chunk_kernel, dim3(grid), dim3(256), 0, s, out, in, conv_w, state, rc, channels);
+    if (rc <= 0) return 0;
+    dim3 grid((channels + 255) / 256, batch, rc);
+    launch_pdl(conv1d_chunk_kernel, dim3(grid), dim3(256), 0, s, out, in, conv_w, static_cast<const float*>(state), rc, channels);
+    dim3 grid2((channels + 255) / 256, batch);
+    launch_pdl(conv1d_chunk_state_kernel, dim3(grid2), dim3(256), 0, s, in, state, rc, channels);
     return XB_LAUNCH_OK();
 }
 
