@@ -816,7 +816,8 @@ __global__ void __launch_bounds__(512, 2) gdn_chunk_kernel(__half* out, const __
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     __shared__ __align__(16) float sh_q[8][128], sh_k[8][128];
-    __shared__ float sh_beta[8], sh_eg[8], red[2][16];
+    __shared__ float sh_v[8][128], sh_z[8][128];
+    __shared__ float sh_beta[8], sh_eg[8], red[2][8][4];
     __shared__ float part_sum[2][4][128], attn_all[8][4][128];
     const int h = blockIdx.x, b = blockIdx.y, batch = gridDim.y;
     const int j = threadIdx.x & 127, part = threadIdx.x >> 7;
@@ -831,27 +832,43 @@ __global__ void __launch_bounds__(512, 2) gdn_chunk_kernel(__half* out, const __
     for (int i = 0; i < 32; ++i) col[i] = S[(i0 + i) * 128 + j];
     const float exp_a_log = expf(A_log[h]);
     const float dtb = dt_bias[h];
+    const float nw = norm_w[j];
 
+    // Blocks of eight positions.  With one sequence per GPU a chunk is 512 sequential tokens on 48 SMs, so what counts
+    // is the latency of a token: every global load of a block (q, k, v, z of its eight tokens; thread group `part`
+    // takes tokens part and part + 4) is issued at the top of the block and staged in shared memory, and the norms of
+    // all eight tokens share one barrier, so that the recurrence itself touches registers and shared memory only.
     for (int p0 = 0; p0 < rc; p0 += 8) {
         const int nb = rc - p0 < 8 ? rc - p0 : 8;
-        // ---- phase 0: per-token quantities that do not depend on the state (token tt handled by thread group tt % 4)
-        for (int t0 = 0; t0 < nb; t0 += 4) {
-            const int tt = t0 + part;
-            float raw_q = 0.f, raw_k = 0.f;
+        // ---- phase 0: per-token quantities that do not depend on the state
+        float raw_q[2] = {0.f, 0.f}, raw_k[2] = {0.f, 0.f};
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const int tt = part + 4 * u;
             if (tt < nb) {
-                const __half* cur = qkv + chunk_row(p0 + tt, b, batch, rc) * channels;
-                raw_q = __half2float(cur[h_k * 128 + j]);
-                raw_k = __half2float(cur[hk * 128 + h_k * 128 + j]);
+                const long long row = chunk_row(p0 + tt, b, batch, rc);
+                const __half* cur = qkv + row * channels;
+                raw_q[u] = __half2float(cur[h_k * 128 + j]);
+                raw_k[u] = __half2float(cur[hk * 128 + h_k * 128 + j]);
+                sh_v[tt][j] = __half2float(cur[2 * hk * 128 + h * 128 + j]);
+                sh_z[tt][j] = __half2float(z[row * value_dim + h * 128 + j]);
             }
-            const float wq = warp_sum(raw_q * raw_q), wk = warp_sum(raw_k * raw_k);
-            __syncthreads();
-            if (lane == 0) { red[0][part * 4 + wig] = wq; red[1][part * 4 + wig] = wk; }
-            __syncthreads();
+        }
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const int tt = part + 4 * u;
+            const float wq = warp_sum(raw_q[u] * raw_q[u]), wk = warp_sum(raw_k[u] * raw_k[u]);
+            if (lane == 0) { red[0][tt][wig] = wq; red[1][tt][wig] = wk; }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const int tt = part + 4 * u;
             if (tt < nb) {
-                const float q_sq = ((red[0][part * 4] + red[0][part * 4 + 1]) + red[0][part * 4 + 2]) + red[0][part * 4 + 3];
-                const float k_sq = ((red[1][part * 4] + red[1][part * 4 + 1]) + red[1][part * 4 + 2]) + red[1][part * 4 + 3];
-                sh_q[tt][j] = (raw_q * (1.0f / sqrtf(q_sq + 1e-6f))) * 0.08838834764f;
-                sh_k[tt][j] = raw_k * (1.0f / sqrtf(k_sq + 1e-6f));
+                const float q_sq = ((red[0][tt][0] + red[0][tt][1]) + red[0][tt][2]) + red[0][tt][3];
+                const float k_sq = ((red[1][tt][0] + red[1][tt][1]) + red[1][tt][2]) + red[1][tt][3];
+                sh_q[tt][j] = (raw_q[u] * (1.0f / sqrtf(q_sq + 1e-6f))) * 0.08838834764f;
+                sh_k[tt][j] = raw_k[u] * (1.0f / sqrtf(k_sq + 1e-6f));
                 if (j == 0) {
                     const long long row = chunk_row(p0 + tt, b, batch, rc);
                     const float b_val = __half2float(bb[row * hv + h]);
@@ -866,8 +883,7 @@ __global__ void __launch_bounds__(512, 2) gdn_chunk_kernel(__half* out, const __
 
         // ---- phase 1: the recurrence
         for (int t = 0; t < nb; ++t) {
-            const long long row = chunk_row(p0 + t, b, batch, rc);
-            const float v = __half2float(qkv[row * channels + 2 * hk * 128 + h * 128 + j]);
+            const float v = sh_v[t][j];
             const float eg = sh_eg[t];
             float kv_mem = 0.f;
             const float4* k4 = reinterpret_cast<const float4*>(&sh_k[t][i0]);
@@ -903,22 +919,26 @@ __global__ void __launch_bounds__(512, 2) gdn_chunk_kernel(__half* out, const __
         }
         __syncthreads();
 
-        // ---- phase 2: gated RMSNorm of every token's output (token tt handled by thread group tt % 4)
-        for (int t0 = 0; t0 < nb; t0 += 4) {
-            const int tt = t0 + part;
-            float attn = 0.f;
-            if (tt < nb) attn = ((attn_all[tt][0][j] + attn_all[tt][1][j]) + attn_all[tt][2][j]) + attn_all[tt][3][j];
-            const float wsq = warp_sum(attn * attn);
-            __syncthreads();
-            if (lane == 0) red[0][part * 4 + wig] = wsq;
-            __syncthreads();
+        // ---- phase 2: gated RMSNorm of every token's output
+        float attn2[2];
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const int tt = part + 4 * u;
+            attn2[u] = tt < nb ? ((attn_all[tt][0][j] + attn_all[tt][1][j]) + attn_all[tt][2][j]) + attn_all[tt][3][j] : 0.f;
+            const float wsq = warp_sum(attn2[u] * attn2[u]);
+            if (lane == 0) red[0][tt][wig] = wsq;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const int tt = part + 4 * u;
             if (tt < nb) {
-                const float sq = ((red[0][part * 4] + red[0][part * 4 + 1]) + red[0][part * 4 + 2]) + red[0][part * 4 + 3];
+                const float sq = ((red[0][tt][0] + red[0][tt][1]) + red[0][tt][2]) + red[0][tt][3];
                 const float inv_std = 1.0f / sqrtf(sq / 128.0f + 1e-6f);
                 const long long row = chunk_row(p0 + tt, b, batch, rc);
-                const float zv = __half2float(z[row * value_dim + h * 128 + j]);
+                const float zv = sh_z[tt][j];
                 const float silu_z = zv / (1.0f + expf(-zv));
-                out[row * value_dim + h * 128 + j] = __float2half_rn(attn * inv_std * norm_w[j] * silu_z);
+                out[row * value_dim + h * 128 + j] = __float2half_rn(attn2[u] * inv_std * nw * silu_z);
             }
         }
         __syncthreads();
